@@ -1,0 +1,243 @@
+/*
+ * fth_b200.h — C ABI of the B200 (sm_100a) quantized-linear backend for Feather.
+ *
+ * Every entry point takes plain pointers and sizes, launches hand-written CUDA kernels on the caller's
+ * stream and returns an int status (0 = ok, negative = FTH_B200_ERR_*).  Unless a comment says otherwise
+ * an entry point never allocates, never synchronises and never reads device memory back, so it is legal
+ * inside CUDA-graph capture (the reference's CUDA INT8 kernels are not: src/kernel/cuda/int8.cu:287-367).
+ * There is no CPU fallback anywhere below this header: a shape or contract the kernels do not implement
+ * returns FTH_B200_ERR_UNSUPPORTED so that the caller (Feather's KernelBase::Supports(),
+ * include/core/kernel.h:158) can answer StatusCode::kUnsupported and let the next CUDA candidate try.
+ *
+ * Each declaration names the reference interface it replaces (paths are relative to the Feather tree).
+ */
+#ifndef FTH_B200_H
+#define FTH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque CUDA stream handle (cudaStream_t). */
+typedef void* fth_b200_stream_t;
+
+/* Element types; the values are feather::DataType's (include/util/types.h:32-47). */
+enum {
+    FTH_B200_INT8 = 1,
+    FTH_B200_FP16 = 3,
+    FTH_B200_FP32 = 4,
+    FTH_B200_INT32 = 5,
+    FTH_B200_BF16 = 11,
+    FTH_B200_FP8E4M3 = 12,
+    FTH_B200_FP8E5M2 = 13
+};
+
+/* Status codes. */
+enum {
+    FTH_B200_OK = 0,
+    FTH_B200_ERR_INVALID = -1,     /* null pointer, bad size, non-finite scale: the reference kernels return -1 */
+    FTH_B200_ERR_UNSUPPORTED = -2, /* valid request this backend declines (→ StatusCode::kUnsupported) */
+    FTH_B200_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed */
+    FTH_B200_ERR_OVERFLOW = -4,    /* K·255·255 + max|bias| may leave int32 (int8_kernel_utils.h:99-114) */
+    FTH_B200_ERR_TIMEOUT = -5      /* a bounded device-side wait gave up (read from a status word) */
+};
+
+/* Operator flavour: decides how bias / alpha / beta enter (FC and MatMul: alpha = beta = 1). */
+enum { FTH_B200_OP_FC = 0, FTH_B200_OP_MATMUL = 1, FTH_B200_OP_GEMM = 2 };
+
+/* Bias layout, the encoding of src/kernel/cuda/linear_kernels.cuh:40-42. */
+enum { FTH_B200_BIAS_NONE = 0, FTH_B200_BIAS_VECTOR = 1, FTH_B200_BIAS_MATRIX = 2 };
+
+/* Kernel family selector for `variant` (0 lets the library split by shape). */
+enum {
+    FTH_B200_VARIANT_AUTO = 0,
+    FTH_B200_VARIANT_SIMT = 1,   /* ragged-shape CUDA-core tile kernel (any M, K, N, any alignment) */
+    FTH_B200_VARIANT_SKINNY = 2, /* weight-streaming GEMV / skinny GEMM, M <= 16 */
+    FTH_B200_VARIANT_TCGEN05 = 3 /* tcgen05 MMA, TMEM accumulators, TMA-fed shared-memory tiles */
+};
+
+int fth_b200_abi_version(void);
+/* Name of the kernel family the last call on this host thread launched ("skinny", "tcgen05", "simt", …);
+ * the counterpart of LastCudaFp8MatmulBackend() (src/kernel/cuda/runtime.h:141-143). */
+const char* fth_b200_last_variant(void);
+/* Kernels launched by this library on this host thread since the last reset. */
+int64_t fth_b200_launch_count(void);
+void fth_b200_reset_launch_count(void);
+
+/* -------------------------------------------------------------------------------------------------
+ * FP8 (E4M3 / E5M2) FC, MatMul, Gemm.
+ * Replaces RunFp8Fc / RunFp8MatMul / RunFp8Gemm → LaunchFp8MatMulKernelCuda
+ * (src/kernel/cuda/fc.cu:91-142, matmul.cu:230-272, gemm.cu:125-183, linear_kernels.cuh:815-837) and
+ * follows the numerical contract of the Common kernels (src/kernel/common/fc.cc:48-76, gemm.cc:62-99):
+ *
+ *   acc = Σ_k decode(a[m,k]) · decode(w[k,n])              FP32 accumulation
+ *   y   = alpha · acc · a_scale · w_scale(n) + beta · decode(bias) · bias_scale
+ *   out = encode_saturating_rne(y / out_scale)             (include/util/fp8.h:81-172)
+ *
+ * a [M,K] row-major; w [K,N] row-major, or [N,K] when trans_b; out [M,N] with row stride ldo elements.
+ * a_dtype may be BF16 or FP32 instead of `dtype`: the activation is then first quantised exactly as the
+ * reference's Cast node would (encode(x / a_scale), src/kernel/common/cast.cc:103-110).  out_dtype may be
+ * BF16 or FP32: the FP8 result is then decoded again (decode(out)·out_scale) as the Cast node after the
+ * MatMul would; both rounding points are kept, so the fused call equals Cast → MatMul → Cast.
+ * w_channel_scales (device, N floats) is an extension the reference cannot express (its FP8 tensors are
+ * per-tensor only, src/kernel/fp8_host.h:150-157); when non-null it replaces w_scale.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t dtype;     /* FTH_B200_FP8E4M3 or FTH_B200_FP8E5M2: weight, bias and FP8 output format */
+    int32_t op;        /* FTH_B200_OP_* */
+    int64_t m, k, n;
+    int32_t trans_b;   /* 0: w is [K,N]; 1: w is [N,K] (GemmParam::trans_b) */
+    int32_t a_dtype;   /* 0 or dtype: FP8 activations; FTH_B200_BF16 / FTH_B200_FP32: fused Cast prologue */
+    int32_t out_dtype; /* 0 or dtype: FP8 output; FTH_B200_BF16 / FTH_B200_FP32: fused Cast epilogue */
+    int32_t bias_mode; /* FTH_B200_BIAS_*; bias is FP8 of `dtype` */
+    const void* a;
+    const void* w;
+    const void* bias;
+    void* out;
+    int64_t ldo;       /* output row stride in elements; 0 means n */
+    float a_scale, w_scale, bias_scale, out_scale;
+    const float* w_channel_scales;
+    float alpha, beta;
+    int32_t weight_clean; /* 1: caller scanned w with fth_b200_fp8_count_specials and found no NaN/Inf code */
+    int32_t variant;      /* FTH_B200_VARIANT_* */
+} fth_b200_fp8_linear_desc;
+
+int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t stream);
+/* Capability check only (what Supports() calls): 0 if fth_b200_fp8_linear would run this descriptor. */
+int fth_b200_fp8_linear_supported(const fth_b200_fp8_linear_desc* desc);
+
+/* Counts NaN / Inf codes in an FP8 buffer into *count (device int32, zeroed by the call).  Used once in
+ * Prepare() on immutable weights so the streaming kernels may take the branch-free decode. */
+int fth_b200_fp8_count_specials(int32_t dtype, const void* data, int64_t count, int32_t* device_count,
+                                fth_b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * INT8 FC, MatMul, Gemm (bit-exact with the Common kernels).
+ * Replaces RunCudaInt8Linear / RunCudaInt8MatMul → Int8LinearKernel / Int8MatMulKernel
+ * (src/kernel/cuda/int8.cu:112-208, 313-368); contract of src/kernel/common/fc.cc:105-159,
+ * gemm.cc:136-198, matmul.cc:156-261 and int8_kernel_utils.h:159-179:
+ *
+ *   acc  = Σ_k (a - a_zp)(w - w_zp[n])                      int32 (the host rejects shapes that could overflow)
+ *   FC / MatMul: real = double(acc + bias) · (double(a_scale) · w_scale[n])
+ *   Gemm:        real = (double(alpha)·acc + double(beta)·bias) · (double(a_scale) · w_scale[n])
+ *   out  = clamp(round_half_away(real / double(out_scale) + out_zp), -128, 127)
+ *
+ * w_scales / w_zps are DEVICE arrays with w_params entries: 1 (per tensor) or n (per output channel);
+ * w_zps may be null (all zero).  bias is int32 [N] or [M,N].
+ * a_dtype FP32 fuses QuantizeLinear (quantization.h:94-99) in front, out_dtype FP32 fuses
+ * DequantizeLinear ((q - out_zp)·out_scale) behind; both keep the int8 rounding point.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t op;
+    int64_t m, k, n;
+    int32_t trans_b;
+    int32_t a_dtype;   /* 0 / FTH_B200_INT8, or FTH_B200_FP32 (fused QuantizeLinear) */
+    int32_t out_dtype; /* 0 / FTH_B200_INT8, or FTH_B200_FP32 (fused DequantizeLinear) */
+    int32_t bias_mode;
+    const void* a;
+    const int8_t* w;
+    const int32_t* bias;
+    void* out;
+    int64_t ldo;
+    float a_scale;
+    int32_t a_zp;
+    const float* w_scales;
+    const int32_t* w_zps;
+    int64_t w_params;
+    int32_t w_zp_max_abs; /* host-known bound on |w_zp| (0 when symmetric); used by the overflow pre-check */
+    float out_scale;
+    int32_t out_zp;
+    float alpha, beta;
+    int64_t bias_max_abs; /* host-known bound on |bias| for the overflow pre-check */
+    int32_t variant;
+} fth_b200_int8_linear_desc;
+
+int fth_b200_int8_linear(const fth_b200_int8_linear_desc* desc, fth_b200_stream_t stream);
+int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* desc);
+
+/* -------------------------------------------------------------------------------------------------
+ * INT8 Conv2D, NCHW activations, OIHW weights, int32 bias, optional fused INT8 ReLU table.
+ * Replaces RunCudaInt8Conv2D → Int8Conv2DKernel (src/kernel/cuda/int8.cu:217-285, 370-506); contract of
+ * src/kernel/common/conv2d.cc:481-581 (padded taps contribute nothing).  When relu_lut is non-null the
+ * 256-entry table of the INT8 ReLU node (src/kernel/common/int8_standard.cc:114-128) is applied to the
+ * requantised int8 value, i.e. Conv2D → ReLU in one launch with both rounding points kept.
+ * `workspace` (device, fth_b200_int8_conv2d_workspace_bytes) is used by the implicit-GEMM path for the
+ * channels-last copy of the input and the repacked weights; it may be null for VARIANT_SIMT.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct {
+    int64_t batch, ic, ih, iw, oc, kh, kw;
+    int32_t stride_h, stride_w, pad_h, pad_w, dilation_h, dilation_w, group;
+    const int8_t* x;
+    const int8_t* w;
+    const int32_t* bias; /* [OC] or null */
+    int8_t* out;
+    float x_scale;
+    int32_t x_zp;
+    const float* w_scales; /* device, w_params entries (1 or OC) */
+    const int32_t* w_zps;  /* device or null */
+    int64_t w_params;
+    int32_t w_zp_max_abs;
+    float out_scale;
+    int32_t out_zp;
+    const int8_t* relu_lut; /* device, 256 entries indexed by q + 128, or null */
+    int64_t bias_max_abs;
+    void* workspace;
+    size_t workspace_bytes;
+    int32_t weights_packed; /* 1: workspace already holds the packed weights of a previous call (same w) */
+    int32_t variant;
+} fth_b200_int8_conv2d_desc;
+
+int fth_b200_int8_conv2d(const fth_b200_int8_conv2d_desc* desc, fth_b200_stream_t stream);
+int fth_b200_int8_conv2d_supported(const fth_b200_int8_conv2d_desc* desc);
+size_t fth_b200_int8_conv2d_workspace_bytes(const fth_b200_int8_conv2d_desc* desc);
+
+/* Builds the 256-entry INT8 ReLU table on the host (src/kernel/common/int8_standard.cc:114-128). */
+int fth_b200_int8_relu_table(float in_scale, int32_t in_zp, float out_scale, int32_t out_zp, int8_t* lut256);
+/* Standalone INT8 ReLU node through a device table (RunUnaryInt8Lookup, int8_standard.cc:148-176). */
+int fth_b200_int8_lookup(const int8_t* x, int8_t* out, int64_t count, const int8_t* device_lut256,
+                         fth_b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * QuantizeLinear / DequantizeLinear.  The reference has COMMON kernels only
+ * (src/kernel/common/quantize_linear.cc:24-42, dequantize_linear.cc:25-36), so a CUDA plan with
+ * KernelFallbackPolicy::kRequireRequested cannot be built without these.  Contract:
+ * src/kernel/common/quantize_linear_utils.h:236-341.  x is [rows, channels]; scales / zps are DEVICE
+ * arrays with `params` entries: 1 (per tensor) or `channels` (per channel on the last axis).
+ * ------------------------------------------------------------------------------------------------- */
+int fth_b200_quantize_linear(int32_t x_dtype, const void* x, const float* scales, const int32_t* zps,
+                             int64_t params, int8_t* out, int64_t rows, int64_t channels,
+                             fth_b200_stream_t stream);
+int fth_b200_dequantize_linear(const int8_t* x, const float* scales, const int32_t* zps, int64_t params, void* out,
+                               int32_t to_dtype, int64_t rows, int64_t channels, fth_b200_stream_t stream);
+
+/* Cast among FP32 / FP16 / BF16 / FP8 with per-tensor FP8 scales.
+ * Replaces CastFloatingKernelCuda (src/kernel/cuda/cast.cu:54-93); contract src/kernel/common/cast.cc:62-126. */
+int fth_b200_cast(int32_t in_dtype, const void* x, float in_scale, int32_t out_dtype, void* out, float out_scale,
+                  int64_t count, fth_b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * Host-buffer plans: the shape of KernelBase::Prepare() / compute() (include/core/kernel.h:162-163) for a
+ * linear node whose weight is immutable.  create() uploads weight, scales and bias once (it allocates and
+ * synchronises — never call it during capture); run() copies the activation from host memory, launches,
+ * and copies the result back, all on `stream`, then waits for the stream.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct fth_b200_plan fth_b200_plan;
+
+/* Pointers in `host_desc` are HOST pointers (a and out may be null here; they are given to run()). */
+int fth_b200_plan_create_fp8_linear(const fth_b200_fp8_linear_desc* host_desc, fth_b200_plan** plan);
+int fth_b200_plan_create_int8_linear(const fth_b200_int8_linear_desc* host_desc, fth_b200_plan** plan);
+int fth_b200_plan_create_int8_conv2d(const fth_b200_int8_conv2d_desc* host_desc, fth_b200_plan** plan);
+int fth_b200_plan_run(fth_b200_plan* plan, const void* host_in, void* host_out, fth_b200_stream_t stream);
+/* Device-resident variant of run(): no copies, no wait. */
+int fth_b200_plan_launch(fth_b200_plan* plan, const void* device_in, void* device_out, fth_b200_stream_t stream);
+int64_t fth_b200_plan_input_bytes(const fth_b200_plan* plan);
+int64_t fth_b200_plan_output_bytes(const fth_b200_plan* plan);
+void fth_b200_plan_destroy(fth_b200_plan* plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTH_B200_H */

@@ -1,0 +1,174 @@
+// C ABI entry points for the linear ops: validation (the contract checks of the reference kernels),
+// shape split between kernel families, launch bookkeeping.
+#include <cmath>
+
+#include "common.cuh"
+#include "linear_internal.h"
+
+namespace fth {
+
+namespace {
+thread_local const char* g_last_variant = "none";
+thread_local int64_t g_launches = 0;
+}  // namespace
+
+void NoteLaunch(const char* variant, int64_t launches) {
+    g_last_variant = variant;
+    g_launches += launches;
+}
+
+int CheckLaunch() { return cudaPeekAtLastError() == cudaSuccess ? FTH_B200_OK : FTH_B200_ERR_CUDA; }
+
+namespace {
+
+bool ValidScale(float s) { return std::isfinite(s) && s > 0.0f; }  // fp8_host.h:150-157, quantization.h:64-66
+bool IsFp8(int dtype) { return dtype == FTH_B200_FP8E4M3 || dtype == FTH_B200_FP8E5M2; }
+
+int ValidateFp8(const fth_b200_fp8_linear_desc* d) {
+    if (d == nullptr || !IsFp8(d->dtype)) return FTH_B200_ERR_INVALID;
+    if (d->m <= 0 || d->k <= 0 || d->n <= 0 || !d->a || !d->w || !d->out) return FTH_B200_ERR_INVALID;
+    if (d->op < FTH_B200_OP_FC || d->op > FTH_B200_OP_GEMM) return FTH_B200_ERR_INVALID;
+    if (!ValidScale(d->a_scale) || !ValidScale(d->out_scale)) return FTH_B200_ERR_INVALID;
+    if (d->w_channel_scales == nullptr && !ValidScale(d->w_scale)) return FTH_B200_ERR_INVALID;
+    if (d->bias_mode < FTH_B200_BIAS_NONE || d->bias_mode > FTH_B200_BIAS_MATRIX) return FTH_B200_ERR_INVALID;
+    if (d->bias_mode != FTH_B200_BIAS_NONE && (!d->bias || !ValidScale(d->bias_scale))) return FTH_B200_ERR_INVALID;
+    if (d->op == FTH_B200_OP_MATMUL && d->bias_mode != FTH_B200_BIAS_NONE) return FTH_B200_ERR_INVALID;
+    if (d->op == FTH_B200_OP_GEMM && (!std::isfinite(d->alpha) || !std::isfinite(d->beta))) return FTH_B200_ERR_INVALID;
+    if (d->trans_b && d->op != FTH_B200_OP_GEMM) return FTH_B200_ERR_INVALID;  // only GemmParam has trans_b
+    if (d->a_dtype != 0 && d->a_dtype != d->dtype && d->a_dtype != FTH_B200_BF16 && d->a_dtype != FTH_B200_FP32) return FTH_B200_ERR_UNSUPPORTED;
+    if (d->out_dtype != 0 && d->out_dtype != d->dtype && d->out_dtype != FTH_B200_BF16 && d->out_dtype != FTH_B200_FP32) return FTH_B200_ERR_UNSUPPORTED;
+    if (d->ldo != 0 && d->ldo < d->n) return FTH_B200_ERR_INVALID;
+    if (d->m > (int64_t{1} << 31) || d->n > (int64_t{1} << 31) || d->k > (int64_t{1} << 31)) return FTH_B200_ERR_UNSUPPORTED;
+    return FTH_B200_OK;
+}
+
+int ValidateInt8(const fth_b200_int8_linear_desc* d) {
+    if (d == nullptr) return FTH_B200_ERR_INVALID;
+    if (d->m <= 0 || d->k <= 0 || d->n <= 0 || !d->a || !d->w || !d->out || !d->w_scales) return FTH_B200_ERR_INVALID;
+    if (d->op < FTH_B200_OP_FC || d->op > FTH_B200_OP_GEMM) return FTH_B200_ERR_INVALID;
+    if (!ValidScale(d->a_scale) || !ValidScale(d->out_scale)) return FTH_B200_ERR_INVALID;
+    if (d->a_zp < -128 || d->a_zp > 127 || d->out_zp < -128 || d->out_zp > 127) return FTH_B200_ERR_INVALID;
+    if (d->w_params != 1 && d->w_params != d->n) return FTH_B200_ERR_INVALID;
+    if (d->bias_mode < FTH_B200_BIAS_NONE || d->bias_mode > FTH_B200_BIAS_MATRIX) return FTH_B200_ERR_INVALID;
+    if (d->bias_mode != FTH_B200_BIAS_NONE && !d->bias) return FTH_B200_ERR_INVALID;
+    if (d->op == FTH_B200_OP_MATMUL && d->bias_mode != FTH_B200_BIAS_NONE) return FTH_B200_ERR_INVALID;
+    if (d->op == FTH_B200_OP_GEMM && (!std::isfinite(d->alpha) || !std::isfinite(d->beta))) return FTH_B200_ERR_INVALID;
+    if (d->trans_b && d->op != FTH_B200_OP_GEMM) return FTH_B200_ERR_INVALID;
+    if (d->a_dtype != 0 && d->a_dtype != FTH_B200_INT8 && d->a_dtype != FTH_B200_FP32) return FTH_B200_ERR_UNSUPPORTED;
+    if (d->out_dtype != 0 && d->out_dtype != FTH_B200_INT8 && d->out_dtype != FTH_B200_FP32) return FTH_B200_ERR_UNSUPPORTED;
+    if (d->ldo != 0 && d->ldo < d->n) return FTH_B200_ERR_INVALID;
+    if (d->w_zp_max_abs < 0 || d->w_zp_max_abs > 128 || d->bias_max_abs < 0) return FTH_B200_ERR_INVALID;
+    // Every running sum must stay inside int32 (FitsInt32 after each term, int8_kernel_utils.h:99-114).
+    // Decide it on the host from the worst case, as the reference's x86 path does (x86/int8.cc:1963-1980),
+    // so that no device-side error flag or synchronisation is needed.
+    const int64_t a_span = 128 + (d->a_zp < 0 ? -d->a_zp : d->a_zp);
+    const int64_t w_span = 128 + d->w_zp_max_abs;
+    const int64_t worst = d->k * a_span * w_span + d->bias_max_abs;
+    if (worst > 2147483647LL) return FTH_B200_ERR_OVERFLOW;
+    if (d->m > (int64_t{1} << 31) || d->n > (int64_t{1} << 31)) return FTH_B200_ERR_UNSUPPORTED;
+    return FTH_B200_OK;
+}
+
+int PickVariant(int requested, int dtype, const LinearArgs& args) {
+    if (requested == FTH_B200_VARIANT_SIMT) return FTH_B200_VARIANT_SIMT;
+    if (requested == FTH_B200_VARIANT_SKINNY) return SkinnySupported(dtype, args) ? requested : FTH_B200_ERR_UNSUPPORTED;
+    if (requested == FTH_B200_VARIANT_TCGEN05) return Tcgen05Supported(dtype, args) ? requested : FTH_B200_ERR_UNSUPPORTED;
+    if (requested != FTH_B200_VARIANT_AUTO) return FTH_B200_ERR_INVALID;
+    // Shape split: M <= 4 streams weights on the CUDA cores (HBM-bound either way); everything larger that
+    // TMA can address goes to the tensor cores; ragged leftovers take the CUDA-core tile kernel.
+    if (args.m <= 4 && SkinnySupported(dtype, args)) return FTH_B200_VARIANT_SKINNY;
+    if (Tcgen05Supported(dtype, args)) return FTH_B200_VARIANT_TCGEN05;
+    if (SkinnySupported(dtype, args)) return FTH_B200_VARIANT_SKINNY;
+    return FTH_B200_VARIANT_SIMT;
+}
+
+int Dispatch(int variant, int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
+             cudaStream_t stream) {
+    switch (variant) {
+        case FTH_B200_VARIANT_SIMT: return LaunchLinearSimt(dtype, args, fe, ie, stream);
+        case FTH_B200_VARIANT_SKINNY: return LaunchLinearSkinny(dtype, args, fe, ie, stream);
+        case FTH_B200_VARIANT_TCGEN05: return LaunchLinearTcgen05(dtype, args, fe, ie, stream);
+        default: return variant;  // negative status from PickVariant
+    }
+}
+
+void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* fe) {
+    args->a = d->a; args->w = d->w; args->m = d->m; args->k = d->k; args->n = d->n; args->trans_b = d->trans_b;
+    args->a_dtype = (d->a_dtype == d->dtype) ? 0 : d->a_dtype;
+    args->a_scale = d->a_scale;
+    args->weight_clean = d->weight_clean;
+    fe->ab_scale = d->w_channel_scales ? d->a_scale : d->a_scale * d->w_scale;
+    fe->w_channel_scales = d->w_channel_scales;
+    fe->is_gemm = d->op == FTH_B200_OP_GEMM;
+    fe->alpha = fe->is_gemm ? d->alpha : 1.0f;
+    fe->beta = fe->is_gemm ? d->beta : 1.0f;
+    fe->bias = static_cast<const uint8_t*>(d->bias);
+    fe->bias_mode = d->bias_mode;
+    fe->bias_scale = d->bias_scale;
+    fe->out_scale = d->out_scale;
+    fe->out = d->out;
+    fe->out_dtype = (d->out_dtype == d->dtype) ? 0 : d->out_dtype;
+    fe->ldo = d->ldo ? d->ldo : d->n;
+    fe->n = d->n;
+}
+
+void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogue* ie) {
+    args->a = d->a; args->w = d->w; args->m = d->m; args->k = d->k; args->n = d->n; args->trans_b = d->trans_b;
+    args->a_dtype = (d->a_dtype == FTH_B200_INT8) ? 0 : d->a_dtype;
+    args->a_scale = d->a_scale;
+    args->weight_clean = 1;
+    ie->w_scales = d->w_scales; ie->w_zps = d->w_zps; ie->per_channel = d->w_params != 1;
+    ie->a_scale = d->a_scale; ie->a_zp = d->a_zp; ie->out_scale = d->out_scale; ie->out_zp = d->out_zp;
+    ie->bias = d->bias; ie->bias_mode = d->bias_mode;
+    ie->is_gemm = d->op == FTH_B200_OP_GEMM;
+    ie->alpha = ie->is_gemm ? d->alpha : 1.0f;
+    ie->beta = ie->is_gemm ? d->beta : 1.0f;
+    ie->out = d->out;
+    ie->out_dtype = (d->out_dtype == FTH_B200_INT8) ? 0 : d->out_dtype;
+    ie->ldo = d->ldo ? d->ldo : d->n;
+    ie->n = d->n; ie->k = d->k;
+}
+
+}  // namespace
+}  // namespace fth
+
+using namespace fth;
+
+extern "C" int fth_b200_abi_version(void) { return 1; }
+extern "C" const char* fth_b200_last_variant(void) { return g_last_variant; }
+extern "C" int64_t fth_b200_launch_count(void) { return g_launches; }
+extern "C" void fth_b200_reset_launch_count(void) { g_launches = 0; }
+
+extern "C" int fth_b200_fp8_linear_supported(const fth_b200_fp8_linear_desc* d) {
+    const int rc = ValidateFp8(d);
+    if (rc != FTH_B200_OK) return rc;
+    LinearArgs args; Fp8Epilogue fe;
+    BuildFp8(d, &args, &fe);
+    const int v = PickVariant(d->variant, d->dtype, args);
+    return v < 0 ? v : FTH_B200_OK;
+}
+
+extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_stream_t stream) {
+    const int rc = ValidateFp8(d);
+    if (rc != FTH_B200_OK) return rc;
+    LinearArgs args; Fp8Epilogue fe; Int8Epilogue ie = {};
+    BuildFp8(d, &args, &fe);
+    return Dispatch(PickVariant(d->variant, d->dtype, args), d->dtype, args, fe, ie, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* d) {
+    const int rc = ValidateInt8(d);
+    if (rc != FTH_B200_OK) return rc;
+    LinearArgs args; Int8Epilogue ie;
+    BuildInt8(d, &args, &ie);
+    const int v = PickVariant(d->variant, FTH_B200_INT8, args);
+    return v < 0 ? v : FTH_B200_OK;
+}
+
+extern "C" int fth_b200_int8_linear(const fth_b200_int8_linear_desc* d, fth_b200_stream_t stream) {
+    const int rc = ValidateInt8(d);
+    if (rc != FTH_B200_OK) return rc;
+    LinearArgs args; Int8Epilogue ie; Fp8Epilogue fe = {};
+    BuildInt8(d, &args, &ie);
+    return Dispatch(PickVariant(d->variant, FTH_B200_INT8, args), FTH_B200_INT8, args, fe, ie, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,33 @@
+// Internal launcher interface shared by the linear kernel families and the C ABI dispatch.
+#pragma once
+
+#include "common.cuh"
+
+namespace fth {
+
+// Operand description common to FP8 and INT8 linear kernels.
+struct LinearArgs {
+    const void* a;   // [M,K] activations (FP8 / INT8, or BF16 / FP32 when a Cast / QuantizeLinear is fused)
+    const void* w;   // [K,N] or [N,K] weights, one byte per element
+    int64_t m, k, n;
+    int trans_b;
+    int a_dtype;     // 0 = same as the weight dtype
+    float a_scale;   // used only by the fused-cast activation load
+    int weight_clean;
+};
+
+int LaunchLinearSimt(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
+                     cudaStream_t stream);
+
+// Weight-streaming GEMV / skinny GEMM for M <= kSkinnyMaxM.
+constexpr int kSkinnyMaxM = 16;
+bool SkinnySupported(int dtype, const LinearArgs& args);
+int LaunchLinearSkinny(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
+                       cudaStream_t stream);
+
+// tcgen05 / TMEM / TMA dense GEMM.
+bool Tcgen05Supported(int dtype, const LinearArgs& args);
+int LaunchLinearTcgen05(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
+                        cudaStream_t stream);
+
+}  // namespace fth

@@ -1,0 +1,214 @@
+// Host-buffer plans: Prepare()/compute() for one node with an immutable weight.
+//
+// create  = what KernelBase::Prepare() does once per session: upload weight, scales, zero points, bias and
+//           tables, scan FP8 weights for NaN/Inf codes, size the workspace.  Allocates and synchronises.
+// run     = what compute() does in the reference CUDA kernels (src/kernel/cuda/matmul.cu:230-272):
+//           activation host→device, launch, result device→host, on the caller's stream, then waits.
+// launch  = the same launch on device-resident buffers, no copies and no wait.
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+namespace {
+
+enum class Kind { kFp8Linear, kInt8Linear, kInt8Conv };
+
+struct DeviceBuffer {
+    void* ptr{nullptr};
+    ~DeviceBuffer() { if (ptr) cudaFree(ptr); }
+    int Upload(const void* host, size_t bytes) {
+        if (bytes == 0) return FTH_B200_OK;
+        if (cudaMalloc(&ptr, bytes) != cudaSuccess) return FTH_B200_ERR_CUDA;
+        if (host && cudaMemcpy(ptr, host, bytes, cudaMemcpyHostToDevice) != cudaSuccess) return FTH_B200_ERR_CUDA;
+        return FTH_B200_OK;
+    }
+};
+
+size_t ElemBytes(int dtype) {
+    switch (dtype) {
+        case FTH_B200_FP32: case FTH_B200_INT32: return 4;
+        case FTH_B200_BF16: case FTH_B200_FP16: return 2;
+        default: return 1;
+    }
+}
+
+}  // namespace
+
+struct fth_b200_plan {
+    Kind kind;
+    fth_b200_fp8_linear_desc fp8{};
+    fth_b200_int8_linear_desc int8{};
+    fth_b200_int8_conv2d_desc conv{};
+    DeviceBuffer in, out, w, bias, scales, zps, lut, workspace, flag;
+    int64_t in_bytes{0}, out_bytes{0};
+};
+
+#define FTH_TRY(expr) do { const int rc_ = (expr); if (rc_ != FTH_B200_OK) { delete p; return rc_; } } while (0)
+
+extern "C" int fth_b200_plan_create_fp8_linear(const fth_b200_fp8_linear_desc* h, fth_b200_plan** plan) {
+    if (!h || !plan || !h->w || h->m <= 0 || h->k <= 0 || h->n <= 0) return FTH_B200_ERR_INVALID;
+    auto* p = new (std::nothrow) fth_b200_plan();
+    if (!p) return FTH_B200_ERR_INVALID;
+    p->kind = Kind::kFp8Linear;
+    p->fp8 = *h;
+    const int a_dtype = h->a_dtype ? h->a_dtype : h->dtype;
+    const int out_dtype = h->out_dtype ? h->out_dtype : h->dtype;
+    const int64_t ldo = h->ldo ? h->ldo : h->n;
+    p->in_bytes = h->m * h->k * static_cast<int64_t>(ElemBytes(a_dtype));
+    p->out_bytes = h->m * ldo * static_cast<int64_t>(ElemBytes(out_dtype));
+    FTH_TRY(p->w.Upload(h->w, static_cast<size_t>(h->k * h->n)));
+    FTH_TRY(p->in.Upload(nullptr, static_cast<size_t>(p->in_bytes)));
+    FTH_TRY(p->out.Upload(nullptr, static_cast<size_t>(p->out_bytes)));
+    if (h->bias_mode != FTH_B200_BIAS_NONE) {
+        if (!h->bias) { delete p; return FTH_B200_ERR_INVALID; }
+        FTH_TRY(p->bias.Upload(h->bias, static_cast<size_t>(h->bias_mode == FTH_B200_BIAS_VECTOR ? h->n : h->m * h->n)));
+    }
+    if (h->w_channel_scales) FTH_TRY(p->scales.Upload(h->w_channel_scales, static_cast<size_t>(h->n) * 4));
+    p->fp8.w = p->w.ptr; p->fp8.bias = p->bias.ptr; p->fp8.w_channel_scales = static_cast<const float*>(p->scales.ptr);
+    p->fp8.a = p->in.ptr; p->fp8.out = p->out.ptr;
+    // One scan of the immutable weight decides whether the branch-free decode is legal.
+    FTH_TRY(p->flag.Upload(nullptr, sizeof(int32_t)));
+    FTH_TRY(fth_b200_fp8_count_specials(h->dtype, p->w.ptr, h->k * h->n, static_cast<int32_t*>(p->flag.ptr), nullptr));
+    int32_t specials = 0;
+    if (cudaMemcpy(&specials, p->flag.ptr, sizeof(specials), cudaMemcpyDeviceToHost) != cudaSuccess) { delete p; return FTH_B200_ERR_CUDA; }
+    p->fp8.weight_clean = specials == 0;
+    FTH_TRY(fth_b200_fp8_linear_supported(&p->fp8));
+    *plan = p;
+    return FTH_B200_OK;
+}
+
+extern "C" int fth_b200_plan_create_int8_linear(const fth_b200_int8_linear_desc* h, fth_b200_plan** plan) {
+    if (!h || !plan || !h->w || !h->w_scales || h->m <= 0 || h->k <= 0 || h->n <= 0) return FTH_B200_ERR_INVALID;
+    if (h->w_params != 1 && h->w_params != h->n) return FTH_B200_ERR_INVALID;
+    auto* p = new (std::nothrow) fth_b200_plan();
+    if (!p) return FTH_B200_ERR_INVALID;
+    p->kind = Kind::kInt8Linear;
+    p->int8 = *h;
+    const int a_dtype = h->a_dtype ? h->a_dtype : FTH_B200_INT8;
+    const int out_dtype = h->out_dtype ? h->out_dtype : FTH_B200_INT8;
+    const int64_t ldo = h->ldo ? h->ldo : h->n;
+    p->in_bytes = h->m * h->k * static_cast<int64_t>(ElemBytes(a_dtype));
+    p->out_bytes = h->m * ldo * static_cast<int64_t>(ElemBytes(out_dtype));
+    FTH_TRY(p->w.Upload(h->w, static_cast<size_t>(h->k * h->n)));
+    FTH_TRY(p->in.Upload(nullptr, static_cast<size_t>(p->in_bytes)));
+    FTH_TRY(p->out.Upload(nullptr, static_cast<size_t>(p->out_bytes)));
+    FTH_TRY(p->scales.Upload(h->w_scales, static_cast<size_t>(h->w_params) * 4));
+    int32_t zp_max = 0;
+    if (h->w_zps) {
+        for (int64_t i = 0; i < h->w_params; ++i) {
+            if (h->w_zps[i] < -128 || h->w_zps[i] > 127) { delete p; return FTH_B200_ERR_INVALID; }
+            zp_max = std::max(zp_max, std::abs(h->w_zps[i]));
+        }
+        if (zp_max != 0) FTH_TRY(p->zps.Upload(h->w_zps, static_cast<size_t>(h->w_params) * 4));
+    }
+    for (int64_t i = 0; i < h->w_params; ++i)
+        if (!(h->w_scales[i] > 0.0f) || !(h->w_scales[i] < INFINITY)) { delete p; return FTH_B200_ERR_INVALID; }
+    int64_t bias_max = 0;
+    if (h->bias_mode != FTH_B200_BIAS_NONE) {
+        if (!h->bias) { delete p; return FTH_B200_ERR_INVALID; }
+        const int64_t count = h->bias_mode == FTH_B200_BIAS_VECTOR ? h->n : h->m * h->n;
+        for (int64_t i = 0; i < count; ++i) bias_max = std::max<int64_t>(bias_max, std::llabs(static_cast<long long>(h->bias[i])));
+        FTH_TRY(p->bias.Upload(h->bias, static_cast<size_t>(count) * 4));
+    }
+    p->int8.w = static_cast<const int8_t*>(p->w.ptr);
+    p->int8.w_scales = static_cast<const float*>(p->scales.ptr);
+    p->int8.w_zps = static_cast<const int32_t*>(p->zps.ptr);
+    p->int8.bias = static_cast<const int32_t*>(p->bias.ptr);
+    p->int8.w_zp_max_abs = zp_max;
+    p->int8.bias_max_abs = bias_max;
+    p->int8.a = p->in.ptr; p->int8.out = p->out.ptr;
+    FTH_TRY(fth_b200_int8_linear_supported(&p->int8));
+    *plan = p;
+    return FTH_B200_OK;
+}
+
+extern "C" int fth_b200_plan_create_int8_conv2d(const fth_b200_int8_conv2d_desc* h, fth_b200_plan** plan) {
+    if (!h || !plan || !h->w || !h->w_scales || h->group <= 0 || h->oc <= 0) return FTH_B200_ERR_INVALID;
+    if (h->w_params != 1 && h->w_params != h->oc) return FTH_B200_ERR_INVALID;
+    auto* p = new (std::nothrow) fth_b200_plan();
+    if (!p) return FTH_B200_ERR_INVALID;
+    p->kind = Kind::kInt8Conv;
+    p->conv = *h;
+    const int64_t oh = (h->ih + 2 * h->pad_h - h->dilation_h * (h->kh - 1) - 1) / h->stride_h + 1;
+    const int64_t ow = (h->iw + 2 * h->pad_w - h->dilation_w * (h->kw - 1) - 1) / h->stride_w + 1;
+    if (oh <= 0 || ow <= 0) { delete p; return FTH_B200_ERR_INVALID; }
+    p->in_bytes = h->batch * h->ic * h->ih * h->iw;
+    p->out_bytes = h->batch * h->oc * oh * ow;
+    FTH_TRY(p->w.Upload(h->w, static_cast<size_t>(h->oc * (h->ic / h->group) * h->kh * h->kw)));
+    FTH_TRY(p->in.Upload(nullptr, static_cast<size_t>(p->in_bytes)));
+    FTH_TRY(p->out.Upload(nullptr, static_cast<size_t>(p->out_bytes)));
+    FTH_TRY(p->scales.Upload(h->w_scales, static_cast<size_t>(h->w_params) * 4));
+    int32_t zp_max = 0;
+    if (h->w_zps) {
+        for (int64_t i = 0; i < h->w_params; ++i) zp_max = std::max(zp_max, std::abs(h->w_zps[i]));
+        if (zp_max > 128) { delete p; return FTH_B200_ERR_INVALID; }
+        if (zp_max != 0) FTH_TRY(p->zps.Upload(h->w_zps, static_cast<size_t>(h->w_params) * 4));
+    }
+    int64_t bias_max = 0;
+    if (h->bias) {
+        for (int64_t i = 0; i < h->oc; ++i) bias_max = std::max<int64_t>(bias_max, std::llabs(static_cast<long long>(h->bias[i])));
+        FTH_TRY(p->bias.Upload(h->bias, static_cast<size_t>(h->oc) * 4));
+    }
+    if (h->relu_lut) FTH_TRY(p->lut.Upload(h->relu_lut, 256));
+    p->conv.w = static_cast<const int8_t*>(p->w.ptr);
+    p->conv.w_scales = static_cast<const float*>(p->scales.ptr);
+    p->conv.w_zps = static_cast<const int32_t*>(p->zps.ptr);
+    p->conv.bias = static_cast<const int32_t*>(p->bias.ptr);
+    p->conv.relu_lut = static_cast<const int8_t*>(p->lut.ptr);
+    p->conv.w_zp_max_abs = zp_max;
+    p->conv.bias_max_abs = bias_max;
+    p->conv.x = static_cast<const int8_t*>(p->in.ptr);
+    p->conv.out = static_cast<int8_t*>(p->out.ptr);
+    p->conv.workspace = nullptr; p->conv.workspace_bytes = 0; p->conv.weights_packed = 0;
+    const size_t ws = fth_b200_int8_conv2d_workspace_bytes(&p->conv);
+    if (ws) {
+        FTH_TRY(p->workspace.Upload(nullptr, ws));
+        p->conv.workspace = p->workspace.ptr;
+        p->conv.workspace_bytes = ws;
+    }
+    FTH_TRY(fth_b200_int8_conv2d_supported(&p->conv));
+    *plan = p;
+    return FTH_B200_OK;
+}
+
+extern "C" int fth_b200_plan_launch(fth_b200_plan* p, const void* device_in, void* device_out, fth_b200_stream_t stream) {
+    if (!p || !device_in || !device_out) return FTH_B200_ERR_INVALID;
+    switch (p->kind) {
+        case Kind::kFp8Linear: {
+            fth_b200_fp8_linear_desc d = p->fp8;
+            d.a = device_in; d.out = device_out;
+            return fth_b200_fp8_linear(&d, stream);
+        }
+        case Kind::kInt8Linear: {
+            fth_b200_int8_linear_desc d = p->int8;
+            d.a = device_in; d.out = device_out;
+            return fth_b200_int8_linear(&d, stream);
+        }
+        case Kind::kInt8Conv: {
+            fth_b200_int8_conv2d_desc d = p->conv;
+            d.x = static_cast<const int8_t*>(device_in); d.out = static_cast<int8_t*>(device_out);
+            const int rc = fth_b200_int8_conv2d(&d, stream);
+            if (rc == FTH_B200_OK) p->conv.weights_packed = 1;  // the packed weights stay in the workspace
+            return rc;
+        }
+    }
+    return FTH_B200_ERR_INVALID;
+}
+
+extern "C" int fth_b200_plan_run(fth_b200_plan* p, const void* host_in, void* host_out, fth_b200_stream_t stream_) {
+    if (!p || !host_in || !host_out) return FTH_B200_ERR_INVALID;
+    auto stream = static_cast<cudaStream_t>(stream_);
+    if (cudaMemcpyAsync(p->in.ptr, host_in, static_cast<size_t>(p->in_bytes), cudaMemcpyHostToDevice, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    const int rc = fth_b200_plan_launch(p, p->in.ptr, p->out.ptr, stream_);
+    if (rc != FTH_B200_OK) return rc;
+    if (cudaMemcpyAsync(host_out, p->out.ptr, static_cast<size_t>(p->out_bytes), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    return FTH_B200_OK;
+}
+
+extern "C" int64_t fth_b200_plan_input_bytes(const fth_b200_plan* p) { return p ? p->in_bytes : -1; }
+extern "C" int64_t fth_b200_plan_output_bytes(const fth_b200_plan* p) { return p ? p->out_bytes : -1; }
+extern "C" void fth_b200_plan_destroy(fth_b200_plan* p) { delete p; }

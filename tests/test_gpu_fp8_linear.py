@@ -1,0 +1,142 @@
+"""FP8 FC / MatMul / Gemm on the GPU against the CPU oracle (Common semantics).
+
+Tolerance: every output byte within ONE FP8 code of the oracle after FP32 accumulation, and the class of
+non-finite outputs (NaN / Inf codes) must match exactly."""
+import numpy as np
+import pytest
+
+import infer_b200 as B
+import oracle as O
+from tests import util
+from tests.gpu_helpers import run_fp8_linear
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [O.E4M3, O.E5M2]
+
+
+def check_codes(got, want, dtype, what):
+    dist = util.fp8_code_distance(got, want)
+    special = (want & 0x7F) >= (0x7F if dtype == O.E4M3 else 0x7C)
+    assert np.array_equal(got[special], want[special]), f"{what}: non-finite codes differ"
+    assert dist.max() <= 1, f"{what}: max code distance {dist.max()} (> 1), {int((dist > 1).sum())} outputs"
+    return int((dist > 0).sum())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY])
+@pytest.mark.parametrize("m,k,n", [(1, 1024, 3072), (2, 1024, 1024), (3, 3584, 1024), (4, 1024, 3584), (16, 512, 256),
+                                   (1, 48, 16), (5, 130, 272), (1, 8192, 512)])
+def test_matmul_kn(cuda, dtype, variant, m, k, n):
+    case = util.make_fp8_linear(dtype, m, k, n, seed=m * 7 + k + n)
+    want = O.fp8_linear(O.OP_MATMUL, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"])
+    got = run_fp8_linear(cuda, dtype, B.OP_MATMUL, case, variant=variant)
+    check_codes(got, want, dtype, f"matmul {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY])
+@pytest.mark.parametrize("m,k,n", [(1, 1024, 3072), (2, 1024, 1000), (4, 2048, 77), (7, 528, 19), (1, 8192, 640)])
+def test_gemm_trans_b(cuda, dtype, variant, m, k, n):
+    case = util.make_fp8_linear(dtype, m, k, n, seed=k + n, trans_b=True, bias_mode=1)
+    kw = dict(bias=case["bias"], bias_scale=case["sb"], trans_b=True, alpha=0.75, beta=1.25)
+    want = O.fp8_linear(O.OP_GEMM, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"], **kw)
+    got = run_fp8_linear(cuda, dtype, B.OP_GEMM, case, trans_b=True, variant=variant, alpha=0.75, beta=1.25)
+    check_codes(got, want, dtype, f"gemm^T {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("op,bias_mode", [(B.OP_FC, 1), (B.OP_FC, 2), (B.OP_GEMM, 2), (B.OP_GEMM, 0)])
+def test_bias_modes_auto_variant(cuda, dtype, op, bias_mode):
+    case = util.make_fp8_linear(dtype, 3, 256, 320, seed=11 + bias_mode, bias_mode=bias_mode, pow2=True)
+    kw = dict(bias=case["bias"], bias_scale=case["sb"])
+    want = O.fp8_linear(op, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"], **kw)
+    got = run_fp8_linear(cuda, dtype, op, case)
+    check_codes(got, want, dtype, f"op {op} bias {bias_mode}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_ragged_shapes_simt(cuda, dtype):
+    # every tail of the 64x64x32 tiling, including sizes no TMA / 16-byte path can take
+    for m, k, n in [(1, 1, 1), (2, 3, 5), (17, 33, 65), (63, 64, 65), (65, 127, 129), (128, 31, 63)]:
+        case = util.make_fp8_linear(dtype, m, k, n, seed=m + k + n, bias_mode=1)
+        want = O.fp8_linear(O.OP_FC, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"],
+                            bias=case["bias"], bias_scale=case["sb"])
+        got = run_fp8_linear(cuda, dtype, B.OP_FC, case)
+        assert B.last_variant() == "simt"
+        check_codes(got, want, dtype, f"ragged {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_clean_weight_decode_matches_exact_decode(cuda, dtype):
+    """The branch-free weight decode (legal when a scan found no NaN/Inf code) is bit-identical to the
+    converter-based decode on every finite code, subnormals included."""
+    rng = np.random.default_rng(5)
+    finite = np.array([c for c in range(256) if (c & 0x7F) < (0x7F if dtype == O.E4M3 else 0x7C)], np.uint8)
+    for trans_b in (False, True):
+        m, k, n = 2, 512, 256
+        case = util.make_fp8_linear(dtype, m, k, n, seed=3, trans_b=trans_b)
+        case["w"] = rng.choice(finite, size=case["w"].shape).astype(np.uint8)
+        case["so"] = case["so"] * 64.0
+        op = B.OP_GEMM if trans_b else B.OP_MATMUL
+        exact = run_fp8_linear(cuda, dtype, op, case, trans_b=trans_b, variant=B.VARIANT_SKINNY, weight_clean=0)
+        clean = run_fp8_linear(cuda, dtype, op, case, trans_b=trans_b, variant=B.VARIANT_SKINNY, weight_clean=1)
+        assert np.array_equal(exact, clean)
+
+
+def test_nonfinite_codes_propagate(cuda):
+    """E5M2 Inf in an operand reaches the output as the Inf code 0x7C; E4M3 NaN as 0x7F
+    (reference test/x86_fp8_linear_test.cc:142-156)."""
+    for dtype, code in ((O.E5M2, 0x7C), (O.E4M3, 0x7F)):
+        for variant in (B.VARIANT_SIMT, B.VARIANT_SKINNY):
+            case = util.make_fp8_linear(dtype, 1, 64, 32, seed=9)
+            case["a"][:] = O.fp8_encode(dtype, np.ones((1, 64), np.float32))
+            case["w"][:] = O.fp8_encode(dtype, np.ones((64, 32), np.float32))
+            case["w"][5, 7] = code
+            case.update(sa=1.0, sw=1.0, so=1.0)
+            want = O.fp8_linear(O.OP_MATMUL, dtype, case["a"], 1.0, case["w"], 1.0, 1.0)
+            got = run_fp8_linear(cuda, dtype, B.OP_MATMUL, case, variant=variant)
+            assert got[0, 7] == want[0, 7] == code
+            assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_fused_cast_prologue_and_epilogue(cuda, dtype):
+    """Cast(BF16→FP8) → MatMul → Cast(FP8→BF16) in one call equals the three reference nodes."""
+    rng = np.random.default_rng(21)
+    m, k, n = 2, 1024, 768
+    case = util.make_fp8_linear(dtype, m, k, n, seed=21, pow2=True)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x_bf16 = (x.view(np.uint32) >> 16).astype(np.uint16)
+    a_codes = O.cast(O.BF16, x_bf16, 1.0, dtype, case["sa"]).reshape(m, k)
+    mid = O.fp8_linear(O.OP_MATMUL, dtype, a_codes, case["sa"], case["w"], case["sw"], case["so"])
+    want = O.cast(dtype, mid, case["so"], O.BF16, 1.0).reshape(m, n)
+    got = run_fp8_linear(cuda, dtype, B.OP_MATMUL, case, a_dtype=B.BF16, out_dtype=B.BF16, a_raw=x_bf16)
+    # compare through the FP8 codes the BF16 values stand for
+    got_codes = O.cast(O.BF16, got, 1.0, dtype, case["so"]).reshape(m, n)
+    check_codes(got_codes, mid, dtype, "fused cast")
+    same = got_codes == mid
+    assert np.array_equal(got[same], want[same])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_output_row_stride(cuda, dtype):
+    """ldo > n: a column shard writes its slice straight into a wider [M, N_total] buffer."""
+    case = util.make_fp8_linear(dtype, 2, 256, 256, seed=31)
+    want = O.fp8_linear(O.OP_MATMUL, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"])
+    got = run_fp8_linear(cuda, dtype, B.OP_MATMUL, case, ldo=1024)
+    check_codes(got, want, dtype, "ldo")
+
+
+def test_rejections(cuda):
+    """Contract violations the reference kernels answer with -1 (src/kernel/fp8_host.h:150-203)."""
+    import ctypes as C
+    case = util.make_fp8_linear(O.E4M3, 1, 64, 64, seed=1)
+    from tests.gpu_helpers import dev
+    a, w = dev(cuda, case["a"]), dev(cuda, case["w"])
+    out = cuda.empty((1, 64), dtype=cuda.uint8, device="cuda")
+    base = dict(dtype=B.E4M3, op=B.OP_MATMUL, m=1, k=64, n=64, a=a, w=w, out=out, a_scale=1.0, w_scale=1.0, out_scale=1.0)
+    for bad in (dict(a_scale=0.0), dict(out_scale=float("nan")), dict(w_scale=float("inf")), dict(m=0), dict(dtype=B.INT8),
+                dict(trans_b=True), dict(out=None), dict(bias_mode=1)):
+        d = B.fp8_linear_desc(**{**base, **bad})
+        assert B.lib().fth_b200_fp8_linear(C.byref(d), B.current_stream()) == B.ERR_INVALID, bad
