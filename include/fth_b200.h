@@ -55,14 +55,18 @@ enum { FTH_B200_BIAS_NONE = 0, FTH_B200_BIAS_VECTOR = 1, FTH_B200_BIAS_MATRIX = 
 enum {
     FTH_B200_VARIANT_AUTO = 0,
     FTH_B200_VARIANT_SIMT = 1,   /* ragged-shape CUDA-core tile kernel (any M, K, N, any alignment) */
-    FTH_B200_VARIANT_SKINNY = 2, /* weight-streaming GEMV / skinny GEMM, M <= 16 */
-    FTH_B200_VARIANT_TCGEN05 = 3 /* tcgen05 MMA, TMEM accumulators, TMA-fed shared-memory tiles */
+    FTH_B200_VARIANT_SKINNY = 2, /* weight-streaming GEMV / skinny GEMM with direct 16-byte loads, M <= 16 */
+    FTH_B200_VARIANT_TCGEN05 = 3,/* tcgen05 MMA, TMEM accumulators, TMA-fed shared-memory tiles */
+    FTH_B200_VARIANT_STREAM = 4  /* persistent GEMV, weights staged through a TMA shared-memory ring ([K,N] weights) */
 };
 
 int fth_b200_abi_version(void);
 /* Name of the kernel family the last call on this host thread launched ("skinny", "tcgen05", "simt", …);
  * the counterpart of LastCudaFp8MatmulBackend() (src/kernel/cuda/runtime.h:141-143). */
 const char* fth_b200_last_variant(void);
+/* Reads and clears the per-device status word (synchronises the device): 0 when no bounded device-side wait
+ * ever gave up, else (site << 16) | detail of the first that did. */
+int fth_b200_device_status(void);
 /* Kernels launched by this library on this host thread since the last reset. */
 int64_t fth_b200_launch_count(void);
 void fth_b200_reset_launch_count(void);
@@ -101,18 +105,19 @@ typedef struct {
     float a_scale, w_scale, bias_scale, out_scale;
     const float* w_channel_scales;
     float alpha, beta;
-    int32_t weight_clean; /* 1: caller scanned w with fth_b200_fp8_count_specials and found no NaN/Inf code */
+    /* Device scratch for the split-K partial sums of VARIANT_STREAM (fth_b200_fp8_linear_workspace_bytes).
+     * It must be zero-filled once after allocation; every call leaves its counters zero again.  Calls that
+     * share a workspace must not overlap on the GPU.  May be null: the library then picks kernels that
+     * need no scratch. */
+    void* workspace;
+    size_t workspace_bytes;
     int32_t variant;      /* FTH_B200_VARIANT_* */
 } fth_b200_fp8_linear_desc;
 
 int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t stream);
 /* Capability check only (what Supports() calls): 0 if fth_b200_fp8_linear would run this descriptor. */
 int fth_b200_fp8_linear_supported(const fth_b200_fp8_linear_desc* desc);
-
-/* Counts NaN / Inf codes in an FP8 buffer into *count (device int32, zeroed by the call).  Used once in
- * Prepare() on immutable weights so the streaming kernels may take the branch-free decode. */
-int fth_b200_fp8_count_specials(int32_t dtype, const void* data, int64_t count, int32_t* device_count,
-                                fth_b200_stream_t stream);
+size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc);
 
 /* -------------------------------------------------------------------------------------------------
  * INT8 FC, MatMul, Gemm (bit-exact with the Common kernels).
@@ -152,11 +157,14 @@ typedef struct {
     int32_t out_zp;
     float alpha, beta;
     int64_t bias_max_abs; /* host-known bound on |bias| for the overflow pre-check */
+    void* workspace;      /* as in fth_b200_fp8_linear_desc */
+    size_t workspace_bytes;
     int32_t variant;
 } fth_b200_int8_linear_desc;
 
 int fth_b200_int8_linear(const fth_b200_int8_linear_desc* desc, fth_b200_stream_t stream);
 int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* desc);
+size_t fth_b200_int8_linear_workspace_bytes(const fth_b200_int8_linear_desc* desc);
 
 /* -------------------------------------------------------------------------------------------------
  * INT8 Conv2D, NCHW activations, OIHW weights, int32 bias, optional fused INT8 ReLU table.

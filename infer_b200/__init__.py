@@ -17,13 +17,14 @@ LIB_PATH = os.path.join(_HERE, "libfth_b200.so")
 INT8, FP16, FP32, INT32, BF16, E4M3, E5M2 = 1, 3, 4, 5, 11, 12, 13
 OP_FC, OP_MATMUL, OP_GEMM = 0, 1, 2
 BIAS_NONE, BIAS_VECTOR, BIAS_MATRIX = 0, 1, 2
-VARIANT_AUTO, VARIANT_SIMT, VARIANT_SKINNY, VARIANT_TCGEN05 = 0, 1, 2, 3
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_SKINNY, VARIANT_TCGEN05, VARIANT_STREAM = 0, 1, 2, 3, 4
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_OVERFLOW, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
 
 EXPORTS = [
     "fth_b200_abi_version", "fth_b200_last_variant", "fth_b200_launch_count", "fth_b200_reset_launch_count",
-    "fth_b200_fp8_linear", "fth_b200_fp8_linear_supported", "fth_b200_fp8_count_specials",
-    "fth_b200_int8_linear", "fth_b200_int8_linear_supported",
+    "fth_b200_fp8_linear", "fth_b200_fp8_linear_supported", "fth_b200_fp8_linear_workspace_bytes",
+    "fth_b200_device_status",
+    "fth_b200_int8_linear", "fth_b200_int8_linear_supported", "fth_b200_int8_linear_workspace_bytes",
     "fth_b200_int8_conv2d", "fth_b200_int8_conv2d_supported", "fth_b200_int8_conv2d_workspace_bytes",
     "fth_b200_int8_relu_table", "fth_b200_int8_lookup",
     "fth_b200_quantize_linear", "fth_b200_dequantize_linear", "fth_b200_cast",
@@ -40,7 +41,7 @@ class Fp8LinearDesc(C.Structure):
         ("a", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int64),
         ("a_scale", C.c_float), ("w_scale", C.c_float), ("bias_scale", C.c_float), ("out_scale", C.c_float),
         ("w_channel_scales", C.c_void_p), ("alpha", C.c_float), ("beta", C.c_float),
-        ("weight_clean", C.c_int32), ("variant", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32),
     ]
 
 
@@ -51,7 +52,8 @@ class Int8LinearDesc(C.Structure):
         ("a", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int64),
         ("a_scale", C.c_float), ("a_zp", C.c_int32), ("w_scales", C.c_void_p), ("w_zps", C.c_void_p),
         ("w_params", C.c_int64), ("w_zp_max_abs", C.c_int32), ("out_scale", C.c_float), ("out_zp", C.c_int32),
-        ("alpha", C.c_float), ("beta", C.c_float), ("bias_max_abs", C.c_int64), ("variant", C.c_int32),
+        ("alpha", C.c_float), ("beta", C.c_float), ("bias_max_abs", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32),
     ]
 
 
@@ -84,6 +86,8 @@ def lib():
         handle.fth_b200_last_variant.restype = C.c_char_p
         handle.fth_b200_launch_count.restype = C.c_int64
         handle.fth_b200_int8_conv2d_workspace_bytes.restype = C.c_size_t
+        handle.fth_b200_fp8_linear_workspace_bytes.restype = C.c_size_t
+        handle.fth_b200_int8_linear_workspace_bytes.restype = C.c_size_t
         handle.fth_b200_plan_input_bytes.restype = C.c_int64
         handle.fth_b200_plan_output_bytes.restype = C.c_int64
         handle.fth_b200_plan_input_bytes.argtypes = [C.c_void_p]
@@ -129,20 +133,23 @@ def current_stream():
 
 def fp8_linear_desc(*, dtype, op, m, k, n, a, w, out, a_scale, w_scale, out_scale, trans_b=False, bias=None,
                     bias_mode=BIAS_NONE, bias_scale=1.0, alpha=1.0, beta=1.0, a_dtype=0, out_dtype=0, ldo=0,
-                    w_channel_scales=None, weight_clean=0, variant=VARIANT_AUTO) -> Fp8LinearDesc:
+                    w_channel_scales=None, workspace=None, workspace_bytes=0,
+                    variant=VARIANT_AUTO) -> Fp8LinearDesc:
     d = Fp8LinearDesc()
     d.dtype, d.op, d.m, d.k, d.n, d.trans_b = dtype, op, m, k, n, int(trans_b)
     d.a_dtype, d.out_dtype, d.bias_mode = a_dtype, out_dtype, bias_mode
     d.a, d.w, d.bias, d.out, d.ldo = ptr(a), ptr(w), ptr(bias), ptr(out), ldo
     d.a_scale, d.w_scale, d.bias_scale, d.out_scale = a_scale, w_scale, bias_scale, out_scale
     d.w_channel_scales = ptr(w_channel_scales)
-    d.alpha, d.beta, d.weight_clean, d.variant = alpha, beta, weight_clean, variant
+    d.alpha, d.beta, d.variant = alpha, beta, variant
+    d.workspace, d.workspace_bytes = ptr(workspace), workspace_bytes
     return d
 
 
 def int8_linear_desc(*, op, m, k, n, a, w, out, a_scale, a_zp, w_scales, w_zps, w_params, out_scale, out_zp,
                      trans_b=False, bias=None, bias_mode=BIAS_NONE, alpha=1.0, beta=1.0, a_dtype=0, out_dtype=0,
-                     ldo=0, w_zp_max_abs=0, bias_max_abs=0, variant=VARIANT_AUTO) -> Int8LinearDesc:
+                     ldo=0, w_zp_max_abs=0, bias_max_abs=0, workspace=None, workspace_bytes=0,
+                     variant=VARIANT_AUTO) -> Int8LinearDesc:
     d = Int8LinearDesc()
     d.op, d.m, d.k, d.n, d.trans_b = op, m, k, n, int(trans_b)
     d.a_dtype, d.out_dtype, d.bias_mode = a_dtype, out_dtype, bias_mode
@@ -150,6 +157,7 @@ def int8_linear_desc(*, op, m, k, n, a, w, out, a_scale, a_zp, w_scales, w_zps, 
     d.a_scale, d.a_zp, d.w_scales, d.w_zps, d.w_params = a_scale, a_zp, ptr(w_scales), ptr(w_zps), w_params
     d.w_zp_max_abs, d.out_scale, d.out_zp = w_zp_max_abs, out_scale, out_zp
     d.alpha, d.beta, d.bias_max_abs, d.variant = alpha, beta, bias_max_abs, variant
+    d.workspace, d.workspace_bytes = ptr(workspace), workspace_bytes
     return d
 
 
@@ -214,10 +222,20 @@ def int8_relu_table(in_scale, in_zp, out_scale, out_zp):
     return lut
 
 
-def fp8_count_specials(dtype, data, count, device_counter, stream=None) -> None:
-    check(lib().fth_b200_fp8_count_specials(C.c_int32(dtype), C.c_void_p(ptr(data)), C.c_int64(count),
-                                            C.c_void_p(ptr(device_counter)), stream or current_stream()),
-          "fth_b200_fp8_count_specials")
+def device_status() -> int:
+    return lib().fth_b200_device_status()
+
+
+def linear_workspace(torch, desc):
+    """Allocates and zero-fills the scratch a linear descriptor may use and attaches it; returns the tensor."""
+    fn = lib().fth_b200_fp8_linear_workspace_bytes if isinstance(desc, Fp8LinearDesc) else lib().fth_b200_int8_linear_workspace_bytes
+    fn.restype = C.c_size_t
+    need = fn(C.byref(desc))
+    if not need:
+        return None
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    desc.workspace, desc.workspace_bytes = ws.data_ptr(), need
+    return ws
 
 
 class Plan:

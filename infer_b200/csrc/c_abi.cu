@@ -69,13 +69,25 @@ int ValidateInt8(const fth_b200_int8_linear_desc* d) {
     return FTH_B200_OK;
 }
 
-int PickVariant(int requested, int dtype, const LinearArgs& args) {
+bool StreamUsable(int dtype, const LinearArgs& args, const void* workspace, size_t workspace_bytes) {
+    if (!StreamSupported(dtype, args)) return false;
+    const size_t need = StreamScratchBytes(dtype, args);
+    return need == 0 || (workspace != nullptr && workspace_bytes >= need);
+}
+
+int PickVariant(int requested, int dtype, const LinearArgs& args, const void* workspace, size_t workspace_bytes) {
     if (requested == FTH_B200_VARIANT_SIMT) return FTH_B200_VARIANT_SIMT;
     if (requested == FTH_B200_VARIANT_SKINNY) return SkinnySupported(dtype, args) ? requested : FTH_B200_ERR_UNSUPPORTED;
     if (requested == FTH_B200_VARIANT_TCGEN05) return Tcgen05Supported(dtype, args) ? requested : FTH_B200_ERR_UNSUPPORTED;
+    if (requested == FTH_B200_VARIANT_STREAM) {
+        if (!StreamSupported(dtype, args)) return FTH_B200_ERR_UNSUPPORTED;
+        return StreamUsable(dtype, args, workspace, workspace_bytes) ? requested : FTH_B200_ERR_INVALID;
+    }
     if (requested != FTH_B200_VARIANT_AUTO) return FTH_B200_ERR_INVALID;
-    // Shape split: M <= 4 streams weights on the CUDA cores (HBM-bound either way); everything larger that
+    // Shape split.  Decode shapes stream the weights once on the CUDA cores (HBM-bound): the persistent
+    // TMA-ring kernel when its scratch is available, else the direct-load kernels.  Everything larger that
     // TMA can address goes to the tensor cores; ragged leftovers take the CUDA-core tile kernel.
+    if (StreamUsable(dtype, args, workspace, workspace_bytes)) return FTH_B200_VARIANT_STREAM;
     if (args.m <= 4 && SkinnySupported(dtype, args)) return FTH_B200_VARIANT_SKINNY;
     if (Tcgen05Supported(dtype, args)) return FTH_B200_VARIANT_TCGEN05;
     if (SkinnySupported(dtype, args)) return FTH_B200_VARIANT_SKINNY;
@@ -83,11 +95,12 @@ int PickVariant(int requested, int dtype, const LinearArgs& args) {
 }
 
 int Dispatch(int variant, int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
-             cudaStream_t stream) {
+             void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     switch (variant) {
         case FTH_B200_VARIANT_SIMT: return LaunchLinearSimt(dtype, args, fe, ie, stream);
         case FTH_B200_VARIANT_SKINNY: return LaunchLinearSkinny(dtype, args, fe, ie, stream);
         case FTH_B200_VARIANT_TCGEN05: return LaunchLinearTcgen05(dtype, args, fe, ie, stream);
+        case FTH_B200_VARIANT_STREAM: return LaunchLinearStream(dtype, args, fe, ie, workspace, workspace_bytes, stream);
         default: return variant;  // negative status from PickVariant
     }
 }
@@ -96,7 +109,6 @@ void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* 
     args->a = d->a; args->w = d->w; args->m = d->m; args->k = d->k; args->n = d->n; args->trans_b = d->trans_b;
     args->a_dtype = (d->a_dtype == d->dtype) ? 0 : d->a_dtype;
     args->a_scale = d->a_scale;
-    args->weight_clean = d->weight_clean;
     fe->ab_scale = d->w_channel_scales ? d->a_scale : d->a_scale * d->w_scale;
     fe->w_channel_scales = d->w_channel_scales;
     fe->is_gemm = d->op == FTH_B200_OP_GEMM;
@@ -116,7 +128,6 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
     args->a = d->a; args->w = d->w; args->m = d->m; args->k = d->k; args->n = d->n; args->trans_b = d->trans_b;
     args->a_dtype = (d->a_dtype == FTH_B200_INT8) ? 0 : d->a_dtype;
     args->a_scale = d->a_scale;
-    args->weight_clean = 1;
     ie->w_scales = d->w_scales; ie->w_zps = d->w_zps; ie->per_channel = d->w_params != 1;
     ie->a_scale = d->a_scale; ie->a_zp = d->a_zp; ie->out_scale = d->out_scale; ie->out_zp = d->out_zp;
     ie->bias = d->bias; ie->bias_mode = d->bias_mode;
@@ -144,8 +155,15 @@ extern "C" int fth_b200_fp8_linear_supported(const fth_b200_fp8_linear_desc* d) 
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Fp8Epilogue fe;
     BuildFp8(d, &args, &fe);
-    const int v = PickVariant(d->variant, d->dtype, args);
+    const int v = PickVariant(d->variant, d->dtype, args, d->workspace, d->workspace_bytes);
     return v < 0 ? v : FTH_B200_OK;
+}
+
+extern "C" size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* d) {
+    if (ValidateFp8(d) != FTH_B200_OK) return 0;
+    LinearArgs args; Fp8Epilogue fe;
+    BuildFp8(d, &args, &fe);
+    return StreamSupported(d->dtype, args) ? StreamScratchBytes(d->dtype, args) : 0;
 }
 
 extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_stream_t stream) {
@@ -153,7 +171,8 @@ extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_s
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Fp8Epilogue fe; Int8Epilogue ie = {};
     BuildFp8(d, &args, &fe);
-    return Dispatch(PickVariant(d->variant, d->dtype, args), d->dtype, args, fe, ie, static_cast<cudaStream_t>(stream));
+    return Dispatch(PickVariant(d->variant, d->dtype, args, d->workspace, d->workspace_bytes), d->dtype, args, fe, ie,
+                    d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* d) {
@@ -161,8 +180,15 @@ extern "C" int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* d
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Int8Epilogue ie;
     BuildInt8(d, &args, &ie);
-    const int v = PickVariant(d->variant, FTH_B200_INT8, args);
+    const int v = PickVariant(d->variant, FTH_B200_INT8, args, d->workspace, d->workspace_bytes);
     return v < 0 ? v : FTH_B200_OK;
+}
+
+extern "C" size_t fth_b200_int8_linear_workspace_bytes(const fth_b200_int8_linear_desc* d) {
+    if (ValidateInt8(d) != FTH_B200_OK) return 0;
+    LinearArgs args; Int8Epilogue ie;
+    BuildInt8(d, &args, &ie);
+    return StreamSupported(FTH_B200_INT8, args) ? StreamScratchBytes(FTH_B200_INT8, args) : 0;
 }
 
 extern "C" int fth_b200_int8_linear(const fth_b200_int8_linear_desc* d, fth_b200_stream_t stream) {
@@ -170,5 +196,6 @@ extern "C" int fth_b200_int8_linear(const fth_b200_int8_linear_desc* d, fth_b200
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Int8Epilogue ie; Fp8Epilogue fe = {};
     BuildInt8(d, &args, &ie);
-    return Dispatch(PickVariant(d->variant, FTH_B200_INT8, args), FTH_B200_INT8, args, fe, ie, static_cast<cudaStream_t>(stream));
+    return Dispatch(PickVariant(d->variant, FTH_B200_INT8, args, d->workspace, d->workspace_bytes), FTH_B200_INT8, args,
+                    fe, ie, d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -35,26 +35,6 @@ __device__ __forceinline__ float Decode(uint8_t code) {
     return DecodePair<DTYPE>(static_cast<uint16_t>(code)).x;
 }
 
-// Branch-free decode of four codes that are known not to be NaN / Inf: each byte's exponent and
-// mantissa bits are placed into an FP32 pattern and the bias difference (2^120 for E4M3, 2^112 for
-// E5M2) is applied by one multiply.  Subnormal codes become FP32 subnormals, which the multiply
-// scales exactly.  NaN / Inf codes would come out as large finite numbers — callers use this only for
-// weights a Prepare()-time scan found clean.
-template <int DTYPE>
-__device__ __forceinline__ void DecodeClean4(uint32_t word, float (&out)[4]) {
-    constexpr int kShift = DTYPE == FTH_B200_FP8E4M3 ? 4 : 3;
-    constexpr uint32_t kMask = DTYPE == FTH_B200_FP8E4M3 ? 0x87f00000u : 0x8fe00000u;
-    const float kBias = DTYPE == FTH_B200_FP8E4M3 ? 1.329227995784916e36f /* 2^120 */
-                                                  : 5.192296858534828e33f /* 2^112 */;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int32_t top = static_cast<int32_t>(__byte_perm(word, 0u, 0x0444 | ((i) << 12)));
-        // top now holds byte i in bits 31..24 and zeros below
-        const uint32_t bits = static_cast<uint32_t>(top >> kShift) & kMask;
-        out[i] = __uint_as_float(bits) * kBias;
-    }
-}
-
 // Saturating round-to-nearest-even encode with the reference's treatment of non-finite inputs
 // (include/util/fp8.h:148-172): E4M3 NaN → sign|0x7F, ±Inf → sign|0x7E; E5M2 NaN → sign|0x7D, ±Inf → sign|0x7C.
 template <int DTYPE>

@@ -1,4 +1,4 @@
-// Cast, QuantizeLinear, DequantizeLinear, INT8 table lookup, FP8 special-code scan.
+// Cast, QuantizeLinear, DequantizeLinear, INT8 table lookup.
 // All are HBM-bound byte streams: 16 bytes per thread per access on the widest side, grid-stride loops
 // over a grid sized in multiples of the SM count.
 #include "common.cuh"
@@ -28,7 +28,11 @@ __device__ __forceinline__ void WriteAs(void* out, int64_t i, float v, float out
     if constexpr (OUT == FTH_B200_FP32) static_cast<float*>(out)[i] = v;
     else if constexpr (OUT == FTH_B200_BF16) static_cast<uint16_t*>(out)[i] = EncodeBf16Cast(v);
     else if constexpr (OUT == FTH_B200_FP16) static_cast<__half*>(out)[i] = __float2half_rn(v);
-    else static_cast<uint8_t*>(out)[i] = Encode<OUT>(__fdiv_rn(v, out_scale));
+    else {
+        // a NaN keeps its sign through the reference's division on the host; GPU arithmetic would canonicalise
+        // it, so NaNs skip the divide
+        static_cast<uint8_t*>(out)[i] = (v != v) ? Encode<OUT>(v) : Encode<OUT>(__fdiv_rn(v, out_scale));
+    }
 }
 
 template <int N> struct Bytes { static constexpr int value = (N == FTH_B200_FP32) ? 4 : (N == FTH_B200_BF16 || N == FTH_B200_FP16) ? 2 : 1; };
@@ -136,21 +140,6 @@ __global__ void __launch_bounds__(kThreads) LookupKernel(const int8_t* __restric
     }
 }
 
-// E4M3: 0x7F / 0xFF are NaN.  E5M2: exponent field 31 is Inf / NaN.
-template <int DTYPE>
-__global__ void __launch_bounds__(kThreads) CountSpecialsKernel(const uint8_t* __restrict__ data, int64_t count,
-                                                                int32_t* __restrict__ result) {
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    int found = 0;
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < count; i += stride) {
-        const uint8_t c = data[i];
-        if constexpr (DTYPE == FTH_B200_FP8E4M3) found += (c & 0x7f) == 0x7f;
-        else found += (c & 0x7c) == 0x7c;
-    }
-    found = __reduce_add_sync(0xffffffffu, found);
-    if ((threadIdx.x & 31) == 0 && found != 0) atomicAdd(result, found);
-}
-
 }  // namespace
 }  // namespace fth
 
@@ -219,20 +208,6 @@ extern "C" int fth_b200_int8_lookup(const int8_t* x, int8_t* out, int64_t count,
     if (count == 0) return FTH_B200_OK;
     LookupKernel<<<GridFor(count / 16 + 1), kThreads, 0, stream>>>(x, out, count, device_lut256);
     NoteLaunch("int8_lookup");
-    return CheckLaunch();
-}
-
-extern "C" int fth_b200_fp8_count_specials(int32_t dtype, const void* data, int64_t count, int32_t* device_count,
-                                           fth_b200_stream_t stream_) {
-    auto stream = static_cast<cudaStream_t>(stream_);
-    if (!data || !device_count || count < 0) return FTH_B200_ERR_INVALID;
-    if (cudaMemsetAsync(device_count, 0, sizeof(int32_t), stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
-    if (count == 0) return FTH_B200_OK;
-    const int grid = GridFor(count);
-    if (dtype == FTH_B200_FP8E4M3) CountSpecialsKernel<FTH_B200_FP8E4M3><<<grid, kThreads, 0, stream>>>(static_cast<const uint8_t*>(data), count, device_count);
-    else if (dtype == FTH_B200_FP8E5M2) CountSpecialsKernel<FTH_B200_FP8E5M2><<<grid, kThreads, 0, stream>>>(static_cast<const uint8_t*>(data), count, device_count);
-    else return FTH_B200_ERR_INVALID;
-    NoteLaunch("fp8_count_specials");
     return CheckLaunch();
 }
 

@@ -13,7 +13,6 @@ struct LinearArgs {
     int trans_b;
     int a_dtype;     // 0 = same as the weight dtype
     float a_scale;   // used only by the fused-cast activation load
-    int weight_clean;
 };
 
 int LaunchLinearSimt(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
@@ -24,6 +23,13 @@ constexpr int kSkinnyMaxM = 16;
 bool SkinnySupported(int dtype, const LinearArgs& args);
 int LaunchLinearSkinny(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
                        cudaStream_t stream);
+
+// Persistent TMA-ring GEMV for [K,N] weights.
+bool StreamSupported(int dtype, const LinearArgs& args);
+size_t StreamCounterBytes(const LinearArgs& args);
+size_t StreamScratchBytes(int dtype, const LinearArgs& args);
+int LaunchLinearStream(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* scratch,
+                       size_t scratch_bytes, cudaStream_t stream);
 
 // tcgen05 / TMEM / TMA dense GEMM.
 bool Tcgen05Supported(int dtype, const LinearArgs& args);

@@ -49,20 +49,14 @@ __host__ __device__ inline int SplitForK(int64_t k) {
     return p;
 }
 
-template <int DTYPE, bool CLEAN>
+template <int DTYPE>
 __device__ __forceinline__ void Decode16(const uint4& v, float (&out)[16]) {
     const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        if constexpr (CLEAN) {
-            float t[4];
-            DecodeClean4<DTYPE>(words[i], t);
-            out[4 * i + 0] = t[0]; out[4 * i + 1] = t[1]; out[4 * i + 2] = t[2]; out[4 * i + 3] = t[3];
-        } else {
-            const float2 lo = DecodePair<DTYPE>(static_cast<uint16_t>(words[i] & 0xffffu));
-            const float2 hi = DecodePair<DTYPE>(static_cast<uint16_t>(words[i] >> 16));
-            out[4 * i + 0] = lo.x; out[4 * i + 1] = lo.y; out[4 * i + 2] = hi.x; out[4 * i + 3] = hi.y;
-        }
+        const float2 lo = DecodePair<DTYPE>(static_cast<uint16_t>(words[i] & 0xffffu));
+        const float2 hi = DecodePair<DTYPE>(static_cast<uint16_t>(words[i] >> 16));
+        out[4 * i + 0] = lo.x; out[4 * i + 1] = lo.y; out[4 * i + 2] = hi.x; out[4 * i + 3] = hi.y;
     }
 }
 
@@ -81,7 +75,7 @@ __device__ __forceinline__ void Transpose4x4(uint32_t r0, uint32_t r1, uint32_t 
 // ---------------------------------------------------------------------------------------------------
 // KN kernel
 // ---------------------------------------------------------------------------------------------------
-template <int DTYPE, int MB, bool CLEAN>
+template <int DTYPE, int MB>
 __global__ void __launch_bounds__(kThreads) SkinnyKnKernel(LinearArgs args, Fp8Epilogue fe, Int8Epilogue ie, int split,
                                                            int64_t chunk) {
     using T = typename Acc<DTYPE>::type;
@@ -196,7 +190,7 @@ __global__ void __launch_bounds__(kThreads) SkinnyKnKernel(LinearArgs args, Fp8E
                     for (int u = 0; u < kUnroll; ++u) {
                         const int row = r + u * kRowLanes;  // < kSubK + kPadK by construction
                         float wv[16];
-                        Decode16<DTYPE, CLEAN>(v[u], wv);
+                        Decode16<DTYPE>(v[u], wv);
 #pragma unroll
                         for (int m = 0; m < MB; ++m) {
                             const float av = a_s[m * (kSubK + kPadK) + row];
@@ -291,14 +285,14 @@ constexpr size_t KnSmemBytes() {
            (kTileN + MB + 4) * 4;
 }
 
-template <int DTYPE, int MB, bool CLEAN>
+template <int DTYPE, int MB>
 int LaunchKn(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     const int split = SplitForK(args.k);
     // chunk: rows per cluster rank, a multiple of 64 so INT8 quads and row lanes never straddle chunks
     int64_t chunk = (args.k + split - 1) / split;
     chunk = (chunk + 63) / 64 * 64;
     const size_t smem = KnSmemBytes<DTYPE, MB>();
-    auto kernel = SkinnyKnKernel<DTYPE, MB, CLEAN>;
+    auto kernel = SkinnyKnKernel<DTYPE, MB>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return FTH_B200_ERR_CUDA;
@@ -325,7 +319,7 @@ int LaunchKn(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& 
 // ---------------------------------------------------------------------------------------------------
 // NK kernel
 // ---------------------------------------------------------------------------------------------------
-template <int DTYPE, int MB, int R, bool CLEAN>
+template <int DTYPE, int MB, int R>
 __global__ void __launch_bounds__(kThreads) SkinnyNkKernel(LinearArgs args, Fp8Epilogue fe, Int8Epilogue ie) {
     constexpr bool kInt8 = DTYPE == FTH_B200_INT8;
     using T = typename Acc<DTYPE>::type;
@@ -407,7 +401,7 @@ __global__ void __launch_bounds__(kThreads) SkinnyNkKernel(LinearArgs args, Fp8E
                 const float* a_s = reinterpret_cast<const float*>(smem);
                 float wv[R][16];
 #pragma unroll
-                for (int r = 0; r < R; ++r) Decode16<DTYPE, CLEAN>(v[u][r], wv[r]);
+                for (int r = 0; r < R; ++r) Decode16<DTYPE>(v[u][r], wv[r]);
 #pragma unroll
                 for (int m = 0; m < MB; ++m) {
                     float av[16];
@@ -456,11 +450,11 @@ __global__ void __launch_bounds__(kThreads) SkinnyNkKernel(LinearArgs args, Fp8E
     }
 }
 
-template <int DTYPE, int MB, int R, bool CLEAN>
+template <int DTYPE, int MB, int R>
 int LaunchNk(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     constexpr bool kInt8 = DTYPE == FTH_B200_INT8;
     const size_t smem = static_cast<size_t>(MB) * args.k * (kInt8 ? 1 : 4);
-    auto kernel = SkinnyNkKernel<DTYPE, MB, R, CLEAN>;
+    auto kernel = SkinnyNkKernel<DTYPE, MB, R>;
     static size_t configured = 0;
     if (smem > configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return FTH_B200_ERR_CUDA;
@@ -474,20 +468,20 @@ int LaunchNk(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& 
 
 constexpr size_t kNkSmemLimit = 200 * 1024;
 
-template <int DTYPE, bool CLEAN>
+template <int DTYPE>
 int LaunchSkinnyTyped(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     const int mb = args.m >= 4 ? 4 : (args.m >= 2 ? 2 : 1);
     if (args.trans_b) {
         switch (mb) {
-            case 1: return LaunchNk<DTYPE, 1, 4, CLEAN>(args, fe, ie, stream);
-            case 2: return LaunchNk<DTYPE, 2, 4, CLEAN>(args, fe, ie, stream);
-            default: return LaunchNk<DTYPE, 4, 2, CLEAN>(args, fe, ie, stream);
+            case 1: return LaunchNk<DTYPE, 1, 4>(args, fe, ie, stream);
+            case 2: return LaunchNk<DTYPE, 2, 4>(args, fe, ie, stream);
+            default: return LaunchNk<DTYPE, 4, 2>(args, fe, ie, stream);
         }
     }
     switch (mb) {
-        case 1: return LaunchKn<DTYPE, 1, CLEAN>(args, fe, ie, stream);
-        case 2: return LaunchKn<DTYPE, 2, CLEAN>(args, fe, ie, stream);
-        default: return LaunchKn<DTYPE, 4, CLEAN>(args, fe, ie, stream);
+        case 1: return LaunchKn<DTYPE, 1>(args, fe, ie, stream);
+        case 2: return LaunchKn<DTYPE, 2>(args, fe, ie, stream);
+        default: return LaunchKn<DTYPE, 4>(args, fe, ie, stream);
     }
 }
 
@@ -509,13 +503,9 @@ int LaunchLinearSkinny(int dtype, const LinearArgs& args, const Fp8Epilogue& fe,
                        cudaStream_t stream) {
     if (!SkinnySupported(dtype, args)) return FTH_B200_ERR_UNSUPPORTED;
     switch (dtype) {
-        case FTH_B200_FP8E4M3:
-            return args.weight_clean ? LaunchSkinnyTyped<FTH_B200_FP8E4M3, true>(args, fe, ie, stream)
-                                     : LaunchSkinnyTyped<FTH_B200_FP8E4M3, false>(args, fe, ie, stream);
-        case FTH_B200_FP8E5M2:
-            return args.weight_clean ? LaunchSkinnyTyped<FTH_B200_FP8E5M2, true>(args, fe, ie, stream)
-                                     : LaunchSkinnyTyped<FTH_B200_FP8E5M2, false>(args, fe, ie, stream);
-        case FTH_B200_INT8: return LaunchSkinnyTyped<FTH_B200_INT8, false>(args, fe, ie, stream);
+        case FTH_B200_FP8E4M3: return LaunchSkinnyTyped<FTH_B200_FP8E4M3>(args, fe, ie, stream);
+        case FTH_B200_FP8E5M2: return LaunchSkinnyTyped<FTH_B200_FP8E5M2>(args, fe, ie, stream);
+        case FTH_B200_INT8: return LaunchSkinnyTyped<FTH_B200_INT8>(args, fe, ie, stream);
         default: return FTH_B200_ERR_INVALID;
     }
 }

@@ -42,7 +42,7 @@ struct fth_b200_plan {
     fth_b200_fp8_linear_desc fp8{};
     fth_b200_int8_linear_desc int8{};
     fth_b200_int8_conv2d_desc conv{};
-    DeviceBuffer in, out, w, bias, scales, zps, lut, workspace, flag;
+    DeviceBuffer in, out, w, bias, scales, zps, lut, workspace;
     int64_t in_bytes{0}, out_bytes{0};
 };
 
@@ -69,12 +69,12 @@ extern "C" int fth_b200_plan_create_fp8_linear(const fth_b200_fp8_linear_desc* h
     if (h->w_channel_scales) FTH_TRY(p->scales.Upload(h->w_channel_scales, static_cast<size_t>(h->n) * 4));
     p->fp8.w = p->w.ptr; p->fp8.bias = p->bias.ptr; p->fp8.w_channel_scales = static_cast<const float*>(p->scales.ptr);
     p->fp8.a = p->in.ptr; p->fp8.out = p->out.ptr;
-    // One scan of the immutable weight decides whether the branch-free decode is legal.
-    FTH_TRY(p->flag.Upload(nullptr, sizeof(int32_t)));
-    FTH_TRY(fth_b200_fp8_count_specials(h->dtype, p->w.ptr, h->k * h->n, static_cast<int32_t*>(p->flag.ptr), nullptr));
-    int32_t specials = 0;
-    if (cudaMemcpy(&specials, p->flag.ptr, sizeof(specials), cudaMemcpyDeviceToHost) != cudaSuccess) { delete p; return FTH_B200_ERR_CUDA; }
-    p->fp8.weight_clean = specials == 0;
+    p->fp8.workspace = nullptr; p->fp8.workspace_bytes = 0;
+    if (const size_t ws = fth_b200_fp8_linear_workspace_bytes(&p->fp8)) {
+        FTH_TRY(p->workspace.Upload(nullptr, ws));
+        if (cudaMemset(p->workspace.ptr, 0, ws) != cudaSuccess) { delete p; return FTH_B200_ERR_CUDA; }
+        p->fp8.workspace = p->workspace.ptr; p->fp8.workspace_bytes = ws;
+    }
     FTH_TRY(fth_b200_fp8_linear_supported(&p->fp8));
     *plan = p;
     return FTH_B200_OK;
@@ -120,6 +120,12 @@ extern "C" int fth_b200_plan_create_int8_linear(const fth_b200_int8_linear_desc*
     p->int8.w_zp_max_abs = zp_max;
     p->int8.bias_max_abs = bias_max;
     p->int8.a = p->in.ptr; p->int8.out = p->out.ptr;
+    p->int8.workspace = nullptr; p->int8.workspace_bytes = 0;
+    if (const size_t ws = fth_b200_int8_linear_workspace_bytes(&p->int8)) {
+        FTH_TRY(p->workspace.Upload(nullptr, ws));
+        if (cudaMemset(p->workspace.ptr, 0, ws) != cudaSuccess) { delete p; return FTH_B200_ERR_CUDA; }
+        p->int8.workspace = p->workspace.ptr; p->int8.workspace_bytes = ws;
+    }
     FTH_TRY(fth_b200_int8_linear_supported(&p->int8));
     *plan = p;
     return FTH_B200_OK;

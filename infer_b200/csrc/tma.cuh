@@ -1,0 +1,104 @@
+// TMA (cp.async.bulk.tensor) and mbarrier helpers, plus host-side tensor-map creation.
+//
+// Every wait in this file is bounded: a spin that does not complete within its iteration budget records
+// a code in the device status word and returns false, and callers unwind (free TMEM, stop issuing copies)
+// instead of hanging the GPU.  No load here uses cluster multicast.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fth {
+
+// ---- device status word ------------------------------------------------------------------------------
+// One int per device, 0 = ok.  A bounded wait that gives up stores (site << 16) | detail with atomicCAS from
+// 0, so the first failure is kept.  Kernels receive its device address as a parameter (DeviceStatusPtr());
+// the host reads and clears it through fth_b200_device_status().
+int* DeviceStatusPtr();
+
+__device__ __forceinline__ void ReportTimeout(int* status, int site, int detail) {
+    if (status != nullptr) atomicCAS(status, 0, (site << 16) | (detail & 0xffff));
+}
+
+// ---- shared-memory addresses and barriers ---------------------------------------------------------------
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void MbarInit(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void FenceBarrierInit() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void FenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void MbarExpectTx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void MbarArrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(SmemAddr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Waits for the phase with the given parity.  After a short fast spin the loop backs off with nanosleep and
+// watches the global nanosecond timer; one second after the first miss it reports (site, detail) in the
+// status word and returns false.
+constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;
+__device__ __forceinline__ uint64_t GlobalTimerNs() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity, int* status, int site, int detail) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+        if (MbarTryWait(bar, parity)) return true;
+    }
+    const uint64_t start = GlobalTimerNs();
+#pragma unroll 1
+    for (;;) {
+        if (MbarTryWait(bar, parity)) return true;
+        __nanosleep(64);
+        if (GlobalTimerNs() - start > kWaitBudgetNs) break;
+    }
+    ReportTimeout(status, site, detail);
+    return false;
+}
+
+// ---- TMA loads (no multicast) -----------------------------------------------------------------------------
+// x is the innermost coordinate; x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void TmaLoad2D(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(SmemAddr(smem_dst)), "l"(map), "r"(SmemAddr(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void TmaLoad4D(void* smem_dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2,
+                                          int32_t c3, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(SmemAddr(smem_dst)), "l"(map), "r"(SmemAddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void TmaPrefetchDescriptor(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// ---- host: tensor maps ---------------------------------------------------------------------------------------
+enum class TmaSwizzle { kNone, k32B, k64B, k128B };
+
+// rank-2 uint8 tensor [rows][cols] with a row pitch in bytes; box = box_cols x box_rows.
+// Returns false if the driver entry point is unavailable or the encode fails (bad alignment).
+bool MakeTensorMap2D(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t row_pitch_bytes,
+                     uint32_t box_cols, uint32_t box_rows, TmaSwizzle swizzle);
+// rank-4 uint8 tensor, dims listed innermost first; strides_bytes has 3 entries (dims 1..3).
+bool MakeTensorMap4D(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                     const uint32_t box[4], TmaSwizzle swizzle);
+
+}  // namespace fth

@@ -14,7 +14,7 @@ _OUT_NP = {0: np.uint8, B.E4M3: np.uint8, B.E5M2: np.uint8, B.BF16: np.uint16, B
 
 
 def run_fp8_linear(torch, dtype, op, case, *, trans_b=False, variant=B.VARIANT_AUTO, alpha=1.0, beta=1.0,
-                   a_dtype=0, out_dtype=0, a_raw=None, weight_clean=0, w_channel_scales=None, ldo=0, canary=True):
+                   a_dtype=0, out_dtype=0, a_raw=None, w_channel_scales=None, ldo=0, canary=True, workspace=True):
     a_np = case["a"] if a_raw is None else a_raw
     m, k = case["a"].shape
     n = case["w"].shape[0] if trans_b else case["w"].shape[1]
@@ -31,8 +31,8 @@ def run_fp8_linear(torch, dtype, op, case, *, trans_b=False, variant=B.VARIANT_A
     d = B.fp8_linear_desc(dtype=dtype, op=op, m=m, k=k, n=n, a=a, w=w, out=out, a_scale=case["sa"],
                           w_scale=case["sw"], out_scale=case["so"], trans_b=trans_b, bias=bias,
                           bias_mode=bias_mode, bias_scale=case["sb"], alpha=alpha, beta=beta, a_dtype=a_dtype,
-                          out_dtype=out_dtype, ldo=ldo, w_channel_scales=wcs, weight_clean=weight_clean,
-                          variant=variant)
+                          out_dtype=out_dtype, ldo=ldo, w_channel_scales=wcs, variant=variant)
+    ws_keep = B.linear_workspace(torch, d) if workspace else None
     B.fp8_linear(d)
     torch.cuda.synchronize()
     host = buf.cpu().numpy().view(np_out)
@@ -45,7 +45,7 @@ def run_fp8_linear(torch, dtype, op, case, *, trans_b=False, variant=B.VARIANT_A
 
 
 def run_int8_linear(torch, op, case, *, trans_b=False, variant=B.VARIANT_AUTO, alpha=1.0, beta=1.0, a_dtype=0,
-                    out_dtype=0, a_raw=None):
+                    out_dtype=0, a_raw=None, workspace=True):
     a_np = case["a"] if a_raw is None else a_raw
     m, k = case["a"].shape
     n = case["w"].shape[0] if trans_b else case["w"].shape[1]
@@ -62,6 +62,7 @@ def run_int8_linear(torch, op, case, *, trans_b=False, variant=B.VARIANT_AUTO, a
                            out_zp=case["out_zp"], trans_b=trans_b, bias=bias, bias_mode=bias_mode, alpha=alpha,
                            beta=beta, a_dtype=a_dtype, out_dtype=out_dtype, w_zp_max_abs=zmax,
                            bias_max_abs=bias_max, variant=variant)
+    ws_keep = B.linear_workspace(torch, d) if workspace else None
     B.int8_linear(d)
     torch.cuda.synchronize()
     host = buf.cpu().numpy()

@@ -127,13 +127,3 @@ def test_relu_table_and_lookup(cuda):
         B.int8_lookup(dev(cuda, x), out, x.size, dev(cuda, lut))
         cuda.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy(), O.int8_relu(x, si, zi, so, zo))
-
-
-def test_count_specials(cuda):
-    rng = np.random.default_rng(6)
-    for dtype, is_special in ((B.E4M3, lambda c: (c & 0x7F) == 0x7F), (B.E5M2, lambda c: (c & 0x7C) == 0x7C)):
-        codes = rng.integers(0, 256, 1 << 20).astype(np.uint8)
-        counter = cuda.zeros(1, dtype=cuda.int32, device="cuda")
-        B.fp8_count_specials(dtype, dev(cuda, codes), codes.size, counter)
-        cuda.cuda.synchronize()
-        assert int(counter.item()) == int(is_special(codes).sum())

@@ -17,17 +17,24 @@ DTYPES = [O.E4M3, O.E5M2]
 
 def check_codes(got, want, dtype, what):
     dist = util.fp8_code_distance(got, want)
+    # Non-finite class must match exactly: same Inf code, NaN code up to its sign bit (the sign of a NaN made
+    # by arithmetic, e.g. 0 x Inf, is a host-FPU convention: x86 generates it negative, the GPU positive).
     special = (want & 0x7F) >= (0x7F if dtype == O.E4M3 else 0x7C)
-    assert np.array_equal(got[special], want[special]), f"{what}: non-finite codes differ"
+    nan = (want & 0x7F) >= (0x7F if dtype == O.E4M3 else 0x7D)
+    assert np.array_equal(got[special & ~nan], want[special & ~nan]), f"{what}: Inf codes differ"
+    assert np.array_equal(got[nan] & 0x7F, want[nan] & 0x7F), f"{what}: NaN codes differ"
+    dist = np.where(nan, 0, dist)
     assert dist.max() <= 1, f"{what}: max code distance {dist.max()} (> 1), {int((dist > 1).sum())} outputs"
     return int((dist > 0).sum())
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY])
+@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_STREAM])
 @pytest.mark.parametrize("m,k,n", [(1, 1024, 3072), (2, 1024, 1024), (3, 3584, 1024), (4, 1024, 3584), (16, 512, 256),
-                                   (1, 48, 16), (5, 130, 272), (1, 8192, 512)])
+                                   (1, 48, 16), (5, 130, 272), (1, 8192, 512), (2, 200, 400), (1, 8192, 1040)])
 def test_matmul_kn(cuda, dtype, variant, m, k, n):
+    if variant == B.VARIANT_STREAM and m > 2:
+        pytest.skip("the TMA-ring GEMV takes M <= 2 for FP8")
     case = util.make_fp8_linear(dtype, m, k, n, seed=m * 7 + k + n)
     want = O.fp8_linear(O.OP_MATMUL, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"])
     got = run_fp8_linear(cuda, dtype, B.OP_MATMUL, case, variant=variant)
@@ -67,28 +74,11 @@ def test_ragged_shapes_simt(cuda, dtype):
         check_codes(got, want, dtype, f"ragged {m}x{k}x{n}")
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_clean_weight_decode_matches_exact_decode(cuda, dtype):
-    """The branch-free weight decode (legal when a scan found no NaN/Inf code) is bit-identical to the
-    converter-based decode on every finite code, subnormals included."""
-    rng = np.random.default_rng(5)
-    finite = np.array([c for c in range(256) if (c & 0x7F) < (0x7F if dtype == O.E4M3 else 0x7C)], np.uint8)
-    for trans_b in (False, True):
-        m, k, n = 2, 512, 256
-        case = util.make_fp8_linear(dtype, m, k, n, seed=3, trans_b=trans_b)
-        case["w"] = rng.choice(finite, size=case["w"].shape).astype(np.uint8)
-        case["so"] = case["so"] * 64.0
-        op = B.OP_GEMM if trans_b else B.OP_MATMUL
-        exact = run_fp8_linear(cuda, dtype, op, case, trans_b=trans_b, variant=B.VARIANT_SKINNY, weight_clean=0)
-        clean = run_fp8_linear(cuda, dtype, op, case, trans_b=trans_b, variant=B.VARIANT_SKINNY, weight_clean=1)
-        assert np.array_equal(exact, clean)
-
-
 def test_nonfinite_codes_propagate(cuda):
     """E5M2 Inf in an operand reaches the output as the Inf code 0x7C; E4M3 NaN as 0x7F
     (reference test/x86_fp8_linear_test.cc:142-156)."""
     for dtype, code in ((O.E5M2, 0x7C), (O.E4M3, 0x7F)):
-        for variant in (B.VARIANT_SIMT, B.VARIANT_SKINNY):
+        for variant in (B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_STREAM):
             case = util.make_fp8_linear(dtype, 1, 64, 32, seed=9)
             case["a"][:] = O.fp8_encode(dtype, np.ones((1, 64), np.float32))
             case["w"][:] = O.fp8_encode(dtype, np.ones((64, 32), np.float32))
@@ -136,7 +126,49 @@ def test_rejections(cuda):
     a, w = dev(cuda, case["a"]), dev(cuda, case["w"])
     out = cuda.empty((1, 64), dtype=cuda.uint8, device="cuda")
     base = dict(dtype=B.E4M3, op=B.OP_MATMUL, m=1, k=64, n=64, a=a, w=w, out=out, a_scale=1.0, w_scale=1.0, out_scale=1.0)
+    assert B.lib().fth_b200_fp8_linear(C.byref(B.fp8_linear_desc(**base, variant=B.VARIANT_STREAM)), B.current_stream()) == B.OK  # K=64: no split, no scratch
+    d = B.fp8_linear_desc(**{**base, 'k': 64}, variant=7)
+    assert B.lib().fth_b200_fp8_linear(C.byref(d), B.current_stream()) == B.ERR_INVALID
     for bad in (dict(a_scale=0.0), dict(out_scale=float("nan")), dict(w_scale=float("inf")), dict(m=0), dict(dtype=B.INT8),
                 dict(trans_b=True), dict(out=None), dict(bias_mode=1)):
         d = B.fp8_linear_desc(**{**base, **bad})
         assert B.lib().fth_b200_fp8_linear(C.byref(d), B.current_stream()) == B.ERR_INVALID, bad
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_stream_workspace_is_left_clean_and_reusable(cuda, dtype):
+    """The TMA-ring kernel's arrival counters return to zero, so one zero-filled workspace serves every
+    later call; a column shard gives the same bytes as the same columns of the full weight."""
+    import ctypes as C
+    from tests.gpu_helpers import dev
+    m, k, n = 2, 4096, 1024
+    case = util.make_fp8_linear(dtype, m, k, n, seed=77)
+    want = O.fp8_linear(O.OP_MATMUL, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"])
+    a, w = dev(cuda, case["a"]), dev(cuda, case["w"])
+    out = cuda.zeros((m, n), dtype=cuda.uint8, device="cuda")
+    d = B.fp8_linear_desc(dtype=dtype, op=B.OP_MATMUL, m=m, k=k, n=n, a=a, w=w, out=out, a_scale=case["sa"],
+                          w_scale=case["sw"], out_scale=case["so"], variant=B.VARIANT_STREAM)
+    ws = B.linear_workspace(cuda, d)
+    assert ws is not None
+    full = None
+    for _ in range(3):
+        out.zero_()
+        B.fp8_linear(d)
+        cuda.cuda.synchronize()
+        got = out.cpu().numpy()
+        check_codes(got, want, dtype, "stream reuse")
+        assert full is None or np.array_equal(full, got)
+        full = got
+    counters = ws[:256].cpu().numpy().view(np.int32)
+    assert (counters == 0).all()
+    assert B.device_status() == 0
+    # column shard: columns [256, 768) through a strided view of the same weight is not expressible in the
+    # ABI (weights are dense), so shard by copying the slice — the bytes must equal the full run's slice
+    w_shard = dev(cuda, np.ascontiguousarray(case["w"][:, 256:768]))
+    out_s = cuda.zeros((m, 512), dtype=cuda.uint8, device="cuda")
+    ds = B.fp8_linear_desc(dtype=dtype, op=B.OP_MATMUL, m=m, k=k, n=512, a=a, w=w_shard, out=out_s, a_scale=case["sa"],
+                           w_scale=case["sw"], out_scale=case["so"], variant=B.VARIANT_STREAM)
+    ws2 = B.linear_workspace(cuda, ds)
+    B.fp8_linear(ds)
+    cuda.cuda.synchronize()
+    assert np.array_equal(out_s.cpu().numpy(), full[:, 256:768])
