@@ -69,6 +69,12 @@ int ValidateInt8(const fth_b200_int8_linear_desc* d) {
     return FTH_B200_OK;
 }
 
+bool Tcgen05Usable(int dtype, const LinearArgs& args, const void* workspace, size_t workspace_bytes) {
+    if (!Tcgen05Supported(dtype, args)) return false;
+    const size_t need = Tcgen05ScratchBytes(dtype, args);
+    return need == 0 || (workspace != nullptr && workspace_bytes >= need);
+}
+
 bool StreamUsable(int dtype, const LinearArgs& args, const void* workspace, size_t workspace_bytes) {
     if (!StreamSupported(dtype, args)) return false;
     const size_t need = StreamScratchBytes(dtype, args);
@@ -78,7 +84,10 @@ bool StreamUsable(int dtype, const LinearArgs& args, const void* workspace, size
 int PickVariant(int requested, int dtype, const LinearArgs& args, const void* workspace, size_t workspace_bytes) {
     if (requested == FTH_B200_VARIANT_SIMT) return FTH_B200_VARIANT_SIMT;
     if (requested == FTH_B200_VARIANT_SKINNY) return SkinnySupported(dtype, args) ? requested : FTH_B200_ERR_UNSUPPORTED;
-    if (requested == FTH_B200_VARIANT_TCGEN05) return Tcgen05Supported(dtype, args) ? requested : FTH_B200_ERR_UNSUPPORTED;
+    if (requested == FTH_B200_VARIANT_TCGEN05) {
+        if (!Tcgen05Supported(dtype, args)) return FTH_B200_ERR_UNSUPPORTED;
+        return Tcgen05Usable(dtype, args, workspace, workspace_bytes) ? requested : FTH_B200_ERR_INVALID;
+    }
     if (requested == FTH_B200_VARIANT_STREAM) {
         if (!StreamSupported(dtype, args)) return FTH_B200_ERR_UNSUPPORTED;
         return StreamUsable(dtype, args, workspace, workspace_bytes) ? requested : FTH_B200_ERR_INVALID;
@@ -89,7 +98,7 @@ int PickVariant(int requested, int dtype, const LinearArgs& args, const void* wo
     // TMA can address goes to the tensor cores; ragged leftovers take the CUDA-core tile kernel.
     if (StreamUsable(dtype, args, workspace, workspace_bytes)) return FTH_B200_VARIANT_STREAM;
     if (args.m <= 4 && SkinnySupported(dtype, args)) return FTH_B200_VARIANT_SKINNY;
-    if (Tcgen05Supported(dtype, args)) return FTH_B200_VARIANT_TCGEN05;
+    if (Tcgen05Usable(dtype, args, workspace, workspace_bytes)) return FTH_B200_VARIANT_TCGEN05;
     if (SkinnySupported(dtype, args)) return FTH_B200_VARIANT_SKINNY;
     return FTH_B200_VARIANT_SIMT;
 }
@@ -99,7 +108,7 @@ int Dispatch(int variant, int dtype, const LinearArgs& args, const Fp8Epilogue& 
     switch (variant) {
         case FTH_B200_VARIANT_SIMT: return LaunchLinearSimt(dtype, args, fe, ie, stream);
         case FTH_B200_VARIANT_SKINNY: return LaunchLinearSkinny(dtype, args, fe, ie, stream);
-        case FTH_B200_VARIANT_TCGEN05: return LaunchLinearTcgen05(dtype, args, fe, ie, stream);
+        case FTH_B200_VARIANT_TCGEN05: return LaunchLinearTcgen05(dtype, args, fe, ie, workspace, workspace_bytes, stream);
         case FTH_B200_VARIANT_STREAM: return LaunchLinearStream(dtype, args, fe, ie, workspace, workspace_bytes, stream);
         default: return variant;  // negative status from PickVariant
     }
@@ -109,6 +118,7 @@ void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* 
     args->a = d->a; args->w = d->w; args->m = d->m; args->k = d->k; args->n = d->n; args->trans_b = d->trans_b;
     args->a_dtype = (d->a_dtype == d->dtype) ? 0 : d->a_dtype;
     args->a_scale = d->a_scale;
+    args->zero_points = 0;
     fe->ab_scale = d->w_channel_scales ? d->a_scale : d->a_scale * d->w_scale;
     fe->w_channel_scales = d->w_channel_scales;
     fe->is_gemm = d->op == FTH_B200_OP_GEMM;
@@ -128,6 +138,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
     args->a = d->a; args->w = d->w; args->m = d->m; args->k = d->k; args->n = d->n; args->trans_b = d->trans_b;
     args->a_dtype = (d->a_dtype == FTH_B200_INT8) ? 0 : d->a_dtype;
     args->a_scale = d->a_scale;
+    args->zero_points = (d->a_zp != 0 || d->w_zps != nullptr) ? 1 : 0;
     ie->w_scales = d->w_scales; ie->w_zps = d->w_zps; ie->per_channel = d->w_params != 1;
     ie->a_scale = d->a_scale; ie->a_zp = d->a_zp; ie->out_scale = d->out_scale; ie->out_zp = d->out_zp;
     ie->bias = d->bias; ie->bias_mode = d->bias_mode;
@@ -163,7 +174,9 @@ extern "C" size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_
     if (ValidateFp8(d) != FTH_B200_OK) return 0;
     LinearArgs args; Fp8Epilogue fe;
     BuildFp8(d, &args, &fe);
-    return StreamSupported(d->dtype, args) ? StreamScratchBytes(d->dtype, args) : 0;
+    const size_t a = StreamSupported(d->dtype, args) ? StreamScratchBytes(d->dtype, args) : 0;
+    const size_t b = Tcgen05Supported(d->dtype, args) ? Tcgen05ScratchBytes(d->dtype, args) : 0;
+    return a > b ? a : b;
 }
 
 extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_stream_t stream) {
@@ -188,7 +201,9 @@ extern "C" size_t fth_b200_int8_linear_workspace_bytes(const fth_b200_int8_linea
     if (ValidateInt8(d) != FTH_B200_OK) return 0;
     LinearArgs args; Int8Epilogue ie;
     BuildInt8(d, &args, &ie);
-    return StreamSupported(FTH_B200_INT8, args) ? StreamScratchBytes(FTH_B200_INT8, args) : 0;
+    const size_t a = StreamSupported(FTH_B200_INT8, args) ? StreamScratchBytes(FTH_B200_INT8, args) : 0;
+    const size_t b = Tcgen05Supported(FTH_B200_INT8, args) ? Tcgen05ScratchBytes(FTH_B200_INT8, args) : 0;
+    return a > b ? a : b;
 }
 
 extern "C" int fth_b200_int8_linear(const fth_b200_int8_linear_desc* d, fth_b200_stream_t stream) {

@@ -13,6 +13,7 @@ struct LinearArgs {
     int trans_b;
     int a_dtype;     // 0 = same as the weight dtype
     float a_scale;   // used only by the fused-cast activation load
+    int zero_points; // INT8: activation or weight zero point is non-zero
 };
 
 int LaunchLinearSimt(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
@@ -33,7 +34,8 @@ int LaunchLinearStream(int dtype, const LinearArgs& args, const Fp8Epilogue& fe,
 
 // tcgen05 / TMEM / TMA dense GEMM.
 bool Tcgen05Supported(int dtype, const LinearArgs& args);
-int LaunchLinearTcgen05(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
-                        cudaStream_t stream);
+size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& args);
+int LaunchLinearTcgen05(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* scratch,
+                        size_t scratch_bytes, cudaStream_t stream);
 
 }  // namespace fth

@@ -1,0 +1,82 @@
+"""CPU: the C-ABI library loads without a GPU, exports every symbol include/fth_b200.h declares, and the
+ctypes mirrors of its structs have the C compiler's layout.  No compute call is made here."""
+import ctypes as C
+import os
+import re
+import subprocess
+import tempfile
+
+import pytest
+
+import infer_b200 as B
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "fth_b200.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fth_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    lib = B.lib()
+    names = declared_functions()
+    assert len(names) >= 25
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/fth_b200.h but not exported"
+    assert set(B.EXPORTS) <= set(names)
+    assert lib.fth_b200_abi_version() == 1
+
+
+def test_struct_layouts_match_the_c_compiler():
+    src = r'''
+#include <stdio.h>
+#include <stddef.h>
+#include "fth_b200.h"
+#define P(T, F) printf(#T "." #F " %zu\n", offsetof(T, F))
+int main(void) {
+  printf("sizeof.fp8 %zu\nsizeof.int8 %zu\nsizeof.conv %zu\n", sizeof(fth_b200_fp8_linear_desc), sizeof(fth_b200_int8_linear_desc), sizeof(fth_b200_int8_conv2d_desc));
+  P(fth_b200_fp8_linear_desc, a); P(fth_b200_fp8_linear_desc, ldo); P(fth_b200_fp8_linear_desc, w_channel_scales);
+  P(fth_b200_fp8_linear_desc, workspace); P(fth_b200_fp8_linear_desc, variant);
+  P(fth_b200_int8_linear_desc, a); P(fth_b200_int8_linear_desc, w_scales); P(fth_b200_int8_linear_desc, bias_max_abs);
+  P(fth_b200_int8_linear_desc, workspace); P(fth_b200_int8_linear_desc, variant);
+  P(fth_b200_int8_conv2d_desc, x); P(fth_b200_int8_conv2d_desc, relu_lut); P(fth_b200_int8_conv2d_desc, workspace_bytes);
+  P(fth_b200_int8_conv2d_desc, variant);
+  return 0; }
+'''
+    with tempfile.TemporaryDirectory() as tmp:
+        c = os.path.join(tmp, "layout.c")
+        open(c, "w").write(src)
+        exe = os.path.join(tmp, "layout")
+        subprocess.check_call(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
+        got = dict(line.rsplit(" ", 1) for line in subprocess.check_output([exe], text=True).strip().splitlines())
+    py = {"fth_b200_fp8_linear_desc": B.Fp8LinearDesc, "fth_b200_int8_linear_desc": B.Int8LinearDesc,
+          "fth_b200_int8_conv2d_desc": B.Int8Conv2dDesc}
+    assert int(got["sizeof.fp8"]) == C.sizeof(B.Fp8LinearDesc)
+    assert int(got["sizeof.int8"]) == C.sizeof(B.Int8LinearDesc)
+    assert int(got["sizeof.conv"]) == C.sizeof(B.Int8Conv2dDesc)
+    for key, value in got.items():
+        if key.startswith("sizeof"):
+            continue
+        struct, field = key.split(".")
+        assert getattr(py[struct], field).offset == int(value), key
+
+
+def test_validation_needs_no_gpu():
+    """Contract checks run on the host before any launch."""
+    d = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=1, k=64, n=64, a=16, w=16, out=16, a_scale=0.0, w_scale=1.0, out_scale=1.0)
+    assert B.lib().fth_b200_fp8_linear_supported(C.byref(d)) == B.ERR_INVALID
+    d = B.int8_linear_desc(op=B.OP_MATMUL, m=1, k=300000, n=64, a=16, w=16, out=16, a_scale=1.0, a_zp=0, w_scales=16, w_zps=None,
+                           w_params=64, out_scale=1.0, out_zp=0)
+    assert B.lib().fth_b200_int8_linear_supported(C.byref(d)) == B.ERR_OVERFLOW
+    lut = B.int8_relu_table(0.5, 0, 0.5, 0)
+    assert lut[128 + 5] == 5 and lut[128 - 5] == 0
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(B, "_lib", None)
+    monkeypatch.setattr(B, "LIB_PATH", "/nonexistent/libfth_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or library fallback"):
+        B.lib()
