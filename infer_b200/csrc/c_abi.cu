@@ -93,12 +93,12 @@ int PickVariant(int requested, int dtype, const LinearArgs& args, const void* wo
         return StreamUsable(dtype, args, workspace, workspace_bytes) ? requested : FTH_B200_ERR_INVALID;
     }
     if (requested != FTH_B200_VARIANT_AUTO) return FTH_B200_ERR_INVALID;
-    // Shape split.  Decode shapes stream the weights once on the CUDA cores (HBM-bound): the persistent
-    // TMA-ring kernel when its scratch is available, else the direct-load kernels.  Everything larger that
-    // TMA can address goes to the tensor cores; ragged leftovers take the CUDA-core tile kernel.
-    if (StreamUsable(dtype, args, workspace, workspace_bytes)) return FTH_B200_VARIANT_STREAM;
-    if (args.m <= 4 && SkinnySupported(dtype, args)) return FTH_B200_VARIANT_SKINNY;
+    // Shape split.  Every shape TMA can address runs on the tensor cores: decode shapes (M <= 128) with the
+    // weights on the 128 TMEM lanes, where the kernel is a pure HBM weight stream; dense shapes with 128 x 256
+    // tiles.  Shapes the tensor-core kernel declines (fused Cast / QuantizeLinear prologue, zero points,
+    // strides TMA cannot express, no scratch) stream on the CUDA cores; ragged leftovers take the tile kernel.
     if (Tcgen05Usable(dtype, args, workspace, workspace_bytes)) return FTH_B200_VARIANT_TCGEN05;
+    if (StreamUsable(dtype, args, workspace, workspace_bytes)) return FTH_B200_VARIANT_STREAM;
     if (SkinnySupported(dtype, args)) return FTH_B200_VARIANT_SKINNY;
     return FTH_B200_VARIANT_SIMT;
 }

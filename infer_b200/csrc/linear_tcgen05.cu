@@ -13,8 +13,10 @@
 // K-major operands — no repacking pass, no second copy of the weights.
 //
 // Swapped mode splits K into S chunks (S depends on K only) so that a 28672-column weight gives ~1800 work
-// units for 148 SMs; partial accumulators go to a global scratch buffer and the CTA delivering the last
-// chunk of a tile adds them in chunk order and runs the epilogue (no CTA ever waits for another).
+// units for 148 SMs; partial accumulators go to a global scratch buffer with plain coalesced stores and a
+// small second kernel adds the S partials of every output in chunk order and runs the epilogue.  (A
+// single-kernel hand-off through fences and arrival counters was measured first: the gpu-scope fence per
+// work unit stalled the epilogue warps behind the streaming loads and cost more than the extra launch.)
 #include "common.cuh"
 #include "linear_internal.h"
 #include "tcgen05.cuh"
@@ -40,9 +42,9 @@ struct TcParams {
     int64_t k_blocks;          // ceil(K / 128)
     int64_t units;             // p_tiles * q_tiles * split
     uint32_t idesc;
-    int fp8_dtype;
+    int e4m3;                  // FP8 format of operands and output (1 = E4M3, 0 = E5M2)
+    int fast;                  // 1: no bias, alpha = beta = 1, native output dtype → vectorised epilogue
     void* scratch;             // [split][q_total][p_pad] partial accumulators
-    int32_t* counters;         // [p_tiles * q_tiles], zero between launches
     int64_t p_pad;
     int* status;
 };
@@ -51,45 +53,87 @@ template <int BQ>
 struct Cfg {
     static constexpr int kQBytes = BQ * kBlockK;
     static constexpr int kStageBytes = kPBytes + kQBytes;
-    static constexpr int kStagesRaw = static_cast<int>(kSmemBudget / kStageBytes);
+    // Decode-sized tiles (BQ <= 32) run two CTAs per SM with half the ring each: two independent epilogue
+    // warpgroups hide the split-K hand-off latency.  Larger tiles take the whole SM.
+    static constexpr int kCtasPerSm = BQ <= 32 ? 2 : 1;
+    static constexpr size_t kBudget = kCtasPerSm == 2 ? 100 * 1024 : 200 * 1024;
+    static constexpr int kStagesRaw = static_cast<int>(kBudget / kStageBytes);
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
-    static constexpr uint32_t kTmemCols = 2 * BQ < 32 ? 32 : 2 * BQ;
-    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+    // accumulator buffers in tensor memory (512 columns per SM shared by the resident CTAs)
+    static constexpr int kAccBuffers = BQ <= 32 ? 4 : 2;
+    static constexpr uint32_t kTmemColsRaw = kAccBuffers * BQ;
+    static constexpr uint32_t kTmemCols = kTmemColsRaw < 32 ? 32 : kTmemColsRaw;
+    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
+                                         (BQ > 128 ? BQ * 16 : 0) /*per-column epilogue constants*/;
 };
 
 __device__ __forceinline__ void EpilogueBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory"); }
 
-// Writes one finished accumulator value through the shared epilogue helpers.
+// Generic (slow) store of one finished accumulator through the shared epilogue helpers: every bias mode,
+// Gemm alpha / beta and fused Cast / DequantizeLinear output.
 template <bool INT8>
-__device__ __forceinline__ void StoreOne(const Fp8Epilogue& fe, const Int8Epilogue& ie, int fp8_dtype, int64_t m, int64_t n,
+__device__ __forceinline__ void StoreOne(const Fp8Epilogue& fe, const Int8Epilogue& ie, int e4m3, int64_t m, int64_t n,
                                          uint32_t raw) {
     if constexpr (INT8) {
         StoreInt8Result(ie, m, n, static_cast<int32_t>(raw), 0, 0);
     } else {
-        if (fp8_dtype == FTH_B200_FP8E4M3) StoreFp8Result<FTH_B200_FP8E4M3>(fe, m, n, __uint_as_float(raw));
+        if (e4m3) StoreFp8Result<FTH_B200_FP8E4M3>(fe, m, n, __uint_as_float(raw));
         else StoreFp8Result<FTH_B200_FP8E5M2>(fe, m, n, __uint_as_float(raw));
     }
 }
 
+// INT8 requantisation with an FP32 estimate and an exact fallback.
+//   est = fma(float(acc), float(scale / out_scale), zp) differs from the exact value T by at most
+//   (|T| + |zp|) * 4 * 2^-24 < 1e-4 for |T| <= 300 (three FP32 roundings of relative size 2^-24), and the
+//   reference's double sequence differs from T by less than 1e-12.  So whenever est is farther than 2e-4 from
+//   a rounding boundary x.5 both round to the same integer; the few values inside the band (about 4 in 10^4)
+//   take the exact double sequence.  |est| >= 300 saturates either way.
+__device__ __forceinline__ int8_t RequantFast(int32_t acc, float mult_f, double scale_d, double so_d, int32_t zp) {
+    const float est = fmaf(__int2float_rn(acc), mult_f, static_cast<float>(zp));
+    if (est >= 300.0f) return 127;
+    if (est <= -300.0f) return -128;
+    const float fl = floorf(est);
+    const float frac = est - fl;
+    if (fabsf(frac - 0.5f) < 2e-4f) return RequantExact(__dmul_rn(static_cast<double>(acc), scale_d), so_d, zp);
+    const float r = frac < 0.5f ? fl : fl + 1.0f;
+    return static_cast<int8_t>(static_cast<int32_t>(fmaxf(-128.0f, fminf(127.0f, r))));
+}
+
+// Encodes y0, y1 (already divided by the output scale) into two FP8 codes: low byte = y0, high byte = y1.
+__device__ __forceinline__ uint32_t EncodePair(int e4m3, float y0, float y1) {
+    const bool special = ((__float_as_uint(y0) & 0x7f800000u) == 0x7f800000u) || ((__float_as_uint(y1) & 0x7f800000u) == 0x7f800000u);
+    if (special) {
+        if (e4m3) return Encode<FTH_B200_FP8E4M3>(y0) | (static_cast<uint32_t>(Encode<FTH_B200_FP8E4M3>(y1)) << 8);
+        return Encode<FTH_B200_FP8E5M2>(y0) | (static_cast<uint32_t>(Encode<FTH_B200_FP8E5M2>(y1)) << 8);
+    }
+    uint16_t packed;
+    if (e4m3) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(packed) : "f"(y1), "f"(y0));
+    else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(packed) : "f"(y1), "f"(y0));
+    return packed;
+}
+
 template <bool INT8, bool P_MN, bool Q_MN, int BQ>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, Cfg<BQ>::kCtasPerSm)
 LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, TcParams p,
                     Fp8Epilogue fe, Int8Epilogue ie) {
     using C = Cfg<BQ>;
+    constexpr int kAcc = C::kAccBuffers;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(C::kStages) * C::kStageBytes);
     uint64_t* empty = full + C::kStages;
-    uint64_t* tmem_full = empty + C::kStages;   // [2]
-    uint64_t* tmem_empty = tmem_full + 2;       // [2]
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
-    int32_t* last_flag = reinterpret_cast<int32_t*>(tmem_base_slot + 1);
+    uint64_t* tmem_full = empty + C::kStages;      // [kAcc]
+    uint64_t* tmem_empty = tmem_full + kAcc;       // [kAcc]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + kAcc);
+    // per-column epilogue constants of the current tile (normal mode only): [BQ] doubles, then [BQ] floats
+    double* col_scale = reinterpret_cast<double*>(reinterpret_cast<uint8_t*>(full) + 256);
+    float* col_mult = reinterpret_cast<float*>(col_scale + BQ);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], 4); }
+        for (int b = 0; b < kAcc; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], 4); }
         FenceBarrierInit();
     }
     if (warp == 1) umma::TmemAlloc(tmem_base_slot, C::kTmemCols);
@@ -98,8 +142,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     umma::FenceAfterThreadSync();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    // unit → (p tile, q tile, K chunk); q tile varies fastest after the chunk so CTAs running together share
-    // the same weight rows through L2 in normal mode.
+    // unit → (p tile, q tile, K chunk).  Normal mode walks the activation tiles fastest so the CTAs running
+    // together share one weight column block through L2 and the weights stream from HBM once.
     auto decode_unit = [&](int64_t u, int64_t* pt, int64_t* qt, int* s) {
         *s = static_cast<int>(u % p.split);
         const int64_t t = u / p.split;
@@ -155,8 +199,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 int64_t pt, qt; int s;
                 decode_unit(u, &pt, &qt, &s);
                 const int64_t nb = blocks_of(s);
-                const int acc = static_cast<int>(iter & 1);
-                const uint32_t acc_phase = static_cast<uint32_t>((iter >> 1) & 1);
+                const int acc = static_cast<int>(iter % kAcc);
+                const uint32_t acc_phase = static_cast<uint32_t>((iter / kAcc) & 1);
                 if (!MbarWait(&tmem_empty[acc], acc_phase ^ 1u, p.status, 11, acc)) { failed = true; break; }
                 umma::FenceAfterThreadSync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BQ);
@@ -182,19 +226,125 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         const int et = threadIdx.x - 64;            // 0..127
         const int lane_group = warp & 3;            // TMEM lanes 32*lane_group .. +31 belong to this warp
         const int row = lane_group * 32 + lane;     // row inside the P tile
+        const double so_d = static_cast<double>(ie.out_scale);
+        const float so_f = fe.out_scale;
+        const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
+        uint8_t* out8 = static_cast<uint8_t*>(INT8 ? ie.out : fe.out);
         bool failed = false;
         int64_t iter = 0;
+        int64_t staged_qt = -1;
+
         for (int64_t u = blockIdx.x; u < p.units; u += gridDim.x, ++iter) {
             int64_t pt, qt; int s;
             decode_unit(u, &pt, &qt, &s);
-            const int acc = static_cast<int>(iter & 1);
-            const uint32_t acc_phase = static_cast<uint32_t>((iter >> 1) & 1);
-            if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 13, acc)) failed = true;
-            umma::FenceAfterThreadSync();
+            const int acc = static_cast<int>(iter % kAcc);
+            const uint32_t acc_phase = static_cast<uint32_t>((iter / kAcc) & 1);
             const int64_t pg = pt * kBlockP + row;
+            const bool row_ok = pg < p.p_total;
             const int64_t q_begin = qt * BQ;
             const int64_t q_left = p.q_total - q_begin;
             const int q_count = static_cast<int>(q_left < BQ ? q_left : BQ);
+
+            // ---- scale constants: per lane (swapped: the lane is an output channel) or per column via smem ----
+            double row_scale_d = 0.0;
+            float row_mult = 0.0f;
+            if (p.fast) {
+                if (p.swap) {
+                    if (row_ok) {
+                        if constexpr (INT8) {
+                            row_scale_d = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? pg : 0]);
+                            row_mult = static_cast<float>(row_scale_d / so_d);
+                        } else {
+                            row_mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[pg] : fe.ab_scale;
+                        }
+                    }
+                } else if (qt != staged_qt) {  // uniform across the epilogue warps
+                    EpilogueBarrier();         // readers of the previous tile's constants are done
+                    for (int c = et; c < BQ; c += kEpilogueThreads) {
+                        const int64_t n = q_begin + c;
+                        if (n < p.q_total) {
+                            if constexpr (INT8) {
+                                const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
+                                col_scale[c] = sd;
+                                col_mult[c] = static_cast<float>(sd / so_d);
+                            } else {
+                                col_mult[c] = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
+                            }
+                        }
+                    }
+                    EpilogueBarrier();
+                    staged_qt = qt;
+                }
+            }
+
+            // Turns 16 finished accumulators (columns c0 .. c0+cnt-1 of this thread's row) into output.
+            auto finish = [&](const uint32_t (&v)[16], int c0, int cnt) {
+                if (!p.fast) {
+                    if (row_ok) {
+                        for (int j = 0; j < cnt; ++j) {
+                            const int64_t qg = q_begin + c0 + j;
+                            if (p.swap) StoreOne<INT8>(fe, ie, p.e4m3, qg, pg, v[j]);
+                            else StoreOne<INT8>(fe, ie, p.e4m3, pg, qg, v[j]);
+                        }
+                    }
+                    return;
+                }
+                uint32_t b[16];  // one output byte each
+                if constexpr (INT8) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float mult = p.swap ? row_mult : col_mult[c0 + j];
+                        const double sd = p.swap ? row_scale_d : col_scale[c0 + j];
+                        b[j] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[j]), mult, sd, so_d, ie.out_zp));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const float m0 = p.swap ? row_mult : col_mult[c0 + j];
+                        const float m1 = p.swap ? row_mult : col_mult[c0 + j + 1];
+                        const float y0 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j]), m0), so_f);
+                        const float y1 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j + 1]), m1), so_f);
+                        const uint32_t pair = EncodePair(p.e4m3, y0, y1);
+                        b[j] = pair & 0xffu;
+                        b[j + 1] = pair >> 8;
+                    }
+                }
+                if (!p.swap) {
+                    if (!row_ok) return;
+                    uint8_t* dst = out8 + pg * ldo + q_begin + c0;
+                    if (cnt == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                        uint4 w;
+                        w.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+                        w.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+                        w.z = b[8] | (b[9] << 8) | (b[10] << 16) | (b[11] << 24);
+                        w.w = b[12] | (b[13] << 8) | (b[14] << 16) | (b[15] << 24);
+                        *reinterpret_cast<uint4*>(dst) = w;
+                    } else {
+                        for (int j = 0; j < cnt; ++j) dst[j] = static_cast<uint8_t>(b[j]);
+                    }
+                } else {
+                    // lanes are consecutive output channels: four neighbouring lanes pack one 32-bit store
+                    const int64_t base_pg = pg - (lane & 3);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j >= cnt) break;  // uniform
+                        const uint32_t other1 = __shfl_xor_sync(0xffffffffu, b[j], 1);
+                        const uint32_t pair = (lane & 1) ? (other1 | (b[j] << 8)) : (b[j] | (other1 << 8));
+                        const uint32_t other2 = __shfl_xor_sync(0xffffffffu, pair, 2);
+                        const uint32_t word = (lane & 2) ? (other2 | (pair << 16)) : (pair | (other2 << 16));
+                        uint8_t* dst = out8 + (q_begin + c0 + j) * ldo + base_pg;
+                        const bool group_ok = base_pg + 3 < p.p_total && (reinterpret_cast<uintptr_t>(dst) & 3) == 0;
+                        if (group_ok) {
+                            if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = word;
+                        } else if (row_ok) {
+                            dst[lane & 3] = static_cast<uint8_t>(b[j]);
+                        }
+                    }
+                }
+            };
+
+            if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 13, acc)) failed = true;
+            umma::FenceAfterThreadSync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BQ);
 #pragma unroll 1
             for (int c0 = 0; c0 < BQ; c0 += 16) {
@@ -202,18 +352,12 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 uint32_t v[16];
                 umma::TmemLoad16(taddr + c0, v);
                 umma::TmemLoadWait();
-                if (pg < p.p_total) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j >= q_count) break;
-                        const int64_t qg = q_begin + c0 + j;
-                        if (p.split == 1) {
-                            if (p.swap) StoreOne<INT8>(fe, ie, p.fp8_dtype, qg, pg, v[j]);
-                            else StoreOne<INT8>(fe, ie, p.fp8_dtype, pg, qg, v[j]);
-                        } else {
-                            static_cast<uint32_t*>(p.scratch)[(static_cast<int64_t>(s) * p.q_total + qg) * p.p_pad + pg] = v[j];
-                        }
-                    }
+                const int cnt = q_count - c0 < 16 ? q_count - c0 : 16;
+                if (p.split == 1) {
+                    finish(v, c0, cnt);
+                } else if (row_ok) {
+                    uint32_t* part = static_cast<uint32_t*>(p.scratch);
+                    for (int j = 0; j < cnt; ++j) part[(static_cast<int64_t>(s) * p.q_total + q_begin + c0 + j) * p.p_pad + pg] = v[j];
                 }
             }
             // accumulator buffer drained: hand it back to the MMA warp
@@ -221,38 +365,6 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             __syncwarp();
             if (lane == 0) MbarArrive(&tmem_empty[acc]);
 
-            if (p.split > 1) {
-                __threadfence();
-                EpilogueBarrier();
-                const int64_t tile = pt * p.q_tiles + qt;
-                if (et == 0) {
-                    const int32_t ticket = atomicAdd(&p.counters[tile], 1);
-                    *last_flag = (ticket == p.split - 1);
-                    if (ticket == p.split - 1) p.counters[tile] = 0;
-                }
-                EpilogueBarrier();
-                if (*last_flag && pg < p.p_total) {
-                    __threadfence();
-                    for (int c = 0; c < q_count; ++c) {
-                        const int64_t qg = q_begin + c;
-                        uint32_t raw;
-                        if constexpr (INT8) {
-                            int32_t sum = 0;
-                            for (int ss = 0; ss < p.split; ++ss)
-                                sum += __ldcg(&static_cast<const int32_t*>(p.scratch)[(static_cast<int64_t>(ss) * p.q_total + qg) * p.p_pad + pg]);
-                            raw = static_cast<uint32_t>(sum);
-                        } else {
-                            float sum = 0.0f;
-                            for (int ss = 0; ss < p.split; ++ss)
-                                sum += __ldcg(&static_cast<const float*>(p.scratch)[(static_cast<int64_t>(ss) * p.q_total + qg) * p.p_pad + pg]);
-                            raw = __float_as_uint(sum);
-                        }
-                        if (p.swap) StoreOne<INT8>(fe, ie, p.fp8_dtype, qg, pg, raw);
-                        else StoreOne<INT8>(fe, ie, p.fp8_dtype, pg, qg, raw);
-                    }
-                }
-                EpilogueBarrier();
-            }
         }
     }
 
@@ -261,6 +373,64 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     if (warp == 1) {
         umma::FenceAfterThreadSync();
         umma::TmemDealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+
+// Second pass of the split-K path (swapped tiling only: rows p are output channels n, columns q are
+// activation rows m).  One thread owns four consecutive channels of one activation row: it adds the S partial
+// accumulators in chunk order (the same order whatever the grid was), runs the epilogue and stores 4 bytes.
+template <bool INT8>
+__global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue fe, Int8Epilogue ie) {
+    const int64_t groups = p.p_pad / 4;
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= groups * p.q_total) return;
+    const int64_t q = idx / groups;
+    const int64_t p4 = (idx % groups) * 4;
+    if (p4 >= p.p_total) return;
+    const uint4* part = static_cast<const uint4*>(p.scratch);
+    uint32_t v[4];
+    if constexpr (INT8) {
+        int32_t sum[4] = {0, 0, 0, 0};
+        for (int ss = 0; ss < p.split; ++ss) {
+            const uint4 t = __ldcg(&part[((static_cast<int64_t>(ss) * p.q_total + q) * p.p_pad + p4) / 4]);
+            sum[0] += static_cast<int32_t>(t.x); sum[1] += static_cast<int32_t>(t.y);
+            sum[2] += static_cast<int32_t>(t.z); sum[3] += static_cast<int32_t>(t.w);
+        }
+        for (int i = 0; i < 4; ++i) v[i] = static_cast<uint32_t>(sum[i]);
+    } else {
+        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int ss = 0; ss < p.split; ++ss) {
+            const uint4 t = __ldcg(&part[((static_cast<int64_t>(ss) * p.q_total + q) * p.p_pad + p4) / 4]);
+            sum[0] += __uint_as_float(t.x); sum[1] += __uint_as_float(t.y);
+            sum[2] += __uint_as_float(t.z); sum[3] += __uint_as_float(t.w);
+        }
+        for (int i = 0; i < 4; ++i) v[i] = __float_as_uint(sum[i]);
+    }
+    if (!p.fast) {
+        for (int i = 0; i < 4; ++i)
+            if (p4 + i < p.p_total) StoreOne<INT8>(fe, ie, p.e4m3, q, p4 + i, v[i]);
+        return;
+    }
+    uint32_t b[4];
+    for (int i = 0; i < 4; ++i) {
+        const int64_t n = p4 + i < p.p_total ? p4 + i : p.p_total - 1;
+        if constexpr (INT8) {
+            const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
+            const double so_d = static_cast<double>(ie.out_scale);
+            b[i] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[i]), static_cast<float>(sd / so_d), sd, so_d, ie.out_zp));
+        } else {
+            const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
+            const float y = __fdiv_rn(__fmul_rn(__uint_as_float(v[i]), mult), fe.out_scale);
+            b[i] = p.e4m3 ? Encode<FTH_B200_FP8E4M3>(y) : Encode<FTH_B200_FP8E5M2>(y);
+        }
+    }
+    const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
+    uint8_t* dst = static_cast<uint8_t*>(INT8 ? ie.out : fe.out) + q * ldo + p4;
+    if (p4 + 3 < p.p_total && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+        *reinterpret_cast<uint32_t*>(dst) = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    } else {
+        for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) dst[i] = static_cast<uint8_t>(b[i]);
     }
 }
 
@@ -295,7 +465,6 @@ TcGeometry GeometryFor(const LinearArgs& a) {
     return g;
 }
 
-size_t CounterBytes(const TcGeometry& g) { return static_cast<size_t>((g.p_tiles * g.q_tiles * 4 + 255) / 256 * 256); }
 
 int SmCountTc() {
     static int count = 0;
@@ -316,7 +485,8 @@ int LaunchTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcPara
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg<BQ>::kSmemBytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
         configured = true;
     }
-    const int grid = static_cast<int>(p.units < SmCountTc() ? p.units : SmCountTc());
+    const int64_t slots = static_cast<int64_t>(SmCountTc()) * Cfg<BQ>::kCtasPerSm;
+    const int grid = static_cast<int>(p.units < slots ? p.units : slots);
     kernel<<<grid, kThreads, Cfg<BQ>::kSmemBytes, stream>>>(map_p, map_q, p, fe, ie);
     NoteLaunch("tcgen05");
     return CheckLaunch();
@@ -357,7 +527,7 @@ size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& a) {
     (void)dtype;
     const TcGeometry g = GeometryFor(a);
     if (g.split == 1) return 0;
-    return CounterBytes(g) + static_cast<size_t>(g.split) * g.q_total * g.p_pad * 4;
+    return static_cast<size_t>(g.split) * g.q_total * g.p_pad * 4;
 }
 
 int LaunchLinearTcgen05(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* scratch,
@@ -385,17 +555,25 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, c
     p.p_total = g.p_total; p.q_total = g.q_total; p.p_tiles = g.p_tiles; p.q_tiles = g.q_tiles;
     p.split = g.split; p.chunk_blocks = g.chunk_blocks; p.k_blocks = g.k_blocks; p.units = g.units;
     p.p_pad = g.p_pad;
-    p.fp8_dtype = dtype;
-    p.counters = static_cast<int32_t*>(scratch);
-    p.scratch = scratch ? static_cast<uint8_t*>(scratch) + CounterBytes(g) : nullptr;
+    p.e4m3 = dtype == FTH_B200_FP8E4M3;
+    if (int8) p.fast = ie.bias_mode == FTH_B200_BIAS_NONE && ie.out_dtype == 0 && !(ie.is_gemm && (ie.alpha != 1.0f || ie.beta != 1.0f));
+    else p.fast = fe.bias_mode == FTH_B200_BIAS_NONE && fe.out_dtype == 0 && !(fe.is_gemm && fe.alpha != 1.0f);
+    p.scratch = scratch;
     p.status = DeviceStatusPtr();
     // operand formats: kind::f8f6f4 0 = E4M3, 1 = E5M2; kind::i8 1 = signed 8-bit.  D: 1 = F32, 2 = S32.
     const uint32_t fmt = int8 ? 1u : (dtype == FTH_B200_FP8E5M2 ? 1u : 0u);
     const bool p_mn = g.swap && weights_mn;
     const bool q_mn = !g.swap && weights_mn;
     p.idesc = umma::InstrDesc(int8 ? 2u : 1u, fmt, fmt, p_mn, q_mn, kBlockP, static_cast<uint32_t>(g.bq));
-    return int8 ? LaunchForLayout<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
-                : LaunchForLayout<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
+    const int rc = int8 ? LaunchForLayout<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
+                        : LaunchForLayout<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
+    if (rc != FTH_B200_OK || g.split == 1) return rc;
+    const int64_t threads = (g.p_pad / 4) * g.q_total;
+    const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+    if (int8) SplitReduceKernel<true><<<blocks, 256, 0, stream>>>(p, fe, ie);
+    else SplitReduceKernel<false><<<blocks, 256, 0, stream>>>(p, fe, ie);
+    NoteLaunch("tcgen05");
+    return CheckLaunch();
 }
 
 }  // namespace fth

@@ -6,6 +6,14 @@ import numpy as np
 import infer_b200 as B
 
 
+def _skip_if_declined(fn, desc, variant):
+    """A forced kernel family may decline a shape (ERR_UNSUPPORTED); the AUTO split never does."""
+    import ctypes
+    import pytest
+    if variant != B.VARIANT_AUTO and fn(ctypes.byref(desc)) == B.ERR_UNSUPPORTED:
+        pytest.skip("this kernel family declines the shape")
+
+
 def dev(torch, arr):
     return None if arr is None else torch.from_numpy(np.ascontiguousarray(arr)).cuda()
 
@@ -33,6 +41,7 @@ def run_fp8_linear(torch, dtype, op, case, *, trans_b=False, variant=B.VARIANT_A
                           bias_mode=bias_mode, bias_scale=case["sb"], alpha=alpha, beta=beta, a_dtype=a_dtype,
                           out_dtype=out_dtype, ldo=ldo, w_channel_scales=wcs, variant=variant)
     ws_keep = B.linear_workspace(torch, d) if workspace else None
+    _skip_if_declined(B.lib().fth_b200_fp8_linear_supported, d, variant)
     B.fp8_linear(d)
     torch.cuda.synchronize()
     host = buf.cpu().numpy().view(np_out)
@@ -63,6 +72,7 @@ def run_int8_linear(torch, op, case, *, trans_b=False, variant=B.VARIANT_AUTO, a
                            beta=beta, a_dtype=a_dtype, out_dtype=out_dtype, w_zp_max_abs=zmax,
                            bias_max_abs=bias_max, variant=variant)
     ws_keep = B.linear_workspace(torch, d) if workspace else None
+    _skip_if_declined(B.lib().fth_b200_int8_linear_supported, d, variant)
     B.int8_linear(d)
     torch.cuda.synchronize()
     host = buf.cpu().numpy()

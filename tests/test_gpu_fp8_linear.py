@@ -15,7 +15,10 @@ pytestmark = pytest.mark.gpu
 DTYPES = [O.E4M3, O.E5M2]
 
 
-def check_codes(got, want, dtype, what):
+def check_codes(got, want, dtype, what, case=None, trans_b=False):
+    """Tolerance: one output code.  Near zero the FP8 codes are far denser than FP32 accumulation error
+    (two FP32 summation orders of 8192 terms already differ by several subnormal codes there), so an output
+    also passes when its value is within the FP32 accumulation bound 2^-20 * sum_k |a_k w_k| of the oracle's."""
     dist = util.fp8_code_distance(got, want)
     # Non-finite class must match exactly: same Inf code, NaN code up to its sign bit (the sign of a NaN made
     # by arithmetic, e.g. 0 x Inf, is a host-FPU convention: x86 generates it negative, the GPU positive).
@@ -24,12 +27,18 @@ def check_codes(got, want, dtype, what):
     assert np.array_equal(got[special & ~nan], want[special & ~nan]), f"{what}: Inf codes differ"
     assert np.array_equal(got[nan] & 0x7F, want[nan] & 0x7F), f"{what}: NaN codes differ"
     dist = np.where(nan, 0, dist)
+    if dist.max() > 1 and case is not None:
+        a = np.abs(O.fp8_decode(dtype, case["a"]).astype(np.float64)) * case["sa"]
+        w = np.abs(O.fp8_decode(dtype, case["w"]).astype(np.float64)) * case["sw"]
+        bound = (a @ (w.T if trans_b else w)) * 2.0 ** -20
+        err = np.abs(O.fp8_decode(dtype, got).astype(np.float64) - O.fp8_decode(dtype, want).astype(np.float64)) * case["so"]
+        dist = np.where((dist > 1) & (err <= bound), 1, dist)
     assert dist.max() <= 1, f"{what}: max code distance {dist.max()} (> 1), {int((dist > 1).sum())} outputs"
     return int((dist > 0).sum())
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_STREAM])
+@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_STREAM, B.VARIANT_TCGEN05])
 @pytest.mark.parametrize("m,k,n", [(1, 1024, 3072), (2, 1024, 1024), (3, 3584, 1024), (4, 1024, 3584), (16, 512, 256),
                                    (1, 48, 16), (5, 130, 272), (1, 8192, 512), (2, 200, 400), (1, 8192, 1040)])
 def test_matmul_kn(cuda, dtype, variant, m, k, n):
@@ -42,7 +51,7 @@ def test_matmul_kn(cuda, dtype, variant, m, k, n):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY])
+@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_TCGEN05])
 @pytest.mark.parametrize("m,k,n", [(1, 1024, 3072), (2, 1024, 1000), (4, 2048, 77), (7, 528, 19), (1, 8192, 640)])
 def test_gemm_trans_b(cuda, dtype, variant, m, k, n):
     case = util.make_fp8_linear(dtype, m, k, n, seed=k + n, trans_b=True, bias_mode=1)
@@ -78,7 +87,7 @@ def test_nonfinite_codes_propagate(cuda):
     """E5M2 Inf in an operand reaches the output as the Inf code 0x7C; E4M3 NaN as 0x7F
     (reference test/x86_fp8_linear_test.cc:142-156)."""
     for dtype, code in ((O.E5M2, 0x7C), (O.E4M3, 0x7F)):
-        for variant in (B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_STREAM):
+        for variant in (B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_STREAM, B.VARIANT_TCGEN05):
             case = util.make_fp8_linear(dtype, 1, 64, 32, seed=9)
             case["a"][:] = O.fp8_encode(dtype, np.ones((1, 64), np.float32))
             case["w"][:] = O.fp8_encode(dtype, np.ones((64, 32), np.float32))
@@ -172,3 +181,17 @@ def test_stream_workspace_is_left_clean_and_reusable(cuda, dtype):
     B.fp8_linear(ds)
     cuda.cuda.synchronize()
     assert np.array_equal(out_s.cpu().numpy(), full[:, 256:768])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,k,n,trans_b", [(16, 8192, 2048, False), (64, 1024, 1024, False), (128, 1024, 1024, True),
+                                           (300, 512, 528, False), (257, 2048, 272, True), (33, 4096, 640, False)])
+def test_tensor_core_path_shapes(cuda, dtype, m, k, n, trans_b):
+    """Dense and mid-size shapes on tcgen05: both weight layouts, swapped (M <= 128) and normal tiling, ragged
+    M and N tails handled by TMA zero fill."""
+    case = util.make_fp8_linear(dtype, m, k, n, seed=m + n, trans_b=trans_b)
+    op = B.OP_GEMM if trans_b else B.OP_MATMUL
+    want = O.fp8_linear(op, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"], trans_b=trans_b)
+    got = run_fp8_linear(cuda, dtype, op, case, trans_b=trans_b, variant=B.VARIANT_TCGEN05)
+    assert B.last_variant() == "tcgen05" and B.device_status() == 0
+    check_codes(got, want, dtype, f"tcgen05 {m}x{k}x{n}", case=case, trans_b=trans_b)

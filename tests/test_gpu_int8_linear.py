@@ -16,7 +16,7 @@ def oracle_int8(op, case, **kw):
                          case["out_zp"], bias=case["bias"], **kw)
 
 
-@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_STREAM])
+@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_STREAM, B.VARIANT_TCGEN05])
 @pytest.mark.parametrize("m,k,n", [(1, 1024, 3072), (2, 1024, 1024), (4, 8192, 512), (16, 512, 256), (3, 100, 48), (1, 4, 16), (3, 8192, 1040)])
 @pytest.mark.parametrize("zero_points", [False, True])
 def test_matmul_kn(cuda, variant, m, k, n, zero_points):
@@ -28,7 +28,7 @@ def test_matmul_kn(cuda, variant, m, k, n, zero_points):
     assert np.array_equal(got, want), f"{int((got != want).sum())} of {want.size} bytes differ"
 
 
-@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY])
+@pytest.mark.parametrize("variant", [B.VARIANT_SIMT, B.VARIANT_SKINNY, B.VARIANT_TCGEN05])
 @pytest.mark.parametrize("m,k,n", [(1, 1024, 3072), (2, 2048, 1000), (5, 528, 19), (16, 256, 77)])
 @pytest.mark.parametrize("zero_points", [False, True])
 def test_gemm_trans_b(cuda, variant, m, k, n, zero_points):
@@ -117,3 +117,36 @@ def test_overflow_and_rejections(cuda):
     assert f(C.byref(B.int8_linear_desc(**{**base, "bias_max_abs": 2 ** 31}))) == B.ERR_OVERFLOW
     for bad in (dict(a_scale=-1.0), dict(out_zp=200), dict(w_params=3), dict(w_scales=None), dict(trans_b=True)):
         assert f(C.byref(B.int8_linear_desc(**{**base, **bad}))) == B.ERR_INVALID, bad
+
+
+@pytest.mark.parametrize("m,k,n,trans_b", [(16, 8192, 2048, False), (64, 1024, 1024, False), (128, 1024, 1024, True),
+                                           (300, 512, 528, False), (257, 2048, 272, True), (33, 4096, 640, False)])
+@pytest.mark.parametrize("per_channel", [True, False])
+def test_tensor_core_path_shapes(cuda, m, k, n, trans_b, per_channel):
+    """kind::i8 MMA with int32 TMEM accumulators and the estimate-plus-exact-fallback requantisation: bit-exact."""
+    case = util.make_int8_linear(m, k, n, seed=m + n, trans_b=trans_b, per_channel=per_channel)
+    op = B.OP_GEMM if trans_b else B.OP_MATMUL
+    want = oracle_int8(op, case, trans_b=trans_b)
+    got = run_int8_linear(cuda, op, case, trans_b=trans_b, variant=B.VARIANT_TCGEN05)
+    assert B.last_variant() == "tcgen05" and B.device_status() == 0
+    assert np.array_equal(got, want), f"{int((got != want).sum())} of {want.size} bytes differ"
+
+
+def test_tensor_core_requant_near_ties(cuda):
+    """Accumulators that land exactly on and right next to x.5 after scaling: the FP32 estimate must hand
+    them to the exact double sequence (ties round away from zero)."""
+    k, n = 64, 128
+    a = np.zeros((130, k), np.int8)
+    a[:, 0] = np.arange(-65, 65)
+    a[:, 1] = 1
+    w = np.zeros((k, n), np.int8)
+    w[0, :] = 1
+    w[1, :] = np.arange(n) % 3
+    case = dict(a=a, w=w, bias=None, sa=1.0, a_zp=0, ws=np.full(n, 1.0, np.float32), w_zps=None, so=2.0, out_zp=0)
+    want = oracle_int8(O.OP_MATMUL, case)
+    got = run_int8_linear(cuda, B.OP_MATMUL, case, variant=B.VARIANT_TCGEN05)
+    assert np.array_equal(got, want)
+    case["ws"] = np.full(n, np.float32(1.0000001), np.float32)
+    want = oracle_int8(O.OP_MATMUL, case)
+    got = run_int8_linear(cuda, B.OP_MATMUL, case, variant=B.VARIANT_TCGEN05)
+    assert np.array_equal(got, want)
