@@ -241,7 +241,7 @@ def run_gpu_arm(args):
         if rc != 0:
             raise RuntimeError(f"fth_b200_fp8_linear failed: {rc}")
         if world > 1:
-            dist.all_gather_into_tensor(gathered, local_out)
+            dist.all_gather_into_tensor(gathered.view(world, width), local_out)
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -279,7 +279,7 @@ def run_gpu_arm(args):
         pc[0] += 1
         if world > 1:
             local_out.copy_(out_host, non_blocking=True)
-            dist.all_gather_into_tensor(gathered, local_out)
+            dist.all_gather_into_tensor(gathered.view(world, width), local_out)
 
     e2e_steps = min(args.steps, 500)
     e2e_ms = event_time_ms(torch, e2e_step, e2e_steps, max(args.warmup, 3), barrier) / e2e_steps

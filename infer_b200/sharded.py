@@ -60,8 +60,9 @@ class ShardedLinear:
         self.compute(a, local_out)
         if self.world == 1:
             return local_out[:, : self.n1 - self.n0]
-        self.dist.all_gather_into_tensor(gathered, local_out)
         m = local_out.shape[0]
+        # concatenation along dim 0: rank r's [M, width] block lands at rows r*M .. (r+1)*M
+        self.dist.all_gather_into_tensor(gathered.view(self.world * m, self.width), local_out)
         if self.equal and m == 1:
             return gathered.view(1, self.n)
         if self.equal:
