@@ -141,12 +141,25 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     __syncthreads();
     umma::FenceAfterThreadSync();
     const uint32_t tmem_base = *tmem_base_slot;
+    // Lets a dependent grid (the split-K reduce pass) be scheduled while this one runs; it still waits for this
+    // grid to finish before it reads anything.  No effect when launched without programmatic serialization.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // unit → (p tile, q tile, K chunk).  Normal mode walks the activation tiles fastest so the CTAs running
     // together share one weight column block through L2 and the weights stream from HBM once.
+    // Swapped mode with [K,N] weights walks the column tiles fastest (chunk-major): the CTAs running together
+    // then read whole contiguous weight rows of one K range, which keeps DRAM pages open; with [N,K] weights the
+    // chunks of one tile are the contiguous direction, so the chunk index varies fastest instead.
     auto decode_unit = [&](int64_t u, int64_t* pt, int64_t* qt, int* s) {
-        *s = static_cast<int>(u % p.split);
-        const int64_t t = u / p.split;
+        int64_t t;
+        if (P_MN) {
+            const int64_t tiles = p.p_tiles * p.q_tiles;
+            *s = static_cast<int>(u / tiles);
+            t = u % tiles;
+        } else {
+            *s = static_cast<int>(u % p.split);
+            t = u / p.split;
+        }
         if (p.swap) { *qt = t % p.q_tiles; *pt = t / p.q_tiles; }
         else { *pt = t % p.p_tiles; *qt = t / p.p_tiles; }
     };
@@ -382,6 +395,9 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 // accumulators in chunk order (the same order whatever the grid was), runs the epilogue and stores 4 bytes.
 template <bool INT8>
 __global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue fe, Int8Epilogue ie) {
+    // Launched with programmatic stream serialization: wait until the producing grid has completed and its
+    // partial sums are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t groups = p.p_pad / 4;
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (idx >= groups * p.q_total) return;
@@ -476,6 +492,23 @@ int SmCountTc() {
     return count;
 }
 
+// Encoding a tensor map costs a few microseconds of host time; decode steps call the same (pointer, shape)
+// pairs over and over, so the last few encodings are kept per host thread.
+bool CachedMap(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols, uint32_t box_rows) {
+    struct Entry { const void* base; uint64_t cols, rows; uint32_t bc, br; CUtensorMap map; };
+    thread_local Entry cache[16] = {};
+    thread_local int next = 0;
+    for (const Entry& e : cache) {
+        if (e.base == base && e.cols == cols && e.rows == rows && e.bc == box_cols && e.br == box_rows) { *out = e.map; return true; }
+    }
+    CUtensorMap map;
+    if (!MakeTensorMap2D(&map, base, cols, rows, cols, box_cols, box_rows, TmaSwizzle::k128B)) return false;
+    cache[next] = Entry{base, cols, rows, box_cols, box_rows, map};
+    next = (next + 1) % 16;
+    *out = map;
+    return true;
+}
+
 template <bool INT8, bool P_MN, bool Q_MN, int BQ>
 int LaunchTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p, const Fp8Epilogue& fe,
                 const Int8Epilogue& ie, cudaStream_t stream) {
@@ -541,10 +574,10 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, c
     CUtensorMap map_w, map_a, map_p, map_q;
     const uint32_t w_rows_box = g.swap ? kBlockP : 256;
     bool ok;
-    if (weights_mn) ok = MakeTensorMap2D(&map_w, a.w, static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), 128, 128, TmaSwizzle::k128B);
-    else ok = MakeTensorMap2D(&map_w, a.w, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k), 128, w_rows_box, TmaSwizzle::k128B);
-    ok = ok && MakeTensorMap2D(&map_a, a.a, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m), static_cast<uint64_t>(a.k), 128,
-                               g.swap ? static_cast<uint32_t>(g.bq) : kBlockP, TmaSwizzle::k128B);
+    if (weights_mn) ok = CachedMap(&map_w, a.w, static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k), 128, 128);
+    else ok = CachedMap(&map_w, a.w, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), 128, w_rows_box);
+    ok = ok && CachedMap(&map_a, a.a, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m), 128,
+                         g.swap ? static_cast<uint32_t>(g.bq) : kBlockP);
     if (!ok) return FTH_B200_ERR_CUDA;
     map_p = g.swap ? map_w : map_a;
     map_q = g.swap ? map_a : map_w;
@@ -570,8 +603,18 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, c
     if (rc != FTH_B200_OK || g.split == 1) return rc;
     const int64_t threads = (g.p_pad / 4) * g.q_total;
     const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
-    if (int8) SplitReduceKernel<true><<<blocks, 256, 0, stream>>>(p, fe, ie);
-    else SplitReduceKernel<false><<<blocks, 256, 0, stream>>>(p, fe, ie);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = int8 ? cudaLaunchKernelEx(&cfg, SplitReduceKernel<true>, p, fe, ie)
+                                 : cudaLaunchKernelEx(&cfg, SplitReduceKernel<false>, p, fe, ie);
+    if (err != cudaSuccess) return FTH_B200_ERR_CUDA;
     NoteLaunch("tcgen05");
     return CheckLaunch();
 }
