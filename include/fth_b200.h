@@ -42,7 +42,8 @@ enum {
     FTH_B200_ERR_UNSUPPORTED = -2, /* valid request this backend declines (→ StatusCode::kUnsupported) */
     FTH_B200_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed */
     FTH_B200_ERR_OVERFLOW = -4,    /* K·255·255 + max|bias| may leave int32 (int8_kernel_utils.h:99-114) */
-    FTH_B200_ERR_TIMEOUT = -5      /* a bounded device-side wait gave up (read from a status word) */
+    FTH_B200_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up (read from a status word) */
+    FTH_B200_ERR_SCRATCH_LIMIT = -6 /* fth_b200_fp8_linear_noalloc: the shape needs more than the built-in scratch */
 };
 
 /* Operator flavour: decides how bias / alpha / beta enter (FC and MatMul: alpha = beta = 1). */
@@ -118,6 +119,23 @@ int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t 
 /* Capability check only (what Supports() calls): 0 if fth_b200_fp8_linear would run this descriptor. */
 int fth_b200_fp8_linear_supported(const fth_b200_fp8_linear_desc* desc);
 size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc);
+
+/* FP8 linear for callers that cannot hand over a scratch buffer because they may not allocate one: a Feather
+ * node built with a workspace limit of zero, or a session whose device memory was fixed when its plan was
+ * compiled.  No counterpart in the reference.  Same contract and results as fth_b200_fp8_linear on the
+ * tensor-core kernel family (desc->variant, workspace and workspace_bytes are ignored), but the split-K
+ * partial sums go to an array built into the library image — fth_b200_noalloc_scratch_bytes() = 4 MiB of device
+ * global memory that every GPU which loads the library holds until the process exits.  The call allocates
+ * nothing and frees nothing.
+ *   - A shape whose partial sums do not fit (fth_b200_fp8_linear_workspace_bytes > 4 MiB; for K >= 1024, M = 1 fits up to
+ *     N = 65536 and M = 16 up to N = 8192) returns FTH_B200_ERR_SCRATCH_LIMIT; shapes the tensor-core
+ *     family declines return FTH_B200_ERR_UNSUPPORTED.
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress) with that device
+ *     current; make that first call before starting any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it has to start at zero and a call reads only
+ *     what it wrote itself, but two calls that overlap on the GPU (different streams, no ordering) race. */
+int fth_b200_fp8_linear_noalloc(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t stream);
+size_t fth_b200_noalloc_scratch_bytes(void);
 
 /* -------------------------------------------------------------------------------------------------
  * INT8 FC, MatMul, Gemm (bit-exact with the Common kernels).

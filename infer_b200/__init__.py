@@ -18,12 +18,12 @@ INT8, FP16, FP32, INT32, BF16, E4M3, E5M2 = 1, 3, 4, 5, 11, 12, 13
 OP_FC, OP_MATMUL, OP_GEMM = 0, 1, 2
 BIAS_NONE, BIAS_VECTOR, BIAS_MATRIX = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_SKINNY, VARIANT_TCGEN05, VARIANT_STREAM = 0, 1, 2, 3, 4
-OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_OVERFLOW, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_OVERFLOW, ERR_TIMEOUT, ERR_SCRATCH_LIMIT = 0, -1, -2, -3, -4, -5, -6
 
 EXPORTS = [
     "fth_b200_abi_version", "fth_b200_last_variant", "fth_b200_launch_count", "fth_b200_reset_launch_count",
     "fth_b200_fp8_linear", "fth_b200_fp8_linear_supported", "fth_b200_fp8_linear_workspace_bytes",
-    "fth_b200_device_status",
+    "fth_b200_device_status", "fth_b200_fp8_linear_noalloc", "fth_b200_noalloc_scratch_bytes",
     "fth_b200_int8_linear", "fth_b200_int8_linear_supported", "fth_b200_int8_linear_workspace_bytes",
     "fth_b200_int8_conv2d", "fth_b200_int8_conv2d_supported", "fth_b200_int8_conv2d_workspace_bytes",
     "fth_b200_int8_relu_table", "fth_b200_int8_lookup",
@@ -88,6 +88,7 @@ def lib():
         handle.fth_b200_int8_conv2d_workspace_bytes.restype = C.c_size_t
         handle.fth_b200_fp8_linear_workspace_bytes.restype = C.c_size_t
         handle.fth_b200_int8_linear_workspace_bytes.restype = C.c_size_t
+        handle.fth_b200_noalloc_scratch_bytes.restype = C.c_size_t
         handle.fth_b200_plan_input_bytes.restype = C.c_int64
         handle.fth_b200_plan_output_bytes.restype = C.c_int64
         handle.fth_b200_plan_input_bytes.argtypes = [C.c_void_p]
