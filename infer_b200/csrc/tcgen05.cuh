@@ -33,6 +33,17 @@ __device__ __forceinline__ void FenceAfterThreadSync() { asm volatile("tcgen05.f
 // MN-major operand ([k rows][128 bytes of M or N], the TMA box {128, k rows}): one k row holds 128 consecutive
 // M/N elements; 8 k rows form a 1024-byte group (stride offset); further 128-element M/N blocks lie
 // `leading` bytes away.  Successive K = 32 slices advance the start address by 32 rows = 4096 bytes.
+// The same descriptor for a 64-byte swizzle (layout type 4): rows of 64 bytes, 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t SmemDescSw64(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((leading_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((stride_bytes >> 4) & 0x3fffu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(4) << 61;
+    return d;
+}
+
 __device__ __forceinline__ uint64_t SmemDesc(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);

@@ -64,5 +64,6 @@ def test_conv_config3_full_size(cuda):
     want = O.int8_relu(conv, case["so"], 0, case["so"], 0)
     lut = B.int8_relu_table(case["so"], 0, case["so"], 0)
     got = run_int8_conv(cuda, case, relu_lut=lut)
+    assert B.last_variant() == "conv_tcgen05" and B.device_status() == 0
     assert np.array_equal(got, want)
     assert np.array_equal(run_int8_conv(cuda, case), conv)
