@@ -27,8 +27,6 @@ namespace {
 
 constexpr int kBlockP = 128;
 constexpr int kBlockK = 128;  // bytes of K per ring stage = one 128-byte swizzle row
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
 constexpr int kPBytes = kBlockP * kBlockK;
 constexpr size_t kSmemBudget = 200 * 1024;
 
@@ -63,11 +61,16 @@ struct Cfg {
     static constexpr int kAccBuffers = BQ <= 32 ? 4 : 2;
     static constexpr uint32_t kTmemColsRaw = kAccBuffers * BQ;
     static constexpr uint32_t kTmemCols = kTmemColsRaw < 32 ? 32 : kTmemColsRaw;
+    // Dense tiles (BQ = 256) use two epilogue warpgroups, each draining 128 of the 256 accumulator columns.
+    static constexpr int kEpilogueGroups = BQ > 128 ? 2 : 1;
+    static constexpr int kEpilogueThreads = 128 * kEpilogueGroups;
+    static constexpr int kThreads = 64 + kEpilogueThreads;
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
                                          (BQ > 128 ? BQ * 16 : 0) /*per-column epilogue constants*/;
 };
 
-__device__ __forceinline__ void EpilogueBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory"); }
+template <int THREADS>
+__device__ __forceinline__ void EpilogueBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
 
 // Generic (slow) store of one finished accumulator through the shared epilogue helpers: every bias mode,
 // Gemm alpha / beta and fused Cast / DequantizeLinear output.
@@ -113,7 +116,7 @@ __device__ __forceinline__ uint32_t EncodePair(int e4m3, float y0, float y1) {
 }
 
 template <bool INT8, bool P_MN, bool Q_MN, int BQ>
-__global__ void __launch_bounds__(kThreads, Cfg<BQ>::kCtasPerSm)
+__global__ void __launch_bounds__(Cfg<BQ>::kThreads, Cfg<BQ>::kCtasPerSm)
 LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, TcParams p,
                     Fp8Epilogue fe, Int8Epilogue ie) {
     using C = Cfg<BQ>;
@@ -133,7 +136,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
-        for (int b = 0; b < kAcc; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], 4); }
+        for (int b = 0; b < kAcc; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], 4 * C::kEpilogueGroups); }
         FenceBarrierInit();
     }
     if (warp == 1) umma::TmemAlloc(tmem_base_slot, C::kTmemCols);
@@ -236,8 +239,10 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         }
     } else {
         // ================================ epilogue ================================
-        const int et = threadIdx.x - 64;            // 0..127
+        const int et = threadIdx.x - 64;            // 0 .. kEpilogueThreads-1
         const int lane_group = warp & 3;            // TMEM lanes 32*lane_group .. +31 belong to this warp
+        const int col_group = (warp - 2) / 4;       // which 128-column half of a dense tile this warpgroup drains
+        constexpr int kColsPerGroup = BQ / C::kEpilogueGroups;
         const int row = lane_group * 32 + lane;     // row inside the P tile
         const double so_d = static_cast<double>(ie.out_scale);
         const float so_f = fe.out_scale;
@@ -272,8 +277,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                         }
                     }
                 } else if (qt != staged_qt) {  // uniform across the epilogue warps
-                    EpilogueBarrier();         // readers of the previous tile's constants are done
-                    for (int c = et; c < BQ; c += kEpilogueThreads) {
+                    EpilogueBarrier<C::kEpilogueThreads>();  // readers of the previous tile's constants are done
+                    for (int c = et; c < BQ; c += C::kEpilogueThreads) {
                         const int64_t n = q_begin + c;
                         if (n < p.q_total) {
                             if constexpr (INT8) {
@@ -285,7 +290,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                             }
                         }
                     }
-                    EpilogueBarrier();
+                    EpilogueBarrier<C::kEpilogueThreads>();
                     staged_qt = qt;
                 }
             }
@@ -360,8 +365,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             umma::FenceAfterThreadSync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BQ);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BQ; c0 += 16) {
-                if (c0 >= q_count) break;  // uniform across the CTA
+            for (int c0 = col_group * kColsPerGroup; c0 < (col_group + 1) * kColsPerGroup; c0 += 16) {
+                if (c0 >= q_count) break;  // uniform across the warp
                 uint32_t v[16];
                 umma::TmemLoad16(taddr + c0, v);
                 umma::TmemLoadWait();
@@ -408,18 +413,28 @@ __global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue
     uint32_t v[4];
     if constexpr (INT8) {
         int32_t sum[4] = {0, 0, 0, 0};
-        for (int ss = 0; ss < p.split; ++ss) {
-            const uint4 t = __ldcg(&part[((static_cast<int64_t>(ss) * p.q_total + q) * p.p_pad + p4) / 4]);
-            sum[0] += static_cast<int32_t>(t.x); sum[1] += static_cast<int32_t>(t.y);
-            sum[2] += static_cast<int32_t>(t.z); sum[3] += static_cast<int32_t>(t.w);
+        uint4 t[8];
+#pragma unroll
+        for (int ss = 0; ss < 8; ++ss)  // all loads in flight before the first add
+            t[ss] = ss < p.split ? __ldcg(&part[((static_cast<int64_t>(ss) * p.q_total + q) * p.p_pad + p4) / 4]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int ss = 0; ss < 8; ++ss) {
+            sum[0] += static_cast<int32_t>(t[ss].x); sum[1] += static_cast<int32_t>(t[ss].y);
+            sum[2] += static_cast<int32_t>(t[ss].z); sum[3] += static_cast<int32_t>(t[ss].w);
         }
         for (int i = 0; i < 4; ++i) v[i] = static_cast<uint32_t>(sum[i]);
     } else {
         float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int ss = 0; ss < p.split; ++ss) {
-            const uint4 t = __ldcg(&part[((static_cast<int64_t>(ss) * p.q_total + q) * p.p_pad + p4) / 4]);
-            sum[0] += __uint_as_float(t.x); sum[1] += __uint_as_float(t.y);
-            sum[2] += __uint_as_float(t.z); sum[3] += __uint_as_float(t.w);
+        uint4 t[8];
+#pragma unroll
+        for (int ss = 0; ss < 8; ++ss)  // all loads in flight before the first add
+            t[ss] = ss < p.split ? __ldcg(&part[((static_cast<int64_t>(ss) * p.q_total + q) * p.p_pad + p4) / 4]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int ss = 0; ss < 8; ++ss) {
+            if (ss < p.split) {  // chunk order, and never add a zero that could flip the sign of -0
+                sum[0] += __uint_as_float(t[ss].x); sum[1] += __uint_as_float(t[ss].y);
+                sum[2] += __uint_as_float(t[ss].z); sum[3] += __uint_as_float(t[ss].w);
+            }
         }
         for (int i = 0; i < 4; ++i) v[i] = __float_as_uint(sum[i]);
     }
@@ -520,7 +535,7 @@ int LaunchTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcPara
     }
     const int64_t slots = static_cast<int64_t>(SmCountTc()) * Cfg<BQ>::kCtasPerSm;
     const int grid = static_cast<int>(p.units < slots ? p.units : slots);
-    kernel<<<grid, kThreads, Cfg<BQ>::kSmemBytes, stream>>>(map_p, map_q, p, fe, ie);
+    kernel<<<grid, Cfg<BQ>::kThreads, Cfg<BQ>::kSmemBytes, stream>>>(map_p, map_q, p, fe, ie);
     NoteLaunch("tcgen05");
     return CheckLaunch();
 }
