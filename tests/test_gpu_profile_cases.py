@@ -1,0 +1,67 @@
+"""GPU: the exact launches the ncu summaries under profiles/ were captured from — four calls of one kernel on the
+named workload (ncu: `-s 3 -c 1`).  As tests they check that the call succeeds on the expected kernel family,
+finishes, and leaves the device status word clean."""
+import ctypes as C
+
+import pytest
+
+import infer_b200 as B
+
+pytestmark = pytest.mark.gpu
+K, N = 8192, 28672
+
+
+def _linear(torch, kind, m):
+    ws = torch.zeros(16 << 20, dtype=torch.uint8, device="cuda")
+    if kind == "fp8":
+        w = torch.randint(0, 120, (K, N), dtype=torch.uint8, device="cuda")
+        a = torch.randint(0, 120, (m, K), dtype=torch.uint8, device="cuda")
+        out = torch.empty((m, N), dtype=torch.uint8, device="cuda")
+        d = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=K, n=N, a=a, w=w, out=out, a_scale=1.0, w_scale=1.0,
+                              out_scale=64.0, variant=B.VARIANT_TCGEN05, workspace=ws, workspace_bytes=ws.numel())
+        call = B.lib().fth_b200_fp8_linear
+    else:
+        w = torch.randint(-127, 127, (K, N), dtype=torch.int8, device="cuda")
+        a = torch.randint(-127, 127, (m, K), dtype=torch.int8, device="cuda")
+        sc = torch.full((N,), 0.005, dtype=torch.float32, device="cuda")
+        out = torch.empty((m, N), dtype=torch.int8, device="cuda")
+        d = B.int8_linear_desc(op=B.OP_MATMUL, m=m, k=K, n=N, a=a, w=w, out=out, a_scale=0.02, a_zp=0, w_scales=sc, w_zps=None,
+                               w_params=N, out_scale=1.0, out_zp=0, variant=B.VARIANT_TCGEN05, workspace=ws, workspace_bytes=ws.numel())
+        call = B.lib().fth_b200_int8_linear
+    for _ in range(4):
+        assert call(C.byref(d), B.current_stream()) == B.OK
+    torch.cuda.synchronize()
+    assert B.last_variant() == "tcgen05"
+
+
+def _conv(torch):
+    from tests import util
+    from tests.gpu_helpers import dev
+    case = util.make_int8_conv(1, 64, 160, 160, 64, 3, 3, seed=3)
+    x, w, b, ws = dev(torch, case["x"]), dev(torch, case["w"]), dev(torch, case["bias"]), dev(torch, case["ws"])
+    out = torch.empty((1, 64, 160, 160), dtype=torch.int8, device="cuda")
+    lut = dev(torch, B.int8_relu_table(case["so"], 0, case["so"], 0))
+    d = B.int8_conv2d_desc(batch=1, ic=64, ih=160, iw=160, oc=64, kh=3, kw=3, x=x, w=w, out=out, x_scale=case["sx"], x_zp=0,
+                           w_scales=ws, w_zps=None, w_params=64, out_scale=case["so"], out_zp=0, bias=b, relu_lut=lut,
+                           bias_max_abs=1 << 15)
+    need = B.lib().fth_b200_int8_conv2d_workspace_bytes(C.byref(d))
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    d.workspace, d.workspace_bytes = scratch.data_ptr(), need
+    for _ in range(4):
+        assert B.lib().fth_b200_int8_conv2d(C.byref(d), B.current_stream()) == B.OK
+        d.weights_packed = 1
+    torch.cuda.synchronize()
+    assert B.last_variant() == "conv_tcgen05"
+
+
+@pytest.mark.parametrize("case", ["gemv_m1_fp8", "dense_m4096_fp8", "dense_m4096_int8", "conv_c3"])
+def test_profile_case(cuda, case):
+    if case == "gemv_m1_fp8":
+        _linear(cuda, "fp8", 1)
+    elif case == "dense_m4096_fp8":
+        _linear(cuda, "fp8", 4096)
+    elif case == "dense_m4096_int8":
+        _linear(cuda, "int8", 4096)
+    else:
+        _conv(cuda)
+    assert B.device_status() == 0
