@@ -38,6 +38,15 @@ namespace {
 
 constexpr int kPriority = 10;  // reference CUDA kernels register with priority 0 (legacy registerKernel)
 
+}  // namespace
+
+// Common base of every kernel of this backend, so that callers (and tests) can tell which candidate the
+// dispatcher finally selected.
+class B200Kernel : public KernelBase {};
+bool IsB200Kernel(const KernelBase* kernel) { return dynamic_cast<const B200Kernel*>(kernel) != nullptr; }
+
+namespace {
+
 Status FromAbi(int rc, const char* what) {
     switch (rc) {
         case FTH_B200_OK: return Status::Ok();
@@ -126,7 +135,7 @@ int BiasMode(const Tensor* bias, int64_t m, int64_t n) {
 // (src/kernel/cuda/fc.cu:91-142, matmul.cu:230-272, gemm.cu:125-183)
 // ---------------------------------------------------------------------------------------------------------
 template <DataType dtype, typename Param>
-class Fp8LinearKernel final : public KernelBase {
+class Fp8LinearKernel final : public B200Kernel {
    public:
     Status Supports() const override {
         fth_b200_fp8_linear_desc d;
@@ -221,7 +230,7 @@ bool ReadInt8Quantization(const Tensor* t, bool allow_per_channel, int64_t axis,
 }
 
 template <typename Param>
-class Int8LinearKernel final : public KernelBase {
+class Int8LinearKernel final : public B200Kernel {
    public:
     Status Supports() const override {
         fth_b200_int8_linear_desc d;
@@ -307,7 +316,7 @@ class Int8LinearKernel final : public KernelBase {
 // INT8 Conv2D — in front of RunCudaInt8Conv2D (src/kernel/cuda/int8.cu:370-506).  NCHW only; other layouts
 // stay on the reference candidate.
 // ---------------------------------------------------------------------------------------------------------
-class Int8Conv2dKernel final : public KernelBase {
+class Int8Conv2dKernel final : public B200Kernel {
    public:
     Status Supports() const override {
         fth_b200_int8_conv2d_desc d;
@@ -392,7 +401,7 @@ class Int8Conv2dKernel final : public KernelBase {
 // ---------------------------------------------------------------------------------------------------------
 // Cast among FP32 / FP16 / BF16 / FP8 — in front of CastFloatingKernelCuda (src/kernel/cuda/cast.cu:54-93)
 // ---------------------------------------------------------------------------------------------------------
-class CastKernelB200 final : public KernelBase {
+class CastKernelB200 final : public B200Kernel {
    public:
     static bool Floating(DataType t) {
         return t == DataType::FP32 || t == DataType::FP16 || t == DataType::BF16 || t == DataType::FP8E4M3 || t == DataType::FP8E5M2;
@@ -436,7 +445,7 @@ namespace kernel {
 namespace b200 {
 
 template <typename Param>
-class QdqBase : public KernelBase {
+class QdqBase : public B200Kernel {
    protected:
     // Reads the (constant) scale / zero-point tensors once and uploads them as float / int32 arrays.
     int32_t PrepareParams(Param* p) {

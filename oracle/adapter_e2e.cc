@@ -1,0 +1,348 @@
+// TEST INFRASTRUCTURE — end-to-end check of the Feather adapter inside the real reference runtime.
+//
+// Linked against the unmodified reference library built WITH its CUDA backend (oracle/_ref/libfeather_ref_cuda.so),
+// this repo's adapter (infer_b200/adapter/b200_candidates.cu) and libfth_b200.so.  It drives kernels the way the
+// reference's own CUDA unit tests do (test/standard_int8_kernel_test.cc:127-162: execution context scope, deferred
+// host sync, SyncTensorToHostIfNeeded) and mirrors its selection-contract tests
+// (test/kernel_selection_contract_test.cc:86-203).
+//
+//   adapter_e2e select   host only: registration, candidate order, kRequireRequested, decline → next CUDA candidate
+//   adapter_e2e run      needs a GPU: the new candidates run through the reference's CUDA runtime (replica cache,
+//                        inference stream) and are compared with the reference's COMMON kernels on the same tensors
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "core/kernel.h"
+#include "core/tensor.h"
+#include "fth_b200.h"
+#include "src/kernel/cuda/runtime.h"
+#include "src/operator/params.h"
+#include "util/fp8.h"
+
+namespace feather { namespace kernel { namespace b200 {
+bool RegisterB200Kernels();
+bool IsB200Kernel(const KernelBase* kernel);
+}}}
+
+using namespace feather;
+namespace cuda = feather::kernel::cuda_detail;
+using feather::kernel::b200::IsB200Kernel;
+
+static int g_failures = 0;
+#define CHECK_THAT(cond, what)                                                        \
+    do {                                                                              \
+        const bool ok_ = (cond);                                                      \
+        std::printf("%s  %s\n", ok_ ? "ok  " : "FAIL", what);                        \
+        if (!ok_) ++g_failures;                                                       \
+    } while (0)
+
+static uint32_t g_lcg = 0x12345678u;
+static uint32_t NextRandom() { g_lcg = g_lcg * 1664525u + 1013904223u; return g_lcg >> 8; }
+static float Uniform(float lo, float hi) { return lo + (hi - lo) * (NextRandom() % 100000) / 100000.0f; }
+
+static size_t Bytes(DataType t) {
+    switch (t) {
+        case DataType::FP32: case DataType::INT32: return 4;
+        case DataType::FP16: case DataType::BF16: return 2;
+        default: return 1;
+    }
+}
+
+static std::shared_ptr<Tensor> MakeTensor(DataType dtype, const std::vector<int64_t>& dims, const void* data = nullptr) {
+    size_t count = 1;
+    for (int64_t d : dims) count *= static_cast<size_t>(d);
+    auto t = std::make_shared<Tensor>(count * Bytes(dtype));
+    t->Resize(dims);
+    void* dst = t->mutable_data(count * Bytes(dtype));
+    if (data) std::memcpy(dst, data, count * Bytes(dtype));
+    else std::memset(dst, 0, count * Bytes(dtype));
+    t->set_data_type(dtype);
+    return t;
+}
+
+static QuantizationParams PerTensor(float scale, int32_t zp = 0) {
+    QuantizationParams q;
+    q.enabled = true; q.scale = scale; q.zero_point = zp;
+    return q;
+}
+static QuantizationParams PerChannel(int64_t axis, const std::vector<float>& scales) {
+    QuantizationParams q;
+    q.enabled = true; q.granularity = QuantizationGranularity::kPerChannel; q.axis = axis;
+    q.scales = scales; q.zero_points.assign(scales.size(), 0);
+    q.scale = scales.front(); q.zero_point = 0;
+    return q;
+}
+
+// create → bind parameters → FinalizeSelection, under kRequireRequested, exactly what OperatorRegistry::Create does.
+template <typename Param>
+static std::unique_ptr<KernelBase> Select(DeviceType device, DataType dtype, const char* op, Param* param, Status* status = nullptr) {
+    KernelSelectionScope scope(KernelFallbackPolicy::kRequireRequested, nullptr);
+    auto kernel = KernelDispatcher::instance().create(device, dtype, op);
+    if (!kernel) { if (status) *status = KernelDispatcher::LastSelectionStatus(); return nullptr; }
+    kernel->SetParam(param);
+    const Status s = KernelBase::FinalizeSelection(&kernel);
+    if (status) *status = s;
+    return s.ok() ? std::move(kernel) : nullptr;
+}
+
+struct Fp8Case {
+    std::shared_ptr<Tensor> a, w, out;
+    operators::MatMulParam param;
+};
+static Fp8Case MakeFp8(DataType dt, int64_t m, int64_t k, int64_t n) {
+    std::vector<uint8_t> a(static_cast<size_t>(m * k)), w(static_cast<size_t>(k * n));
+    for (auto& v : a) v = dt == DataType::FP8E4M3 ? FloatToFp8E4M3(Uniform(-2, 2)) : FloatToFp8E5M2(Uniform(-2, 2));
+    for (auto& v : w) v = dt == DataType::FP8E4M3 ? FloatToFp8E4M3(Uniform(-1, 1)) : FloatToFp8E5M2(Uniform(-1, 1));
+    Fp8Case c;
+    c.a = MakeTensor(dt, {m, k}, a.data()); c.a->set_quantization({true, 0.5f});
+    c.w = MakeTensor(dt, {k, n}, w.data()); c.w->set_quantization({true, 0.03125f}); c.w->set_immutable(true);
+    c.out = MakeTensor(dt, {m, n}); c.out->set_quantization({true, 0.25f});
+    c.param.a = c.a; c.param.b = c.w; c.param.out = c.out;
+    return c;
+}
+
+struct Int8Case {
+    std::shared_ptr<Tensor> a, w, out;
+    operators::MatMulParam param;
+};
+static Int8Case MakeInt8(int64_t m, int64_t k, int64_t n) {
+    std::vector<int8_t> a(static_cast<size_t>(m * k)), w(static_cast<size_t>(k * n));
+    for (auto& v : a) v = static_cast<int8_t>(static_cast<int>(NextRandom() % 255) - 127);
+    for (auto& v : w) v = static_cast<int8_t>(static_cast<int>(NextRandom() % 255) - 127);
+    std::vector<float> scales(static_cast<size_t>(n));
+    for (auto& s : scales) s = Uniform(1e-3f, 1e-2f);
+    Int8Case c;
+    c.a = MakeTensor(DataType::INT8, {m, k}, a.data()); c.a->set_quantization(PerTensor(0.02f));
+    c.w = MakeTensor(DataType::INT8, {k, n}, w.data()); c.w->set_quantization(PerChannel(1, scales)); c.w->set_immutable(true);
+    c.out = MakeTensor(DataType::INT8, {m, n});
+    c.out->set_quantization(PerTensor(2.33f * 73.3f * 73.3f * std::sqrt(static_cast<float>(k)) * 0.02f * 0.0055f / 127.0f));
+    c.param.a = c.a; c.param.b = c.w; c.param.out = c.out;
+    return c;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// select: host only
+// ---------------------------------------------------------------------------------------------------------
+static void RunSelect() {
+    // Before registration the reference cannot build a statically quantised INT8 plan for CUDA under
+    // kRequireRequested: DequantizeLinear has no CUDA candidate and INT8 requests never fall back to COMMON.
+    {
+        KernelSelectionScope scope(KernelFallbackPolicy::kRequireRequested, nullptr);
+        CHECK_THAT(KernelDispatcher::instance().create(DeviceType::CUDA, DataType::INT8, "DequantizeLinear") == nullptr,
+                   "reference alone: create(CUDA, INT8, DequantizeLinear) under kRequireRequested is null");
+        CHECK_THAT(KernelDispatcher::instance().create(DeviceType::CUDA, DataType::FP32, "QuantizeLinear") == nullptr,
+                   "reference alone: create(CUDA, FP32, QuantizeLinear) under kRequireRequested is null");
+    }
+    CHECK_THAT(feather::kernel::b200::RegisterB200Kernels(), "RegisterB200Kernels()");
+    {
+        KernelSelectionScope scope(KernelFallbackPolicy::kRequireRequested, nullptr);
+        const DataType fp8[] = {DataType::FP8E4M3, DataType::FP8E5M2, DataType::INT8};
+        bool all = true;
+        for (DataType dt : fp8)
+            for (const char* op : {"FC", "MatMul", "Gemm"}) all = all && KernelDispatcher::instance().create(DeviceType::CUDA, dt, op) != nullptr;
+        all = all && KernelDispatcher::instance().create(DeviceType::CUDA, DataType::INT8, "Conv2D") != nullptr;
+        all = all && KernelDispatcher::instance().create(DeviceType::CUDA, DataType::INT8, "DequantizeLinear") != nullptr;
+        all = all && KernelDispatcher::instance().create(DeviceType::CUDA, DataType::FP32, "QuantizeLinear") != nullptr;
+        all = all && KernelDispatcher::instance().create(DeviceType::CUDA, DataType::BF16, "Cast") != nullptr;
+        CHECK_THAT(all, "after registration every hot-path (dtype, op) has a CUDA candidate under kRequireRequested");
+    }
+    // the new candidate is tried first and accepted
+    for (DataType dt : {DataType::FP8E4M3, DataType::FP8E5M2}) {
+        Fp8Case c = MakeFp8(dt, 1, 1024, 3072);
+        Status st;
+        auto k = Select(DeviceType::CUDA, dt, "MatMul", &c.param, &st);
+        CHECK_THAT(k && IsB200Kernel(k.get()) && k->device() == DeviceType::CUDA, "FP8 MatMul [1,1024]x[1024,3072] selects the b200 candidate");
+    }
+    {
+        Int8Case c = MakeInt8(128, 1024, 1024);
+        auto k = Select(DeviceType::CUDA, DataType::INT8, "MatMul", &c.param);
+        CHECK_THAT(k && IsB200Kernel(k.get()), "INT8 MatMul [128,1024]x[1024,1024] per-channel selects the b200 candidate");
+    }
+    // a request the new backend declines moves on to the reference's CUDA candidate, never to a CPU kernel
+    {
+        Fp8Case c = MakeFp8(DataType::FP8E4M3, 2, 64, 32);
+        std::vector<uint8_t> wb(static_cast<size_t>(3 * 64 * 32), 0x38);
+        c.w = MakeTensor(DataType::FP8E4M3, {3, 64, 32}, wb.data()); c.w->set_quantization({true, 1.0f});
+        c.a = MakeTensor(DataType::FP8E4M3, {3, 2, 64}); c.a->set_quantization({true, 1.0f});
+        c.out = MakeTensor(DataType::FP8E4M3, {3, 2, 32}); c.out->set_quantization({true, 1.0f});
+        c.param.a = c.a; c.param.b = c.w; c.param.out = c.out;
+        auto k = Select(DeviceType::CUDA, DataType::FP8E4M3, "MatMul", &c.param);
+        CHECK_THAT(k && !IsB200Kernel(k.get()) && k->device() == DeviceType::CUDA,
+                   "batched FP8 MatMul (rank-3 B): b200 answers kUnsupported, the reference CUDA kernel is selected");
+    }
+    {
+        // the int32 accumulator could overflow (K * 128 * 128 > 2^31 - 1): declined up front
+        Int8Case c = MakeInt8(1, 140000, 16);
+        auto k = Select(DeviceType::CUDA, DataType::INT8, "MatMul", &c.param);
+        CHECK_THAT(k && !IsB200Kernel(k.get()) && k->device() == DeviceType::CUDA, "INT8 K = 140000: b200 declines (overflow bound), reference CUDA kernel selected");
+    }
+    {
+        // FEATHER selection without the strict policy still prefers CUDA candidates (priority order)
+        Int8Case c = MakeInt8(4, 256, 64);
+        KernelSelectionScope scope(KernelFallbackPolicy::kAllowCommon, nullptr);
+        auto k = KernelDispatcher::instance().create(DeviceType::CUDA, DataType::INT8, "MatMul");
+        k->SetParam(&c.param);
+        CHECK_THAT(KernelBase::FinalizeSelection(&k).ok() && IsB200Kernel(k.get()), "kAllowCommon: the b200 candidate is still first");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// run: on a GPU, inside the reference's CUDA runtime
+// ---------------------------------------------------------------------------------------------------------
+static int CodeIndex(uint8_t c) { return (c & 0x80) ? -(c & 0x7f) : (c & 0x7f); }
+
+template <typename Param>
+static int RunCommon(DataType dtype, const char* op, Param* param) {
+    auto k = KernelDispatcher::instance().create(DeviceType::COMMON, dtype, op);
+    if (!k) return -1;
+    k->SetParam(param);
+    return k->compute();
+}
+
+static void RunGpu() {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        std::printf("skip  no CUDA device\n");
+        return;
+    }
+    feather::kernel::b200::RegisterB200Kernels();
+    auto context = cuda::CreateExecutionContext();
+    cuda::ExecutionContextScope scope(context);
+
+    // ---- FP8 MatMul (config 1 shape), both formats, twice (the second run hits the replica cache) ----
+    for (DataType dt : {DataType::FP8E4M3, DataType::FP8E5M2}) {
+        Fp8Case c = MakeFp8(dt, 1, 1024, 3072);
+        auto k = Select(DeviceType::CUDA, dt, "MatMul", &c.param);
+        bool ok = k && IsB200Kernel(k.get()) && k->Prepare() == 0;
+        int max_dist = -1;
+        if (ok) {
+            cuda::DeferredHostSyncScope deferred;
+            for (int run = 0; run < 2 && ok; ++run) {
+                ok = k->compute() == 0 && cuda::SyncTensorToHostIfNeeded(c.out.get(), c.out->memory_size(), c.out->raw_data()) == 0;
+            }
+            std::vector<uint8_t> got(static_cast<const uint8_t*>(c.out->raw_data()), static_cast<const uint8_t*>(c.out->raw_data()) + 3072);
+            auto ref_out = MakeTensor(dt, {1, 3072}); ref_out->set_quantization({true, 0.25f});
+            operators::MatMulParam rp; rp.a = c.a; rp.b = c.w; rp.out = ref_out;
+            ok = ok && RunCommon(dt, "MatMul", &rp) == 0;
+            const uint8_t* want = static_cast<const uint8_t*>(ref_out->raw_data());
+            max_dist = 0;
+            for (int i = 0; i < 3072; ++i) max_dist = std::max(max_dist, std::abs(CodeIndex(got[i]) - CodeIndex(want[i])));
+        }
+        std::printf("      [%s] max code distance vs COMMON: %d\n", fth_b200_last_variant(), max_dist);
+        CHECK_THAT(ok && max_dist >= 0 && max_dist <= 1, dt == DataType::FP8E4M3 ? "CUDA FP8E4M3 MatMul through the reference runtime matches COMMON within one code"
+                                                                               : "CUDA FP8E5M2 MatMul through the reference runtime matches COMMON within one code");
+    }
+
+    // ---- INT8 MatMul (config 2 shape), per-channel weight scales: bit-exact ----
+    {
+        Int8Case c = MakeInt8(128, 1024, 1024);
+        auto k = Select(DeviceType::CUDA, DataType::INT8, "MatMul", &c.param);
+        bool ok = k && IsB200Kernel(k.get()) && k->Prepare() == 0;
+        if (ok) {
+            cuda::DeferredHostSyncScope deferred;
+            ok = k->compute() == 0 && cuda::SyncTensorToHostIfNeeded(c.out.get(), c.out->memory_size(), c.out->raw_data()) == 0;
+        }
+        std::vector<int8_t> got(static_cast<const int8_t*>(c.out->raw_data()), static_cast<const int8_t*>(c.out->raw_data()) + 128 * 1024);
+        auto ref_out = MakeTensor(DataType::INT8, {128, 1024}); ref_out->set_quantization(c.out->quantization());
+        operators::MatMulParam rp; rp.a = c.a; rp.b = c.w; rp.out = ref_out;
+        ok = ok && RunCommon(DataType::INT8, "MatMul", &rp) == 0;
+        int diff = 0;
+        for (int i = 0; i < 128 * 1024; ++i) diff += got[i] != static_cast<const int8_t*>(ref_out->raw_data())[i];
+        std::printf("      [%s] bytes differing from COMMON: %d of %d\n", fth_b200_last_variant(), diff, 128 * 1024);
+        CHECK_THAT(ok && diff == 0, "CUDA INT8 MatMul (M=128, per-channel) through the reference runtime is bit-exact with COMMON");
+    }
+
+    // ---- QuantizeLinear → INT8 MatMul → DequantizeLinear, all on CUDA with deferred host sync ----
+    {
+        const int64_t m = 4, kk = 512, n = 256;
+        Int8Case c = MakeInt8(m, kk, n);
+        std::vector<float> x(static_cast<size_t>(m * kk));
+        for (auto& v : x) v = Uniform(-2.5f, 2.5f);
+        auto xin = MakeTensor(DataType::FP32, {m, kk}, x.data());
+        const float qs = 0.02f; const int32_t qz = 0;
+        auto scale_t = MakeTensor(DataType::FP32, {1}, &qs);
+        auto zp_t = MakeTensor(DataType::INT32, {1}, &qz);
+        const float dqs = c.out->quantization().scale;
+        auto dscale_t = MakeTensor(DataType::FP32, {1}, &dqs);
+        auto y_gpu = MakeTensor(DataType::FP32, {m, n});
+        auto q_gpu = MakeTensor(DataType::INT8, {m, kk});
+        operators::QuantizeLinearParam qp; qp.input = xin; qp.scale = scale_t; qp.zero_point = zp_t; qp.out = q_gpu; qp.axis = -1;
+        operators::MatMulParam mp; mp.a = q_gpu; mp.b = c.w; mp.out = c.out;
+        operators::DequantizeLinearParam dp; dp.input = c.out; dp.scale = dscale_t; dp.zero_point = zp_t; dp.out = y_gpu; dp.to = DataType::FP32; dp.axis = -1;
+        // QuantizeLinear sets its output's quantisation at run time; the MatMul candidate is selected after it has run once on COMMON metadata
+        q_gpu->set_quantization(PerTensor(qs, qz));
+        auto kq = Select(DeviceType::CUDA, DataType::FP32, "QuantizeLinear", &qp);
+        auto km = Select(DeviceType::CUDA, DataType::INT8, "MatMul", &mp);
+        auto kd = Select(DeviceType::CUDA, DataType::INT8, "DequantizeLinear", &dp);
+        bool ok = kq && km && kd && IsB200Kernel(kq.get()) && IsB200Kernel(km.get()) && IsB200Kernel(kd.get()) &&
+                  kq->Prepare() == 0 && km->Prepare() == 0 && kd->Prepare() == 0;
+        if (ok) {
+            cuda::DeferredHostSyncScope deferred;
+            ok = kq->compute() == 0 && km->compute() == 0 && kd->compute() == 0 &&
+                 cuda::SyncTensorToHostIfNeeded(y_gpu.get(), y_gpu->memory_size(), y_gpu->raw_data()) == 0;
+        }
+        std::vector<float> got(static_cast<const float*>(y_gpu->raw_data()), static_cast<const float*>(y_gpu->raw_data()) + m * n);
+        // the same three nodes on COMMON
+        auto q_ref = MakeTensor(DataType::INT8, {m, kk});
+        auto o_ref = MakeTensor(DataType::INT8, {m, n}); o_ref->set_quantization(c.out->quantization());
+        auto y_ref = MakeTensor(DataType::FP32, {m, n});
+        operators::QuantizeLinearParam qr = qp; qr.out = q_ref;
+        operators::MatMulParam mr; mr.a = q_ref; mr.b = c.w; mr.out = o_ref;
+        operators::DequantizeLinearParam dr = dp; dr.input = o_ref; dr.out = y_ref;
+        ok = ok && RunCommon(DataType::FP32, "QuantizeLinear", &qr) == 0 && RunCommon(DataType::INT8, "MatMul", &mr) == 0 &&
+             RunCommon(DataType::INT8, "DequantizeLinear", &dr) == 0;
+        int diff = 0;
+        for (int64_t i = 0; i < m * n; ++i) diff += std::memcmp(&got[static_cast<size_t>(i)], static_cast<const float*>(y_ref->raw_data()) + i, 4) != 0;
+        std::printf("      Q -> MatMul -> DQ on CUDA: %d of %d floats differ from COMMON\n", diff, static_cast<int>(m * n));
+        CHECK_THAT(ok && diff == 0, "QuantizeLinear -> INT8 MatMul -> DequantizeLinear runs entirely on CUDA candidates, identical to COMMON");
+    }
+
+    // ---- INT8 Conv2D 3x3 pad 1 with int32 bias ----
+    {
+        const int64_t ic = 64, oc = 64, h = 24, w = 40;
+        std::vector<int8_t> x(static_cast<size_t>(ic * h * w)), wt(static_cast<size_t>(oc * ic * 9));
+        for (auto& v : x) v = static_cast<int8_t>(static_cast<int>(NextRandom() % 256) - 128);
+        for (auto& v : wt) v = static_cast<int8_t>(static_cast<int>(NextRandom() % 256) - 128);
+        std::vector<float> scales(static_cast<size_t>(oc));
+        for (auto& s : scales) s = Uniform(1e-3f, 1e-2f);
+        std::vector<int32_t> bias(static_cast<size_t>(oc));
+        for (auto& b : bias) b = static_cast<int32_t>(NextRandom() % 65536) - 32768;
+        auto tx = MakeTensor(DataType::INT8, {1, ic, h, w}, x.data()); tx->set_quantization(PerTensor(0.05f));
+        auto tw = MakeTensor(DataType::INT8, {oc, ic, 3, 3}, wt.data()); tw->set_quantization(PerChannel(0, scales)); tw->set_immutable(true);
+        auto tb = MakeTensor(DataType::INT32, {oc}, bias.data());
+        const QuantizationParams oq = PerTensor(2.33f * 74.0f * 74.0f * 24.0f * 0.05f * 0.0055f / 127.0f);
+        auto out = MakeTensor(DataType::INT8, {1, oc, h, w}); out->set_quantization(oq);
+        auto ref = MakeTensor(DataType::INT8, {1, oc, h, w}); ref->set_quantization(oq);
+        operators::Conv2dParam cp; cp.input = tx; cp.w = tw; cp.bias = tb; cp.out = out;
+        cp.stride_h = cp.stride_w = 1; cp.pad_h = cp.pad_w = 1; cp.dilation_h = cp.dilation_w = 1; cp.group = 1;
+        operators::Conv2dParam cr = cp; cr.out = ref;
+        auto k = Select(DeviceType::CUDA, DataType::INT8, "Conv2D", &cp);
+        bool ok = k && IsB200Kernel(k.get()) && k->Prepare() == 0;
+        if (ok) {
+            cuda::DeferredHostSyncScope deferred;
+            ok = k->compute() == 0 && k->compute() == 0 &&
+                 cuda::SyncTensorToHostIfNeeded(out.get(), out->memory_size(), out->raw_data()) == 0;
+        }
+        ok = ok && RunCommon(DataType::INT8, "Conv2D", &cr) == 0;
+        const int diff = ok ? std::memcmp(out->raw_data(), ref->raw_data(), static_cast<size_t>(oc * h * w)) : 1;
+        std::printf("      [%s]\n", fth_b200_last_variant());
+        CHECK_THAT(ok && diff == 0, "CUDA INT8 Conv2D 3x3 (64->64, int32 bias) through the reference runtime is bit-exact with COMMON");
+    }
+    CHECK_THAT(fth_b200_device_status() == 0, "no bounded device-side wait gave up");
+}
+
+int main(int argc, char** argv) {
+    const std::string mode = argc > 1 ? argv[1] : "select";
+    if (mode == "select") RunSelect();
+    else if (mode == "run") RunGpu();
+    else { std::fprintf(stderr, "usage: adapter_e2e select|run\n"); return 2; }
+    std::printf("%s: %d failure(s)\n", mode.c_str(), g_failures);
+    return g_failures == 0 ? 0 : 1;
+}

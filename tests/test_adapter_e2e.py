@@ -1,0 +1,38 @@
+"""The Feather adapter inside the real reference runtime (oracle/_ref/adapter_e2e, built by `make -C oracle refcuda`
+from the unmodified reference sources + infer_b200/adapter/b200_candidates.cu + oracle/adapter_e2e.cc).
+
+* CPU: registration and selection contract — kRequireRequested holds, the new candidates are tried first, a
+  declined request moves on to the reference's CUDA kernel (never to a CPU kernel), and QuantizeLinear /
+  DequantizeLinear gain the CUDA candidates a statically quantised plan needs.
+* GPU: the candidates run through the reference's own CUDA runtime (replica cache, inference stream, deferred
+  host sync) and are compared with the reference's COMMON kernels on the same tensors."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+EXE = os.path.join(ROOT, "oracle", "_ref", "adapter_e2e")
+needs_binary = pytest.mark.skipif(not os.path.exists(EXE), reason="oracle/_ref/adapter_e2e not built (needs a reference checkout)")
+
+
+def _run(mode):
+    proc = subprocess.run([EXE, mode], capture_output=True, text=True, timeout=600)
+    print(proc.stdout)
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    assert "FAIL" not in proc.stdout
+    return proc.stdout
+
+
+@needs_binary
+def test_selection_contract_inside_reference_dispatcher():
+    out = _run("select")
+    assert out.count("ok  ") >= 10
+
+
+@needs_binary
+@pytest.mark.gpu
+def test_candidates_run_through_reference_cuda_runtime():
+    out = _run("run")
+    assert "skip" not in out
+    assert out.count("ok  ") >= 6
