@@ -43,6 +43,8 @@ template <int IN, int OUT>
 __global__ void __launch_bounds__(kThreads) CastKernel(const void* __restrict__ x, void* __restrict__ out,
                                                        int64_t count, float in_scale, float out_scale,
                                                        int aligned) {
+    // lets a dependent kernel launched with programmatic serialization set itself up while this one runs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t groups = count / 16;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     if (aligned) {
@@ -117,6 +119,16 @@ __global__ void __launch_bounds__(kThreads) DequantizeKernel(const int8_t* __res
     }
 }
 
+// QuantizeLinear with one (scale, zero point) passed by value: the fused prologue of the tensor-core linear.
+template <int IN>
+__global__ void __launch_bounds__(kThreads) QuantizeScalarKernel(const void* __restrict__ x, float scale, int32_t zp,
+                                                                 int8_t* __restrict__ out, int64_t count) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < count; i += stride)
+        out[i] = QuantizeValue(ReadAs<IN>(x, i, 1.0f), scale, zp);
+}
+
 __global__ void __launch_bounds__(kThreads) LookupKernel(const int8_t* __restrict__ x, int8_t* __restrict__ out,
                                                          int64_t count, const int8_t* __restrict__ lut) {
     __shared__ int8_t table[256];
@@ -141,6 +153,19 @@ __global__ void __launch_bounds__(kThreads) LookupKernel(const int8_t* __restric
 }
 
 }  // namespace
+
+int LaunchQuantizePerTensor(int x_dtype, const void* x, float scale, int32_t zp, int8_t* out, int64_t count, cudaStream_t stream) {
+    const int grid = GridFor(count);
+    switch (x_dtype) {
+        case FTH_B200_FP32: QuantizeScalarKernel<FTH_B200_FP32><<<grid, kThreads, 0, stream>>>(x, scale, zp, out, count); break;
+        case FTH_B200_BF16: QuantizeScalarKernel<FTH_B200_BF16><<<grid, kThreads, 0, stream>>>(x, scale, zp, out, count); break;
+        case FTH_B200_FP16: QuantizeScalarKernel<FTH_B200_FP16><<<grid, kThreads, 0, stream>>>(x, scale, zp, out, count); break;
+        default: return FTH_B200_ERR_UNSUPPORTED;
+    }
+    NoteLaunch("quantize_linear");
+    return CheckLaunch();
+}
+
 }  // namespace fth
 
 using namespace fth;

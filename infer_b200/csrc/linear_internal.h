@@ -32,6 +32,9 @@ size_t StreamScratchBytes(int dtype, const LinearArgs& args);
 int LaunchLinearStream(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* scratch,
                        size_t scratch_bytes, cudaStream_t stream);
 
+// QuantizeLinear with scalar parameters (elementwise.cu), used as the fused prologue of the tensor-core linear.
+int LaunchQuantizePerTensor(int x_dtype, const void* x, float scale, int32_t zp, int8_t* out, int64_t count, cudaStream_t stream);
+
 // tcgen05 / TMEM / TMA dense GEMM.
 bool Tcgen05Supported(int dtype, const LinearArgs& args);
 size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& args);

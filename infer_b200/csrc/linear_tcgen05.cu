@@ -147,6 +147,9 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     // Lets a dependent grid (the split-K reduce pass) be scheduled while this one runs; it still waits for this
     // grid to finish before it reads anything.  No effect when launched without programmatic serialization.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Everything above (barriers, tensor memory) overlapped the tail of the previous kernel in the stream; the
+    // operands may be that kernel's output, so nothing is read before it has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // unit → (p tile, q tile, K chunk).  Normal mode walks the activation tiles fastest so the CTAs running
     // together share one weight column block through L2 and the weights stream from HBM once.
@@ -535,7 +538,17 @@ int LaunchTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcPara
     }
     const int64_t slots = static_cast<int64_t>(SmCountTc()) * Cfg<BQ>::kCtasPerSm;
     const int grid = static_cast<int>(p.units < slots ? p.units : slots);
-    kernel<<<grid, Cfg<BQ>::kThreads, Cfg<BQ>::kSmemBytes, stream>>>(map_p, map_q, p, fe, ie);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(Cfg<BQ>::kThreads);
+    cfg.dynamicSmemBytes = Cfg<BQ>::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, map_p, map_q, p, fe, ie) != cudaSuccess) return FTH_B200_ERR_CUDA;
     NoteLaunch("tcgen05");
     return CheckLaunch();
 }
@@ -560,11 +573,16 @@ int LaunchForLayout(const TcGeometry& g, bool weights_mn, const CUtensorMap& map
 
 }  // namespace
 
+// A fused Cast / QuantizeLinear in front of the MatMul runs as one elementwise pass that writes the quantised
+// activations (1 byte each) to the front of the scratch buffer; TMA then reads them like any FP8 / INT8 input.
+size_t PrologueBytes(const LinearArgs& a) { return a.a_dtype == 0 ? 0 : static_cast<size_t>((a.m * a.k + 255) / 256 * 256); }
+
 bool Tcgen05Supported(int dtype, const LinearArgs& a) {
-    if (a.a_dtype != 0 || a.zero_points) return false;       // fused Cast / QuantizeLinear prologue, zero points: other kernels
+    if (a.zero_points) return false;                          // non-zero zero points: the CUDA-core kernels
     if (a.k % 16 != 0) return false;                          // TMA row pitch of the K-major activation tile
     if (!a.trans_b && a.n % 16 != 0) return false;            // TMA row pitch of [K,N] weights
-    if (reinterpret_cast<uintptr_t>(a.w) % 16 != 0 || reinterpret_cast<uintptr_t>(a.a) % 16 != 0) return false;
+    if (reinterpret_cast<uintptr_t>(a.w) % 16 != 0) return false;
+    if (a.a_dtype == 0 && reinterpret_cast<uintptr_t>(a.a) % 16 != 0) return false;
     if (a.k < 32 || a.m < 1 || a.n < 1) return false;
     if (a.m > 0x7fffffff || a.n > 0x7fffffff || a.k > 0x7fffffff) return false;
     (void)dtype;
@@ -574,16 +592,27 @@ bool Tcgen05Supported(int dtype, const LinearArgs& a) {
 size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& a) {
     (void)dtype;
     const TcGeometry g = GeometryFor(a);
-    if (g.split == 1) return 0;
-    return static_cast<size_t>(g.split) * g.q_total * g.p_pad * 4;
+    return PrologueBytes(a) + (g.split == 1 ? 0 : static_cast<size_t>(g.split) * g.q_total * g.p_pad * 4);
 }
 
-int LaunchLinearTcgen05(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* scratch,
+int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* scratch_in,
                         size_t scratch_bytes, cudaStream_t stream) {
-    if (!Tcgen05Supported(dtype, a)) return FTH_B200_ERR_UNSUPPORTED;
-    const TcGeometry g = GeometryFor(a);
-    if (g.split > 1 && (scratch == nullptr || scratch_bytes < Tcgen05ScratchBytes(dtype, a))) return FTH_B200_ERR_INVALID;
+    if (!Tcgen05Supported(dtype, a_in)) return FTH_B200_ERR_UNSUPPORTED;
+    const TcGeometry g = GeometryFor(a_in);
+    const size_t need = Tcgen05ScratchBytes(dtype, a_in);
+    if (need > 0 && (scratch_in == nullptr || scratch_bytes < need || reinterpret_cast<uintptr_t>(scratch_in) % 256 != 0)) return FTH_B200_ERR_INVALID;
     const bool int8 = dtype == FTH_B200_INT8;
+    LinearArgs a = a_in;
+    void* scratch = scratch_in;
+    if (a.a_dtype != 0) {
+        int rc;
+        if (int8) rc = LaunchQuantizePerTensor(a.a_dtype, a.a, ie.a_scale, ie.a_zp, static_cast<int8_t*>(scratch_in), a.m * a.k, stream);
+        else rc = fth_b200_cast(a.a_dtype, a.a, 1.0f, dtype, scratch_in, a.a_scale, a.m * a.k, stream);
+        if (rc != FTH_B200_OK) return rc;
+        a.a = scratch_in;
+        a.a_dtype = 0;
+        scratch = static_cast<uint8_t*>(scratch_in) + PrologueBytes(a_in);
+    }
     const bool weights_mn = !a.trans_b;
 
     CUtensorMap map_w, map_a, map_p, map_q;

@@ -25,8 +25,10 @@ def oracle_project(h_bits, weight):
 
 
 class GpuProjector:
-    def __init__(self, torch, weights):
+    def __init__(self, torch, weights, with_workspace=True):
         self.torch = torch
+        self.with_workspace = with_workspace
+        self.variants = set()
         self.dev = {id(layer[name][0]): dev(torch, layer[name][0]) for layer in weights for name, _, _ in D.PROJ}
         self.launches = 0
 
@@ -39,7 +41,9 @@ class GpuProjector:
         out = torch.empty((m, n), dtype=torch.int16, device="cuda")
         d = B.fp8_linear_desc(dtype=B.E5M2, op=B.OP_MATMUL, m=m, k=k, n=n, a=a, w=self.dev[id(codes)], out=out,
                               a_scale=D.ACT_SCALE, w_scale=sw, out_scale=D.OUT_SCALE, a_dtype=B.BF16, out_dtype=B.BF16)
+        keep = B.linear_workspace(torch, d) if self.with_workspace else None
         B.fp8_linear(d)
+        self.variants.add(B.last_variant())
         self.launches += 1
         return out.cpu().numpy().view(np.uint16)
 
@@ -57,7 +61,13 @@ def test_decoder_stack_matches_oracle(cuda, stack_weights, m):
     want = D.from_bf16(D.run_stack(oracle_project, stack_weights, x0, trace)).astype(np.float64)
     gpu = GpuProjector(cuda, stack_weights)
     got = D.from_bf16(D.run_stack(gpu, stack_weights, x0)).astype(np.float64)
-    assert gpu.launches == 7 * D.LAYERS
+    assert gpu.launches == 7 * D.LAYERS and gpu.variants == {"tcgen05"}
+    if m in (1, 16):  # the same stack without a workspace runs on the scratch-free CUDA-core kernels: same bytes
+        plain = GpuProjector(cuda, stack_weights, with_workspace=False)
+        got_plain = D.from_bf16(D.run_stack(plain, stack_weights, x0)).astype(np.float64)
+        assert "tcgen05" not in plain.variants
+        cos_plain = float((got_plain * want).sum() / (np.linalg.norm(got_plain) * np.linalg.norm(want)))
+        assert cos_plain >= 0.999
     assert np.isfinite(got).all() and np.isfinite(want).all()
     cos = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want)))
     rmse = float(np.sqrt(((got - want) ** 2).mean()))
