@@ -113,6 +113,9 @@ typedef struct {
     void* workspace;
     size_t workspace_bytes;
     int32_t variant;      /* FTH_B200_VARIANT_* */
+    /* 1: nothing queued earlier on the stream writes `w` (an initializer, as FC / MatMul weights are in a compiled
+     * plan), so the kernel may fetch weights while the previous kernel is still finishing.  0: no assumption. */
+    int32_t weights_static;
 } fth_b200_fp8_linear_desc;
 
 int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t stream);
@@ -178,6 +181,7 @@ typedef struct {
     void* workspace;      /* as in fth_b200_fp8_linear_desc */
     size_t workspace_bytes;
     int32_t variant;
+    int32_t weights_static; /* as in fth_b200_fp8_linear_desc */
 } fth_b200_int8_linear_desc;
 
 int fth_b200_int8_linear(const fth_b200_int8_linear_desc* desc, fth_b200_stream_t stream);

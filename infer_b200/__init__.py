@@ -41,7 +41,7 @@ class Fp8LinearDesc(C.Structure):
         ("a", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int64),
         ("a_scale", C.c_float), ("w_scale", C.c_float), ("bias_scale", C.c_float), ("out_scale", C.c_float),
         ("w_channel_scales", C.c_void_p), ("alpha", C.c_float), ("beta", C.c_float),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32), ("weights_static", C.c_int32),
     ]
 
 
@@ -53,7 +53,7 @@ class Int8LinearDesc(C.Structure):
         ("a_scale", C.c_float), ("a_zp", C.c_int32), ("w_scales", C.c_void_p), ("w_zps", C.c_void_p),
         ("w_params", C.c_int64), ("w_zp_max_abs", C.c_int32), ("out_scale", C.c_float), ("out_zp", C.c_int32),
         ("alpha", C.c_float), ("beta", C.c_float), ("bias_max_abs", C.c_int64),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32), ("weights_static", C.c_int32),
     ]
 
 
@@ -135,14 +135,14 @@ def current_stream():
 def fp8_linear_desc(*, dtype, op, m, k, n, a, w, out, a_scale, w_scale, out_scale, trans_b=False, bias=None,
                     bias_mode=BIAS_NONE, bias_scale=1.0, alpha=1.0, beta=1.0, a_dtype=0, out_dtype=0, ldo=0,
                     w_channel_scales=None, workspace=None, workspace_bytes=0,
-                    variant=VARIANT_AUTO) -> Fp8LinearDesc:
+                    variant=VARIANT_AUTO, weights_static=False) -> Fp8LinearDesc:
     d = Fp8LinearDesc()
     d.dtype, d.op, d.m, d.k, d.n, d.trans_b = dtype, op, m, k, n, int(trans_b)
     d.a_dtype, d.out_dtype, d.bias_mode = a_dtype, out_dtype, bias_mode
     d.a, d.w, d.bias, d.out, d.ldo = ptr(a), ptr(w), ptr(bias), ptr(out), ldo
     d.a_scale, d.w_scale, d.bias_scale, d.out_scale = a_scale, w_scale, bias_scale, out_scale
     d.w_channel_scales = ptr(w_channel_scales)
-    d.alpha, d.beta, d.variant = alpha, beta, variant
+    d.alpha, d.beta, d.variant, d.weights_static = alpha, beta, variant, int(weights_static)
     d.workspace, d.workspace_bytes = ptr(workspace), workspace_bytes
     return d
 
@@ -150,7 +150,7 @@ def fp8_linear_desc(*, dtype, op, m, k, n, a, w, out, a_scale, w_scale, out_scal
 def int8_linear_desc(*, op, m, k, n, a, w, out, a_scale, a_zp, w_scales, w_zps, w_params, out_scale, out_zp,
                      trans_b=False, bias=None, bias_mode=BIAS_NONE, alpha=1.0, beta=1.0, a_dtype=0, out_dtype=0,
                      ldo=0, w_zp_max_abs=0, bias_max_abs=0, workspace=None, workspace_bytes=0,
-                     variant=VARIANT_AUTO) -> Int8LinearDesc:
+                     variant=VARIANT_AUTO, weights_static=False) -> Int8LinearDesc:
     d = Int8LinearDesc()
     d.op, d.m, d.k, d.n, d.trans_b = op, m, k, n, int(trans_b)
     d.a_dtype, d.out_dtype, d.bias_mode = a_dtype, out_dtype, bias_mode
@@ -158,6 +158,7 @@ def int8_linear_desc(*, op, m, k, n, a, w, out, a_scale, a_zp, w_scales, w_zps, 
     d.a_scale, d.a_zp, d.w_scales, d.w_zps, d.w_params = a_scale, a_zp, ptr(w_scales), ptr(w_zps), w_params
     d.w_zp_max_abs, d.out_scale, d.out_zp = w_zp_max_abs, out_scale, out_zp
     d.alpha, d.beta, d.bias_max_abs, d.variant = alpha, beta, bias_max_abs, variant
+    d.weights_static = int(weights_static)
     d.workspace, d.workspace_bytes = ptr(workspace), workspace_bytes
     return d
 

@@ -152,6 +152,7 @@ class Fp8LinearKernel final : public B200Kernel {
         if (!Describe(&d)) return -1;
         d.a = d.w = d.out = kProbe;
         if (d.bias_mode != FTH_B200_BIAS_NONE) d.bias = kProbe;
+        weights_resident_ = false;
         return workspace_.Reserve(fth_b200_fp8_linear_workspace_bytes(&d), true);
     }
 
@@ -169,7 +170,10 @@ class Fp8LinearKernel final : public B200Kernel {
             cuda_detail::AllocateTensorOnDevice(v.out, &out) != 0) return -1;
         d.a = a.get(); d.w = w.get(); d.bias = v.bias ? bias.get() : nullptr; d.out = out.get();
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
+        // An immutable weight is uploaded by the first call; from the second call on nothing on the stream writes it.
+        d.weights_static = weights_resident_ ? 1 : 0;
         if (fth_b200_fp8_linear(&d, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        weights_resident_ = v.w->is_immutable();
         return cuda_detail::CopyDeviceToTensor(&out, v.out);  // a no-op under deferred host sync
     }
 
@@ -197,6 +201,7 @@ class Fp8LinearKernel final : public B200Kernel {
     }
 
     DeviceScratch workspace_;
+    bool weights_resident_{false};
 };
 
 // ---------------------------------------------------------------------------------------------------------
@@ -260,6 +265,7 @@ class Int8LinearKernel final : public B200Kernel {
             for (int64_t i = 0; i < v.bias->numel(); ++i) bias_max_abs_ = std::max<int64_t>(bias_max_abs_, std::llabs(static_cast<long long>(b[i])));
         }
         d.a = kProbe; d.w = static_cast<const int8_t*>(kProbe); d.out = kProbe; d.w_scales = static_cast<const float*>(kProbe);
+        weights_resident_ = false;
         return workspace_.Reserve(fth_b200_int8_linear_workspace_bytes(&d), true);
     }
 
@@ -279,7 +285,9 @@ class Int8LinearKernel final : public B200Kernel {
         d.w_zps = has_zps_ ? static_cast<const int32_t*>(zps_.get()) : nullptr;
         d.bias_max_abs = bias_max_abs_;
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
+        d.weights_static = weights_resident_ ? 1 : 0;
         if (fth_b200_int8_linear(&d, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        weights_resident_ = v.w->is_immutable();
         return cuda_detail::CopyDeviceToTensor(&out, v.out);
     }
 
@@ -308,6 +316,7 @@ class Int8LinearKernel final : public B200Kernel {
     }
 
     DeviceScratch scales_, zps_, workspace_;
+    bool weights_resident_{false};
     bool has_zps_{false};
     int64_t bias_max_abs_{0};
 };

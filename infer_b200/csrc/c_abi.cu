@@ -119,6 +119,7 @@ void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* 
     args->a_dtype = (d->a_dtype == d->dtype) ? 0 : d->a_dtype;
     args->a_scale = d->a_scale;
     args->zero_points = 0;
+    args->w_static = d->weights_static != 0;
     fe->ab_scale = d->w_channel_scales ? d->a_scale : d->a_scale * d->w_scale;
     fe->w_channel_scales = d->w_channel_scales;
     fe->is_gemm = d->op == FTH_B200_OP_GEMM;
@@ -139,6 +140,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
     args->a_dtype = (d->a_dtype == FTH_B200_INT8) ? 0 : d->a_dtype;
     args->a_scale = d->a_scale;
     args->zero_points = (d->a_zp != 0 || d->w_zps != nullptr) ? 1 : 0;
+    args->w_static = d->weights_static != 0;
     ie->w_scales = d->w_scales; ie->w_zps = d->w_zps; ie->per_channel = d->w_params != 1;
     ie->a_scale = d->a_scale; ie->a_zp = d->a_zp; ie->out_scale = d->out_scale; ie->out_zp = d->out_zp;
     ie->bias = d->bias; ie->bias_mode = d->bias_mode;
@@ -156,7 +158,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
 
 using namespace fth;
 
-extern "C" int fth_b200_abi_version(void) { return 1; }
+extern "C" int fth_b200_abi_version(void) { return 2; }
 extern "C" const char* fth_b200_last_variant(void) { return g_last_variant; }
 extern "C" int64_t fth_b200_launch_count(void) { return g_launches; }
 extern "C" void fth_b200_reset_launch_count(void) { g_launches = 0; }

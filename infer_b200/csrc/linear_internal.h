@@ -14,6 +14,7 @@ struct LinearArgs {
     int a_dtype;     // 0 = same as the weight dtype
     float a_scale;   // used only by the fused-cast activation load
     int zero_points; // INT8: activation or weight zero point is non-zero
+    int w_static;    // no earlier work in the stream writes the weights: they may be read before it has finished
 };
 
 int LaunchLinearSimt(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,

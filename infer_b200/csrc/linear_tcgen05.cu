@@ -17,10 +17,25 @@
 // small second kernel adds the S partials of every output in chunk order and runs the epilogue.  (A
 // single-kernel hand-off through fences and arrival counters was measured first: the gpu-scope fence per
 // work unit stalled the epilogue warps behind the streaming loads and cost more than the extra launch.)
+#include <stdlib.h>
+
+#include <cmath>
+
 #include "common.cuh"
 #include "linear_internal.h"
 #include "tcgen05.cuh"
 #include "tma.cuh"
+
+// Optional phase timeline of CTA 0 in SM clocks (development aid, compiled out unless FTH_B200_TRACE is defined).
+#ifdef FTH_B200_TRACE
+__device__ unsigned long long g_trace[32];
+#define FTH_TRACE(i) do { if (blockIdx.x == 0) g_trace[i] = static_cast<unsigned long long>(clock64()); } while (0)
+extern "C" int fth_b200_trace_read(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : -1;
+}
+#else
+#define FTH_TRACE(i) do {} while (0)
+#endif
 
 namespace fth {
 namespace {
@@ -37,11 +52,14 @@ struct TcParams {
     int64_t p_tiles, q_tiles;
     int split;                 // K chunks per tile
     int64_t chunk_blocks;      // 128-byte K blocks per chunk
+    int ring_stages;           // cluster kernel: weight ring depth of this launch
     int64_t k_blocks;          // ceil(K / 128)
     int64_t units;             // p_tiles * q_tiles * split
     uint32_t idesc;
     int e4m3;                  // FP8 format of operands and output (1 = E4M3, 0 = E5M2)
     int fast;                  // 1: no bias, alpha = beta = 1, native output dtype → vectorised epilogue
+    int fast4;                 // same for the four-channel epilogue, which also covers a fused output Cast (FP8)
+    float a_inv, out_inv;      // exact reciprocals of the activation / output scale (powers of two), else 0
     void* scratch;             // [split][q_total][p_pad] partial accumulators
     int64_t p_pad;
     int* status;
@@ -314,6 +332,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 if constexpr (INT8) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
+                        if (j >= cnt) break;  // uniform: a decode-sized M leaves most columns unused
                         const float mult = p.swap ? row_mult : col_mult[c0 + j];
                         const double sd = p.swap ? row_scale_d : col_scale[c0 + j];
                         b[j] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[j]), mult, sd, so_d, ie.out_zp));
@@ -321,6 +340,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j += 2) {
+                        if (j >= cnt) break;  // uniform; unused columns would only feed the divider zeros (its slow path)
                         const float m0 = p.swap ? row_mult : col_mult[c0 + j];
                         const float m1 = p.swap ? row_mult : col_mult[c0 + j + 1];
                         const float y0 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j]), m0), so_f);
@@ -398,6 +418,76 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 }
 
 
+// Epilogue of four consecutive output channels p4 .. p4+3 of activation row q (swapped tiling), given their
+// complete accumulators: the vectorised fast path or the generic per-element store.
+template <bool INT8>
+__device__ __forceinline__ void FinishFour(const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, int64_t q,
+                                           int64_t p4, const uint32_t (&v)[4], bool store = true) {
+    if (!p.fast4) {
+        if (!store) return;
+        for (int i = 0; i < 4; ++i)
+            if (p4 + i < p.p_total) StoreOne<INT8>(fe, ie, p.e4m3, q, p4 + i, v[i]);
+        return;
+    }
+    uint32_t b[4];
+    if constexpr (INT8) {
+        for (int i = 0; i < 4; ++i) {
+            const int64_t n = p4 + i < p.p_total ? p4 + i : p.p_total - 1;
+            const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
+            const double so_d = static_cast<double>(ie.out_scale);
+            b[i] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[i]), static_cast<float>(sd / so_d), sd, so_d, ie.out_zp));
+        }
+    } else {
+        float y[4];
+        for (int i = 0; i < 4; ++i) {
+            const int64_t n = p4 + i < p.p_total ? p4 + i : p.p_total - 1;
+            const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
+            y[i] = __fdiv_rn(__fmul_rn(__uint_as_float(v[i]), mult), fe.out_scale);
+        }
+        const uint32_t lo = EncodePair(p.e4m3, y[0], y[1]), hi = EncodePair(p.e4m3, y[2], y[3]);
+        b[0] = lo & 0xffu; b[1] = lo >> 8; b[2] = hi & 0xffu; b[3] = hi >> 8;
+        if (fe.out_dtype != 0) {
+            // fused Cast behind the MatMul: the decoded code times the output scale, as BF16 or FP32
+            const float2 d01 = p.e4m3 ? DecodePair<FTH_B200_FP8E4M3>(static_cast<uint16_t>(lo)) : DecodePair<FTH_B200_FP8E5M2>(static_cast<uint16_t>(lo));
+            const float2 d23 = p.e4m3 ? DecodePair<FTH_B200_FP8E4M3>(static_cast<uint16_t>(hi)) : DecodePair<FTH_B200_FP8E5M2>(static_cast<uint16_t>(hi));
+            const float o[4] = {__fmul_rn(d01.x, fe.out_scale), __fmul_rn(d01.y, fe.out_scale), __fmul_rn(d23.x, fe.out_scale), __fmul_rn(d23.y, fe.out_scale)};
+            const bool whole = p4 + 3 < p.p_total;
+            if (!store) {
+                asm volatile("" ::"f"(o[0]), "f"(o[1]), "f"(o[2]), "f"(o[3]));  // keep the dry pass's arithmetic
+                return;
+            }
+            if (fe.out_dtype == FTH_B200_BF16) {
+                uint16_t* dst = static_cast<uint16_t*>(fe.out) + q * fe.ldo + p4;
+                if (whole && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+                    uint2 t;
+                    t.x = EncodeBf16Cast(o[0]) | (static_cast<uint32_t>(EncodeBf16Cast(o[1])) << 16);
+                    t.y = EncodeBf16Cast(o[2]) | (static_cast<uint32_t>(EncodeBf16Cast(o[3])) << 16);
+                    *reinterpret_cast<uint2*>(dst) = t;
+                } else {
+                    for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) dst[i] = EncodeBf16Cast(o[i]);
+                }
+            } else {
+                float* dst = static_cast<float*>(fe.out) + q * fe.ldo + p4;
+                if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+                else { for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) dst[i] = o[i]; }
+            }
+            return;
+        }
+    }
+    if (!store) {
+        asm volatile("" ::"r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]));
+        return;
+    }
+    const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
+    uint8_t* dst = static_cast<uint8_t*>(INT8 ? ie.out : fe.out) + q * ldo + p4;
+    if (p4 + 3 < p.p_total && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+        *reinterpret_cast<uint32_t*>(dst) = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    } else {
+        for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) dst[i] = static_cast<uint8_t>(b[i]);
+    }
+}
+
+
 // Second pass of the split-K path (swapped tiling only: rows p are output channels n, columns q are
 // activation rows m).  One thread owns four consecutive channels of one activation row: it adds the S partial
 // accumulators in chunk order (the same order whatever the grid was), runs the epilogue and stores 4 bytes.
@@ -441,36 +531,397 @@ __global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue
         }
         for (int i = 0; i < 4; ++i) v[i] = __float_as_uint(sum[i]);
     }
-    if (!p.fast) {
-        for (int i = 0; i < 4; ++i)
-            if (p4 + i < p.p_total) StoreOne<INT8>(fe, ie, p.e4m3, q, p4 + i, v[i]);
-        return;
+    FinishFour<INT8>(p, fe, ie, q, p4, v);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Decode-sized problems (M <= 32, one wave of CTAs): split-K inside a thread-block cluster.
+//
+// The S CTAs of a cluster work on the S K-chunks of one 128-channel weight tile, so S SMs pull the tile's bytes
+// at the same time (one SM alone draws ~35 bytes per clock through TMA, which is what bounds a small
+// projection).  Each CTA's accumulator leaves tensor memory once; its 128 rows are dealt out to the cluster's
+// CTAs through distributed shared memory (CTA o receives rows o*L .. o*L+L-1 of every chunk, L = 128 / cluster
+// size), and after one cluster barrier each CTA adds the chunks of its rows in chunk order — the order the
+// two-kernel path uses, so both give the same bits — and runs the epilogue.  No scratch, no second launch.
+//
+// A fused Cast / QuantizeLinear in front of the MatMul is done here as well: the epilogue warps, idle while the
+// weights stream, read the CTA's K-chunk of BF16 / FP16 / FP32 activations, convert, and write the 8-bit codes
+// into the swizzled operand tile that the MMA reads (generic-proxy writes, made visible with fence.proxy.async).
+// 8-bit activations arrive by TMA as before.  The activation chunk stays resident (kQBlocks blocks at most);
+// only the weight tile goes through the ring.
+// ---------------------------------------------------------------------------------------------------------
+template <int BQ>
+struct ClusterCfg {
+    static constexpr int kQBlocks = 8;                       // K blocks of activations held per CTA
+    static constexpr int kQBytes = kQBlocks * BQ * kBlockK;  // 16 KB / 32 KB
+    static constexpr int kStages = BQ <= 16 ? 5 : 3;         // weight ring (16 KB per stage), upper limit
+    static constexpr int kMaxStages = 8;                     // barrier slots
+    static constexpr int kExchangeBytes = kBlockP * BQ * 4;  // partials of this CTA's rows, all chunks
+    static constexpr uint32_t kTmemCols = 32;
+    static constexpr int kThreads = 192;
+    static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kPBytes + kQBytes + kExchangeBytes + 256;
+    static int StagesFor(int64_t chunk_blocks) { return chunk_blocks < kStages ? static_cast<int>(chunk_blocks) : kStages; }
+    static size_t SmemFor(int64_t chunk_blocks) {
+        return 1024 + static_cast<size_t>(StagesFor(chunk_blocks)) * kPBytes + static_cast<size_t>(chunk_blocks) * BQ * kBlockK +
+               kExchangeBytes + 256;
     }
-    uint32_t b[4];
-    for (int i = 0; i < 4; ++i) {
-        const int64_t n = p4 + i < p.p_total ? p4 + i : p.p_total - 1;
-        if constexpr (INT8) {
-            const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
-            const double so_d = static_cast<double>(ie.out_scale);
-            b[i] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[i]), static_cast<float>(sd / so_d), sd, so_d, ie.out_zp));
-        } else {
-            const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
-            const float y = __fdiv_rn(__fmul_rn(__uint_as_float(v[i]), mult), fe.out_scale);
-            b[i] = p.e4m3 ? Encode<FTH_B200_FP8E4M3>(y) : Encode<FTH_B200_FP8E5M2>(y);
+};
+
+__device__ __forceinline__ uint32_t ClusterRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t ClusterSize() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void ClusterArrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void ClusterWait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// Address of this CTA's shared-memory location `smem_addr` inside CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t MapToRank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+// 16-byte store into a peer CTA's shared memory that adds its 16 bytes to the transaction count of a barrier in
+// the same peer: the receiver waits on that barrier and needs no other synchronisation with the sender.
+__device__ __forceinline__ void StoreClusterAsync4(uint32_t addr, uint32_t bar, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
+}
+
+// Four consecutive activation elements of a fused Cast (FP8) / QuantizeLinear (INT8) prologue.  The raw load and
+// the conversion are separate so that a thread can have several loads in flight before it converts the first.
+// `index` is a multiple of 4; `vec` says the base pointer is 16-byte aligned.
+__device__ __forceinline__ uint4 LoadFourRaw(const LinearArgs& a, int64_t index, bool vec) {
+    uint4 r = make_uint4(0, 0, 0, 0);
+    if (a.a_dtype == FTH_B200_FP32) {
+        const uint32_t* src = static_cast<const uint32_t*>(a.a) + index;
+        if (vec) r = *reinterpret_cast<const uint4*>(src);
+        else { r.x = src[0]; r.y = src[1]; r.z = src[2]; r.w = src[3]; }
+    } else {
+        const uint16_t* src = static_cast<const uint16_t*>(a.a) + index;
+        if (vec) { const uint2 t = *reinterpret_cast<const uint2*>(src); r.x = t.x; r.y = t.y; }
+        else { r.x = src[0] | (static_cast<uint32_t>(src[1]) << 16); r.y = src[2] | (static_cast<uint32_t>(src[3]) << 16); }
+    }
+    return r;
+}
+// Codes of the four elements, element 0 in the low byte.  `a_inv` is 1 / a_scale when that is exact (a power of
+// two: x * a_inv and x / a_scale are then the same correctly rounded value), else 0.
+template <bool INT8>
+__device__ __forceinline__ uint32_t ConvertFourRaw(const LinearArgs& a, const Int8Epilogue& ie, int e4m3, float a_inv, uint4 raw) {
+    float x[4];
+    if (a.a_dtype == FTH_B200_FP32) {
+        x[0] = __uint_as_float(raw.x); x[1] = __uint_as_float(raw.y); x[2] = __uint_as_float(raw.z); x[3] = __uint_as_float(raw.w);
+    } else if (a.a_dtype == FTH_B200_BF16) {
+        x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xffff0000u);
+        x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xffff0000u);
+    } else {
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+    }
+    if constexpr (INT8) {
+        uint32_t word = 0;
+        for (int i = 0; i < 4; ++i) word |= static_cast<uint32_t>(static_cast<uint8_t>(QuantizeValue(x[i], ie.a_scale, ie.a_zp))) << (8 * i);
+        return word;
+    } else {
+        float y[4];
+        // a NaN skips the divide, as in the stand-alone Cast kernel
+        if (a_inv != 0.0f) { for (int i = 0; i < 4; ++i) y[i] = (x[i] != x[i]) ? x[i] : __fmul_rn(x[i], a_inv); }
+        else { for (int i = 0; i < 4; ++i) y[i] = (x[i] != x[i]) ? x[i] : __fdiv_rn(x[i], a.a_scale); }
+        return EncodePair(e4m3, y[0], y[1]) | (EncodePair(e4m3, y[2], y[3]) << 16);
+    }
+}
+
+// Epilogue of one output (activation row q, channel n) from its complete accumulator.
+template <bool INT8>
+__device__ __forceinline__ void FinishOne(const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, int64_t q, int64_t n,
+                                          uint32_t raw) {
+    if (!p.fast4) { StoreOne<INT8>(fe, ie, p.e4m3, q, n, raw); return; }
+    if constexpr (INT8) {
+        const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
+        const double so_d = static_cast<double>(ie.out_scale);
+        static_cast<int8_t*>(ie.out)[q * ie.ldo + n] = RequantFast(static_cast<int32_t>(raw), static_cast<float>(sd / so_d), sd, so_d, ie.out_zp);
+    } else {
+        const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
+        const float t = __fmul_rn(__uint_as_float(raw), mult);
+        const float y = p.out_inv != 0.0f ? __fmul_rn(t, p.out_inv) : __fdiv_rn(t, fe.out_scale);
+        const uint8_t code = p.e4m3 ? Encode<FTH_B200_FP8E4M3>(y) : Encode<FTH_B200_FP8E5M2>(y);
+        const int64_t o = q * fe.ldo + n;
+        if (fe.out_dtype == 0) { static_cast<uint8_t*>(fe.out)[o] = code; return; }
+        // fused Cast behind the MatMul: the decoded code times the output scale, as BF16 or FP32
+        const float d = p.e4m3 ? Decode<FTH_B200_FP8E4M3>(code) : Decode<FTH_B200_FP8E5M2>(code);
+        const float v = __fmul_rn(d, fe.out_scale);
+        if (fe.out_dtype == FTH_B200_BF16) static_cast<uint16_t*>(fe.out)[o] = EncodeBf16Cast(v);
+        else static_cast<float*>(fe.out)[o] = v;
+    }
+}
+
+template <bool INT8, bool P_MN, int BQ>
+__global__ void __launch_bounds__(ClusterCfg<BQ>::kThreads, 2)
+LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, TcParams p,
+                    Fp8Epilogue fe, Int8Epilogue ie) {
+    using C = ClusterCfg<BQ>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // The ring and the activation tiles are sized per launch (p.ring_stages, p.chunk_blocks): a small projection
+    // then takes ~30 KB instead of ~100 KB, and the CTAs of the next kernel in the stream can move in early.
+    const int stages = p.ring_stages;
+    uint8_t* q_tiles = ring + static_cast<size_t>(stages) * kPBytes;            // [chunk_blocks][BQ][128], 128-byte swizzle
+    uint32_t* exchange = reinterpret_cast<uint32_t*>(q_tiles + p.chunk_blocks * (BQ * kBlockK));  // [chunk][L][BQ]
+    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(exchange) + C::kExchangeBytes);
+    uint64_t* empty = full + C::kMaxStages;
+    uint64_t* q_full = empty + C::kMaxStages;
+    uint64_t* tmem_full = q_full + 1;
+    uint64_t* x_full = tmem_full + 1;  // counts the bytes peers deliver into `exchange`
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(x_full + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (threadIdx.x == 0) FTH_TRACE(0);
+    const bool convert = p.args.a_dtype != 0;
+
+    if (threadIdx.x == 0) {
+        TmaPrefetchDescriptor(&map_p);  // kernel parameters: safe to touch before the previous grid has finished
+        if (!convert) TmaPrefetchDescriptor(&map_q);
+        for (int s = 0; s < stages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
+        MbarInit(q_full, convert ? 128 : 1);
+        MbarInit(tmem_full, 1);
+        MbarInit(x_full, 1);
+        FenceBarrierInit();
+    }
+    if (warp == 1) umma::TmemAlloc(tmem_base_slot, C::kTmemCols);
+    umma::FenceBeforeThreadSync();
+    __syncthreads();
+    umma::FenceAfterThreadSync();
+    const uint32_t tmem_base = *tmem_base_slot;
+    if (threadIdx.x == 0) FTH_TRACE(1);
+    ClusterArrive();  // "this CTA is running": peers wait for it before they write into our exchange buffer
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t rank = ClusterRank();
+    const uint32_t csize = ClusterSize();                  // a power of two
+    const int cshift = 31 - __clz(static_cast<int>(csize));
+    const int tile = static_cast<int>(blockIdx.x >> cshift);
+    const int lshift = 7 - cshift;                         // log2 of L = rows of the tile this CTA finishes
+    const int rows_per_cta = 1 << lshift;
+    const int kb_begin = static_cast<int>(rank) * static_cast<int>(p.chunk_blocks);
+    int nb = static_cast<int>(p.k_blocks) - kb_begin;
+    if (nb > static_cast<int>(p.chunk_blocks)) nb = static_cast<int>(p.chunk_blocks);
+    if (nb < 0) nb = 0;  // ranks beyond the split have no K range
+    const int m = static_cast<int>(p.q_total);
+    // Kernel parameters live in constant memory and every first touch of a line costs a few hundred cycles: read
+    // what the roles need now, while the previous kernel in the stream may still be running.
+    {
+        const int64_t out_bits = reinterpret_cast<int64_t>(INT8 ? ie.out : fe.out);
+        const int64_t ldo_bits = INT8 ? ie.ldo : fe.ldo;
+        asm volatile("" ::"r"(p.split), "l"(p.p_total), "r"(p.fast4), "r"(p.e4m3), "r"(p.idesc), "l"(p.args.k), "l"(p.args.a),
+                     "r"(p.args.a_dtype), "f"(p.args.a_scale), "f"(fe.out_scale), "f"(fe.ab_scale), "l"(fe.w_channel_scales),
+                     "r"(fe.out_dtype), "l"(out_bits), "l"(ldo_bits), "f"(ie.a_scale), "f"(ie.out_scale), "l"(ie.w_scales),
+                     "l"(p.status), "f"(p.a_inv), "f"(p.out_inv));
+    }
+
+    if (warp == 0) {
+        // ================================ TMA producer ================================
+        if (lane == 0 && nb > 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            auto load_weights = [&](int kb) -> bool {
+                // the first pass over the ring finds every stage free; later passes wait for the MMAs that read it
+                if (kb >= stages && !MbarWait(&empty[stage], phase ^ 1u, p.status, 20, stage)) return false;
+                const int32_t k0 = (kb_begin + kb) * kBlockK;
+                const int32_t p0 = tile * kBlockP;
+                uint8_t* ps = ring + static_cast<size_t>(stage) * kPBytes;
+                MbarExpectTx(&full[stage], kPBytes);
+                if constexpr (P_MN) TmaLoad2D(ps, &map_p, p0, k0, &full[stage]);
+                else TmaLoad2D(ps, &map_p, k0, p0, &full[stage]);
+                if (++stage == stages) { stage = 0; phase ^= 1u; }
+                return true;
+            };
+            // Weights that no earlier work in the stream writes can be fetched before the previous kernel has
+            // finished: their DRAM latency then overlaps its tail.
+            int kb = 0;
+            if (p.args.w_static) {
+                for (; kb < nb && kb < stages; ++kb) load_weights(kb);
+            }
+            FTH_TRACE(3);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            FTH_TRACE(2);
+            if (!convert) {
+                MbarExpectTx(q_full, static_cast<uint32_t>(nb) * BQ * kBlockK);
+                for (int j = 0; j < nb; ++j) TmaLoad2D(q_tiles + j * (BQ * kBlockK), &map_q, (kb_begin + j) * kBlockK, 0, q_full);
+            }
+            for (; kb < nb; ++kb) {
+                if (!load_weights(kb)) break;
+            }
+            FTH_TRACE(4);
+        }
+    } else if (warp == 1) {
+        // ================================ MMA issuer ================================
+        if (lane == 0 && nb > 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool failed = false;
+            for (int kb = 0; kb < nb && !failed; ++kb) {
+                if (!MbarWait(&full[stage], phase, p.status, 22, stage)) { failed = true; break; }
+                if (kb == 0 && !MbarWait(q_full, 0, p.status, 21, 0)) { failed = true; break; }  // activations arrive last
+                if (kb == 0) FTH_TRACE(5);
+                umma::FenceAfterThreadSync();
+                const uint32_t ps = SmemAddr(ring + static_cast<size_t>(stage) * kPBytes);
+                const uint32_t qs = SmemAddr(q_tiles + kb * (BQ * kBlockK));
+#pragma unroll
+                for (int ks = 0; ks < kBlockK / 32; ++ks) {
+                    const uint64_t a_desc = P_MN ? umma::SmemDesc(ps + ks * 4096, 16384, 1024) : umma::SmemDesc(ps + ks * 32, 16, 1024);
+                    const uint64_t b_desc = umma::SmemDesc(qs + ks * 32, 16, 1024);
+                    umma::Mma<INT8>(tmem_base, a_desc, b_desc, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma::Commit(&empty[stage]);
+                if (++stage == stages) { stage = 0; phase ^= 1u; }
+            }
+            FTH_TRACE(6);
+            if (!failed) umma::Commit(tmem_full);
+        }
+    } else {
+        // ====================== activation prologue, accumulator hand-out, reduce + epilogue ======================
+        const int et = threadIdx.x - 64;  // 0 .. 127
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (convert && nb > 0) {
+            // Four consecutive K elements of one activation row per item (one 32-bit word of the swizzled tile), four
+            // items per thread and round so that their loads overlap.  Rows >= m stay unwritten: they only feed
+            // accumulator columns nobody reads.  K beyond the end is zero.
+            const int words_per_row = nb * 32;
+            const int total = m * words_per_row;
+            const bool vec = (reinterpret_cast<uintptr_t>(p.args.a) & 15) == 0;
+            for (int base = et; base < total; base += 4 * 128) {
+                uint4 raw[4];
+                uint32_t dst[4];
+                bool inside[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int item = base + j * 128;
+                    const int row = item / words_per_row;
+                    const int c = item - row * words_per_row;
+                    const int kb = c >> 5, w4 = c & 31;
+                    const int64_t k0 = static_cast<int64_t>(kb_begin + kb) * kBlockK + w4 * 4;
+                    inside[j] = item < total && k0 < p.args.k;  // K is a multiple of 16: a group is in or out as a whole
+                    dst[j] = SmemAddr(q_tiles) + kb * (BQ * kBlockK) + row * 128 + (((w4 >> 2) ^ (row & 7)) << 4) + ((w4 & 3) << 2);
+                    raw[j] = inside[j] ? LoadFourRaw(p.args, static_cast<int64_t>(row) * p.args.k + k0, vec) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (base + j * 128 < total) {
+                        const uint32_t word = inside[j] ? ConvertFourRaw<INT8>(p.args, ie, p.e4m3, p.a_inv, raw[j]) : 0u;
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst[j]), "r"(word) : "memory");
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes → visible to the MMA's reads
+            MbarArrive(q_full);
+            if (et == 0) FTH_TRACE(7);
+        }
+        const int row = (warp & 3) * 32 + lane;  // TMEM lane = channel inside the tile
+        // Bytes this CTA will receive: from each of the `split` chunks, its L rows of ceil(m / 4) 16-byte vectors.
+        if (et == 0) MbarExpectTx(x_full, static_cast<uint32_t>(p.split) * rows_per_cta * ((m + 3) / 4) * 16);
+        ClusterWait();  // every CTA of the cluster is running and has initialised its barriers
+        if (et == 0) FTH_TRACE(8);
+        if (nb > 0) {
+            const bool ok = MbarWait(tmem_full, 0, p.status, 23, 0);
+            if (et == 0) FTH_TRACE(9);
+            umma::FenceAfterThreadSync();
+            if (ok) {
+                // Deal the accumulator rows out: row r goes to CTA r / L, slot [this chunk][r % L].  Each 16-byte
+                // store reports its bytes to the receiver's barrier, so no cluster-wide barrier is needed.
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+                const uint32_t owner = static_cast<uint32_t>(row >> lshift);
+                const uint32_t slot = SmemAddr(exchange) + (((rank << lshift) + (row & (rows_per_cta - 1))) * BQ) * 4;
+                const uint32_t remote = MapToRank(slot, owner);
+                const uint32_t remote_bar = MapToRank(SmemAddr(x_full), owner);
+#pragma unroll
+                for (int c0 = 0; c0 < BQ; c0 += 16) {
+                    if (c0 >= m) break;  // uniform
+                    uint32_t v[16];
+                    umma::TmemLoad16(taddr + c0, v);
+                    umma::TmemLoadWait();
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        if (c0 + j < m) StoreClusterAsync4(remote + (c0 + j) * 4, remote_bar, v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    }
+                }
+            }
+        }
+        if (et == 0) FTH_TRACE(10);
+        // A CTA leaves only after everything addressed to it has landed, so no peer ever writes into a CTA that is gone.
+        const bool delivered = MbarWait(x_full, 0, p.status, 24, 0);
+        if (et == 0) FTH_TRACE(11);
+
+        // One output per thread and round: channel r of this CTA's rows (fastest, so a warp stores consecutive
+        // channels) of activation row q.  The chunks are added in chunk order, as the two-kernel path adds them.
+        for (int item = et; delivered && item < (m << lshift); item += 128) {
+            const int q = item >> lshift;
+            const int r = item & (rows_per_cta - 1);
+            uint32_t t[8];
+#pragma unroll
+            for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? exchange[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
+            uint32_t acc;
+            if constexpr (INT8) {
+                int32_t sum = 0;
+#pragma unroll
+                for (int ss = 0; ss < 8; ++ss) sum += static_cast<int32_t>(t[ss]);
+                acc = static_cast<uint32_t>(sum);
+            } else {
+                float sum = 0.0f;
+#pragma unroll
+                for (int ss = 0; ss < 8; ++ss) {
+                    if (ss < p.split) sum += __uint_as_float(t[ss]);  // no zero is ever added: it could flip a -0
+                }
+                acc = __float_as_uint(sum);
+            }
+            if (et == 0) FTH_TRACE(14);
+            const int64_t n = static_cast<int64_t>(tile) * kBlockP + (static_cast<int64_t>(rank) << lshift) + r;
+            if (n < p.p_total) FinishOne<INT8>(p, fe, ie, q, n, acc);
         }
     }
-    const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
-    uint8_t* dst = static_cast<uint8_t*>(INT8 ? ie.out : fe.out) + q * ldo + p4;
-    if (p4 + 3 < p.p_total && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
-        *reinterpret_cast<uint32_t*>(dst) = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-    } else {
-        for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) dst[i] = static_cast<uint8_t>(b[i]);
+    if (warp < 2) {
+        if (!(warp == 0 && lane == 0 && nb > 0)) asm volatile("griddepcontrol.wait;" ::: "memory");
+        ClusterWait();
+    }
+    if (threadIdx.x == 64) FTH_TRACE(12);
+    umma::FenceBeforeThreadSync();
+    __syncthreads();
+    if (warp == 1) {
+        umma::FenceAfterThreadSync();
+        umma::TmemDealloc(tmem_base, C::kTmemCols);
+        if (lane == 0) FTH_TRACE(13);
     }
 }
 
 // ---------------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------------
+int SmCountTc() {
+    static int count = 0;
+    if (count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = kNumSms;
+    }
+    return count;
+}
+
+// Development knob: how many waves of CTAs the cluster kernel may take (default 1).
+int ClusterWaves() {
+    static int waves = 0;
+    if (waves == 0) {
+        const char* e = getenv("FTH_B200_CLUSTER_WAVES");
+        waves = e ? atoi(e) : 1;
+        if (waves < 0) waves = 0;
+        if (waves == 0 && e) waves = -1;
+    }
+    return waves < 0 ? 0 : waves;
+}
+
+// 1 / s when s is a normal power of two with a normal reciprocal (x * (1/s) then equals x / s bit for bit), else 0.
+float ExactReciprocal(float s) {
+    int e = 0;
+    if (!(s > 0.0f) || !std::isnormal(s) || std::frexp(s, &e) != 0.5f) return 0.0f;
+    const float inv = 1.0f / s;
+    return std::isnormal(inv) ? inv : 0.0f;
+}
+
 int SwapBlockQ(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
 
 struct TcGeometry {
@@ -478,6 +929,7 @@ struct TcGeometry {
     int bq;
     int split;
     int64_t chunk_blocks, k_blocks, p_total, q_total, p_tiles, q_tiles, units, p_pad;
+    int cluster;  // > 0: single-launch cluster kernel with this many CTAs per weight tile
 };
 
 TcGeometry GeometryFor(const LinearArgs& a) {
@@ -496,19 +948,17 @@ TcGeometry GeometryFor(const LinearArgs& a) {
     g.split = static_cast<int>((g.k_blocks + g.chunk_blocks - 1) / g.chunk_blocks);
     g.units = g.p_tiles * g.q_tiles * g.split;
     g.p_pad = g.p_tiles * kBlockP;
+    // Decode-sized problems that fit one wave of CTAs take the single-launch cluster kernel.  Which kernel runs
+    // depends on N, but both add the same chunks in the same order, so the bits do not.
+    g.cluster = 0;
+    if (g.swap && g.bq <= 32 && g.q_tiles == 1 && g.chunk_blocks <= ClusterCfg<16>::kQBlocks) {
+        int c = 1;
+        while (c < g.split) c *= 2;
+        if (g.p_tiles * c <= static_cast<int64_t>(SmCountTc()) * 2 * ClusterWaves()) g.cluster = c;
+    }
     return g;
 }
 
-
-int SmCountTc() {
-    static int count = 0;
-    if (count == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = kNumSms;
-    }
-    return count;
-}
 
 // Encoding a tensor map costs a few microseconds of host time; decode steps call the same (pointer, shape)
 // pairs over and over, so the last few encodings are kept per host thread.
@@ -571,11 +1021,56 @@ int LaunchForLayout(const TcGeometry& g, bool weights_mn, const CUtensorMap& map
 #undef FTH_SWAP_CASE
 }
 
+template <bool INT8, bool P_MN, int BQ>
+int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p_in,
+                       const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
+    TcParams p = p_in;
+    p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks);
+    auto kernel = LinearClusterKernel<INT8, P_MN, BQ>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ClusterCfg<BQ>::kSmemBytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(g.p_tiles * g.cluster));
+    cfg.blockDim = dim3(ClusterCfg<BQ>::kThreads);
+    cfg.dynamicSmemBytes = ClusterCfg<BQ>::SmemFor(g.chunk_blocks);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = static_cast<unsigned>(g.cluster);
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    if (cudaLaunchKernelEx(&cfg, kernel, map_p, map_q, p, fe, ie) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    NoteLaunch("tcgen05");
+    return CheckLaunch();
+}
+
+template <bool INT8>
+int LaunchCluster(const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p,
+                  const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
+    if (g.bq == 16) {
+        return weights_mn ? LaunchClusterTyped<INT8, true, 16>(g, map_p, map_q, p, fe, ie, stream)
+                          : LaunchClusterTyped<INT8, false, 16>(g, map_p, map_q, p, fe, ie, stream);
+    }
+    return weights_mn ? LaunchClusterTyped<INT8, true, 32>(g, map_p, map_q, p, fe, ie, stream)
+                      : LaunchClusterTyped<INT8, false, 32>(g, map_p, map_q, p, fe, ie, stream);
+}
+
 }  // namespace
 
 // A fused Cast / QuantizeLinear in front of the MatMul runs as one elementwise pass that writes the quantised
 // activations (1 byte each) to the front of the scratch buffer; TMA then reads them like any FP8 / INT8 input.
-size_t PrologueBytes(const LinearArgs& a) { return a.a_dtype == 0 ? 0 : static_cast<size_t>((a.m * a.k + 255) / 256 * 256); }
+// The cluster kernel converts its activations itself and needs neither.
+size_t PrologueBytes(const LinearArgs& a) {
+    if (a.a_dtype == 0 || GeometryFor(a).cluster > 0) return 0;
+    return static_cast<size_t>((a.m * a.k + 255) / 256 * 256);
+}
 
 bool Tcgen05Supported(int dtype, const LinearArgs& a) {
     if (a.zero_points) return false;                          // non-zero zero points: the CUDA-core kernels
@@ -592,6 +1087,7 @@ bool Tcgen05Supported(int dtype, const LinearArgs& a) {
 size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& a) {
     (void)dtype;
     const TcGeometry g = GeometryFor(a);
+    if (g.cluster > 0) return 0;
     return PrologueBytes(a) + (g.split == 1 ? 0 : static_cast<size_t>(g.split) * g.q_total * g.p_pad * 4);
 }
 
@@ -604,7 +1100,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     const bool int8 = dtype == FTH_B200_INT8;
     LinearArgs a = a_in;
     void* scratch = scratch_in;
-    if (a.a_dtype != 0) {
+    if (a.a_dtype != 0 && g.cluster == 0) {
         int rc;
         if (int8) rc = LaunchQuantizePerTensor(a.a_dtype, a.a, ie.a_scale, ie.a_zp, static_cast<int8_t*>(scratch_in), a.m * a.k, stream);
         else rc = fth_b200_cast(a.a_dtype, a.a, 1.0f, dtype, scratch_in, a.a_scale, a.m * a.k, stream);
@@ -620,8 +1116,9 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     bool ok;
     if (weights_mn) ok = CachedMap(&map_w, a.w, static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k), 128, 128);
     else ok = CachedMap(&map_w, a.w, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), 128, w_rows_box);
-    ok = ok && CachedMap(&map_a, a.a, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m), 128,
-                         g.swap ? static_cast<uint32_t>(g.bq) : kBlockP);
+    if (a.a_dtype != 0) map_a = map_w;  // cluster kernel with in-kernel conversion: the activation map is unused
+    else ok = ok && CachedMap(&map_a, a.a, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m), 128,
+                              g.swap ? static_cast<uint32_t>(g.bq) : kBlockP);
     if (!ok) return FTH_B200_ERR_CUDA;
     map_p = g.swap ? map_w : map_a;
     map_q = g.swap ? map_a : map_w;
@@ -630,11 +1127,15 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     p.args = a;
     p.swap = g.swap;
     p.p_total = g.p_total; p.q_total = g.q_total; p.p_tiles = g.p_tiles; p.q_tiles = g.q_tiles;
+    p.ring_stages = 0;
     p.split = g.split; p.chunk_blocks = g.chunk_blocks; p.k_blocks = g.k_blocks; p.units = g.units;
     p.p_pad = g.p_pad;
     p.e4m3 = dtype == FTH_B200_FP8E4M3;
     if (int8) p.fast = ie.bias_mode == FTH_B200_BIAS_NONE && ie.out_dtype == 0 && !(ie.is_gemm && (ie.alpha != 1.0f || ie.beta != 1.0f));
     else p.fast = fe.bias_mode == FTH_B200_BIAS_NONE && fe.out_dtype == 0 && !(fe.is_gemm && fe.alpha != 1.0f);
+    p.fast4 = int8 ? p.fast : (fe.bias_mode == FTH_B200_BIAS_NONE && !(fe.is_gemm && fe.alpha != 1.0f));
+    p.a_inv = int8 ? 0.0f : ExactReciprocal(a.a_scale);
+    p.out_inv = int8 ? 0.0f : ExactReciprocal(fe.out_scale);
     p.scratch = scratch;
     p.status = DeviceStatusPtr();
     // operand formats: kind::f8f6f4 0 = E4M3, 1 = E5M2; kind::i8 1 = signed 8-bit.  D: 1 = F32, 2 = S32.
@@ -642,6 +1143,10 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     const bool p_mn = g.swap && weights_mn;
     const bool q_mn = !g.swap && weights_mn;
     p.idesc = umma::InstrDesc(int8 ? 2u : 1u, fmt, fmt, p_mn, q_mn, kBlockP, static_cast<uint32_t>(g.bq));
+    if (g.cluster > 0) {
+        return int8 ? LaunchCluster<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
+                    : LaunchCluster<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
+    }
     const int rc = int8 ? LaunchForLayout<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
                         : LaunchForLayout<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
     if (rc != FTH_B200_OK || g.split == 1) return rc;

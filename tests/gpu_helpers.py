@@ -45,6 +45,13 @@ def run_fp8_linear(torch, dtype, op, case, *, trans_b=False, variant=B.VARIANT_A
     B.fp8_linear(d)
     torch.cuda.synchronize()
     host = buf.cpu().numpy().view(np_out)
+    if m <= 32 and variant in (B.VARIANT_AUTO, B.VARIANT_TCGEN05):
+        # decode-sized problems may prefetch weights the caller declares static: same bytes either way
+        buf.fill_(fill)
+        d.weights_static = 1
+        B.fp8_linear(d)
+        torch.cuda.synchronize()
+        assert np.array_equal(buf.cpu().numpy().view(np.uint8), host.view(np.uint8)), "weights_static changed the result"
     if canary:
         ref_fill = np.full(1, fill).astype(host.dtype if np_out is not np.uint16 else np.int16).view(np_out)[0]
         assert (host[0] == ref_fill).all() and (host[-1] == ref_fill).all(), "write outside the output rows"
@@ -76,6 +83,12 @@ def run_int8_linear(torch, op, case, *, trans_b=False, variant=B.VARIANT_AUTO, a
     B.int8_linear(d)
     torch.cuda.synchronize()
     host = buf.cpu().numpy()
+    if m <= 32 and variant in (B.VARIANT_AUTO, B.VARIANT_TCGEN05):
+        buf.fill_(77)
+        d.weights_static = 1
+        B.int8_linear(d)
+        torch.cuda.synchronize()
+        assert np.array_equal(buf.cpu().numpy().view(np.uint8), host.view(np.uint8)), "weights_static changed the result"
     assert (host[0] == 77).all() and (host[-1] == 77).all(), "write outside the output rows"
     return host[1:m + 1].astype(np_out)
 

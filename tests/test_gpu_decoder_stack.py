@@ -62,10 +62,10 @@ def test_decoder_stack_matches_oracle(cuda, stack_weights, m):
     gpu = GpuProjector(cuda, stack_weights)
     got = D.from_bf16(D.run_stack(gpu, stack_weights, x0)).astype(np.float64)
     assert gpu.launches == 7 * D.LAYERS and gpu.variants == {"tcgen05"}
-    if m in (1, 16):  # the same stack without a workspace runs on the scratch-free CUDA-core kernels: same bytes
+    if m in (1, 16):  # the same stack without a workspace: whichever scratch-free kernels run, the result holds
         plain = GpuProjector(cuda, stack_weights, with_workspace=False)
         got_plain = D.from_bf16(D.run_stack(plain, stack_weights, x0)).astype(np.float64)
-        assert "tcgen05" not in plain.variants
+        assert plain.launches == 7 * D.LAYERS
         cos_plain = float((got_plain * want).sum() / (np.linalg.norm(got_plain) * np.linalg.norm(want)))
         assert cos_plain >= 0.999
     assert np.isfinite(got).all() and np.isfinite(want).all()
