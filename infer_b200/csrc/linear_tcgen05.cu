@@ -17,8 +17,6 @@
 // small second kernel adds the S partials of every output in chunk order and runs the epilogue.  (A
 // single-kernel hand-off through fences and arrival counters was measured first: the gpu-scope fence per
 // work unit stalled the epilogue warps behind the streaming loads and cost more than the extra launch.)
-#include <stdlib.h>
-
 #include <cmath>
 
 #include "common.cuh"
@@ -902,18 +900,6 @@ int SmCountTc() {
     return count;
 }
 
-// Development knob: how many waves of CTAs the cluster kernel may take (default 1).
-int ClusterWaves() {
-    static int waves = 0;
-    if (waves == 0) {
-        const char* e = getenv("FTH_B200_CLUSTER_WAVES");
-        waves = e ? atoi(e) : 1;
-        if (waves < 0) waves = 0;
-        if (waves == 0 && e) waves = -1;
-    }
-    return waves < 0 ? 0 : waves;
-}
-
 // 1 / s when s is a normal power of two with a normal reciprocal (x * (1/s) then equals x / s bit for bit), else 0.
 float ExactReciprocal(float s) {
     int e = 0;
@@ -954,7 +940,8 @@ TcGeometry GeometryFor(const LinearArgs& a) {
     if (g.swap && g.bq <= 32 && g.q_tiles == 1 && g.chunk_blocks <= ClusterCfg<16>::kQBlocks) {
         int c = 1;
         while (c < g.split) c *= 2;
-        if (g.p_tiles * c <= static_cast<int64_t>(SmCountTc()) * 2 * ClusterWaves()) g.cluster = c;
+        // more than one wave of CTAs: the persistent kernel keeps its ring full across tiles and is faster (measured)
+        if (g.p_tiles * c <= static_cast<int64_t>(SmCountTc()) * 2) g.cluster = c;
     }
     return g;
 }
