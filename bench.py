@@ -227,7 +227,7 @@ def run_gpu_arm(args):
 
     def make_desc(m, w, sw, a, out, ldo=0):
         d = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=K, n=w.shape[1], a=a, w=w, out=out, a_scale=sa,
-                              w_scale=sw, out_scale=out_scale, ldo=ldo)
+                              w_scale=sw, out_scale=out_scale, ldo=ldo, weights_static=True)
         ws = B.linear_workspace(torch, d)
         return d, ws
 
@@ -344,13 +344,14 @@ def extra_measurements(torch, B, dev, peaks, fp8_call, int8_call, stream, sa, ou
                 a = torch.randint(0, 0x7E, (m, K), dtype=torch.uint8, device=dev)
                 o = torch.empty((m, n), dtype=torch.uint8, device=dev)
                 ds = [B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=K, n=n, a=a, w=ww, out=o, a_scale=sa, w_scale=sw,
-                                        out_scale=out_scale * 4) for ww in (w, w2)]
+                                        out_scale=out_scale * 4, weights_static=True) for ww in (w, w2)]
                 call = fp8_call
             else:
                 a = torch.randint(-127, 128, (m, K), dtype=torch.int8, device=dev)
                 o = torch.empty((m, n), dtype=torch.int8, device=dev)
                 ds = [B.int8_linear_desc(op=B.OP_MATMUL, m=m, k=K, n=n, a=a, w=ww.view(torch.int8), out=o, a_scale=0.02, a_zp=0,
-                                         w_scales=scales, w_zps=None, w_params=n, out_scale=2.0, out_zp=0) for ww in (w, w2)]
+                                         w_scales=scales, w_zps=None, w_params=n, out_scale=2.0, out_zp=0, weights_static=True)
+                      for ww in (w, w2)]
                 call = int8_call
             keep = [B.linear_workspace(torch, d) for d in ds]
             i = [0]

@@ -54,6 +54,7 @@ extern "C" int fth_b200_plan_create_fp8_linear(const fth_b200_fp8_linear_desc* h
     if (!p) return FTH_B200_ERR_INVALID;
     p->kind = Kind::kFp8Linear;
     p->fp8 = *h;
+    p->fp8.weights_static = 1;  // uploaded once, synchronously, below; never written again
     const int a_dtype = h->a_dtype ? h->a_dtype : h->dtype;
     const int out_dtype = h->out_dtype ? h->out_dtype : h->dtype;
     const int64_t ldo = h->ldo ? h->ldo : h->n;
@@ -87,6 +88,7 @@ extern "C" int fth_b200_plan_create_int8_linear(const fth_b200_int8_linear_desc*
     if (!p) return FTH_B200_ERR_INVALID;
     p->kind = Kind::kInt8Linear;
     p->int8 = *h;
+    p->int8.weights_static = 1;
     const int a_dtype = h->a_dtype ? h->a_dtype : FTH_B200_INT8;
     const int out_dtype = h->out_dtype ? h->out_dtype : FTH_B200_INT8;
     const int64_t ldo = h->ldo ? h->ldo : h->n;
