@@ -17,6 +17,8 @@
 // small second kernel adds the S partials of every output in chunk order and runs the epilogue.  (A
 // single-kernel hand-off through fences and arrival counters was measured first: the gpu-scope fence per
 // work unit stalled the epilogue warps behind the streaming loads and cost more than the extra launch.)
+#include <stdlib.h>
+
 #include <cmath>
 
 #include "common.cuh"
@@ -82,7 +84,7 @@ struct Cfg {
     static constexpr int kEpilogueThreads = 128 * kEpilogueGroups;
     static constexpr int kThreads = 64 + kEpilogueThreads;
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
-                                         (BQ > 128 ? BQ * 16 : 0) /*per-column epilogue constants*/;
+                                         (BQ > 128 ? BQ * 24 : 0) /*per-column epilogue constants*/;
 };
 
 template <int THREADS>
@@ -101,19 +103,23 @@ __device__ __forceinline__ void StoreOne(const Fp8Epilogue& fe, const Int8Epilog
     }
 }
 
-// INT8 requantisation with an FP32 estimate and an exact fallback.
-//   est = fma(float(acc), float(scale / out_scale), zp) differs from the exact value T by at most
-//   (|T| + |zp|) * 4 * 2^-24 < 1e-4 for |T| <= 300 (three FP32 roundings of relative size 2^-24), and the
-//   reference's double sequence differs from T by less than 1e-12.  So whenever est is farther than 2e-4 from
-//   a rounding boundary x.5 both round to the same integer; the few values inside the band (about 4 in 10^4)
-//   take the exact double sequence.  |est| >= 300 saturates either way.
-__device__ __forceinline__ int8_t RequantFast(int32_t acc, float mult_f, double scale_d, double so_d, int32_t zp) {
+// INT8 requantisation in three stages, each deciding only what its error bound allows.
+//   1. est = fma(float(acc), float(scale / out_scale), zp) differs from the exact value T by at most
+//      (|T| + |zp|) * 4 * 2^-24 < 1e-4 for |T| <= 300 (three FP32 roundings), and the reference's double sequence
+//      differs from T by less than 1e-12.  Farther than 2e-4 from a rounding boundary x.5, both round alike.
+//      |est| >= 300 saturates either way.
+//   2. The ~4 values in 10^4 inside that band take one double FMA with mult_d = scale / out_scale to within a few
+//      2^-53 (RequantInt32: within 1e-12 of the reference's value, decided unless within 1e-6 of a boundary).
+//   3. What is left runs the reference's own sequence (double multiply, divide, add, round).
+// A warp takes a stage whenever one of its lanes needs it, and the double divide of stage 3 costs a thousand
+// cycles: with stage 2 in between it is practically never reached.
+__device__ __forceinline__ int8_t RequantFast(int32_t acc, float mult_f, double mult_d, double scale_d, double so_d, int32_t zp) {
     const float est = fmaf(__int2float_rn(acc), mult_f, static_cast<float>(zp));
     if (est >= 300.0f) return 127;
     if (est <= -300.0f) return -128;
     const float fl = floorf(est);
     const float frac = est - fl;
-    if (fabsf(frac - 0.5f) < 2e-4f) return RequantExact(__dmul_rn(static_cast<double>(acc), scale_d), so_d, zp);
+    if (fabsf(frac - 0.5f) < 2e-4f) return RequantInt32(acc, scale_d, mult_d, so_d, zp);
     const float r = frac < 0.5f ? fl : fl + 1.0f;
     return static_cast<int8_t>(static_cast<int32_t>(fmaxf(-128.0f, fminf(127.0f, r))));
 }
@@ -146,7 +152,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + kAcc);
     // per-column epilogue constants of the current tile (normal mode only): [BQ] doubles, then [BQ] floats
     double* col_scale = reinterpret_cast<double*>(reinterpret_cast<uint8_t*>(full) + 256);
-    float* col_mult = reinterpret_cast<float*>(col_scale + BQ);
+    double* col_multd = col_scale + BQ;
+    float* col_mult = reinterpret_cast<float*>(col_multd + BQ);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
@@ -264,6 +271,9 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         constexpr int kColsPerGroup = BQ / C::kEpilogueGroups;
         const int row = lane_group * 32 + lane;     // row inside the P tile
         const double so_d = static_cast<double>(ie.out_scale);
+        // One double divide per thread; scale * so_inv is within 2^-52 of scale / out_scale, which the error bounds of
+        // the two estimate stages of RequantFast absorb.
+        const double so_inv = INT8 ? 1.0 / so_d : 0.0;
         const float so_f = fe.out_scale;
         const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
         uint8_t* out8 = static_cast<uint8_t*>(INT8 ? ie.out : fe.out);
@@ -283,14 +293,15 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const int q_count = static_cast<int>(q_left < BQ ? q_left : BQ);
 
             // ---- scale constants: per lane (swapped: the lane is an output channel) or per column via smem ----
-            double row_scale_d = 0.0;
+            double row_scale_d = 0.0, row_mult_d = 0.0;
             float row_mult = 0.0f;
             if (p.fast) {
                 if (p.swap) {
                     if (row_ok) {
                         if constexpr (INT8) {
                             row_scale_d = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? pg : 0]);
-                            row_mult = static_cast<float>(row_scale_d / so_d);
+                            row_mult_d = row_scale_d * so_inv;
+                            row_mult = static_cast<float>(row_mult_d);
                         } else {
                             row_mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[pg] : fe.ab_scale;
                         }
@@ -303,7 +314,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                             if constexpr (INT8) {
                                 const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
                                 col_scale[c] = sd;
-                                col_mult[c] = static_cast<float>(sd / so_d);
+                                col_multd[c] = sd * so_inv;
+                                col_mult[c] = static_cast<float>(sd * so_inv);
                             } else {
                                 col_mult[c] = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
                             }
@@ -333,7 +345,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                         if (j >= cnt) break;  // uniform: a decode-sized M leaves most columns unused
                         const float mult = p.swap ? row_mult : col_mult[c0 + j];
                         const double sd = p.swap ? row_scale_d : col_scale[c0 + j];
-                        b[j] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[j]), mult, sd, so_d, ie.out_zp));
+                        const double md = p.swap ? row_mult_d : col_multd[c0 + j];
+                        b[j] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[j]), mult, md, sd, so_d, ie.out_zp));
                     }
                 } else {
 #pragma unroll
@@ -416,6 +429,229 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 }
 
 
+// ---------------------------------------------------------------------------------------------------------
+// Dense tiles on CTA pairs (M > 128): tcgen05.mma.cta_group::2.
+//
+// With one CTA per 128 x 256 tile every MMA reads 4 KB of A and 8 KB of B from shared memory, and that read
+// bandwidth (measured 77 % busy) is what holds the tensor pipe at ~72 %.  A pair of CTAs on neighbouring SMs works
+// on a 256 x 256 tile instead: each CTA stages its own 128 rows of A and its own 128 of the 256 B columns, the
+// leader issues M = 256 MMAs that read both CTAs' shared memory, and each CTA's tensor memory receives its 128 rows
+// of D.  Per MMA a CTA now reads 4 KB + 4 KB, and pulls a third less through L2 as well.  No multicast loads: each
+// CTA fetches exactly the bytes it stages.
+//
+//   warp 0 (each CTA)   TMA producer for the CTA's own A / B halves; bytes are reported to the LEADER's full barrier
+//   warp 1 (leader)     MMA issue; tcgen05.commit multicast frees the stage in both CTAs / publishes the accumulator
+//   warps 2-9 (each)    epilogue of the CTA's own 128 rows; buffers are handed back on the leader's barrier
+// ---------------------------------------------------------------------------------------------------------
+struct PairCfg {
+    static constexpr int kTileN = 256;
+    static constexpr int kHalfN = 128;                          // B columns staged by one CTA
+    static constexpr int kStageBytes = kPBytes + kHalfN * kBlockK;  // 32 KB
+    static constexpr int kStages = 6;
+    static constexpr uint32_t kTmemCols = 512;                  // two 256-column accumulator buffers
+    static constexpr int kEpilogueThreads = 256;
+    static constexpr int kThreads = 64 + kEpilogueThreads;
+    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kTileN * 24;
+};
+
+template <bool INT8, bool Q_MN>
+__global__ void __launch_bounds__(PairCfg::kThreads, 1)
+LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, TcParams p,
+                 Fp8Epilogue fe, Int8Epilogue ie) {
+    using C = PairCfg;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(C::kStages) * C::kStageBytes);
+    uint64_t* empty = full + C::kStages;
+    uint64_t* tmem_full = empty + C::kStages;      // [2]
+    uint64_t* tmem_empty = tmem_full + 2;          // [2], used in the leader only
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    double* col_scale = reinterpret_cast<double*>(reinterpret_cast<uint8_t*>(full) + 256);
+    double* col_multd = col_scale + C::kTileN;
+    float* col_mult = reinterpret_cast<float*>(col_multd + C::kTileN);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t rank = ClusterRank();           // 0 = leader
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], 2 * 8); }  // 8 epilogue warps per CTA
+        FenceBarrierInit();
+    }
+    if (warp == 1) umma::TmemAllocPair(tmem_base_slot, C::kTmemCols);
+    umma::FenceBeforeThreadSync();
+    __syncthreads();
+    umma::FenceAfterThreadSync();
+    const uint32_t tmem_base = *tmem_base_slot;
+    // both CTAs' barriers and tensor memory exist before either touches the other's
+    ClusterArrive();
+    ClusterWait();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const int64_t m_pairs = (p.p_total + 255) / 256;
+    const int64_t units = m_pairs * p.q_tiles;
+    const int64_t pair_id = blockIdx.x / 2, pairs = gridDim.x / 2;
+    bool failed = false;
+
+    if (warp == 0) {
+        // ================================ TMA producer (both CTAs) ================================
+        if (lane == 0) {
+            TmaPrefetchDescriptor(&map_p);
+            TmaPrefetchDescriptor(&map_q);
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int64_t u = pair_id; u < units && !failed; u += pairs) {
+                const int64_t mt = u % m_pairs, nt = u / m_pairs;  // row tiles fastest: the pairs running together share weights in L2
+                const int32_t p0 = static_cast<int32_t>(mt * 256 + rank * 128);
+                const int32_t q0 = static_cast<int32_t>(nt * C::kTileN + rank * C::kHalfN);
+                for (int64_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!MbarWait(&empty[stage], phase ^ 1u, p.status, 30, stage)) { failed = true; break; }
+                    const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+                    uint8_t* ps = ring + static_cast<size_t>(stage) * C::kStageBytes;
+                    uint8_t* qs = ps + kPBytes;
+                    // the leader's barrier counts the bytes of both CTAs
+                    if (leader) MbarExpectTx(&full[stage], 2 * C::kStageBytes);
+                    const uint32_t bar = MapToRank(SmemAddr(&full[stage]), 0);
+                    TmaLoad2DPair(ps, &map_p, k0, p0, bar);
+                    if constexpr (Q_MN) TmaLoad2DPair(qs, &map_q, q0, k0, bar);
+                    else TmaLoad2DPair(qs, &map_q, k0, q0, bar);
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================================ MMA issuer (leader only) ================================
+        if (lane == 0 && leader) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int64_t iter = 0;
+            for (int64_t u = pair_id; u < units && !failed; u += pairs, ++iter) {
+                const int acc = static_cast<int>(iter & 1);
+                const uint32_t acc_phase = static_cast<uint32_t>((iter >> 1) & 1);
+                if (!MbarWait(&tmem_empty[acc], acc_phase ^ 1u, p.status, 31, acc)) { failed = true; break; }
+                umma::FenceAfterThreadSync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * C::kTileN);
+                for (int64_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!MbarWait(&full[stage], phase, p.status, 32, stage)) { failed = true; break; }
+                    umma::FenceAfterThreadSync();
+                    const uint32_t ps = SmemAddr(ring + static_cast<size_t>(stage) * C::kStageBytes);
+                    const uint32_t qs = ps + kPBytes;
+#pragma unroll
+                    for (int ks = 0; ks < kBlockK / 32; ++ks) {
+                        const uint64_t a_desc = umma::SmemDesc(ps + ks * 32, 16, 1024);
+                        const uint64_t b_desc = Q_MN ? umma::SmemDesc(qs + ks * 4096, 16384, 1024) : umma::SmemDesc(qs + ks * 32, 16, 1024);
+                        umma::MmaPair<INT8>(d_tmem, a_desc, b_desc, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma::CommitPair(&empty[stage], 3);  // the stage is free in both CTAs once these MMAs have read it
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!failed) umma::CommitPair(&tmem_full[acc], 3);
+            }
+        }
+    } else {
+        // ================================ epilogue (both CTAs, own 128 rows) ================================
+        const int et = threadIdx.x - 64;            // 0 .. 255
+        const int lane_group = warp & 3;
+        const int col_group = (warp - 2) / 4;       // which 128-column half this warpgroup drains
+        const int row = lane_group * 32 + lane;
+        const double so_d = static_cast<double>(ie.out_scale);
+        const double so_inv = INT8 ? 1.0 / so_d : 0.0;  // see the single-CTA kernel
+        const float so_f = fe.out_scale;
+        const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
+        uint8_t* out8 = static_cast<uint8_t*>(INT8 ? ie.out : fe.out);
+        const uint32_t leader_empty = MapToRank(SmemAddr(tmem_empty), 0);
+        int64_t iter = 0;
+        int64_t staged_nt = -1;
+        for (int64_t u = pair_id; u < units; u += pairs, ++iter) {
+            const int64_t mt = u % m_pairs, nt = u / m_pairs;
+            const int acc = static_cast<int>(iter & 1);
+            const uint32_t acc_phase = static_cast<uint32_t>((iter >> 1) & 1);
+            const int64_t mg = mt * 256 + rank * 128 + row;
+            const bool row_ok = mg < p.p_total;
+            const int64_t n_begin = nt * C::kTileN;
+            const int64_t n_left = p.q_total - n_begin;
+            const int n_count = static_cast<int>(n_left < C::kTileN ? n_left : C::kTileN);
+            if (p.fast && nt != staged_nt) {  // uniform across the epilogue warps
+                EpilogueBarrier<C::kEpilogueThreads>();  // readers of the previous tile's constants are done
+                for (int c = et; c < C::kTileN; c += C::kEpilogueThreads) {
+                    const int64_t n = n_begin + c;
+                    if (n < p.q_total) {
+                        if constexpr (INT8) {
+                            const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
+                            col_scale[c] = sd;
+                            col_multd[c] = sd * so_inv;
+                            col_mult[c] = static_cast<float>(sd * so_inv);
+                        } else {
+                            col_mult[c] = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
+                        }
+                    }
+                }
+                EpilogueBarrier<C::kEpilogueThreads>();
+                staged_nt = nt;
+            }
+            if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 33, acc)) failed = true;
+            umma::FenceAfterThreadSync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * C::kTileN);
+#pragma unroll 1
+            for (int c0 = col_group * 128; c0 < (col_group + 1) * 128; c0 += 16) {
+                if (c0 >= n_count) break;  // uniform across the warp
+                uint32_t v[16];
+                umma::TmemLoad16(taddr + c0, v);
+                umma::TmemLoadWait();
+                const int cnt = n_count - c0 < 16 ? n_count - c0 : 16;
+                if (failed || !row_ok) continue;
+                if (!p.fast) {
+                    for (int j = 0; j < cnt; ++j) StoreOne<INT8>(fe, ie, p.e4m3, mg, n_begin + c0 + j, v[j]);
+                    continue;
+                }
+                uint32_t b[16];
+                if constexpr (INT8) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        b[j] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[j]), col_mult[c0 + j], col_multd[c0 + j], col_scale[c0 + j], so_d, ie.out_zp));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const float y0 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j]), col_mult[c0 + j]), so_f);
+                        const float y1 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j + 1]), col_mult[c0 + j + 1]), so_f);
+                        const uint32_t pair = EncodePair(p.e4m3, y0, y1);
+                        b[j] = pair & 0xffu;
+                        b[j + 1] = pair >> 8;
+                    }
+                }
+                uint8_t* dst = out8 + mg * ldo + n_begin + c0;
+                if (cnt == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    uint4 w;
+                    w.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+                    w.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+                    w.z = b[8] | (b[9] << 8) | (b[10] << 16) | (b[11] << 24);
+                    w.w = b[12] | (b[13] << 8) | (b[14] << 16) | (b[15] << 24);
+                    *reinterpret_cast<uint4*>(dst) = w;
+                } else {
+                    for (int j = 0; j < cnt; ++j) dst[j] = static_cast<uint8_t>(b[j]);
+                }
+            }
+            // this CTA's half of the accumulator buffer is drained: tell the leader's MMA warp
+            umma::FenceBeforeThreadSync();
+            __syncwarp();
+            if (lane == 0) MbarArriveRemote(leader_empty + acc * 8);
+        }
+    }
+
+    // Neither CTA may leave (or free its tensor memory) while the leader's MMAs can still read the peer's shared
+    // memory or write its tensor memory, or while remote arrivals are in flight.
+    umma::FenceBeforeThreadSync();
+    __syncthreads();
+    ClusterArrive();
+    ClusterWait();
+    if (warp == 1) {
+        umma::FenceAfterThreadSync();
+        umma::TmemDeallocPair(tmem_base, C::kTmemCols);
+    }
+}
+
 // Epilogue of four consecutive output channels p4 .. p4+3 of activation row q (swapped tiling), given their
 // complete accumulators: the vectorised fast path or the generic per-element store.
 template <bool INT8>
@@ -433,7 +669,8 @@ __device__ __forceinline__ void FinishFour(const TcParams& p, const Fp8Epilogue&
             const int64_t n = p4 + i < p.p_total ? p4 + i : p.p_total - 1;
             const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
             const double so_d = static_cast<double>(ie.out_scale);
-            b[i] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[i]), static_cast<float>(sd / so_d), sd, so_d, ie.out_zp));
+            const double md = sd / so_d;
+            b[i] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[i]), static_cast<float>(md), md, sd, so_d, ie.out_zp));
         }
     } else {
         float y[4];
@@ -565,23 +802,6 @@ struct ClusterCfg {
     }
 };
 
-__device__ __forceinline__ uint32_t ClusterRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ uint32_t ClusterSize() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void ClusterArrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
-__device__ __forceinline__ void ClusterWait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
-// Address of this CTA's shared-memory location `smem_addr` inside CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t MapToRank(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-// 16-byte store into a peer CTA's shared memory that adds its 16 bytes to the transaction count of a barrier in
-// the same peer: the receiver waits on that barrier and needs no other synchronisation with the sender.
-__device__ __forceinline__ void StoreClusterAsync4(uint32_t addr, uint32_t bar, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
-    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
-                 ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
-}
-
 // Four consecutive activation elements of a fused Cast (FP8) / QuantizeLinear (INT8) prologue.  The raw load and
 // the conversion are separate so that a thread can have several loads in flight before it converts the first.
 // `index` is a multiple of 4; `vec` says the base pointer is 16-byte aligned.
@@ -634,7 +854,8 @@ __device__ __forceinline__ void FinishOne(const TcParams& p, const Fp8Epilogue& 
     if constexpr (INT8) {
         const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
         const double so_d = static_cast<double>(ie.out_scale);
-        static_cast<int8_t*>(ie.out)[q * ie.ldo + n] = RequantFast(static_cast<int32_t>(raw), static_cast<float>(sd / so_d), sd, so_d, ie.out_zp);
+        const double md = sd / so_d;
+        static_cast<int8_t*>(ie.out)[q * ie.ldo + n] = RequantFast(static_cast<int32_t>(raw), static_cast<float>(md), md, sd, so_d, ie.out_zp);
     } else {
         const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
         const float t = __fmul_rn(__uint_as_float(raw), mult);
@@ -1008,6 +1229,37 @@ int LaunchForLayout(const TcGeometry& g, bool weights_mn, const CUtensorMap& map
 #undef FTH_SWAP_CASE
 }
 
+template <bool INT8, bool Q_MN>
+int LaunchPairTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p, const Fp8Epilogue& fe,
+                    const Int8Epilogue& ie, cudaStream_t stream) {
+    auto kernel = LinearPairKernel<INT8, Q_MN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PairCfg::kSmemBytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
+        configured = true;
+    }
+    const int64_t units = ((p.p_total + 255) / 256) * p.q_tiles;
+    const int64_t slots = SmCountTc() / 2;
+    const int64_t pairs = units < slots ? units : slots;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(pairs * 2));
+    cfg.blockDim = dim3(PairCfg::kThreads);
+    cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    if (cudaLaunchKernelEx(&cfg, kernel, map_p, map_q, p, fe, ie) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    NoteLaunch("tcgen05");
+    return CheckLaunch();
+}
+
 template <bool INT8, bool P_MN, int BQ>
 int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p_in,
                        const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
@@ -1133,6 +1385,16 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     if (g.cluster > 0) {
         return int8 ? LaunchCluster<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
                     : LaunchCluster<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
+    }
+    if (!g.swap && getenv("FTH_B200_DENSE_SINGLE") == nullptr) {
+        // CTA pairs: each CTA stages 128 activation rows and 128 weight columns of a 256 x 256 tile
+        CUtensorMap map_w_half = map_w;
+        if (!weights_mn && !CachedMap(&map_w_half, a.w, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), 128, 128)) return FTH_B200_ERR_CUDA;
+        p.idesc = umma::InstrDesc(int8 ? 2u : 1u, fmt, fmt, false, q_mn, 256, 256);
+        if (int8) return weights_mn ? LaunchPairTyped<true, true>(map_a, map_w_half, p, fe, ie, stream)
+                                    : LaunchPairTyped<true, false>(map_a, map_w_half, p, fe, ie, stream);
+        return weights_mn ? LaunchPairTyped<false, true>(map_a, map_w_half, p, fe, ie, stream)
+                          : LaunchPairTyped<false, false>(map_a, map_w_half, p, fe, ie, stream);
     }
     const int rc = int8 ? LaunchForLayout<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
                         : LaunchForLayout<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);

@@ -83,6 +83,41 @@ __device__ __forceinline__ void Commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(bar)) : "memory");
 }
 
+// ---- CTA-pair forms (cta_group::2): one MMA spans the two CTAs of a cluster pair --------------------------------
+// Allocation and release are executed by one warp of EACH CTA of the pair; both receive the same address.
+__device__ __forceinline__ void TmemAllocPair(uint32_t* smem_result, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(smem_result)), "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void TmemDeallocPair(uint32_t base, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+// Issued by one thread of the leader CTA (even rank).  M = 256: rows 0..127 come from the leader's A tile, rows
+// 128..255 from the peer's tile at the same shared-memory offset; the N columns of B are split the same way
+// (first half in the leader's shared memory, second half in the peer's).  Each CTA's tensor memory receives its
+// 128 rows of D.
+template <bool INT8>
+__device__ __forceinline__ void MmaPair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (INT8) {
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n}"
+            ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
+            ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+// One arrival on the barrier at the same shared-memory offset in every CTA named by `cta_mask`, once all MMAs this
+// thread issued so far have completed.
+__device__ __forceinline__ void CommitPair(uint64_t* bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(SmemAddr(bar)), "h"(cta_mask) : "memory");
+}
+
 // ---- TMEM → registers: 32 lanes x 16 consecutive 32-bit columns per warp --------------------------------------
 __device__ __forceinline__ void TmemLoad16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(

@@ -71,12 +71,42 @@ __device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity, int* st
     return false;
 }
 
+// ---- thread-block clusters: ranks, barrier, distributed shared memory ------------------------------------
+__device__ __forceinline__ uint32_t ClusterRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t ClusterSize() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void ClusterArrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void ClusterWait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// Address of this CTA's shared-memory location `smem_addr` inside CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t MapToRank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+// 16-byte store into a peer CTA's shared memory that adds its 16 bytes to the transaction count of a barrier in
+// the same peer: the receiver waits on that barrier and needs no other synchronisation with the sender.
+__device__ __forceinline__ void StoreClusterAsync4(uint32_t addr, uint32_t bar, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
+}
+// One arrival on a barrier in a peer CTA's shared memory (`bar` is a shared::cluster address).
+__device__ __forceinline__ void MbarArriveRemote(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // ---- TMA loads (no multicast) -----------------------------------------------------------------------------
 // x is the innermost coordinate; x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void TmaLoad2D(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(SmemAddr(smem_dst)), "l"(map), "r"(SmemAddr(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+// Load issued by either CTA of a pair into its own shared memory; the bytes are reported to `bar_cluster_addr`, a
+// shared::cluster address that may name a barrier of the other CTA of the pair.  No multicast.
+__device__ __forceinline__ void TmaLoad2DPair(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(SmemAddr(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
         : "memory");
 }
 __device__ __forceinline__ void TmaLoad4D(void* smem_dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2,
