@@ -1,24 +1,20 @@
-// Tensor-core linear kernel: tcgen05.mma (kind::f8f6f4 / kind::i8) with accumulators in tensor memory,
-// operands staged by TMA into a 128-byte-swizzled shared-memory ring, fused scale / bias / requant / encode
-// epilogue.  One persistent CTA per SM, warp-specialised:
-//   warp 0     TMA producer (one thread)        — full[] / empty[] mbarriers per ring stage
-//   warp 1     TMEM allocation + MMA issue (one thread)
-//   warps 2-5  epilogue: tcgen05.ld from one of two accumulator buffers while the next tile's MMAs run
+// Tensor-core linear kernels: tcgen05.mma (kind::f8f6f4 / kind::i8) with accumulators in tensor memory, operands
+// staged by TMA into 128-byte-swizzled shared memory, fused scale / bias / requant / encode epilogues.
+// Weights are consumed in the layout Feather stores them: [K,N] tiles are MN-major operands, [N,K] tiles K-major
+// operands — no repacking pass, no second copy of the weights.  Three kernels, chosen by shape:
 //
-// The 128 TMEM lanes carry the "P" operand's rows, the accumulator columns the "Q" operand's rows:
-//   normal (M > 128):  P = activations [M,K],  Q = weights       → D[m][n]
-//   swapped (M <= 128): P = weights,           Q = activations  → D[n][m], so a decode-sized M pads only the
-//                       narrow UMMA N dimension (16..128) and the weight stream fills all 128 lanes.
-// Weights are consumed in the layout Feather stores them: [K,N] tiles are MN-major operands, [N,K] tiles
-// K-major operands — no repacking pass, no second copy of the weights.
-//
-// Swapped mode splits K into S chunks (S depends on K only) so that a 28672-column weight gives ~1800 work
-// units for 148 SMs; partial accumulators go to a global scratch buffer with plain coalesced stores and a
-// small second kernel adds the S partials of every output in chunk order and runs the epilogue.  (A
-// single-kernel hand-off through fences and arrival counters was measured first: the gpu-scope fence per
-// work unit stalled the epilogue warps behind the streaming loads and cost more than the extra launch.)
-#include <stdlib.h>
-
+//   LinearPairKernel     M > 128: 256 x 256 output tiles on CTA pairs (cta_group::2), activations on the TMEM lanes.
+//   LinearTcgen05Kernel  M <= 128, more than one wave of work: operands swapped — weights on the 128 TMEM lanes,
+//                        activations on a 16..128-wide UMMA N — so a decode-sized M pads only the narrow dimension and
+//                        the weight stream fills all lanes.  One or two persistent CTAs per SM, warp-specialised
+//                        (warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2-5 epilogue draining one of
+//                        2-4 accumulator buffers while the next unit's MMAs run).  K is split into S chunks (S depends
+//                        on K and M only) so that a 28672-column weight gives ~1800 work units; partial accumulators
+//                        go to a scratch buffer with coalesced stores and SplitReduceKernel adds the S partials of
+//                        every output in chunk order and runs the epilogue.  (A single-kernel hand-off through fences
+//                        and arrival counters was measured first: the gpu-scope fence per work unit stalled the
+//                        epilogue warps behind the streaming loads and cost more than the extra launch.)
+//   LinearClusterKernel  M <= 32, one wave of work: the same split, inside a thread-block cluster, in one launch.
 #include <cmath>
 
 #include "common.cuh"
@@ -79,12 +75,9 @@ struct Cfg {
     static constexpr int kAccBuffers = BQ <= 32 ? 4 : 2;
     static constexpr uint32_t kTmemColsRaw = kAccBuffers * BQ;
     static constexpr uint32_t kTmemCols = kTmemColsRaw < 32 ? 32 : kTmemColsRaw;
-    // Dense tiles (BQ = 256) use two epilogue warpgroups, each draining 128 of the 256 accumulator columns.
-    static constexpr int kEpilogueGroups = BQ > 128 ? 2 : 1;
-    static constexpr int kEpilogueThreads = 128 * kEpilogueGroups;
+    static constexpr int kEpilogueThreads = 128;
     static constexpr int kThreads = 64 + kEpilogueThreads;
-    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
-                                         (BQ > 128 ? BQ * 24 : 0) /*per-column epilogue constants*/;
+    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int THREADS>
@@ -137,7 +130,7 @@ __device__ __forceinline__ uint32_t EncodePair(int e4m3, float y0, float y1) {
     return packed;
 }
 
-template <bool INT8, bool P_MN, bool Q_MN, int BQ>
+template <bool INT8, bool P_MN, int BQ>
 __global__ void __launch_bounds__(Cfg<BQ>::kThreads, Cfg<BQ>::kCtasPerSm)
 LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, TcParams p,
                     Fp8Epilogue fe, Int8Epilogue ie) {
@@ -150,16 +143,12 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     uint64_t* tmem_full = empty + C::kStages;      // [kAcc]
     uint64_t* tmem_empty = tmem_full + kAcc;       // [kAcc]
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + kAcc);
-    // per-column epilogue constants of the current tile (normal mode only): [BQ] doubles, then [BQ] floats
-    double* col_scale = reinterpret_cast<double*>(reinterpret_cast<uint8_t*>(full) + 256);
-    double* col_multd = col_scale + BQ;
-    float* col_mult = reinterpret_cast<float*>(col_multd + BQ);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
-        for (int b = 0; b < kAcc; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], 4 * C::kEpilogueGroups); }
+        for (int b = 0; b < kAcc; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], 4); }
         FenceBarrierInit();
     }
     if (warp == 1) umma::TmemAlloc(tmem_base_slot, C::kTmemCols);
@@ -174,11 +163,9 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     // operands may be that kernel's output, so nothing is read before it has completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // unit → (p tile, q tile, K chunk).  Normal mode walks the activation tiles fastest so the CTAs running
-    // together share one weight column block through L2 and the weights stream from HBM once.
-    // Swapped mode with [K,N] weights walks the column tiles fastest (chunk-major): the CTAs running together
-    // then read whole contiguous weight rows of one K range, which keeps DRAM pages open; with [N,K] weights the
-    // chunks of one tile are the contiguous direction, so the chunk index varies fastest instead.
+    // unit → (p tile, q tile, K chunk).  [K,N] weights walk the column tiles fastest (chunk-major): the CTAs running
+    // together then read whole contiguous weight rows of one K range, which keeps DRAM pages open; with [N,K]
+    // weights the chunks of one tile are the contiguous direction, so the chunk index varies fastest instead.
     auto decode_unit = [&](int64_t u, int64_t* pt, int64_t* qt, int* s) {
         int64_t t;
         if (P_MN) {
@@ -189,8 +176,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             *s = static_cast<int>(u % p.split);
             t = u / p.split;
         }
-        if (p.swap) { *qt = t % p.q_tiles; *pt = t / p.q_tiles; }
-        else { *pt = t % p.p_tiles; *qt = t / p.p_tiles; }
+        *qt = t % p.q_tiles;
+        *pt = t / p.q_tiles;
     };
     auto blocks_of = [&](int s) -> int64_t {
         const int64_t begin = static_cast<int64_t>(s) * p.chunk_blocks;
@@ -220,12 +207,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     MbarExpectTx(&full[stage], C::kStageBytes);
                     if constexpr (P_MN) TmaLoad2D(ps, &map_p, p0, k0, &full[stage]);
                     else TmaLoad2D(ps, &map_p, k0, p0, &full[stage]);
-                    if constexpr (Q_MN) {
-#pragma unroll
-                        for (int j = 0; j < (BQ + 127) / 128; ++j) TmaLoad2D(qs + j * 16384, &map_q, q0 + j * 128, k0, &full[stage]);
-                    } else {
-                        TmaLoad2D(qs, &map_q, k0, q0, &full[stage]);
-                    }
+                    TmaLoad2D(qs, &map_q, k0, q0, &full[stage]);
                     if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -254,7 +236,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 #pragma unroll
                     for (int ks = 0; ks < kBlockK / 32; ++ks) {
                         const uint64_t a_desc = P_MN ? umma::SmemDesc(ps + ks * 4096, 16384, 1024) : umma::SmemDesc(ps + ks * 32, 16, 1024);
-                        const uint64_t b_desc = Q_MN ? umma::SmemDesc(qs + ks * 4096, 16384, 1024) : umma::SmemDesc(qs + ks * 32, 16, 1024);
+                        const uint64_t b_desc = umma::SmemDesc(qs + ks * 32, 16, 1024);
                         umma::Mma<INT8>(d_tmem, a_desc, b_desc, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
                     }
                     umma::Commit(&empty[stage]);  // the stage is free once these MMAs have read it
@@ -267,8 +249,6 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         // ================================ epilogue ================================
         const int et = threadIdx.x - 64;            // 0 .. kEpilogueThreads-1
         const int lane_group = warp & 3;            // TMEM lanes 32*lane_group .. +31 belong to this warp
-        const int col_group = (warp - 2) / 4;       // which 128-column half of a dense tile this warpgroup drains
-        constexpr int kColsPerGroup = BQ / C::kEpilogueGroups;
         const int row = lane_group * 32 + lane;     // row inside the P tile
         const double so_d = static_cast<double>(ie.out_scale);
         // One double divide per thread; scale * so_inv is within 2^-52 of scale / out_scale, which the error bounds of
@@ -279,7 +259,6 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         uint8_t* out8 = static_cast<uint8_t*>(INT8 ? ie.out : fe.out);
         bool failed = false;
         int64_t iter = 0;
-        int64_t staged_qt = -1;
 
         for (int64_t u = blockIdx.x; u < p.units; u += gridDim.x, ++iter) {
             int64_t pt, qt; int s;
@@ -292,37 +271,16 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const int64_t q_left = p.q_total - q_begin;
             const int q_count = static_cast<int>(q_left < BQ ? q_left : BQ);
 
-            // ---- scale constants: per lane (swapped: the lane is an output channel) or per column via smem ----
+            // ---- scale constants of this lane's output channel ----
             double row_scale_d = 0.0, row_mult_d = 0.0;
             float row_mult = 0.0f;
-            if (p.fast) {
-                if (p.swap) {
-                    if (row_ok) {
-                        if constexpr (INT8) {
-                            row_scale_d = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? pg : 0]);
-                            row_mult_d = row_scale_d * so_inv;
-                            row_mult = static_cast<float>(row_mult_d);
-                        } else {
-                            row_mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[pg] : fe.ab_scale;
-                        }
-                    }
-                } else if (qt != staged_qt) {  // uniform across the epilogue warps
-                    EpilogueBarrier<C::kEpilogueThreads>();  // readers of the previous tile's constants are done
-                    for (int c = et; c < BQ; c += C::kEpilogueThreads) {
-                        const int64_t n = q_begin + c;
-                        if (n < p.q_total) {
-                            if constexpr (INT8) {
-                                const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
-                                col_scale[c] = sd;
-                                col_multd[c] = sd * so_inv;
-                                col_mult[c] = static_cast<float>(sd * so_inv);
-                            } else {
-                                col_mult[c] = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
-                            }
-                        }
-                    }
-                    EpilogueBarrier<C::kEpilogueThreads>();
-                    staged_qt = qt;
+            if (p.fast && row_ok) {
+                if constexpr (INT8) {
+                    row_scale_d = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? pg : 0]);
+                    row_mult_d = row_scale_d * so_inv;
+                    row_mult = static_cast<float>(row_mult_d);
+                } else {
+                    row_mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[pg] : fe.ab_scale;
                 }
             }
 
@@ -332,8 +290,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     if (row_ok) {
                         for (int j = 0; j < cnt; ++j) {
                             const int64_t qg = q_begin + c0 + j;
-                            if (p.swap) StoreOne<INT8>(fe, ie, p.e4m3, qg, pg, v[j]);
-                            else StoreOne<INT8>(fe, ie, p.e4m3, pg, qg, v[j]);
+                            StoreOne<INT8>(fe, ie, p.e4m3, qg, pg, v[j]);
                         }
                     }
                     return;
@@ -343,54 +300,34 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         if (j >= cnt) break;  // uniform: a decode-sized M leaves most columns unused
-                        const float mult = p.swap ? row_mult : col_mult[c0 + j];
-                        const double sd = p.swap ? row_scale_d : col_scale[c0 + j];
-                        const double md = p.swap ? row_mult_d : col_multd[c0 + j];
-                        b[j] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[j]), mult, md, sd, so_d, ie.out_zp));
+                        b[j] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[j]), row_mult, row_mult_d, row_scale_d, so_d, ie.out_zp));
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j += 2) {
                         if (j >= cnt) break;  // uniform; unused columns would only feed the divider zeros (its slow path)
-                        const float m0 = p.swap ? row_mult : col_mult[c0 + j];
-                        const float m1 = p.swap ? row_mult : col_mult[c0 + j + 1];
-                        const float y0 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j]), m0), so_f);
-                        const float y1 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j + 1]), m1), so_f);
+                        const float y0 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j]), row_mult), so_f);
+                        const float y1 = __fdiv_rn(__fmul_rn(__uint_as_float(v[j + 1]), row_mult), so_f);
                         const uint32_t pair = EncodePair(p.e4m3, y0, y1);
                         b[j] = pair & 0xffu;
                         b[j + 1] = pair >> 8;
                     }
                 }
-                if (!p.swap) {
-                    if (!row_ok) return;
-                    uint8_t* dst = out8 + pg * ldo + q_begin + c0;
-                    if (cnt == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                        uint4 w;
-                        w.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-                        w.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
-                        w.z = b[8] | (b[9] << 8) | (b[10] << 16) | (b[11] << 24);
-                        w.w = b[12] | (b[13] << 8) | (b[14] << 16) | (b[15] << 24);
-                        *reinterpret_cast<uint4*>(dst) = w;
-                    } else {
-                        for (int j = 0; j < cnt; ++j) dst[j] = static_cast<uint8_t>(b[j]);
-                    }
-                } else {
-                    // lanes are consecutive output channels: four neighbouring lanes pack one 32-bit store
-                    const int64_t base_pg = pg - (lane & 3);
+                // lanes are consecutive output channels: four neighbouring lanes pack one 32-bit store
+                const int64_t base_pg = pg - (lane & 3);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (j >= cnt) break;  // uniform
-                        const uint32_t other1 = __shfl_xor_sync(0xffffffffu, b[j], 1);
-                        const uint32_t pair = (lane & 1) ? (other1 | (b[j] << 8)) : (b[j] | (other1 << 8));
-                        const uint32_t other2 = __shfl_xor_sync(0xffffffffu, pair, 2);
-                        const uint32_t word = (lane & 2) ? (other2 | (pair << 16)) : (pair | (other2 << 16));
-                        uint8_t* dst = out8 + (q_begin + c0 + j) * ldo + base_pg;
-                        const bool group_ok = base_pg + 3 < p.p_total && (reinterpret_cast<uintptr_t>(dst) & 3) == 0;
-                        if (group_ok) {
-                            if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = word;
-                        } else if (row_ok) {
-                            dst[lane & 3] = static_cast<uint8_t>(b[j]);
-                        }
+                for (int j = 0; j < 16; ++j) {
+                    if (j >= cnt) break;  // uniform
+                    const uint32_t other1 = __shfl_xor_sync(0xffffffffu, b[j], 1);
+                    const uint32_t pair = (lane & 1) ? (other1 | (b[j] << 8)) : (b[j] | (other1 << 8));
+                    const uint32_t other2 = __shfl_xor_sync(0xffffffffu, pair, 2);
+                    const uint32_t word = (lane & 2) ? (other2 | (pair << 16)) : (pair | (other2 << 16));
+                    uint8_t* dst = out8 + (q_begin + c0 + j) * ldo + base_pg;
+                    const bool group_ok = base_pg + 3 < p.p_total && (reinterpret_cast<uintptr_t>(dst) & 3) == 0;
+                    if (group_ok) {
+                        if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = word;
+                    } else if (row_ok) {
+                        dst[lane & 3] = static_cast<uint8_t>(b[j]);
                     }
                 }
             };
@@ -399,7 +336,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             umma::FenceAfterThreadSync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BQ);
 #pragma unroll 1
-            for (int c0 = col_group * kColsPerGroup; c0 < (col_group + 1) * kColsPerGroup; c0 += 16) {
+            for (int c0 = 0; c0 < BQ; c0 += 16) {
                 if (c0 >= q_count) break;  // uniform across the warp
                 uint32_t v[16];
                 umma::TmemLoad16(taddr + c0, v);
@@ -1185,10 +1122,10 @@ bool CachedMap(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows,
     return true;
 }
 
-template <bool INT8, bool P_MN, bool Q_MN, int BQ>
+template <bool INT8, bool P_MN, int BQ>
 int LaunchTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p, const Fp8Epilogue& fe,
                 const Int8Epilogue& ie, cudaStream_t stream) {
-    auto kernel = LinearTcgen05Kernel<INT8, P_MN, Q_MN, BQ>;
+    auto kernel = LinearTcgen05Kernel<INT8, P_MN, BQ>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg<BQ>::kSmemBytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
@@ -1214,14 +1151,10 @@ int LaunchTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcPara
 template <bool INT8>
 int LaunchForLayout(const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q,
                     const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
-    if (!g.swap) {
-        return weights_mn ? LaunchTyped<INT8, false, true, 256>(map_p, map_q, p, fe, ie, stream)
-                          : LaunchTyped<INT8, false, false, 256>(map_p, map_q, p, fe, ie, stream);
-    }
-#define FTH_SWAP_CASE(BQV)                                                                                   \
-    case BQV:                                                                                                \
-        return weights_mn ? LaunchTyped<INT8, true, false, BQV>(map_p, map_q, p, fe, ie, stream)             \
-                          : LaunchTyped<INT8, false, false, BQV>(map_p, map_q, p, fe, ie, stream);
+#define FTH_SWAP_CASE(BQV)                                                                            \
+    case BQV:                                                                                         \
+        return weights_mn ? LaunchTyped<INT8, true, BQV>(map_p, map_q, p, fe, ie, stream)             \
+                          : LaunchTyped<INT8, false, BQV>(map_p, map_q, p, fe, ie, stream);
     switch (g.bq) {
         FTH_SWAP_CASE(16) FTH_SWAP_CASE(32) FTH_SWAP_CASE(64) FTH_SWAP_CASE(128)
         default: return FTH_B200_ERR_INVALID;
@@ -1386,7 +1319,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
         return int8 ? LaunchCluster<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
                     : LaunchCluster<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
     }
-    if (!g.swap && getenv("FTH_B200_DENSE_SINGLE") == nullptr) {
+    if (!g.swap) {
         // CTA pairs: each CTA stages 128 activation rows and 128 weight columns of a 256 x 256 tile
         CUtensorMap map_w_half = map_w;
         if (!weights_mn && !CachedMap(&map_w_half, a.w, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), 128, 128)) return FTH_B200_ERR_CUDA;
