@@ -34,19 +34,6 @@ struct ConvTcParams {
     int* status;
 };
 
-__device__ __forceinline__ int8_t RequantFastConv(int32_t acc, float mult_f, double scale_d, double so_d, int32_t zp) {
-    // FP32 estimate with an exact double fallback near rounding boundaries; see RequantFast in
-    // linear_tcgen05.cu for the error bound (|estimate - exact| < 1e-4 for |t| <= 300).
-    const float est = fmaf(__int2float_rn(acc), mult_f, static_cast<float>(zp));
-    if (est >= 300.0f) return 127;
-    if (est <= -300.0f) return -128;
-    const float fl = floorf(est);
-    const float frac = est - fl;
-    if (fabsf(frac - 0.5f) < 2e-4f) return RequantExact(__dmul_rn(static_cast<double>(acc), scale_d), so_d, zp);
-    const float r = frac < 0.5f ? fl : fl + 1.0f;
-    return static_cast<int8_t>(static_cast<int32_t>(fmaxf(-128.0f, fminf(127.0f, r))));
-}
-
 // ---- pass 1: NCHW -> NHWC ----------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) NchwToNhwcKernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int64_t n, int64_t c,
                                                         int64_t h, int64_t w) {
@@ -92,7 +79,8 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     uint64_t* w_ready = tmem_empty + kAcc;
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(w_ready + 1);
     double* col_scale = reinterpret_cast<double*>(reinterpret_cast<uint8_t*>(full) + 256);  // [BQ]
-    float* col_mult = reinterpret_cast<float*>(col_scale + BQ);                            // [BQ]
+    double* col_multd = col_scale + BQ;                                                    // [BQ]
+    float* col_mult = reinterpret_cast<float*>(col_multd + BQ);                            // [BQ]
     int32_t* col_bias = reinterpret_cast<int32_t*>(col_mult + BQ);                         // [BQ]
     int8_t* lut = reinterpret_cast<int8_t*>(col_bias + BQ);                                // [256]
 
@@ -113,6 +101,7 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (o < c.oc) {
             const double sd = static_cast<double>(c.x_scale) * static_cast<double>(c.w_scales[c.per_channel ? o : 0]);
             col_scale[o] = sd;
+            col_multd[o] = sd / so_d;
             col_mult[o] = static_cast<float>(sd / so_d);
             col_bias[o] = c.bias ? c.bias[o] : 0;
         }
@@ -208,7 +197,7 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 for (int j = 0; j < 16; ++j) {
                     const int o = c0 + j;
                     if (o >= c.oc) break;  // uniform
-                    int8_t q = RequantFastConv(static_cast<int32_t>(v[j]) + col_bias[o], col_mult[o], col_scale[o], so_d, c.out_zp);
+                    int8_t q = RequantFast(static_cast<int32_t>(v[j]) + col_bias[o], col_mult[o], col_multd[o], col_scale[o], so_d, c.out_zp);
                     if (c.relu_lut != nullptr) q = lut[static_cast<uint8_t>(static_cast<uint8_t>(q) + 128)];
                     const uint32_t b = static_cast<uint8_t>(q);
                     const uint32_t other1 = __shfl_xor_sync(0xffffffffu, b, 1);
@@ -243,7 +232,7 @@ int BlockQFor(int64_t oc) { return oc <= 32 ? 32 : oc <= 64 ? 64 : oc <= 128 ? 1
 size_t Align256(size_t v) { return (v + 255) / 256 * 256; }
 
 size_t SmemBytesFor(int bq, int kblocks) {
-    return static_cast<size_t>((kblocks * bq * kRowBytes + 1023) / 1024 * 1024) + kStages * kABytes + 256 + bq * 16 + 256 + 1024;
+    return static_cast<size_t>((kblocks * bq * kRowBytes + 1023) / 1024 * 1024) + kStages * kABytes + 256 + bq * 24 + 256 + 1024;
 }
 
 template <int BQ>

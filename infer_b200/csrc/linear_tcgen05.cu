@@ -96,27 +96,6 @@ __device__ __forceinline__ void StoreOne(const Fp8Epilogue& fe, const Int8Epilog
     }
 }
 
-// INT8 requantisation in three stages, each deciding only what its error bound allows.
-//   1. est = fma(float(acc), float(scale / out_scale), zp) differs from the exact value T by at most
-//      (|T| + |zp|) * 4 * 2^-24 < 1e-4 for |T| <= 300 (three FP32 roundings), and the reference's double sequence
-//      differs from T by less than 1e-12.  Farther than 2e-4 from a rounding boundary x.5, both round alike.
-//      |est| >= 300 saturates either way.
-//   2. The ~4 values in 10^4 inside that band take one double FMA with mult_d = scale / out_scale to within a few
-//      2^-53 (RequantInt32: within 1e-12 of the reference's value, decided unless within 1e-6 of a boundary).
-//   3. What is left runs the reference's own sequence (double multiply, divide, add, round).
-// A warp takes a stage whenever one of its lanes needs it, and the double divide of stage 3 costs a thousand
-// cycles: with stage 2 in between it is practically never reached.
-__device__ __forceinline__ int8_t RequantFast(int32_t acc, float mult_f, double mult_d, double scale_d, double so_d, int32_t zp) {
-    const float est = fmaf(__int2float_rn(acc), mult_f, static_cast<float>(zp));
-    if (est >= 300.0f) return 127;
-    if (est <= -300.0f) return -128;
-    const float fl = floorf(est);
-    const float frac = est - fl;
-    if (fabsf(frac - 0.5f) < 2e-4f) return RequantInt32(acc, scale_d, mult_d, so_d, zp);
-    const float r = frac < 0.5f ? fl : fl + 1.0f;
-    return static_cast<int8_t>(static_cast<int32_t>(fmaxf(-128.0f, fminf(127.0f, r))));
-}
-
 // Encodes y0, y1 (already divided by the output scale) into two FP8 codes: low byte = y0, high byte = y1.
 __device__ __forceinline__ uint32_t EncodePair(int e4m3, float y0, float y1) {
     const bool special = ((__float_as_uint(y0) & 0x7f800000u) == 0x7f800000u) || ((__float_as_uint(y1) & 0x7f800000u) == 0x7f800000u);
