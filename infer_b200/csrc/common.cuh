@@ -177,6 +177,19 @@ __device__ __forceinline__ int8_t RequantFast(int32_t acc, float mult_f, double 
     return static_cast<int8_t>(static_cast<int32_t>(fmaxf(-128.0f, fminf(127.0f, r))));
 }
 
+// Stage 1 of RequantFast without a branch, for epilogues that requantise many accumulators per thread: straight-line
+// code lets the independent chains overlap.  Returns the stage-1 result as an unsigned byte and sets bit `bit` of
+// `near` when the estimate lies inside the undecided band; those few values are redone with RequantInt32
+// afterwards.  Saturation falls out of the clamp (an estimate beyond +-300 is never inside the band).
+__device__ __forceinline__ uint32_t RequantEstimate(int32_t acc, float mult_f, float zp_f, uint32_t bit, uint32_t* near) {
+    const float est = fmaf(__int2float_rn(acc), mult_f, zp_f);
+    const float fl = floorf(est);
+    const float frac = est - fl;
+    *near |= (fabsf(frac - 0.5f) < 2e-4f && fabsf(est) < 300.0f) ? (1u << bit) : 0u;
+    const float r = frac < 0.5f ? fl : fl + 1.0f;
+    return static_cast<uint32_t>(static_cast<int32_t>(fmaxf(-128.0f, fminf(127.0f, r)))) & 0xffu;
+}
+
 // QuantizeLinear on one value (include/quant/quantization.h:94-99).
 __device__ __forceinline__ int8_t QuantizeValue(float value, float scale, int32_t zp) {
     const double t = __dadd_rn(__ddiv_rn(static_cast<double>(value), static_cast<double>(scale)),

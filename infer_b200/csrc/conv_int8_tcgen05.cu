@@ -16,6 +16,17 @@
 #include "tcgen05.cuh"
 #include "tma.cuh"
 
+// Optional phase timeline of CTA 0 in SM clocks (development aid, compiled out unless FTH_B200_TRACE is defined).
+#ifdef FTH_B200_TRACE
+__device__ unsigned long long g_conv_trace[32];
+#define FTH_CTRACE(i) do { if (blockIdx.x == 0) g_conv_trace[i] = static_cast<unsigned long long>(clock64()); } while (0)
+extern "C" int fth_b200_conv_trace_read(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, g_conv_trace, sizeof(g_conv_trace)) == cudaSuccess ? 0 : -1;
+}
+#else
+#define FTH_CTRACE(i) do {} while (0)
+#endif
+
 namespace fth {
 namespace {
 
@@ -23,7 +34,10 @@ constexpr int kTileW = 32, kTileH = 4;          // 128 output pixels per tile
 constexpr int kRowBytes = 64;                   // one K block: 64 input channels of one tap
 constexpr int kABytes = kTileW * kTileH * kRowBytes;  // 8 KB per ring stage
 constexpr int kStages = 8;
-constexpr int kThreads = 192;
+// 16 epilogue warps: the requantisation is scalar code with long dependent chains, and one warp per scheduler ran it
+// at ~0.2 instructions per clock.  Four warps share each 32-lane slice of tensor memory and split its channels.
+constexpr int kEpilogueWarps = 16;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kAcc = 2;
 
 struct ConvTcParams {
@@ -50,6 +64,40 @@ __global__ void __launch_bounds__(256) NchwToNhwcKernel(const int8_t* __restrict
     for (int idx = threadIdx.x; idx < 64 * 32; idx += 256) {
         const int ww = idx / 64, cc = idx % 64;
         if (c0 + cc < c && w0 + ww < w) y[((img * h + row) * w + w0 + ww) * c + c0 + cc] = tile[cc][ww];
+    }
+}
+
+// Same pass for the common aligned case (w % 4 == 0, c % 16 == 0, 4-byte aligned x, 16-byte aligned y): one block
+// per image row and 64-channel block; 32-bit loads along w, a byte tile in shared memory, and 16-byte stores of 16
+// channels of one pixel — the row's pixels x 64 channels are one contiguous run of the NHWC copy.
+constexpr int kRowTileW = 256;  // widest row handled by the fast pass
+__global__ void __launch_bounds__(256) NchwToNhwcRowKernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int64_t c, int64_t h,
+                                                           int64_t w) {
+    // lets the conv kernel behind it set up and fetch its weights while this pass runs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ __align__(16) uint8_t tile[64][kRowTileW + 4];
+    const int64_t c0 = static_cast<int64_t>(blockIdx.y) * 64;
+    const int64_t nh = blockIdx.x;  // n * h + row
+    const int64_t img = nh / h, row = nh % h;
+    const int words = static_cast<int>(w / 4);
+    const int channels = static_cast<int>(c - c0 < 64 ? c - c0 : 64);
+    for (int idx = threadIdx.x; idx < channels * words; idx += 256) {
+        const int cc = idx / words, w4 = idx - cc * words;
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(x + ((img * c + c0 + cc) * h + row) * w + w4 * 4);
+        *reinterpret_cast<uint32_t*>(&tile[cc][w4 * 4]) = v;
+    }
+    __syncthreads();
+    const int groups = channels / 16;
+    for (int idx = threadIdx.x; idx < static_cast<int>(w) * groups; idx += 256) {
+        const int px = idx / groups, g = idx - px * groups;
+        uint32_t out[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int cc = g * 16 + q * 4;
+            out[q] = tile[cc][px] | (static_cast<uint32_t>(tile[cc + 1][px]) << 8) | (static_cast<uint32_t>(tile[cc + 2][px]) << 16) |
+                     (static_cast<uint32_t>(tile[cc + 3][px]) << 24);
+        }
+        *reinterpret_cast<uint4*>(y + ((img * h + row) * w + px) * c + c0 + g * 16) = make_uint4(out[0], out[1], out[2], out[3]);
     }
 }
 
@@ -86,15 +134,25 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
     const ConvArgs& c = p.c;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (threadIdx.x == 0) FTH_CTRACE(0);
     constexpr uint32_t kTmemCols = kAcc * BQ < 32 ? 32 : kAcc * BQ;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
-        for (int b = 0; b < kAcc; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], 4); }
+        for (int b = 0; b < kAcc; ++b) { MbarInit(&tmem_full[b], 1); MbarInit(&tmem_empty[b], kEpilogueWarps); }
         MbarInit(w_ready, 1);
         FenceBarrierInit();
+        TmaPrefetchDescriptor(&map_x);
+        TmaPrefetchDescriptor(&map_w);
+        // Weights packed by an earlier call are not written by anything still running: fetch them (the whole
+        // repacked weight, once) before waiting for the layout pass in front of this kernel.
+        if (c.weights_packed) {
+            MbarExpectTx(w_ready, static_cast<uint32_t>(p.kblocks * w_block));
+            for (int kb = 0; kb < p.kblocks; ++kb) TmaLoad2D(w_smem + kb * w_block, &map_w, kb * kRowBytes, 0, w_ready);
+        }
     }
     if (warp == 1) umma::TmemAlloc(tmem_base_slot, kTmemCols);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // per-output-channel constants and the optional ReLU table, once per CTA
     const double so_d = static_cast<double>(c.out_scale);
     for (int o = threadIdx.x; o < BQ; o += kThreads) {
@@ -112,6 +170,7 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     __syncthreads();
     umma::FenceAfterThreadSync();
     const uint32_t tmem_base = *tmem_base_slot;
+    if (threadIdx.x == 0) FTH_CTRACE(1);
 
     auto decode_tile = [&](int64_t t, int64_t* n, int64_t* oh0, int64_t* ow0) {
         *ow0 = (t % p.tiles_w) * kTileW;
@@ -121,27 +180,47 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     };
 
     if (warp == 0) {
+        // One thread takes ~350 clocks per TMA it issues (expect + copy), which for a CTA with one or two tiles is most
+        // of the time to the first MMA.  So the first pass over the ring — every stage is free — is issued by as many
+        // lanes as there are stages, one k-block each, at once; lane 0 carries on alone from there.
+        const int first = p.kblocks < kStages ? p.kblocks : kStages;
+        if (blockIdx.x < p.tiles && lane < first) {
+            int64_t n, oh0, ow0;
+            decode_tile(blockIdx.x, &n, &oh0, &ow0);
+            const int tap = lane / p.cblocks, cb = lane - tap * p.cblocks;
+            const int ky = tap / static_cast<int>(c.kw), kx = tap - ky * static_cast<int>(c.kw);
+            MbarExpectTx(&full[lane], kABytes);
+            TmaLoad4D(ring + lane * kABytes, &map_x, cb * kRowBytes, static_cast<int32_t>(ow0 - c.pad_w) + kx,
+                      static_cast<int32_t>(oh0 - c.pad_h) + ky, static_cast<int32_t>(n), &full[lane]);
+        }
+        __syncwarp();
         if (lane == 0) {
-            TmaPrefetchDescriptor(&map_x);
-            TmaPrefetchDescriptor(&map_w);
-            // the whole repacked weight, once
-            MbarExpectTx(w_ready, static_cast<uint32_t>(p.kblocks * w_block));
-            for (int kb = 0; kb < p.kblocks; ++kb) TmaLoad2D(w_smem + kb * w_block, &map_w, kb * kRowBytes, 0, w_ready);
+            if (!c.weights_packed) {  // packed by the kernel in front of this one: only now safe to read
+                MbarExpectTx(w_ready, static_cast<uint32_t>(p.kblocks * w_block));
+                for (int kb = 0; kb < p.kblocks; ++kb) TmaLoad2D(w_smem + kb * w_block, &map_w, kb * kRowBytes, 0, w_ready);
+            }
+            FTH_CTRACE(2);
+            int issued = 0;
             int stage = 0;
             uint32_t phase = 0;
             bool failed = false;
             for (int64_t t = blockIdx.x; t < p.tiles && !failed; t += gridDim.x) {
                 int64_t n, oh0, ow0;
                 decode_tile(t, &n, &oh0, &ow0);
+                const int32_t x0 = static_cast<int32_t>(ow0 - c.pad_w), y0 = static_cast<int32_t>(oh0 - c.pad_h);
+                int ky = 0, kx = 0, cb = 0;  // k-block order: tap-major (ky, kx), then the 64-channel block
                 for (int kb = 0; kb < p.kblocks; ++kb) {
-                    const int tap = kb / p.cblocks, cb = kb % p.cblocks;
-                    const int ky = tap / static_cast<int>(c.kw), kx = tap % static_cast<int>(c.kw);
-                    if (!MbarWait(&empty[stage], phase ^ 1u, p.status, 20, stage)) { failed = true; break; }
-                    MbarExpectTx(&full[stage], kABytes);
-                    TmaLoad4D(ring + stage * kABytes, &map_x, cb * kRowBytes, static_cast<int32_t>(ow0 + kx - c.pad_w),
-                              static_cast<int32_t>(oh0 + ky - c.pad_h), static_cast<int32_t>(n), &full[stage]);
+                    if (issued >= first) {
+                        // (stages of the first pass beyond `first` are free as well)
+                        if (issued >= kStages && !MbarWait(&empty[stage], phase ^ 1u, p.status, 20, stage)) { failed = true; break; }
+                        MbarExpectTx(&full[stage], kABytes);
+                        TmaLoad4D(ring + stage * kABytes, &map_x, cb * kRowBytes, x0 + kx, y0 + ky, static_cast<int32_t>(n), &full[stage]);
+                    }
+                    ++issued;
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (++cb == p.cblocks) { cb = 0; if (++kx == static_cast<int>(c.kw)) { kx = 0; ++ky; } }
                 }
+                if (t == blockIdx.x) FTH_CTRACE(3);
             }
         }
     } else if (warp == 1) {
@@ -149,6 +228,7 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             bool failed = !MbarWait(w_ready, 0, p.status, 21, 0);
+            FTH_CTRACE(4);
             int64_t iter = 0;
             for (int64_t t = blockIdx.x; t < p.tiles && !failed; t += gridDim.x, ++iter) {
                 const int acc = static_cast<int>(iter % kAcc);
@@ -169,11 +249,13 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     umma::Commit(&empty[stage]);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
+                if (iter == 0) FTH_CTRACE(5);
                 if (!failed) umma::Commit(&tmem_full[acc]);
             }
         }
     } else {
-        const int lane_group = warp & 3;  // = row of the 32 x 4 pixel tile
+        const int lane_group = warp & 3;      // = row of the 32 x 4 pixel tile
+        const int slice = (warp - 2) / 4;     // which 16-channel groups this warp requantises: slice, slice + 4, ...
         bool failed = false;
         int64_t iter = 0;
         for (int64_t t = blockIdx.x; t < p.tiles; t += gridDim.x, ++iter) {
@@ -186,36 +268,69 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             const int64_t ow_base = ow - (lane & 3);
             if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 24, acc)) failed = true;
             umma::FenceAfterThreadSync();
+            if (threadIdx.x == 64 + 64) FTH_CTRACE(6 + 2 * static_cast<int>(iter));
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BQ);
+            // Output is NCHW: for one channel the tile's 32 pixels of a row are contiguous.  Each thread requantises 16
+            // channels of its pixel (independent chains, no branches between them), then every quad of lanes
+            // transposes 4 channels x 4 pixels in registers (two shuffles + two byte permutes per 4 channels) so that
+            // each lane stores one 32-bit word: 4 pixels of channel o + (lane & 3).
+            const int quad = lane & 3;
+            int8_t* out_px = c.out + ((n * c.oc) * c.oh + oh) * c.ow + ow_base;  // channel 0, this quad's first pixel
+            const int64_t plane = c.oh * c.ow;
+            const bool row_in = oh < c.oh;
+            const bool quad_whole = row_in && ow_base + 3 < c.ow && ((reinterpret_cast<uintptr_t>(out_px) | static_cast<uintptr_t>(plane)) & 3) == 0;
+            const bool use_lut = c.relu_lut != nullptr;
+            const float zp_f = static_cast<float>(c.out_zp);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BQ; c0 += 16) {
+            for (int c0 = slice * 16; c0 < BQ; c0 += 16 * (kEpilogueWarps / 4)) {
                 if (c0 >= c.oc) break;
                 uint32_t v[16];
                 umma::TmemLoad16(taddr + c0, v);
                 umma::TmemLoadWait();
+                uint32_t q[16];
+                uint32_t near = 0;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const int o = c0 + j;
-                    if (o >= c.oc) break;  // uniform
-                    int8_t q = RequantFast(static_cast<int32_t>(v[j]) + col_bias[o], col_mult[o], col_multd[o], col_scale[o], so_d, c.out_zp);
-                    if (c.relu_lut != nullptr) q = lut[static_cast<uint8_t>(static_cast<uint8_t>(q) + 128)];
-                    const uint32_t b = static_cast<uint8_t>(q);
-                    const uint32_t other1 = __shfl_xor_sync(0xffffffffu, b, 1);
-                    const uint32_t pair = (lane & 1) ? (other1 | (b << 8)) : (b | (other1 << 8));
-                    const uint32_t other2 = __shfl_xor_sync(0xffffffffu, pair, 2);
-                    const uint32_t word = (lane & 2) ? (other2 | (pair << 16)) : (pair | (other2 << 16));
-                    int8_t* dst = c.out + ((n * c.oc + o) * c.oh + oh) * c.ow + ow_base;
-                    const bool group_ok = oh < c.oh && ow_base + 3 < c.ow && (reinterpret_cast<uintptr_t>(dst) & 3) == 0;
-                    if (group_ok) {
-                        if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = word;
-                    } else if (pix_ok) {
-                        dst[lane & 3] = q;
+                    const int o = c0 + j < c.oc ? c0 + j : static_cast<int>(c.oc) - 1;  // clamp: no branch in the chain
+                    q[j] = RequantEstimate(static_cast<int32_t>(v[j]) + col_bias[o], col_mult[o], zp_f, j, &near);
+                }
+                while (near != 0) {  // a few values in 10^4: decided in double
+                    const int j = __ffs(near) - 1;
+                    near &= near - 1;
+                    const int o = c0 + j < c.oc ? c0 + j : static_cast<int>(c.oc) - 1;
+                    int32_t vj = 0;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) vj = i == j ? static_cast<int32_t>(v[i]) : vj;  // keeps v[] in registers
+                    const uint32_t exact = static_cast<uint8_t>(RequantInt32(vj + col_bias[o], col_scale[o], col_multd[o], so_d, c.out_zp));
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) q[i] = i == j ? exact : q[i];
+                }
+                if (use_lut) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) q[j] = static_cast<uint8_t>(lut[static_cast<uint8_t>(q[j] + 128)]);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int o = c0 + 4 * g + quad;  // the channel this lane stores
+                    // (the shuffles run in every lane: quads at the ragged edge differ only in how they store)
+                    const uint32_t w = q[4 * g] | (q[4 * g + 1] << 8) | (q[4 * g + 2] << 16) | (q[4 * g + 3] << 24);
+                    const uint32_t x = __shfl_xor_sync(0xffffffffu, w, 2);
+                    const uint32_t r = (lane & 2) ? __byte_perm(x, w, 0x7632) : __byte_perm(w, x, 0x5410);
+                    const uint32_t y = __shfl_xor_sync(0xffffffffu, r, 1);
+                    const uint32_t t = (lane & 1) ? __byte_perm(y, r, 0x7351) : __byte_perm(r, y, 0x6240);
+                    if (quad_whole) {
+                        if (o < c.oc) *reinterpret_cast<uint32_t*>(out_px + o * plane) = t;
+                    } else if (pix_ok) {  // ragged edge or unaligned rows: this thread's own bytes
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (c0 + 4 * g + i < c.oc) out_px[(c0 + 4 * g + i) * plane + quad] = static_cast<int8_t>(q[4 * g + i]);
                     }
                 }
             }
             umma::FenceBeforeThreadSync();
             __syncwarp();
             if (lane == 0) MbarArrive(&tmem_empty[acc]);
+            if (threadIdx.x == 64 + 64) FTH_CTRACE(7 + 2 * static_cast<int>(iter));
         }
     }
 
@@ -247,7 +362,17 @@ int LaunchTyped(const CUtensorMap& map_x, const CUtensorMap& map_w, const ConvTc
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     const int grid = static_cast<int>(p.tiles < sms ? p.tiles : sms);
-    kernel<<<grid, kThreads, smem, stream>>>(map_x, map_w, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // set-up overlaps the layout pass in front
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, map_x, map_w, p) != cudaSuccess) return FTH_B200_ERR_CUDA;
     NoteLaunch("conv_tcgen05");
     return CheckLaunch();
 }
@@ -283,8 +408,15 @@ int LaunchConvTcgen05(const ConvArgs& c, cudaStream_t stream) {
         NoteLaunch("conv_tcgen05");
     }
     {
-        const dim3 grid(static_cast<unsigned>((c.iw + 31) / 32), static_cast<unsigned>((c.ic + 63) / 64), static_cast<unsigned>(c.batch * c.ih));
-        NchwToNhwcKernel<<<grid, 256, 0, stream>>>(c.x, nhwc, c.batch, c.ic, c.ih, c.iw);
+        const bool aligned = c.iw % 4 == 0 && c.iw <= kRowTileW && c.ic % 16 == 0 && reinterpret_cast<uintptr_t>(c.x) % 4 == 0 &&
+                             c.batch * c.ih <= 0x7fffffff;
+        if (aligned) {
+            const dim3 grid(static_cast<unsigned>(c.batch * c.ih), static_cast<unsigned>((c.ic + 63) / 64));
+            NchwToNhwcRowKernel<<<grid, 256, 0, stream>>>(c.x, nhwc, c.ic, c.ih, c.iw);
+        } else {
+            const dim3 grid(static_cast<unsigned>((c.iw + 31) / 32), static_cast<unsigned>((c.ic + 63) / 64), static_cast<unsigned>(c.batch * c.ih));
+            NchwToNhwcKernel<<<grid, 256, 0, stream>>>(c.x, nhwc, c.batch, c.ic, c.ih, c.iw);
+        }
         NoteLaunch("conv_tcgen05");
     }
     ConvTcParams p;
