@@ -473,7 +473,8 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         const int col_group = (warp - 2) / 4;       // which 128-column half this warpgroup drains
         const int row = lane_group * 32 + lane;
         const double so_d = static_cast<double>(ie.out_scale);
-        const double so_inv = INT8 ? 1.0 / so_d : 0.0;  // see the single-CTA kernel
+        const double so_inv = INT8 ? 1.0 / so_d : 0.0;  // one divide per thread; see RequantFast for the error budget
+        const float zp_f = static_cast<float>(ie.out_zp);
         const float so_f = fe.out_scale;
         const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
         uint8_t* out8 = static_cast<uint8_t*>(INT8 ? ie.out : fe.out);
@@ -524,9 +525,19 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                 }
                 uint32_t b[16];
                 if constexpr (INT8) {
+                    uint32_t near = 0;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        b[j] = static_cast<uint8_t>(RequantFast(static_cast<int32_t>(v[j]), col_mult[c0 + j], col_multd[c0 + j], col_scale[c0 + j], so_d, ie.out_zp));
+                    for (int j = 0; j < 16; ++j) b[j] = RequantEstimate(static_cast<int32_t>(v[j]), col_mult[c0 + j], zp_f, j, &near);
+                    while (near != 0) {  // a few values in 10^4: decided in double
+                        const int j = __ffs(near) - 1;
+                        near &= near - 1;
+                        int32_t vj = 0;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) vj = i == j ? static_cast<int32_t>(v[i]) : vj;  // keeps v[] in registers
+                        const uint32_t exact = static_cast<uint8_t>(RequantInt32(vj, col_scale[c0 + j], col_multd[c0 + j], so_d, ie.out_zp));
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) b[i] = i == j ? exact : b[i];
+                    }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j += 2) {
