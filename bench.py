@@ -223,7 +223,6 @@ def run_gpu_arm(args):
         del w_full
     a_dev, sa = synth(torch, (1, K), 1.0, SEED + 1, dev)
     local_out = torch.zeros((1, width), dtype=torch.uint8, device=dev)
-    gathered = torch.zeros((world, 1, width), dtype=torch.uint8, device=dev) if world > 1 else None
 
     def make_desc(m, w, sw, a, out, ldo=0):
         d = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=K, n=w.shape[1], a=a, w=w, out=out, a_scale=sa,
@@ -234,14 +233,23 @@ def run_gpu_arm(args):
     descs = [make_desc(1, weights[i], w_scales[i], a_dev, local_out, ldo=width) for i in range(2)]
     counter = [0]
 
+    # N > 1: every rank's kernel stores its columns into all ranks' output buffers (peer-mapped) and a signal / wait
+    # kernel ends the step; no collective library on the data path.
+    gather = None
+    if world > 1:
+        from infer_b200.sharded import PeerGather, ShardedLinear, forward_peer
+        gather = PeerGather(B.lib(), dist, world, rank, 1, N)
+        shard = ShardedLinear(N, world, rank, compute=None, dist=dist)
+
     def step():
         d, _ = descs[counter[0] & 1]
         counter[0] += 1
+        if world > 1:
+            forward_peer(shard, gather, d, lambda desc, s: fp8_call(C.byref(desc), s), stream)
+            return
         rc = fp8_call(C.byref(d), stream)
         if rc != 0:
             raise RuntimeError(f"fth_b200_fp8_linear failed: {rc}")
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(world, width), local_out)
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -274,12 +282,22 @@ def run_gpu_arm(args):
         del w_host
     pc = [0]
 
+    a_stage = torch.empty((1, K), dtype=torch.uint8, device=dev)
+    full_host = torch.empty((1, N), dtype=torch.uint8).pin_memory()
+    e2e_descs = [make_desc(1, weights[i], w_scales[i], a_stage, local_out, ldo=width) for i in range(2)] if world > 1 else []
+
     def e2e_step():
-        plans[pc[0] & 1].run(a_host, out_host, stream)
+        if world == 1:
+            plans[pc[0] & 1].run(a_host, out_host, stream)
+            pc[0] += 1
+            return
+        # N > 1: pinned-host activation in, sharded kernels with peer stores, the gathered row back to the host
+        a_stage.copy_(a_host, non_blocking=True)
+        d, _ = e2e_descs[pc[0] & 1]
         pc[0] += 1
-        if world > 1:
-            local_out.copy_(out_host, non_blocking=True)
-            dist.all_gather_into_tensor(gathered.view(world, width), local_out)
+        parity = forward_peer(shard, gather, d, lambda desc, s: fp8_call(C.byref(desc), s), stream)
+        full_host.copy_(gather.view(torch, parity), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
 
     e2e_steps = min(args.steps, 500)
     e2e_ms = event_time_ms(torch, e2e_step, e2e_steps, max(args.warmup, 3), barrier) / e2e_steps
@@ -306,14 +324,16 @@ def run_gpu_arm(args):
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"C5 FP8-E4M3 Linear M=1 K={K} N={N}" + (f", N column-sharded over {world} GPUs + NCCL all-gather" if world > 1 else ""),
+            "config": {"workload": f"C5 FP8-E4M3 Linear M=1 K={K} N={N}" + (f", N column-sharded over {world} GPUs, outputs stored to all ranks over NVLink (peer stores + flag wait)" if world > 1 else ""),
                        "l2": "inputs larger than L2: two 235 MB weight sets rotated", "kernel": variant,
                        "algorithmic_bytes_per_step": bytes_step, "seed": SEED},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
                          "peak_source": peaks["source"], "note": "per GPU; step = tcgen05 GEMV + split-K reduce kernel"},
-            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": K, "d2h_bytes_per_step": width,
-                    "ms_per_step": round(e2e_ms, 5), "api": "fth_b200_plan_run (pinned host activation in, host result out)"},
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": K, "d2h_bytes_per_step": width if world == 1 else N,
+                    "ms_per_step": round(e2e_ms, 5),
+                    "api": "fth_b200_plan_run (pinned host activation in, host result out)" if world == 1 else
+                           "pinned host activation in, fth_b200_fp8_linear with peer stores + fth_b200_gather_sync, gathered row out"},
             "gpu_launches": int(launches),
             "clocks": sampler.summary(),
             "cpu_baseline": cpu_baseline,
@@ -322,6 +342,8 @@ def run_gpu_arm(args):
         print(json.dumps(line))
     if dist:
         dist.barrier()
+        if gather is not None:
+            gather.close()
         dist.destroy_process_group()
     return 0
 

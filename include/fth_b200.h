@@ -116,6 +116,13 @@ typedef struct {
     /* 1: nothing queued earlier on the stream writes `w` (an initializer, as FC / MatMul weights are in a compiled
      * plan), so the kernel may fetch weights while the previous kernel is still finishing.  0: no assumption. */
     int32_t weights_static;
+    /* Column-sharded projections on several GPUs of one box: `gather_peers` other ranks hold a buffer shaped like this
+     * rank's output buffer; gather_out[r] is the peer-mapped address in rank r's buffer that corresponds to `out`.
+     * Every output element is stored there as well (by the linear kernel's own epilogue for decode-sized M, by a
+     * block copy behind it otherwise).  Follow the call with fth_b200_gather_sync.  No counterpart in the reference
+     * (one CudaExecutionContext = one device, src/kernel/cuda/runtime.cu:318-321). */
+    int32_t gather_peers;   /* 0 .. 7 */
+    void* gather_out[7];
 } fth_b200_fp8_linear_desc;
 
 int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t stream);
@@ -182,6 +189,8 @@ typedef struct {
     size_t workspace_bytes;
     int32_t variant;
     int32_t weights_static; /* as in fth_b200_fp8_linear_desc */
+    int32_t gather_peers;   /* as in fth_b200_fp8_linear_desc */
+    void* gather_out[7];
 } fth_b200_int8_linear_desc;
 
 int fth_b200_int8_linear(const fth_b200_int8_linear_desc* desc, fth_b200_stream_t stream);
@@ -266,6 +275,20 @@ int fth_b200_plan_launch(fth_b200_plan* plan, const void* device_in, void* devic
 int64_t fth_b200_plan_input_bytes(const fth_b200_plan* plan);
 int64_t fth_b200_plan_output_bytes(const fth_b200_plan* plan);
 void fth_b200_plan_destroy(fth_b200_plan* plan);
+
+/* ---- multi-GPU gather without a collective library (no counterpart in the reference) -------------------------
+ * fth_b200_peer_buffer_create allocates zeroed device memory and returns a 64-byte handle another process of the same
+ * box turns into a peer-mapped pointer with fth_b200_peer_buffer_open (CUDA IPC).  fth_b200_gather_sync ends a
+ * gather step: on `stream`, after this rank's earlier work, it writes `epoch` into slot [rank] of every rank's flag
+ * array (rank_flags[r]: uint32[world], peer-mapped; rank_flags[rank] is this rank's own) and waits, for at most one
+ * second, until every slot of its own array has reached `epoch`; a time-out is reported through
+ * fth_b200_device_status.  Epochs grow by one per step; flags are never reset. */
+#define FTH_B200_PEER_HANDLE_BYTES 64
+int fth_b200_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle);
+int fth_b200_peer_buffer_open(const unsigned char* handle, void** ptr);
+int fth_b200_peer_buffer_close(void* ptr);
+int fth_b200_peer_buffer_destroy(void* ptr);
+int fth_b200_gather_sync(void* const* rank_flags, int32_t world, int32_t rank, uint32_t epoch, fth_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -31,6 +31,8 @@ EXPORTS = [
     "fth_b200_plan_create_fp8_linear", "fth_b200_plan_create_int8_linear", "fth_b200_plan_create_int8_conv2d",
     "fth_b200_plan_run", "fth_b200_plan_launch", "fth_b200_plan_input_bytes", "fth_b200_plan_output_bytes",
     "fth_b200_plan_destroy",
+    "fth_b200_peer_buffer_create", "fth_b200_peer_buffer_open", "fth_b200_peer_buffer_close", "fth_b200_peer_buffer_destroy",
+    "fth_b200_gather_sync",
 ]
 
 
@@ -42,6 +44,7 @@ class Fp8LinearDesc(C.Structure):
         ("a_scale", C.c_float), ("w_scale", C.c_float), ("bias_scale", C.c_float), ("out_scale", C.c_float),
         ("w_channel_scales", C.c_void_p), ("alpha", C.c_float), ("beta", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32), ("weights_static", C.c_int32),
+        ("gather_peers", C.c_int32), ("gather_out", C.c_void_p * 7),
     ]
 
 
@@ -54,6 +57,7 @@ class Int8LinearDesc(C.Structure):
         ("w_params", C.c_int64), ("w_zp_max_abs", C.c_int32), ("out_scale", C.c_float), ("out_zp", C.c_int32),
         ("alpha", C.c_float), ("beta", C.c_float), ("bias_max_abs", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32), ("weights_static", C.c_int32),
+        ("gather_peers", C.c_int32), ("gather_out", C.c_void_p * 7),
     ]
 
 

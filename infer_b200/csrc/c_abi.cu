@@ -114,12 +114,39 @@ int Dispatch(int variant, int dtype, const LinearArgs& args, const Fp8Epilogue& 
     }
 }
 
+// Peer replicas of the output: byte distance from the local output to each peer's copy.
+template <typename Desc>
+int BuildPeers(const Desc* d, PeerOut* peers) {
+    peers->count = 0;
+    if (d->gather_peers < 0 || d->gather_peers > kMaxPeers) return FTH_B200_ERR_INVALID;
+    for (int r = 0; r < d->gather_peers; ++r) {
+        if (d->gather_out[r] == nullptr) return FTH_B200_ERR_INVALID;
+        peers->delta[r] = static_cast<int64_t>(reinterpret_cast<intptr_t>(d->gather_out[r]) - reinterpret_cast<intptr_t>(d->out));
+    }
+    peers->count = d->gather_peers;
+    return FTH_B200_OK;
+}
+
+// Runs the chosen kernel family; when the output has peer replicas and that kernel does not write them itself, a
+// block copy follows on the same stream.
+int Run(int variant, int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* workspace,
+        size_t workspace_bytes, cudaStream_t stream) {
+    const int rc = Dispatch(variant, dtype, args, fe, ie, workspace, workspace_bytes, stream);
+    if (rc != FTH_B200_OK || args.peers.count == 0) return rc;
+    if (variant == FTH_B200_VARIANT_TCGEN05 && Tcgen05StoresToPeers(dtype, args, fe, ie)) return rc;
+    const bool int8 = dtype == FTH_B200_INT8;
+    const int out_dtype = int8 ? ie.out_dtype : fe.out_dtype;
+    const int elem = out_dtype == FTH_B200_FP32 ? 4 : (out_dtype == FTH_B200_BF16 || out_dtype == FTH_B200_FP16) ? 2 : 1;
+    return LaunchPeerCopy(int8 ? ie.out : fe.out, args.m, args.n, int8 ? ie.ldo : fe.ldo, elem, args.peers, stream);
+}
+
 void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* fe) {
     args->a = d->a; args->w = d->w; args->m = d->m; args->k = d->k; args->n = d->n; args->trans_b = d->trans_b;
     args->a_dtype = (d->a_dtype == d->dtype) ? 0 : d->a_dtype;
     args->a_scale = d->a_scale;
     args->zero_points = 0;
     args->w_static = d->weights_static != 0;
+    args->peers.count = 0;
     fe->ab_scale = d->w_channel_scales ? d->a_scale : d->a_scale * d->w_scale;
     fe->w_channel_scales = d->w_channel_scales;
     fe->is_gemm = d->op == FTH_B200_OP_GEMM;
@@ -141,6 +168,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
     args->a_scale = d->a_scale;
     args->zero_points = (d->a_zp != 0 || d->w_zps != nullptr) ? 1 : 0;
     args->w_static = d->weights_static != 0;
+    args->peers.count = 0;
     ie->w_scales = d->w_scales; ie->w_zps = d->w_zps; ie->per_channel = d->w_params != 1;
     ie->a_scale = d->a_scale; ie->a_zp = d->a_zp; ie->out_scale = d->out_scale; ie->out_zp = d->out_zp;
     ie->bias = d->bias; ie->bias_mode = d->bias_mode;
@@ -158,7 +186,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
 
 using namespace fth;
 
-extern "C" int fth_b200_abi_version(void) { return 2; }
+extern "C" int fth_b200_abi_version(void) { return 3; }
 extern "C" const char* fth_b200_last_variant(void) { return g_last_variant; }
 extern "C" int64_t fth_b200_launch_count(void) { return g_launches; }
 extern "C" void fth_b200_reset_launch_count(void) { g_launches = 0; }
@@ -186,8 +214,9 @@ extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_s
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Fp8Epilogue fe; Int8Epilogue ie = {};
     BuildFp8(d, &args, &fe);
-    return Dispatch(PickVariant(d->variant, d->dtype, args, d->workspace, d->workspace_bytes), d->dtype, args, fe, ie,
-                    d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
+    if (BuildPeers(d, &args.peers) != FTH_B200_OK) return FTH_B200_ERR_INVALID;
+    return Run(PickVariant(d->variant, d->dtype, args, d->workspace, d->workspace_bytes), d->dtype, args, fe, ie,
+               d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* d) {
@@ -213,6 +242,7 @@ extern "C" int fth_b200_int8_linear(const fth_b200_int8_linear_desc* d, fth_b200
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Int8Epilogue ie; Fp8Epilogue fe = {};
     BuildInt8(d, &args, &ie);
-    return Dispatch(PickVariant(d->variant, FTH_B200_INT8, args, d->workspace, d->workspace_bytes), FTH_B200_INT8, args,
-                    fe, ie, d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
+    if (BuildPeers(d, &args.peers) != FTH_B200_OK) return FTH_B200_ERR_INVALID;
+    return Run(PickVariant(d->variant, FTH_B200_INT8, args, d->workspace, d->workspace_bytes), FTH_B200_INT8, args,
+               fe, ie, d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -5,6 +5,14 @@
 
 namespace fth {
 
+// Other GPUs' copies of the output buffer (column-sharded projections): every byte a kernel stores at address X of
+// the local output is also stored at X + delta[r].  The buffers are peer-mapped device memory of the same shape.
+constexpr int kMaxPeers = 7;
+struct PeerOut {
+    int count;
+    int64_t delta[kMaxPeers];
+};
+
 // Operand description common to FP8 and INT8 linear kernels.
 struct LinearArgs {
     const void* a;   // [M,K] activations (FP8 / INT8, or BF16 / FP32 when a Cast / QuantizeLinear is fused)
@@ -15,6 +23,7 @@ struct LinearArgs {
     float a_scale;   // used only by the fused-cast activation load
     int zero_points; // INT8: activation or weight zero point is non-zero
     int w_static;    // no earlier work in the stream writes the weights: they may be read before it has finished
+    PeerOut peers;   // replicas of the output on other GPUs (count 0: none)
 };
 
 int LaunchLinearSimt(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
@@ -41,5 +50,10 @@ bool Tcgen05Supported(int dtype, const LinearArgs& args);
 size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& args);
 int LaunchLinearTcgen05(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* scratch,
                         size_t scratch_bytes, cudaStream_t stream);
+// True when that launch writes the peer replicas from its own epilogue (otherwise the caller copies the block over).
+bool Tcgen05StoresToPeers(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie);
+
+// Copies the [m, n] output block (elements of `elem_bytes`, row stride ldo elements) to every peer replica.
+int LaunchPeerCopy(const void* out, int64_t m, int64_t n, int64_t ldo, int elem_bytes, const PeerOut& peers, cudaStream_t stream);
 
 }  // namespace fth

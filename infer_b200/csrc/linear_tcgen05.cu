@@ -579,6 +579,13 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     }
 }
 
+// Stores `value` at `dst` and at the same place in every peer replica of the output.
+template <typename T>
+__device__ __forceinline__ void StoreWithPeers(const PeerOut& peers, T* dst, T value) {
+    *dst = value;
+    for (int r = 0; r < peers.count; ++r) *reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(dst) + peers.delta[r]) = value;
+}
+
 // Epilogue of four consecutive output channels p4 .. p4+3 of activation row q (swapped tiling), given their
 // complete accumulators: the vectorised fast path or the generic per-element store.
 template <bool INT8>
@@ -624,14 +631,14 @@ __device__ __forceinline__ void FinishFour(const TcParams& p, const Fp8Epilogue&
                     uint2 t;
                     t.x = EncodeBf16Cast(o[0]) | (static_cast<uint32_t>(EncodeBf16Cast(o[1])) << 16);
                     t.y = EncodeBf16Cast(o[2]) | (static_cast<uint32_t>(EncodeBf16Cast(o[3])) << 16);
-                    *reinterpret_cast<uint2*>(dst) = t;
+                    StoreWithPeers(p.args.peers, reinterpret_cast<uint2*>(dst), t);
                 } else {
-                    for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) dst[i] = EncodeBf16Cast(o[i]);
+                    for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) StoreWithPeers(p.args.peers, dst + i, EncodeBf16Cast(o[i]));
                 }
             } else {
                 float* dst = static_cast<float*>(fe.out) + q * fe.ldo + p4;
-                if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
-                else { for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) dst[i] = o[i]; }
+                if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) StoreWithPeers(p.args.peers, reinterpret_cast<float4*>(dst), make_float4(o[0], o[1], o[2], o[3]));
+                else { for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) StoreWithPeers(p.args.peers, dst + i, o[i]); }
             }
             return;
         }
@@ -643,9 +650,9 @@ __device__ __forceinline__ void FinishFour(const TcParams& p, const Fp8Epilogue&
     const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
     uint8_t* dst = static_cast<uint8_t*>(INT8 ? ie.out : fe.out) + q * ldo + p4;
     if (p4 + 3 < p.p_total && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
-        *reinterpret_cast<uint32_t*>(dst) = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+        StoreWithPeers(p.args.peers, reinterpret_cast<uint32_t*>(dst), b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24));
     } else {
-        for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) dst[i] = static_cast<uint8_t>(b[i]);
+        for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) StoreWithPeers(p.args.peers, dst + i, static_cast<uint8_t>(b[i]));
     }
 }
 
@@ -782,19 +789,20 @@ __device__ __forceinline__ void FinishOne(const TcParams& p, const Fp8Epilogue& 
         const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
         const double so_d = static_cast<double>(ie.out_scale);
         const double md = sd / so_d;
-        static_cast<int8_t*>(ie.out)[q * ie.ldo + n] = RequantFast(static_cast<int32_t>(raw), static_cast<float>(md), md, sd, so_d, ie.out_zp);
+        StoreWithPeers(p.args.peers, static_cast<int8_t*>(ie.out) + q * ie.ldo + n,
+                       RequantFast(static_cast<int32_t>(raw), static_cast<float>(md), md, sd, so_d, ie.out_zp));
     } else {
         const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
         const float t = __fmul_rn(__uint_as_float(raw), mult);
         const float y = p.out_inv != 0.0f ? __fmul_rn(t, p.out_inv) : __fdiv_rn(t, fe.out_scale);
         const uint8_t code = p.e4m3 ? Encode<FTH_B200_FP8E4M3>(y) : Encode<FTH_B200_FP8E5M2>(y);
         const int64_t o = q * fe.ldo + n;
-        if (fe.out_dtype == 0) { static_cast<uint8_t*>(fe.out)[o] = code; return; }
+        if (fe.out_dtype == 0) { StoreWithPeers(p.args.peers, static_cast<uint8_t*>(fe.out) + o, code); return; }
         // fused Cast behind the MatMul: the decoded code times the output scale, as BF16 or FP32
         const float d = p.e4m3 ? Decode<FTH_B200_FP8E4M3>(code) : Decode<FTH_B200_FP8E5M2>(code);
         const float v = __fmul_rn(d, fe.out_scale);
-        if (fe.out_dtype == FTH_B200_BF16) static_cast<uint16_t*>(fe.out)[o] = EncodeBf16Cast(v);
-        else static_cast<float*>(fe.out)[o] = v;
+        if (fe.out_dtype == FTH_B200_BF16) StoreWithPeers(p.args.peers, static_cast<uint16_t*>(fe.out) + o, EncodeBf16Cast(v));
+        else StoreWithPeers(p.args.peers, static_cast<float*>(fe.out) + o, v);
     }
 }
 
@@ -1246,6 +1254,18 @@ bool Tcgen05Supported(int dtype, const LinearArgs& a) {
     return true;
 }
 
+// The four-/one-channel epilogues have a direct path when no bias, alpha or beta is in play (a fused output Cast is
+// fine for FP8); that path also writes the peer replicas.
+static bool DirectEpilogue(bool int8, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
+    if (int8) return ie.bias_mode == FTH_B200_BIAS_NONE && ie.out_dtype == 0 && !(ie.is_gemm && (ie.alpha != 1.0f || ie.beta != 1.0f));
+    return fe.bias_mode == FTH_B200_BIAS_NONE && !(fe.is_gemm && fe.alpha != 1.0f);
+}
+
+bool Tcgen05StoresToPeers(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
+    const TcGeometry g = GeometryFor(a);
+    return g.swap && (g.cluster > 0 || g.split > 1) && DirectEpilogue(dtype == FTH_B200_INT8, fe, ie);
+}
+
 size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& a) {
     (void)dtype;
     const TcGeometry g = GeometryFor(a);
@@ -1295,7 +1315,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     p.e4m3 = dtype == FTH_B200_FP8E4M3;
     if (int8) p.fast = ie.bias_mode == FTH_B200_BIAS_NONE && ie.out_dtype == 0 && !(ie.is_gemm && (ie.alpha != 1.0f || ie.beta != 1.0f));
     else p.fast = fe.bias_mode == FTH_B200_BIAS_NONE && fe.out_dtype == 0 && !(fe.is_gemm && fe.alpha != 1.0f);
-    p.fast4 = int8 ? p.fast : (fe.bias_mode == FTH_B200_BIAS_NONE && !(fe.is_gemm && fe.alpha != 1.0f));
+    p.fast4 = DirectEpilogue(int8, fe, ie);
     p.a_inv = int8 ? 0.0f : ExactReciprocal(a.a_scale);
     p.out_inv = int8 ? 0.0f : ExactReciprocal(fe.out_scale);
     p.scratch = scratch;

@@ -1,0 +1,101 @@
+// Multi-GPU plumbing for column-sharded projections: peer-mapped output buffers (CUDA IPC), the block copy used by
+// kernels that do not write the peer replicas themselves, and the signal / wait step that ends a gather.
+//
+// A gather works without a collective library: every rank's linear kernel stores its columns into all ranks'
+// output buffers (plain peer stores over NVLink), then each rank raises a flag in every rank's flag array and
+// waits — bounded — for everybody's flag.  Flags carry the caller's step number, so nothing is ever reset.
+#include <string.h>
+
+#include "common.cuh"
+#include "linear_internal.h"
+#include "tma.cuh"
+
+namespace fth {
+namespace {
+
+__global__ void __launch_bounds__(256) PeerCopyKernel(const uint8_t* __restrict__ out, int64_t rows, int64_t row_bytes, int64_t pitch_bytes,
+                                                      PeerOut peers) {
+    const int64_t total = rows * row_bytes;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t offset = (i / row_bytes) * pitch_bytes + i % row_bytes;
+        const uint8_t v = out[offset];
+        for (int r = 0; r < peers.count; ++r) const_cast<uint8_t*>(out)[offset + peers.delta[r]] = v;
+    }
+}
+
+struct FlagPtrs { uint32_t* rank_flags[kMaxPeers + 1]; };
+
+// Thread r tells rank r "rank `self` has finished step `epoch`" and then waits until rank r has said the same here.
+// The kernels whose stores this publishes ran earlier on the same stream, so they are complete; the release at
+// system scope orders them before the flag for a peer that acquires it.
+__global__ void GatherSyncKernel(FlagPtrs flags, int world, int self, uint32_t epoch, int* status) {
+    const int r = threadIdx.x;
+    if (r >= world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.rank_flags[r] + self), "r"(epoch) : "memory");
+    const uint32_t* mine = flags.rank_flags[self] + r;
+    const uint64_t start = GlobalTimerNs();
+    for (;;) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if (static_cast<int32_t>(seen - epoch) >= 0) break;  // steps only grow (wrap-around safe)
+        if (GlobalTimerNs() - start > kWaitBudgetNs) { ReportTimeout(status, 40, r); break; }
+        __nanosleep(100);
+    }
+}
+
+}  // namespace
+
+int LaunchPeerCopy(const void* out, int64_t m, int64_t n, int64_t ldo, int elem_bytes, const PeerOut& peers, cudaStream_t stream) {
+    if (peers.count <= 0 || m <= 0 || n <= 0) return FTH_B200_OK;
+    const int64_t total = m * n * elem_bytes;
+    const int64_t blocks = (total + 255) / 256;
+    PeerCopyKernel<<<static_cast<unsigned>(blocks < 1184 ? blocks : 1184), 256, 0, stream>>>(static_cast<const uint8_t*>(out), m, n * elem_bytes,
+                                                                                           ldo * elem_bytes, peers);
+    NoteLaunch("peer_copy");
+    return CheckLaunch();
+}
+
+}  // namespace fth
+
+using namespace fth;
+
+extern "C" int fth_b200_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle) {
+    if (ptr == nullptr || handle == nullptr || bytes == 0) return FTH_B200_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == FTH_B200_PEER_HANDLE_BYTES, "IPC handle size");
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    cudaIpcMemHandle_t h;
+    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess || cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        cudaFree(p);
+        return FTH_B200_ERR_CUDA;
+    }
+    memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return FTH_B200_OK;
+}
+
+extern "C" int fth_b200_peer_buffer_open(const unsigned char* handle, void** ptr) {
+    if (ptr == nullptr || handle == nullptr) return FTH_B200_ERR_INVALID;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? FTH_B200_OK : FTH_B200_ERR_CUDA;
+}
+
+extern "C" int fth_b200_peer_buffer_close(void* ptr) {
+    return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? FTH_B200_OK : FTH_B200_ERR_CUDA;
+}
+
+extern "C" int fth_b200_peer_buffer_destroy(void* ptr) { return cudaFree(ptr) == cudaSuccess ? FTH_B200_OK : FTH_B200_ERR_CUDA; }
+
+extern "C" int fth_b200_gather_sync(void* const* rank_flags, int32_t world, int32_t rank, uint32_t epoch, fth_b200_stream_t stream_) {
+    if (rank_flags == nullptr || world < 1 || world > kMaxPeers + 1 || rank < 0 || rank >= world) return FTH_B200_ERR_INVALID;
+    FlagPtrs flags = {};
+    for (int r = 0; r < world; ++r) {
+        if (rank_flags[r] == nullptr) return FTH_B200_ERR_INVALID;
+        flags.rank_flags[r] = static_cast<uint32_t*>(rank_flags[r]);
+    }
+    GatherSyncKernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(flags, world, rank, epoch, DeviceStatusPtr());
+    NoteLaunch("gather_sync");
+    return CheckLaunch();
+}

@@ -6,6 +6,11 @@ box; per-output-channel scales / zero points / vector bias split the same way.  
 inside the kernels depends on K and M alone, so the bytes equal the single-GPU result — and ONE all-gather of
 the 1-byte outputs follows.  There is no other data-path collective.
 
+On the GPUs the gather needs no collective library at all: ``PeerGather`` maps every rank's output buffer into
+every rank (CUDA IPC), the linear kernels store their columns into all of them from their own epilogue, and one
+small signal / wait kernel ends the step (``ShardedLinear.forward_peer``).  The NCCL path stays for hosts where
+peer mapping is not available and for the CPU (gloo) tests of the host logic.
+
 The reference has no multi-device code at all (one ``CudaExecutionContext`` = one device,
 src/kernel/cuda/runtime.cu:318-321, 453-472); the single-GPU result is the oracle for this module.
 """
@@ -71,3 +76,87 @@ class ShardedLinear:
         for r, (b0, b1) in enumerate(self.bounds):
             full_out[:, b0:b1].copy_(gathered[r, :, : b1 - b0])
         return full_out
+
+
+class PeerGather:
+    """Every rank's [M, N] output buffer, mapped into every rank of one box, with the flags that end a step.
+
+    Two buffers per rank, used by step parity: a rank can run at most one step ahead of the slowest one (it
+    cannot pass step s before every rank has signalled s), so the buffer of step s is not written again until
+    everybody has consumed it.  `dist` is only used to exchange the 64-byte handles at set-up.
+    """
+
+    def __init__(self, lib, dist, world: int, rank: int, m: int, n: int, elem_bytes: int = 1):
+        import ctypes as C
+        self.lib, self.world, self.rank = lib, world, rank
+        self.m, self.n, self.elem = m, n, elem_bytes
+        self.block = (m * n * elem_bytes + 255) // 256 * 256
+        total = 2 * self.block + 256  # two output buffers, then uint32 flags[world]
+        own = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        if lib.fth_b200_peer_buffer_create(C.c_size_t(total), C.byref(own), handle) != 0:
+            raise RuntimeError("fth_b200_peer_buffer_create failed")
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, bytes(handle))
+        self.base = [0] * world
+        self.base[rank] = own.value
+        for r in range(world):
+            if r == rank:
+                continue
+            ptr = C.c_void_p()
+            peer_handle = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+            if lib.fth_b200_peer_buffer_open(peer_handle, C.byref(ptr)) != 0:
+                raise RuntimeError(f"fth_b200_peer_buffer_open failed for rank {r}")
+            self.base[r] = ptr.value
+        self.flags = (C.c_void_p * world)(*[b + 2 * self.block for b in self.base])
+        self.epoch = 0
+        if world > 1:
+            dist.barrier()  # nobody stores into a buffer before every rank has mapped it
+
+    def buffer(self, r: int, parity: int) -> int:
+        """Device address of rank r's output buffer for steps of this parity, as seen from this rank."""
+        return self.base[r] + parity * self.block
+
+    def view(self, torch, parity: int):
+        """This rank's gathered [M, N] buffer as a uint8 tensor of M * N * elem_bytes bytes per row block."""
+        class _Raw:
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (self.m, self.n * self.elem), "typestr": "|u1",
+                                        "data": (self.buffer(self.rank, parity), False), "version": 3}
+        return torch.as_tensor(raw, device="cuda")
+
+    def sync(self, stream) -> None:
+        """Signals this step to every rank and waits (on the stream) for theirs."""
+        import ctypes as C
+        if self.lib.fth_b200_gather_sync(self.flags, C.c_int32(self.world), C.c_int32(self.rank), C.c_uint32(self.epoch), stream) != 0:
+            raise RuntimeError("fth_b200_gather_sync failed")
+
+    def close(self) -> None:
+        for r, b in enumerate(self.base):
+            if b and r != self.rank:
+                self.lib.fth_b200_peer_buffer_close(b)
+        if self.base[self.rank]:
+            self.lib.fth_b200_peer_buffer_destroy(self.base[self.rank])
+        self.base = [0] * self.world
+
+
+def forward_peer(shard: "ShardedLinear", gather: PeerGather, desc, call, stream):
+    """One gathered step: `desc` is this rank's linear descriptor (weights = its column slice); its output and
+    peer fields are pointed at the step's buffers, `call(desc, stream)` launches the C ABI, then the step is
+    signalled.  Returns the parity of the buffer that holds the [M, N] result once the stream has run."""
+    gather.epoch += 1
+    parity = gather.epoch & 1
+    offset = shard.n0 * gather.elem
+    desc.out = gather.buffer(gather.rank, parity) + offset
+    desc.ldo = gather.n
+    others = [r for r in range(gather.world) if r != gather.rank]
+    desc.gather_peers = len(others)
+    for i, r in enumerate(others):
+        desc.gather_out[i] = gather.buffer(r, parity) + offset
+    rc = call(desc, stream)
+    if rc != 0:
+        raise RuntimeError(f"linear call failed: {rc}")
+    gather.sync(stream)
+    return parity

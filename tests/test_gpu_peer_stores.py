@@ -1,0 +1,89 @@
+"""Peer replicas of the output on ONE GPU: the "peers" are two more local buffers, so every kernel family's way of
+writing them (from its own epilogue, or through the block copy behind it) is checked without a second device."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import infer_b200 as B
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch
+
+
+# (m, k, n, variant): cluster kernel, two-kernel split path, CTA-pair dense kernel, CUDA-core kernels
+CASES = [(1, 1024, 2048, B.VARIANT_AUTO), (16, 8192, 8192, B.VARIANT_AUTO), (48, 2048, 4096, B.VARIANT_AUTO),
+         (300, 512, 640, B.VARIANT_AUTO), (4, 256, 384, B.VARIANT_SKINNY), (3, 96, 80, B.VARIANT_SIMT)]
+
+
+@pytest.mark.parametrize("m,k,n,variant", CASES)
+def test_fp8_output_reaches_every_replica(cuda, m, k, n, variant):
+    torch = cuda
+    rng = np.random.default_rng(m * 7 + n)
+    a = torch.from_numpy(rng.integers(0, 0x78, (m, k), dtype=np.uint8)).cuda()
+    w = torch.from_numpy(rng.integers(0, 0x78, (k, n), dtype=np.uint8)).cuda()
+    width, col0 = n + 256, 128  # the block sits inside a wider row, as a column shard does
+    bufs = [torch.full((m + 2, width), 0x5A, dtype=torch.uint8, device="cuda") for _ in range(3)]
+    d = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=k, n=n, a=a, w=w, out=None, a_scale=0.5, w_scale=2.0 ** -6,
+                          out_scale=float(k) / 64, ldo=width, variant=variant, weights_static=True)
+    d.out = bufs[0].data_ptr() + width + col0
+    d.gather_peers = 2
+    d.gather_out[0] = bufs[1].data_ptr() + width + col0
+    d.gather_out[1] = bufs[2].data_ptr() + width + col0
+    ws = B.linear_workspace(torch, d)
+    if B.lib().fth_b200_fp8_linear_supported(C.byref(d)) != 0:
+        pytest.skip("variant declines this shape")
+    B.fp8_linear(d)
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
+    host = [b.cpu().numpy() for b in bufs]
+    # the same call without replicas is the reference for the block
+    plain = torch.full((m + 2, width), 0x5A, dtype=torch.uint8, device="cuda")
+    d.out = plain.data_ptr() + width + col0
+    d.gather_peers = 0
+    B.fp8_linear(d)
+    torch.cuda.synchronize()
+    want = plain.cpu().numpy()
+    assert (want[1:m + 1, col0:col0 + n] != 0x5A).any()
+    for h in host:
+        assert np.array_equal(h, want), "a replica differs from the local output (or bytes outside the block moved)"
+    del ws
+
+
+def test_int8_output_reaches_every_replica(cuda):
+    torch = cuda
+    m, k, n = 8, 1024, 1024
+    rng = np.random.default_rng(5)
+    a = torch.from_numpy(rng.integers(-127, 128, (m, k), dtype=np.int8)).cuda()
+    w = torch.from_numpy(rng.integers(-127, 128, (k, n), dtype=np.int8)).cuda()
+    scales = torch.full((n,), 0.004, dtype=torch.float32, device="cuda")
+    bufs = [torch.full((m, n), 77, dtype=torch.int8, device="cuda") for _ in range(3)]
+    d = B.int8_linear_desc(op=B.OP_MATMUL, m=m, k=k, n=n, a=a, w=w, out=bufs[0], a_scale=0.02, a_zp=0, w_scales=scales,
+                           w_zps=None, w_params=n, out_scale=1.5, out_zp=0)
+    d.gather_peers = 2
+    d.gather_out[0], d.gather_out[1] = bufs[1].data_ptr(), bufs[2].data_ptr()
+    ws = B.linear_workspace(torch, d)
+    B.int8_linear(d)
+    torch.cuda.synchronize()
+    host = [b.cpu().numpy() for b in bufs]
+    assert (host[0] != 77).any() and np.array_equal(host[0], host[1]) and np.array_equal(host[0], host[2])
+    del ws
+
+
+def test_gather_sync_single_rank(cuda):
+    torch = cuda
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    ptrs = (C.c_void_p * 1)(flags.data_ptr())
+    for epoch in (1, 2, 3):
+        assert B.lib().fth_b200_gather_sync(ptrs, C.c_int32(1), C.c_int32(0), C.c_uint32(epoch), B.current_stream()) == 0
+        torch.cuda.synchronize()
+        assert int(flags[0].item()) == epoch and B.device_status() == 0
+    assert B.lib().fth_b200_gather_sync(ptrs, C.c_int32(9), C.c_int32(0), C.c_uint32(1), B.current_stream()) == B.ERR_INVALID
