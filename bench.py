@@ -391,9 +391,72 @@ def extra_measurements(torch, B, dev, peaks, fp8_call, int8_call, stream, sa, ou
                                    "hbm_frac": round(gbs / peaks["hbm_gbs"], 3),
                                    "tensor_frac": round(tfl / (2.0 * peaks["bf16_tflops"]), 3), "kernel": B.last_variant()}
             del keep
+    out["config4_decode_step"] = config4_decode_step(torch, B, dev, fp8_call, stream)
+    out["config3_conv"] = config3_conv(torch, B, dev, stream)
     out["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "fp8_int8_dense_tflops": 2.0 * peaks["bf16_tflops"],
                     "note": "8-bit dense peak taken as twice the measured bf16 burst figure", "source": peaks["source"]}
     return out
+
+
+def config4_decode_step(torch, B, dev, fp8_call, stream):
+    """Config 4: the 168 projections of a 24-layer decode step (hidden 1024, intermediate 3584, FP8 E5M2, BF16 in and
+    out — Cast -> MatMul -> Cast fused per projection), replayed as one CUDA graph.  Synthetic weights and inputs."""
+    hidden, inter, layers = 1024, 3584, 24
+    shapes = [(hidden, hidden)] * 4 + [(hidden, inter), (hidden, inter), (inter, hidden)]
+    result = {}
+    for m in (1, 16):
+        descs, keep = [], []
+        for _ in range(layers):
+            for k, n in shapes:
+                w = torch.randint(0, 120, (k, n), dtype=torch.uint8, device=dev)
+                a = torch.randn((m, k), device=dev).to(torch.bfloat16)
+                o = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+                d = B.fp8_linear_desc(dtype=B.E5M2, op=B.OP_MATMUL, m=m, k=k, n=n, a=a, w=w, out=o, a_scale=2.0 ** -9, w_scale=2.0 ** -20,
+                                      out_scale=2.0 ** -9, a_dtype=B.BF16, out_dtype=B.BF16, weights_static=True)
+                keep += [w, a, o, B.linear_workspace(torch, d)]
+                descs.append(d)
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            s2 = C.c_void_p(side.cuda_stream)
+            for d in descs:
+                fp8_call(C.byref(d), s2)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for d in descs:
+                    if fp8_call(C.byref(d), C.c_void_p(torch.cuda.current_stream().cuda_stream)) != 0:
+                        raise RuntimeError("linear call failed during capture")
+        ms = event_time_ms(torch, graph.replay, 20, 3) / 20
+        wbytes = layers * sum(k * n for k, n in shapes)
+        result[f"m{m}"] = {"us": round(ms * 1e3, 1), "projections": len(descs), "weight_GB/s": round(wbytes / (ms * 1e-3) / 1e9, 1),
+                           "kernel": B.last_variant()}
+        del keep, graph
+    return result
+
+
+def config3_conv(torch, B, dev, stream):
+    """Config 3: INT8 3x3 conv 1x64x160x160 (*) 64x64x3x3, pad 1, per-channel scales, int32 bias, fused ReLU table."""
+    x = torch.randint(-128, 128, (1, 64, 160, 160), dtype=torch.int8, device=dev)
+    w = torch.randint(-128, 128, (64, 64, 3, 3), dtype=torch.int8, device=dev)
+    bias = torch.randint(-(1 << 15), 1 << 15, (64,), dtype=torch.int32, device=dev)
+    ws = torch.empty(64, dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2)
+    out = torch.empty((1, 64, 160, 160), dtype=torch.int8, device=dev)
+    so = 0.4
+    lut = torch.from_numpy(B.int8_relu_table(so, 0, so, 0)).to(dev)
+    d = B.int8_conv2d_desc(batch=1, ic=64, ih=160, iw=160, oc=64, kh=3, kw=3, x=x, w=w, out=out, x_scale=0.02, x_zp=0, w_scales=ws, w_zps=None,
+                           w_params=64, out_scale=so, out_zp=0, bias=bias, relu_lut=lut, bias_max_abs=1 << 15)
+    need = B.lib().fth_b200_int8_conv2d_workspace_bytes(C.byref(d))
+    wsb = torch.empty(max(int(need), 16), dtype=torch.uint8, device=dev)
+    d.workspace, d.workspace_bytes = wsb.data_ptr(), need
+    call = B.lib().fth_b200_int8_conv2d
+
+    def fn():
+        if call(C.byref(d), stream) != 0:
+            raise RuntimeError("conv call failed")
+        d.weights_packed = 1
+    fn()
+    ms = event_time_ms(torch, fn, 100, 3) / 100
+    return {"us": round(ms * 1e3, 2), "TOP/s": round(2.0 * 160 * 160 * 64 * 576 / (ms * 1e-3) / 1e12, 1), "kernel": B.last_variant()}
 
 
 def cpu_baseline_measurement(torch):

@@ -17,7 +17,10 @@ void NoteLaunch(const char* variant, int64_t launches) {
     g_launches += launches;
 }
 
-int CheckLaunch() { return cudaPeekAtLastError() == cudaSuccess ? FTH_B200_OK : FTH_B200_ERR_CUDA; }
+int CheckLaunch() { return cudaGetLastError() == cudaSuccess ? FTH_B200_OK : FTH_B200_ERR_CUDA; }
+// A non-sticky error some other library left behind in this thread (NCCL's peer-access probes do) must not be blamed on
+// the next launch here: every entry point that launches starts by discarding it.
+void ClearStaleError() { (void)cudaGetLastError(); }
 
 namespace {
 
@@ -210,6 +213,7 @@ extern "C" size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_
 }
 
 extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_stream_t stream) {
+    ClearStaleError();
     const int rc = ValidateFp8(d);
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Fp8Epilogue fe; Int8Epilogue ie = {};
@@ -238,6 +242,7 @@ extern "C" size_t fth_b200_int8_linear_workspace_bytes(const fth_b200_int8_linea
 }
 
 extern "C" int fth_b200_int8_linear(const fth_b200_int8_linear_desc* d, fth_b200_stream_t stream) {
+    ClearStaleError();
     const int rc = ValidateInt8(d);
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Int8Epilogue ie; Fp8Epilogue fe = {};

@@ -14,7 +14,8 @@ constexpr int kNumSms = 148;  // B200: 2 dies x 74 SMs
 
 // ---- launch bookkeeping (host) ---------------------------------------------------------------------
 void NoteLaunch(const char* variant, int64_t launches = 1);
-int CheckLaunch();  // FTH_B200_OK or FTH_B200_ERR_CUDA after cudaPeekAtLastError
+int CheckLaunch();  // FTH_B200_OK or FTH_B200_ERR_CUDA (reads and clears the last error)
+void ClearStaleError();  // discards an error left behind by other code before this library launches
 
 // ---- FP8 codec -------------------------------------------------------------------------------------
 // Decode through the hardware converters: exact for every code, including subnormals, the E4M3 NaN

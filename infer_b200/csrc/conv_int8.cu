@@ -122,6 +122,7 @@ extern "C" size_t fth_b200_int8_conv2d_workspace_bytes(const fth_b200_int8_conv2
 }
 
 extern "C" int fth_b200_int8_conv2d(const fth_b200_int8_conv2d_desc* d, fth_b200_stream_t stream_) {
+    ClearStaleError();
     auto stream = static_cast<cudaStream_t>(stream_);
     ConvArgs c;
     const int rc = Validate(d, &c);

@@ -172,6 +172,7 @@ using namespace fth;
 
 extern "C" int fth_b200_cast(int32_t in_dtype, const void* x, float in_scale, int32_t out_dtype, void* out,
                              float out_scale, int64_t count, fth_b200_stream_t stream_) {
+    ClearStaleError();
     auto stream = static_cast<cudaStream_t>(stream_);
     if (x == nullptr || out == nullptr || count < 0) return FTH_B200_ERR_INVALID;
     const bool in_fp8 = in_dtype == FTH_B200_FP8E4M3 || in_dtype == FTH_B200_FP8E5M2;
@@ -193,6 +194,7 @@ extern "C" int fth_b200_cast(int32_t in_dtype, const void* x, float in_scale, in
 extern "C" int fth_b200_quantize_linear(int32_t x_dtype, const void* x, const float* scales, const int32_t* zps,
                                         int64_t params, int8_t* out, int64_t rows, int64_t channels,
                                         fth_b200_stream_t stream_) {
+    ClearStaleError();
     auto stream = static_cast<cudaStream_t>(stream_);
     if (!x || !scales || !zps || !out || rows <= 0 || channels <= 0) return FTH_B200_ERR_INVALID;
     if (params != 1 && params != channels) return FTH_B200_ERR_INVALID;
@@ -211,6 +213,7 @@ extern "C" int fth_b200_quantize_linear(int32_t x_dtype, const void* x, const fl
 extern "C" int fth_b200_dequantize_linear(const int8_t* x, const float* scales, const int32_t* zps, int64_t params,
                                           void* out, int32_t to_dtype, int64_t rows, int64_t channels,
                                           fth_b200_stream_t stream_) {
+    ClearStaleError();
     auto stream = static_cast<cudaStream_t>(stream_);
     if (!x || !scales || !zps || !out || rows <= 0 || channels <= 0) return FTH_B200_ERR_INVALID;
     if (params != 1 && params != channels) return FTH_B200_ERR_INVALID;
@@ -228,6 +231,7 @@ extern "C" int fth_b200_dequantize_linear(const int8_t* x, const float* scales, 
 
 extern "C" int fth_b200_int8_lookup(const int8_t* x, int8_t* out, int64_t count, const int8_t* device_lut256,
                                     fth_b200_stream_t stream_) {
+    ClearStaleError();
     auto stream = static_cast<cudaStream_t>(stream_);
     if (!x || !out || !device_lut256 || count < 0) return FTH_B200_ERR_INVALID;
     if (count == 0) return FTH_B200_OK;

@@ -89,6 +89,7 @@ extern "C" int fth_b200_peer_buffer_close(void* ptr) {
 extern "C" int fth_b200_peer_buffer_destroy(void* ptr) { return cudaFree(ptr) == cudaSuccess ? FTH_B200_OK : FTH_B200_ERR_CUDA; }
 
 extern "C" int fth_b200_gather_sync(void* const* rank_flags, int32_t world, int32_t rank, uint32_t epoch, fth_b200_stream_t stream_) {
+    ClearStaleError();
     if (rank_flags == nullptr || world < 1 || world > kMaxPeers + 1 || rank < 0 || rank >= world) return FTH_B200_ERR_INVALID;
     FlagPtrs flags = {};
     for (int r = 0; r < world; ++r) {

@@ -62,3 +62,35 @@ def test_two_rank_sharded_linear_equals_single_process(m, n, trans_b):
     results = manager.dict()
     mp.spawn(_worker, args=(2, port, m, n, trans_b, results), nprocs=2, join=True)
     assert dict(results) == {0: True, 1: True}
+
+
+def test_forward_peer_points_the_descriptor_at_every_rank(monkeypatch):
+    """Host logic of the library-free gather, no GPU: the step's parity picks the buffers, this rank's column
+    offset is applied to its own and to every peer's address, and the step ends with a sync of that epoch."""
+    import infer_b200 as B
+    from infer_b200.sharded import ShardedLinear, forward_peer
+
+    class FakeGather:
+        world, rank, n, elem = 4, 2, 1024, 1
+        epoch = 0
+        synced = []
+
+        def buffer(self, r, parity):
+            return 0x10000000 * (r + 1) + parity * 0x100000
+
+        def sync(self, stream):
+            self.synced.append(self.epoch)
+
+    shard = ShardedLinear(1024, 4, 2, compute=None)
+    gather = FakeGather()
+    d = B.Fp8LinearDesc()
+    seen = []
+    for step in (1, 2, 3):
+        parity = forward_peer(shard, gather, d, lambda desc, s: seen.append((desc.out, desc.ldo, desc.gather_peers, list(desc.gather_out[:3]))) or 0, None)
+        assert parity == step & 1
+        out, ldo, peers, others = seen[-1]
+        assert out == gather.buffer(2, parity) + shard.n0 and ldo == 1024 and peers == 3
+        assert others == [gather.buffer(r, parity) + shard.n0 for r in (0, 1, 3)]
+    assert gather.synced == [1, 2, 3]
+    with pytest.raises(RuntimeError):
+        forward_peer(shard, gather, d, lambda desc, s: -3, None)
