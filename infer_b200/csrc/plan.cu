@@ -182,17 +182,20 @@ extern "C" int fth_b200_plan_create_int8_conv2d(const fth_b200_int8_conv2d_desc*
     return FTH_B200_OK;
 }
 
-extern "C" int fth_b200_plan_launch(fth_b200_plan* p, const void* device_in, void* device_out, fth_b200_stream_t stream) {
+// `mirror`: device-visible address of a second copy of the output (pinned host memory), or null.
+static int LaunchPlan(fth_b200_plan* p, const void* device_in, void* device_out, void* mirror, fth_b200_stream_t stream) {
     if (!p || !device_in || !device_out) return FTH_B200_ERR_INVALID;
     switch (p->kind) {
         case Kind::kFp8Linear: {
             fth_b200_fp8_linear_desc d = p->fp8;
             d.a = device_in; d.out = device_out;
+            if (mirror) { d.gather_peers = 1; d.gather_out[0] = mirror; }
             return fth_b200_fp8_linear(&d, stream);
         }
         case Kind::kInt8Linear: {
             fth_b200_int8_linear_desc d = p->int8;
             d.a = device_in; d.out = device_out;
+            if (mirror) { d.gather_peers = 1; d.gather_out[0] = mirror; }
             return fth_b200_int8_linear(&d, stream);
         }
         case Kind::kInt8Conv: {
@@ -206,13 +209,27 @@ extern "C" int fth_b200_plan_launch(fth_b200_plan* p, const void* device_in, voi
     return FTH_B200_ERR_INVALID;
 }
 
+extern "C" int fth_b200_plan_launch(fth_b200_plan* p, const void* device_in, void* device_out, fth_b200_stream_t stream) {
+    return LaunchPlan(p, device_in, device_out, nullptr, stream);
+}
+
 extern "C" int fth_b200_plan_run(fth_b200_plan* p, const void* host_in, void* host_out, fth_b200_stream_t stream_) {
     if (!p || !host_in || !host_out) return FTH_B200_ERR_INVALID;
     auto stream = static_cast<cudaStream_t>(stream_);
     if (cudaMemcpyAsync(p->in.ptr, host_in, static_cast<size_t>(p->in_bytes), cudaMemcpyHostToDevice, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
-    const int rc = fth_b200_plan_launch(p, p->in.ptr, p->out.ptr, stream_);
+    // A result buffer in pinned (device-mapped) host memory is written by the linear kernels' own epilogue, as a
+    // second copy of the output: no device-to-host copy is queued behind them.
+    void* mirror = nullptr;
+    if (p->kind != Kind::kInt8Conv) {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, host_out) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr)
+            mirror = attr.devicePointer;
+        else
+            (void)cudaGetLastError();
+    }
+    const int rc = LaunchPlan(p, p->in.ptr, p->out.ptr, mirror, stream_);
     if (rc != FTH_B200_OK) return rc;
-    if (cudaMemcpyAsync(host_out, p->out.ptr, static_cast<size_t>(p->out_bytes), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    if (!mirror && cudaMemcpyAsync(host_out, p->out.ptr, static_cast<size_t>(p->out_bytes), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
     if (cudaStreamSynchronize(stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
     return FTH_B200_OK;
 }

@@ -1,0 +1,77 @@
+"""Host-buffer plans (fth_b200_plan_*): the convenience layer bench.py's end-to-end figure goes through.  The result
+must be the bytes of the direct device call, whether the host result buffer is pageable (copied back) or pinned
+(written by the kernels themselves as a second copy of the output)."""
+import numpy as np
+import pytest
+
+import infer_b200 as B
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 1024, 2048), (16, 8192, 8192), (200, 512, 768)])
+def test_fp8_plan_matches_device_call(cuda, m, k, n):
+    torch = cuda
+    rng = np.random.default_rng(m + n)
+    a = rng.integers(0, 0x78, (m, k), dtype=np.uint8)
+    w = rng.integers(0, 0x78, (k, n), dtype=np.uint8)
+    a_dev, w_dev = torch.from_numpy(a).cuda(), torch.from_numpy(w).cuda()
+    out_dev = torch.empty((m, n), dtype=torch.uint8, device="cuda")
+    d = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=k, n=n, a=a_dev, w=w_dev, out=out_dev, a_scale=0.5, w_scale=2.0 ** -6,
+                          out_scale=float(k) / 64)
+    ws = B.linear_workspace(torch, d)
+    B.fp8_linear(d)
+    torch.cuda.synchronize()
+    want = out_dev.cpu().numpy()
+    hd = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=k, n=n, a=None, w=None, out=None, a_scale=0.5, w_scale=2.0 ** -6,
+                           out_scale=float(k) / 64)
+    hd.w = w.ctypes.data
+    plan = B.Plan(hd)
+    pageable = np.zeros((m, n), dtype=np.uint8)
+    plan.run(a, pageable)
+    assert np.array_equal(pageable, want)
+    pinned_in = torch.from_numpy(a).pin_memory()
+    pinned_out = torch.zeros((m, n), dtype=torch.uint8).pin_memory()
+    for _ in range(2):
+        pinned_out.zero_()
+        plan.run(pinned_in, pinned_out)
+        assert np.array_equal(pinned_out.numpy(), want)
+    plan.close()
+    assert B.device_status() == 0
+    del ws
+
+
+def test_int8_plan_matches_device_call(cuda):
+    torch = cuda
+    m, k, n = 4, 1024, 1024
+    rng = np.random.default_rng(11)
+    a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    w = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    scales = np.full(n, 0.004, dtype=np.float32)
+    a_dev, w_dev, s_dev = torch.from_numpy(a).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(scales).cuda()
+    out_dev = torch.empty((m, n), dtype=torch.int8, device="cuda")
+    d = B.int8_linear_desc(op=B.OP_MATMUL, m=m, k=k, n=n, a=a_dev, w=w_dev, out=out_dev, a_scale=0.02, a_zp=0, w_scales=s_dev, w_zps=None,
+                           w_params=n, out_scale=1.5, out_zp=0)
+    ws = B.linear_workspace(torch, d)
+    B.int8_linear(d)
+    torch.cuda.synchronize()
+    want = out_dev.cpu().numpy()
+    hd = B.int8_linear_desc(op=B.OP_MATMUL, m=m, k=k, n=n, a=None, w=None, out=None, a_scale=0.02, a_zp=0, w_scales=None, w_zps=None,
+                            w_params=n, out_scale=1.5, out_zp=0)
+    hd.w, hd.w_scales = w.ctypes.data, scales.ctypes.data
+    plan = B.Plan(hd)
+    pageable = np.zeros((m, n), dtype=np.int8)
+    plan.run(a, pageable)
+    pinned_out = torch.zeros((m, n), dtype=torch.int8).pin_memory()
+    plan.run(torch.from_numpy(a).pin_memory(), pinned_out)
+    plan.close()
+    assert np.array_equal(pageable, want) and np.array_equal(pinned_out.numpy(), want)
+    del ws
