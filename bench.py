@@ -238,14 +238,18 @@ def run_gpu_arm(args):
     gather = None
     if world > 1:
         from infer_b200.sharded import PeerGather, ShardedLinear, forward_peer
+        from infer_b200.sharded import point_at_step_buffers
         gather = PeerGather(B.lib(), dist, world, rank, 1, N)
         shard = ShardedLinear(N, world, rank, compute=None, dist=dist)
+        # per weight set, one descriptor per step parity, pointed at that parity's buffers once
+        prepared = [tuple(point_at_step_buffers(shard, gather, type(d).from_buffer_copy(d), parity) for parity in (0, 1)) for d, _ in descs]
+        call_desc = lambda desc, s: fp8_call(C.byref(desc), s)  # noqa: E731
 
     def step():
         d, _ = descs[counter[0] & 1]
         counter[0] += 1
         if world > 1:
-            forward_peer(shard, gather, d, lambda desc, s: fp8_call(C.byref(desc), s), stream)
+            forward_peer(shard, gather, d, call_desc, stream, prepared[(counter[0] - 1) & 1])
             return
         rc = fp8_call(C.byref(d), stream)
         if rc != 0:

@@ -99,6 +99,7 @@ def lib():
         handle.fth_b200_plan_output_bytes.argtypes = [C.c_void_p]
         handle.fth_b200_plan_destroy.argtypes = [C.c_void_p]
         handle.fth_b200_plan_destroy.restype = None
+        handle.fth_b200_gather_sync.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]
         handle.fth_b200_plan_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         handle.fth_b200_plan_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = handle

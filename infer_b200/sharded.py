@@ -110,6 +110,7 @@ class PeerGather:
                 raise RuntimeError(f"fth_b200_peer_buffer_open failed for rank {r}")
             self.base[r] = ptr.value
         self.flags = (C.c_void_p * world)(*[b + 2 * self.block for b in self.base])
+        self._world, self._rank = C.c_int32(world), C.c_int32(rank)
         self.epoch = 0
         if world > 1:
             dist.barrier()  # nobody stores into a buffer before every rank has mapped it
@@ -129,8 +130,7 @@ class PeerGather:
 
     def sync(self, stream) -> None:
         """Signals this step to every rank and waits (on the stream) for theirs."""
-        import ctypes as C
-        if self.lib.fth_b200_gather_sync(self.flags, C.c_int32(self.world), C.c_int32(self.rank), C.c_uint32(self.epoch), stream) != 0:
+        if self.lib.fth_b200_gather_sync(self.flags, self._world, self._rank, self.epoch & 0xffffffff, stream) != 0:
             raise RuntimeError("fth_b200_gather_sync failed")
 
     def close(self) -> None:
@@ -142,12 +142,9 @@ class PeerGather:
         self.base = [0] * self.world
 
 
-def forward_peer(shard: "ShardedLinear", gather: PeerGather, desc, call, stream):
-    """One gathered step: `desc` is this rank's linear descriptor (weights = its column slice); its output and
-    peer fields are pointed at the step's buffers, `call(desc, stream)` launches the C ABI, then the step is
-    signalled.  Returns the parity of the buffer that holds the [M, N] result once the stream has run."""
-    gather.epoch += 1
-    parity = gather.epoch & 1
+def point_at_step_buffers(shard: "ShardedLinear", gather: PeerGather, desc, parity: int):
+    """Points `desc` (this rank's linear descriptor, weights = its column slice) at the buffers of steps with this
+    parity: its own block in its own buffer, and the same block in every other rank's."""
     offset = shard.n0 * gather.elem
     desc.out = gather.buffer(gather.rank, parity) + offset
     desc.ldo = gather.n
@@ -155,7 +152,18 @@ def forward_peer(shard: "ShardedLinear", gather: PeerGather, desc, call, stream)
     desc.gather_peers = len(others)
     for i, r in enumerate(others):
         desc.gather_out[i] = gather.buffer(r, parity) + offset
-    rc = call(desc, stream)
+    return desc
+
+
+def forward_peer(shard: "ShardedLinear", gather: PeerGather, desc, call, stream, prepared=None):
+    """One gathered step: `call(desc, stream)` launches the C ABI with the output pointed at the step's buffers, then
+    the step is signalled.  `prepared` = (desc for even steps, desc for odd steps) from point_at_step_buffers saves
+    the per-step pointer set-up (a decode step is a few microseconds of GPU time).  Returns the parity of the buffer
+    that holds the [M, N] result once the stream has run."""
+    gather.epoch += 1
+    parity = gather.epoch & 1
+    step_desc = prepared[parity] if prepared is not None else point_at_step_buffers(shard, gather, desc, parity)
+    rc = call(step_desc, stream)
     if rc != 0:
         raise RuntimeError(f"linear call failed: {rc}")
     gather.sync(stream)
