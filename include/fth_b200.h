@@ -282,7 +282,9 @@ void fth_b200_plan_destroy(fth_b200_plan* plan);
  * gather step: on `stream`, after this rank's earlier work, it writes `epoch` into slot [rank] of every rank's flag
  * array (rank_flags[r]: uint32[world], peer-mapped; rank_flags[rank] is this rank's own) and waits, for at most one
  * second, until every slot of its own array has reached `epoch`; a time-out is reported through
- * fth_b200_device_status.  Epochs grow by one per step; flags are never reset. */
+ * fth_b200_device_status.  Epochs grow by one per step; flags are never reset.  epoch = 0 takes the step number from a
+ * counter on the device (slot [world] of this rank's own array, incremented by the call), so that a captured CUDA graph
+ * can be replayed; all ranks must then use epoch = 0 for every step.  Each array has room for world + 1 words. */
 #define FTH_B200_PEER_HANDLE_BYTES 64
 int fth_b200_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle);
 int fth_b200_peer_buffer_open(const unsigned char* handle, void** ptr);

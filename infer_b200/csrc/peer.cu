@@ -29,16 +29,30 @@ struct FlagPtrs { uint32_t* rank_flags[kMaxPeers + 1]; };
 // The kernels whose stores this publishes ran earlier on the same stream, so they are complete; the release at
 // system scope orders them before the flag for a peer that acquires it.
 __global__ void GatherSyncKernel(FlagPtrs flags, int world, int self, uint32_t epoch, int* status) {
+    __shared__ uint32_t step;
+    if (threadIdx.x == 0) {
+        // epoch 0: the step number lives on the device (slot [world] of this rank's own flag array) and grows by one
+        // per call, so the same launch can be replayed from a CUDA graph
+        uint32_t e = epoch;
+        if (e == 0) {
+            e = flags.rank_flags[self][world] + 1;
+            if (e == 0) e = 1;
+            flags.rank_flags[self][world] = e;
+        }
+        step = e;
+    }
+    __syncthreads();
     const int r = threadIdx.x;
     if (r >= world) return;
+    const uint32_t e = step;
     __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.rank_flags[r] + self), "r"(epoch) : "memory");
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.rank_flags[r] + self), "r"(e) : "memory");
     const uint32_t* mine = flags.rank_flags[self] + r;
     const uint64_t start = GlobalTimerNs();
     for (;;) {
         uint32_t seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-        if (static_cast<int32_t>(seen - epoch) >= 0) break;  // steps only grow (wrap-around safe)
+        if (static_cast<int32_t>(seen - e) >= 0) break;  // steps only grow (wrap-around safe)
         if (GlobalTimerNs() - start > kWaitBudgetNs) { ReportTimeout(status, 40, r); break; }
         __nanosleep(100);
     }

@@ -130,7 +130,9 @@ class PeerGather:
 
     def sync(self, stream) -> None:
         """Signals this step to every rank and waits (on the stream) for theirs."""
-        if self.lib.fth_b200_gather_sync(self.flags, self._world, self._rank, self.epoch & 0xffffffff, stream) != 0:
+        # step numbers are kept on the device (epoch 0), which makes the step replayable from a CUDA graph; the host
+        # counter only picks the buffer parity
+        if self.lib.fth_b200_gather_sync(self.flags, self._world, self._rank, 0, stream) != 0:
             raise RuntimeError("fth_b200_gather_sync failed")
 
     def close(self) -> None:
