@@ -117,6 +117,18 @@ int Dispatch(int variant, int dtype, const LinearArgs& args, const Fp8Epilogue& 
     }
 }
 
+// Scratch the kernel family that will run needs: AUTO takes the tensor-core kernels whenever they support the shape
+// (they never fall back to the TMA-ring GEMV then), so only their need counts.
+size_t WorkspaceFor(int variant, int dtype, const LinearArgs& args) {
+    const bool tc = Tcgen05Supported(dtype, args);
+    const size_t tc_bytes = tc ? Tcgen05ScratchBytes(dtype, args) : 0;
+    const size_t stream_bytes = StreamSupported(dtype, args) ? StreamScratchBytes(dtype, args) : 0;
+    if (variant == FTH_B200_VARIANT_TCGEN05) return tc_bytes;
+    if (variant == FTH_B200_VARIANT_STREAM) return stream_bytes;
+    if (variant == FTH_B200_VARIANT_AUTO) return tc ? tc_bytes : stream_bytes;
+    return 0;
+}
+
 // Peer replicas of the output: byte distance from the local output to each peer's copy.
 template <typename Desc>
 int BuildPeers(const Desc* d, PeerOut* peers) {
@@ -207,9 +219,7 @@ extern "C" size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_
     if (ValidateFp8(d) != FTH_B200_OK) return 0;
     LinearArgs args; Fp8Epilogue fe;
     BuildFp8(d, &args, &fe);
-    const size_t a = StreamSupported(d->dtype, args) ? StreamScratchBytes(d->dtype, args) : 0;
-    const size_t b = Tcgen05Supported(d->dtype, args) ? Tcgen05ScratchBytes(d->dtype, args) : 0;
-    return a > b ? a : b;
+    return WorkspaceFor(d->variant, d->dtype, args);
 }
 
 extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_stream_t stream) {
@@ -236,9 +246,7 @@ extern "C" size_t fth_b200_int8_linear_workspace_bytes(const fth_b200_int8_linea
     if (ValidateInt8(d) != FTH_B200_OK) return 0;
     LinearArgs args; Int8Epilogue ie;
     BuildInt8(d, &args, &ie);
-    const size_t a = StreamSupported(FTH_B200_INT8, args) ? StreamScratchBytes(FTH_B200_INT8, args) : 0;
-    const size_t b = Tcgen05Supported(FTH_B200_INT8, args) ? Tcgen05ScratchBytes(FTH_B200_INT8, args) : 0;
-    return a > b ? a : b;
+    return WorkspaceFor(d->variant, FTH_B200_INT8, args);
 }
 
 extern "C" int fth_b200_int8_linear(const fth_b200_int8_linear_desc* d, fth_b200_stream_t stream) {

@@ -54,9 +54,28 @@ def _conv(torch):
     assert B.last_variant() == "conv_tcgen05"
 
 
-@pytest.mark.parametrize("case", ["gemv_m1_fp8", "dense_m4096_fp8", "dense_m4096_int8", "conv_c3"])
+def _decode_projection(torch):
+    """Config-4 projection (hidden 1024 -> intermediate 3584, FP8 E5M2, BF16 in and out) on the single-launch cluster
+    kernel: 40 different weights (147 MB, more than L2) in turn, then one more round for the capture."""
+    k, n = 1024, 3584
+    a = torch.randn((1, k), device="cuda").to(torch.bfloat16)
+    out = torch.empty((1, n), dtype=torch.bfloat16, device="cuda")
+    weights = [torch.randint(0, 120, (k, n), dtype=torch.uint8, device="cuda") for _ in range(40)]
+    descs = [B.fp8_linear_desc(dtype=B.E5M2, op=B.OP_MATMUL, m=1, k=k, n=n, a=a, w=w, out=out, a_scale=2.0 ** -9, w_scale=2.0 ** -20,
+                               out_scale=2.0 ** -9, a_dtype=B.BF16, out_dtype=B.BF16, weights_static=True) for w in weights]
+    assert B.lib().fth_b200_fp8_linear_workspace_bytes(C.byref(descs[0])) == 0  # no scratch on this path
+    for _ in range(2):
+        for d in descs:
+            assert B.lib().fth_b200_fp8_linear(C.byref(d), B.current_stream()) == B.OK
+    torch.cuda.synchronize()
+    assert B.last_variant() == "tcgen05"
+
+
+@pytest.mark.parametrize("case", ["gemv_m1_fp8", "dense_m4096_fp8", "dense_m4096_int8", "conv_c3", "decode_projection"])
 def test_profile_case(cuda, case):
-    if case == "gemv_m1_fp8":
+    if case == "decode_projection":
+        _decode_projection(cuda)
+    elif case == "gemv_m1_fp8":
         _linear(cuda, "fp8", 1)
     elif case == "dense_m4096_fp8":
         _linear(cuda, "fp8", 4096)
