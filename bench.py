@@ -404,7 +404,7 @@ def run_gpu_arm(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one tcgen05 GEMV launch on the bench workload, from the ncu
 # capture summarised in profiles/ (per launch, bytes).
-TRAFFIC_BYTES_PER_LAUNCH = 240180224
+TRAFFIC_BYTES_PER_LAUNCH = 239648512
 
 
 def extra_measurements(torch, B, dev, peaks, fp8_call, int8_call, stream, sa, out_scale, w, sw):
