@@ -217,16 +217,9 @@ extern "C" int fth_b200_plan_run(fth_b200_plan* p, const void* host_in, void* ho
     if (!p || !host_in || !host_out) return FTH_B200_ERR_INVALID;
     auto stream = static_cast<cudaStream_t>(stream_);
     if (cudaMemcpyAsync(p->in.ptr, host_in, static_cast<size_t>(p->in_bytes), cudaMemcpyHostToDevice, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
-    // A result buffer in pinned (device-mapped) host memory is written by the linear kernels' own epilogue, as a
-    // second copy of the output: no device-to-host copy is queued behind them.
+    // (Writing a pinned result buffer straight from the kernels' epilogue, as a second copy of the output, was
+    // measured: it saves the copy below and costs the same again in the reduce pass, whose stores then cross PCIe.)
     void* mirror = nullptr;
-    if (p->kind != Kind::kInt8Conv) {
-        cudaPointerAttributes attr;
-        if (cudaPointerGetAttributes(&attr, host_out) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr)
-            mirror = attr.devicePointer;
-        else
-            (void)cudaGetLastError();
-    }
     const int rc = LaunchPlan(p, p->in.ptr, p->out.ptr, mirror, stream_);
     if (rc != FTH_B200_OK) return rc;
     if (!mirror && cudaMemcpyAsync(host_out, p->out.ptr, static_cast<size_t>(p->out_bytes), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;

@@ -1,6 +1,5 @@
 """Host-buffer plans (fth_b200_plan_*): the convenience layer bench.py's end-to-end figure goes through.  The result
-must be the bytes of the direct device call, whether the host result buffer is pageable (copied back) or pinned
-(written by the kernels themselves as a second copy of the output)."""
+must be the bytes of the direct device call, for pageable and for pinned host buffers."""
 import numpy as np
 import pytest
 
