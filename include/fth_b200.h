@@ -126,6 +126,12 @@ typedef struct {
 } fth_b200_fp8_linear_desc;
 
 int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t stream);
+/* The same linear plus greedy selection over each output row, fused into the epilogue: indices[row] receives the column
+ * of the largest decoded output value (NaN codes skipped, ties to the lowest column, -1 when a row has no candidate) —
+ * what an ArgMax node behind the MatMul would return, with the rule of the reference's fused BF16 lm-head kernel
+ * (src/kernel/cuda/qwen_gemm_argmax.cu:55-64), which has no FP8 counterpart.  The output is written as usual.  Decode-sized
+ * shapes on the tensor-core kernels only (FTH_B200_ERR_UNSUPPORTED otherwise; run the linear and an ArgMax node then). */
+int fth_b200_fp8_linear_argmax(const fth_b200_fp8_linear_desc* desc, int64_t* indices, fth_b200_stream_t stream);
 /* Capability check only (what Supports() calls): 0 if fth_b200_fp8_linear would run this descriptor. */
 int fth_b200_fp8_linear_supported(const fth_b200_fp8_linear_desc* desc);
 size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc);

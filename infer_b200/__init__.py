@@ -32,7 +32,7 @@ EXPORTS = [
     "fth_b200_plan_run", "fth_b200_plan_launch", "fth_b200_plan_input_bytes", "fth_b200_plan_output_bytes",
     "fth_b200_plan_destroy",
     "fth_b200_peer_buffer_create", "fth_b200_peer_buffer_open", "fth_b200_peer_buffer_close", "fth_b200_peer_buffer_destroy",
-    "fth_b200_gather_sync",
+    "fth_b200_gather_sync", "fth_b200_fp8_linear_argmax",
 ]
 
 

@@ -162,6 +162,7 @@ void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* 
     args->zero_points = 0;
     args->w_static = d->weights_static != 0;
     args->peers.count = 0;
+    args->argmax_keys = nullptr;
     fe->ab_scale = d->w_channel_scales ? d->a_scale : d->a_scale * d->w_scale;
     fe->w_channel_scales = d->w_channel_scales;
     fe->is_gemm = d->op == FTH_B200_OP_GEMM;
@@ -184,6 +185,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
     args->zero_points = (d->a_zp != 0 || d->w_zps != nullptr) ? 1 : 0;
     args->w_static = d->weights_static != 0;
     args->peers.count = 0;
+    args->argmax_keys = nullptr;
     ie->w_scales = d->w_scales; ie->w_zps = d->w_zps; ie->per_channel = d->w_params != 1;
     ie->a_scale = d->a_scale; ie->a_zp = d->a_zp; ie->out_scale = d->out_scale; ie->out_zp = d->out_zp;
     ie->bias = d->bias; ie->bias_mode = d->bias_mode;
@@ -231,6 +233,26 @@ extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_s
     if (BuildPeers(d, &args.peers) != FTH_B200_OK) return FTH_B200_ERR_INVALID;
     return Run(PickVariant(d->variant, d->dtype, args, d->workspace, d->workspace_bytes), d->dtype, args, fe, ie,
                d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fth_b200_fp8_linear_argmax(const fth_b200_fp8_linear_desc* d, int64_t* indices, fth_b200_stream_t stream_) {
+    ClearStaleError();
+    const int rc = ValidateFp8(d);
+    if (rc != FTH_B200_OK) return rc;
+    if (indices == nullptr || reinterpret_cast<uintptr_t>(indices) % 8 != 0) return FTH_B200_ERR_INVALID;
+    auto stream = static_cast<cudaStream_t>(stream_);
+    LinearArgs args; Fp8Epilogue fe; Int8Epilogue ie = {};
+    BuildFp8(d, &args, &fe);
+    if (BuildPeers(d, &args.peers) != FTH_B200_OK) return FTH_B200_ERR_INVALID;
+    const int variant = PickVariant(d->variant, d->dtype, args, d->workspace, d->workspace_bytes);
+    if (variant < 0) return variant;
+    // only the decode-sized tensor-core kernels carry the fused selection (their epilogue sees every output once)
+    if (variant != FTH_B200_VARIANT_TCGEN05 || !Tcgen05StoresToPeers(d->dtype, args, fe, ie)) return FTH_B200_ERR_UNSUPPORTED;
+    if (cudaMemsetAsync(indices, 0, static_cast<size_t>(d->m) * 8, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    args.argmax_keys = reinterpret_cast<unsigned long long*>(indices);
+    const int run = Run(variant, d->dtype, args, fe, ie, d->workspace, d->workspace_bytes, stream);
+    if (run != FTH_B200_OK) return run;
+    return LaunchArgmaxFinalize(args.argmax_keys, d->m, stream);
 }
 
 extern "C" int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* d) {

@@ -24,6 +24,7 @@ struct LinearArgs {
     int zero_points; // INT8: activation or weight zero point is non-zero
     int w_static;    // no earlier work in the stream writes the weights: they may be read before it has finished
     PeerOut peers;   // replicas of the output on other GPUs (count 0: none)
+    unsigned long long* argmax_keys;  // [m] running (value, index) maxima of each output row, or null
 };
 
 int LaunchLinearSimt(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
@@ -52,6 +53,9 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& args, const Fp8Epilogue& fe
                         size_t scratch_bytes, cudaStream_t stream);
 // True when that launch writes the peer replicas from its own epilogue (otherwise the caller copies the block over).
 bool Tcgen05StoresToPeers(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie);
+
+// Turns the packed (value, index) keys a fused argmax left in `keys` into int64 indices in place (-1: no candidate).
+int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, cudaStream_t stream);
 
 // Copies the [m, n] output block (elements of `elem_bytes`, row stride ldo elements) to every peer replica.
 int LaunchPeerCopy(const void* out, int64_t m, int64_t n, int64_t ldo, int elem_bytes, const PeerOut& peers, cudaStream_t stream);

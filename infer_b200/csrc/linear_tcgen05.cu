@@ -579,6 +579,39 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     }
 }
 
+// ---- fused greedy selection (argmax over each output row) ---------------------------------------------------
+// A candidate is one 64-bit key: the value mapped to an order-preserving 32-bit pattern in the high word, the
+// complemented column in the low word — the largest key is the largest value and, among equals, the lowest column.
+// Key 0 means "no candidate" (a NaN code).  -0 counts as +0, as a floating-point comparison would have it.
+template <bool INT8>
+__device__ __forceinline__ unsigned long long ArgmaxKey(int e4m3, uint32_t code, int64_t column) {
+    float v;
+    if constexpr (INT8) v = static_cast<float>(static_cast<int8_t>(code));
+    else v = e4m3 ? Decode<FTH_B200_FP8E4M3>(static_cast<uint8_t>(code)) : Decode<FTH_B200_FP8E5M2>(static_cast<uint8_t>(code));
+    if (v != v) return 0ull;
+    if (v == 0.0f) v = 0.0f;
+    const uint32_t bits = __float_as_uint(v);
+    const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    return (static_cast<unsigned long long>(ordered) << 32) | (0xffffffffu - static_cast<uint32_t>(column));
+}
+// Called by all 32 lanes of a warp: row < 0 marks a lane without a candidate.  Lanes of one row are combined with
+// shuffles so that a warp costs one atomic; a warp that straddles rows falls back to one atomic per lane.
+__device__ __forceinline__ void ArgmaxUpdate(unsigned long long* keys, int row, unsigned long long key) {
+    const int top = __reduce_max_sync(0xffffffffu, row);
+    const bool one_row = __all_sync(0xffffffffu, row == top || row < 0);
+    if (one_row) {
+        if (row < 0) key = 0ull;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, offset);
+            key = other > key ? other : key;
+        }
+        if ((threadIdx.x & 31) == 0 && top >= 0 && key != 0ull) atomicMax(&keys[top], key);
+    } else if (row >= 0 && key != 0ull) {
+        atomicMax(&keys[row], key);
+    }
+}
+
 // Stores `value` at `dst` and at the same place in every peer replica of the output.
 template <typename T>
 __device__ __forceinline__ void StoreWithPeers(const PeerOut& peers, T* dst, T value) {
@@ -588,14 +621,14 @@ __device__ __forceinline__ void StoreWithPeers(const PeerOut& peers, T* dst, T v
 
 // Epilogue of four consecutive output channels p4 .. p4+3 of activation row q (swapped tiling), given their
 // complete accumulators: the vectorised fast path or the generic per-element store.
+// Returns the four output codes (channel p4 in the low byte) on the direct path, which the fused argmax reads.
 template <bool INT8>
-__device__ __forceinline__ void FinishFour(const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, int64_t q,
-                                           int64_t p4, const uint32_t (&v)[4], bool store = true) {
+__device__ __forceinline__ uint32_t FinishFour(const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, int64_t q,
+                                               int64_t p4, const uint32_t (&v)[4]) {
     if (!p.fast4) {
-        if (!store) return;
         for (int i = 0; i < 4; ++i)
             if (p4 + i < p.p_total) StoreOne<INT8>(fe, ie, p.e4m3, q, p4 + i, v[i]);
-        return;
+        return 0;
     }
     uint32_t b[4];
     if constexpr (INT8) {
@@ -621,10 +654,6 @@ __device__ __forceinline__ void FinishFour(const TcParams& p, const Fp8Epilogue&
             const float2 d23 = p.e4m3 ? DecodePair<FTH_B200_FP8E4M3>(static_cast<uint16_t>(hi)) : DecodePair<FTH_B200_FP8E5M2>(static_cast<uint16_t>(hi));
             const float o[4] = {__fmul_rn(d01.x, fe.out_scale), __fmul_rn(d01.y, fe.out_scale), __fmul_rn(d23.x, fe.out_scale), __fmul_rn(d23.y, fe.out_scale)};
             const bool whole = p4 + 3 < p.p_total;
-            if (!store) {
-                asm volatile("" ::"f"(o[0]), "f"(o[1]), "f"(o[2]), "f"(o[3]));  // keep the dry pass's arithmetic
-                return;
-            }
             if (fe.out_dtype == FTH_B200_BF16) {
                 uint16_t* dst = static_cast<uint16_t*>(fe.out) + q * fe.ldo + p4;
                 if (whole && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
@@ -640,12 +669,8 @@ __device__ __forceinline__ void FinishFour(const TcParams& p, const Fp8Epilogue&
                 if (whole && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) StoreWithPeers(p.args.peers, reinterpret_cast<float4*>(dst), make_float4(o[0], o[1], o[2], o[3]));
                 else { for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) StoreWithPeers(p.args.peers, dst + i, o[i]); }
             }
-            return;
+            return b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
         }
-    }
-    if (!store) {
-        asm volatile("" ::"r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]));
-        return;
     }
     const int64_t ldo = INT8 ? ie.ldo : fe.ldo;
     uint8_t* dst = static_cast<uint8_t*>(INT8 ? ie.out : fe.out) + q * ldo + p4;
@@ -654,6 +679,7 @@ __device__ __forceinline__ void FinishFour(const TcParams& p, const Fp8Epilogue&
     } else {
         for (int i = 0; i < 4 && p4 + i < p.p_total; ++i) StoreWithPeers(p.args.peers, dst + i, static_cast<uint8_t>(b[i]));
     }
+    return b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
 }
 
 
@@ -667,12 +693,13 @@ __global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t groups = p.p_pad / 4;
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    if (idx >= groups * p.q_total) return;
     const int64_t q = idx / groups;
     const int64_t p4 = (idx % groups) * 4;
-    if (p4 >= p.p_total) return;
+    const bool valid = idx < groups * p.q_total && p4 < p.p_total;
+    if (!valid && p.args.argmax_keys == nullptr) return;
     const uint4* part = static_cast<const uint4*>(p.scratch);
-    uint32_t v[4];
+    uint32_t v[4] = {0, 0, 0, 0};
+    if (valid) {
     if constexpr (INT8) {
         int32_t sum[4] = {0, 0, 0, 0};
         uint4 t[8];
@@ -700,7 +727,18 @@ __global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue
         }
         for (int i = 0; i < 4; ++i) v[i] = __float_as_uint(sum[i]);
     }
-    FinishFour<INT8>(p, fe, ie, q, p4, v);
+    }
+    const uint32_t codes = valid ? FinishFour<INT8>(p, fe, ie, q, p4, v) : 0u;
+    if (p.args.argmax_keys != nullptr) {  // every lane of the warp is here
+        unsigned long long key = 0ull;
+        for (int i = 0; i < 4; ++i) {
+            if (valid && p4 + i < p.p_total) {
+                const unsigned long long k = ArgmaxKey<INT8>(p.e4m3, (codes >> (8 * i)) & 0xffu, p4 + i);
+                key = k > key ? k : key;
+            }
+        }
+        ArgmaxUpdate(p.args.argmax_keys, valid ? static_cast<int>(q) : -1, key);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -781,28 +819,31 @@ __device__ __forceinline__ uint32_t ConvertFourRaw(const LinearArgs& a, const In
 }
 
 // Epilogue of one output (activation row q, channel n) from its complete accumulator.
+// Returns the output code on the direct path (read by the fused argmax).
 template <bool INT8>
-__device__ __forceinline__ void FinishOne(const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, int64_t q, int64_t n,
-                                          uint32_t raw) {
-    if (!p.fast4) { StoreOne<INT8>(fe, ie, p.e4m3, q, n, raw); return; }
+__device__ __forceinline__ uint32_t FinishOne(const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, int64_t q, int64_t n,
+                                              uint32_t raw) {
+    if (!p.fast4) { StoreOne<INT8>(fe, ie, p.e4m3, q, n, raw); return 0; }
     if constexpr (INT8) {
         const double sd = static_cast<double>(ie.a_scale) * static_cast<double>(ie.w_scales[ie.per_channel ? n : 0]);
         const double so_d = static_cast<double>(ie.out_scale);
         const double md = sd / so_d;
-        StoreWithPeers(p.args.peers, static_cast<int8_t*>(ie.out) + q * ie.ldo + n,
-                       RequantFast(static_cast<int32_t>(raw), static_cast<float>(md), md, sd, so_d, ie.out_zp));
+        const int8_t r = RequantFast(static_cast<int32_t>(raw), static_cast<float>(md), md, sd, so_d, ie.out_zp);
+        StoreWithPeers(p.args.peers, static_cast<int8_t*>(ie.out) + q * ie.ldo + n, r);
+        return static_cast<uint8_t>(r);
     } else {
         const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
         const float t = __fmul_rn(__uint_as_float(raw), mult);
         const float y = p.out_inv != 0.0f ? __fmul_rn(t, p.out_inv) : __fdiv_rn(t, fe.out_scale);
         const uint8_t code = p.e4m3 ? Encode<FTH_B200_FP8E4M3>(y) : Encode<FTH_B200_FP8E5M2>(y);
         const int64_t o = q * fe.ldo + n;
-        if (fe.out_dtype == 0) { StoreWithPeers(p.args.peers, static_cast<uint8_t*>(fe.out) + o, code); return; }
+        if (fe.out_dtype == 0) { StoreWithPeers(p.args.peers, static_cast<uint8_t*>(fe.out) + o, code); return code; }
         // fused Cast behind the MatMul: the decoded code times the output scale, as BF16 or FP32
         const float d = p.e4m3 ? Decode<FTH_B200_FP8E4M3>(code) : Decode<FTH_B200_FP8E5M2>(code);
         const float v = __fmul_rn(d, fe.out_scale);
         if (fe.out_dtype == FTH_B200_BF16) StoreWithPeers(p.args.peers, static_cast<uint16_t*>(fe.out) + o, EncodeBf16Cast(v));
         else StoreWithPeers(p.args.peers, static_cast<float*>(fe.out) + o, v);
+        return code;
     }
 }
 
@@ -1004,29 +1045,38 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 
         // One output per thread and round: channel r of this CTA's rows (fastest, so a warp stores consecutive
         // channels) of activation row q.  The chunks are added in chunk order, as the two-kernel path adds them.
-        for (int item = et; delivered && item < (m << lshift); item += 128) {
+        const int total = m << lshift;
+        for (int base = 0; base < total; base += 128) {  // the same trip count in every lane: the argmax step below shuffles
+            const int item = base + et;
+            const bool valid = delivered && item < total;
             const int q = item >> lshift;
             const int r = item & (rows_per_cta - 1);
-            uint32_t t[8];
-#pragma unroll
-            for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? exchange[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
-            uint32_t acc;
-            if constexpr (INT8) {
-                int32_t sum = 0;
-#pragma unroll
-                for (int ss = 0; ss < 8; ++ss) sum += static_cast<int32_t>(t[ss]);
-                acc = static_cast<uint32_t>(sum);
-            } else {
-                float sum = 0.0f;
-#pragma unroll
-                for (int ss = 0; ss < 8; ++ss) {
-                    if (ss < p.split) sum += __uint_as_float(t[ss]);  // no zero is ever added: it could flip a -0
-                }
-                acc = __float_as_uint(sum);
-            }
-            if (et == 0) FTH_TRACE(14);
             const int64_t n = static_cast<int64_t>(tile) * kBlockP + (static_cast<int64_t>(rank) << lshift) + r;
-            if (n < p.p_total) FinishOne<INT8>(p, fe, ie, q, n, acc);
+            uint32_t code = 0;
+            bool stored = false;
+            if (valid) {
+                uint32_t t[8];
+#pragma unroll
+                for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? exchange[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
+                uint32_t acc;
+                if constexpr (INT8) {
+                    int32_t sum = 0;
+#pragma unroll
+                    for (int ss = 0; ss < 8; ++ss) sum += static_cast<int32_t>(t[ss]);
+                    acc = static_cast<uint32_t>(sum);
+                } else {
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int ss = 0; ss < 8; ++ss) {
+                        if (ss < p.split) sum += __uint_as_float(t[ss]);  // no zero is ever added: it could flip a -0
+                    }
+                    acc = __float_as_uint(sum);
+                }
+                if (et == 0) FTH_TRACE(14);
+                if (n < p.p_total) { code = FinishOne<INT8>(p, fe, ie, q, n, acc); stored = true; }
+            }
+            if (p.args.argmax_keys != nullptr)
+                ArgmaxUpdate(p.args.argmax_keys, stored ? q : -1, stored ? ArgmaxKey<INT8>(p.e4m3, code, n) : 0ull);
         }
     }
     if (warp < 2) {

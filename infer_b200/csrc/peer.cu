@@ -58,7 +58,20 @@ __global__ void GatherSyncKernel(FlagPtrs flags, int world, int self, uint32_t e
     }
 }
 
+__global__ void ArgmaxFinalizeKernel(unsigned long long* keys, int64_t m) {
+    const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i >= m) return;
+    const unsigned long long key = keys[i];
+    reinterpret_cast<long long*>(keys)[i] = key == 0 ? -1ll : static_cast<long long>(0xffffffffu - static_cast<uint32_t>(key & 0xffffffffu));
+}
+
 }  // namespace
+
+int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, cudaStream_t stream) {
+    ArgmaxFinalizeKernel<<<static_cast<unsigned>((m + 127) / 128), 128, 0, stream>>>(keys, m);
+    NoteLaunch("argmax_finalize");
+    return CheckLaunch();
+}
 
 int LaunchPeerCopy(const void* out, int64_t m, int64_t n, int64_t ldo, int elem_bytes, const PeerOut& peers, cudaStream_t stream) {
     if (peers.count <= 0 || m <= 0 || n <= 0) return FTH_B200_OK;
