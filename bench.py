@@ -221,10 +221,13 @@ def run_gpu_arm(args):
     n_sets = max(2, -(-2 * L2_BYTES // (K * n_local)))
     weights, w_scales = [], []
     for i in range(n_sets):
-        w_full, sw = synth(torch, (K, N), 0.02, SEED + 10 * i, dev)
-        weights.append(w_full[:, n0:n1].contiguous())
+        if world == 1:
+            w_part, sw = synth(torch, (K, N), 0.02, SEED + 10 * i, dev)
+        else:  # this rank's columns of weight set i, drawn directly (the same distribution; no 235 MB detour per set)
+            w_part, sw = synth(torch, (K, n_local), 0.02, SEED + 10 * i + 1000 * (rank + 1), dev)
+        weights.append(w_part.contiguous())
         w_scales.append(sw)
-        del w_full
+        del w_part
     a_dev, sa = synth(torch, (1, K), 1.0, SEED + 1, dev)
     local_out = torch.zeros((1, width), dtype=torch.uint8, device=dev)
 
