@@ -162,6 +162,10 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the reference kernel should have the host cores it can use
+    # (its own cap is 4 threads for this path), so the variable is lifted before any OpenMP runtime is loaded
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import torch
     run, info = cpu_reference_kernel(torch, 1)
     for _ in range(max(args.warmup, 1)):
