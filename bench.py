@@ -250,27 +250,36 @@ def run_gpu_arm(args):
     if world > 1:
         from infer_b200.sharded import PeerGather, ShardedLinear, forward_peer
         from infer_b200.sharded import point_at_step_buffers
-        gather = PeerGather(B.lib(), dist, world, rank, 1, N)
         shard = ShardedLinear(N, world, rank, compute=None, dist=dist)
-        # per weight set, one descriptor per step parity, pointed at that parity's buffers once
-        prepared = [tuple(point_at_step_buffers(shard, gather, type(d).from_buffer_copy(d), parity) for parity in (0, 1)) for d, _ in descs]
         call_desc = lambda desc, s: fp8_call(C.byref(desc), s)  # noqa: E731
+        try:
+            gather = PeerGather(B.lib(), dist, world, rank, 1, N)  # raises on every rank or on none
+            # per weight set, one descriptor per step parity, pointed at that parity's buffers once
+            prepared = [tuple(point_at_step_buffers(shard, gather, type(d).from_buffer_copy(d), parity) for parity in (0, 1)) for d, _ in descs]
+        except RuntimeError as exc:
+            # no peer mapping on this box: the gather falls back to one NCCL all-gather of the 1-byte outputs
+            gather = None
+            if rank == 0:
+                print(f"[bench] {exc}; using NCCL all_gather_into_tensor", file=sys.stderr)
+    nccl_gathered = torch.zeros((world, width), dtype=torch.uint8, device=dev) if world > 1 and gather is None else None
 
     def step():
         i = counter[0] % n_sets
         counter[0] += 1
-        if world > 1:
+        if gather is not None:
             forward_peer(shard, gather, descs[i][0], call_desc, stream, prepared[i])
             return
         rc = fp8_call(C.byref(descs[i][0]), stream)
         if rc != 0:
             raise RuntimeError(f"fth_b200_fp8_linear failed: {rc}")
+        if world > 1:
+            dist.all_gather_into_tensor(nccl_gathered, local_out)
 
     # N > 1: a sharded step is a few microseconds of GPU time, less than the host needs to issue it, so the steps are
     # replayed from a CUDA graph of one full rotation (every weight set, both buffer parities); the gather's step
     # numbers live on the device for that.  Steps that do not fill a whole rotation are issued one by one.
     timed_step, steps_per_call = step, 1
-    if world > 1:
+    if gather is not None:
         rotation = n_sets * (2 if n_sets % 2 else 1)  # an even number of steps: the buffer parity repeats
         for _ in range(rotation):
             step()
@@ -279,18 +288,30 @@ def run_gpu_arm(args):
         side = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
         main_stream = stream
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-                for _ in range(rotation):
-                    step()
+        epoch_before, counter_before = gather.epoch, counter[0]
+        captured = True
+        try:
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+                    for _ in range(rotation):
+                        step()
+        except Exception as exc:  # capture is an optimisation of the issue rate, never a requirement
+            captured = False
+            gather.epoch, counter[0] = epoch_before, counter_before
+            print(f"[bench] rank {rank}: CUDA-graph capture failed ({type(exc).__name__}: {exc}); issuing steps one by one", file=sys.stderr)
         stream = main_stream
+        verdict = torch.tensor([1 if captured else 0], device=dev)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)  # all ranks replay, or none does
+        if int(verdict.item()) == 1:
+            # the capture ran the host-side counters forward without running a step: put them back
+            gather.epoch, counter[0] = epoch_before, counter_before
 
-        def replay():
-            graph.replay()
-            gather.epoch += rotation
-            counter[0] += rotation
-        timed_step, steps_per_call = replay, rotation
+            def replay():
+                graph.replay()
+                gather.epoch += rotation
+                counter[0] += rotation
+            timed_step, steps_per_call = replay, rotation
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -356,8 +377,14 @@ def run_gpu_arm(args):
         a_stage.copy_(a_host, non_blocking=True)
         d, _ = e2e_descs[pc[0] % n_sets]
         pc[0] += 1
-        parity = forward_peer(shard, gather, d, lambda desc, s: fp8_call(C.byref(desc), s), stream)
-        full_host.copy_(gather.view(torch, parity), non_blocking=True)
+        if gather is not None:
+            parity = forward_peer(shard, gather, d, call_desc, stream)
+            full_host.copy_(gather.view(torch, parity), non_blocking=True)
+        else:
+            if fp8_call(C.byref(d), stream) != 0:
+                raise RuntimeError("fth_b200_fp8_linear failed")
+            dist.all_gather_into_tensor(nccl_gathered, local_out)
+            full_host.copy_(nccl_gathered.view(1, -1)[:, :N], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = min(args.steps, 500)
@@ -385,7 +412,7 @@ def run_gpu_arm(args):
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"C5 FP8-E4M3 Linear M=1 K={K} N={N}" + (f", N column-sharded over {world} GPUs, outputs stored to all ranks over NVLink (peer stores + flag wait)" if world > 1 else ""),
+            "config": {"workload": f"C5 FP8-E4M3 Linear M=1 K={K} N={N}" + ((f", N column-sharded over {world} GPUs, " + ("outputs stored to all ranks over NVLink (peer stores + flag wait)" if gather is not None else "NCCL all-gather")) if world > 1 else ""),
                        "l2": f"inputs larger than L2: {n_sets} weight sets of {K * n_local / 1e6:.0f} MB rotated", "kernel": variant,
                        "algorithmic_bytes_per_step": bytes_step, "seed": SEED},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",

@@ -94,21 +94,31 @@ class PeerGather:
         total = 2 * self.block + 256  # two output buffers, then uint32 flags[world]
         own = C.c_void_p()
         handle = (C.c_ubyte * 64)()
-        if lib.fth_b200_peer_buffer_create(C.c_size_t(total), C.byref(own), handle) != 0:
-            raise RuntimeError("fth_b200_peer_buffer_create failed")
-        handles = [None] * world
+        created = lib.fth_b200_peer_buffer_create(C.c_size_t(total), C.byref(own), handle) == 0
+        # every rank takes part in every exchange, whatever happened locally, so that a failure on one rank ends in the
+        # same exception on all of them instead of a collective that never completes
+        handles = [bytes(handle) if created else None] * world
         if world > 1:
-            dist.all_gather_object(handles, bytes(handle))
+            dist.all_gather_object(handles, bytes(handle) if created else None)
         self.base = [0] * world
-        self.base[rank] = own.value
-        for r in range(world):
-            if r == rank:
-                continue
-            ptr = C.c_void_p()
-            peer_handle = (C.c_ubyte * 64).from_buffer_copy(handles[r])
-            if lib.fth_b200_peer_buffer_open(peer_handle, C.byref(ptr)) != 0:
-                raise RuntimeError(f"fth_b200_peer_buffer_open failed for rank {r}")
-            self.base[r] = ptr.value
+        self.base[rank] = own.value if created else 0
+        opened = created and all(h is not None for h in handles)
+        if opened:
+            for r in range(world):
+                if r == rank:
+                    continue
+                ptr = C.c_void_p()
+                peer_handle = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+                if lib.fth_b200_peer_buffer_open(peer_handle, C.byref(ptr)) != 0:
+                    opened = False
+                    break
+                self.base[r] = ptr.value
+        verdicts = [opened] * world
+        if world > 1:
+            dist.all_gather_object(verdicts, opened)
+        if not all(verdicts):
+            self.close()
+            raise RuntimeError("peer-mapped output buffers are not available on this box (CUDA IPC create / open failed on some rank)")
         self.flags = (C.c_void_p * world)(*[b + 2 * self.block for b in self.base])
         self._world, self._rank = C.c_int32(world), C.c_int32(rank)
         self.epoch = 0
