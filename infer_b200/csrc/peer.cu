@@ -29,6 +29,11 @@ struct FlagPtrs { uint32_t* rank_flags[kMaxPeers + 1]; };
 // The kernels whose stores this publishes ran earlier on the same stream, so they are complete; the release at
 // system scope orders them before the flag for a peer that acquires it.
 __global__ void GatherSyncKernel(FlagPtrs flags, int world, int self, uint32_t epoch, int* status) {
+    // Launched with programmatic stream serialization: the next kernel in the stream (the next step's linear, which
+    // writes the other pair of buffers) may set up and fetch static weights while this one waits for the peers; this
+    // kernel itself starts only after the kernels whose stores it publishes have completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ uint32_t step;
     if (threadIdx.x == 0) {
         // epoch 0: the step number lives on the device (slot [world] of this rank's own flag array) and grows by one
@@ -123,7 +128,17 @@ extern "C" int fth_b200_gather_sync(void* const* rank_flags, int32_t world, int3
         if (rank_flags[r] == nullptr) return FTH_B200_ERR_INVALID;
         flags.rank_flags[r] = static_cast<uint32_t*>(rank_flags[r]);
     }
-    GatherSyncKernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(flags, world, rank, epoch, DeviceStatusPtr());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = static_cast<cudaStream_t>(stream_);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int world_arg = world, rank_arg = rank;
+    if (cudaLaunchKernelEx(&cfg, GatherSyncKernel, flags, world_arg, rank_arg, epoch, DeviceStatusPtr()) != cudaSuccess) return FTH_B200_ERR_CUDA;
     NoteLaunch("gather_sync");
     return CheckLaunch();
 }
