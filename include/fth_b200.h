@@ -106,10 +106,12 @@ typedef struct {
     float a_scale, w_scale, bias_scale, out_scale;
     const float* w_channel_scales;
     float alpha, beta;
-    /* Device scratch for the split-K partial sums of VARIANT_STREAM (fth_b200_fp8_linear_workspace_bytes).
-     * It must be zero-filled once after allocation; every call leaves its counters zero again.  Calls that
-     * share a workspace must not overlap on the GPU.  May be null: the library then picks kernels that
-     * need no scratch. */
+    /* Device scratch (256-byte aligned) of the kernel family `variant` selects: split-K partial sums and, for a fused
+     * Cast / QuantizeLinear that runs as a separate pass, the 8-bit activations.  fth_b200_fp8_linear_workspace_bytes
+     * says how much that family needs for this descriptor — 0 for shapes the single-launch cluster kernel and the dense
+     * kernel take.  It must be zero-filled once after allocation (VARIANT_STREAM keeps arrival counters in it and leaves
+     * them zero again).  Calls that share a workspace must not overlap on the GPU.  May be null: the library then picks
+     * kernels that need no scratch. */
     void* workspace;
     size_t workspace_bytes;
     int32_t variant;      /* FTH_B200_VARIANT_* */
