@@ -1,0 +1,392 @@
+#include "linear_tc.cuh"
+
+// Optional phase timeline of CTA 0 in SM clocks (development aid, compiled out unless FTH_B200_TRACE is defined).
+#ifdef FTH_B200_TRACE
+__device__ unsigned long long g_trace[32];
+#define FTH_TRACE(i) do { if (blockIdx.x == 0) g_trace[i] = static_cast<unsigned long long>(clock64()); } while (0)
+extern "C" int fth_b200_trace_read(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : -1;
+}
+#else
+#define FTH_TRACE(i) do {} while (0)
+#endif
+
+
+namespace fth {
+namespace tc {
+namespace {
+
+// ---------------------------------------------------------------------------------------------------------
+// Decode-sized problems (M <= 32, one wave of CTAs): split-K inside a thread-block cluster.
+//
+// The S CTAs of a cluster work on the S K-chunks of one 128-channel weight tile, so S SMs pull the tile's bytes
+// at the same time (one SM alone draws ~35 bytes per clock through TMA, which is what bounds a small
+// projection).  Each CTA's accumulator leaves tensor memory once; its 128 rows are dealt out to the cluster's
+// CTAs through distributed shared memory (CTA o receives rows o*L .. o*L+L-1 of every chunk, L = 128 / cluster
+// size), and after one cluster barrier each CTA adds the chunks of its rows in chunk order — the order the
+// two-kernel path uses, so both give the same bits — and runs the epilogue.  No scratch, no second launch.
+//
+// A fused Cast / QuantizeLinear in front of the MatMul is done here as well: the epilogue warps, idle while the
+// weights stream, read the CTA's K-chunk of BF16 / FP16 / FP32 activations, convert, and write the 8-bit codes
+// into the swizzled operand tile that the MMA reads (generic-proxy writes, made visible with fence.proxy.async).
+// 8-bit activations arrive by TMA as before.  The activation chunk stays resident (kQBlocks blocks at most);
+// only the weight tile goes through the ring.
+// ---------------------------------------------------------------------------------------------------------
+template <int BQ>
+struct ClusterCfg {
+    static constexpr int kQBlocks = kClusterQBlocks;                       // K blocks of activations held per CTA
+    static constexpr int kQBytes = kQBlocks * BQ * kBlockK;  // 16 KB / 32 KB
+    static constexpr int kStages = BQ <= 16 ? 5 : 3;         // weight ring (16 KB per stage), upper limit
+    static constexpr int kMaxStages = 8;                     // barrier slots
+    static constexpr int kExchangeBytes = kBlockP * BQ * 4;  // partials of this CTA's rows, all chunks
+    static constexpr uint32_t kTmemCols = 32;
+    static constexpr int kThreads = 192;
+    static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kPBytes + kQBytes + kExchangeBytes + 256;
+    static int StagesFor(int64_t chunk_blocks) { return chunk_blocks < kStages ? static_cast<int>(chunk_blocks) : kStages; }
+    static size_t SmemFor(int64_t chunk_blocks) {
+        return 1024 + static_cast<size_t>(StagesFor(chunk_blocks)) * kPBytes + static_cast<size_t>(chunk_blocks) * BQ * kBlockK +
+               kExchangeBytes + 256;
+    }
+};
+
+// Four consecutive activation elements of a fused Cast (FP8) / QuantizeLinear (INT8) prologue.  The raw load and
+// the conversion are separate so that a thread can have several loads in flight before it converts the first.
+// `index` is a multiple of 4; `vec` says the base pointer is 16-byte aligned.
+__device__ __forceinline__ uint4 LoadFourRaw(const LinearArgs& a, int64_t index, bool vec) {
+    uint4 r = make_uint4(0, 0, 0, 0);
+    if (a.a_dtype == FTH_B200_FP32) {
+        const uint32_t* src = static_cast<const uint32_t*>(a.a) + index;
+        if (vec) r = *reinterpret_cast<const uint4*>(src);
+        else { r.x = src[0]; r.y = src[1]; r.z = src[2]; r.w = src[3]; }
+    } else {
+        const uint16_t* src = static_cast<const uint16_t*>(a.a) + index;
+        if (vec) { const uint2 t = *reinterpret_cast<const uint2*>(src); r.x = t.x; r.y = t.y; }
+        else { r.x = src[0] | (static_cast<uint32_t>(src[1]) << 16); r.y = src[2] | (static_cast<uint32_t>(src[3]) << 16); }
+    }
+    return r;
+}
+// Codes of the four elements, element 0 in the low byte.  `a_inv` is 1 / a_scale when that is exact (a power of
+// two: x * a_inv and x / a_scale are then the same correctly rounded value), else 0.
+template <bool INT8>
+__device__ __forceinline__ uint32_t ConvertFourRaw(const LinearArgs& a, const Int8Epilogue& ie, int e4m3, float a_inv, uint4 raw) {
+    float x[4];
+    if (a.a_dtype == FTH_B200_FP32) {
+        x[0] = __uint_as_float(raw.x); x[1] = __uint_as_float(raw.y); x[2] = __uint_as_float(raw.z); x[3] = __uint_as_float(raw.w);
+    } else if (a.a_dtype == FTH_B200_BF16) {
+        x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xffff0000u);
+        x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xffff0000u);
+    } else {
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+    }
+    if constexpr (INT8) {
+        uint32_t word = 0;
+        for (int i = 0; i < 4; ++i) word |= static_cast<uint32_t>(static_cast<uint8_t>(QuantizeValue(x[i], ie.a_scale, ie.a_zp))) << (8 * i);
+        return word;
+    } else {
+        float y[4];
+        // a NaN skips the divide, as in the stand-alone Cast kernel
+        if (a_inv != 0.0f) { for (int i = 0; i < 4; ++i) y[i] = (x[i] != x[i]) ? x[i] : __fmul_rn(x[i], a_inv); }
+        else { for (int i = 0; i < 4; ++i) y[i] = (x[i] != x[i]) ? x[i] : __fdiv_rn(x[i], a.a_scale); }
+        return EncodePair(e4m3, y[0], y[1]) | (EncodePair(e4m3, y[2], y[3]) << 16);
+    }
+}
+
+template <bool INT8, bool P_MN, int BQ>
+__global__ void __launch_bounds__(ClusterCfg<BQ>::kThreads, 2)
+LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, TcParams p,
+                    Fp8Epilogue fe, Int8Epilogue ie) {
+    using C = ClusterCfg<BQ>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // The ring and the activation tiles are sized per launch (p.ring_stages, p.chunk_blocks): a small projection
+    // then takes ~30 KB instead of ~100 KB, and the CTAs of the next kernel in the stream can move in early.
+    const int stages = p.ring_stages;
+    uint8_t* q_tiles = ring + static_cast<size_t>(stages) * kPBytes;            // [chunk_blocks][BQ][128], 128-byte swizzle
+    uint32_t* exchange = reinterpret_cast<uint32_t*>(q_tiles + p.chunk_blocks * (BQ * kBlockK));  // [chunk][L][BQ]
+    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(exchange) + C::kExchangeBytes);
+    uint64_t* empty = full + C::kMaxStages;
+    uint64_t* q_full = empty + C::kMaxStages;
+    uint64_t* tmem_full = q_full + 1;
+    uint64_t* x_full = tmem_full + 1;  // counts the bytes peers deliver into `exchange`
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(x_full + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (threadIdx.x == 0) FTH_TRACE(0);
+    const bool convert = p.args.a_dtype != 0;
+
+    if (threadIdx.x == 0) {
+        TmaPrefetchDescriptor(&map_p);  // kernel parameters: safe to touch before the previous grid has finished
+        if (!convert) TmaPrefetchDescriptor(&map_q);
+        for (int s = 0; s < stages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
+        MbarInit(q_full, convert ? 128 : 1);
+        MbarInit(tmem_full, 1);
+        MbarInit(x_full, 1);
+        FenceBarrierInit();
+    }
+    if (warp == 1) umma::TmemAlloc(tmem_base_slot, C::kTmemCols);
+    umma::FenceBeforeThreadSync();
+    __syncthreads();
+    umma::FenceAfterThreadSync();
+    const uint32_t tmem_base = *tmem_base_slot;
+    if (threadIdx.x == 0) FTH_TRACE(1);
+    ClusterArrive();  // "this CTA is running": peers wait for it before they write into our exchange buffer
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t rank = ClusterRank();
+    const uint32_t csize = ClusterSize();                  // a power of two
+    const int cshift = 31 - __clz(static_cast<int>(csize));
+    const int tile = static_cast<int>(blockIdx.x >> cshift);
+    const int lshift = 7 - cshift;                         // log2 of L = rows of the tile this CTA finishes
+    const int rows_per_cta = 1 << lshift;
+    const int kb_begin = static_cast<int>(rank) * static_cast<int>(p.chunk_blocks);
+    int nb = static_cast<int>(p.k_blocks) - kb_begin;
+    if (nb > static_cast<int>(p.chunk_blocks)) nb = static_cast<int>(p.chunk_blocks);
+    if (nb < 0) nb = 0;  // ranks beyond the split have no K range
+    const int m = static_cast<int>(p.q_total);
+    // Kernel parameters live in constant memory and every first touch of a line costs a few hundred cycles: read
+    // what the roles need now, while the previous kernel in the stream may still be running.
+    {
+        const int64_t out_bits = reinterpret_cast<int64_t>(INT8 ? ie.out : fe.out);
+        const int64_t ldo_bits = INT8 ? ie.ldo : fe.ldo;
+        asm volatile("" ::"r"(p.split), "l"(p.p_total), "r"(p.fast4), "r"(p.e4m3), "r"(p.idesc), "l"(p.args.k), "l"(p.args.a),
+                     "r"(p.args.a_dtype), "f"(p.args.a_scale), "f"(fe.out_scale), "f"(fe.ab_scale), "l"(fe.w_channel_scales),
+                     "r"(fe.out_dtype), "l"(out_bits), "l"(ldo_bits), "f"(ie.a_scale), "f"(ie.out_scale), "l"(ie.w_scales),
+                     "l"(p.status), "f"(p.a_inv), "f"(p.out_inv));
+    }
+
+    if (warp == 0) {
+        // ================================ TMA producer ================================
+        if (lane == 0 && nb > 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            auto load_weights = [&](int kb) -> bool {
+                // the first pass over the ring finds every stage free; later passes wait for the MMAs that read it
+                if (kb >= stages && !MbarWait(&empty[stage], phase ^ 1u, p.status, 20, stage)) return false;
+                const int32_t k0 = (kb_begin + kb) * kBlockK;
+                const int32_t p0 = tile * kBlockP;
+                uint8_t* ps = ring + static_cast<size_t>(stage) * kPBytes;
+                MbarExpectTx(&full[stage], kPBytes);
+                if constexpr (P_MN) TmaLoad2D(ps, &map_p, p0, k0, &full[stage]);
+                else TmaLoad2D(ps, &map_p, k0, p0, &full[stage]);
+                if (++stage == stages) { stage = 0; phase ^= 1u; }
+                return true;
+            };
+            // Weights that no earlier work in the stream writes can be fetched before the previous kernel has
+            // finished: their DRAM latency then overlaps its tail.
+            int kb = 0;
+            if (p.args.w_static) {
+                for (; kb < nb && kb < stages; ++kb) load_weights(kb);
+            }
+            FTH_TRACE(3);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            FTH_TRACE(2);
+            if (!convert) {
+                MbarExpectTx(q_full, static_cast<uint32_t>(nb) * BQ * kBlockK);
+                for (int j = 0; j < nb; ++j) TmaLoad2D(q_tiles + j * (BQ * kBlockK), &map_q, (kb_begin + j) * kBlockK, 0, q_full);
+            }
+            for (; kb < nb; ++kb) {
+                if (!load_weights(kb)) break;
+            }
+            FTH_TRACE(4);
+        }
+    } else if (warp == 1) {
+        // ================================ MMA issuer ================================
+        if (lane == 0 && nb > 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool failed = false;
+            for (int kb = 0; kb < nb && !failed; ++kb) {
+                if (!MbarWait(&full[stage], phase, p.status, 22, stage)) { failed = true; break; }
+                if (kb == 0 && !MbarWait(q_full, 0, p.status, 21, 0)) { failed = true; break; }  // activations arrive last
+                if (kb == 0) FTH_TRACE(5);
+                umma::FenceAfterThreadSync();
+                const uint32_t ps = SmemAddr(ring + static_cast<size_t>(stage) * kPBytes);
+                const uint32_t qs = SmemAddr(q_tiles + kb * (BQ * kBlockK));
+#pragma unroll
+                for (int ks = 0; ks < kBlockK / 32; ++ks) {
+                    const uint64_t a_desc = P_MN ? umma::SmemDesc(ps + ks * 4096, 16384, 1024) : umma::SmemDesc(ps + ks * 32, 16, 1024);
+                    const uint64_t b_desc = umma::SmemDesc(qs + ks * 32, 16, 1024);
+                    umma::Mma<INT8>(tmem_base, a_desc, b_desc, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma::Commit(&empty[stage]);
+                if (++stage == stages) { stage = 0; phase ^= 1u; }
+            }
+            FTH_TRACE(6);
+            if (!failed) umma::Commit(tmem_full);
+        }
+    } else {
+        // ====================== activation prologue, accumulator hand-out, reduce + epilogue ======================
+        const int et = threadIdx.x - 64;  // 0 .. 127
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (convert && nb > 0) {
+            // Four consecutive K elements of one activation row per item (one 32-bit word of the swizzled tile), four
+            // items per thread and round so that their loads overlap.  Rows >= m stay unwritten: they only feed
+            // accumulator columns nobody reads.  K beyond the end is zero.
+            const int words_per_row = nb * 32;
+            const int total = m * words_per_row;
+            const bool vec = (reinterpret_cast<uintptr_t>(p.args.a) & 15) == 0;
+            for (int base = et; base < total; base += 4 * 128) {
+                uint4 raw[4];
+                uint32_t dst[4];
+                bool inside[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int item = base + j * 128;
+                    const int row = item / words_per_row;
+                    const int c = item - row * words_per_row;
+                    const int kb = c >> 5, w4 = c & 31;
+                    const int64_t k0 = static_cast<int64_t>(kb_begin + kb) * kBlockK + w4 * 4;
+                    inside[j] = item < total && k0 < p.args.k;  // K is a multiple of 16: a group is in or out as a whole
+                    dst[j] = SmemAddr(q_tiles) + kb * (BQ * kBlockK) + row * 128 + (((w4 >> 2) ^ (row & 7)) << 4) + ((w4 & 3) << 2);
+                    raw[j] = inside[j] ? LoadFourRaw(p.args, static_cast<int64_t>(row) * p.args.k + k0, vec) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (base + j * 128 < total) {
+                        const uint32_t word = inside[j] ? ConvertFourRaw<INT8>(p.args, ie, p.e4m3, p.a_inv, raw[j]) : 0u;
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst[j]), "r"(word) : "memory");
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes → visible to the MMA's reads
+            MbarArrive(q_full);
+            if (et == 0) FTH_TRACE(7);
+        }
+        const int row = (warp & 3) * 32 + lane;  // TMEM lane = channel inside the tile
+        // Bytes this CTA will receive: from each of the `split` chunks, its L rows of ceil(m / 4) 16-byte vectors.
+        if (et == 0) MbarExpectTx(x_full, static_cast<uint32_t>(p.split) * rows_per_cta * ((m + 3) / 4) * 16);
+        ClusterWait();  // every CTA of the cluster is running and has initialised its barriers
+        if (et == 0) FTH_TRACE(8);
+        if (nb > 0) {
+            const bool ok = MbarWait(tmem_full, 0, p.status, 23, 0);
+            if (et == 0) FTH_TRACE(9);
+            umma::FenceAfterThreadSync();
+            if (ok) {
+                // Deal the accumulator rows out: row r goes to CTA r / L, slot [this chunk][r % L].  Each 16-byte
+                // store reports its bytes to the receiver's barrier, so no cluster-wide barrier is needed.
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+                const uint32_t owner = static_cast<uint32_t>(row >> lshift);
+                const uint32_t slot = SmemAddr(exchange) + (((rank << lshift) + (row & (rows_per_cta - 1))) * BQ) * 4;
+                const uint32_t remote = MapToRank(slot, owner);
+                const uint32_t remote_bar = MapToRank(SmemAddr(x_full), owner);
+#pragma unroll
+                for (int c0 = 0; c0 < BQ; c0 += 16) {
+                    if (c0 >= m) break;  // uniform
+                    uint32_t v[16];
+                    umma::TmemLoad16(taddr + c0, v);
+                    umma::TmemLoadWait();
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        if (c0 + j < m) StoreClusterAsync4(remote + (c0 + j) * 4, remote_bar, v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    }
+                }
+            }
+        }
+        if (et == 0) FTH_TRACE(10);
+        // A CTA leaves only after everything addressed to it has landed, so no peer ever writes into a CTA that is gone.
+        const bool delivered = MbarWait(x_full, 0, p.status, 24, 0);
+        if (et == 0) FTH_TRACE(11);
+
+        // One output per thread and round: channel r of this CTA's rows (fastest, so a warp stores consecutive
+        // channels) of activation row q.  The chunks are added in chunk order, as the two-kernel path adds them.
+        const int total = m << lshift;
+        for (int base = 0; base < total; base += 128) {  // the same trip count in every lane: the argmax step below shuffles
+            const int item = base + et;
+            const bool valid = delivered && item < total;
+            const int q = item >> lshift;
+            const int r = item & (rows_per_cta - 1);
+            const int64_t n = static_cast<int64_t>(tile) * kBlockP + (static_cast<int64_t>(rank) << lshift) + r;
+            uint32_t code = 0;
+            bool stored = false;
+            if (valid) {
+                uint32_t t[8];
+#pragma unroll
+                for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? exchange[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
+                uint32_t acc;
+                if constexpr (INT8) {
+                    int32_t sum = 0;
+#pragma unroll
+                    for (int ss = 0; ss < 8; ++ss) sum += static_cast<int32_t>(t[ss]);
+                    acc = static_cast<uint32_t>(sum);
+                } else {
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int ss = 0; ss < 8; ++ss) {
+                        if (ss < p.split) sum += __uint_as_float(t[ss]);  // no zero is ever added: it could flip a -0
+                    }
+                    acc = __float_as_uint(sum);
+                }
+                if (et == 0) FTH_TRACE(14);
+                if (n < p.p_total) { code = FinishOne<INT8>(p, fe, ie, q, n, acc); stored = true; }
+            }
+            if (p.args.argmax_keys != nullptr)
+                ArgmaxUpdate(p.args.argmax_keys, stored ? q : -1, stored ? ArgmaxKey<INT8>(p.e4m3, code, n) : 0ull);
+        }
+    }
+    if (warp < 2) {
+        if (!(warp == 0 && lane == 0 && nb > 0)) asm volatile("griddepcontrol.wait;" ::: "memory");
+        ClusterWait();
+    }
+    if (threadIdx.x == 64) FTH_TRACE(12);
+    umma::FenceBeforeThreadSync();
+    __syncthreads();
+    if (warp == 1) {
+        umma::FenceAfterThreadSync();
+        umma::TmemDealloc(tmem_base, C::kTmemCols);
+        if (lane == 0) FTH_TRACE(13);
+    }
+}
+
+template <bool INT8, bool P_MN, int BQ>
+int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p_in,
+                       const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
+    TcParams p = p_in;
+    p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks);
+    auto kernel = LinearClusterKernel<INT8, P_MN, BQ>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ClusterCfg<BQ>::kSmemBytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(g.p_tiles * g.cluster));
+    cfg.blockDim = dim3(ClusterCfg<BQ>::kThreads);
+    cfg.dynamicSmemBytes = ClusterCfg<BQ>::SmemFor(g.chunk_blocks);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = static_cast<unsigned>(g.cluster);
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    if (cudaLaunchKernelEx(&cfg, kernel, map_p, map_q, p, fe, ie) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    NoteLaunch("tcgen05");
+    return CheckLaunch();
+}
+
+template <bool INT8>
+int LaunchClusterFor(const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p,
+                  const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
+    if (g.bq == 16) {
+        return weights_mn ? LaunchClusterTyped<INT8, true, 16>(g, map_p, map_q, p, fe, ie, stream)
+                          : LaunchClusterTyped<INT8, false, 16>(g, map_p, map_q, p, fe, ie, stream);
+    }
+    return weights_mn ? LaunchClusterTyped<INT8, true, 32>(g, map_p, map_q, p, fe, ie, stream)
+                      : LaunchClusterTyped<INT8, false, 32>(g, map_p, map_q, p, fe, ie, stream);
+}
+
+}  // namespace
+
+int LaunchCluster(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p,
+                  const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
+    return int8 ? LaunchClusterFor<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
+                : LaunchClusterFor<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
+}
+
+}  // namespace tc
+}  // namespace fth
