@@ -87,3 +87,24 @@ def test_gather_sync_single_rank(cuda):
         torch.cuda.synchronize()
         assert int(flags[0].item()) == epoch and B.device_status() == 0
     assert B.lib().fth_b200_gather_sync(ptrs, C.c_int32(9), C.c_int32(0), C.c_uint32(1), B.current_stream()) == B.ERR_INVALID
+
+
+def test_gather_sync_gives_up_when_a_peer_never_signals(cuda):
+    """Failure detection without a fault: rank 0 of a two-rank gather whose peer never raises its flag.  The wait runs
+    out after its one-second budget, the kernel returns, the status word names the wait (site 40) and the silent rank,
+    and the device keeps working."""
+    torch = cuda
+    mine = torch.zeros(8, dtype=torch.int32, device="cuda")
+    peer = torch.zeros(8, dtype=torch.int32, device="cuda")   # stands in for rank 1's flag array; rank 1 does not exist
+    ptrs = (C.c_void_p * 2)(mine.data_ptr(), peer.data_ptr())
+    assert B.device_status() == 0
+    assert B.lib().fth_b200_gather_sync(ptrs, C.c_int32(2), C.c_int32(0), C.c_uint32(1), B.current_stream()) == 0
+    torch.cuda.synchronize()
+    status = B.device_status()
+    assert status >> 16 == 40 and status & 0xffff == 1
+    assert int(peer[0].item()) == 1 and int(mine[0].item()) == 1   # this rank did signal both arrays
+    # the context is intact: the next step, with the peer "answering", completes cleanly
+    mine[1] = 2
+    assert B.lib().fth_b200_gather_sync(ptrs, C.c_int32(2), C.c_int32(0), C.c_uint32(2), B.current_stream()) == 0
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
