@@ -247,7 +247,7 @@ extern "C" int fth_b200_fp8_linear_argmax(const fth_b200_fp8_linear_desc* d, int
     const int variant = PickVariant(d->variant, d->dtype, args, d->workspace, d->workspace_bytes);
     if (variant < 0) return variant;
     // only the decode-sized tensor-core kernels carry the fused selection (their epilogue sees every output once)
-    if (variant != FTH_B200_VARIANT_TCGEN05 || !Tcgen05StoresToPeers(d->dtype, args, fe, ie)) return FTH_B200_ERR_UNSUPPORTED;
+    if (variant != FTH_B200_VARIANT_TCGEN05 || !Tcgen05SelectsInEpilogue(d->dtype, args, fe, ie)) return FTH_B200_ERR_UNSUPPORTED;
     if (cudaMemsetAsync(indices, 0, static_cast<size_t>(d->m) * 8, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
     args.argmax_keys = reinterpret_cast<unsigned long long*>(indices);
     const int run = Run(variant, d->dtype, args, fe, ie, d->workspace, d->workspace_bytes, stream);

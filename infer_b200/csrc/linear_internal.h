@@ -53,6 +53,8 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& args, const Fp8Epilogue& fe
                         size_t scratch_bytes, cudaStream_t stream);
 // True when that launch writes the peer replicas from its own epilogue (otherwise the caller copies the block over).
 bool Tcgen05StoresToPeers(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie);
+// True when that launch can also run the fused greedy selection (the decode-sized kernels, direct epilogue).
+bool Tcgen05SelectsInEpilogue(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie);
 
 // Turns the packed (value, index) keys a fused argmax left in `keys` into int64 indices in place (-1: no candidate).
 int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, cudaStream_t stream);

@@ -214,9 +214,9 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                     w.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
                     w.z = b[8] | (b[9] << 8) | (b[10] << 16) | (b[11] << 24);
                     w.w = b[12] | (b[13] << 8) | (b[14] << 16) | (b[15] << 24);
-                    *reinterpret_cast<uint4*>(dst) = w;
+                    StoreWithPeers(p.args.peers, reinterpret_cast<uint4*>(dst), w);  // peers: a column shard's replicas on other GPUs
                 } else {
-                    for (int j = 0; j < cnt; ++j) dst[j] = static_cast<uint8_t>(b[j]);
+                    for (int j = 0; j < cnt; ++j) StoreWithPeers(p.args.peers, dst + j, static_cast<uint8_t>(b[j]));
                 }
             }
             // this CTA's half of the accumulator buffer is drained: tell the leader's MMA warp

@@ -125,9 +125,16 @@ static bool DirectEpilogue(bool int8, const Fp8Epilogue& fe, const Int8Epilogue&
     return fe.bias_mode == FTH_B200_BIAS_NONE && !(fe.is_gemm && fe.alpha != 1.0f);
 }
 
-bool Tcgen05StoresToPeers(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
+bool Tcgen05SelectsInEpilogue(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
     const TcGeometry g = GeometryFor(a);
     return g.swap && (g.cluster > 0 || g.split > 1) && DirectEpilogue(dtype == FTH_B200_INT8, fe, ie);
+}
+
+bool Tcgen05StoresToPeers(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
+    if (Tcgen05SelectsInEpilogue(dtype, a, fe, ie)) return true;
+    // the dense kernel's vectorised epilogue (native output dtype, no bias / alpha / beta) writes the replicas too
+    const bool int8 = dtype == FTH_B200_INT8;
+    return !GeometryFor(a).swap && DirectEpilogue(int8, fe, ie) && (int8 ? ie.out_dtype : fe.out_dtype) == 0;
 }
 
 size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& a) {
