@@ -120,8 +120,8 @@ typedef struct {
     int32_t weights_static;
     /* Column-sharded projections on several GPUs of one box: `gather_peers` other ranks hold a buffer shaped like this
      * rank's output buffer; gather_out[r] is the peer-mapped address in rank r's buffer that corresponds to `out`.
-     * Every output element is stored there as well (by the linear kernel's own epilogue for decode-sized M, by a
-     * block copy behind it otherwise).  Follow the call with fth_b200_gather_sync.  No counterpart in the reference
+     * Every output element is stored there as well (by the tensor-core kernels' own epilogue when no bias, alpha or
+     * beta is involved; by a block copy behind the kernel otherwise).  Follow the call with fth_b200_gather_sync.  No counterpart in the reference
      * (one CudaExecutionContext = one device, src/kernel/cuda/runtime.cu:318-321). */
     int32_t gather_peers;   /* 0 .. 7 */
     void* gather_out[7];
