@@ -4,15 +4,27 @@
 Workload (config 5 of the baseline: the one the metric is quoted on): FP8 E4M3 Linear, K = 8192, N = 28672,
 weights N(0, 0.02) quantised per tensor, activations N(0, 1).  One "step" is one decode-shaped (M = 1) linear
 call over the whole weight; `value` is the algorithmic HBM GB/s of that step with everything resident in HBM.
-The dense M = 4096 TFLOP/s figure of the same metric, the INT8 variants and the decode sweep are reported in
-`extra`, measured outside the timed steps.  Two weight sets (2 x 235 MB > 126 MB of L2) are rotated so no
-step finds its weights in L2.
+The K timed steps are run as a block, the block is repeated (`blocks` in the JSON line) and the median block is
+reported, so that the clock ramp of a GPU that was idle a moment ago does not set the number.  Enough weight sets
+are rotated that no step finds its weights in L2.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--quick]
 
-N > 1 (under torchrun): the weight is column-sharded across the ranks, each rank computes its slice and one
-NCCL all-gather assembles the 1-byte outputs (strong scaling: total work is fixed).
-`--impl reference` times the reference's own x86 kernel for the same configuration on the host cores.
+N > 1 (under torchrun): the weight is column-sharded across the ranks; every rank's kernel stores its columns into
+all ranks' output buffers over NVLink (peer stores from the epilogue) and a small signal / wait kernel ends the step
+(strong scaling: total work is fixed).  There is no collective library on the data path; NCCL is used for set-up
+and is the fallback gather on a box without peer mapping.
+
+Checks outside the timed regions (any failure makes the run exit non-zero):
+  * N = 1: the output row of the timed kernel is compared with the CPU oracle (`parity` in the JSON line);
+  * N > 1: with one seeded weight shared by all ranks, every rank compares the gathered [M, N] result with the
+    result of its own single-GPU run (`gather_mismatch_bytes`), FP8 and INT8;
+  * every rank reads the device status word after the timed and the end-to-end regions (`device_status`).
+
+`extra` carries the rest of the metric: FP8 and INT8 at M = 1, 16, 256, 4096 (at N > 1 on the column shards, step
+time including the gather), the config-4 decode step, the config-3 conv, and the reference's x86 kernels timed on
+the host cores for configs 2, 3, 4 and 5-INT8.  `--impl reference` times the reference's own x86 kernel for the
+headline configuration on the host cores.
 """
 from __future__ import annotations
 
@@ -33,6 +45,11 @@ K, N = 8192, 28672
 L2_BYTES = 126 * 1024 * 1024
 SEED = 0xFEA70005
 METRIC = "quant Linear HBM GB/s at M=1 & TFLOP/s at M=4096 (% B200 peak), 1/2/4/8 GPU"
+WORKLOAD = f"C5 FP8-E4M3 Linear M=1 K={K} N={N}"
+BLOCKS = 7
+# dram__bytes_read.sum + dram__bytes_write.sum of one tcgen05 GEMV launch on the bench workload, from the ncu
+# capture summarised in profiles/ (per launch, bytes).
+TRAFFIC_BYTES_PER_LAUNCH = 239648512
 
 
 def measured_peaks():
@@ -102,6 +119,12 @@ def synth(torch, shape, std, seed, device):
     return e4m3_codes_torch(torch, x, scale), scale
 
 
+def synth_int8(torch, shape, seed, device):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return torch.randint(-127, 128, shape, generator=g, device=device, dtype=torch.int8)
+
+
 def event_time_ms(torch, fn, steps, warmup, barrier=None):
     """W untimed warm-up calls, then exactly `steps` calls between two CUDA events on the launching stream,
     with a barrier + synchronize on both sides.  Returns total milliseconds."""
@@ -127,6 +150,9 @@ def algorithmic_bytes(m, n, per_channel=False):
     return K * n + m * K + m * n + (4 * n if per_channel else 0)
 
 
+FP8_OUT_SCALE = float(np.float32(0.02 * np.sqrt(K) * 4.0 / 448.0))
+
+
 # ------------------------------------------------------------------------------------------------------------
 # reference arm: the reference's own x86 kernel on the host cores
 # ------------------------------------------------------------------------------------------------------------
@@ -137,7 +163,7 @@ def cpu_reference_kernel(torch, m=1):
     w, sw = synth(torch, (K, N), 0.02, SEED, "cpu")
     a, sa = synth(torch, (m, K), 1.0, SEED + 1, "cpu")
     w, a = w.numpy(), a.numpy()
-    so = float(np.float32(0.02 * np.sqrt(K) * 4.0 / 448.0))
+    so = FP8_OUT_SCALE
     if O.have_ref():
         kern = O.fp8_linear(O.OP_MATMUL, O.E4M3, a, sa, w, sw, so, impl="ref", device=O.X86, return_kernel=True)
         t0 = time.time()
@@ -156,6 +182,15 @@ def cpu_reference_kernel(torch, m=1):
             best = min(best, time.time() - t0)
         return best
     return run, dict(kind="port", cores=threads, prepare_s=0.0)
+
+
+def bench_config(world, extra=None):
+    """`config` of the JSON line; both arms carry the same keys."""
+    cfg = {"workload": WORKLOAD, "gpus": world, "host_cpus": os.cpu_count(), "seed": SEED, "algorithmic_bytes_per_step": algorithmic_bytes(1, N),
+           "sharding": None, "l2": None, "kernel": None}
+    if extra:
+        cfg.update(extra)
+    return cfg
 
 
 def run_reference_arm(args):
@@ -181,7 +216,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"C5 FP8-E4M3 Linear M=1 K={K} N={N}", "host_cpus": os.cpu_count()},
+        "config": bench_config(args.gpus, {"kernel": "reference x86 MatMulKernel<X86,FP8E4M3> (packed BF16 GEMV)"}),
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": info["cores"], "kind": info["kind"], "sample": sample},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -193,296 +228,319 @@ def run_reference_arm(args):
 # ------------------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------------------
-def run_gpu_arm(args):
-    import torch
-    import infer_b200 as B
-    from infer_b200.sharded import ShardedLinear
+class Ctx:
+    """What every measured case needs: torch, the library, this rank's place in the job and its column shard."""
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        dist = dist_mod
-    barrier = (lambda: dist.barrier()) if dist else None
-    dev = torch.device("cuda", local_rank)
-    B.lib()  # fails loudly if the CUDA library is missing
-    peaks = measured_peaks()
-    stream = B.current_stream()
-    fp8_call = B.lib().fth_b200_fp8_linear
-    int8_call = B.lib().fth_b200_int8_linear
+    def __init__(self, torch, B, dist, world, rank, dev):
+        from infer_b200.sharded import ShardedLinear
+        self.torch, self.B, self.dist, self.world, self.rank, self.dev = torch, B, dist, world, rank, dev
+        self.shard = ShardedLinear(N, world, rank, compute=None, dist=dist)
+        self.n0, self.n1 = self.shard.n0, self.shard.n1
+        self.n_local = self.n1 - self.n0
+        self.stream = B.current_stream()
+        self.fp8_call = B.lib().fth_b200_fp8_linear
+        self.int8_call = B.lib().fth_b200_int8_linear
+        self.peer_ok = world > 1  # cleared on the first failure to map peer buffers
 
-    # ---- this rank's column shard of two weight sets (rotated so steps never hit L2-resident weights) ----
-    shard = ShardedLinear(N, world, rank, compute=None, dist=dist)
-    n0, n1 = shard.n0, shard.n1
-    n_local, width = n1 - n0, shard.width
-    out_scale = float(np.float32(0.02 * np.sqrt(K) * 4.0 / 448.0))
-    # enough weight sets that one rotation moves at least twice the L2 capacity through the GPU (a 29 MB shard
-    # on 8 GPUs needs 9 of them; the full 235 MB weight needs 2)
-    n_sets = max(2, -(-2 * L2_BYTES // (K * n_local)))
-    weights, w_scales = [], []
-    for i in range(n_sets):
-        if world == 1:
-            w_part, sw = synth(torch, (K, N), 0.02, SEED + 10 * i, dev)
-        else:  # this rank's columns of weight set i, drawn directly (the same distribution; no 235 MB detour per set)
-            w_part, sw = synth(torch, (K, n_local), 0.02, SEED + 10 * i + 1000 * (rank + 1), dev)
-        weights.append(w_part.contiguous())
-        w_scales.append(sw)
-        del w_part
-    a_dev, sa = synth(torch, (1, K), 1.0, SEED + 1, dev)
-    local_out = torch.zeros((1, width), dtype=torch.uint8, device=dev)
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
 
-    def make_desc(m, w, sw, a, out, ldo=0):
-        d = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=K, n=w.shape[1], a=a, w=w, out=out, a_scale=sa,
-                              w_scale=sw, out_scale=out_scale, ldo=ldo, weights_static=True)
-        ws = B.linear_workspace(torch, d)
-        return d, ws
+    def max_over_ranks(self, value):
+        if not self.dist:
+            return value
+        t = self.torch.tensor([value], device=self.dev, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
 
-    descs = [make_desc(1, weights[i], w_scales[i], a_dev, local_out, ldo=width) for i in range(n_sets)]
-    counter = [0]
+    def sum_over_ranks(self, value):
+        if not self.dist:
+            return value
+        t = self.torch.tensor([value], device=self.dev, dtype=self.torch.int64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return int(t.item())
 
-    # N > 1: every rank's kernel stores its columns into all ranks' output buffers (peer-mapped) and a signal / wait
-    # kernel ends the step; no collective library on the data path.
-    gather = None
-    if world > 1:
-        from infer_b200.sharded import PeerGather, ShardedLinear, forward_peer
-        from infer_b200.sharded import point_at_step_buffers
-        shard = ShardedLinear(N, world, rank, compute=None, dist=dist)
-        call_desc = lambda desc, s: fp8_call(C.byref(desc), s)  # noqa: E731
-        try:
-            gather = PeerGather(B.lib(), dist, world, rank, 1, N)  # raises on every rank or on none
-            # per weight set, one descriptor per step parity, pointed at that parity's buffers once
-            prepared = [tuple(point_at_step_buffers(shard, gather, type(d).from_buffer_copy(d), parity) for parity in (0, 1)) for d, _ in descs]
-        except RuntimeError as exc:
-            # no peer mapping on this box: the gather falls back to one NCCL all-gather of the 1-byte outputs
-            gather = None
-            if rank == 0:
-                print(f"[bench] {exc}; using NCCL all_gather_into_tensor", file=sys.stderr)
-    nccl_gathered = torch.zeros((world, width), dtype=torch.uint8, device=dev) if world > 1 and gather is None else None
 
-    def step():
-        i = counter[0] % n_sets
-        counter[0] += 1
-        if gather is not None:
-            forward_peer(shard, gather, descs[i][0], call_desc, stream, prepared[i])
+class LinearCase:
+    """One (kind, M) linear over this rank's columns of the C5 weight, with rotating weight sets.
+
+    world == 1: the kernel writes a local [M, N] buffer.  world > 1: the output goes to every rank's [M, N] buffer
+    (peer stores) and fth_b200_gather_sync ends the step; steps are replayed from a CUDA graph of one rotation
+    because a sharded decode step is less GPU time than the host needs to issue it.  Without peer mapping the
+    gather is one NCCL all-gather of the 1-byte outputs."""
+
+    def __init__(self, ctx, kind, m, weights=None, seed=SEED, rotate_bytes=2 * L2_BYTES, use_graph=None):
+        torch, B = ctx.torch, ctx.B
+        self.ctx, self.kind, self.m = ctx, kind, m
+        self.int8 = kind == "int8"
+        n_local = ctx.n_local
+        if weights is None:
+            n_sets = max(2, -(-rotate_bytes // (K * n_local)))
+            weights = []
+            for i in range(n_sets):
+                if self.int8:
+                    weights.append((synth_int8(torch, (K, n_local), seed + 10 * i + 1000 * (ctx.rank + 1), ctx.dev), None))
+                elif ctx.world == 1:
+                    weights.append(synth(torch, (K, N), 0.02, seed + 10 * i, ctx.dev))
+                else:  # this rank's columns of weight set i, drawn directly (same distribution; no 235 MB detour per set)
+                    weights.append(synth(torch, (K, n_local), 0.02, seed + 10 * i + 1000 * (ctx.rank + 1), ctx.dev))
+        self.weights = weights
+        self.n_sets = len(weights)
+        if self.int8:
+            g = torch.Generator(device=ctx.dev)
+            g.manual_seed(seed + 77)
+            full_scales = torch.empty(N, dtype=torch.float32, device=ctx.dev).uniform_(1e-3, 1e-2, generator=g)
+            self.scales = full_scales[ctx.n0:ctx.n1].contiguous()
+            self.a = synth_int8(torch, (m, K), seed + 1, ctx.dev)
+            self.sa = 0.02
+            sigma = 73.3 ** 2 * np.sqrt(K) * self.sa * 5.5e-3
+            self.so = float(np.float32(2.33 * sigma / 127.0))
+        else:
+            self.a, self.sa = synth(torch, (m, K), 1.0, seed + 1, ctx.dev)
+            self.so = FP8_OUT_SCALE
+        self.call = ctx.int8_call if self.int8 else ctx.fp8_call
+        self.local_out = torch.zeros((m, N if ctx.world > 1 else n_local), dtype=torch.uint8, device=ctx.dev)
+        self.keep = []
+        self.descs = [self._desc(w, sw, self.a, self.local_out, ldo=self.local_out.shape[1]) for (w, sw) in weights]
+        self.counter = 0
+        self.gather = None
+        self.graph = None
+        self.rotation = 0
+        self.stream = ctx.stream
+        self.nccl_gathered = None
+        if ctx.world > 1:
+            self._setup_gather()
+            if self.gather is not None and (use_graph if use_graph is not None else True):
+                self._capture()
+
+    # ---- descriptors ----
+    def _desc(self, w, sw, a, out, ldo=0):
+        B, torch = self.ctx.B, self.ctx.torch
+        n = w.shape[1]
+        if self.int8:
+            d = B.int8_linear_desc(op=B.OP_MATMUL, m=self.m, k=K, n=n, a=a, w=w, out=out, a_scale=self.sa, a_zp=0, w_scales=self.scales,
+                                   w_zps=None, w_params=n, out_scale=self.so, out_zp=0, ldo=ldo, weights_static=True)
+        else:
+            d = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=self.m, k=K, n=n, a=a, w=w, out=out, a_scale=self.sa,
+                                  w_scale=sw, out_scale=self.so, ldo=ldo, weights_static=True)
+        self.keep.append(B.linear_workspace(torch, d))
+        return d
+
+    def _call_desc(self, desc, stream):
+        return self.call(C.byref(desc), stream)
+
+    def _setup_gather(self):
+        from infer_b200.sharded import PeerGather, forward_peer, point_at_step_buffers
+        self._forward_peer = forward_peer
+        ctx = self.ctx
+        if ctx.peer_ok:
+            try:
+                self.gather = PeerGather(ctx.B.lib(), ctx.dist, ctx.world, ctx.rank, self.m, N)  # raises on every rank or on none
+                self.prepared = [tuple(point_at_step_buffers(ctx.shard, self.gather, type(d).from_buffer_copy(d), parity) for parity in (0, 1))
+                                 for d in self.descs]
+                return
+            except RuntimeError as exc:
+                ctx.peer_ok = False
+                self.gather = None
+                if ctx.rank == 0:
+                    print(f"[bench] {exc}; using NCCL all_gather_into_tensor", file=sys.stderr)
+        # fallback: local [M, width] block, one NCCL all-gather (row-major only for M = 1)
+        torch = ctx.torch
+        self.local_out = torch.zeros((self.m, ctx.shard.width), dtype=torch.uint8, device=ctx.dev)
+        self.keep = []
+        self.descs = [self._desc(w, sw, self.a, self.local_out, ldo=ctx.shard.width) for (w, sw) in self.weights]
+        self.nccl_gathered = torch.zeros((ctx.world, self.m, ctx.shard.width), dtype=torch.uint8, device=ctx.dev)
+
+    # ---- one step ----
+    def step(self):
+        i = self.counter % self.n_sets
+        self.counter += 1
+        if self.gather is not None:
+            self._forward_peer(self.ctx.shard, self.gather, self.descs[i], self._call_desc, self.stream, self.prepared[i])
             return
-        rc = fp8_call(C.byref(descs[i][0]), stream)
+        rc = self.call(C.byref(self.descs[i]), self.stream)
         if rc != 0:
-            raise RuntimeError(f"fth_b200_fp8_linear failed: {rc}")
-        if world > 1:
-            dist.all_gather_into_tensor(nccl_gathered, local_out)
+            raise RuntimeError(f"linear call failed: {rc}")
+        if self.nccl_gathered is not None:
+            self.ctx.dist.all_gather_into_tensor(self.nccl_gathered.view(self.ctx.world * self.m, -1), self.local_out)
 
-    # N > 1: a sharded step is a few microseconds of GPU time, less than the host needs to issue it, so the steps are
-    # replayed from a CUDA graph of one full rotation (every weight set, both buffer parities); the gather's step
-    # numbers live on the device for that.  Steps that do not fill a whole rotation are issued one by one.
-    timed_step, steps_per_call = step, 1
-    if gather is not None:
-        rotation = n_sets * (2 if n_sets % 2 else 1)  # an even number of steps: the buffer parity repeats
-        for _ in range(rotation):
-            step()
+    def result(self):
+        """The [M, N] (world > 1) or [M, n_local] output of the last step, as a device tensor."""
+        torch = self.ctx.torch
         torch.cuda.synchronize()
-        dist.barrier()
+        if self.gather is not None:
+            return self.gather.view(torch, self.gather.epoch & 1)
+        if self.nccl_gathered is not None:
+            return self.nccl_gathered.transpose(0, 1).reshape(self.m, -1)[:, :N]
+        return self.local_out
+
+    # ---- CUDA graph of one rotation (every weight set, both buffer parities) ----
+    def _capture(self):
+        ctx, torch, gather = self.ctx, self.ctx.torch, self.gather
+        rotation = self.n_sets * (2 if self.n_sets % 2 else 1)  # an even number of steps: the buffer parity repeats
+        for _ in range(rotation):
+            self.step()
+        torch.cuda.synchronize()
+        ctx.barrier()
         side = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
-        main_stream = stream
-        epoch_before, counter_before = gather.epoch, counter[0]
+        epoch_before, counter_before = gather.epoch, self.counter
         captured = True
         try:
             with torch.cuda.stream(side):
                 with torch.cuda.graph(graph, stream=side):
-                    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+                    self.stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
                     for _ in range(rotation):
-                        step()
+                        self.step()
         except Exception as exc:  # capture is an optimisation of the issue rate, never a requirement
             captured = False
-            gather.epoch, counter[0] = epoch_before, counter_before
-            print(f"[bench] rank {rank}: CUDA-graph capture failed ({type(exc).__name__}: {exc}); issuing steps one by one", file=sys.stderr)
-        stream = main_stream
-        verdict = torch.tensor([1 if captured else 0], device=dev)
-        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)  # all ranks replay, or none does
+            print(f"[bench] rank {ctx.rank}: CUDA-graph capture failed ({type(exc).__name__}: {exc}); issuing steps one by one", file=sys.stderr)
+        self.stream = ctx.stream
+        # the capture ran the host-side counters forward without running a step: put them back
+        gather.epoch, self.counter = epoch_before, counter_before
+        verdict = torch.tensor([1 if captured else 0], device=ctx.dev)
+        ctx.dist.all_reduce(verdict, op=ctx.dist.ReduceOp.MIN)  # all ranks replay, or none does
         if int(verdict.item()) == 1:
-            # the capture ran the host-side counters forward without running a step: put them back
-            gather.epoch, counter[0] = epoch_before, counter_before
+            self.graph, self.rotation, self.graph_parity = graph, rotation, epoch_before & 1
 
-            def replay():
-                graph.replay()
-                gather.epoch += rotation
-                counter[0] += rotation
-            timed_step, steps_per_call = replay, rotation
-
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-
-    # ---- timed region: exactly K steps, device-timed, max over ranks ----
-    B.lib().fth_b200_reset_launch_count()
-    if steps_per_call == 1:
-        total_ms = event_time_ms(torch, step, args.steps, args.warmup, barrier)
-        launches_total = B.lib().fth_b200_launch_count()
-        launches = launches_total * args.steps // (args.steps + args.warmup)
-    else:
-        calls, rest = divmod(args.steps, steps_per_call)
-        B.lib().fth_b200_reset_launch_count()
-        step()
-        per_step_launches = B.lib().fth_b200_launch_count()  # kernels one step launches (counted outside the graph)
-        step_odd = gather.epoch & 1
-        if step_odd:
-            step()  # keep the parity the graph was captured with
-
-        def timed_block():
-            for _ in range(calls):
-                timed_step()
-            for _ in range(rest):
-                step()
-        # warm-up: W steps one by one, then the timed block once: exactly K steps between the events
-        for _ in range(args.warmup + (args.warmup & 1)):
-            step()
-        total_ms = event_time_ms(torch, timed_block, 1, 0, barrier)
-        launches = per_step_launches * args.steps
-    variant = B.last_variant()
-    if world > 1:
-        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
-    bytes_step = algorithmic_bytes(1, N)
-    value = bytes_step / (ms_per_step * 1e-3) / 1e9
-
-    # ---- end to end through the host-buffer plan API: H2D of the activation, launch, D2H of the result ----
-    a_host = torch.empty((1, K), dtype=torch.uint8).pin_memory()
-    a_host.copy_(a_dev.cpu())
-    out_host = torch.empty((1, width), dtype=torch.uint8).pin_memory()
-    plans = []
-    for i in range(2 if world == 1 else 0):
-        hd = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=1, k=K, n=n_local, a=None, w=None, out=None, a_scale=sa,
-                               w_scale=w_scales[i], out_scale=out_scale, ldo=width)
-        w_host = weights[i].cpu()
-        hd.w = w_host.data_ptr()
-        plans.append(B.Plan(hd))
-        del w_host
-    pc = [0]
-
-    a_stage = torch.empty((1, K), dtype=torch.uint8, device=dev)
-    full_host = torch.empty((1, N), dtype=torch.uint8).pin_memory()
-    e2e_descs = [make_desc(1, weights[i], w_scales[i], a_stage, local_out, ldo=width) for i in range(n_sets)] if world > 1 else []
-
-    def e2e_step():
-        if world == 1:
-            plans[pc[0] & 1].run(a_host, out_host, stream)
-            pc[0] += 1
+    def run_steps(self, steps):
+        """Issues exactly `steps` steps on the stream (graph replays of whole rotations, the rest one by one)."""
+        if self.graph is None:
+            for _ in range(steps):
+                self.step()
             return
-        # N > 1: pinned-host activation in, sharded kernels with peer stores, the gathered row back to the host
-        a_stage.copy_(a_host, non_blocking=True)
-        d, _ = e2e_descs[pc[0] % n_sets]
-        pc[0] += 1
-        if gather is not None:
-            parity = forward_peer(shard, gather, d, call_desc, stream)
-            full_host.copy_(gather.view(torch, parity), non_blocking=True)
-        else:
-            if fp8_call(C.byref(d), stream) != 0:
-                raise RuntimeError("fth_b200_fp8_linear failed")
-            dist.all_gather_into_tensor(nccl_gathered, local_out)
-            full_host.copy_(nccl_gathered.view(1, -1)[:, :N], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if (self.gather.epoch & 1) != self.graph_parity:
+            raise RuntimeError("buffer parity differs from the captured one")
+        calls, rest = divmod(steps, self.rotation)
+        for _ in range(calls):
+            self.graph.replay()
+            self.gather.epoch += self.rotation
+            self.counter += self.rotation
+        for _ in range(rest):
+            self.step()
 
-    e2e_steps = min(args.steps, 500)
-    e2e_ms = event_time_ms(torch, e2e_step, e2e_steps, max(args.warmup, 3), barrier) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = bytes_step / (e2e_ms * 1e-3) / 1e9
-    for p in plans:
-        p.close()
+    def align(self):
+        """Brings the step parity back to the one the graph was captured with."""
+        if self.graph is not None and (self.gather.epoch & 1) != self.graph_parity:
+            self.step()
 
-    extra = {}
-    cpu_baseline = None
-    if rank == 0 and not args.quick:
-        extra = extra_measurements(torch, B, dev, peaks, fp8_call, int8_call, stream, sa, out_scale, weights[0], w_scales[0])
-    sampler.stop_flag = True
-    sampler.join(timeout=1.0)
-    if rank == 0 and world == 1:
-        cpu_baseline = cpu_baseline_measurement(torch)
+    def time_blocks(self, steps, warmup, blocks):
+        """W warm-up steps, then `blocks` blocks of exactly `steps` steps, each between two CUDA events with a barrier
+        + synchronize on both sides; returns the per-block milliseconds, max over ranks."""
+        ctx, torch = self.ctx, self.ctx.torch
+        self.align()
+        for _ in range(warmup + (warmup & 1)):
+            self.step()
+        out = []
+        for _ in range(blocks):
+            self.align()
+            ms = event_time_ms(torch, lambda: self.run_steps(steps), 1, 0, ctx.barrier if ctx.dist else None)
+            out.append(ctx.max_over_ranks(ms))
+        return out
 
-    if rank == 0:
-        achieved = value if world == 1 else value / world
-        line = {
-            "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"C5 FP8-E4M3 Linear M=1 K={K} N={N}" + ((f", N column-sharded over {world} GPUs, " + ("outputs stored to all ranks over NVLink (peer stores + flag wait)" if gather is not None else "NCCL all-gather")) if world > 1 else ""),
-                       "l2": f"inputs larger than L2: {n_sets} weight sets of {K * n_local / 1e6:.0f} MB rotated", "kernel": variant,
-                       "algorithmic_bytes_per_step": bytes_step, "seed": SEED},
-            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
-                         "peak_source": peaks["source"], "note": "per GPU; step = tcgen05 GEMV + split-K reduce kernel"},
-            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": K, "d2h_bytes_per_step": width if world == 1 else N,
-                    "ms_per_step": round(e2e_ms, 5),
-                    "api": "fth_b200_plan_run (pinned host activation in, host result out)" if world == 1 else
-                           "pinned host activation in, fth_b200_fp8_linear with peer stores + fth_b200_gather_sync, gathered row out"},
-            "gpu_launches": int(launches),
-            "clocks": sampler.summary(),
-            "cpu_baseline": cpu_baseline,
-            "extra": extra,
-        }
-        print(json.dumps(line))
-    if dist:
-        dist.barrier()
-        if gather is not None:
-            gather.close()
-        dist.destroy_process_group()
-    return 0
+    def launches_per_step(self):
+        lib = self.ctx.B.lib()
+        lib.fth_b200_reset_launch_count()
+        self.step()
+        n = lib.fth_b200_launch_count()
+        self.ctx.torch.cuda.synchronize()
+        return int(n)
+
+    def close(self):
+        if self.gather is not None:
+            self.ctx.torch.cuda.synchronize()
+            self.ctx.barrier()
+            self.graph = None
+            self.gather.close()
+            self.gather = None
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one tcgen05 GEMV launch on the bench workload, from the ncu
-# capture summarised in profiles/ (per launch, bytes).
-TRAFFIC_BYTES_PER_LAUNCH = 239648512
+def oracle_row_check(ctx, case):
+    """N = 1: the timed kernel's output row for weight set 0 against the CPU oracle (full row, M = 1)."""
+    import oracle as O
+    from tests import util
+    torch = ctx.torch
+    case.counter = 0
+    case.step()
+    got = case.result().cpu().numpy()
+    w, sw = case.weights[0]
+    a = case.a.cpu().numpy()
+    w_host = w.cpu().numpy()
+    want = O.fp8_linear(O.OP_MATMUL, O.E4M3, a, case.sa, w_host, sw, case.so)
+
+    def bound():
+        aa = np.abs(O.fp8_decode(O.E4M3, a).astype(np.float64)) * case.sa
+        ww = np.abs(O.fp8_decode(O.E4M3, w_host).astype(np.float64)) * sw
+        return (aa @ ww) * 2.0 ** -20
+    rep = util.fp8_parity_report(got, want, O.E4M3, bound, case.so)
+    rep["oracle"] = "CPU restatement of the reference Common kernel (oracle/feather_oracle.c), full output row of the timed kernel"
+    rep["ok"] = bool(rep["failed"] == 0 and rep["class_ok"])
+    del torch
+    return rep
 
 
-def extra_measurements(torch, B, dev, peaks, fp8_call, int8_call, stream, sa, out_scale, w, sw):
-    """The rest of the metric on one GPU, outside the timed steps: decode sweep and dense M=4096, FP8 and INT8."""
+def gather_check(ctx):
+    """N > 1: with one seeded weight shared by all ranks, the gathered [M, N] result on every rank against that rank's
+    own single-GPU result on the full weight.  Returns the number of differing bytes summed over ranks and cases."""
+    torch, B = ctx.torch, ctx.B
+    total, cases = 0, []
+    w_full, sw = synth(torch, (K, N), 0.02, SEED + 7, ctx.dev)  # same seed on every rank: the same weight
+    w_i8 = w_full.view(torch.int8)
+    for kind, m in (("fp8_e4m3", 1), ("fp8_e4m3", 256), ("int8", 16)):
+        w_src = w_i8 if kind == "int8" else w_full
+        part = w_src[:, ctx.n0:ctx.n1].contiguous()
+        sharded = LinearCase(ctx, kind, m, weights=[(part, sw), (part, sw)], use_graph=False)
+        single_ctx = Ctx.__new__(Ctx)
+        single_ctx.__dict__.update(ctx.__dict__)
+        single_ctx.world, single_ctx.dist, single_ctx.n0, single_ctx.n1, single_ctx.n_local = 1, None, 0, N, N
+        single = LinearCase(single_ctx, kind, m, weights=[(w_src, sw)])
+        if kind == "int8":  # the single-GPU run sees all N channel scales, the shard its slice of the same vector
+            assert torch.equal(single.scales[ctx.n0:ctx.n1], sharded.scales)
+        single.step()
+        want = single.result().clone()
+        bad = 0
+        for _ in range(2):  # both buffer parities
+            sharded.step()
+            got = sharded.result()
+            bad += int((got != want).sum().item())
+        sharded.close()
+        cases.append(f"{kind} M={m}")
+        total += bad
+        del sharded, single, part
+    del w_full
+    return ctx.sum_over_ranks(total), cases
+
+
+def sweep(ctx, peaks, quick):
+    """FP8 and INT8 at M = 1, 16, 256, 4096 over this rank's columns; at N > 1 the step includes the gather."""
+    torch, B = ctx.torch, ctx.B
     out = {}
-    n = w.shape[1]
-    w_i8 = w.view(torch.int8)
-    scales = torch.empty(n, dtype=torch.float32, device=dev).uniform_(1e-3, 1e-2)
-    w2 = torch.roll(w, 1, 0)  # a second weight set for the rotation
+    shared = {}
     for kind in ("fp8_e4m3", "int8"):
         for m in (1, 16, 256, 4096):
-            if kind == "fp8_e4m3":
-                a = torch.randint(0, 0x7E, (m, K), dtype=torch.uint8, device=dev)
-                o = torch.empty((m, n), dtype=torch.uint8, device=dev)
-                ds = [B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=m, k=K, n=n, a=a, w=ww, out=o, a_scale=sa, w_scale=sw,
-                                        out_scale=out_scale * 4, weights_static=True) for ww in (w, w2)]
-                call = fp8_call
-            else:
-                a = torch.randint(-127, 128, (m, K), dtype=torch.int8, device=dev)
-                o = torch.empty((m, n), dtype=torch.int8, device=dev)
-                ds = [B.int8_linear_desc(op=B.OP_MATMUL, m=m, k=K, n=n, a=a, w=ww.view(torch.int8), out=o, a_scale=0.02, a_zp=0,
-                                         w_scales=scales, w_zps=None, w_params=n, out_scale=2.0, out_zp=0, weights_static=True)
-                      for ww in (w, w2)]
-                call = int8_call
-            keep = [B.linear_workspace(torch, d) for d in ds]
-            i = [0]
-
-            def fn():
-                rc = call(C.byref(ds[i[0] & 1]), stream)
-                i[0] += 1
-                if rc != 0:
-                    raise RuntimeError(f"linear call failed: {rc}")
-            iters = 200 if m <= 256 else 20
-            ms = event_time_ms(torch, fn, iters, 3) / iters
-            gbs = algorithmic_bytes(m, n, kind == "int8") / (ms * 1e-3) / 1e9
-            tfl = 2.0 * m * K * n / (ms * 1e-3) / 1e12
-            out[f"{kind}_m{m}"] = {"us": round(ms * 1e3, 2), "GB/s": round(gbs, 1), "TFLOP/s": round(tfl, 2),
-                                   "hbm_frac": round(gbs / peaks["hbm_gbs"], 3),
-                                   "tensor_frac": round(tfl / (2.0 * peaks["bf16_tflops"]), 3), "kernel": B.last_variant()}
-            del keep
-    out["config4_decode_step"] = config4_decode_step(torch, B, dev, fp8_call, stream)
-    out["config3_conv"] = config3_conv(torch, B, dev, stream)
-    out["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "fp8_int8_dense_tflops": 2.0 * peaks["bf16_tflops"],
-                    "note": "8-bit dense peak taken as twice the measured bf16 burst figure", "source": peaks["source"]}
+            if quick and m in (16, 256):
+                continue
+            key = kind
+            case = LinearCase(ctx, kind, m, weights=shared.get(key))
+            shared[key] = case.weights
+            steps = 200 if m <= 256 else 20
+            blocks = case.time_blocks(steps, 4, 3)
+            ms = float(np.median(blocks)) / steps
+            n_local = ctx.n_local
+            gbs = algorithmic_bytes(m, n_local, kind == "int8") / (ms * 1e-3) / 1e9
+            tfl = 2.0 * m * K * n_local / (ms * 1e-3) / 1e12
+            rec = {"us": round(ms * 1e3, 2), "GB/s_per_gpu": round(gbs, 1), "TFLOP/s_per_gpu": round(tfl, 2),
+                   "hbm_frac": round(gbs / peaks["hbm_gbs"], 3), "tensor_frac": round(tfl / (2.0 * peaks["bf16_tflops"]), 3),
+                   "kernel": B.last_variant() if ctx.world == 1 else "tcgen05 + gather_sync"}
+            if ctx.world > 1:
+                rec["whole_job_TFLOP/s"] = round(tfl * ctx.world, 1)
+                rec["whole_job_weight_GB/s"] = round(K * N / (ms * 1e-3) / 1e9, 1)
+                rec["nvlink_bytes_out_per_rank_per_step"] = m * n_local * (ctx.world - 1)
+                rec["nvlink_GB/s_out_per_rank"] = round(m * n_local * (ctx.world - 1) / (ms * 1e-3) / 1e9, 1)
+                rec["gather"] = "peer stores + flag wait" if case.gather is not None else "NCCL all-gather"
+            out[f"{kind}_m{m}"] = rec
+            case.close()
+            del case
     return out
 
 
@@ -562,19 +620,229 @@ def cpu_baseline_measurement(torch):
         return {"value": None, "unit": "GB/s", "cores": 0, "kind": "unavailable", "sample": f"{type(exc).__name__}: {exc}"}
 
 
+def reference_x86_other_configs():
+    """The reference's x86 kernels for configs 2, 3, 4 and 5-INT8 on this box's host cores: best of a few compute()
+    calls after Prepare(), through the unmodified reference library.  Thread counts are the reference's own: FP8 linear
+    at most 4 OpenMP threads (src/kernel/x86/linear_fp8.cc:45-70), INT8 linear one thread (scalar loops,
+    src/kernel/x86/int8.cc:461-682), INT8 conv all OpenMP threads (src/kernel/x86/int8.cc:684-2346)."""
+    import oracle as O
+    from tests import util
+    if not O.have_ref():
+        return {"unavailable": "the reference library is not present on this box"}
+    out = {"host_cpus": os.cpu_count()}
+    try:
+        # config 2: INT8 MatMul M=128 K=1024 N=1024
+        case = util.make_int8_linear(128, 1024, 1024, seed=2)
+        kern = O.int8_linear(O.OP_MATMUL, case["a"], case["sa"], 0, case["w"], case["ws"], None, case["so"], 0, impl="ref", device=O.X86, return_kernel=True)
+        kern.prepare()
+        out["config2_int8_m128_k1024_n1024"] = {"ms": round(kern.time_compute(2) * 1e3, 2), "threads": 1}
+        # config 3: INT8 conv + the INT8 ReLU node behind it
+        case = util.make_int8_conv(1, 64, 160, 160, 64, 3, 3, seed=3)
+        kern = O.int8_conv2d(case["x"], case["sx"], 0, case["w"], case["ws"], None, case["bias"], case["so"], 0, impl="ref", device=O.X86,
+                             return_kernel=True)
+        kern.prepare()
+        flags = open("/proc/cpuinfo").read()
+        out["config3_conv_64x160x160"] = {"ms": round(kern.time_compute(5) * 1e3, 2), "threads": os.cpu_count(), "avx_vnni": " avx_vnni" in flags,
+                                          "note": "conv node only; the ReLU node behind it is a 1.6 MB table lookup"}
+        # config 4: the three projection shapes at M = 1 (FP8 E5M2, packed BF16 GEMV), times their count per decode step
+        total = 0.0
+        per_shape = {}
+        for (k, n, count) in ((1024, 1024, 4 * 24), (1024, 3584, 2 * 24), (3584, 1024, 24)):
+            c = util.make_fp8_linear(O.E5M2, 1, k, n, seed=k + n, pow2=True)
+            kern = O.fp8_linear(O.OP_MATMUL, O.E5M2, c["a"], c["sa"], c["w"], c["sw"], c["so"], impl="ref", device=O.X86, return_kernel=True)
+            kern.prepare()
+            t = kern.time_compute(20)
+            per_shape[f"{k}x{n}"] = round(t * 1e6, 1)
+            total += t * count
+        out["config4_decode_step_m1"] = {"ms": round(total * 1e3, 2), "threads": min(4, os.cpu_count() or 1), "per_projection_us": per_shape,
+                                         "note": "168 MatMul nodes only (per-shape time x count, weights of one shape stay cached); Cast / RMSNorm / Add nodes not included"}
+        # config 5 INT8, M = 1: a 2048-column slice of the weight, scaled to N = 28672 (the kernel is a scalar loop over
+        # outputs; its time is proportional to the number of columns)
+        cols = 2048
+        w, ws = util.make_int8_weight(K, cols, seed=5)
+        a = np.random.default_rng(5).integers(-127, 128, (1, K), dtype=np.int8)
+        kern = O.int8_linear(O.OP_MATMUL, a, 0.02, 0, w, ws, None, util.int8_out_scale(K, ws), 0, impl="ref", device=O.X86, return_kernel=True)
+        kern.prepare()
+        t = kern.time_compute(2)
+        out["config5_int8_m1"] = {"ms": round(t * N / cols * 1e3, 1), "threads": 1, "extrapolated": f"measured {round(t * 1e3, 2)} ms on {cols} of {N} columns"}
+    except Exception as exc:  # reported, never required
+        out["error"] = f"{type(exc).__name__}: {exc}"
+    return out
+
+
+def run_gpu_arm(args):
+    import torch
+    import infer_b200 as B
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    dev = torch.device("cuda", local_rank)
+    B.lib()  # fails loudly if the CUDA library is missing
+    peaks = measured_peaks()
+    ctx = Ctx(torch, B, dist, world, rank, dev)
+    failures = []
+
+    # ---- N > 1: prove the gathered bytes before timing anything ----
+    gather_mismatch, gather_cases = None, None
+    if world > 1:
+        gather_mismatch, gather_cases = gather_check(ctx)
+        if gather_mismatch != 0:
+            failures.append(f"gathered result differs from the single-GPU result in {gather_mismatch} bytes")
+
+    main = LinearCase(ctx, "fp8_e4m3", 1)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    # ---- timed region: blocks of exactly K steps, device-timed, max over ranks; the median block is reported ----
+    per_step_launches = main.launches_per_step()
+    block_ms = main.time_blocks(args.steps, args.warmup, BLOCKS)
+    total_ms = float(np.median(block_ms))
+    variant = B.last_variant()
+    status_timed = B.device_status()
+    ms_per_step = total_ms / args.steps
+    bytes_step = algorithmic_bytes(1, N)
+    value = bytes_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: pinned host activation in, host result out, every step ----
+    a_host = torch.empty((1, K), dtype=torch.uint8).pin_memory()
+    a_host.copy_(main.a.cpu())
+    width = ctx.shard.width
+    out_host = torch.empty((1, width), dtype=torch.uint8).pin_memory()
+    full_host = torch.empty((1, N), dtype=torch.uint8).pin_memory()
+    plans = []
+    if world == 1:
+        for i in range(2):
+            w, sw = main.weights[i]
+            hd = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=1, k=K, n=N, a=None, w=None, out=None, a_scale=main.sa,
+                                   w_scale=sw, out_scale=main.so, ldo=width)
+            w_host = w.cpu()
+            hd.w = w_host.data_ptr()
+            plans.append(B.Plan(hd))
+            del w_host
+    pc = [0]
+    e2e_case = None
+    if world > 1:
+        e2e_case = LinearCase(ctx, "fp8_e4m3", 1, weights=main.weights, use_graph=False)
+        a_stage = e2e_case.a
+
+    def e2e_step():
+        if world == 1:
+            plans[pc[0] & 1].run(a_host, out_host, ctx.stream)
+            pc[0] += 1
+            return
+        # N > 1: pinned-host activation in, sharded kernels with peer stores, the gathered row back to the host
+        a_stage.copy_(a_host, non_blocking=True)
+        e2e_case.step()
+        if e2e_case.gather is not None:
+            full_host.copy_(e2e_case.gather.view(torch, e2e_case.gather.epoch & 1), non_blocking=True)
+        else:
+            full_host.copy_(e2e_case.nccl_gathered.view(1, -1)[:, :N], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = min(args.steps, 500)
+    e2e_blocks = [ctx.max_over_ranks(event_time_ms(torch, e2e_step, e2e_steps, max(args.warmup, 3) if b == 0 else 0, ctx.barrier if dist else None))
+                  for b in range(3)]
+    e2e_ms = float(np.median(e2e_blocks)) / e2e_steps
+    e2e_value = bytes_step / (e2e_ms * 1e-3) / 1e9
+    status_e2e = B.device_status()
+    for p in plans:
+        p.close()
+    if e2e_case is not None:
+        e2e_case.close()
+        e2e_case = None
+
+    # ---- N = 1: the timed kernel's output against the CPU oracle ----
+    parity = None
+    if world == 1:
+        parity = oracle_row_check(ctx, main)
+        if not parity["ok"]:
+            failures.append(f"output of the timed kernel differs from the oracle: {parity}")
+    gather_kind = None
+    if world > 1:
+        gather_kind = "outputs stored to all ranks over NVLink (peer stores + flag wait)" if main.gather is not None else "NCCL all-gather"
+    n_sets, graph_used = main.n_sets, main.graph is not None
+    main.close()
+    del main
+
+    extra = {}
+    if not args.quick or world > 1:
+        extra = sweep(ctx, peaks, quick=args.quick)
+        if rank == 0 and world == 1:
+            extra["config4_decode_step"] = config4_decode_step(torch, B, dev, ctx.fp8_call, ctx.stream)
+            extra["config3_conv"] = config3_conv(torch, B, dev, ctx.stream)
+        extra["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "fp8_int8_dense_tflops": 2.0 * peaks["bf16_tflops"],
+                          "note": "8-bit dense peak taken as twice the measured bf16 burst figure", "source": peaks["source"]}
+    status_extra = B.device_status()
+    device_status = ctx.max_over_ranks(float(max(abs(status_timed), abs(status_e2e), abs(status_extra))))
+    if device_status != 0:
+        failures.append(f"device status word non-zero on some rank: {int(device_status)}")
+    sampler.stop_flag = True
+    sampler.join(timeout=1.0)
+    cpu_baseline = None
+    if rank == 0 and world == 1:
+        cpu_baseline = cpu_baseline_measurement(torch)
+        if not args.quick:
+            extra["reference_x86"] = reference_x86_other_configs()
+
+    if rank == 0:
+        achieved = value if world == 1 else value / world
+        cluster = variant == "tcgen05" and per_step_launches - (1 if world > 1 else 0) == 1
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "blocks": BLOCKS, "block_ms": [round(b, 4) for b in block_ms],
+            "config": bench_config(world, {
+                "sharding": (f"N column-sharded over {world} GPUs, {gather_kind}" + (", steps replayed from a CUDA graph" if graph_used else "")) if world > 1 else "one GPU",
+                "l2": f"inputs larger than L2: {n_sets} weight sets of {K * ctx.n_local / 1e6:.0f} MB rotated", "kernel": variant}),
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
+                         "peak_source": peaks["source"],
+                         "note": "per GPU; step = " + ("single-launch tcgen05 cluster kernel" if cluster else "tcgen05 GEMV + split-K reduce kernel") +
+                                 (" + gather signal/wait kernel" if world > 1 else "") + "; median of the timed blocks"},
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": K, "d2h_bytes_per_step": width if world == 1 else N,
+                    "ms_per_step": round(e2e_ms, 5),
+                    "api": "fth_b200_plan_run (pinned host activation in, host result out)" if world == 1 else
+                           "pinned host activation in, fth_b200_fp8_linear with peer stores + fth_b200_gather_sync, gathered row out"},
+            "gpu_launches": int(per_step_launches * args.steps),
+            "device_status": int(device_status),
+            "parity": parity,
+            "gather_mismatch_bytes": gather_mismatch,
+            "gather_checked": gather_cases,
+            "clocks": sampler.summary(),
+            "cpu_baseline": cpu_baseline,
+            "extra": extra,
+        }
+        if failures:
+            line["failures"] = failures
+        print(json.dumps(line))
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    if failures:
+        print("[bench] FAILED: " + "; ".join(failures), file=sys.stderr)
+        return 1
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--quick", action="store_true", help="skip the extra sweep (decode / dense / INT8)")
+    ap.add_argument("--quick", action="store_true", help="shorter sweep: M = 1 and 4096 only, no x86 timings of the other configs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference_arm(args)
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        args.quick = True
     return run_gpu_arm(args)
 
 

@@ -146,7 +146,7 @@ size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc)
  * global memory that every GPU which loads the library holds until the process exits.  The call allocates
  * nothing and frees nothing.
  *   - A shape whose partial sums do not fit (fth_b200_fp8_linear_workspace_bytes > 4 MiB; for K >= 1024, M = 1 fits up to
- *     N = 65536 and M = 16 up to N = 8192) returns FTH_B200_ERR_SCRATCH_LIMIT; shapes the tensor-core
+ *     N = 131072 and M = 16 up to N = 8192) returns FTH_B200_ERR_SCRATCH_LIMIT; shapes the tensor-core
  *     family declines return FTH_B200_ERR_UNSUPPORTED.
  *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress) with that device
  *     current; make that first call before starting any stream capture.

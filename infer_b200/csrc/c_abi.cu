@@ -1,6 +1,8 @@
 // C ABI entry points for the linear ops: validation (the contract checks of the reference kernels),
 // shape split between kernel families, launch bookkeeping.
 #include <cmath>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "linear_internal.h"
@@ -21,6 +23,43 @@ int CheckLaunch() { return cudaGetLastError() == cudaSuccess ? FTH_B200_OK : FTH
 // A non-sticky error some other library left behind in this thread (NCCL's peer-access probes do) must not be blamed on
 // the next launch here: every entry point that launches starts by discarding it.
 void ClearStaleError() { (void)cudaGetLastError(); }
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_setup_mutex;
+int g_sm_count[kMaxDevices] = {};
+struct SmemOptIn { const void* kernel; int device; size_t bytes; };
+std::vector<SmemOptIn> g_smem_opt_in;
+}  // namespace
+
+int SmCount() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return kNumSms;
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    if (g_sm_count[device] == 0) {
+        int count = 0;
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = kNumSms;
+        g_sm_count[device] = count;
+    }
+    return g_sm_count[device];
+}
+
+int EnsureDynamicSmem(const void* kernel, size_t bytes) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    for (SmemOptIn& e : g_smem_opt_in) {
+        if (e.kernel == kernel && e.device == device) {
+            if (e.bytes >= bytes) return FTH_B200_OK;
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
+            e.bytes = bytes;
+            return FTH_B200_OK;
+        }
+    }
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    g_smem_opt_in.push_back(SmemOptIn{kernel, device, bytes});
+    return FTH_B200_OK;
+}
 
 namespace {
 
@@ -64,6 +103,7 @@ int ValidateInt8(const fth_b200_int8_linear_desc* d) {
     // Every running sum must stay inside int32 (FitsInt32 after each term, int8_kernel_utils.h:99-114).
     // Decide it on the host from the worst case, as the reference's x86 path does (x86/int8.cc:1963-1980),
     // so that no device-side error flag or synchronisation is needed.
+    if (d->k > (int64_t{1} << 31)) return FTH_B200_ERR_OVERFLOW;  // also keeps the product below from wrapping
     const int64_t a_span = 128 + (d->a_zp < 0 ? -d->a_zp : d->a_zp);
     const int64_t w_span = 128 + d->w_zp_max_abs;
     const int64_t worst = d->k * a_span * w_span + d->bias_max_abs;

@@ -16,6 +16,11 @@ constexpr int kNumSms = 148;  // B200: 2 dies x 74 SMs
 void NoteLaunch(const char* variant, int64_t launches = 1);
 int CheckLaunch();  // FTH_B200_OK or FTH_B200_ERR_CUDA (reads and clears the last error)
 void ClearStaleError();  // discards an error left behind by other code before this library launches
+// Per-device launch set-up.  One process may drive several GPUs (one session per device), and both the SM count and
+// a kernel's dynamic shared-memory limit belong to the device that is current at the launch.
+int SmCount();  // SMs of the current device (looked up once per device)
+// Raises `kernel`'s dynamic shared-memory limit to `bytes` on the current device unless it is already that high there.
+int EnsureDynamicSmem(const void* kernel, size_t bytes);  // FTH_B200_OK or FTH_B200_ERR_CUDA
 
 // ---- FP8 codec -------------------------------------------------------------------------------------
 // Decode through the hardware converters: exact for every code, including subnormals, the E4M3 NaN

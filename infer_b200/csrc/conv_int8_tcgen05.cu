@@ -16,17 +16,6 @@
 #include "tcgen05.cuh"
 #include "tma.cuh"
 
-// Optional phase timeline of CTA 0 in SM clocks (development aid, compiled out unless FTH_B200_TRACE is defined).
-#ifdef FTH_B200_TRACE
-__device__ unsigned long long g_conv_trace[32];
-#define FTH_CTRACE(i) do { if (blockIdx.x == 0) g_conv_trace[i] = static_cast<unsigned long long>(clock64()); } while (0)
-extern "C" int fth_b200_conv_trace_read(unsigned long long* out) {
-    return cudaMemcpyFromSymbol(out, g_conv_trace, sizeof(g_conv_trace)) == cudaSuccess ? 0 : -1;
-}
-#else
-#define FTH_CTRACE(i) do {} while (0)
-#endif
-
 namespace fth {
 namespace {
 
@@ -134,7 +123,6 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
     const ConvArgs& c = p.c;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    if (threadIdx.x == 0) FTH_CTRACE(0);
     constexpr uint32_t kTmemCols = kAcc * BQ < 32 ? 32 : kAcc * BQ;
 
     if (threadIdx.x == 0) {
@@ -170,7 +158,6 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     __syncthreads();
     umma::FenceAfterThreadSync();
     const uint32_t tmem_base = *tmem_base_slot;
-    if (threadIdx.x == 0) FTH_CTRACE(1);
 
     auto decode_tile = [&](int64_t t, int64_t* n, int64_t* oh0, int64_t* ow0) {
         *ow0 = (t % p.tiles_w) * kTileW;
@@ -199,7 +186,6 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 MbarExpectTx(w_ready, static_cast<uint32_t>(p.kblocks * w_block));
                 for (int kb = 0; kb < p.kblocks; ++kb) TmaLoad2D(w_smem + kb * w_block, &map_w, kb * kRowBytes, 0, w_ready);
             }
-            FTH_CTRACE(2);
             int issued = 0;
             int stage = 0;
             uint32_t phase = 0;
@@ -220,7 +206,6 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                     if (++cb == p.cblocks) { cb = 0; if (++kx == static_cast<int>(c.kw)) { kx = 0; ++ky; } }
                 }
-                if (t == blockIdx.x) FTH_CTRACE(3);
             }
         }
     } else if (warp == 1) {
@@ -228,7 +213,6 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             bool failed = !MbarWait(w_ready, 0, p.status, 21, 0);
-            FTH_CTRACE(4);
             int64_t iter = 0;
             for (int64_t t = blockIdx.x; t < p.tiles && !failed; t += gridDim.x, ++iter) {
                 const int acc = static_cast<int>(iter % kAcc);
@@ -249,7 +233,6 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     umma::Commit(&empty[stage]);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
-                if (iter == 0) FTH_CTRACE(5);
                 if (!failed) umma::Commit(&tmem_full[acc]);
             }
         }
@@ -268,7 +251,6 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             const int64_t ow_base = ow - (lane & 3);
             if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 24, acc)) failed = true;
             umma::FenceAfterThreadSync();
-            if (threadIdx.x == 64 + 64) FTH_CTRACE(6 + 2 * static_cast<int>(iter));
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BQ);
             // Output is NCHW: for one channel the tile's 32 pixels of a row are contiguous.  Each thread requantises 16
             // channels of its pixel (independent chains, no branches between them), then every quad of lanes
@@ -330,7 +312,6 @@ ConvTcgen05Kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             umma::FenceBeforeThreadSync();
             __syncwarp();
             if (lane == 0) MbarArrive(&tmem_empty[acc]);
-            if (threadIdx.x == 64 + 64) FTH_CTRACE(7 + 2 * static_cast<int>(iter));
         }
     }
 
@@ -353,14 +334,8 @@ size_t SmemBytesFor(int bq, int kblocks) {
 template <int BQ>
 int LaunchTyped(const CUtensorMap& map_x, const CUtensorMap& map_w, const ConvTcParams& p, size_t smem, cudaStream_t stream) {
     auto kernel = ConvTcgen05Kernel<BQ>;
-    static size_t configured = 0;
-    if (smem > configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return FTH_B200_ERR_CUDA;
-        configured = smem;
-    }
-    int sms = kNumSms, device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), smem) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
+    const int sms = SmCount();
     const int grid = static_cast<int>(p.tiles < sms ? p.tiles : sms);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));

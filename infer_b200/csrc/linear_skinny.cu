@@ -293,11 +293,7 @@ int LaunchKn(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& 
     chunk = (chunk + 63) / 64 * 64;
     const size_t smem = KnSmemBytes<DTYPE, MB>();
     auto kernel = SkinnyKnKernel<DTYPE, MB>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return FTH_B200_ERR_CUDA;
-        configured = true;
-    }
+    if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), smem) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>((args.n + kTileN - 1) / kTileN), static_cast<unsigned>(split),
                        static_cast<unsigned>((args.m + MB - 1) / MB));
@@ -455,11 +451,7 @@ int LaunchNk(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& 
     constexpr bool kInt8 = DTYPE == FTH_B200_INT8;
     const size_t smem = static_cast<size_t>(MB) * args.k * (kInt8 ? 1 : 4);
     auto kernel = SkinnyNkKernel<DTYPE, MB, R>;
-    static size_t configured = 0;
-    if (smem > configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return FTH_B200_ERR_CUDA;
-        configured = smem;
-    }
+    if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), smem) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     const dim3 grid(static_cast<unsigned>((args.n + kWarps * R - 1) / (kWarps * R)), static_cast<unsigned>((args.m + MB - 1) / MB));
     kernel<<<grid, kThreads, smem, stream>>>(args, fe, ie);
     NoteLaunch("skinny");

@@ -365,15 +365,6 @@ bool GetWeightMap(const void* w, int64_t k, int64_t n, CUtensorMap* out) {
     return true;
 }
 
-int SmCount() {
-    static int count = 0;
-    if (count == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = kNumSms;
-    }
-    return count;
-}
 
 template <int DTYPE, int MB>
 int LaunchStream(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* scratch,
@@ -386,11 +377,7 @@ int LaunchStream(const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilog
     CUtensorMap map;
     if (!GetWeightMap(args.w, args.k, args.n, &map)) return FTH_B200_ERR_CUDA;
     auto kernel = StreamKnKernel<DTYPE, MB>;
-    static size_t configured = 0;
-    if (smem > configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemLimit)) != cudaSuccess) return FTH_B200_ERR_CUDA;
-        configured = kSmemLimit;
-    }
+    if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), kSmemLimit) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     StreamParams p;
     p.args = args;
     p.geo = geo;

@@ -46,7 +46,6 @@ struct TcGeometry {
 
 
 // ---- launchers, one per kernel family (each in its own translation unit) ------------------------------------------
-int SmCountTc();
 // M <= 128, several waves of work: persistent swapped kernel (+ the split-K reduce pass when g.split > 1).
 int LaunchSwapped(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p,
                   const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream);

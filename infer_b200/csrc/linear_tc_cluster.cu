@@ -1,17 +1,5 @@
 #include "linear_tc.cuh"
 
-// Optional phase timeline of CTA 0 in SM clocks (development aid, compiled out unless FTH_B200_TRACE is defined).
-#ifdef FTH_B200_TRACE
-__device__ unsigned long long g_trace[32];
-#define FTH_TRACE(i) do { if (blockIdx.x == 0) g_trace[i] = static_cast<unsigned long long>(clock64()); } while (0)
-extern "C" int fth_b200_trace_read(unsigned long long* out) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : -1;
-}
-#else
-#define FTH_TRACE(i) do {} while (0)
-#endif
-
-
 namespace fth {
 namespace tc {
 namespace {
@@ -113,7 +101,6 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(x_full + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    if (threadIdx.x == 0) FTH_TRACE(0);
     const bool convert = p.args.a_dtype != 0;
 
     if (threadIdx.x == 0) {
@@ -130,7 +117,6 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     __syncthreads();
     umma::FenceAfterThreadSync();
     const uint32_t tmem_base = *tmem_base_slot;
-    if (threadIdx.x == 0) FTH_TRACE(1);
     ClusterArrive();  // "this CTA is running": peers wait for it before they write into our exchange buffer
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -179,9 +165,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             if (p.args.w_static) {
                 for (; kb < nb && kb < stages; ++kb) load_weights(kb);
             }
-            FTH_TRACE(3);
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            FTH_TRACE(2);
             if (!convert) {
                 MbarExpectTx(q_full, static_cast<uint32_t>(nb) * BQ * kBlockK);
                 for (int j = 0; j < nb; ++j) TmaLoad2D(q_tiles + j * (BQ * kBlockK), &map_q, (kb_begin + j) * kBlockK, 0, q_full);
@@ -189,7 +173,6 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             for (; kb < nb; ++kb) {
                 if (!load_weights(kb)) break;
             }
-            FTH_TRACE(4);
         }
     } else if (warp == 1) {
         // ================================ MMA issuer ================================
@@ -200,7 +183,6 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             for (int kb = 0; kb < nb && !failed; ++kb) {
                 if (!MbarWait(&full[stage], phase, p.status, 22, stage)) { failed = true; break; }
                 if (kb == 0 && !MbarWait(q_full, 0, p.status, 21, 0)) { failed = true; break; }  // activations arrive last
-                if (kb == 0) FTH_TRACE(5);
                 umma::FenceAfterThreadSync();
                 const uint32_t ps = SmemAddr(ring + static_cast<size_t>(stage) * kPBytes);
                 const uint32_t qs = SmemAddr(q_tiles + kb * (BQ * kBlockK));
@@ -213,7 +195,6 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 umma::Commit(&empty[stage]);
                 if (++stage == stages) { stage = 0; phase ^= 1u; }
             }
-            FTH_TRACE(6);
             if (!failed) umma::Commit(tmem_full);
         }
     } else {
@@ -252,16 +233,13 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes → visible to the MMA's reads
             MbarArrive(q_full);
-            if (et == 0) FTH_TRACE(7);
         }
         const int row = (warp & 3) * 32 + lane;  // TMEM lane = channel inside the tile
         // Bytes this CTA will receive: from each of the `split` chunks, its L rows of ceil(m / 4) 16-byte vectors.
         if (et == 0) MbarExpectTx(x_full, static_cast<uint32_t>(p.split) * rows_per_cta * ((m + 3) / 4) * 16);
         ClusterWait();  // every CTA of the cluster is running and has initialised its barriers
-        if (et == 0) FTH_TRACE(8);
         if (nb > 0) {
             const bool ok = MbarWait(tmem_full, 0, p.status, 23, 0);
-            if (et == 0) FTH_TRACE(9);
             umma::FenceAfterThreadSync();
             if (ok) {
                 // Deal the accumulator rows out: row r goes to CTA r / L, slot [this chunk][r % L].  Each 16-byte
@@ -284,10 +262,12 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 }
             }
         }
-        if (et == 0) FTH_TRACE(10);
         // A CTA leaves only after everything addressed to it has landed, so no peer ever writes into a CTA that is gone.
+        // Second phase of the cluster barrier: "this CTA has sent everything it will ever send".  The matching wait is
+        // at the very end of the kernel, so that no CTA leaves while a peer could still store into its shared memory —
+        // also when a bounded wait gave up somewhere.  In a healthy run every peer has long arrived by then.
+        ClusterArrive();
         const bool delivered = MbarWait(x_full, 0, p.status, 24, 0);
-        if (et == 0) FTH_TRACE(11);
 
         // One output per thread and round: channel r of this CTA's rows (fastest, so a warp stores consecutive
         // channels) of activation row q.  The chunks are added in chunk order, as the two-kernel path adds them.
@@ -318,7 +298,6 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     }
                     acc = __float_as_uint(sum);
                 }
-                if (et == 0) FTH_TRACE(14);
                 if (n < p.p_total) { code = FinishOne<INT8>(p, fe, ie, q, n, acc); stored = true; }
             }
             if (p.args.argmax_keys != nullptr)
@@ -328,14 +307,14 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     if (warp < 2) {
         if (!(warp == 0 && lane == 0 && nb > 0)) asm volatile("griddepcontrol.wait;" ::: "memory");
         ClusterWait();
+        ClusterArrive();  // these warps send nothing: second phase right away
     }
-    if (threadIdx.x == 64) FTH_TRACE(12);
+    ClusterWait();  // second phase: every CTA of the cluster has finished sending
     umma::FenceBeforeThreadSync();
     __syncthreads();
     if (warp == 1) {
         umma::FenceAfterThreadSync();
         umma::TmemDealloc(tmem_base, C::kTmemCols);
-        if (lane == 0) FTH_TRACE(13);
     }
 }
 
@@ -345,11 +324,7 @@ int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUte
     TcParams p = p_in;
     p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks);
     auto kernel = LinearClusterKernel<INT8, P_MN, BQ>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ClusterCfg<BQ>::kSmemBytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
-        configured = true;
-    }
+    if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), ClusterCfg<BQ>::kSmemBytes) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(g.p_tiles * g.cluster));
     cfg.blockDim = dim3(ClusterCfg<BQ>::kThreads);

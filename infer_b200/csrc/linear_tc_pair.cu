@@ -242,13 +242,9 @@ template <bool INT8, bool Q_MN>
 int LaunchPairTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p, const Fp8Epilogue& fe,
                     const Int8Epilogue& ie, cudaStream_t stream) {
     auto kernel = LinearPairKernel<INT8, Q_MN>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PairCfg::kSmemBytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
-        configured = true;
-    }
+    if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), PairCfg::kSmemBytes) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     const int64_t units = ((p.p_total + 255) / 256) * p.q_tiles;
-    const int64_t slots = SmCountTc() / 2;
+    const int64_t slots = SmCount() / 2;
     const int64_t pairs = units < slots ? units : slots;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(pairs * 2));

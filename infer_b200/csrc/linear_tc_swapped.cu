@@ -232,7 +232,9 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BQ);
 #pragma unroll 1
             for (int c0 = 0; c0 < BQ; c0 += 16) {
-                if (c0 >= q_count) break;  // uniform across the warp
+                // uniform across the warp; after a wait has given up the accumulator is not valid: nothing is read or
+                // stored any more (the status word tells the host), the loop only keeps handing buffers back
+                if (c0 >= q_count || failed) break;
                 uint32_t v[16];
                 umma::TmemLoad16(taddr + c0, v);
                 umma::TmemLoadWait();
@@ -387,12 +389,8 @@ template <bool INT8, bool P_MN, int BQ>
 int LaunchTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p, const Fp8Epilogue& fe,
                 const Int8Epilogue& ie, cudaStream_t stream) {
     auto kernel = LinearTcgen05Kernel<INT8, P_MN, BQ>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg<BQ>::kSmemBytes)) != cudaSuccess) return FTH_B200_ERR_CUDA;
-        configured = true;
-    }
-    const int64_t slots = static_cast<int64_t>(SmCountTc()) * Cfg<BQ>::kCtasPerSm;
+    if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), Cfg<BQ>::kSmemBytes) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
+    const int64_t slots = static_cast<int64_t>(SmCount()) * Cfg<BQ>::kCtasPerSm;
     const int grid = static_cast<int>(p.units < slots ? p.units : slots);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));

@@ -24,16 +24,6 @@
 namespace fth {
 namespace tc {
 
-int SmCountTc() {
-    static int count = 0;
-    if (count == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = kNumSms;
-    }
-    return count;
-}
-
 // 1 / s when s is a normal power of two with a normal reciprocal (x * (1/s) then equals x / s bit for bit), else 0.
 float ExactReciprocal(float s) {
     int e = 0;
@@ -70,7 +60,7 @@ TcGeometry GeometryFor(const LinearArgs& a) {
         int c = 1;
         while (c < g.split) c *= 2;
         // more than one wave of CTAs: the persistent kernel keeps its ring full across tiles and is faster (measured)
-        if (g.p_tiles * c <= static_cast<int64_t>(SmCountTc()) * 2) g.cluster = c;
+        if (g.p_tiles * c <= static_cast<int64_t>(SmCount()) * 2) g.cluster = c;
     }
     return g;
 }

@@ -1,7 +1,7 @@
 // Host-buffer plans: Prepare()/compute() for one node with an immutable weight.
 //
 // create  = what KernelBase::Prepare() does once per session: upload weight, scales, zero points, bias and
-//           tables, scan FP8 weights for NaN/Inf codes, size the workspace.  Allocates and synchronises.
+//           tables, size the workspace.  Allocates and synchronises.
 // run     = what compute() does in the reference CUDA kernels (src/kernel/cuda/matmul.cu:230-272):
 //           activation host→device, launch, result device→host, on the caller's stream, then waits.
 // launch  = the same launch on device-resident buffers, no copies and no wait.
@@ -136,6 +136,10 @@ extern "C" int fth_b200_plan_create_int8_linear(const fth_b200_int8_linear_desc*
 extern "C" int fth_b200_plan_create_int8_conv2d(const fth_b200_int8_conv2d_desc* h, fth_b200_plan** plan) {
     if (!h || !plan || !h->w || !h->w_scales || h->group <= 0 || h->oc <= 0) return FTH_B200_ERR_INVALID;
     if (h->w_params != 1 && h->w_params != h->oc) return FTH_B200_ERR_INVALID;
+    // geometry first: everything below divides by these or sizes allocations from them
+    if (h->batch <= 0 || h->ic <= 0 || h->ih <= 0 || h->iw <= 0 || h->kh <= 0 || h->kw <= 0) return FTH_B200_ERR_INVALID;
+    if (h->stride_h <= 0 || h->stride_w <= 0 || h->dilation_h <= 0 || h->dilation_w <= 0 || h->pad_h < 0 || h->pad_w < 0) return FTH_B200_ERR_INVALID;
+    if (h->ic % h->group != 0 || h->oc % h->group != 0) return FTH_B200_ERR_INVALID;
     auto* p = new (std::nothrow) fth_b200_plan();
     if (!p) return FTH_B200_ERR_INVALID;
     p->kind = Kind::kInt8Conv;
@@ -182,20 +186,17 @@ extern "C" int fth_b200_plan_create_int8_conv2d(const fth_b200_int8_conv2d_desc*
     return FTH_B200_OK;
 }
 
-// `mirror`: device-visible address of a second copy of the output (pinned host memory), or null.
-static int LaunchPlan(fth_b200_plan* p, const void* device_in, void* device_out, void* mirror, fth_b200_stream_t stream) {
+static int LaunchPlan(fth_b200_plan* p, const void* device_in, void* device_out, fth_b200_stream_t stream) {
     if (!p || !device_in || !device_out) return FTH_B200_ERR_INVALID;
     switch (p->kind) {
         case Kind::kFp8Linear: {
             fth_b200_fp8_linear_desc d = p->fp8;
             d.a = device_in; d.out = device_out;
-            if (mirror) { d.gather_peers = 1; d.gather_out[0] = mirror; }
             return fth_b200_fp8_linear(&d, stream);
         }
         case Kind::kInt8Linear: {
             fth_b200_int8_linear_desc d = p->int8;
             d.a = device_in; d.out = device_out;
-            if (mirror) { d.gather_peers = 1; d.gather_out[0] = mirror; }
             return fth_b200_int8_linear(&d, stream);
         }
         case Kind::kInt8Conv: {
@@ -210,19 +211,16 @@ static int LaunchPlan(fth_b200_plan* p, const void* device_in, void* device_out,
 }
 
 extern "C" int fth_b200_plan_launch(fth_b200_plan* p, const void* device_in, void* device_out, fth_b200_stream_t stream) {
-    return LaunchPlan(p, device_in, device_out, nullptr, stream);
+    return LaunchPlan(p, device_in, device_out, stream);
 }
 
 extern "C" int fth_b200_plan_run(fth_b200_plan* p, const void* host_in, void* host_out, fth_b200_stream_t stream_) {
     if (!p || !host_in || !host_out) return FTH_B200_ERR_INVALID;
     auto stream = static_cast<cudaStream_t>(stream_);
     if (cudaMemcpyAsync(p->in.ptr, host_in, static_cast<size_t>(p->in_bytes), cudaMemcpyHostToDevice, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
-    // (Writing a pinned result buffer straight from the kernels' epilogue, as a second copy of the output, was
-    // measured: it saves the copy below and costs the same again in the reduce pass, whose stores then cross PCIe.)
-    void* mirror = nullptr;
-    const int rc = LaunchPlan(p, p->in.ptr, p->out.ptr, mirror, stream_);
+    const int rc = LaunchPlan(p, p->in.ptr, p->out.ptr, stream_);
     if (rc != FTH_B200_OK) return rc;
-    if (!mirror && cudaMemcpyAsync(host_out, p->out.ptr, static_cast<size_t>(p->out_bytes), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    if (cudaMemcpyAsync(host_out, p->out.ptr, static_cast<size_t>(p->out_bytes), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
     if (cudaStreamSynchronize(stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
     return FTH_B200_OK;
 }

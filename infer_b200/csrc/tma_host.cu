@@ -41,8 +41,10 @@ CUtensorMapSwizzle ToDriver(TmaSwizzle s) {
 int* DeviceStatusPtr() {
     // One address per device; looked up on first use while that device is current.
     static int* ptrs[64] = {};
+    static std::mutex mutex;
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mutex);
     if (ptrs[device] == nullptr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;

@@ -106,9 +106,11 @@ float fo_fp8_decode(int dtype, uint8_t bits) {
 }
 
 void fo_fp8_encode_array(int dtype, const float* v, uint8_t* out, int64_t n) {
+#pragma omp parallel for schedule(static) if (n > 65536)
     for (int64_t i = 0; i < n; ++i) out[i] = fo_fp8_encode(dtype, v[i]);
 }
 void fo_fp8_decode_array(int dtype, const uint8_t* b, float* out, int64_t n) {
+#pragma omp parallel for schedule(static) if (n > 65536)
     for (int64_t i = 0; i < n; ++i) out[i] = fo_fp8_decode(dtype, b[i]);
 }
 
@@ -159,8 +161,11 @@ static int fits_int32(int64_t v) { return v >= INT32_MIN && v <= INT32_MAX; }
  * a [M,K]; w [K,N] (trans_b: [N,K]); bias FP8 [N] (mode 1) or [M,N] (mode 2), mode 0 none.
  * op 0 FC / 1 MatMul: sum (+ bias);  op 2 Gemm: sum *= alpha; sum += beta * bias.
  * Each term is (decode(a)·s_a)·(decode(w)·s_w) in FP32, added in ascending k; the result is
- * encode(sum / s_out) with an FP32 divide (src/kernel/common/kernel_io.h:58-78). */
-int fo_fp8_linear(int op, int dtype, const uint8_t* a, float a_scale, const uint8_t* w, float w_scale,
+ * encode(sum / s_out) with an FP32 divide (src/kernel/common/kernel_io.h:58-78).
+ * fo_fp8_linear_plain is the loop nest as the reference writes it (one output at a time); fo_fp8_linear below
+ * computes the same values in the same per-output order, blocked over columns so that large slices finish in
+ * seconds.  tests/test_oracle_blocked.py checks that the two agree byte for byte. */
+int fo_fp8_linear_plain(int op, int dtype, const uint8_t* a, float a_scale, const uint8_t* w, float w_scale,
                   const uint8_t* bias, float bias_scale, int bias_mode, uint8_t* out, float out_scale, int64_t m,
                   int64_t k, int64_t n, int trans_b, float alpha, float beta) {
     if (m <= 0 || k <= 0 || n <= 0 || !a || !w || !out) return -1;
@@ -194,10 +199,82 @@ int fo_fp8_linear(int op, int dtype, const uint8_t* a, float a_scale, const uint
     return 0;
 }
 
+/* Column-blocked evaluation of the same contract.  A block of FO_BLOCK output columns is decoded once
+ * (value·s_w, the factor the plain loop multiplies with) and every activation row then walks k in ascending order
+ * with one partial sum per column: each output still sees sum = ((0 + a_0·w_0) + a_1·w_1) + …, an FP32 multiply
+ * followed by an FP32 add (no contraction: the file is compiled with -ffp-contract=off), so the bits are the
+ * plain loop's.  Threads split column blocks only. */
+#define FO_BLOCK 64
+int fo_fp8_linear(int op, int dtype, const uint8_t* a, float a_scale, const uint8_t* w, float w_scale,
+                  const uint8_t* bias, float bias_scale, int bias_mode, uint8_t* out, float out_scale, int64_t m,
+                  int64_t k, int64_t n, int trans_b, float alpha, float beta) {
+    if (m <= 0 || k <= 0 || n <= 0 || !a || !w || !out) return -1;
+    float dec_a[256], dec_w[256], dec_b[256];
+    for (int i = 0; i < 256; ++i) {
+        dec_a[i] = fo_fp8_decode(dtype, (uint8_t)i) * a_scale;
+        dec_w[i] = fo_fp8_decode(dtype, (uint8_t)i) * w_scale;
+        dec_b[i] = fo_fp8_decode(dtype, (uint8_t)i) * bias_scale;
+    }
+    const int64_t blocks = (n + FO_BLOCK - 1) / FO_BLOCK;
+    int failed = 0;
+#pragma omp parallel
+    {
+        float* wdec = (float*)malloc((size_t)k * FO_BLOCK * sizeof(float));
+        float* arow = (float*)malloc((size_t)k * sizeof(float));
+        if (!wdec || !arow) {
+#pragma omp atomic write
+            failed = 1;
+        }
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t jb = 0; jb < blocks; ++jb) {
+            if (!wdec || !arow) continue;
+            const int64_t j0 = jb * FO_BLOCK;
+            const int cnt = (int)(n - j0 < FO_BLOCK ? n - j0 : FO_BLOCK);
+            if (trans_b) {
+                for (int c = 0; c < FO_BLOCK; ++c) {
+                    if (c < cnt) { const uint8_t* wr = w + (j0 + c) * k; for (int64_t t = 0; t < k; ++t) wdec[t * FO_BLOCK + c] = dec_w[wr[t]]; }
+                    else { for (int64_t t = 0; t < k; ++t) wdec[t * FO_BLOCK + c] = 0.0f; }
+                }
+            } else {
+                for (int64_t t = 0; t < k; ++t) {
+                    const uint8_t* wr = w + t * n + j0;
+                    for (int c = 0; c < FO_BLOCK; ++c) wdec[t * FO_BLOCK + c] = c < cnt ? dec_w[wr[c]] : 0.0f;
+                }
+            }
+            for (int64_t i = 0; i < m; ++i) {
+                for (int64_t t = 0; t < k; ++t) arow[t] = dec_a[a[i * k + t]];
+                float sum[FO_BLOCK];
+                for (int c = 0; c < FO_BLOCK; ++c) sum[c] = 0.0f;
+                for (int64_t t = 0; t < k; ++t) {
+                    const float av = arow[t];
+                    const float* wr = wdec + t * FO_BLOCK;
+                    for (int c = 0; c < FO_BLOCK; ++c) sum[c] += av * wr[c];
+                }
+                for (int c = 0; c < cnt; ++c) {
+                    const int64_t j = j0 + c;
+                    float s = sum[c];
+                    if (op == 2) {
+                        s *= alpha;
+                        if (bias_mode == 1) s += beta * dec_b[bias[j]];
+                        else if (bias_mode == 2) s += beta * dec_b[bias[i * n + j]];
+                    } else {
+                        if (bias_mode == 1) s += dec_b[bias[j]];
+                        else if (bias_mode == 2) s += dec_b[bias[i * n + j]];
+                    }
+                    out[i * n + j] = fo_fp8_encode(dtype, s / out_scale);
+                }
+            }
+        }
+        free(wdec);
+        free(arow);
+    }
+    return failed ? -1 : 0;
+}
+
 /* ---- INT8 FC / MatMul / Gemm: src/kernel/common/fc.cc:105-159, gemm.cc:136-198, matmul.cc:156-261 --------
  * w_scales/w_zps hold `w_channels` entries (per output channel) or one entry when w_channels == 0.
  * bias int32 [N] (mode 1) / [M,N] (mode 2).  Returns -1 if any running sum leaves int32. */
-int fo_int8_linear(int op, const int8_t* a, float a_scale, int32_t a_zp, const int8_t* w, const float* w_scales,
+int fo_int8_linear_plain(int op, const int8_t* a, float a_scale, int32_t a_zp, const int8_t* w, const float* w_scales,
                    const int32_t* w_zps, int64_t w_channels, const int32_t* bias, int bias_mode, int8_t* out,
                    float out_scale, int32_t out_zp, int64_t m, int64_t k, int64_t n, int trans_b, float alpha,
                    float beta) {
@@ -232,6 +309,85 @@ int fo_int8_linear(int op, const int8_t* a, float a_scale, int32_t a_zp, const i
             }
             out[i * n + j] = q;
         }
+    }
+    return failed ? -1 : 0;
+}
+
+/* Column-blocked evaluation of fo_int8_linear_plain.  Integer sums do not depend on the order of their terms, and
+ * when K·(128+|zp_a|)·(128+max|zp_w|) + max|bias| fits int32 no prefix of any sum can leave int32, so the plain
+ * loop's overflow checks cannot fire and 32-bit accumulation gives the same accumulator.  Shapes outside that
+ * bound take the plain loop. */
+int fo_int8_linear(int op, const int8_t* a, float a_scale, int32_t a_zp, const int8_t* w, const float* w_scales,
+                   const int32_t* w_zps, int64_t w_channels, const int32_t* bias, int bias_mode, int8_t* out,
+                   float out_scale, int32_t out_zp, int64_t m, int64_t k, int64_t n, int trans_b, float alpha,
+                   float beta) {
+    if (m <= 0 || k <= 0 || n <= 0 || !a || !w || !out) return -1;
+    int64_t wzp_max = 0, bias_max = 0;
+    if (w_zps) {
+        const int64_t cnt = w_channels ? n : 1;
+        for (int64_t j = 0; j < cnt; ++j) { const int64_t v = llabs((long long)w_zps[j]); if (v > wzp_max) wzp_max = v; }
+    }
+    if (bias_mode) {
+        const int64_t cnt = bias_mode == 1 ? n : m * n;
+        for (int64_t j = 0; j < cnt; ++j) { const int64_t v = llabs((long long)bias[j]); if (v > bias_max) bias_max = v; }
+    }
+    const int64_t worst = k * (128 + llabs((long long)a_zp)) * (128 + wzp_max) + bias_max;
+    if (worst > INT32_MAX || k > (1 << 24))
+        return fo_int8_linear_plain(op, a, a_scale, a_zp, w, w_scales, w_zps, w_channels, bias, bias_mode, out, out_scale,
+                                    out_zp, m, k, n, trans_b, alpha, beta);
+    const int64_t blocks = (n + FO_BLOCK - 1) / FO_BLOCK;
+    int failed = 0;
+#pragma omp parallel
+    {
+        int32_t* wq = (int32_t*)malloc((size_t)k * FO_BLOCK * sizeof(int32_t));
+        int32_t* arow = (int32_t*)malloc((size_t)k * sizeof(int32_t));
+        if (!wq || !arow) {
+#pragma omp atomic write
+            failed = 1;
+        }
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t jb = 0; jb < blocks; ++jb) {
+            if (!wq || !arow) continue;
+            const int64_t j0 = jb * FO_BLOCK;
+            const int cnt = (int)(n - j0 < FO_BLOCK ? n - j0 : FO_BLOCK);
+            for (int c = 0; c < FO_BLOCK; ++c) {
+                const int64_t j = j0 + c;
+                const int32_t wzp = (c < cnt && w_zps) ? (w_channels ? w_zps[j] : w_zps[0]) : 0;
+                for (int64_t t = 0; t < k; ++t) {
+                    int32_t v = 0;
+                    if (c < cnt) v = (int32_t)(trans_b ? w[j * k + t] : w[t * n + j]) - wzp;
+                    wq[t * FO_BLOCK + c] = v;
+                }
+            }
+            for (int64_t i = 0; i < m; ++i) {
+                for (int64_t t = 0; t < k; ++t) arow[t] = (int32_t)a[i * k + t] - a_zp;
+                int32_t sum[FO_BLOCK];
+                for (int c = 0; c < FO_BLOCK; ++c) sum[c] = 0;
+                for (int64_t t = 0; t < k; ++t) {
+                    const int32_t av = arow[t];
+                    const int32_t* wr = wq + t * FO_BLOCK;
+                    for (int c = 0; c < FO_BLOCK; ++c) sum[c] += av * wr[c];
+                }
+                for (int c = 0; c < cnt; ++c) {
+                    const int64_t j = j0 + c;
+                    const float ws = w_channels ? w_scales[j] : w_scales[0];
+                    int64_t acc = sum[c];
+                    const int32_t b = bias_mode == 1 ? bias[j] : bias_mode == 2 ? bias[i * n + j] : 0;
+                    const double scale = (double)a_scale * ws;
+                    double real;
+                    if (op == 2) real = ((double)alpha * (double)acc + (double)beta * (double)b) * scale;
+                    else { acc += b; real = (double)acc * scale; }
+                    int8_t q = 0;
+                    if (quantize_real(real, out_scale, out_zp, &q) != 0) {
+#pragma omp atomic write
+                        failed = 1;
+                    }
+                    out[i * n + j] = q;
+                }
+            }
+        }
+        free(wq);
+        free(arow);
     }
     return failed ? -1 : 0;
 }

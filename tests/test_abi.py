@@ -73,6 +73,25 @@ def test_validation_needs_no_gpu():
     assert B.lib().fth_b200_int8_linear_supported(C.byref(d)) == B.ERR_OVERFLOW
     lut = B.int8_relu_table(0.5, 0, 0.5, 0)
     assert lut[128 + 5] == 5 and lut[128 - 5] == 0
+    # K beyond 2^31 is rejected before the worst-case product could wrap
+    d = B.int8_linear_desc(op=B.OP_MATMUL, m=1, k=1 << 40, n=64, a=16, w=16, out=16, a_scale=1.0, a_zp=0, w_scales=16, w_zps=None,
+                           w_params=64, out_scale=1.0, out_zp=0)
+    assert B.lib().fth_b200_int8_linear_supported(C.byref(d)) == B.ERR_OVERFLOW
+
+
+def test_conv_plan_rejects_degenerate_geometry_before_using_it():
+    """A stride, dilation or kernel size of zero returns ERR_INVALID: it must never reach a division or an allocation."""
+    import numpy as np
+    w = np.zeros((8, 8, 3, 3), np.int8)
+    ws = np.ones(8, np.float32)
+    for bad in (dict(stride=(0, 1)), dict(stride=(1, 0)), dict(dil=(0, 1)), dict(kh=0), dict(batch=0), dict(group=3)):
+        kw = dict(batch=1, ic=8, ih=16, iw=16, oc=8, kh=3, kw=3, x=None, w=w, out=None, x_scale=1.0, x_zp=0, w_scales=ws, w_zps=None,
+                  w_params=8, out_scale=1.0, out_zp=0)
+        kw.update(bad)
+        d = B.int8_conv2d_desc(**kw)
+        plan = C.c_void_p()
+        assert B.lib().fth_b200_plan_create_int8_conv2d(C.byref(d), C.byref(plan)) == B.ERR_INVALID, bad
+        assert not plan.value
 
 
 def test_missing_library_fails_loudly(monkeypatch):

@@ -25,26 +25,36 @@ def both_entry_points(torch, dtype, m, k, n, seed, trans_b=False):
         d = B.fp8_linear_desc(dtype=dtype, op=B.OP_GEMM if trans_b else B.OP_MATMUL, m=m, k=k, n=n, a=a, w=w, out=out,
                               a_scale=case["sa"], w_scale=case["sw"], out_scale=case["so"], trans_b=trans_b,
                               variant=B.VARIANT_TCGEN05)
+        # the shape must be one whose split-K partial sums really go through scratch memory (decode-sized shapes
+        # that fit one wave of CTAs run on a kernel that needs none, and would not touch the built-in array at all)
+        need = B.lib().fth_b200_fp8_linear_workspace_bytes(C.byref(d))
+        assert 0 < need <= B.lib().fth_b200_noalloc_scratch_bytes()
+        B.lib().fth_b200_reset_launch_count()
         if noalloc:
             rc = B.lib().fth_b200_fp8_linear_noalloc(C.byref(d), B.current_stream())
         else:
             keep = B.linear_workspace(torch, d)
             rc = B.lib().fth_b200_fp8_linear(C.byref(d), B.current_stream())
         assert rc == B.OK, rc
+        assert B.lib().fth_b200_launch_count() == 2  # weight-streaming pass + the pass that adds the partial sums
         torch.cuda.synchronize()
         outs.append(out.cpu().numpy())
     want = O.fp8_linear(O.OP_GEMM if trans_b else O.OP_MATMUL, dtype, case["a"], case["sa"], case["w"], case["sw"], case["so"], trans_b=trans_b)
-    return outs[0], outs[1], want
+    return outs[0], outs[1], want, need
 
 
 def test_noalloc_matches_ordinary_entry_point_twice_in_a_row(cuda):
     assert B.lib().fth_b200_noalloc_scratch_bytes() == 4 << 20
-    # first call: 8-way split-K decode shape; second call: other data, other shape, other layout — stale partial
-    # sums of the first call lie in the shared scratch while it runs
-    for (dtype, m, k, n, seed, trans_b) in [(O.E4M3, 4, 4096, 2048, 101, False), (O.E5M2, 1, 2048, 1024, 202, True)]:
-        ordinary, noalloc, want = both_entry_points(cuda, dtype, m, k, n, seed, trans_b)
+    # first call: 1 MiB of partial sums (8 K chunks x 4 rows x 8192 channels); second call: other data, other format,
+    # other weight layout and a smaller footprint, so the first call's partial sums still lie under and behind the
+    # region it uses — a call may only ever read what it wrote itself
+    needs = []
+    for (dtype, m, k, n, seed, trans_b) in [(O.E4M3, 4, 4096, 8192, 101, False), (O.E5M2, 1, 2048, 8192, 202, True)]:
+        ordinary, noalloc, want, need = both_entry_points(cuda, dtype, m, k, n, seed, trans_b)
+        needs.append(need)
         assert np.array_equal(ordinary, noalloc)
         assert util.fp8_code_distance(noalloc, want).max() <= 1
+    assert needs[1] < needs[0]
     assert B.device_status() == 0
 
 

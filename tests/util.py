@@ -86,3 +86,81 @@ def make_int8_conv(batch, ic, ih, iw, oc, kh, kw, seed, *, per_channel=True, zer
     w_zps = rng.integers(-5, 6, oc if per_channel else 1).astype(np.int32) if zero_points else None
     out_zp = int(rng.integers(-10, 11)) if zero_points else 0
     return dict(x=x, w=w, bias=b, sx=float(sx), x_zp=x_zp, ws=ws, w_zps=w_zps, so=float(so), out_zp=out_zp)
+
+
+# ---- large shapes (config 5: K = 8192, N = 28672) -----------------------------------------------------------------
+# The generators above build a float64 reference product to pick the output scale; at 8192 x 28672 that costs more than
+# the test itself, so the large cases take the output scale from the distribution instead: the product of N(0,1)
+# activations and N(0,0.02) weights over K terms has sigma = 0.02 * sqrt(K), and 4.2 sigma is the expected absolute
+# maximum over a few 10^4 outputs.
+
+def _parallel_normal(k, n, seed, std):
+    """Seeded N(0, std) float32 matrix [K,N], drawn in row bands by independent child generators on a few threads (numpy
+    releases the interpreter lock while it draws), so that a 235 M-element weight takes a second or two."""
+    import concurrent.futures as cf
+    bands = min(16, k)
+    seeds = np.random.SeedSequence(seed).spawn(bands)
+    out = np.empty((k, n), np.float32)
+    edges = np.linspace(0, k, bands + 1).astype(int)
+
+    def fill(i):
+        np.random.default_rng(seeds[i]).standard_normal(out=out[edges[i]:edges[i + 1]], dtype=np.float32)
+        out[edges[i]:edges[i + 1]] *= np.float32(std)
+    with cf.ThreadPoolExecutor(max_workers=bands) as pool:
+        list(pool.map(fill, range(bands)))
+    return out
+
+
+def make_fp8_weight(dtype, k, n, seed):
+    """N(0, 0.02) weight [K,N] quantised per tensor with the absmax scale -> (codes uint8, scale)."""
+    wf = _parallel_normal(k, n, seed, 0.02)
+    sw = fp8_scale(max(float(wf.max()), -float(wf.min())), dtype, False)
+    wf /= sw
+    return O.fp8_encode(dtype, wf), float(sw)
+
+
+def make_fp8_activation(dtype, m, k, seed):
+    rng = np.random.default_rng(seed)
+    af = rng.standard_normal((m, k), dtype=np.float32)
+    sa = fp8_scale(float(np.abs(af).max()), dtype, False)
+    return O.fp8_encode(dtype, af / sa), float(sa)
+
+
+def fp8_out_scale(dtype, k):
+    return float(np.float32(0.02 * np.sqrt(k) * 4.2 / FP8_MAX[dtype]))
+
+
+def make_int8_weight(k, n, seed):
+    """Uniform int8 weight [K,N] in [-127, 127] with per-output-channel scales in [1e-3, 1e-2]."""
+    rng = np.random.default_rng(seed)
+    w = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    ws = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    return w, ws
+
+
+def int8_out_scale(k, ws, sa=0.02, z=2.33):
+    """Output scale such that about 2 % of the outputs saturate."""
+    sigma = 73.3 ** 2 * np.sqrt(k) * float(sa) * float(ws.mean())
+    return float(np.float32(z * sigma / 127.0))
+
+
+def fp8_parity_report(got, want, dtype, bound_fn=None, out_scale=1.0):
+    """Code-distance statistics of `got` against the oracle's `want`.
+
+    Returns a dict: outputs, exact, one_code (distance exactly 1), relaxed (distance > 1 but within the FP32
+    accumulation bound that bound_fn() returns, same shape as the outputs, in real units), failed (neither),
+    max_distance, and whether the Inf / NaN classes agree.  The caller asserts failed == 0 and class_ok."""
+    dist = fp8_code_distance(got, want)
+    inf_code = 0x7E if dtype == O.E4M3 else 0x7C  # E4M3 has no Inf: 0x7E is a finite code there
+    nan_lo = 0x7F if dtype == O.E4M3 else 0x7D
+    nan = (want & 0x7F) >= nan_lo
+    inf = ((want & 0x7F) == inf_code) & (dtype == O.E5M2)
+    class_ok = bool(np.array_equal(got[inf], want[inf]) and np.array_equal((got[nan] & 0x7F) >= nan_lo, np.ones(int(nan.sum()), bool)))
+    dist = np.where(nan, 0, dist)
+    far = dist > 1
+    relaxed = np.zeros_like(far)
+    if far.any() and bound_fn is not None:
+        err = np.abs(O.fp8_decode(dtype, got).astype(np.float64) - O.fp8_decode(dtype, want).astype(np.float64)) * out_scale
+        relaxed = far & (err <= bound_fn())
+    return dict(outputs=int(dist.size), exact=int((dist == 0).sum()), one_code=int((dist == 1).sum()),
+                relaxed=int(relaxed.sum()), failed=int((far & ~relaxed).sum()), max_distance=int(dist.max()), class_ok=class_ok)
