@@ -134,6 +134,14 @@ int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t 
  * (src/kernel/cuda/qwen_gemm_argmax.cu:55-64), which has no FP8 counterpart.  The output is written as usual.  Decode-sized
  * shapes on the tensor-core kernels only (FTH_B200_ERR_UNSUPPORTED otherwise; run the linear and an ArgMax node then). */
 int fth_b200_fp8_linear_argmax(const fth_b200_fp8_linear_desc* desc, int64_t* indices, fth_b200_stream_t stream);
+/* The fused lm-head node: a [1,K] times the [N,K] vocabulary weight (trans_b = 1, Gemm), greedy selection, one int64
+ * token.  Replaces QwenGemmArgmaxKernel (param src/operator/params.h:152-168), whose FP8 form exists in the reference
+ * for x86 only (src/kernel/x86/linear_fp8.cc:733-1004: the accumulator is quantised to an FP8 code with
+ * desc->out_scale = QwenGemmArgmaxParam::output_scale, the decoded code times that scale is rounded to BF16, NaN is
+ * skipped, the first index wins among equal values, and token 0 is returned when there is no candidate); its CUDA
+ * candidates are BF16 only (src/kernel/cuda/qwen_gemm_argmax.cu:85-172).  Distinct FP8 codes stay distinct and ordered
+ * after the BF16 rounding, so selecting on the decoded code is the same rule.  desc->out still receives the [1,N] codes. */
+int fth_b200_fp8_lm_head_argmax(const fth_b200_fp8_linear_desc* desc, int64_t* token, fth_b200_stream_t stream);
 /* Capability check only (what Supports() calls): 0 if fth_b200_fp8_linear would run this descriptor. */
 int fth_b200_fp8_linear_supported(const fth_b200_fp8_linear_desc* desc);
 size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc);
@@ -264,6 +272,32 @@ int fth_b200_dequantize_linear(const int8_t* x, const float* scales, const int32
  * Replaces CastFloatingKernelCuda (src/kernel/cuda/cast.cu:54-93); contract src/kernel/common/cast.cc:62-126. */
 int fth_b200_cast(int32_t in_dtype, const void* x, float in_scale, int32_t out_dtype, void* out, float out_scale,
                   int64_t count, fth_b200_stream_t stream);
+
+/* -------------------------------------------------------------------------------------------------
+ * The operators between the quantized projections of a decoder block, for plans that keep the whole block on
+ * the stream: QwenRmsNorm, Add, Mul, SiLU.  All are launched as programmatic dependents of the kernel in front.
+ *
+ * QwenRmsNorm replaces QwenRmsNormKernelCuda (src/kernel/cuda/qwen_rms_norm.cu:78-104); contract of the Common
+ * kernel (src/kernel/common/qwen_rms_norm.cc:71-95): FP32 math,
+ *   out[r,c] = x[r,c] * (1 / sqrt(sum_c x[r,c]^2 / hidden + epsilon)) * (weight[c] + weight_offset),
+ * x / weight / out each FP32 or BF16.  The sum of squares is reduced in parallel, so an output may differ from the
+ * Common kernel's by one code of the output type (its x86 and CUDA kernels reduce in other orders as well).
+ * Add / Mul replace the BF16 / FP16 / FP32 kernels of src/kernel/cuda/add.cu and mul.cu (contract
+ * src/kernel/common/add.cc:80-109): out[i] = lhs[i] op rhs[i % rhs_count], one rounding; rhs_count = 0 means
+ * same shape, else it is the length of the rhs row broadcast over lhs (count % rhs_count == 0).  Bit-exact.
+ * SiLU replaces SiluDirectKernelCuda (src/kernel/cuda/silu.cu:39-47); contract src/kernel/common/silu.cc:38-55:
+ * x / (1 + exp(-x)) in FP32.  fth_b200_silu_mul is the SiLU node followed by the Mul node in one launch
+ * (out = round(silu(gate)) * up, both rounding points kept).
+ * ------------------------------------------------------------------------------------------------- */
+enum { FTH_B200_BINARY_ADD = 0, FTH_B200_BINARY_MUL = 1 };
+int fth_b200_qwen_rms_norm(int32_t x_dtype, const void* x, int32_t weight_dtype, const void* weight, float weight_offset,
+                           float epsilon, int32_t out_dtype, void* out, int64_t rows, int64_t hidden,
+                           fth_b200_stream_t stream);
+int fth_b200_binary(int32_t op, int32_t dtype, const void* lhs, const void* rhs, void* out, int64_t count,
+                    int64_t rhs_count, fth_b200_stream_t stream);
+int fth_b200_silu(int32_t dtype, const void* x, void* out, int64_t count, fth_b200_stream_t stream);
+int fth_b200_silu_mul(int32_t dtype, const void* gate, const void* up, void* out, int64_t count,
+                      fth_b200_stream_t stream);
 
 /* -------------------------------------------------------------------------------------------------
  * Host-buffer plans: the shape of KernelBase::Prepare() / compute() (include/core/kernel.h:162-163) for a

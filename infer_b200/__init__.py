@@ -33,7 +33,9 @@ EXPORTS = [
     "fth_b200_plan_destroy",
     "fth_b200_peer_buffer_create", "fth_b200_peer_buffer_open", "fth_b200_peer_buffer_close", "fth_b200_peer_buffer_destroy",
     "fth_b200_gather_sync", "fth_b200_fp8_linear_argmax",
+    "fth_b200_fp8_lm_head_argmax", "fth_b200_qwen_rms_norm", "fth_b200_binary", "fth_b200_silu", "fth_b200_silu_mul",
 ]
+BINARY_ADD, BINARY_MUL = 0, 1
 
 
 class Fp8LinearDesc(C.Structure):
@@ -227,6 +229,27 @@ def int8_relu_table(in_scale, in_zp, out_scale, out_zp):
     check(lib().fth_b200_int8_relu_table(C.c_float(in_scale), C.c_int32(in_zp), C.c_float(out_scale),
                                          C.c_int32(out_zp), C.c_void_p(lut.ctypes.data)), "fth_b200_int8_relu_table")
     return lut
+
+
+def qwen_rms_norm(x_dtype, x, weight_dtype, weight, weight_offset, epsilon, out_dtype, out, rows, hidden, stream=None) -> None:
+    check(lib().fth_b200_qwen_rms_norm(C.c_int32(x_dtype), C.c_void_p(ptr(x)), C.c_int32(weight_dtype), C.c_void_p(ptr(weight)),
+                                       C.c_float(weight_offset), C.c_float(epsilon), C.c_int32(out_dtype), C.c_void_p(ptr(out)),
+                                       C.c_int64(rows), C.c_int64(hidden), stream or current_stream()), "fth_b200_qwen_rms_norm")
+
+
+def binary(op, dtype, lhs, rhs, out, count, rhs_count=0, stream=None) -> None:
+    check(lib().fth_b200_binary(C.c_int32(op), C.c_int32(dtype), C.c_void_p(ptr(lhs)), C.c_void_p(ptr(rhs)), C.c_void_p(ptr(out)),
+                                C.c_int64(count), C.c_int64(rhs_count), stream or current_stream()), "fth_b200_binary")
+
+
+def silu(dtype, x, out, count, stream=None) -> None:
+    check(lib().fth_b200_silu(C.c_int32(dtype), C.c_void_p(ptr(x)), C.c_void_p(ptr(out)), C.c_int64(count),
+                              stream or current_stream()), "fth_b200_silu")
+
+
+def silu_mul(dtype, gate, up, out, count, stream=None) -> None:
+    check(lib().fth_b200_silu_mul(C.c_int32(dtype), C.c_void_p(ptr(gate)), C.c_void_p(ptr(up)), C.c_void_p(ptr(out)), C.c_int64(count),
+                                  stream or current_stream()), "fth_b200_silu_mul")
 
 
 def device_status() -> int:

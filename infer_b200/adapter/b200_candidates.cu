@@ -28,6 +28,7 @@
 #include "src/kernel/cuda/kernel_io.cuh"
 #include "src/kernel/cuda/runtime.h"
 #include "src/operator/params.h"
+#include "util/bf16.h"
 #include "util/timer.h"
 
 namespace feather {
@@ -137,13 +138,19 @@ int BiasMode(const Tensor* bias, int64_t m, int64_t n) {
 template <DataType dtype, typename Param>
 class Fp8LinearKernel final : public B200Kernel {
    public:
+    // The factory runs inside the node's KernelSelectionScope (include/core/kernel.h:52-72): the scratch budget of the
+    // request is read here and honoured below.
+    Fp8LinearKernel() : workspace_limit_(KernelSelectionScope::WorkspaceLimit()) {}
+
     Status Supports() const override {
         fth_b200_fp8_linear_desc d;
         if (!Describe(&d)) return Status::Error(StatusCode::kUnsupported, "b200: not a 2-D FP8 linear");
         d.a = d.w = d.out = kProbe;
         if (d.bias_mode != FTH_B200_BIAS_NONE) d.bias = kProbe;
-        d.workspace = kProbe;  // Prepare() provides what workspace_bytes() asks for
-        d.workspace_bytes = static_cast<size_t>(-1);
+        if (ScratchMode(d) == Scratch::kOwned) {
+            d.workspace = kProbe;  // Prepare() provides what workspace_bytes() asks for
+            d.workspace_bytes = static_cast<size_t>(-1);
+        }
         return FromAbi(fth_b200_fp8_linear_supported(&d), "FP8 linear");
     }
 
@@ -153,6 +160,8 @@ class Fp8LinearKernel final : public B200Kernel {
         d.a = d.w = d.out = kProbe;
         if (d.bias_mode != FTH_B200_BIAS_NONE) d.bias = kProbe;
         weights_resident_ = false;
+        scratch_ = ScratchMode(d);
+        if (scratch_ != Scratch::kOwned) return 0;
         return workspace_.Reserve(fth_b200_fp8_linear_workspace_bytes(&d), true);
     }
 
@@ -172,12 +181,26 @@ class Fp8LinearKernel final : public B200Kernel {
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
         // An immutable weight is uploaded by the first call; from the second call on nothing on the stream writes it.
         d.weights_static = weights_resident_ ? 1 : 0;
-        if (fth_b200_fp8_linear(&d, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        const int rc = scratch_ == Scratch::kBuiltIn ? fth_b200_fp8_linear_noalloc(&d, cuda_detail::InferenceStream())
+                                                     : fth_b200_fp8_linear(&d, cuda_detail::InferenceStream());
+        if (rc != FTH_B200_OK) return -1;
         weights_resident_ = v.w->is_immutable();
         return cuda_detail::CopyDeviceToTensor(&out, v.out);  // a no-op under deferred host sync
     }
 
    private:
+    // Where split-K partial sums go.  Within the node's budget: a buffer this kernel allocates in Prepare().  Beyond it
+    // (a plan built with workspace limit 0): the array inside the library image when the shape fits it, else no scratch
+    // at all — the library then picks kernels that need none.
+    enum class Scratch { kOwned, kBuiltIn, kNone };
+    Scratch ScratchMode(const fth_b200_fp8_linear_desc& probe) const {
+        fth_b200_fp8_linear_desc d = probe;
+        d.workspace = nullptr; d.workspace_bytes = 0;
+        const size_t need = fth_b200_fp8_linear_workspace_bytes(&d);
+        if (need <= workspace_limit_) return Scratch::kOwned;
+        return need <= fth_b200_noalloc_scratch_bytes() ? Scratch::kBuiltIn : Scratch::kNone;
+    }
+
     bool Describe(fth_b200_fp8_linear_desc* d, LinearView* view = nullptr) const {
         LinearView v;
         if (!View(ParamAs<Param>(), &v)) return false;
@@ -202,6 +225,8 @@ class Fp8LinearKernel final : public B200Kernel {
 
     DeviceScratch workspace_;
     bool weights_resident_{false};
+    size_t workspace_limit_;
+    Scratch scratch_{Scratch::kOwned};
 };
 
 // ---------------------------------------------------------------------------------------------------------
@@ -234,18 +259,33 @@ bool ReadInt8Quantization(const Tensor* t, bool allow_per_channel, int64_t axis,
     return true;
 }
 
+// Largest |bias| of an INT32 bias constant that is readable on the host (the static quantiser's output), else 0.
+int64_t BiasMaxAbs(const Tensor* bias) {
+    int64_t worst = 0;
+    if (bias && bias->IsInitialized() && bias->data_type() == DataType::INT32) {
+        const int32_t* b = bias->data<int32_t>();
+        for (int64_t i = 0; i < bias->numel(); ++i) worst = std::max<int64_t>(worst, std::llabs(static_cast<long long>(b[i])));
+    }
+    return worst;
+}
+
 template <typename Param>
 class Int8LinearKernel final : public B200Kernel {
    public:
+    Int8LinearKernel() : workspace_limit_(KernelSelectionScope::WorkspaceLimit()) {}
+
     Status Supports() const override {
         fth_b200_int8_linear_desc d;
         Int8WeightParams wq;
-        if (!Describe(&d, &wq)) return Status::Error(StatusCode::kUnsupported, "b200: not a 2-D INT8 linear");
+        LinearView v;
+        if (!Describe(&d, &wq, &v)) return Status::Error(StatusCode::kUnsupported, "b200: not a 2-D INT8 linear");
         d.a = kProbe; d.w = static_cast<const int8_t*>(kProbe); d.out = kProbe;
         d.w_scales = static_cast<const float*>(kProbe);
         if (wq.zp_max_abs != 0) d.w_zps = static_cast<const int32_t*>(kProbe);
         if (d.bias_mode != FTH_B200_BIAS_NONE) d.bias = static_cast<const int32_t*>(kProbe);
-        d.workspace = kProbe; d.workspace_bytes = static_cast<size_t>(-1);
+        // selection and compute() must decide the int32 overflow pre-check on the same numbers
+        d.bias_max_abs = BiasMaxAbs(v.bias);
+        if (WithinBudget(d)) { d.workspace = kProbe; d.workspace_bytes = static_cast<size_t>(-1); }
         return FromAbi(fth_b200_int8_linear_supported(&d), "INT8 linear");
     }
 
@@ -259,13 +299,10 @@ class Int8LinearKernel final : public B200Kernel {
         if (scales_.Upload(wq.scales.data(), wq.scales.size() * sizeof(float)) != 0) return -1;
         has_zps_ = wq.zp_max_abs != 0;
         if (has_zps_ && zps_.Upload(wq.zero_points.data(), wq.zero_points.size() * sizeof(int32_t)) != 0) return -1;
-        bias_max_abs_ = 0;
-        if (v.bias) {  // bias is an immutable INT32 constant produced by the static quantiser
-            const int32_t* b = v.bias->data<int32_t>();
-            for (int64_t i = 0; i < v.bias->numel(); ++i) bias_max_abs_ = std::max<int64_t>(bias_max_abs_, std::llabs(static_cast<long long>(b[i])));
-        }
+        bias_max_abs_ = BiasMaxAbs(v.bias);  // bias is an immutable INT32 constant produced by the static quantiser
         d.a = kProbe; d.w = static_cast<const int8_t*>(kProbe); d.out = kProbe; d.w_scales = static_cast<const float*>(kProbe);
         weights_resident_ = false;
+        if (!WithinBudget(d)) return 0;  // no scratch: the library picks kernels that need none
         return workspace_.Reserve(fth_b200_int8_linear_workspace_bytes(&d), true);
     }
 
@@ -292,6 +329,12 @@ class Int8LinearKernel final : public B200Kernel {
     }
 
    private:
+    bool WithinBudget(const fth_b200_int8_linear_desc& probe) const {
+        fth_b200_int8_linear_desc d = probe;
+        d.workspace = nullptr; d.workspace_bytes = 0;
+        return fth_b200_int8_linear_workspace_bytes(&d) <= workspace_limit_;
+    }
+
     bool Describe(fth_b200_int8_linear_desc* d, Int8WeightParams* wq, LinearView* view = nullptr) const {
         LinearView v;
         if (!View(ParamAs<Param>(), &v)) return false;
@@ -319,6 +362,7 @@ class Int8LinearKernel final : public B200Kernel {
     bool weights_resident_{false};
     bool has_zps_{false};
     int64_t bias_max_abs_{0};
+    size_t workspace_limit_;
 };
 
 // ---------------------------------------------------------------------------------------------------------
@@ -542,6 +586,181 @@ class DequantizeLinearKernelB200 final : public QdqBase<operators::DequantizeLin
 };
 
 // ---------------------------------------------------------------------------------------------------------
+// The operators between the projections of a decoder block — in front of the reference's CUDA kernels
+// (src/kernel/cuda/qwen_rms_norm.cu, add.cu, mul.cu, silu.cu), so that a Qwen plan keeps the whole block on the
+// stream with this backend's launch behaviour (programmatic dependents, no per-call allocation).
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+bool PlainFloat(DataType t) { return t == DataType::FP32 || t == DataType::BF16; }
+bool AnyFloat(DataType t) { return t == DataType::FP32 || t == DataType::BF16 || t == DataType::FP16; }
+
+// Device views of an input and an output tensor through the session's replica cache.
+int AcquireIn(const Tensor* t, void** ptr) {
+    return cuda_detail::AcquireTensorDevice(t, static_cast<size_t>(t->numel()) * DataTypeBytes(t->data_type()), t->raw_data(), ptr);
+}
+int FinishOut(Tensor* t, size_t bytes) {
+    if (cuda_detail::DeferredHostSyncEnabled()) return 0;
+    return cuda_detail::SyncTensorToHost(t, bytes, t->raw_data());
+}
+}  // namespace
+
+class QwenRmsNormKernelB200 final : public B200Kernel {
+   public:
+    Status Supports() const override {
+        auto* p = ParamAs<operators::QwenRmsNormParam>();
+        if (!p || !p->input || !p->weight || !p->epsilon || !p->out) return Status::Error(StatusCode::kInvalidArgument, "b200: bad QwenRmsNorm parameters");
+        if (!PlainFloat(p->input->data_type()) || !PlainFloat(p->weight->data_type()) || !PlainFloat(p->out->data_type()))
+            return Status::Error(StatusCode::kUnsupported, "b200: QwenRmsNorm takes FP32 / BF16 tensors");
+        return Status::Ok();
+    }
+    int32_t compute() override {
+        AutoTimer timer("B200::QwenRmsNorm");
+        auto* p = ParamAs<operators::QwenRmsNormParam>();
+        if (!p || !p->input || !p->weight || !p->epsilon || !p->out || p->input->dims().empty() || p->epsilon->numel() != 1) return -1;
+        const int64_t hidden = p->input->dims().data().back();
+        if (hidden <= 0 || p->input->numel() % hidden != 0 || p->weight->numel() != hidden || p->out->numel() != p->input->numel()) return -1;
+        float epsilon = 0.0f;  // a plan constant, read on the host as the reference's CUDA kernel does (qwen_rms_norm.cu:30-45)
+        if (p->epsilon->data_type() == DataType::FP32) epsilon = p->epsilon->data<float>()[0];
+        else if (p->epsilon->data_type() == DataType::BF16) epsilon = BFloat16ToFloat(p->epsilon->data<BFloat16>()[0].bits);
+        else return -1;
+        void* x = nullptr; void* w = nullptr; void* out = nullptr;
+        const size_t out_bytes = static_cast<size_t>(p->out->numel()) * DataTypeBytes(p->out->data_type());
+        if (AcquireIn(p->input.get(), &x) != 0 || AcquireIn(p->weight.get(), &w) != 0 ||
+            cuda_detail::AcquireOutputTensorDevice(p->out.get(), out_bytes, &out) != 0) return -1;
+        if (fth_b200_qwen_rms_norm(static_cast<int32_t>(p->input->data_type()), x, static_cast<int32_t>(p->weight->data_type()), w, p->weight_offset,
+                                   epsilon, static_cast<int32_t>(p->out->data_type()), out, p->input->numel() / hidden, hidden,
+                                   cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        return FinishOut(p->out.get(), out_bytes);
+    }
+};
+
+// Add / Mul with equal shapes, or a trailing-row rhs broadcast over lhs; other broadcasts stay on the reference kernel.
+template <int kOp>
+class BinaryKernelB200 final : public B200Kernel {
+   public:
+    Status Supports() const override {
+        int64_t rhs_count = 0;
+        return Shape(&rhs_count) ? Status::Ok() : Status::Error(StatusCode::kUnsupported, "b200: element-wise op with a general broadcast");
+    }
+    int32_t compute() override {
+        AutoTimer timer(kOp == FTH_B200_BINARY_ADD ? "B200::Add" : "B200::Mul");
+        auto* p = ParamAs<operators::BinaryParam>();
+        int64_t rhs_count = 0;
+        if (!Shape(&rhs_count)) return -1;
+        const DataType dt = p->lhs->data_type();
+        void* lhs = nullptr; void* rhs = nullptr; void* out = nullptr;
+        p->out->set_data_type(dt);
+        const size_t out_bytes = static_cast<size_t>(p->lhs->numel()) * DataTypeBytes(dt);
+        if (AcquireIn(p->lhs.get(), &lhs) != 0 || AcquireIn(p->rhs.get(), &rhs) != 0 ||
+            cuda_detail::AcquireOutputTensorDevice(p->out.get(), out_bytes, &out) != 0) return -1;
+        if (fth_b200_binary(kOp, static_cast<int32_t>(dt), lhs, rhs, out, p->lhs->numel(), rhs_count, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        return FinishOut(p->out.get(), out_bytes);
+    }
+
+   private:
+    bool Shape(int64_t* rhs_count) const {
+        auto* p = ParamAs<operators::BinaryParam>();
+        if (!p || !p->lhs || !p->rhs || !p->out || !AnyFloat(p->lhs->data_type()) || p->rhs->data_type() != p->lhs->data_type()) return false;
+        const auto& l = p->lhs->dims().data();
+        const auto& r = p->rhs->dims().data();
+        if (l.empty() || p->lhs->numel() <= 0 || p->out->numel() != p->lhs->numel()) return false;
+        if (l == r) { *rhs_count = p->lhs->numel(); return true; }
+        // rhs = the trailing dimensions of lhs (leading 1s allowed): one row repeated over the leading dimensions
+        size_t skip = 0;
+        while (skip < r.size() && r[skip] == 1) ++skip;
+        const size_t tail = r.size() - skip;
+        if (tail == 0 || tail > l.size()) return false;
+        for (size_t i = 0; i < tail; ++i)
+            if (r[skip + i] != l[l.size() - tail + i]) return false;
+        *rhs_count = p->rhs->numel();
+        return true;
+    }
+};
+
+class SiluKernelB200 final : public B200Kernel {
+   public:
+    Status Supports() const override {
+        auto* p = ParamAs<operators::UnaryParam>();
+        if (!p || !p->input || !p->out || !AnyFloat(p->input->data_type())) return Status::Error(StatusCode::kUnsupported, "b200: SiLU takes FP32 / FP16 / BF16");
+        return Status::Ok();
+    }
+    int32_t compute() override {
+        AutoTimer timer("B200::SiLU");
+        auto* p = ParamAs<operators::UnaryParam>();
+        if (!p || !p->input || !p->out || p->input->numel() <= 0) return -1;
+        const DataType dt = p->input->data_type();
+        void* x = nullptr; void* out = nullptr;
+        p->out->set_data_type(dt);
+        const size_t out_bytes = static_cast<size_t>(p->input->numel()) * DataTypeBytes(dt);
+        if (AcquireIn(p->input.get(), &x) != 0 || cuda_detail::AcquireOutputTensorDevice(p->out.get(), out_bytes, &out) != 0) return -1;
+        if (fth_b200_silu(static_cast<int32_t>(dt), x, out, p->input->numel(), cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        return FinishOut(p->out.get(), out_bytes);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// Fused FP8 lm-head projection + greedy selection.  The reference has this node for FP8 on x86 only
+// (QwenGemmArgmaxKernel<X86, FP8*>, src/kernel/x86/linear_fp8.cc:733-1004); its CUDA candidates are BF16
+// (src/kernel/cuda/register_all.cu:139), so an FP8 Qwen plan cannot keep the node on the GPU without this one.
+// ---------------------------------------------------------------------------------------------------------
+template <DataType dtype>
+class QwenGemmArgmaxKernelB200 final : public B200Kernel {
+   public:
+    Status Supports() const override {
+        fth_b200_fp8_linear_desc d;
+        if (!Describe(&d)) return Status::Error(StatusCode::kUnsupported, "b200: not an FP8 [1,K] x [N,K] lm-head");
+        d.a = d.w = d.out = kProbe;
+        d.workspace = kProbe; d.workspace_bytes = static_cast<size_t>(-1);
+        return FromAbi(fth_b200_fp8_linear_supported(&d), "FP8 lm-head selection");
+    }
+    int32_t Prepare() override {
+        fth_b200_fp8_linear_desc d;
+        if (!Describe(&d)) return -1;
+        d.a = d.w = d.out = kProbe;
+        if (logits_.Reserve(static_cast<size_t>(d.n), false) != 0) return -1;  // the code row the selection runs over
+        return workspace_.Reserve(fth_b200_fp8_linear_workspace_bytes(&d), true);
+    }
+    int32_t compute() override {
+        AutoTimer timer("B200::QwenGemmArgmax::FP8");
+        using T = cuda_detail::StorageT<dtype>;
+        auto* p = ParamAs<operators::QwenGemmArgmaxParam>();
+        fth_b200_fp8_linear_desc d;
+        if (!Describe(&d) || logits_.get() == nullptr) return -1;
+        cuda_detail::DeviceBuffer<T> a, b;
+        void* token = nullptr;
+        p->out->set_data_type(DataType::INT64);
+        if (cuda_detail::CopyTensorToDevice(p->a.get(), &a) != 0 || cuda_detail::CopyTensorToDevice(p->b.get(), &b) != 0 ||
+            cuda_detail::AcquireOutputTensorDevice(p->out.get(), sizeof(int64_t), &token) != 0) return -1;
+        d.a = a.get(); d.w = b.get(); d.out = logits_.get();
+        d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
+        d.weights_static = weights_resident_ ? 1 : 0;
+        if (fth_b200_fp8_lm_head_argmax(&d, static_cast<int64_t*>(token), cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        weights_resident_ = p->b->is_immutable();
+        return FinishOut(p->out.get(), sizeof(int64_t));
+    }
+
+   private:
+    bool Describe(fth_b200_fp8_linear_desc* d) const {
+        auto* p = ParamAs<operators::QwenGemmArgmaxParam>();
+        if (!p || !p->a || !p->b || !p->out || p->a->data_type() != dtype || p->b->data_type() != dtype) return false;
+        if (p->a->dims().size() < 2 || p->b->dims().size() != 2) return false;
+        if (!HasCompatiblePerTensorQuantization(p->a->quantization()) || !HasCompatiblePerTensorQuantization(p->b->quantization())) return false;
+        const int64_t k = p->a->dims().data().back();
+        const int64_t n = p->b->dims().data()[0];
+        if (k <= 0 || n <= 0 || p->a->numel() != k || p->b->dims().data()[1] != k || p->out->numel() != 1) return false;
+        *d = fth_b200_fp8_linear_desc{};
+        d->dtype = static_cast<int32_t>(dtype);
+        d->op = FTH_B200_OP_GEMM; d->m = 1; d->k = k; d->n = n; d->trans_b = 1;
+        d->a_scale = p->a->quantization_scale(); d->w_scale = p->b->quantization_scale();
+        d->bias_scale = 1.0f; d->out_scale = p->output_scale;
+        d->alpha = 1.0f; d->beta = 1.0f;
+        return true;
+    }
+    DeviceScratch logits_, workspace_;
+    bool weights_resident_{false};
+};
+
+// ---------------------------------------------------------------------------------------------------------
 // Registration.  Call once after the dispatcher exists (KernelDispatcher::instance() registers the built-in
 // kernels lazily, include/core/kernel.h:212-225); the environment variable FEATHER_DISABLE_B200=1 leaves the
 // reference candidates alone, so A/B runs against the reference CUDA kernels need one switch.
@@ -568,6 +787,14 @@ bool RegisterB200Kernels() {
     for (DataType t : {DataType::FP32, DataType::FP16, DataType::BF16}) Add<QuantizeLinearKernelB200>(t, "QuantizeLinear", "b200.quantize_linear");
     Add<DequantizeLinearKernelB200>(DataType::INT8, "DequantizeLinear", "b200.dequantize_linear");
     for (DataType t : {DataType::FP32, DataType::FP16, DataType::BF16, DataType::FP8E4M3, DataType::FP8E5M2}) Add<CastKernelB200>(t, "Cast", "b200.cast");
+    for (DataType t : {DataType::FP32, DataType::BF16}) Add<QwenRmsNormKernelB200>(t, "QwenRmsNorm", "b200.qwen_rms_norm");
+    for (DataType t : {DataType::FP32, DataType::FP16, DataType::BF16}) {
+        Add<BinaryKernelB200<FTH_B200_BINARY_ADD>>(t, "Add", "b200.add");
+        Add<BinaryKernelB200<FTH_B200_BINARY_MUL>>(t, "Mul", "b200.mul");
+        Add<SiluKernelB200>(t, "SiLU", "b200.silu");
+    }
+    Add<QwenGemmArgmaxKernelB200<DataType::FP8E4M3>>(DataType::FP8E4M3, "QwenGemmArgmax", "b200.fp8.qwen_gemm_argmax");
+    Add<QwenGemmArgmaxKernelB200<DataType::FP8E5M2>>(DataType::FP8E5M2, "QwenGemmArgmax", "b200.fp8.qwen_gemm_argmax");
     return true;
 }
 

@@ -243,7 +243,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
 
 using namespace fth;
 
-extern "C" int fth_b200_abi_version(void) { return 3; }
+extern "C" int fth_b200_abi_version(void) { return 4; }
 extern "C" const char* fth_b200_last_variant(void) { return g_last_variant; }
 extern "C" int64_t fth_b200_launch_count(void) { return g_launches; }
 extern "C" void fth_b200_reset_launch_count(void) { g_launches = 0; }
@@ -275,7 +275,7 @@ extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_s
                d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int fth_b200_fp8_linear_argmax(const fth_b200_fp8_linear_desc* d, int64_t* indices, fth_b200_stream_t stream_) {
+static int Fp8LinearArgmax(const fth_b200_fp8_linear_desc* d, int64_t* indices, int64_t none_value, fth_b200_stream_t stream_) {
     ClearStaleError();
     const int rc = ValidateFp8(d);
     if (rc != FTH_B200_OK) return rc;
@@ -292,7 +292,16 @@ extern "C" int fth_b200_fp8_linear_argmax(const fth_b200_fp8_linear_desc* d, int
     args.argmax_keys = reinterpret_cast<unsigned long long*>(indices);
     const int run = Run(variant, d->dtype, args, fe, ie, d->workspace, d->workspace_bytes, stream);
     if (run != FTH_B200_OK) return run;
-    return LaunchArgmaxFinalize(args.argmax_keys, d->m, stream);
+    return LaunchArgmaxFinalize(args.argmax_keys, d->m, none_value, stream);
+}
+
+extern "C" int fth_b200_fp8_linear_argmax(const fth_b200_fp8_linear_desc* d, int64_t* indices, fth_b200_stream_t stream) {
+    return Fp8LinearArgmax(d, indices, -1, stream);
+}
+
+extern "C" int fth_b200_fp8_lm_head_argmax(const fth_b200_fp8_linear_desc* d, int64_t* token, fth_b200_stream_t stream) {
+    if (d == nullptr || d->m != 1 || !d->trans_b || d->bias_mode != FTH_B200_BIAS_NONE) return FTH_B200_ERR_INVALID;
+    return Fp8LinearArgmax(d, token, 0, stream);
 }
 
 extern "C" int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* d) {

@@ -56,8 +56,9 @@ bool Tcgen05StoresToPeers(int dtype, const LinearArgs& args, const Fp8Epilogue& 
 // True when that launch can also run the fused greedy selection (the decode-sized kernels, direct epilogue).
 bool Tcgen05SelectsInEpilogue(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie);
 
-// Turns the packed (value, index) keys a fused argmax left in `keys` into int64 indices in place (-1: no candidate).
-int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, cudaStream_t stream);
+// Turns the packed (value, index) keys a fused argmax left in `keys` into int64 indices in place; a row without a
+// candidate receives `none_value`.
+int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, int64_t none_value, cudaStream_t stream);
 
 // Copies the [m, n] output block (elements of `elem_bytes`, row stride ldo elements) to every peer replica.
 int LaunchPeerCopy(const void* out, int64_t m, int64_t n, int64_t ldo, int elem_bytes, const PeerOut& peers, cudaStream_t stream);

@@ -63,17 +63,17 @@ __global__ void GatherSyncKernel(FlagPtrs flags, int world, int self, uint32_t e
     }
 }
 
-__global__ void ArgmaxFinalizeKernel(unsigned long long* keys, int64_t m) {
+__global__ void ArgmaxFinalizeKernel(unsigned long long* keys, int64_t m, long long none_value) {
     const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (i >= m) return;
     const unsigned long long key = keys[i];
-    reinterpret_cast<long long*>(keys)[i] = key == 0 ? -1ll : static_cast<long long>(0xffffffffu - static_cast<uint32_t>(key & 0xffffffffu));
+    reinterpret_cast<long long*>(keys)[i] = key == 0 ? none_value : static_cast<long long>(0xffffffffu - static_cast<uint32_t>(key & 0xffffffffu));
 }
 
 }  // namespace
 
-int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, cudaStream_t stream) {
-    ArgmaxFinalizeKernel<<<static_cast<unsigned>((m + 127) / 128), 128, 0, stream>>>(keys, m);
+int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, int64_t none_value, cudaStream_t stream) {
+    ArgmaxFinalizeKernel<<<static_cast<unsigned>((m + 127) / 128), 128, 0, stream>>>(keys, m, static_cast<long long>(none_value));
     NoteLaunch("argmax_finalize");
     return CheckLaunch();
 }

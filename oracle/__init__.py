@@ -335,3 +335,63 @@ def cast(in_dtype, x, in_scale, out_dtype, out_scale, *, impl="port", device=COM
     h = ref().ref_cast_create(C.c_int(device), C.c_int(in_dtype), _p(x), C.c_float(in_scale), C.c_int(out_dtype),
                               C.c_float(out_scale), C.c_int64(x.size))
     return RefKernel(h, _NP[out_dtype], (x.size,)).run()
+
+
+# ------------------------------------------------------------------------------------------------
+# QwenRmsNorm / Add / Mul / SiLU (the operators between the projections of a decoder block)
+# ------------------------------------------------------------------------------------------------
+def qwen_rms_norm(x_dtype, x, w_dtype, weight, weight_offset, epsilon, out_dtype, *, impl="port", device=COMMON):
+    x = _arr(x, _NP[x_dtype])
+    weight = _arr(weight, _NP[w_dtype])
+    rows, hidden = x.shape
+    if impl == "port":
+        out = np.empty((rows, hidden), _NP[out_dtype])
+        rc = port().fo_qwen_rms_norm(C.c_int(x_dtype), _p(x), C.c_int(w_dtype), _p(weight), C.c_float(weight_offset),
+                                     C.c_float(epsilon), C.c_int(out_dtype), _p(out), C.c_int64(rows), C.c_int64(hidden))
+        if rc != 0:
+            raise RuntimeError("fo_qwen_rms_norm failed")
+        return out
+    ref().ref_qwen_rms_norm_create.restype = C.c_void_p
+    h = ref().ref_qwen_rms_norm_create(C.c_int(device), C.c_int(x_dtype), _p(x), C.c_int(w_dtype), _p(weight), C.c_float(weight_offset),
+                                       C.c_float(epsilon), C.c_int(out_dtype), C.c_int64(rows), C.c_int64(hidden))
+    return RefKernel(h, _NP[out_dtype], (rows, hidden)).run()
+
+
+def binary(op, dtype, lhs, rhs, *, impl="port", device=COMMON):
+    """op 0 = Add, 1 = Mul; lhs [rows, cols]; rhs the same shape or one row [cols]."""
+    lhs = _arr(lhs, _NP[dtype])
+    rhs = _arr(rhs, _NP[dtype])
+    rows, cols = lhs.shape
+    if impl == "port":
+        out = np.empty((rows, cols), _NP[dtype])
+        rc = port().fo_binary(C.c_int(op), C.c_int(dtype), _p(lhs), _p(rhs), _p(out), C.c_int64(lhs.size), C.c_int64(rhs.size))
+        if rc != 0:
+            raise RuntimeError("fo_binary failed")
+        return out
+    ref().ref_binary_create.restype = C.c_void_p
+    h = ref().ref_binary_create(C.c_int(device), C.c_int(op), C.c_int(dtype), _p(lhs), _p(rhs), C.c_int64(rows), C.c_int64(cols),
+                                C.c_int64(1 if rhs.ndim == 1 else rows))
+    return RefKernel(h, _NP[dtype], (rows, cols)).run()
+
+
+def silu(dtype, x, *, impl="port", device=COMMON):
+    x = _arr(x, _NP[dtype])
+    if impl == "port":
+        out = np.empty(x.shape, _NP[dtype])
+        port().fo_silu(C.c_int(dtype), _p(x), _p(out), C.c_int64(x.size))
+        return out
+    ref().ref_silu_create.restype = C.c_void_p
+    h = ref().ref_silu_create(C.c_int(device), C.c_int(dtype), _p(x), C.c_int64(x.size))
+    return RefKernel(h, _NP[dtype], x.shape).run()
+
+
+def qwen_gemm_argmax(dtype, a, a_scale, b, b_scale, output_scale, *, device=X86):
+    """The reference's fused FP8 lm-head projection + greedy selection (x86 only: src/kernel/x86/linear_fp8.cc:733-1004).
+    a [1, K] codes, b [N, K] codes; returns the selected row of b."""
+    a = _arr(a, np.uint8)
+    b = _arr(b, np.uint8)
+    n, k = b.shape
+    ref().ref_qwen_gemm_argmax_create.restype = C.c_void_p
+    h = ref().ref_qwen_gemm_argmax_create(C.c_int(device), C.c_int(dtype), _p(a), C.c_float(a_scale), _p(b), C.c_float(b_scale),
+                                          C.c_float(output_scale), C.c_int64(k), C.c_int64(n))
+    return int(RefKernel(h, np.int64, (1,)).run()[0])

@@ -9,6 +9,8 @@
 //   adapter_e2e select   host only: registration, candidate order, kRequireRequested, decline → next CUDA candidate
 //   adapter_e2e run      needs a GPU: the new candidates run through the reference's CUDA runtime (replica cache,
 //                        inference stream) and are compared with the reference's COMMON kernels on the same tensors
+//   adapter_e2e time     needs a GPU: microseconds per compute() of FP8 / INT8 MatMul nodes through the reference
+//                        runtime; with FEATHER_DISABLE_B200=1 the same nodes run on the reference's own CUDA kernels
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -24,6 +26,7 @@
 #include "fth_b200.h"
 #include "src/kernel/cuda/runtime.h"
 #include "src/operator/params.h"
+#include "util/bf16.h"
 #include "util/fp8.h"
 
 namespace feather { namespace kernel { namespace b200 {
@@ -184,6 +187,26 @@ static void RunSelect() {
         CHECK_THAT(k && !IsB200Kernel(k.get()) && k->device() == DeviceType::CUDA, "INT8 K = 140000: b200 declines (overflow bound), reference CUDA kernel selected");
     }
     {
+        // the operators between the projections, and the fused FP8 lm-head selection (no CUDA candidate in the reference)
+        KernelSelectionScope scope(KernelFallbackPolicy::kRequireRequested, nullptr);
+        bool all = true;
+        for (const char* op : {"QwenRmsNorm", "Add", "Mul", "SiLU"}) {
+            auto k = KernelDispatcher::instance().create(DeviceType::CUDA, DataType::BF16, op);
+            all = all && k && IsB200Kernel(k.get());
+        }
+        CHECK_THAT(all, "BF16 QwenRmsNorm / Add / Mul / SiLU: the b200 candidate is first");
+        auto k = KernelDispatcher::instance().create(DeviceType::CUDA, DataType::FP8E4M3, "QwenGemmArgmax");
+        CHECK_THAT(k && IsB200Kernel(k.get()), "create(CUDA, FP8E4M3, QwenGemmArgmax) has a candidate (the reference registers BF16 only)");
+    }
+    {
+        // a node built with a scratch budget of zero still selects the b200 candidate (built-in scratch, or kernels without scratch)
+        Fp8Case c = MakeFp8(DataType::FP8E4M3, 4, 4096, 8192);
+        KernelSelectionScope scope(KernelFallbackPolicy::kRequireRequested, nullptr, false, 0);
+        auto k = KernelDispatcher::instance().create(DeviceType::CUDA, DataType::FP8E4M3, "MatMul");
+        k->SetParam(&c.param);
+        CHECK_THAT(KernelBase::FinalizeSelection(&k).ok() && IsB200Kernel(k.get()), "workspace limit 0: FP8 MatMul [4,4096]x[4096,8192] still selects the b200 candidate");
+    }
+    {
         // FEATHER selection without the strict policy still prefers CUDA candidates (priority order)
         Int8Case c = MakeInt8(4, 256, 64);
         KernelSelectionScope scope(KernelFallbackPolicy::kAllowCommon, nullptr);
@@ -335,14 +358,159 @@ static void RunGpu() {
         std::printf("      [%s]\n", fth_b200_last_variant());
         CHECK_THAT(ok && diff == 0, "CUDA INT8 Conv2D 3x3 (64->64, int32 bias) through the reference runtime is bit-exact with COMMON");
     }
+    // ---- the operators between the projections: QwenRmsNorm, Add, SiLU on BF16 [4,1024] ----
+    {
+        const int64_t rows = 4, hidden = 1024;
+        std::vector<uint16_t> x(static_cast<size_t>(rows * hidden)), g(static_cast<size_t>(hidden)), y(static_cast<size_t>(rows * hidden));
+        for (auto& v : x) v = FloatToBFloat16(Uniform(-3, 3));
+        for (auto& v : g) v = FloatToBFloat16(Uniform(-0.2f, 0.2f));
+        for (auto& v : y) v = FloatToBFloat16(Uniform(-1, 1));
+        const float eps = 1e-6f;
+        auto tx = MakeTensor(DataType::BF16, {rows, hidden}, x.data());
+        auto tg = MakeTensor(DataType::BF16, {hidden}, g.data());
+        auto ty = MakeTensor(DataType::BF16, {rows, hidden}, y.data());
+        auto te = MakeTensor(DataType::FP32, {1}, &eps);
+        auto Steps = [](const Tensor* a, const Tensor* b, int64_t n) {
+            int worst = 0;
+            const uint16_t* pa = static_cast<const uint16_t*>(a->raw_data());
+            const uint16_t* pb = static_cast<const uint16_t*>(b->raw_data());
+            for (int64_t i = 0; i < n; ++i) {
+                const int va = (pa[i] & 0x8000) ? -(pa[i] & 0x7fff) : (pa[i] & 0x7fff);
+                const int vb = (pb[i] & 0x8000) ? -(pb[i] & 0x7fff) : (pb[i] & 0x7fff);
+                worst = std::max(worst, std::abs(va - vb));
+            }
+            return worst;
+        };
+        // QwenRmsNorm (weight offset 1)
+        auto o1 = MakeTensor(DataType::BF16, {rows, hidden}); auto r1 = MakeTensor(DataType::BF16, {rows, hidden});
+        operators::QwenRmsNormParam np; np.input = tx; np.weight = tg; np.epsilon = te; np.out = o1; np.weight_offset = 1.0f;
+        operators::QwenRmsNormParam nr = np; nr.out = r1;
+        auto kn = Select(DeviceType::CUDA, DataType::BF16, "QwenRmsNorm", &np);
+        // Add (residual) and SiLU
+        auto o2 = MakeTensor(DataType::BF16, {rows, hidden}); auto r2 = MakeTensor(DataType::BF16, {rows, hidden});
+        operators::BinaryParam ap; ap.lhs = tx; ap.rhs = ty; ap.out = o2;
+        operators::BinaryParam ar = ap; ar.out = r2;
+        auto ka = Select(DeviceType::CUDA, DataType::BF16, "Add", &ap);
+        auto o3 = MakeTensor(DataType::BF16, {rows, hidden}); auto r3 = MakeTensor(DataType::BF16, {rows, hidden});
+        operators::UnaryParam sp; sp.input = tx; sp.out = o3;
+        operators::UnaryParam sr = sp; sr.out = r3;
+        auto ks = Select(DeviceType::CUDA, DataType::BF16, "SiLU", &sp);
+        bool ok = kn && ka && ks && IsB200Kernel(kn.get()) && IsB200Kernel(ka.get()) && IsB200Kernel(ks.get());
+        if (ok) {
+            cuda::DeferredHostSyncScope deferred;
+            ok = kn->compute() == 0 && ka->compute() == 0 && ks->compute() == 0 &&
+                 cuda::SyncTensorToHostIfNeeded(o1.get(), o1->memory_size(), o1->raw_data()) == 0 &&
+                 cuda::SyncTensorToHostIfNeeded(o2.get(), o2->memory_size(), o2->raw_data()) == 0 &&
+                 cuda::SyncTensorToHostIfNeeded(o3.get(), o3->memory_size(), o3->raw_data()) == 0;
+        }
+        ok = ok && RunCommon(DataType::BF16, "QwenRmsNorm", &nr) == 0 && RunCommon(DataType::BF16, "Add", &ar) == 0 && RunCommon(DataType::BF16, "SiLU", &sr) == 0;
+        const int d1 = ok ? Steps(o1.get(), r1.get(), rows * hidden) : 99, d2 = ok ? Steps(o2.get(), r2.get(), rows * hidden) : 99,
+                  d3 = ok ? Steps(o3.get(), r3.get(), rows * hidden) : 99;
+        std::printf("      BF16 codes from COMMON: QwenRmsNorm %d, Add %d, SiLU %d\n", d1, d2, d3);
+        CHECK_THAT(ok && d1 <= 1 && d2 == 0 && d3 <= 1, "CUDA QwenRmsNorm / Add / SiLU (BF16) through the reference runtime: within one code / exact / within one code of COMMON");
+    }
+
+    // ---- fused FP8 lm-head selection against the reference's own x86 kernel (exact integer data, ties and a NaN row) ----
+    {
+        const int64_t k = 64, n = 640;
+        std::vector<uint8_t> a(static_cast<size_t>(k)), b(static_cast<size_t>(n * k));
+        for (auto& v : a) v = FloatToFp8E4M3(static_cast<float>(static_cast<int>(NextRandom() % 5) - 2));
+        for (auto& v : b) v = FloatToFp8E4M3(static_cast<float>(static_cast<int>(NextRandom() % 5) - 2));
+        for (int64_t row : {int64_t{77}, int64_t{300}, int64_t{639}, int64_t{10}})
+            for (int64_t c = 0; c < k; ++c) {
+                const float av = Fp8E4M3ToFloat(a[static_cast<size_t>(c)]);
+                b[static_cast<size_t>(row * k + c)] = FloatToFp8E4M3(av > 0 ? 2.0f : (av < 0 ? -2.0f : 0.0f));
+            }
+        b[static_cast<size_t>(10 * k + 3)] = 0x7f;  // row 10 would win but holds a NaN
+        auto ta = MakeTensor(DataType::FP8E4M3, {1, k}, a.data()); ta->set_quantization({true, 1.0f});
+        auto tb = MakeTensor(DataType::FP8E4M3, {n, k}, b.data()); tb->set_quantization({true, 1.0f}); tb->set_immutable(true);
+        auto tok = MakeTensor(DataType::INT64, {1}); auto tok_ref = MakeTensor(DataType::INT64, {1});
+        operators::QwenGemmArgmaxParam gp; gp.a = ta; gp.b = tb; gp.out = tok; gp.output_scale = 2.0f;
+        operators::QwenGemmArgmaxParam gr = gp; gr.out = tok_ref;
+        auto kg = Select(DeviceType::CUDA, DataType::FP8E4M3, "QwenGemmArgmax", &gp);
+        bool ok = kg && IsB200Kernel(kg.get()) && kg->Prepare() == 0;
+        if (ok) {
+            cuda::DeferredHostSyncScope deferred;
+            ok = kg->compute() == 0 && cuda::SyncTensorToHostIfNeeded(tok.get(), tok->memory_size(), tok->raw_data()) == 0;
+        }
+        auto kx = KernelDispatcher::instance().create(DeviceType::X86, DataType::FP8E4M3, "QwenGemmArgmax");
+        ok = ok && kx != nullptr;
+        if (ok) { kx->SetParam(&gr); ok = kx->Prepare() == 0 && kx->compute() == 0; }
+        const long long got = ok ? static_cast<const int64_t*>(tok->raw_data())[0] : -99, want = ok ? static_cast<const int64_t*>(tok_ref->raw_data())[0] : -98;
+        std::printf("      token: b200 %lld, reference x86 kernel %lld\n", got, want);
+        CHECK_THAT(ok && got == want && got == 77, "CUDA FP8 QwenGemmArgmax selects the token the reference's x86 kernel selects (lowest index among ties, NaN row skipped)");
+    }
+
+    // ---- a node built with a scratch budget of zero: same bytes as the node with its own scratch buffer ----
+    {
+        Fp8Case c1 = MakeFp8(DataType::FP8E4M3, 4, 4096, 8192);
+        Fp8Case c0 = c1;
+        c0.out = MakeTensor(DataType::FP8E4M3, {4, 8192}); c0.out->set_quantization({true, 0.25f});
+        c0.param.out = c0.out;
+        auto k1 = Select(DeviceType::CUDA, DataType::FP8E4M3, "MatMul", &c1.param);
+        std::unique_ptr<KernelBase> k0;
+        {
+            KernelSelectionScope budget(KernelFallbackPolicy::kRequireRequested, nullptr, false, 0);
+            k0 = KernelDispatcher::instance().create(DeviceType::CUDA, DataType::FP8E4M3, "MatMul");
+            if (k0) { k0->SetParam(&c0.param); if (!KernelBase::FinalizeSelection(&k0).ok()) k0.reset(); }
+        }
+        bool ok = k1 && k0 && IsB200Kernel(k0.get()) && k1->Prepare() == 0 && k0->Prepare() == 0;
+        if (ok) {
+            cuda::DeferredHostSyncScope deferred;
+            ok = k1->compute() == 0 && k0->compute() == 0 &&
+                 cuda::SyncTensorToHostIfNeeded(c1.out.get(), c1.out->memory_size(), c1.out->raw_data()) == 0 &&
+                 cuda::SyncTensorToHostIfNeeded(c0.out.get(), c0.out->memory_size(), c0.out->raw_data()) == 0;
+        }
+        CHECK_THAT(ok && std::memcmp(c1.out->raw_data(), c0.out->raw_data(), 4 * 8192) == 0,
+                   "workspace limit 0: FP8 MatMul [4,4096]x[4096,8192] runs without allocating scratch and gives the same bytes");
+    }
     CHECK_THAT(fth_b200_device_status() == 0, "no bounded device-side wait gave up");
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// time: the same MatMul nodes through the reference runtime, on whichever CUDA candidate is selected
+// ---------------------------------------------------------------------------------------------------------
+template <typename Case>
+static void TimeNode(const char* what, DataType dtype, Case* c, int repeats) {
+    auto k = Select(DeviceType::CUDA, dtype, "MatMul", &c->param);
+    if (!k || k->Prepare() != 0) { std::printf("time  %s: no kernel\n", what); ++g_failures; return; }
+    cuda::DeferredHostSyncScope deferred;
+    for (int i = 0; i < 3; ++i) k->compute();
+    cuda::SynchronizeInferenceStream();
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    cudaEventRecord(e0, cuda::InferenceStream());
+    int rc = 0;
+    for (int i = 0; i < repeats; ++i) rc |= k->compute();
+    cudaEventRecord(e1, cuda::InferenceStream());
+    cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    std::printf("time  %s: %.2f us per compute() on %s (%s), rc %d\n", what, ms * 1000.0f / repeats,
+                IsB200Kernel(k.get()) ? "the b200 candidate" : "the reference CUDA kernel", IsB200Kernel(k.get()) ? fth_b200_last_variant() : "reference", rc);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+}
+
+static void RunTime() {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) { std::printf("skip  no CUDA device\n"); return; }
+    const bool registered = feather::kernel::b200::RegisterB200Kernels();
+    std::printf("time  b200 candidates %s\n", registered ? "registered" : "disabled (FEATHER_DISABLE_B200=1): reference CUDA kernels");
+    auto context = cuda::CreateExecutionContext();
+    cuda::ExecutionContextScope scope(context);
+    { Fp8Case c = MakeFp8(DataType::FP8E4M3, 1, 1024, 3072); TimeNode("FP8E4M3 MatMul M=1 K=1024 N=3072 (config 1)", DataType::FP8E4M3, &c, 200); }
+    { Fp8Case c = MakeFp8(DataType::FP8E4M3, 1, 8192, 28672); TimeNode("FP8E4M3 MatMul M=1 K=8192 N=28672 (config 5)", DataType::FP8E4M3, &c, 50); }
+    { Fp8Case c = MakeFp8(DataType::FP8E4M3, 256, 8192, 8192); TimeNode("FP8E4M3 MatMul M=256 K=8192 N=8192", DataType::FP8E4M3, &c, 20); }
+    { Int8Case c = MakeInt8(128, 1024, 1024); TimeNode("INT8 MatMul M=128 K=1024 N=1024 per-channel (config 2)", DataType::INT8, &c, 50); }
+    { Int8Case c = MakeInt8(1, 8192, 28672); TimeNode("INT8 MatMul M=1 K=8192 N=28672 per-channel (config 5)", DataType::INT8, &c, 20); }
 }
 
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "select";
     if (mode == "select") RunSelect();
     else if (mode == "run") RunGpu();
-    else { std::fprintf(stderr, "usage: adapter_e2e select|run\n"); return 2; }
+    else if (mode == "time") RunTime();
+    else { std::fprintf(stderr, "usage: adapter_e2e select|run|time\n"); return 2; }
     std::printf("%s: %d failure(s)\n", mode.c_str(), g_failures);
     return g_failures == 0 ? 0 : 1;
 }

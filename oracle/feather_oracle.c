@@ -504,3 +504,54 @@ int fo_cast(int in_dtype, const void* x, float in_scale, int out_dtype, void* ou
     }
     return 0;
 }
+
+/* ---- QwenRmsNorm: src/kernel/common/qwen_rms_norm.cc:71-95 ----------------------------------------------------
+ * x / weight / out FP32 or BF16.  Squares are added one after another in FP32; inverse_rms = 1 / sqrt(sum / hidden + eps);
+ * out = x * inverse_rms * (weight + weight_offset), each multiply rounded; BF16 output through util/bf16.h. */
+int fo_qwen_rms_norm(int x_dtype, const void* x, int w_dtype, const void* w, float weight_offset, float epsilon,
+                     int out_dtype, void* out, int64_t rows, int64_t hidden) {
+    if (rows <= 0 || hidden <= 0 || !x || !w || !out) return -1;
+    if ((x_dtype != FO_FP32 && x_dtype != FO_BF16) || (w_dtype != FO_FP32 && w_dtype != FO_BF16) ||
+        (out_dtype != FO_FP32 && out_dtype != FO_BF16) || !isfinite(epsilon) || epsilon < 0.0f) return -1;
+#pragma omp parallel for schedule(static) if (rows > 8)
+    for (int64_t r = 0; r < rows; ++r) {
+        float sum_square = 0.0f;
+        for (int64_t c = 0; c < hidden; ++c) {
+            const float v = read_float(x_dtype, x, r * hidden + c);
+            sum_square += v * v;
+        }
+        const float inverse_rms = 1.0f / sqrtf(sum_square / (float)hidden + epsilon);
+        for (int64_t c = 0; c < hidden; ++c) {
+            const float v = read_float(x_dtype, x, r * hidden + c);
+            const float scale = read_float(w_dtype, w, c) + weight_offset;
+            const float y = v * inverse_rms * scale;
+            if (out_dtype == FO_BF16) ((uint16_t*)out)[r * hidden + c] = fo_bf16_encode(y);
+            else ((float*)out)[r * hidden + c] = y;
+        }
+    }
+    return 0;
+}
+
+/* ---- Add / Mul (src/kernel/common/add.cc:80-109, mul.cc) and SiLU (src/kernel/common/silu.cc:38-55) -------------
+ * FP32 / FP16 / BF16: read as float, one operation, one rounding to the output type (TensorIO<dtype>::Write).
+ * rhs is the same shape (rhs_count == count) or one trailing row broadcast over lhs.  op: 0 Add, 1 Mul. */
+static void write_float(int dtype, void* out, int64_t i, float v) {
+    if (dtype == FO_FP32) ((float*)out)[i] = v;
+    else if (dtype == FO_FP16) ((uint16_t*)out)[i] = fo_f16_encode(v);
+    else ((uint16_t*)out)[i] = fo_bf16_encode(v);
+}
+int fo_binary(int op, int dtype, const void* lhs, const void* rhs, void* out, int64_t count, int64_t rhs_count) {
+    if (count <= 0 || rhs_count <= 0 || count % rhs_count != 0 || (op != 0 && op != 1)) return -1;
+    for (int64_t i = 0; i < count; ++i) {
+        const float a = read_float(dtype, lhs, i), b = read_float(dtype, rhs, i % rhs_count);
+        write_float(dtype, out, i, op == 0 ? a + b : a * b);
+    }
+    return 0;
+}
+int fo_silu(int dtype, const void* x, void* out, int64_t count) {
+    for (int64_t i = 0; i < count; ++i) {
+        const float v = read_float(dtype, x, i);
+        write_float(dtype, out, i, v / (1.0f + expf(-v)));
+    }
+    return 0;
+}

@@ -298,6 +298,62 @@ void* ref_dequantize_linear_create(const int8_t* x, const float* scales, const i
     return Finish(std::move(kernel), p, out, static_cast<size_t>(rows * channels) * ElementBytes(to));
 }
 
+// ---- QwenRmsNorm, Add / Mul, SiLU: the operators between the projections of a decoder block --------------------
+// (src/kernel/common/qwen_rms_norm.cc:71-95, add.cc:80-109, mul.cc, silu.cc:38-55; x86 versions on device 1)
+void* ref_qwen_rms_norm_create(int device, int x_dtype, const void* x, int w_dtype, const void* weight, float weight_offset,
+                               float epsilon, int out_dtype, int64_t rows, int64_t hidden) {
+    const DataType x_dt = static_cast<DataType>(x_dtype), w_dt = static_cast<DataType>(w_dtype), o_dt = static_cast<DataType>(out_dtype);
+    auto p = std::make_shared<feather::operators::QwenRmsNormParam>();
+    p->input = MakeTensor(x, x_dt, {rows, hidden});
+    p->weight = MakeTensor(weight, w_dt, {hidden});
+    p->epsilon = MakeTensor(&epsilon, DataType::FP32, {1});
+    auto out = MakeTensor(nullptr, o_dt, {rows, hidden});
+    p->out = out;
+    p->weight_offset = weight_offset;
+    auto kernel = KernelDispatcher::instance().create(ToDevice(device), x_dt, "QwenRmsNorm");
+    return Finish(std::move(kernel), p, out, static_cast<size_t>(rows * hidden) * ElementBytes(o_dt));
+}
+
+// op: 0 = "Add", 1 = "Mul".  rhs is [rows, cols] or, when rhs_rows == 1, one row [cols] broadcast over lhs.
+void* ref_binary_create(int device, int op, int dtype, const void* lhs, const void* rhs, int64_t rows, int64_t cols, int64_t rhs_rows) {
+    const DataType dt = static_cast<DataType>(dtype);
+    auto p = std::make_shared<feather::operators::BinaryParam>();
+    p->lhs = MakeTensor(lhs, dt, {rows, cols});
+    p->rhs = rhs_rows == 1 ? MakeTensor(rhs, dt, {cols}) : MakeTensor(rhs, dt, {rows, cols});
+    auto out = MakeTensor(nullptr, dt, {rows, cols});
+    p->out = out;
+    auto kernel = KernelDispatcher::instance().create(ToDevice(device), dt, op == 0 ? "Add" : "Mul");
+    return Finish(std::move(kernel), p, out, static_cast<size_t>(rows * cols) * ElementBytes(dt));
+}
+
+void* ref_silu_create(int device, int dtype, const void* x, int64_t count) {
+    const DataType dt = static_cast<DataType>(dtype);
+    auto p = std::make_shared<feather::operators::UnaryParam>();
+    p->input = MakeTensor(x, dt, {count});
+    auto out = MakeTensor(nullptr, dt, {count});
+    p->out = out;
+    auto kernel = KernelDispatcher::instance().create(ToDevice(device), dt, "SiLU");
+    return Finish(std::move(kernel), p, out, static_cast<size_t>(count) * ElementBytes(dt));
+}
+
+// ---- fused lm-head projection + greedy selection (FP8: src/kernel/x86/linear_fp8.cc:733-1004; there is no COMMON
+// kernel for it).  a [1, K], b [N, K] (vocabulary rows), per-tensor scales; returns the kernel whose output is one int64.
+void* ref_qwen_gemm_argmax_create(int device, int dtype, const uint8_t* a, float a_scale, const uint8_t* b, float b_scale,
+                                  float output_scale, int64_t k, int64_t n) {
+    const DataType dt = static_cast<DataType>(dtype);
+    auto p = std::make_shared<feather::operators::QwenGemmArgmaxParam>();
+    p->a = MakeTensor(a, dt, {1, k});
+    p->a->set_quantization({true, a_scale});
+    p->b = MakeTensor(b, dt, {n, k});
+    p->b->set_quantization({true, b_scale});
+    p->b->set_immutable(true);
+    auto out = MakeTensor(nullptr, DataType::INT64, {1});
+    p->out = out;
+    p->output_scale = output_scale;
+    auto kernel = KernelDispatcher::instance().create(ToDevice(device), dt, "QwenGemmArgmax");
+    return Finish(std::move(kernel), p, out, sizeof(int64_t));
+}
+
 // ---- handle operations ---------------------------------------------------------------------
 int ref_kernel_device(void* handle) {
     return handle ? static_cast<int>(static_cast<Handle*>(handle)->kernel->device()) : -1;

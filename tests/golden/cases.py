@@ -93,3 +93,62 @@ def codec_values() -> np.ndarray:
         rng = np.random.default_rng(1234)
         return np.concatenate([specials, -specials, lcg_floats(20000), (rng.standard_normal(20000) * 50).astype(np.float32),
                                (rng.standard_normal(20000) * 1e-3).astype(np.float32)])
+
+
+# ---- the operators between the projections of a decoder block, and the fused lm-head selection ----------------------
+def to_bf16(x):
+    """float32 -> BF16 bits, round to nearest even (finite inputs)."""
+    b = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def decoder_op_inputs():
+    rng = np.random.default_rng(0xDEC0DE)
+    d = {}
+    d["rms_x_bf16"] = to_bf16(rng.standard_normal((5, 1024)).astype(np.float32) * np.float32(3.0))
+    d["rms_w_bf16"] = to_bf16(rng.standard_normal(1024).astype(np.float32) * np.float32(0.1))
+    d["rms_x_fp32"] = (rng.standard_normal((3, 130)) * 0.5).astype(np.float32)
+    d["rms_w_fp32"] = (rng.standard_normal(130) * 0.1 + 1.0).astype(np.float32)
+    d["bin_lhs_bf16"] = to_bf16(rng.standard_normal((4, 1030)).astype(np.float32) * np.float32(2.0))
+    d["bin_rhs_bf16"] = to_bf16(rng.standard_normal((4, 1030)).astype(np.float32))
+    d["bin_row_bf16"] = to_bf16(rng.standard_normal(1030).astype(np.float32))
+    d["bin_lhs_fp32"] = rng.standard_normal((2, 77)).astype(np.float32)
+    d["bin_rhs_fp32"] = rng.standard_normal((2, 77)).astype(np.float32)
+    silu = np.concatenate([rng.standard_normal(7000).astype(np.float32) * np.float32(3.0),
+                           np.array([0.0, -0.0, 30.0, -30.0, 88.0, -88.0, 100.0, -100.0, 1e-8, -1e-8], np.float32)])
+    d["silu_bf16"] = to_bf16(silu)
+    d["silu_fp32"] = silu
+    return d
+
+
+ARGMAX = [  # name, dtype, k, n, output_scale factor, kind
+    ("argmax_e4m3_random", O.E4M3, 256, 4096, 1.0, "random"),
+    ("argmax_e5m2_random", O.E5M2, 512, 2048, 0.5, "random"),
+    ("argmax_e4m3_ties", O.E4M3, 64, 640, 1.0, "ties"),
+    ("argmax_e5m2_nan_column", O.E5M2, 64, 256, 2.0, "nan"),
+]
+
+
+def argmax_case(entry):
+    """a [1, K] codes, b [N, K] codes (vocabulary rows), scales.  "ties": small integers, so every product sum is exact
+    in FP32 and several rows reach the same maximum (the lowest index must win); "nan": the best row holds a NaN code
+    and must be skipped."""
+    name, dtype, k, n, so_factor, kind = entry
+    seed = int(hashlib.sha256(name.encode()).hexdigest()[:8], 16)
+    rng = np.random.default_rng(seed)
+    if kind == "random":
+        case = util.make_fp8_linear(dtype, 1, k, n, seed, trans_b=True)
+        return dict(a=case["a"], sa=case["sa"], b=case["w"], sb=case["sw"], so=case["so"] * so_factor)
+    a = O.fp8_encode(dtype, rng.integers(-2, 3, (1, k)).astype(np.float32))
+    b = O.fp8_encode(dtype, rng.integers(-2, 3, (n, k)).astype(np.float32))
+    if kind == "ties":
+        best = O.fp8_encode(dtype, np.sign(O.fp8_decode(dtype, a)).astype(np.float32) * 2.0)  # the largest possible sum
+        for row in (77, 300, 301, 639):
+            b[row] = best[0]
+    else:
+        best = O.fp8_encode(dtype, np.sign(O.fp8_decode(dtype, a)).astype(np.float32) * 2.0)
+        b[10] = best[0]
+        b[10, 3] = 0x7D if dtype == O.E5M2 else 0x7F  # NaN: the whole row's sum is NaN and cannot be selected
+        b[200] = best[0]
+        b[200, :8] = O.fp8_encode(dtype, np.zeros(8, np.float32))
+    return dict(a=a, sa=1.0, b=b, sb=1.0, so=float(k) / 32 * so_factor)

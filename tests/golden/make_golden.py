@@ -63,6 +63,27 @@ def main():
     out["cast/fp32_to_e4m3"] = O.cast(O.FP32, x, 1.0, O.E4M3, 0.03125, impl="ref")
     out["cast/e5m2_to_bf16"] = O.cast(O.E5M2, out["cast/bf16_to_e5m2"], 0.125, O.BF16, 1.0, impl="ref")
     out["cast/e4m3_to_fp32"] = O.cast(O.E4M3, out["cast/fp32_to_e4m3"], 0.03125, O.FP32, 1.0, impl="ref").view(np.uint32)
+    # QwenRmsNorm / Add / Mul / SiLU (Common and x86) and the fused FP8 lm-head selection (x86 only)
+    d = G.decoder_op_inputs()
+    out["dec/digest"] = np.array(G.digest(*[d[k] for k in sorted(d)]))
+    for dev_name, dev in (("common", O.COMMON), ("x86", O.X86)):
+        out[f"dec/rms_bf16/{dev_name}"] = O.qwen_rms_norm(O.BF16, d["rms_x_bf16"], O.BF16, d["rms_w_bf16"], 1.0, 1e-6, O.BF16, impl="ref", device=dev)
+        out[f"dec/rms_fp32/{dev_name}"] = O.qwen_rms_norm(O.FP32, d["rms_x_fp32"], O.FP32, d["rms_w_fp32"], 0.0, 1e-5, O.FP32, impl="ref", device=dev).view(np.uint32)
+        out[f"dec/rms_bf16_to_fp32/{dev_name}"] = O.qwen_rms_norm(O.BF16, d["rms_x_bf16"], O.FP32, O.fp8_decode(O.E4M3, np.arange(1024) % 120), 0.5, 1e-6, O.FP32,
+                                                                 impl="ref", device=dev).view(np.uint32)
+        for op_name, op in (("add", 0), ("mul", 1)):
+            out[f"dec/{op_name}_bf16/{dev_name}"] = O.binary(op, O.BF16, d["bin_lhs_bf16"], d["bin_rhs_bf16"], impl="ref", device=dev)
+            out[f"dec/{op_name}_row_bf16/{dev_name}"] = O.binary(op, O.BF16, d["bin_lhs_bf16"], d["bin_row_bf16"], impl="ref", device=dev)
+            out[f"dec/{op_name}_fp32/{dev_name}"] = O.binary(op, O.FP32, d["bin_lhs_fp32"], d["bin_rhs_fp32"], impl="ref", device=dev).view(np.uint32)
+        out[f"dec/silu_bf16/{dev_name}"] = O.silu(O.BF16, d["silu_bf16"], impl="ref", device=dev)
+        out[f"dec/silu_fp32/{dev_name}"] = O.silu(O.FP32, d["silu_fp32"], impl="ref", device=dev).view(np.uint32)
+    for entry in G.ARGMAX:
+        c = G.argmax_case(entry)
+        name, dtype = entry[0], entry[1]
+        out[f"argmax/{name}/digest"] = np.array(G.digest(c["a"], c["b"]))
+        out[f"argmax/{name}/x86_index"] = np.array(O.qwen_gemm_argmax(dtype, c["a"], c["sa"], c["b"], c["sb"], c["so"]))
+        # the materialised output row of the same projection through the Common Gemm kernel (b is [N, K]: trans_b)
+        out[f"argmax/{name}/common_codes"] = O.fp8_linear(O.OP_GEMM, dtype, c["a"], c["sa"], c["b"], c["sb"], c["so"], trans_b=True, impl="ref", device=O.COMMON)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_outputs.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1024:.0f} KB")

@@ -35,4 +35,18 @@ def test_selection_contract_inside_reference_dispatcher():
 def test_candidates_run_through_reference_cuda_runtime():
     out = _run("run")
     assert "skip" not in out
-    assert out.count("ok  ") >= 6
+    assert out.count("ok  ") >= 9
+
+
+@needs_binary
+@pytest.mark.gpu
+def test_timing_mode_runs_on_both_candidate_sets():
+    """`adapter_e2e time` prints microseconds per compute() for the same MatMul nodes with this backend's candidates
+    and, with FEATHER_DISABLE_B200=1, with the reference's own CUDA kernels (cuBLASLt FP8 + a quantise kernel; a scalar
+    INT8 kernel): the on-box GPU comparator.  The figures are printed, not asserted."""
+    ours = _run("time")
+    assert "the b200 candidate" in ours and "no kernel" not in ours
+    env = dict(os.environ, FEATHER_DISABLE_B200="1")
+    proc = subprocess.run([EXE, "time"], capture_output=True, text=True, timeout=600, env=env)
+    print(proc.stdout)
+    assert proc.returncode == 0 and "the reference CUDA kernel" in proc.stdout and "the b200 candidate" not in proc.stdout

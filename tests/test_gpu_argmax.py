@@ -89,3 +89,38 @@ def test_fused_argmax_skips_nan_and_declines_dense_shapes(cuda):
     big = B.fp8_linear_desc(dtype=B.E4M3, op=B.OP_MATMUL, m=300, k=k, n=n, a=a_dev, w=w_dev, out=out, a_scale=1.0, w_scale=1.0, out_scale=2.0)
     assert B.lib().fth_b200_fp8_linear_argmax(C.byref(big), C.c_void_p(idx.data_ptr()), B.current_stream()) == B.ERR_UNSUPPORTED
     del ws
+
+
+def test_fused_argmax_against_the_reference_x86_lm_head_kernel(cuda):
+    """Pinned to the reference: the seeded lm-head cases of tests/golden/cases.py were run through the reference's own
+    fused FP8 kernel (QwenGemmArgmaxKernel<X86, FP8*>, src/kernel/x86/linear_fp8.cc:733-1004) when the fixtures were
+    made.  On the exact-integer cases (ties between rows, a NaN row, output scale != 1) the selected index must be the
+    same.  On random data the two kernels add the 256 .. 512 products in different orders, so output codes may differ
+    by one and with them the winner among near-equal rows: there the row picked here must hold, in the reference's
+    materialised output, a code within one step of the code of the row the reference picked."""
+    import os
+    from tests.golden import cases as G
+    from tests import util
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_outputs.npz"))
+    torch = cuda
+    for entry in G.ARGMAX:
+        name, dtype = entry[0], entry[1]
+        c = G.argmax_case(entry)
+        n, k = c["b"].shape
+        a_dev, w_dev = torch.from_numpy(c["a"]).cuda(), torch.from_numpy(c["b"]).cuda()
+        out = torch.zeros((1, n), dtype=torch.uint8, device="cuda")
+        idx = torch.full((1,), -7, dtype=torch.int64, device="cuda")
+        d = B.fp8_linear_desc(dtype=dtype, op=B.OP_GEMM, m=1, k=k, n=n, a=a_dev, w=w_dev, out=out, a_scale=c["sa"], w_scale=c["sb"],
+                              out_scale=c["so"], trans_b=True, weights_static=True)
+        ws = B.linear_workspace(torch, d)
+        assert B.lib().fth_b200_fp8_linear_argmax(C.byref(d), C.c_void_p(idx.data_ptr()), B.current_stream()) == 0
+        torch.cuda.synchronize()
+        got, want = int(idx.item()), int(gold[f"argmax/{name}/x86_index"])
+        codes = gold[f"argmax/{name}/common_codes"][0]
+        if entry[5] == "random":
+            assert util.fp8_code_distance(codes[got:got + 1], codes[want:want + 1]).max() <= 1, (name, got, want)
+        else:
+            assert got == want, (name, got, want)
+        print(f"{name}: fused index {got}, reference x86 kernel {want}")
+        del ws
+    assert B.device_status() == 0
