@@ -15,18 +15,7 @@
 //               replica cache (cuda_detail::CopyTensorToDevice / AllocateTensorOnDevice,
 //               src/kernel/cuda/kernel_io.cuh:285-340) and the launch goes to cuda_detail::InferenceStream(), so
 //               deferred host sync and CUDA-graph capture (src/kernel/backend.cc:80-118) keep working.
-#include <algorithm>
-#include <cmath>
-#include <cstdint>
-#include <cstdlib>
-#include <memory>
-#include <vector>
-
-#include "core/kernel.h"
-#include "fth_b200.h"
-#include "quant/quantization.h"
-#include "src/kernel/cuda/kernel_io.cuh"
-#include "src/kernel/cuda/runtime.h"
+#include "b200_common.cuh"
 #include "src/operator/params.h"
 #include "util/bf16.h"
 #include "util/timer.h"
@@ -35,55 +24,11 @@ namespace feather {
 namespace kernel {
 namespace b200 {
 
-namespace {
-
-constexpr int kPriority = 10;  // reference CUDA kernels register with priority 0 (legacy registerKernel)
-
-}  // namespace
-
-// Common base of every kernel of this backend, so that callers (and tests) can tell which candidate the
-// dispatcher finally selected.
-class B200Kernel : public KernelBase {};
 bool IsB200Kernel(const KernelBase* kernel) { return dynamic_cast<const B200Kernel*>(kernel) != nullptr; }
 
 namespace {
 
-Status FromAbi(int rc, const char* what) {
-    switch (rc) {
-        case FTH_B200_OK: return Status::Ok();
-        case FTH_B200_ERR_UNSUPPORTED:
-        case FTH_B200_ERR_OVERFLOW:  // the reference candidate reports int32 overflow itself (int8.cu:101-110)
-            return Status::Error(StatusCode::kUnsupported, std::string("b200 declines ") + what);
-        default: return Status::Error(StatusCode::kInvalidArgument, std::string("b200 rejects ") + what);
-    }
-}
-
-// A fixed, suitably aligned stand-in for device pointers during capability checks (nothing is dereferenced).
-void* const kProbe = reinterpret_cast<void*>(uintptr_t{1} << 20);
-
-// Device scratch owned by one kernel instance (one per session node): allocated in Prepare(), never in compute().
-class DeviceScratch {
-   public:
-    ~DeviceScratch() { if (ptr_) cudaFree(ptr_); }
-    int Reserve(size_t bytes, bool zero) {
-        if (bytes <= bytes_) return 0;
-        if (ptr_) cudaFree(ptr_);
-        ptr_ = nullptr; bytes_ = 0;
-        if (cudaMalloc(&ptr_, bytes) != cudaSuccess) return -1;
-        bytes_ = bytes;
-        return zero && cudaMemsetAsync(ptr_, 0, bytes, cuda_detail::InferenceStream()) != cudaSuccess ? -1 : 0;
-    }
-    int Upload(const void* host, size_t bytes) {
-        if (Reserve(bytes, false) != 0) return -1;
-        return cudaMemcpyAsync(ptr_, host, bytes, cudaMemcpyHostToDevice, cuda_detail::InferenceStream()) == cudaSuccess &&
-                       cudaStreamSynchronize(cuda_detail::InferenceStream()) == cudaSuccess ? 0 : -1;  // host vector is temporary
-    }
-    void* get() const { return ptr_; }
-    size_t bytes() const { return bytes_; }
-   private:
-    void* ptr_{nullptr};
-    size_t bytes_{0};
-};
+void* const kProbe = ProbePointer();
 
 // The three linear operators differ only in their parameter struct (src/operator/params.h:27-55, 141-150).
 struct LinearView {
@@ -232,43 +177,6 @@ class Fp8LinearKernel final : public B200Kernel {
 // ---------------------------------------------------------------------------------------------------------
 // INT8 FC, MatMul, Gemm — in front of RunCudaInt8Linear / RunCudaInt8MatMul (src/kernel/cuda/int8.cu:313-368)
 // ---------------------------------------------------------------------------------------------------------
-struct Int8WeightParams {
-    std::vector<float> scales;
-    std::vector<int32_t> zero_points;
-    int32_t zp_max_abs{0};
-};
-
-// Mirrors int8_detail::BuildQuantizationView (src/kernel/common/int8_kernel_utils.h:55-84).
-bool ReadInt8Quantization(const Tensor* t, bool allow_per_channel, int64_t axis, int64_t channels, Int8WeightParams* out) {
-    if (!t || t->data_type() != DataType::INT8 || !t->IsInitialized()) return false;
-    const QuantizationParams& q = t->quantization();
-    if (!q.enabled || !ValidateQuantizationParams(q, t->dims().data())) return false;
-    if (q.granularity == QuantizationGranularity::kPerChannel) {
-        if (!allow_per_channel || q.axis != axis || q.scales.size() != static_cast<size_t>(channels)) return false;
-        out->scales = q.scales;
-        out->zero_points.resize(static_cast<size_t>(channels));
-        for (int64_t c = 0; c < channels; ++c) out->zero_points[static_cast<size_t>(c)] = q.zero_point_at(static_cast<size_t>(c));
-    } else if (q.granularity == QuantizationGranularity::kPerTensor) {
-        out->scales = {q.scale_at(0)};
-        out->zero_points = {q.zero_point_at(0)};
-    } else {
-        return false;
-    }
-    out->zp_max_abs = 0;
-    for (int32_t z : out->zero_points) out->zp_max_abs = std::max(out->zp_max_abs, std::abs(z));
-    return true;
-}
-
-// Largest |bias| of an INT32 bias constant that is readable on the host (the static quantiser's output), else 0.
-int64_t BiasMaxAbs(const Tensor* bias) {
-    int64_t worst = 0;
-    if (bias && bias->IsInitialized() && bias->data_type() == DataType::INT32) {
-        const int32_t* b = bias->data<int32_t>();
-        for (int64_t i = 0; i < bias->numel(); ++i) worst = std::max<int64_t>(worst, std::llabs(static_cast<long long>(b[i])));
-    }
-    return worst;
-}
-
 template <typename Param>
 class Int8LinearKernel final : public B200Kernel {
    public:
@@ -594,14 +502,6 @@ namespace {
 bool PlainFloat(DataType t) { return t == DataType::FP32 || t == DataType::BF16; }
 bool AnyFloat(DataType t) { return t == DataType::FP32 || t == DataType::BF16 || t == DataType::FP16; }
 
-// Device views of an input and an output tensor through the session's replica cache.
-int AcquireIn(const Tensor* t, void** ptr) {
-    return cuda_detail::AcquireTensorDevice(t, static_cast<size_t>(t->numel()) * DataTypeBytes(t->data_type()), t->raw_data(), ptr);
-}
-int FinishOut(Tensor* t, size_t bytes) {
-    if (cuda_detail::DeferredHostSyncEnabled()) return 0;
-    return cuda_detail::SyncTensorToHost(t, bytes, t->raw_data());
-}
 }  // namespace
 
 class QwenRmsNormKernelB200 final : public B200Kernel {
@@ -765,36 +665,30 @@ class QwenGemmArgmaxKernelB200 final : public B200Kernel {
 // kernels lazily, include/core/kernel.h:212-225); the environment variable FEATHER_DISABLE_B200=1 leaves the
 // reference candidates alone, so A/B runs against the reference CUDA kernels need one switch.
 // ---------------------------------------------------------------------------------------------------------
-template <typename K>
-void Add(DataType dtype, const char* op, const char* id) {
-    KernelDispatcher::instance().RegisterCandidate(DeviceType::CUDA, dtype, DataLayout::ND, op, id,
-                                                   [] { return std::unique_ptr<KernelBase>(new K()); }, {}, kPriority);
-}
-
 bool RegisterB200Kernels() {
     const char* off = std::getenv("FEATHER_DISABLE_B200");
     if (off != nullptr && off[0] == '1') return false;
-    Add<Fp8LinearKernel<DataType::FP8E4M3, operators::FcParam>>(DataType::FP8E4M3, "FC", "b200.fp8.fc");
-    Add<Fp8LinearKernel<DataType::FP8E4M3, operators::MatMulParam>>(DataType::FP8E4M3, "MatMul", "b200.fp8.matmul");
-    Add<Fp8LinearKernel<DataType::FP8E4M3, operators::GemmParam>>(DataType::FP8E4M3, "Gemm", "b200.fp8.gemm");
-    Add<Fp8LinearKernel<DataType::FP8E5M2, operators::FcParam>>(DataType::FP8E5M2, "FC", "b200.fp8.fc");
-    Add<Fp8LinearKernel<DataType::FP8E5M2, operators::MatMulParam>>(DataType::FP8E5M2, "MatMul", "b200.fp8.matmul");
-    Add<Fp8LinearKernel<DataType::FP8E5M2, operators::GemmParam>>(DataType::FP8E5M2, "Gemm", "b200.fp8.gemm");
-    Add<Int8LinearKernel<operators::FcParam>>(DataType::INT8, "FC", "b200.int8.fc");
-    Add<Int8LinearKernel<operators::MatMulParam>>(DataType::INT8, "MatMul", "b200.int8.matmul");
-    Add<Int8LinearKernel<operators::GemmParam>>(DataType::INT8, "Gemm", "b200.int8.gemm");
-    Add<Int8Conv2dKernel>(DataType::INT8, "Conv2D", "b200.int8.conv2d");
-    for (DataType t : {DataType::FP32, DataType::FP16, DataType::BF16}) Add<QuantizeLinearKernelB200>(t, "QuantizeLinear", "b200.quantize_linear");
-    Add<DequantizeLinearKernelB200>(DataType::INT8, "DequantizeLinear", "b200.dequantize_linear");
-    for (DataType t : {DataType::FP32, DataType::FP16, DataType::BF16, DataType::FP8E4M3, DataType::FP8E5M2}) Add<CastKernelB200>(t, "Cast", "b200.cast");
-    for (DataType t : {DataType::FP32, DataType::BF16}) Add<QwenRmsNormKernelB200>(t, "QwenRmsNorm", "b200.qwen_rms_norm");
+    AddCandidate<Fp8LinearKernel<DataType::FP8E4M3, operators::FcParam>>(DataType::FP8E4M3, "FC", "b200.fp8.fc");
+    AddCandidate<Fp8LinearKernel<DataType::FP8E4M3, operators::MatMulParam>>(DataType::FP8E4M3, "MatMul", "b200.fp8.matmul");
+    AddCandidate<Fp8LinearKernel<DataType::FP8E4M3, operators::GemmParam>>(DataType::FP8E4M3, "Gemm", "b200.fp8.gemm");
+    AddCandidate<Fp8LinearKernel<DataType::FP8E5M2, operators::FcParam>>(DataType::FP8E5M2, "FC", "b200.fp8.fc");
+    AddCandidate<Fp8LinearKernel<DataType::FP8E5M2, operators::MatMulParam>>(DataType::FP8E5M2, "MatMul", "b200.fp8.matmul");
+    AddCandidate<Fp8LinearKernel<DataType::FP8E5M2, operators::GemmParam>>(DataType::FP8E5M2, "Gemm", "b200.fp8.gemm");
+    AddCandidate<Int8LinearKernel<operators::FcParam>>(DataType::INT8, "FC", "b200.int8.fc");
+    AddCandidate<Int8LinearKernel<operators::MatMulParam>>(DataType::INT8, "MatMul", "b200.int8.matmul");
+    AddCandidate<Int8LinearKernel<operators::GemmParam>>(DataType::INT8, "Gemm", "b200.int8.gemm");
+    AddCandidate<Int8Conv2dKernel>(DataType::INT8, "Conv2D", "b200.int8.conv2d");
+    for (DataType t : {DataType::FP32, DataType::FP16, DataType::BF16}) AddCandidate<QuantizeLinearKernelB200>(t, "QuantizeLinear", "b200.quantize_linear");
+    AddCandidate<DequantizeLinearKernelB200>(DataType::INT8, "DequantizeLinear", "b200.dequantize_linear");
+    for (DataType t : {DataType::FP32, DataType::FP16, DataType::BF16, DataType::FP8E4M3, DataType::FP8E5M2}) AddCandidate<CastKernelB200>(t, "Cast", "b200.cast");
+    for (DataType t : {DataType::FP32, DataType::BF16}) AddCandidate<QwenRmsNormKernelB200>(t, "QwenRmsNorm", "b200.qwen_rms_norm");
     for (DataType t : {DataType::FP32, DataType::FP16, DataType::BF16}) {
-        Add<BinaryKernelB200<FTH_B200_BINARY_ADD>>(t, "Add", "b200.add");
-        Add<BinaryKernelB200<FTH_B200_BINARY_MUL>>(t, "Mul", "b200.mul");
-        Add<SiluKernelB200>(t, "SiLU", "b200.silu");
+        AddCandidate<BinaryKernelB200<FTH_B200_BINARY_ADD>>(t, "Add", "b200.add");
+        AddCandidate<BinaryKernelB200<FTH_B200_BINARY_MUL>>(t, "Mul", "b200.mul");
+        AddCandidate<SiluKernelB200>(t, "SiLU", "b200.silu");
     }
-    Add<QwenGemmArgmaxKernelB200<DataType::FP8E4M3>>(DataType::FP8E4M3, "QwenGemmArgmax", "b200.fp8.qwen_gemm_argmax");
-    Add<QwenGemmArgmaxKernelB200<DataType::FP8E5M2>>(DataType::FP8E5M2, "QwenGemmArgmax", "b200.fp8.qwen_gemm_argmax");
+    AddCandidate<QwenGemmArgmaxKernelB200<DataType::FP8E4M3>>(DataType::FP8E4M3, "QwenGemmArgmax", "b200.fp8.qwen_gemm_argmax");
+    AddCandidate<QwenGemmArgmaxKernelB200<DataType::FP8E5M2>>(DataType::FP8E5M2, "QwenGemmArgmax", "b200.fp8.qwen_gemm_argmax");
     return true;
 }
 

@@ -1,0 +1,125 @@
+// Shared by the adapter's translation units (b200_candidates.cu: the reference's own operator types; b200_fusion.cu:
+// fused operator types and the graph pass that introduces them): status mapping, probe pointers, per-kernel device
+// scratch, and readers of the reference's quantisation metadata.
+#pragma once
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstdlib>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "core/kernel.h"
+#include "fth_b200.h"
+#include "quant/quantization.h"
+#include "src/kernel/cuda/kernel_io.cuh"
+#include "src/kernel/cuda/runtime.h"
+
+namespace feather {
+namespace kernel {
+namespace b200 {
+
+constexpr int kPriority = 10;  // reference CUDA kernels register with priority 0 (legacy registerKernel)
+
+// Common base of every kernel of this backend, so that callers (and tests) can tell which candidate the
+// dispatcher finally selected.
+class B200Kernel : public KernelBase {};
+bool IsB200Kernel(const KernelBase* kernel);
+
+inline Status FromAbi(int rc, const char* what) {
+    switch (rc) {
+        case FTH_B200_OK: return Status::Ok();
+        case FTH_B200_ERR_UNSUPPORTED:
+        case FTH_B200_ERR_OVERFLOW:  // the reference candidate reports int32 overflow itself (int8.cu:101-110)
+            return Status::Error(StatusCode::kUnsupported, std::string("b200 declines ") + what);
+        default: return Status::Error(StatusCode::kInvalidArgument, std::string("b200 rejects ") + what);
+    }
+}
+
+// A fixed, suitably aligned stand-in for device pointers during capability checks (nothing is dereferenced).
+inline void* ProbePointer() { return reinterpret_cast<void*>(uintptr_t{1} << 20); }
+
+// Device scratch owned by one kernel instance (one per session node): allocated in Prepare(), never in compute().
+class DeviceScratch {
+   public:
+    DeviceScratch() = default;
+    DeviceScratch(const DeviceScratch&) = delete;
+    DeviceScratch& operator=(const DeviceScratch&) = delete;
+    ~DeviceScratch() { if (ptr_) cudaFree(ptr_); }
+    int Reserve(size_t bytes, bool zero) {
+        if (bytes <= bytes_) return 0;
+        if (ptr_) cudaFree(ptr_);
+        ptr_ = nullptr; bytes_ = 0;
+        if (cudaMalloc(&ptr_, bytes) != cudaSuccess) return -1;
+        bytes_ = bytes;
+        return zero && cudaMemsetAsync(ptr_, 0, bytes, cuda_detail::InferenceStream()) != cudaSuccess ? -1 : 0;
+    }
+    int Upload(const void* host, size_t bytes) {
+        if (Reserve(bytes, false) != 0) return -1;
+        return cudaMemcpyAsync(ptr_, host, bytes, cudaMemcpyHostToDevice, cuda_detail::InferenceStream()) == cudaSuccess &&
+                       cudaStreamSynchronize(cuda_detail::InferenceStream()) == cudaSuccess ? 0 : -1;  // host vector is temporary
+    }
+    void* get() const { return ptr_; }
+    size_t bytes() const { return bytes_; }
+   private:
+    void* ptr_{nullptr};
+    size_t bytes_{0};
+};
+
+struct Int8WeightParams {
+    std::vector<float> scales;
+    std::vector<int32_t> zero_points;
+    int32_t zp_max_abs{0};
+};
+
+// Mirrors int8_detail::BuildQuantizationView (src/kernel/common/int8_kernel_utils.h:55-84).
+inline bool ReadInt8Quantization(const Tensor* t, bool allow_per_channel, int64_t axis, int64_t channels, Int8WeightParams* out) {
+    if (!t || t->data_type() != DataType::INT8 || !t->IsInitialized()) return false;
+    const QuantizationParams& q = t->quantization();
+    if (!q.enabled || !ValidateQuantizationParams(q, t->dims().data())) return false;
+    if (q.granularity == QuantizationGranularity::kPerChannel) {
+        if (!allow_per_channel || q.axis != axis || q.scales.size() != static_cast<size_t>(channels)) return false;
+        out->scales = q.scales;
+        out->zero_points.resize(static_cast<size_t>(channels));
+        for (int64_t c = 0; c < channels; ++c) out->zero_points[static_cast<size_t>(c)] = q.zero_point_at(static_cast<size_t>(c));
+    } else if (q.granularity == QuantizationGranularity::kPerTensor) {
+        out->scales = {q.scale_at(0)};
+        out->zero_points = {q.zero_point_at(0)};
+    } else {
+        return false;
+    }
+    out->zp_max_abs = 0;
+    for (int32_t z : out->zero_points) out->zp_max_abs = std::max(out->zp_max_abs, std::abs(z));
+    return true;
+}
+
+// Largest |bias| of an INT32 bias constant that is readable on the host (the static quantiser's output), else 0.
+inline int64_t BiasMaxAbs(const Tensor* bias) {
+    int64_t worst = 0;
+    if (bias && bias->IsInitialized() && bias->data_type() == DataType::INT32) {
+        const int32_t* b = bias->data<int32_t>();
+        for (int64_t i = 0; i < bias->numel(); ++i) worst = std::max<int64_t>(worst, std::llabs(static_cast<long long>(b[i])));
+    }
+    return worst;
+}
+
+// Device views of an input and an output tensor through the session's replica cache.
+inline int AcquireIn(const Tensor* t, void** ptr) {
+    return cuda_detail::AcquireTensorDevice(t, static_cast<size_t>(t->numel()) * DataTypeBytes(t->data_type()), t->raw_data(), ptr);
+}
+inline int FinishOut(Tensor* t, size_t bytes) {
+    if (cuda_detail::DeferredHostSyncEnabled()) return 0;
+    return cuda_detail::SyncTensorToHost(t, bytes, t->raw_data());
+}
+
+template <typename K>
+void AddCandidate(DataType dtype, const char* op, const char* id) {
+    KernelDispatcher::instance().RegisterCandidate(DeviceType::CUDA, dtype, DataLayout::ND, op, id,
+                                                   [] { return std::unique_ptr<KernelBase>(new K()); }, {}, kPriority);
+}
+
+}  // namespace b200
+}  // namespace kernel
+}  // namespace feather

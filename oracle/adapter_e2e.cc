@@ -21,9 +21,13 @@
 
 #include <cuda_runtime.h>
 
+#include "core/execution_plan.h"
 #include "core/kernel.h"
+#include "core/static_graph.h"
 #include "core/tensor.h"
 #include "fth_b200.h"
+#include "pass/graph_pass.h"
+#include "quant/static_quantizer.h"
 #include "src/kernel/cuda/runtime.h"
 #include "src/operator/params.h"
 #include "util/bf16.h"
@@ -31,6 +35,8 @@
 
 namespace feather { namespace kernel { namespace b200 {
 bool RegisterB200Kernels();
+bool RegisterB200FusedOperators();
+std::unique_ptr<GraphPass> CreateB200FusionPass();
 bool IsB200Kernel(const KernelBase* kernel);
 }}}
 
@@ -228,6 +234,8 @@ static int RunCommon(DataType dtype, const char* op, Param* param) {
     k->SetParam(param);
     return k->compute();
 }
+
+static void RunPlansOnGpu();
 
 static void RunGpu() {
     int count = 0;
@@ -464,7 +472,291 @@ static void RunGpu() {
         CHECK_THAT(ok && std::memcmp(c1.out->raw_data(), c0.out->raw_data(), 4 * 8192) == 0,
                    "workspace limit 0: FP8 MatMul [4,4096]x[4096,8192] runs without allocating scratch and gives the same bytes");
     }
+    RunPlansOnGpu();
     CHECK_THAT(fth_b200_device_status() == 0, "no bounded device-side wait gave up");
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// plans: whole graphs through StaticGraph -> passes -> CompiledGraph -> ExecutionSession, as the runners do
+// ---------------------------------------------------------------------------------------------------------
+using model::ModelDesc;
+using model::NodeDesc;
+using model::ValueDesc;
+using TensorTable = std::unordered_map<std::string, std::shared_ptr<Tensor>>;
+
+static ValueDesc Value(const std::string& name, std::vector<int64_t> dims, DataType dtype, bool constant = false, float fp8_scale = 0.0f) {
+    ValueDesc v;
+    v.tensor.name = name;
+    v.tensor.dims = std::move(dims);
+    v.tensor.data_type = dtype;
+    v.constant = constant;
+    if (fp8_scale > 0.0f) { v.tensor.quantization.enabled = true; v.tensor.quantization.scale = fp8_scale; }
+    return v;
+}
+
+// The exporter's projection pattern (tools/export_qwen35_model.py:883-900) twice over one activation:
+//   h -> Cast(E5M2) -> MatMul(gate) -> Cast(BF16) -> gate_out ;  h -> Cast(E5M2) -> MatMul(up) -> Cast(BF16) -> up_out
+struct Fp8Plan {
+    ModelDesc model;
+    TensorTable weights;
+    std::shared_ptr<Tensor> input;
+};
+static Fp8Plan MakeFp8Plan() {
+    const int64_t hidden = 1024, inter = 3584;
+    const float act_scale = 1.0f / 512, w_scale = 1.0f / 1048576, out_scale = 1.0f / 512;
+    Fp8Plan p;
+    p.model.name = "b200_fp8_projections"; p.model.version = 1; p.model.graph.name = "main";
+    p.model.graph.inputs = {"h"};
+    p.model.graph.outputs = {"gate_out", "up_out"};
+    p.model.graph.values = {Value("h", {1, hidden}, DataType::BF16)};
+    std::vector<uint16_t> h(static_cast<size_t>(hidden));
+    for (auto& v : h) v = FloatToBFloat16(Uniform(-3, 3));
+    p.input = MakeTensor(DataType::BF16, {1, hidden}, h.data());
+    for (const char* name : {"gate", "up"}) {
+        const std::string n = name;
+        std::vector<uint8_t> w(static_cast<size_t>(hidden * inter));
+        for (auto& v : w) v = FloatToFp8E5M2(Uniform(-40000, 40000));
+        auto wt = MakeTensor(DataType::FP8E5M2, {hidden, inter}, w.data());
+        wt->set_quantization({true, w_scale});
+        wt->set_immutable(true);
+        p.weights[n + "_w"] = wt;
+        p.model.graph.values.push_back(Value(n + "_in8", {1, hidden}, DataType::FP8E5M2, false, act_scale));
+        p.model.graph.values.push_back(Value(n + "_w", {hidden, inter}, DataType::FP8E5M2, true, w_scale));
+        p.model.graph.values.push_back(Value(n + "_out8", {1, inter}, DataType::FP8E5M2, false, out_scale));
+        p.model.graph.values.push_back(Value(n + "_out", {1, inter}, DataType::BF16));
+        NodeDesc c0; c0.name = n + "_to_fp8"; c0.op_type = "Cast"; c0.inputs = {"h"}; c0.outputs = {n + "_in8"}; c0.attributes["to"] = int64_t{19};
+        NodeDesc mm; mm.name = n + "_matmul"; mm.op_type = "MatMul"; mm.inputs = {n + "_in8", n + "_w"}; mm.outputs = {n + "_out8"};
+        NodeDesc c1; c1.name = n + "_to_bf16"; c1.op_type = "Cast"; c1.inputs = {n + "_out8"}; c1.outputs = {n + "_out"}; c1.attributes["to"] = int64_t{16};
+        p.model.graph.nodes.push_back(c0); p.model.graph.nodes.push_back(mm); p.model.graph.nodes.push_back(c1);
+    }
+    return p;
+}
+
+// A float model quantised by the reference's own static quantiser (src/quant/static_quantizer.cc:602-806):
+//   x -> Conv2D 3x3 (64 -> 64, bias) -> ReLU -> Flatten -> Gemm (bias) -> y
+struct Int8Plan {
+    ModelDesc model;
+    TensorTable weights;
+    std::shared_ptr<Tensor> input;
+    StaticQuantizationReport report;
+    bool ok{false};
+};
+static Int8Plan MakeInt8Plan() {
+    const int64_t c = 64, h = 8, w = 32, features = c * h * w, classes = 256;
+    ModelDesc m;
+    m.name = "b200_static_int8"; m.version = 1; m.graph.name = "main";
+    m.graph.inputs = {"x"}; m.graph.outputs = {"y"};
+    m.graph.values = {Value("x", {1, c, h, w}, DataType::FP32), Value("conv_w", {c, c, 3, 3}, DataType::FP32, true),
+                      Value("conv_b", {c}, DataType::FP32, true), Value("conv_out", {1, c, h, w}, DataType::FP32),
+                      Value("relu_out", {1, c, h, w}, DataType::FP32), Value("flat", {1, features}, DataType::FP32),
+                      Value("fc_w", {features, classes}, DataType::FP32, true), Value("fc_b", {classes}, DataType::FP32, true),
+                      Value("y", {1, classes}, DataType::FP32)};
+    NodeDesc conv; conv.name = "conv"; conv.op_type = "Conv2D"; conv.inputs = {"x", "conv_w", "conv_b"}; conv.outputs = {"conv_out"};
+    conv.attributes["stride_h"] = int64_t{1}; conv.attributes["stride_w"] = int64_t{1}; conv.attributes["pad_h"] = int64_t{1};
+    conv.attributes["pad_w"] = int64_t{1}; conv.attributes["dilation_h"] = int64_t{1}; conv.attributes["dilation_w"] = int64_t{1};
+    conv.attributes["group"] = int64_t{1};
+    NodeDesc relu; relu.name = "relu"; relu.op_type = "ReLU"; relu.inputs = {"conv_out"}; relu.outputs = {"relu_out"};
+    NodeDesc flat; flat.name = "flatten"; flat.op_type = "Flatten"; flat.inputs = {"relu_out"}; flat.outputs = {"flat"}; flat.attributes["axis"] = int64_t{1};
+    NodeDesc gemm; gemm.name = "classifier"; gemm.op_type = "Gemm"; gemm.inputs = {"flat", "fc_w", "fc_b"}; gemm.outputs = {"y"};
+    m.graph.nodes = {conv, relu, flat, gemm};
+    TensorTable weights;
+    auto Fill = [](std::vector<int64_t> dims, float lo, float hi) {
+        size_t count = 1;
+        for (int64_t d : dims) count *= static_cast<size_t>(d);
+        std::vector<float> v(count);
+        for (auto& x : v) x = Uniform(lo, hi);
+        return MakeTensor(DataType::FP32, dims, v.data());
+    };
+    weights["conv_w"] = Fill({c, c, 3, 3}, -0.08f, 0.08f);
+    weights["conv_b"] = Fill({c}, -0.5f, 0.5f);
+    weights["fc_w"] = Fill({features, classes}, -0.02f, 0.02f);
+    weights["fc_b"] = Fill({classes}, -0.5f, 0.5f);
+    Int8Plan p;
+    p.input = Fill({1, c, h, w}, -2.0f, 2.0f);
+    StaticQuantizationConfig config;
+    config.strict = true; config.symmetric = true; config.per_channel_weights = true;
+    const ActivationQuantization x_q{2.0f / 127, 0}, conv_q{3.0f / 127, 0}, relu_q{2.5f / 127, 0}, y_q{6.0f / 127, 0};
+    for (const char* n : {"x"}) config.activations[n] = x_q;
+    for (const char* n : {"conv_out", "conv"}) config.activations[n] = conv_q;
+    for (const char* n : {"relu_out", "relu", "flat", "flatten"}) config.activations[n] = relu_q;
+    for (const char* n : {"y", "classifier"}) config.activations[n] = y_q;
+    p.ok = StaticQuantizeModel(m, weights, config, &p.model, &p.weights, &p.report) == 0;
+    for (auto& item : p.weights)
+        if (item.second) item.second->set_immutable(true);
+    return p;
+}
+
+// One classifier layer through the same quantiser: x [4,512] -> Gemm (bias) -> y, i.e. QuantizeLinear -> Gemm -> DequantizeLinear.
+static Int8Plan MakeInt8GemmPlan() {
+    const int64_t m_rows = 4, k = 512, n = 256;
+    ModelDesc m;
+    m.name = "b200_static_int8_gemm"; m.version = 1; m.graph.name = "main";
+    m.graph.inputs = {"x"}; m.graph.outputs = {"y"};
+    m.graph.values = {Value("x", {m_rows, k}, DataType::FP32), Value("fc_w", {k, n}, DataType::FP32, true), Value("fc_b", {n}, DataType::FP32, true),
+                      Value("y", {m_rows, n}, DataType::FP32)};
+    NodeDesc gemm; gemm.name = "classifier"; gemm.op_type = "Gemm"; gemm.inputs = {"x", "fc_w", "fc_b"}; gemm.outputs = {"y"};
+    m.graph.nodes = {gemm};
+    auto Fill = [](std::vector<int64_t> dims, float lo, float hi) {
+        size_t count = 1;
+        for (int64_t d : dims) count *= static_cast<size_t>(d);
+        std::vector<float> v(count);
+        for (auto& x : v) x = Uniform(lo, hi);
+        return MakeTensor(DataType::FP32, dims, v.data());
+    };
+    TensorTable weights;
+    weights["fc_w"] = Fill({k, n}, -0.05f, 0.05f);
+    weights["fc_b"] = Fill({n}, -0.5f, 0.5f);
+    Int8Plan p;
+    p.input = Fill({m_rows, k}, -2.0f, 2.0f);
+    StaticQuantizationConfig config;
+    config.strict = true; config.symmetric = true; config.per_channel_weights = true;
+    config.activations["x"] = ActivationQuantization{2.0f / 127, 0};
+    for (const char* name : {"y", "classifier"}) config.activations[name] = ActivationQuantization{2.5f / 127, 0};
+    p.ok = StaticQuantizeModel(m, weights, config, &p.model, &p.weights, &p.report) == 0;
+    for (auto& item : p.weights)
+        if (item.second) item.second->set_immutable(true);
+    return p;
+}
+
+struct PlanRun {
+    bool ok{false};
+    std::string error;
+    std::vector<std::string> op_types;                  // live nodes after the passes, in order
+    std::unordered_map<std::string, std::vector<uint8_t>> outputs;
+    int b200_kernels{0}, kernels{0};
+};
+
+// device COMMON: the reference's canonical kernels.  device CUDA: kRequireRequested, the default pass pipeline plus
+// (with_fusion) this backend's pass; `execute` false stops after the passes (host only).
+static PlanRun RunPlan(const ModelDesc& model, const TensorTable& weights, const std::string& input_name, const std::shared_ptr<Tensor>& input,
+                       DeviceType device, bool with_fusion, bool execute) {
+    PlanRun r;
+    StaticGraph graph;
+    graph.SetKernelDevice(device);
+    if (device == DeviceType::CUDA) graph.SetFallbackPolicy(KernelFallbackPolicy::kRequireRequested);
+    auto passes = CreateDefaultPassManager();
+    if (with_fusion) passes->AddPass(feather::kernel::b200::CreateB200FusionPass());
+    graph.SetPassManager(passes);
+    if (graph.SetModel(model) != 0 || graph.SetTensor(input_name, input) != 0) { r.error = "SetModel / SetTensor"; return r; }
+    for (const auto& item : weights)
+        if (graph.SetTensor(item.first, item.second) != 0) { r.error = "SetTensor " + item.first; return r; }
+    Status st = graph.BuildStatus();
+    if (!st.ok()) { r.error = "build: " + st.message(); return r; }
+    st = graph.ApplyPassesStatus();
+    if (!st.ok()) { r.error = "passes: " + st.message(); return r; }
+    for (const auto& node : graph.nodes())
+        if (!node.removed) r.op_types.push_back(node.op_type);
+    if (!execute) { r.ok = true; return r; }
+    std::shared_ptr<const CompiledGraph> compiled;
+    st = CompiledGraph::Compile(graph, &compiled);
+    if (!st.ok()) { r.error = "compile: " + st.message(); return r; }
+    std::unique_ptr<ExecutionSession> session;
+    st = compiled->CreateSession(&session);
+    if (!st.ok()) { r.error = "session: " + st.message(); return r; }
+    for (int run = 0; run < 2; ++run) {  // the second run reuses resident weights and prepared kernels
+        st = session->BindInput(input_name, input);
+        if (st.ok()) st = session->Run();
+        if (!st.ok()) { r.error = "run: " + st.message(); return r; }
+    }
+    for (const auto& name : model.graph.outputs) {
+        std::shared_ptr<Tensor> out;
+        st = session->ReadOutput(name, &out);
+        if (!st.ok() || !out) { r.error = "read " + name + ": " + st.message(); return r; }
+        const size_t bytes = static_cast<size_t>(out->numel()) * Bytes(out->data_type());
+        const uint8_t* p = static_cast<const uint8_t*>(out->raw_data());
+        r.outputs[name] = std::vector<uint8_t>(p, p + bytes);
+    }
+    r.ok = true;
+    return r;
+}
+
+static int Count(const std::vector<std::string>& ops, const char* type) {
+    int n = 0;
+    for (const auto& o : ops) n += o == type;
+    return n;
+}
+static std::string Join(const std::vector<std::string>& ops) {
+    std::string s;
+    for (const auto& o : ops) s += (s.empty() ? "" : " ") + o;
+    return s;
+}
+
+// host only: the pass rewrites the chains (and leaves alone what the backend would decline)
+static void RunPlanRewrite() {
+    feather::kernel::b200::RegisterB200Kernels();
+    CHECK_THAT(feather::kernel::b200::RegisterB200FusedOperators(), "RegisterB200FusedOperators()");
+    {
+        Fp8Plan p = MakeFp8Plan();
+        PlanRun plain = RunPlan(p.model, p.weights, "h", p.input, DeviceType::CUDA, false, false);
+        PlanRun fused = RunPlan(p.model, p.weights, "h", p.input, DeviceType::CUDA, true, false);
+        std::printf("      FP8 plan: %s  ->  %s  %s\n", Join(plain.op_types).c_str(), Join(fused.op_types).c_str(), fused.error.c_str());
+        CHECK_THAT(plain.ok && plain.op_types.size() == 6 && fused.ok && fused.op_types.size() == 2 && Count(fused.op_types, "FusedCastMatMulCast") == 2,
+                   "pass: two Cast -> MatMul -> Cast projections of one activation become two FusedCastMatMulCast nodes (6 nodes -> 2)");
+    }
+    {
+        Int8Plan p = MakeInt8Plan();
+        CHECK_THAT(p.ok && p.report.quantized_nodes.size() == 4, "the reference's StaticQuantizeModel quantises Conv2D / ReLU / Flatten / Gemm");
+        PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, false);
+        PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, false);
+        std::printf("      INT8 plan: %s  ->  %s  %s%s\n", Join(plain.op_types).c_str(), Join(fused.op_types).c_str(), plain.error.c_str(), fused.error.c_str());
+        CHECK_THAT(plain.ok && fused.ok && Count(fused.op_types, "Conv2DRelu") == 1 && Count(fused.op_types, "ReLU") == 0 &&
+                       fused.op_types.size() < plain.op_types.size(),
+                   "pass: the quantiser's Conv2D -> ReLU pair becomes one Conv2DRelu node; the plan builds for CUDA under kRequireRequested");
+    }
+    {
+        Int8Plan p = MakeInt8GemmPlan();
+        PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, false);
+        PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, false);
+        std::printf("      INT8 Gemm plan: %s  ->  %s  %s%s\n", Join(plain.op_types).c_str(), Join(fused.op_types).c_str(), plain.error.c_str(), fused.error.c_str());
+        CHECK_THAT(p.ok && plain.ok && plain.op_types.size() == 3 && fused.ok && fused.op_types.size() == 1 && Count(fused.op_types, "FusedQLinearDQ") == 1,
+                   "pass: the quantiser's QuantizeLinear -> Gemm -> DequantizeLinear becomes one FusedQLinearDQ node");
+    }
+}
+
+// GPU: the same plans executed; outputs against the COMMON run of the unfused plan
+static void RunPlansOnGpu() {
+    feather::kernel::b200::RegisterB200FusedOperators();
+    {
+        Fp8Plan p = MakeFp8Plan();
+        PlanRun ref = RunPlan(p.model, p.weights, "h", p.input, DeviceType::COMMON, false, true);
+        PlanRun plain = RunPlan(p.model, p.weights, "h", p.input, DeviceType::CUDA, false, true);
+        PlanRun fused = RunPlan(p.model, p.weights, "h", p.input, DeviceType::CUDA, true, true);
+        bool ok = ref.ok && plain.ok && fused.ok;
+        int worst = -1;
+        if (ok) {
+            worst = 0;
+            for (const char* name : {"gate_out", "up_out"}) {
+                ok = ok && fused.outputs[name] == plain.outputs[name];  // the fused node returns the bytes of the three-node chain
+                const uint16_t* a = reinterpret_cast<const uint16_t*>(fused.outputs[name].data());
+                const uint16_t* b = reinterpret_cast<const uint16_t*>(ref.outputs[name].data());
+                for (size_t i = 0; i < fused.outputs[name].size() / 2; ++i) {
+                    // both are decoded E5M2 codes times a power of two: compare as codes
+                    const int ca = CodeIndex(FloatToFp8E5M2(BFloat16ToFloat(a[i]) * 512.0f)), cb = CodeIndex(FloatToFp8E5M2(BFloat16ToFloat(b[i]) * 512.0f));
+                    worst = std::max(worst, std::abs(ca - cb));
+                }
+            }
+        }
+        std::printf("      FP8 plan on CUDA: %s%s%s; max code distance from the COMMON plan %d\n", ref.error.c_str(), plain.error.c_str(), fused.error.c_str(), worst);
+        CHECK_THAT(ok && worst >= 0 && worst <= 1, "FP8 projection plan: fused plan == unfused CUDA plan byte for byte, both within one code of the COMMON plan");
+    }
+    {
+        Int8Plan p = MakeInt8Plan();
+        PlanRun ref = RunPlan(p.model, p.weights, "x", p.input, DeviceType::COMMON, false, true);
+        PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, true);
+        PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, true);
+        const bool ok = p.ok && ref.ok && plain.ok && fused.ok;
+        std::printf("      INT8 plan on CUDA: %s%s%s\n", ref.error.c_str(), plain.error.c_str(), fused.error.c_str());
+        CHECK_THAT(ok && plain.outputs["y"] == ref.outputs["y"], "statically quantised plan (the reference's own quantiser) on CUDA under kRequireRequested: identical to COMMON");
+        CHECK_THAT(ok && fused.outputs["y"] == ref.outputs["y"], "the same plan with Conv2D -> ReLU fused by the pass: identical to COMMON");
+    }
+    {
+        Int8Plan p = MakeInt8GemmPlan();
+        PlanRun ref = RunPlan(p.model, p.weights, "x", p.input, DeviceType::COMMON, false, true);
+        PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, true);
+        std::printf("      INT8 Gemm plan on CUDA: %s%s\n", ref.error.c_str(), fused.error.c_str());
+        CHECK_THAT(p.ok && ref.ok && fused.ok && fused.outputs["y"] == ref.outputs["y"],
+                   "QuantizeLinear -> Gemm -> DequantizeLinear as one FusedQLinearDQ node on CUDA: identical to the three COMMON nodes");
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -507,7 +799,7 @@ static void RunTime() {
 
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "select";
-    if (mode == "select") RunSelect();
+    if (mode == "select") { RunSelect(); RunPlanRewrite(); }
     else if (mode == "run") RunGpu();
     else if (mode == "time") RunTime();
     else { std::fprintf(stderr, "usage: adapter_e2e select|run|time\n"); return 2; }

@@ -5,7 +5,10 @@ from the unmodified reference sources + infer_b200/adapter/b200_candidates.cu + 
   declined request moves on to the reference's CUDA kernel (never to a CPU kernel), and QuantizeLinear /
   DequantizeLinear gain the CUDA candidates a statically quantised plan needs.
 * GPU: the candidates run through the reference's own CUDA runtime (replica cache, inference stream, deferred
-  host sync) and are compared with the reference's COMMON kernels on the same tensors."""
+  host sync) and are compared with the reference's COMMON kernels on the same tensors; whole plans — the exporter's
+  FP8 projection pattern and a model quantised by the reference's own StaticQuantizeModel — are built for CUDA under
+  kRequireRequested, rewritten by this backend's GraphPass (infer_b200/adapter/b200_fusion.cu), run in an
+  ExecutionSession and compared with the COMMON run of the unfused plan."""
 import os
 import subprocess
 
@@ -27,7 +30,9 @@ def _run(mode):
 @needs_binary
 def test_selection_contract_inside_reference_dispatcher():
     out = _run("select")
-    assert out.count("ok  ") >= 10
+    assert out.count("ok  ") >= 16
+    # the graph pass, on the host: chains of a plan become fused nodes (and the plan still builds under kRequireRequested)
+    assert "FusedCastMatMulCast FusedCastMatMulCast" in out and "Conv2DRelu" in out and "->  FusedQLinearDQ" in out
 
 
 @needs_binary
@@ -35,7 +40,7 @@ def test_selection_contract_inside_reference_dispatcher():
 def test_candidates_run_through_reference_cuda_runtime():
     out = _run("run")
     assert "skip" not in out
-    assert out.count("ok  ") >= 9
+    assert out.count("ok  ") >= 13
 
 
 @needs_binary
