@@ -281,7 +281,8 @@ int fth_b200_cast(int32_t in_dtype, const void* x, float in_scale, int32_t out_d
  * kernel (src/kernel/common/qwen_rms_norm.cc:71-95): FP32 math,
  *   out[r,c] = x[r,c] * (1 / sqrt(sum_c x[r,c]^2 / hidden + epsilon)) * (weight[c] + weight_offset),
  * x / weight / out each FP32 or BF16.  The sum of squares is reduced in parallel, so an output may differ from the
- * Common kernel's by one code of the output type (its x86 and CUDA kernels reduce in other orders as well).
+ * Common kernel's (which adds the squares one after another) by one BF16 code, or by a few parts in 10^6 for FP32
+ * output (its x86 and CUDA kernels reduce in other orders as well and sit as far from it).
  * Add / Mul replace the BF16 / FP16 / FP32 kernels of src/kernel/cuda/add.cu and mul.cu (contract
  * src/kernel/common/add.cc:80-109): out[i] = lhs[i] op rhs[i % rhs_count], one rounding; rhs_count = 0 means
  * same shape, else it is the length of the rhs row broadcast over lhs (count % rhs_count == 0).  Bit-exact.

@@ -208,6 +208,11 @@ class Int8LinearKernel final : public B200Kernel {
         has_zps_ = wq.zp_max_abs != 0;
         if (has_zps_ && zps_.Upload(wq.zero_points.data(), wq.zero_points.size() * sizeof(int32_t)) != 0) return -1;
         bias_max_abs_ = BiasMaxAbs(v.bias);  // bias is an immutable INT32 constant produced by the static quantiser
+        // An immutable weight keeps its quantisation parameters: compute() need not validate and copy the per-channel
+        // vectors again (28672 entries at the largest projections: more host time per call than the kernel takes).
+        weight_params_cached_ = v.w->is_immutable();
+        cached_w_params_ = static_cast<int64_t>(wq.scales.size());
+        cached_zp_max_abs_ = wq.zp_max_abs;
         d.a = kProbe; d.w = static_cast<const int8_t*>(kProbe); d.out = kProbe; d.w_scales = static_cast<const float*>(kProbe);
         weights_resident_ = false;
         if (!WithinBudget(d)) return 0;  // no scratch: the library picks kernels that need none
@@ -219,7 +224,7 @@ class Int8LinearKernel final : public B200Kernel {
         fth_b200_int8_linear_desc d;
         Int8WeightParams wq;
         LinearView v;
-        if (!Describe(&d, &wq, &v) || scales_.get() == nullptr) return -1;
+        if (!Describe(&d, &wq, &v, weight_params_cached_) || scales_.get() == nullptr) return -1;
         cuda_detail::DeviceBuffer<int8_t> a, w, out;
         cuda_detail::DeviceBuffer<int32_t> bias;
         if (cuda_detail::CopyTensorToDevice(v.a, &a) != 0 || cuda_detail::CopyTensorToDevice(v.w, &w) != 0 ||
@@ -243,21 +248,26 @@ class Int8LinearKernel final : public B200Kernel {
         return fth_b200_int8_linear_workspace_bytes(&d) <= workspace_limit_;
     }
 
-    bool Describe(fth_b200_int8_linear_desc* d, Int8WeightParams* wq, LinearView* view = nullptr) const {
+    bool Describe(fth_b200_int8_linear_desc* d, Int8WeightParams* wq, LinearView* view = nullptr, bool weight_cached = false) const {
         LinearView v;
         if (!View(ParamAs<Param>(), &v)) return false;
         int64_t m = 0, k = 0, n = 0;
         if (!LinearShape(v, &m, &k, &n)) return false;
         Int8WeightParams aq, oq;
-        if (!ReadInt8Quantization(v.a, false, -1, 1, &aq) || !ReadInt8Quantization(v.w, true, v.trans_b ? 0 : 1, n, wq) ||
-            !ReadInt8Quantization(v.out, false, -1, 1, &oq)) return false;
+        if (!ReadInt8Quantization(v.a, false, -1, 1, &aq) || !ReadInt8Quantization(v.out, false, -1, 1, &oq)) return false;
+        if (weight_cached && (cached_w_params_ == 1 || cached_w_params_ == n)) {
+            wq->scales.assign(static_cast<size_t>(cached_w_params_ == 1 ? 1 : 0), 0.0f);  // only the count and the bound are used
+            wq->zp_max_abs = cached_zp_max_abs_;
+        } else if (!ReadInt8Quantization(v.w, true, v.trans_b ? 0 : 1, n, wq)) {
+            return false;
+        }
         const int bias_mode = BiasMode(v.bias, m, n);
         if (bias_mode < 0 || (v.bias && v.bias->data_type() != DataType::INT32)) return false;
         *d = fth_b200_int8_linear_desc{};
         d->op = v.op; d->m = m; d->k = k; d->n = n; d->trans_b = v.trans_b ? 1 : 0;
         d->bias_mode = bias_mode;
         d->a_scale = aq.scales[0]; d->a_zp = aq.zero_points[0];
-        d->w_params = static_cast<int64_t>(wq->scales.size());
+        d->w_params = weight_cached ? cached_w_params_ : static_cast<int64_t>(wq->scales.size());
         d->w_zp_max_abs = wq->zp_max_abs;
         d->out_scale = oq.scales[0]; d->out_zp = oq.zero_points[0];
         d->alpha = v.alpha; d->beta = v.beta;
@@ -269,6 +279,9 @@ class Int8LinearKernel final : public B200Kernel {
     DeviceScratch scales_, zps_, workspace_;
     bool weights_resident_{false};
     bool has_zps_{false};
+    bool weight_params_cached_{false};
+    int64_t cached_w_params_{0};
+    int32_t cached_zp_max_abs_{0};
     int64_t bias_max_abs_{0};
     size_t workspace_limit_;
 };

@@ -11,8 +11,9 @@
 //                out = x * (1 / sqrt(sum(x^2) / hidden + eps)) * (weight + weight_offset), rounded after each
 //                multiply; BF16 output rounds to nearest even and quiets NaNs (include/util/bf16.h:35-46).
 //                The reference adds the squares one after another in FP32; here a row is summed by 128 threads and a
-//                tree, so the sum (and with it every output of the row) can differ in the last FP32 bit — at most one
-//                BF16 code after rounding.  The reference's own x86 and CUDA kernels reduce in other orders too.
+//                tree, so the sum (and with it every output of the row) differs by the rounding error of the sequential
+//                sum, a few parts in 10^6 at 1024 terms: at most one BF16 code after rounding, up to a few tens of FP32
+//                steps for FP32 output.  The reference's own x86 and CUDA kernels reduce in other orders too.
 //   Add / Mul    src/kernel/common/add.cc:80-109, mul.cc: float(lhs) op float(rhs), one rounding to the output
 //                type.  Bit-exact.  rhs may be one row that is broadcast over the rows of lhs.
 //   SiLU         src/kernel/common/silu.cc:38-55: x / (1 + exp(-x)) in FP32 with the C library's expf.  Here

@@ -60,6 +60,7 @@ static size_t Bytes(DataType t) {
     switch (t) {
         case DataType::FP32: case DataType::INT32: return 4;
         case DataType::FP16: case DataType::BF16: return 2;
+        case DataType::INT64: return 8;
         default: return 1;
     }
 }
@@ -752,8 +753,24 @@ static void RunPlansOnGpu() {
     {
         Int8Plan p = MakeInt8GemmPlan();
         PlanRun ref = RunPlan(p.model, p.weights, "x", p.input, DeviceType::COMMON, false, true);
+        PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, true);
         PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, true);
-        std::printf("      INT8 Gemm plan on CUDA: %s%s\n", ref.error.c_str(), fused.error.c_str());
+        std::printf("      INT8 Gemm plan on CUDA: %s%s%s\n", ref.error.c_str(), plain.error.c_str(), fused.error.c_str());
+        if (ref.ok && plain.ok && fused.ok) {
+            const float* r = reinterpret_cast<const float*>(ref.outputs["y"].data());
+            const float* u = reinterpret_cast<const float*>(plain.outputs["y"].data());
+            const float* f = reinterpret_cast<const float*>(fused.outputs["y"].data());
+            const size_t count = ref.outputs["y"].size() / 4;
+            int du = 0, df = 0, shown = 0;
+            for (size_t i = 0; i < count; ++i) {
+                du += u[i] != r[i];
+                if (f[i] != r[i]) {
+                    ++df;
+                    if (shown++ < 6) std::printf("        y[%zu]: COMMON %.6f, unfused CUDA %.6f, fused %.6f\n", i, r[i], u[i], f[i]);
+                }
+            }
+            std::printf("      of %zu outputs: unfused CUDA plan differs in %d, fused plan in %d\n", count, du, df);
+        }
         CHECK_THAT(p.ok && ref.ok && fused.ok && fused.outputs["y"] == ref.outputs["y"],
                    "QuantizeLinear -> Gemm -> DequantizeLinear as one FusedQLinearDQ node on CUDA: identical to the three COMMON nodes");
     }

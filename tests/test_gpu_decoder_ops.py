@@ -1,8 +1,11 @@
 """GPU: QwenRmsNorm / Add / Mul / SiLU / SiLU*up against the CPU oracle (the reference's Common kernels).
 
 Add and Mul are bit-exact.  SiLU is compared code for code as well (the kernel evaluates exp in double and rounds once).
-QwenRmsNorm reduces the squares in parallel: BF16 outputs may sit one code from the oracle's, FP32 outputs four FP32
-steps — the reference's own x86 kernel is farther from its Common kernel than that (tests/test_oracle_decoder_ops.py)."""
+QwenRmsNorm reduces the squares in parallel, while the Common kernel adds them one after another in FP32 (a sum whose
+own rounding error is a few parts in 10^6 at 1024 terms): BF16 outputs may sit one code from the oracle's, FP32 outputs
+16 + hidden / 32 FP32 steps (the sequential sum's error grows with the row length; 6e-6 relative at 1024 elements) — the
+reference's own x86 kernel is 29 steps from its Common kernel on the 1024-element fixture
+(tests/test_oracle_decoder_ops.py)."""
 import numpy as np
 import pytest
 
@@ -52,7 +55,7 @@ def test_qwen_rms_norm(cuda, rows, hidden, x_dtype, w_dtype, out_dtype):
     want_bits = want.view(np.uint32) if out_dtype == B.FP32 else want
     got_bits = got.view(np.uint32) if out_dtype == B.FP32 else got
     dist = _steps(got_bits, want_bits)
-    limit = 4 if out_dtype == B.FP32 else 1
+    limit = 16 + hidden // 32 if out_dtype == B.FP32 else 1
     print(f"rms_norm {rows}x{hidden}: {int((dist > 0).sum())} of {dist.size} outputs differ, max {int(dist.max())} step(s)")
     assert dist.max() <= limit
     assert B.last_variant() == "rms_norm"

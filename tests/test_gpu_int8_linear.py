@@ -102,6 +102,24 @@ def test_fused_quantize_and_dequantize(cuda):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("m", [1, 4, 16, 64, 300])
+@pytest.mark.parametrize("op,bias_mode", [(B.OP_MATMUL, 0), (B.OP_GEMM, 1), (B.OP_FC, 1)])
+def test_fused_quantize_and_dequantize_symmetric(cuda, m, op, bias_mode):
+    """The chain a statically quantised plan holds around a classifier layer — QuantizeLinear -> FC / MatMul / Gemm ->
+    DequantizeLinear with all zero points 0 — as one call on the kernel family AUTO picks (tensor cores), against the
+    three reference nodes."""
+    rng = np.random.default_rng(80 + m)
+    case = util.make_int8_linear(m, 512, 256, seed=8 + m, bias_mode=bias_mode)
+    x = case["a"].astype(np.float32) * np.float32(case["sa"]) + rng.uniform(-0.49, 0.49, case["a"].shape).astype(np.float32) * np.float32(case["sa"])
+    q = O.quantize_linear(O.FP32, x, [case["sa"]], [0])
+    case_q = dict(case, a=q)
+    mid = oracle_int8(op, case_q)
+    want = O.dequantize_linear(mid, [case["so"]], [0], O.FP32)
+    got = run_int8_linear(cuda, op, case_q, a_dtype=B.FP32, out_dtype=B.FP32, a_raw=x)
+    bad = int((got.view(np.uint32) != want.view(np.uint32)).sum())
+    assert bad == 0, f"{bad} of {want.size} outputs differ on kernel {B.last_variant()}"
+
+
 def test_overflow_and_rejections(cuda):
     import ctypes as C
     from tests.gpu_helpers import dev
