@@ -243,11 +243,21 @@ typedef struct {
     size_t workspace_bytes;
     int32_t weights_packed; /* 1: workspace already holds the packed weights of a previous call (same w) */
     int32_t variant;
+    /* Optional: the weight in the implicit-GEMM layout, made once per weight by fth_b200_int8_conv2d_pack_weights
+     * (device memory the caller owns and may share between sessions and plans that use the same weight — the
+     * counterpart of the reference's per-weight cache of packed x86 layouts, src/kernel/x86/prepared_weight_cache.h).
+     * When non-null the call never repacks, `weights_packed` is ignored and `workspace` only holds the channels-last
+     * copy of the input. */
+    const int8_t* packed_w;
 } fth_b200_int8_conv2d_desc;
 
 int fth_b200_int8_conv2d(const fth_b200_int8_conv2d_desc* desc, fth_b200_stream_t stream);
 int fth_b200_int8_conv2d_supported(const fth_b200_int8_conv2d_desc* desc);
 size_t fth_b200_int8_conv2d_workspace_bytes(const fth_b200_int8_conv2d_desc* desc);
+/* Size of, and the pass that fills, the packed copy of desc->w for desc->packed_w ([OC][KH][KW][IC], 256-byte aligned
+ * destination).  0 / FTH_B200_ERR_UNSUPPORTED when the implicit-GEMM kernel does not take the geometry (nothing to pack). */
+size_t fth_b200_int8_conv2d_packed_weight_bytes(const fth_b200_int8_conv2d_desc* desc);
+int fth_b200_int8_conv2d_pack_weights(const fth_b200_int8_conv2d_desc* desc, void* packed, fth_b200_stream_t stream);
 
 /* Builds the 256-entry INT8 ReLU table on the host (src/kernel/common/int8_standard.cc:114-128). */
 int fth_b200_int8_relu_table(float in_scale, int32_t in_zp, float out_scale, int32_t out_zp, int8_t* lut256);

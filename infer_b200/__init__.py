@@ -26,6 +26,7 @@ EXPORTS = [
     "fth_b200_device_status", "fth_b200_fp8_linear_noalloc", "fth_b200_noalloc_scratch_bytes",
     "fth_b200_int8_linear", "fth_b200_int8_linear_supported", "fth_b200_int8_linear_workspace_bytes",
     "fth_b200_int8_conv2d", "fth_b200_int8_conv2d_supported", "fth_b200_int8_conv2d_workspace_bytes",
+    "fth_b200_int8_conv2d_packed_weight_bytes", "fth_b200_int8_conv2d_pack_weights",
     "fth_b200_int8_relu_table", "fth_b200_int8_lookup",
     "fth_b200_quantize_linear", "fth_b200_dequantize_linear", "fth_b200_cast",
     "fth_b200_plan_create_fp8_linear", "fth_b200_plan_create_int8_linear", "fth_b200_plan_create_int8_conv2d",
@@ -73,7 +74,7 @@ class Int8Conv2dDesc(C.Structure):
         ("x_scale", C.c_float), ("x_zp", C.c_int32), ("w_scales", C.c_void_p), ("w_zps", C.c_void_p),
         ("w_params", C.c_int64), ("w_zp_max_abs", C.c_int32), ("out_scale", C.c_float), ("out_zp", C.c_int32),
         ("relu_lut", C.c_void_p), ("bias_max_abs", C.c_int64), ("workspace", C.c_void_p),
-        ("workspace_bytes", C.c_size_t), ("weights_packed", C.c_int32), ("variant", C.c_int32),
+        ("workspace_bytes", C.c_size_t), ("weights_packed", C.c_int32), ("variant", C.c_int32), ("packed_w", C.c_void_p),
     ]
 
 
@@ -92,6 +93,7 @@ def lib():
         handle.fth_b200_last_variant.restype = C.c_char_p
         handle.fth_b200_launch_count.restype = C.c_int64
         handle.fth_b200_int8_conv2d_workspace_bytes.restype = C.c_size_t
+        handle.fth_b200_int8_conv2d_packed_weight_bytes.restype = C.c_size_t
         handle.fth_b200_fp8_linear_workspace_bytes.restype = C.c_size_t
         handle.fth_b200_int8_linear_workspace_bytes.restype = C.c_size_t
         handle.fth_b200_noalloc_scratch_bytes.restype = C.c_size_t

@@ -25,6 +25,7 @@ namespace kernel {
 namespace b200 {
 
 bool IsB200Kernel(const KernelBase* kernel) { return dynamic_cast<const B200Kernel*>(kernel) != nullptr; }
+size_t PackedConvWeightEntries() { return PackedConvWeightCache::LiveEntries(); }
 
 namespace {
 
@@ -319,6 +320,15 @@ class Int8Conv2dKernel final : public B200Kernel {
         d.x = static_cast<const int8_t*>(kProbe); d.w = d.x; d.out = static_cast<int8_t*>(kProbe);
         d.w_scales = static_cast<const float*>(kProbe);
         packed_ = false;
+        // an immutable weight is packed once per process and device, not once per session
+        shared_packed_.reset();
+        void* w_device = nullptr;
+        if (p->w->is_immutable() && AcquireIn(p->w.get(), &w_device) == 0) {
+            fth_b200_int8_conv2d_desc pack = d;
+            pack.w = static_cast<const int8_t*>(w_device);
+            shared_packed_ = PackedConvWeightCache::Acquire(p->w.get(), pack);
+        }
+        if (shared_packed_) d.packed_w = static_cast<const int8_t*>(shared_packed_->get());
         return workspace_.Reserve(fth_b200_int8_conv2d_workspace_bytes(&d), true);
     }
 
@@ -339,8 +349,9 @@ class Int8Conv2dKernel final : public B200Kernel {
         d.bias_max_abs = bias_max_abs_;
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
         d.weights_packed = packed_ ? 1 : 0;
+        d.packed_w = shared_packed_ ? static_cast<const int8_t*>(shared_packed_->get()) : nullptr;
         if (fth_b200_int8_conv2d(&d, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
-        packed_ = p->w->is_immutable();  // an immutable weight is repacked once per session
+        packed_ = p->w->is_immutable();  // without a shared packed copy: repacked once per session
         return cuda_detail::CopyDeviceToTensor(&out, p->out.get());
     }
 
@@ -368,6 +379,7 @@ class Int8Conv2dKernel final : public B200Kernel {
     }
 
     DeviceScratch scales_, zps_, workspace_;
+    std::shared_ptr<DeviceScratch> shared_packed_;
     bool has_zps_{false}, packed_{false};
     int64_t bias_max_abs_{0};
 };

@@ -8,6 +8,8 @@
 #include <cstdint>
 #include <cstdlib>
 #include <memory>
+#include <mutex>
+#include <utility>
 #include <string>
 #include <vector>
 
@@ -113,6 +115,57 @@ inline int FinishOut(Tensor* t, size_t bytes) {
     if (cuda_detail::DeferredHostSyncEnabled()) return 0;
     return cuda_detail::SyncTensorToHost(t, bytes, t->raw_data());
 }
+
+// Packed implicit-GEMM conv weights, one copy per immutable weight and device, shared by every session and plan that
+// uses the weight (the reference keeps packed x86 layouts per weight the same way, src/kernel/x86/prepared_weight_cache.h;
+// before this cache every session packed its own copy into its per-node workspace).  Entries are dropped when the last
+// kernel that holds one goes away.
+class PackedConvWeightCache {
+   public:
+    // `desc` describes the conv with desc->w already pointing at the weight ON THE DEVICE; packs on the inference stream
+    // and waits, so that sessions on other streams may read the result.  Returns null when the geometry has no packed form.
+    static std::shared_ptr<DeviceScratch> Acquire(const Tensor* weight, const fth_b200_int8_conv2d_desc& desc) {
+        const size_t bytes = fth_b200_int8_conv2d_packed_weight_bytes(&desc);
+        if (bytes == 0 || weight == nullptr || !weight->is_immutable()) return nullptr;
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
+        const Key key{weight->raw_data(), weight->mutation_version(), device, desc.oc, desc.ic, desc.kh, desc.kw};
+        std::lock_guard<std::mutex> lock(Mutex());
+        auto& table = Table();
+        for (auto it = table.begin(); it != table.end();) {
+            if (it->second.expired()) { it = table.erase(it); continue; }
+            if (it->first == key) {
+                if (auto hit = it->second.lock()) return hit;
+            }
+            ++it;
+        }
+        auto packed = std::make_shared<DeviceScratch>();
+        if (packed->Reserve(bytes, false) != 0) return nullptr;
+        if (fth_b200_int8_conv2d_pack_weights(&desc, packed->get(), cuda_detail::InferenceStream()) != FTH_B200_OK) return nullptr;
+        if (cudaStreamSynchronize(cuda_detail::InferenceStream()) != cudaSuccess) return nullptr;
+        table.emplace_back(key, packed);
+        return packed;
+    }
+    static size_t LiveEntries() {
+        std::lock_guard<std::mutex> lock(Mutex());
+        size_t n = 0;
+        for (const auto& e : Table()) n += !e.second.expired();
+        return n;
+    }
+
+   private:
+    struct Key {
+        const void* host; uint64_t version; int device; int64_t oc, ic, kh, kw;
+        bool operator==(const Key& o) const {
+            return host == o.host && version == o.version && device == o.device && oc == o.oc && ic == o.ic && kh == o.kh && kw == o.kw;
+        }
+    };
+    static std::mutex& Mutex() { static std::mutex m; return m; }
+    static std::vector<std::pair<Key, std::weak_ptr<DeviceScratch>>>& Table() {
+        static std::vector<std::pair<Key, std::weak_ptr<DeviceScratch>>> t;
+        return t;
+    }
+};
 
 template <typename K>
 void AddCandidate(DataType dtype, const char* op, const char* id) {

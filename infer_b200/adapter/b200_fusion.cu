@@ -15,8 +15,7 @@
 // (include/pass/graph_pass.h:29-36) that matches the chains and rewrites them with StaticGraph::ReplaceNodeDesc /
 // RemoveNode (include/core/static_graph.h:72-87), the way src/pass/qwen_gemm_argmax_fusion_pass.cc:89-180 rewrites
 // the FP8 lm-head.  A chain is rewritten only when the C ABI says it will run the fused descriptor; anything else is
-// left as it was.  The pass also performs the FP8 `Gemm -> Cast(to=16)` lm-head rewrite to QwenGemmArgmax that the
-// reference skips on CUDA for want of an FP8 kernel (qwen_gemm_argmax_fusion_pass.cc:160-164).
+// left as it was.
 #include <cstring>
 #include <unordered_map>
 
@@ -322,6 +321,14 @@ class Conv2DReluKernel final : public B200Kernel {
         d.x = static_cast<const int8_t*>(kProbe); d.w = d.x; d.out = static_cast<int8_t*>(kProbe);
         d.w_scales = static_cast<const float*>(kProbe);
         packed_ = false;
+        shared_packed_.reset();
+        void* w_device = nullptr;
+        if (p->conv.w->is_immutable() && AcquireIn(p->conv.w.get(), &w_device) == 0) {
+            fth_b200_int8_conv2d_desc pack = d;
+            pack.w = static_cast<const int8_t*>(w_device);
+            shared_packed_ = PackedConvWeightCache::Acquire(p->conv.w.get(), pack);
+        }
+        if (shared_packed_) d.packed_w = static_cast<const int8_t*>(shared_packed_->get());
         return workspace_.Reserve(fth_b200_int8_conv2d_workspace_bytes(&d), true);
     }
     int32_t compute() override {
@@ -342,6 +349,7 @@ class Conv2DReluKernel final : public B200Kernel {
         d.relu_lut = static_cast<const int8_t*>(lut_.get());
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
         d.weights_packed = packed_ ? 1 : 0;
+        d.packed_w = shared_packed_ ? static_cast<const int8_t*>(shared_packed_->get()) : nullptr;
         if (fth_b200_int8_conv2d(&d, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
         packed_ = p->conv.w->is_immutable();
         return FinishOut(p->conv.out.get(), out_bytes);
@@ -349,6 +357,7 @@ class Conv2DReluKernel final : public B200Kernel {
 
    private:
     DeviceScratch scales_, zps_, lut_, workspace_;
+    std::shared_ptr<DeviceScratch> shared_packed_;
     bool has_zps_{false}, packed_{false};
 };
 

@@ -92,6 +92,7 @@ int Validate(const fth_b200_int8_conv2d_desc* d, ConvArgs* c) {
     c->per_channel = d->w_params != 1; c->out_scale = d->out_scale; c->out_zp = d->out_zp;
     c->relu_lut = d->relu_lut;
     c->workspace = d->workspace; c->workspace_bytes = d->workspace_bytes; c->weights_packed = d->weights_packed;
+    c->packed_w = d->packed_w;
     return FTH_B200_OK;
 }
 
@@ -119,6 +120,20 @@ extern "C" size_t fth_b200_int8_conv2d_workspace_bytes(const fth_b200_int8_conv2
     ConvArgs c;
     if (Validate(d, &c) != FTH_B200_OK) return 0;
     return ConvTcgen05WorkspaceBytes(c);
+}
+
+extern "C" size_t fth_b200_int8_conv2d_packed_weight_bytes(const fth_b200_int8_conv2d_desc* d) {
+    ConvArgs c;
+    if (Validate(d, &c) != FTH_B200_OK) return 0;
+    return ConvPackedWeightBytes(c);
+}
+
+extern "C" int fth_b200_int8_conv2d_pack_weights(const fth_b200_int8_conv2d_desc* d, void* packed, fth_b200_stream_t stream) {
+    ClearStaleError();
+    ConvArgs c;
+    const int rc = Validate(d, &c);
+    if (rc != FTH_B200_OK) return rc;
+    return LaunchConvPackWeights(c, packed, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fth_b200_int8_conv2d(const fth_b200_int8_conv2d_desc* d, fth_b200_stream_t stream_) {

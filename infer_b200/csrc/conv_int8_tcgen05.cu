@@ -360,6 +360,7 @@ bool ConvTcgen05Supported(const ConvArgs& c) {
     if (c.ic % 64 != 0 || c.oc < 1 || c.oc > 256) return false;
     if (c.workspace == nullptr || c.workspace_bytes < ConvTcgen05WorkspaceBytes(c)) return false;
     if (reinterpret_cast<uintptr_t>(c.workspace) % 256 != 0) return false;
+    if (c.packed_w != nullptr && reinterpret_cast<uintptr_t>(c.packed_w) % 256 != 0) return false;
     const int kblocks = static_cast<int>(c.kh * c.kw * (c.ic / 64));
     if (SmemBytesFor(BlockQFor(c.oc), kblocks) > 220 * 1024) return false;
     if (c.batch > 0x7fffffff || c.ih > 0x7fffffff || c.iw > 0x7fffffff) return false;
@@ -369,17 +370,35 @@ bool ConvTcgen05Supported(const ConvArgs& c) {
 size_t ConvTcgen05WorkspaceBytes(const ConvArgs& c) {
     if (c.stride_h != 1 || c.stride_w != 1 || c.dilation_h != 1 || c.dilation_w != 1 || c.group != 1) return 0;
     if (c.x_zp != 0 || c.w_zps != nullptr || c.ic % 64 != 0 || c.oc > 256) return 0;
-    return Align256(static_cast<size_t>(c.batch * c.ih * c.iw * c.ic)) + Align256(static_cast<size_t>(c.oc * c.kh * c.kw * c.ic));
+    const size_t nhwc = Align256(static_cast<size_t>(c.batch * c.ih * c.iw * c.ic));
+    return c.packed_w != nullptr ? nhwc : nhwc + Align256(static_cast<size_t>(c.oc * c.kh * c.kw * c.ic));
+}
+
+size_t ConvPackedWeightBytes(const ConvArgs& c) {
+    if (c.stride_h != 1 || c.stride_w != 1 || c.dilation_h != 1 || c.dilation_w != 1 || c.group != 1) return 0;
+    if (c.x_zp != 0 || c.w_zps != nullptr || c.ic % 64 != 0 || c.oc > 256) return 0;
+    return Align256(static_cast<size_t>(c.oc * c.kh * c.kw * c.ic));
+}
+
+int LaunchConvPackWeights(const ConvArgs& c, void* packed, cudaStream_t stream) {
+    if (ConvPackedWeightBytes(c) == 0) return FTH_B200_ERR_UNSUPPORTED;
+    if (packed == nullptr || reinterpret_cast<uintptr_t>(packed) % 256 != 0) return FTH_B200_ERR_INVALID;
+    const int64_t taps = c.kh * c.kw;
+    const int64_t total = c.oc * c.ic * taps;
+    PackConvWeightKernel<<<static_cast<unsigned>((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184), 256, 0, stream>>>(
+        c.w, static_cast<int8_t*>(packed), c.oc, c.ic, taps);
+    NoteLaunch("conv_pack");
+    return CheckLaunch();
 }
 
 int LaunchConvTcgen05(const ConvArgs& c, cudaStream_t stream) {
     if (!ConvTcgen05Supported(c)) return FTH_B200_ERR_UNSUPPORTED;
     int8_t* nhwc = static_cast<int8_t*>(c.workspace);
-    int8_t* packed = nhwc + Align256(static_cast<size_t>(c.batch * c.ih * c.iw * c.ic));
+    const int8_t* packed = c.packed_w != nullptr ? c.packed_w : nhwc + Align256(static_cast<size_t>(c.batch * c.ih * c.iw * c.ic));
     const int64_t taps = c.kh * c.kw;
-    if (!c.weights_packed) {
+    if (c.packed_w == nullptr && !c.weights_packed) {
         const int64_t total = c.oc * c.ic * taps;
-        PackConvWeightKernel<<<static_cast<unsigned>((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184), 256, 0, stream>>>(c.w, packed, c.oc, c.ic, taps);
+        PackConvWeightKernel<<<static_cast<unsigned>((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184), 256, 0, stream>>>(c.w, const_cast<int8_t*>(packed), c.oc, c.ic, taps);
         NoteLaunch("conv_tcgen05");
     }
     {
@@ -396,6 +415,7 @@ int LaunchConvTcgen05(const ConvArgs& c, cudaStream_t stream) {
     }
     ConvTcParams p;
     p.c = c;
+    if (c.packed_w != nullptr) p.c.weights_packed = 1;  // packed by an earlier, completed pass: may be fetched early
     p.taps = static_cast<int>(taps);
     p.cblocks = static_cast<int>(c.ic / 64);
     p.kblocks = p.taps * p.cblocks;

@@ -23,10 +23,13 @@ struct ConvArgs {
     void* workspace;
     size_t workspace_bytes;
     int weights_packed;
+    const int8_t* packed_w;  // caller-owned packed weight, or null (then it lives behind the NHWC copy in the workspace)
 };
 
 bool ConvTcgen05Supported(const ConvArgs& c);
 size_t ConvTcgen05WorkspaceBytes(const ConvArgs& c);
 int LaunchConvTcgen05(const ConvArgs& c, cudaStream_t stream);
+size_t ConvPackedWeightBytes(const ConvArgs& c);
+int LaunchConvPackWeights(const ConvArgs& c, void* packed, cudaStream_t stream);
 
 }  // namespace fth

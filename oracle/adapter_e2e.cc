@@ -38,6 +38,7 @@ bool RegisterB200Kernels();
 bool RegisterB200FusedOperators();
 std::unique_ptr<GraphPass> CreateB200FusionPass();
 bool IsB200Kernel(const KernelBase* kernel);
+size_t PackedConvWeightEntries();
 }}}
 
 using namespace feather;
@@ -749,6 +750,42 @@ static void RunPlansOnGpu() {
         std::printf("      INT8 plan on CUDA: %s%s%s\n", ref.error.c_str(), plain.error.c_str(), fused.error.c_str());
         CHECK_THAT(ok && plain.outputs["y"] == ref.outputs["y"], "statically quantised plan (the reference's own quantiser) on CUDA under kRequireRequested: identical to COMMON");
         CHECK_THAT(ok && fused.outputs["y"] == ref.outputs["y"], "the same plan with Conv2D -> ReLU fused by the pass: identical to COMMON");
+    }
+    {
+        // two sessions of one compiled plan share one packed copy of the conv weight; it goes away with the last session
+        Int8Plan p = MakeInt8Plan();
+        StaticGraph graph;
+        graph.SetKernelDevice(DeviceType::CUDA);
+        graph.SetFallbackPolicy(KernelFallbackPolicy::kRequireRequested);
+        auto passes = CreateDefaultPassManager();
+        passes->AddPass(feather::kernel::b200::CreateB200FusionPass());
+        graph.SetPassManager(passes);
+        bool ok = p.ok && graph.SetModel(p.model) == 0 && graph.SetTensor("x", p.input) == 0;
+        for (const auto& item : p.weights) ok = ok && graph.SetTensor(item.first, item.second) == 0;
+        ok = ok && graph.BuildStatus().ok() && graph.ApplyPassesStatus().ok();
+        std::shared_ptr<const CompiledGraph> compiled;
+        ok = ok && CompiledGraph::Compile(graph, &compiled).ok();
+        size_t during = 0;
+        std::vector<uint8_t> first_out, second_out;
+        if (ok) {
+            std::unique_ptr<ExecutionSession> first, second;
+            ok = compiled->CreateSession(&first).ok() && compiled->CreateSession(&second).ok();
+            for (auto* session : {first.get(), second.get()}) {
+                if (!ok) break;
+                ok = session->BindInput("x", p.input).ok() && session->Run().ok();
+                std::shared_ptr<Tensor> out;
+                ok = ok && session->ReadOutput("y", &out).ok() && out != nullptr;
+                if (ok) {
+                    const uint8_t* b = static_cast<const uint8_t*>(out->raw_data());
+                    (session == first.get() ? first_out : second_out).assign(b, b + out->numel() * 4);
+                }
+            }
+            during = feather::kernel::b200::PackedConvWeightEntries();
+        }
+        const size_t after = feather::kernel::b200::PackedConvWeightEntries();
+        std::printf("      packed conv weights alive: %zu with two sessions, %zu after both are gone\n", during, after);
+        CHECK_THAT(ok && during == 1 && after == 0 && first_out == second_out && !first_out.empty(),
+                   "two sessions of one plan share ONE packed copy of the conv weight (packed once per weight, not per session)");
     }
     {
         Int8Plan p = MakeInt8GemmPlan();

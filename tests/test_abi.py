@@ -43,7 +43,7 @@ int main(void) {
   P(fth_b200_int8_linear_desc, a); P(fth_b200_int8_linear_desc, w_scales); P(fth_b200_int8_linear_desc, bias_max_abs);
   P(fth_b200_int8_linear_desc, workspace); P(fth_b200_int8_linear_desc, variant);
   P(fth_b200_int8_conv2d_desc, x); P(fth_b200_int8_conv2d_desc, relu_lut); P(fth_b200_int8_conv2d_desc, workspace_bytes);
-  P(fth_b200_int8_conv2d_desc, variant);
+  P(fth_b200_int8_conv2d_desc, variant); P(fth_b200_int8_conv2d_desc, packed_w);
   return 0; }
 '''
     with tempfile.TemporaryDirectory() as tmp:

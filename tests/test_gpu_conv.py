@@ -67,3 +67,50 @@ def test_conv_config3_full_size(cuda):
     assert B.last_variant() == "conv_tcgen05" and B.device_status() == 0
     assert np.array_equal(got, want)
     assert np.array_equal(run_int8_conv(cuda, case), conv)
+
+
+def test_conv_with_caller_owned_packed_weight(cuda):
+    """The weight packed once by fth_b200_int8_conv2d_pack_weights and handed to two different calls (other inputs, own
+    workspaces): same bytes as the call that packs into its own workspace, and the workspace need shrinks to the
+    channels-last input copy."""
+    import ctypes as C
+    from tests.gpu_helpers import dev
+    case = util.make_int8_conv(1, 64, 24, 40, 64, 3, 3, seed=11)
+    want = O.int8_conv2d(case["x"], case["sx"], 0, case["w"], case["ws"], None, case["bias"], case["so"], 0)
+    lib = B.lib()
+    w, ws, b = dev(cuda, case["w"]), dev(cuda, case["ws"]), dev(cuda, case["bias"])
+
+    def desc(x, out):
+        return B.int8_conv2d_desc(batch=1, ic=64, ih=24, iw=40, oc=64, kh=3, kw=3, x=x, w=w, out=out, x_scale=case["sx"], x_zp=0, w_scales=ws,
+                                  w_zps=None, w_params=64, out_scale=case["so"], out_zp=0, bias=b, bias_max_abs=1 << 15)
+    x = dev(cuda, case["x"])
+    out = cuda.zeros((1, 64, 24, 40), dtype=cuda.int8, device="cuda")
+    d = desc(x, out)
+    own = lib.fth_b200_int8_conv2d_workspace_bytes(C.byref(d))
+    need = lib.fth_b200_int8_conv2d_packed_weight_bytes(C.byref(d))
+    assert need >= 64 * 64 * 9
+    packed = cuda.zeros(need, dtype=cuda.uint8, device="cuda")
+    assert lib.fth_b200_int8_conv2d_pack_weights(C.byref(d), C.c_void_p(packed.data_ptr()), B.current_stream()) == B.OK
+    d.packed_w = packed.data_ptr()
+    shared = lib.fth_b200_int8_conv2d_workspace_bytes(C.byref(d))
+    assert shared + need == own
+    for seed in (11, 12):  # two calls, two inputs, one packed weight
+        c2 = util.make_int8_conv(1, 64, 24, 40, 64, 3, 3, seed=seed)
+        x2 = dev(cuda, c2["x"])
+        out2 = cuda.zeros((1, 64, 24, 40), dtype=cuda.int8, device="cuda")
+        d2 = desc(x2, out2)
+        d2.packed_w = packed.data_ptr()
+        scratch = cuda.zeros(shared, dtype=cuda.uint8, device="cuda")
+        d2.workspace, d2.workspace_bytes = scratch.data_ptr(), shared
+        B.int8_conv2d(d2)
+        cuda.cuda.synchronize()
+        assert B.last_variant() == "conv_tcgen05"
+        want2 = O.int8_conv2d(c2["x"], case["sx"], 0, case["w"], case["ws"], None, case["bias"], case["so"], 0)
+        assert np.array_equal(out2.cpu().numpy(), want2)
+    assert np.array_equal(want, O.int8_conv2d(case["x"], case["sx"], 0, case["w"], case["ws"], None, case["bias"], case["so"], 0))
+    # geometries the implicit-GEMM kernel does not take have nothing to pack
+    d3 = B.int8_conv2d_desc(batch=1, ic=16, ih=8, iw=8, oc=8, kh=3, kw=3, x=x, w=w, out=out, x_scale=1.0, x_zp=0, w_scales=ws, w_zps=None,
+                            w_params=8, out_scale=1.0, out_zp=0)
+    assert lib.fth_b200_int8_conv2d_packed_weight_bytes(C.byref(d3)) == 0
+    assert lib.fth_b200_int8_conv2d_pack_weights(C.byref(d3), C.c_void_p(packed.data_ptr()), B.current_stream()) == B.ERR_UNSUPPORTED
+    assert B.device_status() == 0
