@@ -336,8 +336,9 @@ class LinearCase:
         if ctx.peer_ok:
             try:
                 self.gather = PeerGather(ctx.B.lib(), ctx.dist, ctx.world, ctx.rank, self.m, N)  # raises on every rank or on none
-                self.prepared = [tuple(point_at_step_buffers(ctx.shard, self.gather, type(d).from_buffer_copy(d), parity) for parity in (0, 1))
-                                 for d in self.descs]
+                # the kernels do the step signalling themselves (gather_world in the descriptors): no extra launch per step
+                self.prepared = [tuple(point_at_step_buffers(ctx.shard, self.gather, type(d).from_buffer_copy(d), parity, fold_signal=True)
+                                       for parity in (0, 1)) for d in self.descs]
                 return
             except RuntimeError as exc:
                 ctx.peer_ok = False
@@ -356,7 +357,7 @@ class LinearCase:
         i = self.counter % self.n_sets
         self.counter += 1
         if self.gather is not None:
-            self._forward_peer(self.ctx.shard, self.gather, self.descs[i], self._call_desc, self.stream, self.prepared[i])
+            self._forward_peer(self.ctx.shard, self.gather, self.descs[i], self._call_desc, self.stream, self.prepared[i], fold_signal=True)
             return
         rc = self.call(C.byref(self.descs[i]), self.stream)
         if rc != 0:
@@ -367,9 +368,11 @@ class LinearCase:
     def result(self):
         """The [M, N] (world > 1) or [M, n_local] output of the last step, as a device tensor."""
         torch = self.ctx.torch
-        torch.cuda.synchronize()
         if self.gather is not None:
+            self.gather.wait(self.stream)  # the other ranks' columns of the last step
+            torch.cuda.synchronize()
             return self.gather.view(torch, self.gather.epoch & 1)
+        torch.cuda.synchronize()
         if self.nccl_gathered is not None:
             return self.nccl_gathered.transpose(0, 1).reshape(self.m, -1)[:, :N]
         return self.local_out
@@ -404,7 +407,14 @@ class LinearCase:
             self.graph, self.rotation, self.graph_parity = graph, rotation, epoch_before & 1
 
     def run_steps(self, steps):
-        """Issues exactly `steps` steps on the stream (graph replays of whole rotations, the rest one by one)."""
+        """Issues exactly `steps` steps on the stream (graph replays of whole rotations, the rest one by one).  With the
+        signalling folded into the kernels a step's wait for the other ranks rides in the next step's kernel; the wait
+        of the last step is issued here, so that the timed block ends with every rank's columns in place."""
+        self._run_steps(steps)
+        if self.gather is not None:
+            self.gather.wait(self.stream)
+
+    def _run_steps(self, steps):
         if self.graph is None:
             for _ in range(steps):
                 self.step()
@@ -443,6 +453,7 @@ class LinearCase:
         lib.fth_b200_reset_launch_count()
         self.step()
         n = lib.fth_b200_launch_count()
+        self.variant = self.ctx.B.last_variant()  # the kernel family of the step's last launch
         self.ctx.torch.cuda.synchronize()
         return int(n)
 
@@ -531,7 +542,7 @@ def sweep(ctx, peaks, quick):
             tfl = 2.0 * m * K * n_local / (ms * 1e-3) / 1e12
             rec = {"us": round(ms * 1e3, 2), "GB/s_per_gpu": round(gbs, 1), "TFLOP/s_per_gpu": round(tfl, 2),
                    "hbm_frac": round(gbs / peaks["hbm_gbs"], 3), "tensor_frac": round(tfl / (2.0 * peaks["bf16_tflops"]), 3),
-                   "kernel": B.last_variant() if ctx.world == 1 else "tcgen05 + gather_sync"}
+                   "kernel": B.last_variant() if ctx.world == 1 else "tcgen05, gather signalling folded in"}
             if ctx.world > 1:
                 rec["whole_job_TFLOP/s"] = round(tfl * ctx.world, 1)
                 rec["whole_job_weight_GB/s"] = round(K * N / (ms * 1e-3) / 1e9, 1)
@@ -704,7 +715,7 @@ def run_gpu_arm(args):
     per_step_launches = main.launches_per_step()
     block_ms = main.time_blocks(args.steps, args.warmup, BLOCKS)
     total_ms = float(np.median(block_ms))
-    variant = B.last_variant()
+    variant = main.variant
     status_timed = B.device_status()
     ms_per_step = total_ms / args.steps
     bytes_step = algorithmic_bytes(1, N)
@@ -741,6 +752,7 @@ def run_gpu_arm(args):
         a_stage.copy_(a_host, non_blocking=True)
         e2e_case.step()
         if e2e_case.gather is not None:
+            e2e_case.gather.wait(ctx.stream)
             full_host.copy_(e2e_case.gather.view(torch, e2e_case.gather.epoch & 1), non_blocking=True)
         else:
             full_host.copy_(e2e_case.nccl_gathered.view(1, -1)[:, :N], non_blocking=True)
@@ -766,7 +778,7 @@ def run_gpu_arm(args):
             failures.append(f"output of the timed kernel differs from the oracle: {parity}")
     gather_kind = None
     if world > 1:
-        gather_kind = "outputs stored to all ranks over NVLink (peer stores + flag wait)" if main.gather is not None else "NCCL all-gather"
+        gather_kind = "outputs stored to all ranks over NVLink from the kernels' epilogues, step flags published by the kernels' last thread block" if main.gather is not None else "NCCL all-gather"
     n_sets, graph_used = main.n_sets, main.graph is not None
     main.close()
     del main
@@ -793,7 +805,7 @@ def run_gpu_arm(args):
 
     if rank == 0:
         achieved = value if world == 1 else value / world
-        cluster = variant == "tcgen05" and per_step_launches - (1 if world > 1 else 0) == 1
+        cluster = per_step_launches == 1
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong",
@@ -806,11 +818,11 @@ def run_gpu_arm(args):
                          "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
                          "peak_source": peaks["source"],
                          "note": "per GPU; step = " + ("single-launch tcgen05 cluster kernel" if cluster else "tcgen05 GEMV + split-K reduce kernel") +
-                                 (" + gather signal/wait kernel" if world > 1 else "") + "; median of the timed blocks"},
+                                 (", gather signalling inside the kernel (one fth_b200_gather_wait per timed block)" if world > 1 else "") + "; median of the timed blocks"},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": K, "d2h_bytes_per_step": width if world == 1 else N,
                     "ms_per_step": round(e2e_ms, 5),
                     "api": "fth_b200_plan_run (pinned host activation in, host result out)" if world == 1 else
-                           "pinned host activation in, fth_b200_fp8_linear with peer stores + fth_b200_gather_sync, gathered row out"},
+                           "pinned host activation in, fth_b200_fp8_linear with peer stores and folded step signalling + fth_b200_gather_wait, gathered row out"},
             "gpu_launches": int(per_step_launches * args.steps),
             "device_status": int(device_status),
             "parity": parity,

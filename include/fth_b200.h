@@ -125,6 +125,18 @@ typedef struct {
      * (one CudaExecutionContext = one device, src/kernel/cuda/runtime.cu:318-321). */
     int32_t gather_peers;   /* 0 .. 7 */
     void* gather_out[7];
+    /* Gather signalling folded into the kernel (gather_world >= 2; 0: off, end the step with fth_b200_gather_sync
+     * instead).  gather_flags[r] is rank r's flag array as in fth_b200_gather_sync (peer-mapped; [gather_rank] is this
+     * rank's own; room for gather_world + 2 words each, zero-filled at creation).  The kernel takes the step number s
+     * from the counter in its own array, holds its first store into the peers' buffers until every rank has signalled
+     * step s - 1 (so nobody is still reading the buffer pair being overwritten; bounded wait, reported through
+     * fth_b200_device_status), and when its last thread block has stored its outputs it publishes s in every rank's
+     * array.  A consumer of the gathered buffer waits for the other ranks' data with fth_b200_gather_wait; the next
+     * step's kernel does so by itself.  Kernel families without this path get the same steps as small kernels around
+     * them.  All ranks must use one protocol (this one or fth_b200_gather_sync) for the life of a flag array. */
+    int32_t gather_world;
+    int32_t gather_rank;
+    void* gather_flags[8];
 } fth_b200_fp8_linear_desc;
 
 int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t stream);
@@ -207,6 +219,9 @@ typedef struct {
     int32_t weights_static; /* as in fth_b200_fp8_linear_desc */
     int32_t gather_peers;   /* as in fth_b200_fp8_linear_desc */
     void* gather_out[7];
+    int32_t gather_world;   /* as in fth_b200_fp8_linear_desc */
+    int32_t gather_rank;
+    void* gather_flags[8];
 } fth_b200_int8_linear_desc;
 
 int fth_b200_int8_linear(const fth_b200_int8_linear_desc* desc, fth_b200_stream_t stream);
@@ -337,13 +352,16 @@ void fth_b200_plan_destroy(fth_b200_plan* plan);
  * second, until every slot of its own array has reached `epoch`; a time-out is reported through
  * fth_b200_device_status.  Epochs grow by one per step; flags are never reset.  epoch = 0 takes the step number from a
  * counter on the device (slot [world] of this rank's own array, incremented by the call), so that a captured CUDA graph
- * can be replayed; all ranks must then use epoch = 0 for every step.  Each array has room for world + 1 words. */
+ * can be replayed; all ranks must then use epoch = 0 for every step.  Each array has room for world + 2 words.
+ * fth_b200_gather_wait only waits (bounded, same reporting) until every rank has signalled the step this rank signalled
+ * last — the consumer side of the signalling that the linear kernels do themselves (gather_world in their descriptors). */
 #define FTH_B200_PEER_HANDLE_BYTES 64
 int fth_b200_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle);
 int fth_b200_peer_buffer_open(const unsigned char* handle, void** ptr);
 int fth_b200_peer_buffer_close(void* ptr);
 int fth_b200_peer_buffer_destroy(void* ptr);
 int fth_b200_gather_sync(void* const* rank_flags, int32_t world, int32_t rank, uint32_t epoch, fth_b200_stream_t stream);
+int fth_b200_gather_wait(void* const* rank_flags, int32_t world, int32_t rank, fth_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

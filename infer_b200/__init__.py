@@ -33,7 +33,7 @@ EXPORTS = [
     "fth_b200_plan_run", "fth_b200_plan_launch", "fth_b200_plan_input_bytes", "fth_b200_plan_output_bytes",
     "fth_b200_plan_destroy",
     "fth_b200_peer_buffer_create", "fth_b200_peer_buffer_open", "fth_b200_peer_buffer_close", "fth_b200_peer_buffer_destroy",
-    "fth_b200_gather_sync", "fth_b200_fp8_linear_argmax",
+    "fth_b200_gather_sync", "fth_b200_gather_wait", "fth_b200_fp8_linear_argmax",
     "fth_b200_fp8_lm_head_argmax", "fth_b200_qwen_rms_norm", "fth_b200_binary", "fth_b200_silu", "fth_b200_silu_mul",
 ]
 BINARY_ADD, BINARY_MUL = 0, 1
@@ -48,6 +48,7 @@ class Fp8LinearDesc(C.Structure):
         ("w_channel_scales", C.c_void_p), ("alpha", C.c_float), ("beta", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32), ("weights_static", C.c_int32),
         ("gather_peers", C.c_int32), ("gather_out", C.c_void_p * 7),
+        ("gather_world", C.c_int32), ("gather_rank", C.c_int32), ("gather_flags", C.c_void_p * 8),
     ]
 
 
@@ -61,6 +62,7 @@ class Int8LinearDesc(C.Structure):
         ("alpha", C.c_float), ("beta", C.c_float), ("bias_max_abs", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32), ("weights_static", C.c_int32),
         ("gather_peers", C.c_int32), ("gather_out", C.c_void_p * 7),
+        ("gather_world", C.c_int32), ("gather_rank", C.c_int32), ("gather_flags", C.c_void_p * 8),
     ]
 
 
@@ -104,6 +106,7 @@ def lib():
         handle.fth_b200_plan_destroy.argtypes = [C.c_void_p]
         handle.fth_b200_plan_destroy.restype = None
         handle.fth_b200_gather_sync.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]
+        handle.fth_b200_gather_wait.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
         handle.fth_b200_plan_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         handle.fth_b200_plan_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = handle

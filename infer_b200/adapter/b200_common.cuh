@@ -118,8 +118,10 @@ inline int FinishOut(Tensor* t, size_t bytes) {
 
 // Packed implicit-GEMM conv weights, one copy per immutable weight and device, shared by every session and plan that
 // uses the weight (the reference keeps packed x86 layouts per weight the same way, src/kernel/x86/prepared_weight_cache.h;
-// before this cache every session packed its own copy into its per-node workspace).  Entries are dropped when the last
-// kernel that holds one goes away.
+// before this cache every session packed its own copy into its per-node workspace).  Sessions hold private host copies
+// of a plan's constants (src/core/execution_plan.cc:430-470), so a weight is identified by its bytes — two 64-bit hashes
+// over the content plus its shape — not by an address; the packed layout is a pure function of the content.  Entries are
+// dropped when the last kernel that holds one goes away.
 class PackedConvWeightCache {
    public:
     // `desc` describes the conv with desc->w already pointing at the weight ON THE DEVICE; packs on the inference stream
@@ -129,7 +131,14 @@ class PackedConvWeightCache {
         if (bytes == 0 || weight == nullptr || !weight->is_immutable()) return nullptr;
         int device = 0;
         if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
-        const Key key{weight->raw_data(), weight->mutation_version(), device, desc.oc, desc.ic, desc.kh, desc.kw};
+        const size_t count = static_cast<size_t>(weight->numel());
+        const uint8_t* bytes_host = static_cast<const uint8_t*>(weight->raw_data());
+        uint64_t h1 = 1469598103934665603ull, h2 = 0x9e3779b97f4a7c15ull;  // FNV-1a, and a multiply-rotate mix
+        for (size_t i = 0; i < count; ++i) {
+            h1 = (h1 ^ bytes_host[i]) * 1099511628211ull;
+            h2 = ((h2 << 7) | (h2 >> 57)) + bytes_host[i] * 0xff51afd7ed558ccdull;
+        }
+        const Key key{h1, h2, device, desc.oc, desc.ic, desc.kh, desc.kw};
         std::lock_guard<std::mutex> lock(Mutex());
         auto& table = Table();
         for (auto it = table.begin(); it != table.end();) {
@@ -155,9 +164,9 @@ class PackedConvWeightCache {
 
    private:
     struct Key {
-        const void* host; uint64_t version; int device; int64_t oc, ic, kh, kw;
+        uint64_t h1, h2; int device; int64_t oc, ic, kh, kw;
         bool operator==(const Key& o) const {
-            return host == o.host && version == o.version && device == o.device && oc == o.oc && ic == o.ic && kh == o.kh && kw == o.kw;
+            return h1 == o.h1 && h2 == o.h2 && device == o.device && oc == o.oc && ic == o.ic && kh == o.kh && kw == o.kw;
         }
     };
     static std::mutex& Mutex() { static std::mutex m; return m; }

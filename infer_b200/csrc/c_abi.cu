@@ -182,17 +182,46 @@ int BuildPeers(const Desc* d, PeerOut* peers) {
     return FTH_B200_OK;
 }
 
+template <typename Desc>
+int BuildSignal(const Desc* d, GatherSignal* signal) {
+    *signal = GatherSignal{};
+    if (d->gather_world == 0) return FTH_B200_OK;
+    if (d->gather_world < 1 || d->gather_world > kMaxPeers + 1 || d->gather_rank < 0 || d->gather_rank >= d->gather_world) return FTH_B200_ERR_INVALID;
+    for (int r = 0; r < d->gather_world; ++r) {
+        if (d->gather_flags[r] == nullptr) return FTH_B200_ERR_INVALID;
+        signal->flags[r] = static_cast<uint32_t*>(d->gather_flags[r]);
+    }
+    signal->world = d->gather_world;
+    signal->rank = d->gather_rank;
+    return FTH_B200_OK;
+}
+
 // Runs the chosen kernel family; when the output has peer replicas and that kernel does not write them itself, a
-// block copy follows on the same stream.
-int Run(int variant, int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* workspace,
+// block copy follows on the same stream.  Gather signalling the kernel does not fold in becomes two small kernels
+// around it: wait for the peers' previous step in front, publish this step behind the last store.
+int Run(int variant, int dtype, const LinearArgs& args_in, const Fp8Epilogue& fe, const Int8Epilogue& ie, void* workspace,
         size_t workspace_bytes, cudaStream_t stream) {
-    const int rc = Dispatch(variant, dtype, args, fe, ie, workspace, workspace_bytes, stream);
-    if (rc != FTH_B200_OK || args.peers.count == 0) return rc;
-    if (variant == FTH_B200_VARIANT_TCGEN05 && Tcgen05StoresToPeers(dtype, args, fe, ie)) return rc;
-    const bool int8 = dtype == FTH_B200_INT8;
-    const int out_dtype = int8 ? ie.out_dtype : fe.out_dtype;
-    const int elem = out_dtype == FTH_B200_FP32 ? 4 : (out_dtype == FTH_B200_BF16 || out_dtype == FTH_B200_FP16) ? 2 : 1;
-    return LaunchPeerCopy(int8 ? ie.out : fe.out, args.m, args.n, int8 ? ie.ldo : fe.ldo, elem, args.peers, stream);
+    if (variant < 0) return variant;
+    LinearArgs args = args_in;
+    const bool signalling = args.signal.world > 0;
+    const bool stores_peers = variant == FTH_B200_VARIANT_TCGEN05 && Tcgen05StoresToPeers(dtype, args, fe, ie);
+    const bool folded = signalling && variant == FTH_B200_VARIANT_TCGEN05 && Tcgen05SignalsInKernel(dtype, args, fe, ie);
+    if (signalling && !folded) {
+        args.signal.world = 0;
+        const int rc = LaunchGatherWaitPrevious(args_in.signal, stream);
+        if (rc != FTH_B200_OK) return rc;
+    }
+    int rc = Dispatch(variant, dtype, args, fe, ie, workspace, workspace_bytes, stream);
+    if (rc != FTH_B200_OK) return rc;
+    if (args.peers.count > 0 && !stores_peers) {
+        const bool int8 = dtype == FTH_B200_INT8;
+        const int out_dtype = int8 ? ie.out_dtype : fe.out_dtype;
+        const int elem = out_dtype == FTH_B200_FP32 ? 4 : (out_dtype == FTH_B200_BF16 || out_dtype == FTH_B200_FP16) ? 2 : 1;
+        rc = LaunchPeerCopy(int8 ? ie.out : fe.out, args.m, args.n, int8 ? ie.ldo : fe.ldo, elem, args.peers, stream);
+        if (rc != FTH_B200_OK) return rc;
+    }
+    if (signalling && !folded) return LaunchGatherPublish(args_in.signal, stream);
+    return FTH_B200_OK;
 }
 
 void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* fe) {
@@ -203,6 +232,7 @@ void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* 
     args->w_static = d->weights_static != 0;
     args->peers.count = 0;
     args->argmax_keys = nullptr;
+    args->signal = GatherSignal{};
     fe->ab_scale = d->w_channel_scales ? d->a_scale : d->a_scale * d->w_scale;
     fe->w_channel_scales = d->w_channel_scales;
     fe->is_gemm = d->op == FTH_B200_OP_GEMM;
@@ -226,6 +256,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
     args->w_static = d->weights_static != 0;
     args->peers.count = 0;
     args->argmax_keys = nullptr;
+    args->signal = GatherSignal{};
     ie->w_scales = d->w_scales; ie->w_zps = d->w_zps; ie->per_channel = d->w_params != 1;
     ie->a_scale = d->a_scale; ie->a_zp = d->a_zp; ie->out_scale = d->out_scale; ie->out_zp = d->out_zp;
     ie->bias = d->bias; ie->bias_mode = d->bias_mode;
@@ -270,7 +301,7 @@ extern "C" int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* d, fth_b200_s
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Fp8Epilogue fe; Int8Epilogue ie = {};
     BuildFp8(d, &args, &fe);
-    if (BuildPeers(d, &args.peers) != FTH_B200_OK) return FTH_B200_ERR_INVALID;
+    if (BuildPeers(d, &args.peers) != FTH_B200_OK || BuildSignal(d, &args.signal) != FTH_B200_OK) return FTH_B200_ERR_INVALID;
     return Run(PickVariant(d->variant, d->dtype, args, d->workspace, d->workspace_bytes), d->dtype, args, fe, ie,
                d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
 }
@@ -326,7 +357,7 @@ extern "C" int fth_b200_int8_linear(const fth_b200_int8_linear_desc* d, fth_b200
     if (rc != FTH_B200_OK) return rc;
     LinearArgs args; Int8Epilogue ie; Fp8Epilogue fe = {};
     BuildInt8(d, &args, &ie);
-    if (BuildPeers(d, &args.peers) != FTH_B200_OK) return FTH_B200_ERR_INVALID;
+    if (BuildPeers(d, &args.peers) != FTH_B200_OK || BuildSignal(d, &args.signal) != FTH_B200_OK) return FTH_B200_ERR_INVALID;
     return Run(PickVariant(d->variant, FTH_B200_INT8, args, d->workspace, d->workspace_bytes), FTH_B200_INT8, args,
                fe, ie, d->workspace, d->workspace_bytes, static_cast<cudaStream_t>(stream));
 }

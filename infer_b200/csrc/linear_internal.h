@@ -13,6 +13,15 @@ struct PeerOut {
     int64_t delta[kMaxPeers];
 };
 
+// Step signalling of a gather, folded into the kernels: flags[r] is rank r's flag array (uint32; slot [q] = last step rank
+// q has published there), this rank's own array also holds the step counter (slot [world]) and the arrival counter of the
+// running launch (slot [world + 1]).
+struct GatherSignal {
+    uint32_t* flags[kMaxPeers + 1];
+    int world;  // 0: off
+    int rank;
+};
+
 // Operand description common to FP8 and INT8 linear kernels.
 struct LinearArgs {
     const void* a;   // [M,K] activations (FP8 / INT8, or BF16 / FP32 when a Cast / QuantizeLinear is fused)
@@ -25,6 +34,7 @@ struct LinearArgs {
     int w_static;    // no earlier work in the stream writes the weights: they may be read before it has finished
     PeerOut peers;   // replicas of the output on other GPUs (count 0: none)
     unsigned long long* argmax_keys;  // [m] running (value, index) maxima of each output row, or null
+    GatherSignal signal;              // world 0: none
 };
 
 int LaunchLinearSimt(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
@@ -59,6 +69,13 @@ bool Tcgen05SelectsInEpilogue(int dtype, const LinearArgs& args, const Fp8Epilog
 // Turns the packed (value, index) keys a fused argmax left in `keys` into int64 indices in place; a row without a
 // candidate receives `none_value`.
 int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, int64_t none_value, cudaStream_t stream);
+
+// True when that launch also does the gather's step signalling itself (args.signal).
+bool Tcgen05SignalsInKernel(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie);
+// The two halves of a gather step as kernels of their own, for kernel families that do not fold them in: wait until every
+// rank has published the previous step / count this step and publish it everywhere.
+int LaunchGatherWaitPrevious(const GatherSignal& signal, cudaStream_t stream);
+int LaunchGatherPublish(const GatherSignal& signal, cudaStream_t stream);
 
 // Copies the [m, n] output block (elements of `elem_bytes`, row stride ldo elements) to every peer replica.
 int LaunchPeerCopy(const void* out, int64_t m, int64_t n, int64_t ldo, int elem_bytes, const PeerOut& peers, cudaStream_t stream);

@@ -126,6 +126,45 @@ __device__ __forceinline__ void StoreWithPeers(const PeerOut& peers, T* dst, T v
     for (int r = 0; r < peers.count; ++r) *reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(dst) + peers.delta[r]) = value;
 }
 
+// ---- gather step signalling inside a kernel ---------------------------------------------------------------------
+// The step this launch works on.  Read after griddepcontrol.wait: the launch in front writes the counter at its very end.
+__device__ __forceinline__ uint32_t GatherStep(const GatherSignal& g) {
+    uint32_t s;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(s) : "l"(g.flags[g.rank] + g.world) : "memory");
+    s += 1;
+    return s == 0 ? 1u : s;
+}
+// Called by the threads 0 .. world-1 of a group (index `r`): waits, for at most one second, until rank r has published
+// step - 1 in this rank's array.  Stores into the peers' buffers of this step may only follow.
+__device__ __forceinline__ void GatherWaitPrevious(const GatherSignal& g, int r, uint32_t step, int* status) {
+    const uint32_t* slot = g.flags[g.rank] + r;
+    const uint32_t want = step - 1;
+    uint64_t start = 0;
+    for (int spin = 0;; ++spin) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(slot) : "memory");
+        if (static_cast<int32_t>(seen - want) >= 0) return;
+        if (spin == 64) start = GlobalTimerNs();
+        if (spin > 64) {
+            __nanosleep(100);
+            if (GlobalTimerNs() - start > kWaitBudgetNs) { ReportTimeout(status, 41, r); return; }
+        }
+    }
+}
+// Called by ONE thread of every thread block of the launch after the block's output stores (each storing thread has
+// executed __threadfence_system() and the block has synchronised): the last block to arrive advances the step counter
+// and publishes the step in every rank's array.
+__device__ __forceinline__ void GatherArriveAndPublish(const GatherSignal& g, uint32_t step, unsigned blocks) {
+    uint32_t* mine = g.flags[g.rank];
+    const unsigned arrived = atomicAdd(mine + g.world + 1, 1u);
+    if (arrived != blocks - 1) return;
+    __threadfence_system();  // the other blocks' stores (ordered before their arrivals) before the flags below
+    mine[g.world + 1] = 0;
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(mine + g.world), "r"(step) : "memory");
+    for (int r = 0; r < g.world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flags[r] + g.rank), "r"(step) : "memory");
+}
+
 // Epilogue of one output (activation row q, channel n) from its complete accumulator.
 // Returns the output code on the direct path (read by the fused argmax).
 template <bool INT8>

@@ -269,6 +269,16 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         ClusterArrive();
         const bool delivered = MbarWait(x_full, 0, p.status, 24, 0);
 
+        // Column-sharded projection with the gather's signalling folded in: before the first store into the peers'
+        // buffers every rank must have published the previous step.  The wait sits here, behind the whole weight
+        // stream of this launch, so the NVLink round trip of the peers' flags is normally long over.
+        uint32_t gather_step = 0;
+        if (p.args.signal.world > 0) {
+            gather_step = GatherStep(p.args.signal);
+            if (et < p.args.signal.world) GatherWaitPrevious(p.args.signal, et, gather_step, p.status);
+            EpilogueBarrier<128>();
+        }
+
         // One output per thread and round: channel r of this CTA's rows (fastest, so a warp stores consecutive
         // channels) of activation row q.  The chunks are added in chunk order, as the two-kernel path adds them.
         const int total = m << lshift;
@@ -302,6 +312,11 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             }
             if (p.args.argmax_keys != nullptr)
                 ArgmaxUpdate(p.args.argmax_keys, stored ? q : -1, stored ? ArgmaxKey<INT8>(p.e4m3, code, n) : 0ull);
+        }
+        if (p.args.signal.world > 0) {
+            __threadfence_system();  // this thread's peer stores before the block's arrival
+            EpilogueBarrier<128>();
+            if (et == 0) GatherArriveAndPublish(p.args.signal, gather_step, gridDim.x);
         }
     }
     if (warp < 2) {

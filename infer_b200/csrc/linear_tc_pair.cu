@@ -140,6 +140,14 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         const uint32_t leader_empty = MapToRank(SmemAddr(tmem_empty), 0);
         int64_t iter = 0;
         int64_t staged_nt = -1;
+        // gather signalling folded in (column shards): the peers must have published the previous step before the first
+        // store into their buffers; this CTA arrives when all its tiles are stored
+        uint32_t gather_step = 0;
+        if (p.args.signal.world > 0) {
+            gather_step = GatherStep(p.args.signal);
+            if (et < p.args.signal.world) GatherWaitPrevious(p.args.signal, et, gather_step, p.status);
+            EpilogueBarrier<C::kEpilogueThreads>();
+        }
         for (int64_t u = pair_id; u < units; u += pairs, ++iter) {
             const int64_t mt = u % m_pairs, nt = u / m_pairs;
             const int acc = static_cast<int>(iter & 1);
@@ -223,6 +231,11 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             umma::FenceBeforeThreadSync();
             __syncwarp();
             if (lane == 0) MbarArriveRemote(leader_empty + acc * 8);
+        }
+        if (p.args.signal.world > 0) {
+            __threadfence_system();
+            EpilogueBarrier<C::kEpilogueThreads>();
+            if (et == 0) GatherArriveAndPublish(p.args.signal, gather_step, gridDim.x);
         }
     }
 

@@ -335,12 +335,21 @@ __global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue
     // Launched with programmatic stream serialization: wait until the producing grid has completed and its
     // partial sums are visible.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Column-sharded projection with the gather's signalling folded in: every rank must have published the previous
+    // step before this pass stores into the peers' buffers; the last block of the pass publishes this step.
+    const bool signalling = p.args.signal.world > 0;
+    uint32_t gather_step = 0;
+    if (signalling) {
+        gather_step = GatherStep(p.args.signal);
+        if (threadIdx.x < p.args.signal.world) GatherWaitPrevious(p.args.signal, threadIdx.x, gather_step, p.status);
+        __syncthreads();
+    }
     const int64_t groups = p.p_pad / 4;
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     const int64_t q = idx / groups;
     const int64_t p4 = (idx % groups) * 4;
     const bool valid = idx < groups * p.q_total && p4 < p.p_total;
-    if (!valid && p.args.argmax_keys == nullptr) return;
+    if (!valid && p.args.argmax_keys == nullptr && !signalling) return;
     const uint4* part = static_cast<const uint4*>(p.scratch);
     uint32_t v[4] = {0, 0, 0, 0};
     if (valid) {
@@ -382,6 +391,11 @@ __global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue
             }
         }
         ArgmaxUpdate(p.args.argmax_keys, valid ? static_cast<int>(q) : -1, key);
+    }
+    if (signalling) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) GatherArriveAndPublish(p.args.signal, gather_step, gridDim.x);
     }
 }
 

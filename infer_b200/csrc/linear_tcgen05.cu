@@ -127,6 +127,11 @@ bool Tcgen05StoresToPeers(int dtype, const LinearArgs& a, const Fp8Epilogue& fe,
     return !GeometryFor(a).swap && DirectEpilogue(int8, fe, ie) && (int8 ? ie.out_dtype : fe.out_dtype) == 0;
 }
 
+bool Tcgen05SignalsInKernel(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
+    // exactly the launches whose own epilogue writes the peers' buffers: their last block knows when all stores are out
+    return Tcgen05StoresToPeers(dtype, a, fe, ie);
+}
+
 size_t Tcgen05ScratchBytes(int dtype, const LinearArgs& a) {
     (void)dtype;
     const TcGeometry g = GeometryFor(a);

@@ -8,6 +8,7 @@
 
 #include "common.cuh"
 #include "linear_internal.h"
+#include "linear_tc.cuh"
 #include "tma.cuh"
 
 namespace fth {
@@ -63,6 +64,25 @@ __global__ void GatherSyncKernel(FlagPtrs flags, int world, int self, uint32_t e
     }
 }
 
+// The halves of a folded gather step as kernels of their own (for kernel families without the in-kernel path), and the
+// consumer-side wait.  mode 0: wait for every rank's previous step; 1: count this step and publish it; 2: wait until
+// every rank has published the step this rank published last.
+__global__ void GatherStepKernel(GatherSignal g, int mode, int* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int r = threadIdx.x;
+    if (mode == 1) {
+        if (r == 0) {
+            __threadfence_system();
+            tc::GatherArriveAndPublish(g, tc::GatherStep(g), 1u);
+        }
+        return;
+    }
+    if (r >= g.world) return;
+    const uint32_t next = tc::GatherStep(g);  // counter + 1
+    tc::GatherWaitPrevious(g, r, mode == 0 ? next : next + 1, status);
+}
+
 __global__ void ArgmaxFinalizeKernel(unsigned long long* keys, int64_t m, long long none_value) {
     const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (i >= m) return;
@@ -77,6 +97,23 @@ int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, int64_t none_value
     NoteLaunch("argmax_finalize");
     return CheckLaunch();
 }
+
+static int LaunchGatherStep(const GatherSignal& signal, int mode, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, GatherStepKernel, signal, mode, DeviceStatusPtr()) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    NoteLaunch(mode == 1 ? "gather_publish" : "gather_wait");
+    return CheckLaunch();
+}
+int LaunchGatherWaitPrevious(const GatherSignal& signal, cudaStream_t stream) { return LaunchGatherStep(signal, 0, stream); }
+int LaunchGatherPublish(const GatherSignal& signal, cudaStream_t stream) { return LaunchGatherStep(signal, 1, stream); }
 
 int LaunchPeerCopy(const void* out, int64_t m, int64_t n, int64_t ldo, int elem_bytes, const PeerOut& peers, cudaStream_t stream) {
     if (peers.count <= 0 || m <= 0 || n <= 0) return FTH_B200_OK;
@@ -141,4 +178,17 @@ extern "C" int fth_b200_gather_sync(void* const* rank_flags, int32_t world, int3
     if (cudaLaunchKernelEx(&cfg, GatherSyncKernel, flags, world_arg, rank_arg, epoch, DeviceStatusPtr()) != cudaSuccess) return FTH_B200_ERR_CUDA;
     NoteLaunch("gather_sync");
     return CheckLaunch();
+}
+
+extern "C" int fth_b200_gather_wait(void* const* rank_flags, int32_t world, int32_t rank, fth_b200_stream_t stream_) {
+    ClearStaleError();
+    if (rank_flags == nullptr || world < 1 || world > kMaxPeers + 1 || rank < 0 || rank >= world) return FTH_B200_ERR_INVALID;
+    GatherSignal signal = {};
+    for (int r = 0; r < world; ++r) {
+        if (rank_flags[r] == nullptr) return FTH_B200_ERR_INVALID;
+        signal.flags[r] = static_cast<uint32_t*>(rank_flags[r]);
+    }
+    signal.world = world;
+    signal.rank = rank;
+    return LaunchGatherStep(signal, 2, static_cast<cudaStream_t>(stream_));
 }

@@ -145,6 +145,12 @@ class PeerGather:
         if self.lib.fth_b200_gather_sync(self.flags, self._world, self._rank, 0, stream) != 0:
             raise RuntimeError("fth_b200_gather_sync failed")
 
+    def wait(self, stream) -> None:
+        """Consumer side of the signalling the linear kernels do themselves (gather_world in their descriptors): waits,
+        on the stream, until every rank has published the step this rank published last."""
+        if self.lib.fth_b200_gather_wait(self.flags, self._world, self._rank, stream) != 0:
+            raise RuntimeError("fth_b200_gather_wait failed")
+
     def close(self) -> None:
         for r, b in enumerate(self.base):
             if b and r != self.rank:
@@ -154,9 +160,16 @@ class PeerGather:
         self.base = [0] * self.world
 
 
-def point_at_step_buffers(shard: "ShardedLinear", gather: PeerGather, desc, parity: int):
+def point_at_step_buffers(shard: "ShardedLinear", gather: PeerGather, desc, parity: int, fold_signal: bool = False):
     """Points `desc` (this rank's linear descriptor, weights = its column slice) at the buffers of steps with this
-    parity: its own block in its own buffer, and the same block in every other rank's."""
+    parity: its own block in its own buffer, and the same block in every other rank's.  fold_signal: the kernel also
+    does the step signalling itself (no fth_b200_gather_sync behind it; consumers use PeerGather.wait)."""
+    if fold_signal:
+        desc.gather_world, desc.gather_rank = gather.world, gather.rank
+        for r in range(gather.world):
+            desc.gather_flags[r] = gather.flags[r]
+    else:
+        desc.gather_world = 0
     offset = shard.n0 * gather.elem
     desc.out = gather.buffer(gather.rank, parity) + offset
     desc.ldo = gather.n
@@ -167,16 +180,18 @@ def point_at_step_buffers(shard: "ShardedLinear", gather: PeerGather, desc, pari
     return desc
 
 
-def forward_peer(shard: "ShardedLinear", gather: PeerGather, desc, call, stream, prepared=None):
+def forward_peer(shard: "ShardedLinear", gather: PeerGather, desc, call, stream, prepared=None, fold_signal: bool = False):
     """One gathered step: `call(desc, stream)` launches the C ABI with the output pointed at the step's buffers, then
     the step is signalled.  `prepared` = (desc for even steps, desc for odd steps) from point_at_step_buffers saves
-    the per-step pointer set-up (a decode step is a few microseconds of GPU time).  Returns the parity of the buffer
-    that holds the [M, N] result once the stream has run."""
+    the per-step pointer set-up (a decode step is a few microseconds of GPU time).  fold_signal: the kernel signals by
+    itself and nothing else is launched; whoever reads the gathered buffer calls gather.wait(stream) first (the next
+    step's kernel does that on its own).  Returns the parity of the buffer that holds the [M, N] result."""
     gather.epoch += 1
     parity = gather.epoch & 1
-    step_desc = prepared[parity] if prepared is not None else point_at_step_buffers(shard, gather, desc, parity)
+    step_desc = prepared[parity] if prepared is not None else point_at_step_buffers(shard, gather, desc, parity, fold_signal)
     rc = call(step_desc, stream)
     if rc != 0:
         raise RuntimeError(f"linear call failed: {rc}")
-    gather.sync(stream)
+    if not fold_signal:
+        gather.sync(stream)
     return parity

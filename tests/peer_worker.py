@@ -37,19 +37,26 @@ def main() -> int:
                               w_scale=2.0 ** -6, out_scale=float(k) / 64, weights_static=True)
         d.out = full.data_ptr()  # any valid pointer: workspace sizing only looks at shapes
         ws = B.linear_workspace(torch, d)
-        gather = PeerGather(lib, dist, world, rank, m, n)
         stream = B.current_stream()
-        for step in range(5):
-            parity = forward_peer(shard, gather, d, lambda desc, s: lib.fth_b200_fp8_linear(C.byref(desc), s), stream)
-            torch.cuda.synchronize()
-            got = gather.view(torch, parity)
-            if not torch.equal(got, full):
+        for fold_signal in (False, True):  # a signal / wait kernel behind every step; signalling folded into the linear kernels
+            gather = PeerGather(lib, dist, world, rank, m, n)
+            for step in range(6):
+                parity = forward_peer(shard, gather, d, lambda desc, s: lib.fth_b200_fp8_linear(C.byref(desc), s), stream,
+                                      fold_signal=fold_signal)
+                if fold_signal and step % 2 == 1:
+                    continue  # let the next step's kernel do the waiting: its result is checked below all the same
+                if fold_signal:
+                    gather.wait(stream)
+                torch.cuda.synchronize()
+                got = gather.view(torch, parity)
+                if not torch.equal(got, full):
+                    failures += 1
+                    print(f"rank {rank}: M={m} fold={fold_signal} step {step}: {(got != full).sum().item()} bytes differ", flush=True)
+            if B.device_status() != 0:
                 failures += 1
-                print(f"rank {rank}: M={m} step {step}: {(got != full).sum().item()} bytes differ", flush=True)
-        if B.device_status() != 0:
-            failures += 1
-        dist.barrier()
-        gather.close()
+            torch.cuda.synchronize()
+            dist.barrier()
+            gather.close()
         del ws, ws_full
     t = torch.tensor([failures], device="cuda")
     dist.all_reduce(t)

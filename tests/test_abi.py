@@ -39,7 +39,8 @@ def test_struct_layouts_match_the_c_compiler():
 int main(void) {
   printf("sizeof.fp8 %zu\nsizeof.int8 %zu\nsizeof.conv %zu\n", sizeof(fth_b200_fp8_linear_desc), sizeof(fth_b200_int8_linear_desc), sizeof(fth_b200_int8_conv2d_desc));
   P(fth_b200_fp8_linear_desc, a); P(fth_b200_fp8_linear_desc, ldo); P(fth_b200_fp8_linear_desc, w_channel_scales);
-  P(fth_b200_fp8_linear_desc, workspace); P(fth_b200_fp8_linear_desc, variant);
+  P(fth_b200_fp8_linear_desc, workspace); P(fth_b200_fp8_linear_desc, variant); P(fth_b200_fp8_linear_desc, gather_out);
+  P(fth_b200_fp8_linear_desc, gather_world); P(fth_b200_fp8_linear_desc, gather_flags); P(fth_b200_int8_linear_desc, gather_flags);
   P(fth_b200_int8_linear_desc, a); P(fth_b200_int8_linear_desc, w_scales); P(fth_b200_int8_linear_desc, bias_max_abs);
   P(fth_b200_int8_linear_desc, workspace); P(fth_b200_int8_linear_desc, variant);
   P(fth_b200_int8_conv2d_desc, x); P(fth_b200_int8_conv2d_desc, relu_lut); P(fth_b200_int8_conv2d_desc, workspace_bytes);
