@@ -65,8 +65,8 @@ __global__ void GatherSyncKernel(FlagPtrs flags, int world, int self, uint32_t e
 }
 
 // The halves of a folded gather step as kernels of their own (for kernel families without the in-kernel path), and the
-// consumer-side wait.  mode 0: wait for every rank's previous step; 1: count this step and publish it; 2: wait until
-// every rank has published the step this rank published last.
+// consumer-side wait.  mode 1: count this step and publish it; otherwise wait until every rank has published the step
+// this rank's counter stands at.
 __global__ void GatherStepKernel(GatherSignal g, int mode, int* status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -79,8 +79,9 @@ __global__ void GatherStepKernel(GatherSignal g, int mode, int* status) {
         return;
     }
     if (r >= g.world) return;
-    const uint32_t next = tc::GatherStep(g);  // counter + 1
-    tc::GatherWaitPrevious(g, r, mode == 0 ? next : next + 1, status);
+    // Both waits are for the value of this rank's step counter: in front of a step's kernel that is the previous step;
+    // behind the kernel (which advanced the counter) it is the step itself.
+    tc::GatherWaitPrevious(g, r, tc::GatherStep(g), status);
 }
 
 __global__ void ArgmaxFinalizeKernel(unsigned long long* keys, int64_t m, long long none_value) {
