@@ -141,8 +141,11 @@ __device__ __forceinline__ void GatherWaitPrevious(const GatherSignal& g, int r,
     const uint32_t want = step - 1;
     uint64_t start = 0;
     for (int spin = 0;; ++spin) {
+        // A relaxed load is enough: nothing the peer wrote is read here.  The flag only says that the peer's stream has
+        // passed its reads of the buffers this launch is about to overwrite (it publishes a step from a kernel that its
+        // stream orders behind those reads), and the stores below depend on the value through the branch.
         uint32_t seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(slot) : "memory");
+        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(slot) : "memory");
         if (static_cast<int32_t>(seen - want) >= 0) return;
         if (spin == 64) start = GlobalTimerNs();
         if (spin > 64) {
@@ -151,18 +154,20 @@ __device__ __forceinline__ void GatherWaitPrevious(const GatherSignal& g, int r,
         }
     }
 }
-// Called by ONE thread of every thread block of the launch after the block's output stores (each storing thread has
-// executed __threadfence_system() and the block has synchronised): the last block to arrive advances the step counter
-// and publishes the step in every rank's array.
+// Called by ONE thread of every thread block of the launch, after a block-wide barrier behind the block's output
+// stores: the barrier orders the other threads' stores before this thread, whose system-scope fence then orders them
+// (cumulatively) before its arrival.  The last block to arrive advances the step counter and publishes the step in
+// every rank's array.
 __device__ __forceinline__ void GatherArriveAndPublish(const GatherSignal& g, uint32_t step, unsigned blocks) {
     uint32_t* mine = g.flags[g.rank];
+    __threadfence_system();
     const unsigned arrived = atomicAdd(mine + g.world + 1, 1u);
     if (arrived != blocks - 1) return;
     __threadfence_system();  // the other blocks' stores (ordered before their arrivals) before the flags below
     mine[g.world + 1] = 0;
     asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(mine + g.world), "r"(step) : "memory");
-    for (int r = 0; r < g.world; ++r)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flags[r] + g.rank), "r"(step) : "memory");
+    for (int r = 0; r < g.world; ++r)  // one fence above, then plain system-scope stores: none of them waits for the others
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(g.flags[r] + g.rank), "r"(step) : "memory");
 }
 
 // Epilogue of one output (activation row q, channel n) from its complete accumulator.

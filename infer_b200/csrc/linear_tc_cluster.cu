@@ -314,8 +314,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 ArgmaxUpdate(p.args.argmax_keys, stored ? q : -1, stored ? ArgmaxKey<INT8>(p.e4m3, code, n) : 0ull);
         }
         if (p.args.signal.world > 0) {
-            __threadfence_system();  // this thread's peer stores before the block's arrival
-            EpilogueBarrier<128>();
+            EpilogueBarrier<128>();  // every epilogue thread's peer stores are issued
             if (et == 0) GatherArriveAndPublish(p.args.signal, gather_step, gridDim.x);
         }
     }

@@ -233,7 +233,6 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             if (lane == 0) MbarArriveRemote(leader_empty + acc * 8);
         }
         if (p.args.signal.world > 0) {
-            __threadfence_system();
             EpilogueBarrier<C::kEpilogueThreads>();
             if (et == 0) GatherArriveAndPublish(p.args.signal, gather_step, gridDim.x);
         }

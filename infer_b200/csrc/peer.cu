@@ -72,10 +72,7 @@ __global__ void GatherStepKernel(GatherSignal g, int mode, int* status) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int r = threadIdx.x;
     if (mode == 1) {
-        if (r == 0) {
-            __threadfence_system();
-            tc::GatherArriveAndPublish(g, tc::GatherStep(g), 1u);
-        }
+        if (r == 0) tc::GatherArriveAndPublish(g, tc::GatherStep(g), 1u);
         return;
     }
     if (r >= g.world) return;
