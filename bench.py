@@ -586,8 +586,38 @@ def config4_decode_step(torch, B, dev, fp8_call, stream):
         ms = event_time_ms(torch, graph.replay, 20, 3) / 20
         wbytes = layers * sum(k * n for k, n in shapes)
         result[f"m{m}"] = {"us": round(ms * 1e3, 1), "projections": len(descs), "weight_GB/s": round(wbytes / (ms * 1e-3) / 1e9, 1),
-                           "kernel": B.last_variant()}
+                           "kernel": B.last_variant(), "what": "the 168 projections alone, each on its own input"}
         del keep, graph
+    # the whole step on the device: projections and the operators between them (QwenRmsNorm, Add, SiLU * Mul), chained
+    from infer_b200.decoder_step import DecoderStep
+    names = ["q", "k", "v", "o", "gate", "up", "down"]
+    layer_weights = []
+    for _ in range(layers):
+        layer = {}
+        for name, (k, n) in zip(names, shapes):
+            layer[name] = torch.randint(0, 120, (k, n), dtype=torch.uint8, device=dev)
+            layer[name + "_scale"] = 2.0 ** -20
+        for g in ("g1", "g2"):
+            layer[g] = (torch.randn(hidden, device=dev) * 0.1).to(torch.bfloat16).view(torch.int16)
+        layer_weights.append(layer)
+    wbytes = layers * sum(k * n for k, n in shapes)
+    for m in (1, 16):
+        for fused in (True, False):
+            step = DecoderStep(torch, layer_weights, m, hidden, inter, 2.0 ** -9, 2.0 ** -9, fp8_dtype=B.E5M2, fused=fused)
+            step.x.copy_(torch.randn((m, hidden), device=dev).to(torch.bfloat16).view(torch.int16))
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                step.run(C.c_void_p(side.cuda_stream))
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    step.run(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            ms = event_time_ms(torch, graph.replay, 20, 3) / 20
+            result[f"whole_step_m{m}_{'fused' if fused else 'node_by_node'}"] = {
+                "us": round(ms * 1e3, 1), "launches": step.launches, "weight_GB/s": round(wbytes / (ms * 1e-3) / 1e9, 1),
+                "hbm_frac_of_weights": round(wbytes / (ms * 1e-3) / 1e9 / measured_peaks()["hbm_gbs"], 3),
+                "what": "24 layers, every node on the device: " + ("6 launches per layer (fth_b200_fp8_linear_fused)" if fused else "12 launches per layer")}
+            del graph, step
     return result
 
 

@@ -158,6 +158,40 @@ int fth_b200_fp8_lm_head_argmax(const fth_b200_fp8_linear_desc* desc, int64_t* t
 int fth_b200_fp8_linear_supported(const fth_b200_fp8_linear_desc* desc);
 size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc);
 
+/* -------------------------------------------------------------------------------------------------
+ * A decode-sized FP8 projection with the decoder-block operators around it in the same launch.  The descriptor is the
+ * projection itself as the Qwen exporter wraps it — Cast(BF16 -> FP8) -> MatMul -> Cast(FP8 -> BF16), i.e. a_dtype =
+ * out_dtype = FTH_B200_BF16 — and `fusion` names what else the plan holds around it:
+ *   prologue  FTH_B200_FUSE_RMS_NORM: the activation is first normalised as the QwenRmsNorm node in front would
+ *             (src/kernel/common/qwen_rms_norm.cc:71-95, BF16 output); FTH_B200_FUSE_SILU_MUL: the activation is
+ *             Mul(SiLU(a), a2) of two BF16 tensors (the SiLU and Mul nodes between gate / up and the down projection).
+ *   residual  BF16, laid out like `out`: out = Add(residual, out) (the residual connection behind o / down).
+ *   w2        a second weight of the same format and layout on the same activation (gate and up): [K,n2] / [n2,K]
+ *             with scale w2_scale, output out2 [M,n2] (row stride ldo2, 0 = n2); desc->n must be a multiple of 128.
+ * Every rounding point of the unfused nodes is kept (BF16 after the norm / SiLU / Mul, FP8 after the Cast, FP8 after
+ * the product, BF16 after the second Cast and after the Add), and the squares of a row are summed in the order
+ * fth_b200_qwen_rms_norm uses, so the call returns the bytes of the separate calls.  Shapes of the single-launch
+ * kernel only (M <= 32, K <= 4096 with a norm); FTH_B200_ERR_UNSUPPORTED otherwise: run the nodes one by one then.
+ * No counterpart in the reference, which runs each node as its own kernel (src/kernel/cuda/{qwen_rms_norm,silu,mul,add}.cu).
+ * ------------------------------------------------------------------------------------------------- */
+enum { FTH_B200_FUSE_NONE = 0, FTH_B200_FUSE_RMS_NORM = 1, FTH_B200_FUSE_SILU_MUL = 2 };
+typedef struct {
+    int32_t prologue;            /* FTH_B200_FUSE_* */
+    int32_t norm_weight_dtype;   /* FTH_B200_BF16 or FTH_B200_FP32 */
+    const void* norm_weight;     /* [K] */
+    float norm_weight_offset;    /* QwenRmsNormParam::weight_offset */
+    float norm_epsilon;
+    const void* a2;              /* prologue SILU_MUL: BF16 [M,K] */
+    const void* residual;        /* BF16 or null */
+    const void* w2;              /* or null */
+    float w2_scale;
+    void* out2;
+    int64_t n2;
+    int64_t ldo2;
+} fth_b200_fp8_linear_fusion;
+int fth_b200_fp8_linear_fused(const fth_b200_fp8_linear_desc* desc, const fth_b200_fp8_linear_fusion* fusion, fth_b200_stream_t stream);
+int fth_b200_fp8_linear_fused_supported(const fth_b200_fp8_linear_desc* desc, const fth_b200_fp8_linear_fusion* fusion);
+
 /* FP8 linear for callers that cannot hand over a scratch buffer because they may not allocate one: a Feather
  * node built with a workspace limit of zero, or a session whose device memory was fixed when its plan was
  * compiled.  No counterpart in the reference.  Same contract and results as fth_b200_fp8_linear on the

@@ -34,7 +34,7 @@ EXPORTS = [
     "fth_b200_plan_destroy",
     "fth_b200_peer_buffer_create", "fth_b200_peer_buffer_open", "fth_b200_peer_buffer_close", "fth_b200_peer_buffer_destroy",
     "fth_b200_gather_sync", "fth_b200_gather_wait", "fth_b200_fp8_linear_argmax",
-    "fth_b200_fp8_lm_head_argmax", "fth_b200_qwen_rms_norm", "fth_b200_binary", "fth_b200_silu", "fth_b200_silu_mul",
+    "fth_b200_fp8_lm_head_argmax", "fth_b200_fp8_linear_fused", "fth_b200_fp8_linear_fused_supported", "fth_b200_qwen_rms_norm", "fth_b200_binary", "fth_b200_silu", "fth_b200_silu_mul",
 ]
 BINARY_ADD, BINARY_MUL = 0, 1
 
@@ -50,6 +50,17 @@ class Fp8LinearDesc(C.Structure):
         ("gather_peers", C.c_int32), ("gather_out", C.c_void_p * 7),
         ("gather_world", C.c_int32), ("gather_rank", C.c_int32), ("gather_flags", C.c_void_p * 8),
     ]
+
+
+class Fp8LinearFusion(C.Structure):
+    _fields_ = [
+        ("prologue", C.c_int32), ("norm_weight_dtype", C.c_int32), ("norm_weight", C.c_void_p), ("norm_weight_offset", C.c_float),
+        ("norm_epsilon", C.c_float), ("a2", C.c_void_p), ("residual", C.c_void_p), ("w2", C.c_void_p), ("w2_scale", C.c_float),
+        ("out2", C.c_void_p), ("n2", C.c_int64), ("ldo2", C.c_int64),
+    ]
+
+
+FUSE_NONE, FUSE_RMS_NORM, FUSE_SILU_MUL = 0, 1, 2
 
 
 class Int8LinearDesc(C.Structure):
@@ -193,6 +204,19 @@ def int8_conv2d_desc(*, batch, ic, ih, iw, oc, kh, kw, x, w, out, x_scale, x_zp,
 
 def fp8_linear(desc: Fp8LinearDesc, stream=None) -> None:
     check(lib().fth_b200_fp8_linear(C.byref(desc), stream or current_stream()), "fth_b200_fp8_linear")
+
+
+def fp8_linear_fusion(*, prologue=FUSE_NONE, norm_weight=None, norm_weight_dtype=BF16, norm_weight_offset=0.0, norm_epsilon=1e-6, a2=None,
+                      residual=None, w2=None, w2_scale=1.0, out2=None, n2=0, ldo2=0) -> Fp8LinearFusion:
+    f = Fp8LinearFusion()
+    f.prologue, f.norm_weight_dtype, f.norm_weight = prologue, norm_weight_dtype, ptr(norm_weight)
+    f.norm_weight_offset, f.norm_epsilon = norm_weight_offset, norm_epsilon
+    f.a2, f.residual, f.w2, f.w2_scale, f.out2, f.n2, f.ldo2 = ptr(a2), ptr(residual), ptr(w2), w2_scale, ptr(out2), n2, ldo2
+    return f
+
+
+def fp8_linear_fused(desc: Fp8LinearDesc, fusion: Fp8LinearFusion, stream=None) -> None:
+    check(lib().fth_b200_fp8_linear_fused(C.byref(desc), C.byref(fusion), stream or current_stream()), "fth_b200_fp8_linear_fused")
 
 
 def int8_linear(desc: Int8LinearDesc, stream=None) -> None:

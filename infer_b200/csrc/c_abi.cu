@@ -233,6 +233,7 @@ void BuildFp8(const fth_b200_fp8_linear_desc* d, LinearArgs* args, Fp8Epilogue* 
     args->peers.count = 0;
     args->argmax_keys = nullptr;
     args->signal = GatherSignal{};
+    args->fusion = DecoderFusion{};
     fe->ab_scale = d->w_channel_scales ? d->a_scale : d->a_scale * d->w_scale;
     fe->w_channel_scales = d->w_channel_scales;
     fe->is_gemm = d->op == FTH_B200_OP_GEMM;
@@ -257,6 +258,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
     args->peers.count = 0;
     args->argmax_keys = nullptr;
     args->signal = GatherSignal{};
+    args->fusion = DecoderFusion{};
     ie->w_scales = d->w_scales; ie->w_zps = d->w_zps; ie->per_channel = d->w_params != 1;
     ie->a_scale = d->a_scale; ie->a_zp = d->a_zp; ie->out_scale = d->out_scale; ie->out_zp = d->out_zp;
     ie->bias = d->bias; ie->bias_mode = d->bias_mode;
@@ -333,6 +335,39 @@ extern "C" int fth_b200_fp8_linear_argmax(const fth_b200_fp8_linear_desc* d, int
 extern "C" int fth_b200_fp8_lm_head_argmax(const fth_b200_fp8_linear_desc* d, int64_t* token, fth_b200_stream_t stream) {
     if (d == nullptr || d->m != 1 || !d->trans_b || d->bias_mode != FTH_B200_BIAS_NONE) return FTH_B200_ERR_INVALID;
     return Fp8LinearArgmax(d, token, 0, stream);
+}
+
+static int BuildFused(const fth_b200_fp8_linear_desc* d, const fth_b200_fp8_linear_fusion* f, LinearArgs* args, Fp8Epilogue* fe) {
+    const int rc = ValidateFp8(d);
+    if (rc != FTH_B200_OK) return rc;
+    if (f == nullptr) return FTH_B200_ERR_INVALID;
+    BuildFp8(d, args, fe);
+    DecoderFusion& fu = args->fusion;
+    fu.prologue = f->prologue;
+    fu.norm_weight = f->norm_weight; fu.norm_weight_dtype = f->norm_weight_dtype;
+    fu.norm_offset = f->norm_weight_offset; fu.norm_epsilon = f->norm_epsilon;
+    fu.a2 = f->a2;
+    fu.residual = f->residual;
+    fu.w2 = f->w2; fu.out2 = f->out2; fu.n2 = f->n2; fu.ldo2 = f->ldo2 ? f->ldo2 : f->n2;
+    fu.ab_scale2 = d->a_scale * f->w2_scale;
+    fu.n_first = d->n;
+    if (fu.prologue == 1 && (!std::isfinite(fu.norm_epsilon) || fu.norm_epsilon < 0.0f)) return FTH_B200_ERR_INVALID;
+    if (fu.w2 != nullptr && !ValidScale(f->w2_scale)) return FTH_B200_ERR_INVALID;
+    Int8Epilogue ie = {};
+    return Tcgen05FusionStatus(d->dtype, *args, *fe, ie);
+}
+
+extern "C" int fth_b200_fp8_linear_fused_supported(const fth_b200_fp8_linear_desc* d, const fth_b200_fp8_linear_fusion* f) {
+    LinearArgs args; Fp8Epilogue fe;
+    return BuildFused(d, f, &args, &fe);
+}
+
+extern "C" int fth_b200_fp8_linear_fused(const fth_b200_fp8_linear_desc* d, const fth_b200_fp8_linear_fusion* f, fth_b200_stream_t stream) {
+    ClearStaleError();
+    LinearArgs args; Fp8Epilogue fe; Int8Epilogue ie = {};
+    const int rc = BuildFused(d, f, &args, &fe);
+    if (rc != FTH_B200_OK) return rc;
+    return LaunchLinearTcgen05(d->dtype, args, fe, ie, nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int fth_b200_int8_linear_supported(const fth_b200_int8_linear_desc* d) {

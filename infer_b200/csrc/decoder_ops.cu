@@ -22,87 +22,26 @@
 #include <cmath>
 
 #include "common.cuh"
+#include "rowops.cuh"
 
 namespace fth {
 namespace {
+
+using namespace rowops;
 
 constexpr int kThreads = 128;
 
 bool Aligned16Host(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-template <int DTYPE>
-__device__ __forceinline__ float ReadFloat(const void* x, int64_t i) {
-    if constexpr (DTYPE == FTH_B200_FP32) return static_cast<const float*>(x)[i];
-    else if constexpr (DTYPE == FTH_B200_BF16) return DecodeBf16(static_cast<const uint16_t*>(x)[i]);
-    else return __half2float(static_cast<const __half*>(x)[i]);
-}
-template <int DTYPE>
-__device__ __forceinline__ void WriteFloat(void* out, int64_t i, float v) {
-    if constexpr (DTYPE == FTH_B200_FP32) static_cast<float*>(out)[i] = v;
-    else if constexpr (DTYPE == FTH_B200_BF16) static_cast<uint16_t*>(out)[i] = EncodeBf16Cast(v);
-    else static_cast<__half*>(out)[i] = __float2half_rn(v);
-}
+// One block per row.  kRowGroups groups of eight elements per thread stay in registers between the two passes when the
+// row fits (hidden <= 128 * 8 * kRowGroups); longer rows are read twice.
+constexpr int kGroups = kRowGroups;
+static_assert(kThreads == kRowThreads, "the row helpers assume 128 threads per row");
 
-// Eight consecutive elements starting at a multiple of eight (one 16-byte load for BF16 / FP16, two for FP32).
-template <int DTYPE>
-__device__ __forceinline__ void ReadEight(const void* x, int64_t i, bool vec, float (&v)[8]) {
-    if (!vec) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = ReadFloat<DTYPE>(x, i + j);
-        return;
-    }
-    if constexpr (DTYPE == FTH_B200_FP32) {
-        const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(x) + i);
-        const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(x) + i + 4);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    } else {
-        const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + i);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if constexpr (DTYPE == FTH_B200_BF16) {
-                v[2 * j] = __uint_as_float(w[j] << 16);
-                v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-            } else {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                v[2 * j] = f.x;
-                v[2 * j + 1] = f.y;
-            }
-        }
-    }
-}
-template <int DTYPE>
-__device__ __forceinline__ void WriteEight(void* out, int64_t i, bool vec, const float (&v)[8]) {
-    if (!vec) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) WriteFloat<DTYPE>(out, i + j, v[j]);
-        return;
-    }
-    if constexpr (DTYPE == FTH_B200_FP32) {
-        *reinterpret_cast<float4*>(static_cast<float*>(out) + i) = make_float4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<float4*>(static_cast<float*>(out) + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
-    } else {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if constexpr (DTYPE == FTH_B200_BF16) {
-                w[j] = EncodeBf16Cast(v[2 * j]) | (static_cast<uint32_t>(EncodeBf16Cast(v[2 * j + 1])) << 16);
-            } else {
-                const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                w[j] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-        }
-        *reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + i) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-}
-
-__device__ __forceinline__ bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
-// Sum over the block; every thread receives the total.  Fixed order (lane tree, then warps in order), so the result
-// does not depend on scheduling.
+// Sum over the block; every thread receives the total.  Fixed order (lane tree, then the four warps in order), so the
+// result does not depend on scheduling.
 __device__ __forceinline__ float BlockSum(float v, float* shared) {
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, offset));
+    v = WarpTreeSum(v);
     const int warp = threadIdx.x >> 5;
     if ((threadIdx.x & 31) == 0) shared[warp] = v;
     __syncthreads();
@@ -111,10 +50,6 @@ __device__ __forceinline__ float BlockSum(float v, float* shared) {
     for (int w = 1; w < kThreads / 32; ++w) total = __fadd_rn(total, shared[w]);
     return total;
 }
-
-// One block per row.  kGroups groups of eight elements per thread stay in registers between the two passes when the
-// row fits (hidden <= 128 * 8 * kGroups); longer rows are read twice.
-constexpr int kGroups = 4;
 
 template <int X, int W, int OUT>
 __global__ void __launch_bounds__(kThreads) RmsNormKernel(const void* __restrict__ x, const void* __restrict__ weight,
@@ -142,21 +77,7 @@ __global__ void __launch_bounds__(kThreads) RmsNormKernel(const void* __restrict
     float xv[kGroups][8];
     float sum = 0.0f;
     if (resident) {
-#pragma unroll
-        for (int g = 0; g < kGroups; ++g) {
-            const int64_t gi = threadIdx.x + static_cast<int64_t>(g) * kThreads;
-            if (gi >= groups) continue;
-            if (gi * 8 + 8 <= hidden) {
-                ReadEight<X>(xr, base + gi * 8, vec_x, xv[g]);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) sum = __fadd_rn(sum, __fmul_rn(xv[g][j], xv[g][j]));
-            } else {  // ragged last group
-                for (int64_t c = gi * 8; c < hidden; ++c) {
-                    const float v = ReadFloat<X>(xr, base + c);
-                    sum = __fadd_rn(sum, __fmul_rn(v, v));
-                }
-            }
-        }
+        sum = ThreadSumSquares<X>(xr, base, hidden, vec_x, threadIdx.x, xv);
     } else {
         for (int64_t c = threadIdx.x; c < hidden; c += kThreads) {
             const float v = ReadFloat<X>(xr, base + c);
@@ -164,7 +85,7 @@ __global__ void __launch_bounds__(kThreads) RmsNormKernel(const void* __restrict
         }
     }
     const float total = BlockSum(sum, partial);
-    const float inverse_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(hidden)), epsilon)));
+    const float inverse_rms = InverseRms(total, hidden, epsilon);
     if (resident) {
 #pragma unroll
         for (int g = 0; g < kGroups; ++g) {
@@ -190,11 +111,6 @@ __global__ void __launch_bounds__(kThreads) RmsNormKernel(const void* __restrict
     }
 }
 
-__device__ __forceinline__ float SiluValue(float x) {
-    // exp in double, rounded to FP32 once: the correctly rounded expf(-x) (overflow gives +Inf and x / Inf = 0, as on the host)
-    const float e = static_cast<float>(exp(static_cast<double>(-x)));
-    return __fdiv_rn(x, __fadd_rn(1.0f, e));
-}
 
 enum { kOpAdd = 0, kOpMul = 1, kOpSilu = 2, kOpSiluMul = 3 };
 

@@ -22,6 +22,24 @@ struct GatherSignal {
     int rank;
 };
 
+// Decoder-block operators fused around an FP8 projection with BF16 activations and BF16 outputs (single-launch cluster
+// kernel only): what runs in front of the Cast that quantises the activation, what runs behind the Cast that widens
+// the product, and a second weight that shares the activation.
+struct DecoderFusion {
+    int prologue;             // 0: none; 1: QwenRmsNorm(a) ; 2: Mul(SiLU(a), a2)
+    const void* norm_weight;  // prologue 1: [K] weight (BF16 or FP32), offset and epsilon of the node
+    int norm_weight_dtype;
+    float norm_offset, norm_epsilon;
+    const void* a2;           // prologue 2: the second BF16 input [M,K]
+    const void* residual;     // epilogue: out = Add(residual, out); BF16, laid out like out; null: none
+    const void* w2;           // second weight [K,n2] / [n2,K] on the same activation; null: none
+    float ab_scale2;          // a_scale * scale of w2
+    void* out2;               // its BF16 output [M,n2], row stride ldo2
+    int64_t n2, ldo2;
+    int64_t n_first;          // columns of the first weight (a multiple of 128 when w2 is given)
+    bool active() const { return prologue != 0 || residual != nullptr || w2 != nullptr; }
+};
+
 // Operand description common to FP8 and INT8 linear kernels.
 struct LinearArgs {
     const void* a;   // [M,K] activations (FP8 / INT8, or BF16 / FP32 when a Cast / QuantizeLinear is fused)
@@ -35,6 +53,7 @@ struct LinearArgs {
     PeerOut peers;   // replicas of the output on other GPUs (count 0: none)
     unsigned long long* argmax_keys;  // [m] running (value, index) maxima of each output row, or null
     GatherSignal signal;              // world 0: none
+    DecoderFusion fusion;             // inactive unless set by fth_b200_fp8_linear_fused
 };
 
 int LaunchLinearSimt(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie,
@@ -70,6 +89,8 @@ bool Tcgen05SelectsInEpilogue(int dtype, const LinearArgs& args, const Fp8Epilog
 // candidate receives `none_value`.
 int LaunchArgmaxFinalize(unsigned long long* keys, int64_t m, int64_t none_value, cudaStream_t stream);
 
+// FTH_B200_OK when the tensor-core family runs args.fusion (decoder-block operators fused around the projection).
+int Tcgen05FusionStatus(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie);
 // True when that launch also does the gather's step signalling itself (args.signal).
 bool Tcgen05SignalsInKernel(int dtype, const LinearArgs& args, const Fp8Epilogue& fe, const Int8Epilogue& ie);
 // The two halves of a gather step as kernels of their own, for kernel families that do not fold them in: wait until every

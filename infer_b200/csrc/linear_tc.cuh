@@ -23,6 +23,7 @@ struct TcParams {
     int64_t chunk_blocks;      // 128-byte K blocks per chunk
     int ring_stages;           // cluster kernel: weight ring depth of this launch
     int64_t k_blocks;          // ceil(K / 128)
+    int64_t p_tiles_first;     // cluster kernel with a second weight: tiles that belong to the first one (else p_tiles)
     int64_t units;             // p_tiles * q_tiles * split
     uint32_t idesc;
     int e4m3;                  // FP8 format of operands and output (1 = E4M3, 0 = E5M2)
@@ -53,8 +54,8 @@ int LaunchSwapped(bool int8, const TcGeometry& g, bool weights_mn, const CUtenso
 int LaunchPair(bool int8, bool weights_mn, const CUtensorMap& map_a, const CUtensorMap& map_w, const TcParams& p, const Fp8Epilogue& fe,
                const Int8Epilogue& ie, cudaStream_t stream);
 // M <= 32, one wave: single-launch cluster kernel.
-int LaunchCluster(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p,
-                  const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream);
+int LaunchCluster(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q,
+                  const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream);
 
 // ---- device helpers ---------------------------------------------------------------------------------------------------
 template <int THREADS>
@@ -184,17 +185,25 @@ __device__ __forceinline__ uint32_t FinishOne(const TcParams& p, const Fp8Epilog
         StoreWithPeers(p.args.peers, static_cast<int8_t*>(ie.out) + q * ie.ldo + n, r);
         return static_cast<uint8_t>(r);
     } else {
-        const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
+        const DecoderFusion& fu = p.args.fusion;
+        const bool second = fu.w2 != nullptr && n >= fu.n_first;  // a column of the second weight that shares the activation
+        const float mult = second ? fu.ab_scale2 : (fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale);
         const float t = __fmul_rn(__uint_as_float(raw), mult);
         const float y = p.out_inv != 0.0f ? __fmul_rn(t, p.out_inv) : __fdiv_rn(t, fe.out_scale);
         const uint8_t code = p.e4m3 ? Encode<FTH_B200_FP8E4M3>(y) : Encode<FTH_B200_FP8E5M2>(y);
-        const int64_t o = q * fe.ldo + n;
+        const int64_t o = second ? q * fu.ldo2 + (n - fu.n_first) : q * fe.ldo + n;
         if (fe.out_dtype == 0) { StoreWithPeers(p.args.peers, static_cast<uint8_t*>(fe.out) + o, code); return code; }
         // fused Cast behind the MatMul: the decoded code times the output scale, as BF16 or FP32
         const float d = p.e4m3 ? Decode<FTH_B200_FP8E4M3>(code) : Decode<FTH_B200_FP8E5M2>(code);
         const float v = __fmul_rn(d, fe.out_scale);
-        if (fe.out_dtype == FTH_B200_BF16) StoreWithPeers(p.args.peers, static_cast<uint16_t*>(fe.out) + o, EncodeBf16Cast(v));
-        else StoreWithPeers(p.args.peers, static_cast<float*>(fe.out) + o, v);
+        if (fe.out_dtype == FTH_B200_BF16) {
+            uint16_t bits = EncodeBf16Cast(v);
+            // fused Add node behind that Cast (the residual connection): one more BF16 rounding point
+            if (fu.residual != nullptr) bits = EncodeBf16Cast(__fadd_rn(DecodeBf16(static_cast<const uint16_t*>(fu.residual)[o]), DecodeBf16(bits)));
+            StoreWithPeers(p.args.peers, static_cast<uint16_t*>(second ? fu.out2 : fe.out) + o, bits);
+        } else {
+            StoreWithPeers(p.args.peers, static_cast<float*>(fe.out) + o, v);
+        }
         return code;
     }
 }

@@ -1,4 +1,5 @@
 #include "linear_tc.cuh"
+#include "rowops.cuh"
 
 namespace fth {
 namespace tc {
@@ -29,11 +30,12 @@ struct ClusterCfg {
     static constexpr int kExchangeBytes = kBlockP * BQ * 4;  // partials of this CTA's rows, all chunks
     static constexpr uint32_t kTmemCols = 32;
     static constexpr int kThreads = 192;
-    static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kPBytes + kQBytes + kExchangeBytes + 256;
+    static constexpr int kNormBytes = 256;                   // per-row 1 / rms of a fused QwenRmsNorm + four partial sums
+    static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kPBytes + kQBytes + kExchangeBytes + 256 + kNormBytes;
     static int StagesFor(int64_t chunk_blocks) { return chunk_blocks < kStages ? static_cast<int>(chunk_blocks) : kStages; }
     static size_t SmemFor(int64_t chunk_blocks) {
         return 1024 + static_cast<size_t>(StagesFor(chunk_blocks)) * kPBytes + static_cast<size_t>(chunk_blocks) * BQ * kBlockK +
-               kExchangeBytes + 256;
+               kExchangeBytes + 256 + kNormBytes;
     }
 };
 
@@ -81,10 +83,38 @@ __device__ __forceinline__ uint32_t ConvertFourRaw(const LinearArgs& a, const In
     }
 }
 
+// Four activation elements as FP32 from their raw load (BF16 / FP16 / FP32).
+__device__ __forceinline__ void WidenFour(int dtype, uint4 raw, float (&x)[4]) {
+    if (dtype == FTH_B200_FP32) {
+        x[0] = __uint_as_float(raw.x); x[1] = __uint_as_float(raw.y); x[2] = __uint_as_float(raw.z); x[3] = __uint_as_float(raw.w);
+    } else if (dtype == FTH_B200_BF16) {
+        x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xffff0000u);
+        x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xffff0000u);
+    } else {
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+    }
+}
+// Raw load of four consecutive elements of `dtype` at element `index` of `base` (index a multiple of 4).
+__device__ __forceinline__ uint4 LoadFourOf(const void* base, int dtype, int64_t index, bool vec) {
+    LinearArgs view = {};
+    view.a = base;
+    view.a_dtype = dtype;
+    return LoadFourRaw(view, index, vec);
+}
+// The FP8 codes of four BF16-valued activations h (the Cast node in front of the MatMul): encode(h / a_scale).
+__device__ __forceinline__ uint32_t CastFour(int e4m3, float a_scale, float a_inv, const float (&h)[4]) {
+    float y[4];
+    if (a_inv != 0.0f) { for (int i = 0; i < 4; ++i) y[i] = (h[i] != h[i]) ? h[i] : __fmul_rn(h[i], a_inv); }
+    else { for (int i = 0; i < 4; ++i) y[i] = (h[i] != h[i]) ? h[i] : __fdiv_rn(h[i], a_scale); }
+    return EncodePair(e4m3, y[0], y[1]) | (EncodePair(e4m3, y[2], y[3]) << 16);
+}
+
 template <bool INT8, bool P_MN, int BQ>
 __global__ void __launch_bounds__(ClusterCfg<BQ>::kThreads, 2)
-LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, TcParams p,
-                    Fp8Epilogue fe, Int8Epilogue ie) {
+LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_p2,
+                    const __grid_constant__ CUtensorMap map_q, TcParams p, Fp8Epilogue fe, Int8Epilogue ie) {
     using C = ClusterCfg<BQ>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -99,12 +129,15 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     uint64_t* tmem_full = q_full + 1;
     uint64_t* x_full = tmem_full + 1;  // counts the bytes peers deliver into `exchange`
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(x_full + 1);
+    float* norm_inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full) + 256);  // [<= 32] 1 / rms per activation row
+    float* norm_partial = norm_inv + 32;                                                  // [4] one partial sum per epilogue warp
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const bool convert = p.args.a_dtype != 0;
 
     if (threadIdx.x == 0) {
         TmaPrefetchDescriptor(&map_p);  // kernel parameters: safe to touch before the previous grid has finished
+        if (p.p_tiles_first < p.p_tiles) TmaPrefetchDescriptor(&map_p2);
         if (!convert) TmaPrefetchDescriptor(&map_q);
         for (int s = 0; s < stages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
         MbarInit(q_full, convert ? 128 : 1);
@@ -151,11 +184,14 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 // the first pass over the ring finds every stage free; later passes wait for the MMAs that read it
                 if (kb >= stages && !MbarWait(&empty[stage], phase ^ 1u, p.status, 20, stage)) return false;
                 const int32_t k0 = (kb_begin + kb) * kBlockK;
-                const int32_t p0 = tile * kBlockP;
+                // tiles behind the first weight's belong to the second weight that shares the activation
+                const bool second = tile >= p.p_tiles_first;
+                const CUtensorMap* map = second ? &map_p2 : &map_p;
+                const int32_t p0 = (second ? tile - static_cast<int>(p.p_tiles_first) : tile) * kBlockP;
                 uint8_t* ps = ring + static_cast<size_t>(stage) * kPBytes;
                 MbarExpectTx(&full[stage], kPBytes);
-                if constexpr (P_MN) TmaLoad2D(ps, &map_p, p0, k0, &full[stage]);
-                else TmaLoad2D(ps, &map_p, k0, p0, &full[stage]);
+                if constexpr (P_MN) TmaLoad2D(ps, map, p0, k0, &full[stage]);
+                else TmaLoad2D(ps, map, k0, p0, &full[stage]);
                 if (++stage == stages) { stage = 0; phase ^= 1u; }
                 return true;
             };
@@ -201,6 +237,26 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         // ====================== activation prologue, accumulator hand-out, reduce + epilogue ======================
         const int et = threadIdx.x - 64;  // 0 .. 127
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        const DecoderFusion& fu = p.args.fusion;
+        if (convert && nb > 0 && fu.prologue == 1) {
+            // Fused QwenRmsNorm in front of the Cast: 1 / rms of every activation row, summed in the order the stand-alone
+            // kernel uses (128 threads, their groups of eight elements in turn, lane tree, warps in order), so that the
+            // fused node returns the stand-alone node's bits.  Every CTA computes it for itself: a row is a few KB in L2.
+            const int ew = et >> 5;
+            const bool vec_row = (reinterpret_cast<uintptr_t>(p.args.a) & 15) == 0 && p.args.k % 8 == 0;
+            for (int row = 0; row < m; ++row) {
+                float xv[rowops::kRowGroups][8];
+                float s = rowops::ThreadSumSquares<FTH_B200_BF16>(p.args.a, static_cast<int64_t>(row) * p.args.k, p.args.k, vec_row, et, xv);
+                s = rowops::WarpTreeSum(s);
+                if (lane == 0) norm_partial[ew] = s;
+                EpilogueBarrier<128>();
+                if (et == 0) {
+                    const float total = __fadd_rn(__fadd_rn(__fadd_rn(norm_partial[0], norm_partial[1]), norm_partial[2]), norm_partial[3]);
+                    norm_inv[row] = rowops::InverseRms(total, p.args.k, fu.norm_epsilon);
+                }
+                EpilogueBarrier<128>();
+            }
+        }
         if (convert && nb > 0) {
             // Four consecutive K elements of one activation row per item (one 32-bit word of the swizzled tile), four
             // items per thread and round so that their loads overlap.  Rows >= m stay unwritten: they only feed
@@ -208,9 +264,12 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const int words_per_row = nb * 32;
             const int total = m * words_per_row;
             const bool vec = (reinterpret_cast<uintptr_t>(p.args.a) & 15) == 0;
+            const bool vec2 = fu.prologue == 2 ? (reinterpret_cast<uintptr_t>(fu.a2) & 15) == 0
+                                               : (reinterpret_cast<uintptr_t>(fu.norm_weight) & 15) == 0;
             for (int base = et; base < total; base += 4 * 128) {
-                uint4 raw[4];
+                uint4 raw[4], raw2[4];
                 uint32_t dst[4];
+                int rows[4];
                 bool inside[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -220,13 +279,36 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     const int kb = c >> 5, w4 = c & 31;
                     const int64_t k0 = static_cast<int64_t>(kb_begin + kb) * kBlockK + w4 * 4;
                     inside[j] = item < total && k0 < p.args.k;  // K is a multiple of 16: a group is in or out as a whole
+                    rows[j] = row;
                     dst[j] = SmemAddr(q_tiles) + kb * (BQ * kBlockK) + row * 128 + (((w4 >> 2) ^ (row & 7)) << 4) + ((w4 & 3) << 2);
                     raw[j] = inside[j] ? LoadFourRaw(p.args, static_cast<int64_t>(row) * p.args.k + k0, vec) : make_uint4(0, 0, 0, 0);
+                    raw2[j] = make_uint4(0, 0, 0, 0);
+                    if (inside[j] && fu.prologue == 1) raw2[j] = LoadFourOf(fu.norm_weight, fu.norm_weight_dtype, k0, vec2);
+                    if (inside[j] && fu.prologue == 2) raw2[j] = LoadFourOf(fu.a2, FTH_B200_BF16, static_cast<int64_t>(row) * p.args.k + k0, vec2);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     if (base + j * 128 < total) {
-                        const uint32_t word = inside[j] ? ConvertFourRaw<INT8>(p.args, ie, p.e4m3, p.a_inv, raw[j]) : 0u;
+                        uint32_t word = 0u;
+                        if (inside[j] && fu.prologue == 0) {
+                            word = ConvertFourRaw<INT8>(p.args, ie, p.e4m3, p.a_inv, raw[j]);
+                        } else if (inside[j]) {
+                            // the decoder-block node in front of the Cast, with its own BF16 rounding point(s)
+                            float x[4], y[4], h[4];
+                            WidenFour(FTH_B200_BF16, raw[j], x);
+                            WidenFour(fu.prologue == 1 ? fu.norm_weight_dtype : FTH_B200_BF16, raw2[j], y);
+                            if (fu.prologue == 1) {
+                                const float inv = norm_inv[rows[j]];
+                                for (int i = 0; i < 4; ++i)
+                                    h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(__fmul_rn(x[i], inv), __fadd_rn(y[i], fu.norm_offset))));
+                            } else {
+                                for (int i = 0; i < 4; ++i) {
+                                    const float s = DecodeBf16(EncodeBf16Cast(rowops::SiluValue(x[i])));  // SiLU node
+                                    h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(s, y[i])));                 // Mul node
+                                }
+                            }
+                            word = CastFour(p.e4m3, p.args.a_scale, p.a_inv, h);
+                        }
                         asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst[j]), "r"(word) : "memory");
                     }
                 }
@@ -333,7 +415,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 }
 
 template <bool INT8, bool P_MN, int BQ>
-int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p_in,
+int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q, const TcParams& p_in,
                        const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     TcParams p = p_in;
     p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks);
@@ -353,28 +435,28 @@ int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUte
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    if (cudaLaunchKernelEx(&cfg, kernel, map_p, map_q, p, fe, ie) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    if (cudaLaunchKernelEx(&cfg, kernel, map_p, map_p2, map_q, p, fe, ie) != cudaSuccess) return FTH_B200_ERR_CUDA;
     NoteLaunch("tcgen05");
     return CheckLaunch();
 }
 
 template <bool INT8>
-int LaunchClusterFor(const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p,
-                  const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
+int LaunchClusterFor(const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q,
+                  const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     if (g.bq == 16) {
-        return weights_mn ? LaunchClusterTyped<INT8, true, 16>(g, map_p, map_q, p, fe, ie, stream)
-                          : LaunchClusterTyped<INT8, false, 16>(g, map_p, map_q, p, fe, ie, stream);
+        return weights_mn ? LaunchClusterTyped<INT8, true, 16>(g, map_p, map_p2, map_q, p, fe, ie, stream)
+                          : LaunchClusterTyped<INT8, false, 16>(g, map_p, map_p2, map_q, p, fe, ie, stream);
     }
-    return weights_mn ? LaunchClusterTyped<INT8, true, 32>(g, map_p, map_q, p, fe, ie, stream)
-                      : LaunchClusterTyped<INT8, false, 32>(g, map_p, map_q, p, fe, ie, stream);
+    return weights_mn ? LaunchClusterTyped<INT8, true, 32>(g, map_p, map_p2, map_q, p, fe, ie, stream)
+                      : LaunchClusterTyped<INT8, false, 32>(g, map_p, map_p2, map_q, p, fe, ie, stream);
 }
 
 }  // namespace
 
-int LaunchCluster(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p,
-                  const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
-    return int8 ? LaunchClusterFor<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
-                : LaunchClusterFor<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
+int LaunchCluster(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q,
+                  const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
+    return int8 ? LaunchClusterFor<true>(g, weights_mn, map_p, map_p2, map_q, p, fe, ie, stream)
+                : LaunchClusterFor<false>(g, weights_mn, map_p, map_p2, map_q, p, fe, ie, stream);
 }
 
 }  // namespace tc

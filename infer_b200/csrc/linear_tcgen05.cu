@@ -33,6 +33,8 @@ float ExactReciprocal(float s) {
 }
 
 int SwapBlockQ(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
+// longest row a fused QwenRmsNorm keeps in registers (128 threads x 4 groups x 8 elements)
+int64_t rowops_max_hidden() { return 4096; }
 
 
 namespace {
@@ -41,7 +43,9 @@ TcGeometry GeometryFor(const LinearArgs& a) {
     TcGeometry g;
     g.swap = a.m <= 128;
     g.bq = g.swap ? SwapBlockQ(a.m) : 256;
-    g.p_total = g.swap ? a.n : a.m;
+    // a second weight that shares the activation (decoder-block fusion) lines its columns up behind the first one's
+    const int64_t n_all = a.n + (a.fusion.w2 != nullptr ? a.fusion.n2 : 0);
+    g.p_total = g.swap ? n_all : a.m;
     g.q_total = g.swap ? a.m : a.n;
     g.p_tiles = (g.p_total + kBlockP - 1) / kBlockP;
     g.q_tiles = (g.q_total + g.bq - 1) / g.bq;
@@ -59,8 +63,9 @@ TcGeometry GeometryFor(const LinearArgs& a) {
     if (g.swap && g.bq <= 32 && g.q_tiles == 1 && g.chunk_blocks <= kClusterQBlocks) {
         int c = 1;
         while (c < g.split) c *= 2;
-        // more than one wave of CTAs: the persistent kernel keeps its ring full across tiles and is faster (measured)
-        if (g.p_tiles * c <= static_cast<int64_t>(SmCount()) * 2) g.cluster = c;
+        // more than one wave of CTAs: the persistent kernel keeps its ring full across tiles and is faster (measured).
+        // Decoder-block fusions exist in this kernel only; its CTAs are small (several fit an SM), so twice the limit.
+        if (g.p_tiles * c <= static_cast<int64_t>(SmCount()) * (a.fusion.active() ? 4 : 2)) g.cluster = c;
     }
     return g;
 }
@@ -127,6 +132,26 @@ bool Tcgen05StoresToPeers(int dtype, const LinearArgs& a, const Fp8Epilogue& fe,
     return !GeometryFor(a).swap && DirectEpilogue(int8, fe, ie) && (int8 ? ie.out_dtype : fe.out_dtype) == 0;
 }
 
+// QwenRmsNorm / SiLU * Mul in front, residual Add behind, a second weight beside: BF16 in, FP8 product, BF16 out, on the
+// single-launch cluster kernel only.  FTH_B200_OK when LaunchLinearTcgen05 will run args.fusion.
+int Tcgen05FusionStatus(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
+    if (!Tcgen05Supported(dtype, a)) return FTH_B200_ERR_UNSUPPORTED;
+    const DecoderFusion& fu = a.fusion;
+    const TcGeometry g = GeometryFor(a);
+    if (dtype == FTH_B200_INT8 || g.cluster == 0 || a.a_dtype != FTH_B200_BF16 || fe.out_dtype != FTH_B200_BF16 || !DirectEpilogue(false, fe, ie) ||
+        fe.w_channel_scales != nullptr || a.argmax_keys != nullptr || a.peers.count != 0) return FTH_B200_ERR_UNSUPPORTED;
+    if (fu.prologue < 0 || fu.prologue > 2) return FTH_B200_ERR_INVALID;
+    if (fu.prologue == 1 && fu.norm_weight == nullptr) return FTH_B200_ERR_INVALID;
+    if (fu.prologue == 1 && (fu.norm_weight_dtype != FTH_B200_BF16 && fu.norm_weight_dtype != FTH_B200_FP32)) return FTH_B200_ERR_UNSUPPORTED;
+    if (fu.prologue == 1 && a.k > rowops_max_hidden()) return FTH_B200_ERR_UNSUPPORTED;
+    if (fu.prologue == 2 && fu.a2 == nullptr) return FTH_B200_ERR_INVALID;
+    if (fu.w2 != nullptr) {
+        if (fu.n2 <= 0 || fu.out2 == nullptr || fu.ldo2 < fu.n2) return FTH_B200_ERR_INVALID;
+        if (a.n % kBlockP != 0 || reinterpret_cast<uintptr_t>(fu.w2) % 16 != 0 || (!a.trans_b && fu.n2 % 16 != 0)) return FTH_B200_ERR_UNSUPPORTED;
+    }
+    return FTH_B200_OK;
+}
+
 bool Tcgen05SignalsInKernel(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
     // exactly the launches whose own epilogue writes the peers' buffers: their last block knows when all stores are out
     return Tcgen05StoresToPeers(dtype, a, fe, ie);
@@ -148,6 +173,10 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     const bool int8 = dtype == FTH_B200_INT8;
     LinearArgs a = a_in;
     void* scratch = scratch_in;
+    if (a.fusion.active()) {
+        const int rc = Tcgen05FusionStatus(dtype, a, fe, ie);
+        if (rc != FTH_B200_OK) return rc;
+    }
     if (a.a_dtype != 0 && g.cluster == 0) {
         int rc;
         if (int8) rc = LaunchQuantizePerTensor(a.a_dtype, a.a, ie.a_scale, ie.a_zp, static_cast<int8_t*>(scratch_in), a.m * a.k, stream);
@@ -170,6 +199,12 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     if (!ok) return FTH_B200_ERR_CUDA;
     map_p = g.swap ? map_w : map_a;
     map_q = g.swap ? map_a : map_w;
+    CUtensorMap map_p2 = map_p;
+    if (a.fusion.w2 != nullptr) {
+        if (weights_mn) ok = CachedMap(&map_p2, a.fusion.w2, static_cast<uint64_t>(a.fusion.n2), static_cast<uint64_t>(a.k), 128, 128);
+        else ok = CachedMap(&map_p2, a.fusion.w2, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.fusion.n2), 128, kBlockP);
+        if (!ok) return FTH_B200_ERR_CUDA;
+    }
 
     TcParams p;
     p.args = a;
@@ -177,6 +212,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     p.p_total = g.p_total; p.q_total = g.q_total; p.p_tiles = g.p_tiles; p.q_tiles = g.q_tiles;
     p.ring_stages = 0;
     p.split = g.split; p.chunk_blocks = g.chunk_blocks; p.k_blocks = g.k_blocks; p.units = g.units;
+    p.p_tiles_first = a.fusion.w2 != nullptr ? a.n / kBlockP : g.p_tiles;
     p.p_pad = g.p_pad;
     p.e4m3 = dtype == FTH_B200_FP8E4M3;
     if (int8) p.fast = ie.bias_mode == FTH_B200_BIAS_NONE && ie.out_dtype == 0 && !(ie.is_gemm && (ie.alpha != 1.0f || ie.beta != 1.0f));
@@ -191,7 +227,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     const bool p_mn = g.swap && weights_mn;
     const bool q_mn = !g.swap && weights_mn;
     p.idesc = umma::InstrDesc(int8 ? 2u : 1u, fmt, fmt, p_mn, q_mn, kBlockP, static_cast<uint32_t>(g.bq));
-    if (g.cluster > 0) return LaunchCluster(int8, g, weights_mn, map_p, map_q, p, fe, ie, stream);
+    if (g.cluster > 0) return LaunchCluster(int8, g, weights_mn, map_p, map_p2, map_q, p, fe, ie, stream);
     if (!g.swap) {
         // CTA pairs: each CTA stages 128 activation rows and 128 weight columns of a 256 x 256 tile
         CUtensorMap map_w_half = map_w;

@@ -2,8 +2,9 @@
 GPU run.  Hidden 1024, intermediate 3584; per layer q/k/v/o (1024x1024) chained, then gate/up (1024x3584), SiLU * up,
 down (3584x1024); every projection is Cast(BF16 -> E5M2) -> MatMul(E5M2) -> Cast(E5M2 -> BF16) with per-tensor
 power-of-two scales; BF16 residual adds; RMSNorm in FP32 with BF16 in/out (src/kernel/common/qwen_rms_norm.cc:71-95,
-weight offset 1).  The neighbours of the projections (RMSNorm, Add, SiLU, Mul) are not part of the path under
-test: both runs compute them with the same numpy code below, so any difference comes from the projections."""
+weight offset 1).  run_stack drives the stack with a `project` callback and the neighbours (QwenRmsNorm, Add, SiLU,
+Mul) computed by the CPU oracle — the restatement of the reference's Common kernels pinned in
+tests/test_oracle_decoder_ops.py; tests/test_gpu_decoder_step.py runs the whole step on the GPU against it."""
 from __future__ import annotations
 
 import numpy as np
@@ -44,19 +45,19 @@ def make_weights(encode_e5m2, seed=0xFEA70004, layers=LAYERS):
 
 
 def rmsnorm(x_bits, g_bits):
-    x = from_bf16(x_bits)
-    inv = np.float32(1.0) / np.sqrt((x * x).sum(axis=1, keepdims=True, dtype=np.float32) / np.float32(x.shape[1]) + EPS)
-    return to_bf16(x * inv.astype(np.float32) * (from_bf16(g_bits) + np.float32(1.0)))
+    """QwenRmsNorm node: the pinned restatement of the reference's Common kernel (weight offset 1, BF16 in / out)."""
+    import oracle as O
+    return O.qwen_rms_norm(O.BF16, x_bits, O.BF16, g_bits, 1.0, float(EPS), O.BF16)
 
 
 def add(a_bits, b_bits):
-    return to_bf16(from_bf16(a_bits) + from_bf16(b_bits))
+    import oracle as O
+    return O.binary(0, O.BF16, a_bits, b_bits)
 
 
 def silu_mul(g_bits, u_bits):
-    g = from_bf16(g_bits)
-    s = to_bf16(g / (np.float32(1.0) + np.exp(-g)))   # SiLU node, BF16 out
-    return to_bf16(from_bf16(s) * from_bf16(u_bits))     # Mul node, BF16 out
+    import oracle as O
+    return O.binary(1, O.BF16, O.silu(O.BF16, g_bits), u_bits)   # SiLU node then Mul node, BF16 out each
 
 
 def run_stack(project, weights, x_bits, trace=None):

@@ -37,7 +37,8 @@ def test_struct_layouts_match_the_c_compiler():
 #include "fth_b200.h"
 #define P(T, F) printf(#T "." #F " %zu\n", offsetof(T, F))
 int main(void) {
-  printf("sizeof.fp8 %zu\nsizeof.int8 %zu\nsizeof.conv %zu\n", sizeof(fth_b200_fp8_linear_desc), sizeof(fth_b200_int8_linear_desc), sizeof(fth_b200_int8_conv2d_desc));
+  printf("sizeof.fp8 %zu\nsizeof.int8 %zu\nsizeof.conv %zu\nsizeof.fusion %zu\n", sizeof(fth_b200_fp8_linear_desc), sizeof(fth_b200_int8_linear_desc), sizeof(fth_b200_int8_conv2d_desc), sizeof(fth_b200_fp8_linear_fusion));
+  P(fth_b200_fp8_linear_fusion, norm_weight); P(fth_b200_fp8_linear_fusion, norm_epsilon); P(fth_b200_fp8_linear_fusion, w2_scale); P(fth_b200_fp8_linear_fusion, ldo2);
   P(fth_b200_fp8_linear_desc, a); P(fth_b200_fp8_linear_desc, ldo); P(fth_b200_fp8_linear_desc, w_channel_scales);
   P(fth_b200_fp8_linear_desc, workspace); P(fth_b200_fp8_linear_desc, variant); P(fth_b200_fp8_linear_desc, gather_out);
   P(fth_b200_fp8_linear_desc, gather_world); P(fth_b200_fp8_linear_desc, gather_flags); P(fth_b200_int8_linear_desc, gather_flags);
@@ -54,7 +55,8 @@ int main(void) {
         subprocess.check_call(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
         got = dict(line.rsplit(" ", 1) for line in subprocess.check_output([exe], text=True).strip().splitlines())
     py = {"fth_b200_fp8_linear_desc": B.Fp8LinearDesc, "fth_b200_int8_linear_desc": B.Int8LinearDesc,
-          "fth_b200_int8_conv2d_desc": B.Int8Conv2dDesc}
+          "fth_b200_int8_conv2d_desc": B.Int8Conv2dDesc, "fth_b200_fp8_linear_fusion": B.Fp8LinearFusion}
+    assert int(got["sizeof.fusion"]) == C.sizeof(B.Fp8LinearFusion)
     assert int(got["sizeof.fp8"]) == C.sizeof(B.Fp8LinearDesc)
     assert int(got["sizeof.int8"]) == C.sizeof(B.Int8LinearDesc)
     assert int(got["sizeof.conv"]) == C.sizeof(B.Int8Conv2dDesc)

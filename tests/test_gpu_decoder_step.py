@@ -1,0 +1,100 @@
+"""GPU: a whole decode / prefill-chunk step of the synthetic decoder stack on the device — projections AND the operators
+between them — against the CPU oracle, and the six-launch-per-layer fused form against the twelve-launch form.
+
+* fused == unfused, byte for byte: fth_b200_fp8_linear_fused keeps every rounding point of the nodes it absorbs
+  (QwenRmsNorm, SiLU, Mul, Add, both Casts) and sums the squares of a row in the stand-alone kernel's order.
+* against the oracle (reference Common kernels for every node, tests/decoder_stack.py): cosine of the final hidden state
+  >= 0.999 over all 24 layers, as tools/compare_qwen_logits.py:41-58 computes it."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import infer_b200 as B
+import oracle as O
+from infer_b200.decoder_step import DecoderStep
+from tests import decoder_stack as D
+from tests.gpu_helpers import dev
+
+pytestmark = pytest.mark.gpu
+
+
+def device_layers(torch, weights):
+    layers = []
+    for layer in weights:
+        d = {}
+        for name, _, _ in D.PROJ:
+            codes, scale = layer[name]
+            d[name] = dev(torch, codes)
+            d[name + "_scale"] = scale
+        d["g1"] = dev(torch, layer["g1"].view(np.int16))
+        d["g2"] = dev(torch, layer["g2"].view(np.int16))
+        layers.append(d)
+    return layers
+
+
+def oracle_project(h_bits, weight):
+    codes, sw = weight
+    a = O.cast(O.BF16, h_bits, 1.0, O.E5M2, D.ACT_SCALE).reshape(h_bits.shape)
+    y = O.fp8_linear(O.OP_MATMUL, O.E5M2, a, D.ACT_SCALE, codes, sw, D.OUT_SCALE)
+    return O.cast(O.E5M2, y, D.OUT_SCALE, O.BF16, 1.0).reshape(y.shape)
+
+
+def run_device(torch, layers, x0, m, fused):
+    step = DecoderStep(torch, layers, m, D.HIDDEN, D.INTER, D.ACT_SCALE, D.OUT_SCALE, fp8_dtype=B.E5M2, epsilon=float(D.EPS), fused=fused)
+    step.x.copy_(dev(torch, x0.view(np.int16)))
+    step.run()
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
+    return step.result.cpu().numpy().view(np.uint16), step
+
+
+@pytest.fixture(scope="module")
+def stack_weights():
+    return D.make_weights(lambda x: O.fp8_encode(O.E5M2, x))
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_fused_step_equals_node_by_node_step(cuda, stack_weights, m):
+    layers = device_layers(cuda, stack_weights[:3])
+    rng = np.random.default_rng(300 + m)
+    x0 = D.to_bf16(rng.standard_normal((m, D.HIDDEN)).astype(np.float32))
+    plain, step_plain = run_device(cuda, layers, x0, m, fused=False)
+    fused, step_fused = run_device(cuda, layers, x0, m, fused=True)
+    assert step_plain.launches == 12 * 3 and step_fused.launches == 6 * 3
+    assert np.array_equal(fused, plain), f"{int((fused != plain).sum())} of {plain.size} BF16 outputs differ"
+
+
+@pytest.mark.parametrize("m", [1, 16])
+def test_whole_step_on_device_matches_oracle(cuda, stack_weights, m):
+    layers = device_layers(cuda, stack_weights)
+    rng = np.random.default_rng(100 + m)
+    x0 = D.to_bf16(rng.standard_normal((m, D.HIDDEN)).astype(np.float32))
+    want = D.from_bf16(D.run_stack(oracle_project, stack_weights, x0)).astype(np.float64)
+    got_bits, step = run_device(cuda, layers, x0, m, fused=True)
+    got = D.from_bf16(got_bits).astype(np.float64)
+    assert step.launches == 6 * D.LAYERS
+    assert np.isfinite(got).all() and np.isfinite(want).all()
+    cos = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want)))
+    rmse = float(np.sqrt(((got - want) ** 2).mean()))
+    print(f"M={m}: whole step on device, {step.launches} launches: cosine {cos:.6f} rmse {rmse:.4g} max|err| {np.abs(got - want).max():.4g} "
+          f"argmax equal {bool((got.argmax(axis=1) == want.argmax(axis=1)).all())}")
+    assert cos >= 0.999
+
+
+def test_fused_call_rejections(cuda):
+    torch = cuda
+    a = torch.zeros((1, 1024), dtype=torch.int16, device="cuda")
+    w = torch.zeros((1024, 1024), dtype=torch.uint8, device="cuda")
+    out = torch.zeros((1, 1024), dtype=torch.int16, device="cuda")
+    base = dict(dtype=B.E5M2, op=B.OP_MATMUL, m=1, k=1024, n=1024, a=a, w=w, out=out, a_scale=1.0, w_scale=1.0, out_scale=1.0)
+    ok = B.fp8_linear_desc(a_dtype=B.BF16, out_dtype=B.BF16, **base)
+    sup = B.lib().fth_b200_fp8_linear_fused_supported
+    f = B.fp8_linear_fusion(residual=out)
+    assert sup(C.byref(ok), C.byref(f)) == B.OK
+    assert sup(C.byref(B.fp8_linear_desc(**base)), C.byref(f)) == B.ERR_UNSUPPORTED                       # FP8 in / out: nothing to fuse around
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(prologue=B.FUSE_RMS_NORM))) == B.ERR_INVALID       # no norm weight
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(prologue=B.FUSE_SILU_MUL))) == B.ERR_INVALID       # no second input
+    big = B.fp8_linear_desc(a_dtype=B.BF16, out_dtype=B.BF16, **dict(base, m=64))
+    assert sup(C.byref(big), C.byref(f)) == B.ERR_UNSUPPORTED                                             # not a decode-sized shape
+    assert sup(C.byref(ok), None) == B.ERR_INVALID
