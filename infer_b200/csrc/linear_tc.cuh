@@ -29,6 +29,7 @@ struct TcParams {
     int e4m3;                  // FP8 format of operands and output (1 = E4M3, 0 = E5M2)
     int fast;                  // 1: no bias, alpha = beta = 1, native output dtype → vectorised epilogue
     int fast4;                 // same for the four-channel epilogue, which also covers a fused output Cast (FP8)
+    int decoder;               // cluster kernel: the decoder-block form (BF16 -> FP8 product -> BF16, per-tensor scales, one GPU)
     float a_inv, out_inv;      // exact reciprocals of the activation / output scale (powers of two), else 0
     void* scratch;             // [split][q_total][p_pad] partial accumulators
     int64_t p_pad;
@@ -185,22 +186,17 @@ __device__ __forceinline__ uint32_t FinishOne(const TcParams& p, const Fp8Epilog
         StoreWithPeers(p.args.peers, static_cast<int8_t*>(ie.out) + q * ie.ldo + n, r);
         return static_cast<uint8_t>(r);
     } else {
-        const DecoderFusion& fu = p.args.fusion;
-        const bool second = fu.w2 != nullptr && n >= fu.n_first;  // a column of the second weight that shares the activation
-        const float mult = second ? fu.ab_scale2 : (fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale);
+        const float mult = fe.w_channel_scales ? fe.ab_scale * fe.w_channel_scales[n] : fe.ab_scale;
         const float t = __fmul_rn(__uint_as_float(raw), mult);
         const float y = p.out_inv != 0.0f ? __fmul_rn(t, p.out_inv) : __fdiv_rn(t, fe.out_scale);
         const uint8_t code = p.e4m3 ? Encode<FTH_B200_FP8E4M3>(y) : Encode<FTH_B200_FP8E5M2>(y);
-        const int64_t o = second ? q * fu.ldo2 + (n - fu.n_first) : q * fe.ldo + n;
+        const int64_t o = q * fe.ldo + n;
         if (fe.out_dtype == 0) { StoreWithPeers(p.args.peers, static_cast<uint8_t*>(fe.out) + o, code); return code; }
         // fused Cast behind the MatMul: the decoded code times the output scale, as BF16 or FP32
         const float d = p.e4m3 ? Decode<FTH_B200_FP8E4M3>(code) : Decode<FTH_B200_FP8E5M2>(code);
         const float v = __fmul_rn(d, fe.out_scale);
         if (fe.out_dtype == FTH_B200_BF16) {
-            uint16_t bits = EncodeBf16Cast(v);
-            // fused Add node behind that Cast (the residual connection): one more BF16 rounding point
-            if (fu.residual != nullptr) bits = EncodeBf16Cast(__fadd_rn(DecodeBf16(static_cast<const uint16_t*>(fu.residual)[o]), DecodeBf16(bits)));
-            StoreWithPeers(p.args.peers, static_cast<uint16_t*>(second ? fu.out2 : fe.out) + o, bits);
+            StoreWithPeers(p.args.peers, static_cast<uint16_t*>(fe.out) + o, EncodeBf16Cast(v));
         } else {
             StoreWithPeers(p.args.peers, static_cast<float*>(fe.out) + o, v);
         }

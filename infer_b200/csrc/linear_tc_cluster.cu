@@ -30,7 +30,7 @@ struct ClusterCfg {
     static constexpr int kExchangeBytes = kBlockP * BQ * 4;  // partials of this CTA's rows, all chunks
     static constexpr uint32_t kTmemCols = 32;
     static constexpr int kThreads = 192;
-    static constexpr int kNormBytes = 256;                   // per-row 1 / rms of a fused QwenRmsNorm + four partial sums
+    static constexpr int kNormBytes = 768;                   // a fused QwenRmsNorm: 1 / rms per row + four partial sums per row
     static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kPBytes + kQBytes + kExchangeBytes + 256 + kNormBytes;
     static int StagesFor(int64_t chunk_blocks) { return chunk_blocks < kStages ? static_cast<int>(chunk_blocks) : kStages; }
     static size_t SmemFor(int64_t chunk_blocks) {
@@ -96,13 +96,6 @@ __device__ __forceinline__ void WidenFour(int dtype, uint4 raw, float (&x)[4]) {
         x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
     }
 }
-// Raw load of four consecutive elements of `dtype` at element `index` of `base` (index a multiple of 4).
-__device__ __forceinline__ uint4 LoadFourOf(const void* base, int dtype, int64_t index, bool vec) {
-    LinearArgs view = {};
-    view.a = base;
-    view.a_dtype = dtype;
-    return LoadFourRaw(view, index, vec);
-}
 // The FP8 codes of four BF16-valued activations h (the Cast node in front of the MatMul): encode(h / a_scale).
 __device__ __forceinline__ uint32_t CastFour(int e4m3, float a_scale, float a_inv, const float (&h)[4]) {
     float y[4];
@@ -111,7 +104,24 @@ __device__ __forceinline__ uint32_t CastFour(int e4m3, float a_scale, float a_in
     return EncodePair(e4m3, y[0], y[1]) | (EncodePair(e4m3, y[2], y[3]) << 16);
 }
 
-template <bool INT8, bool P_MN, int BQ>
+// decode(code) for the fused Cast behind the MatMul.  Finite codes widen exactly through FP16 in hardware; Inf / NaN
+// codes take the software path, whose NaN pattern is the reference's.
+__device__ __forceinline__ float DecodeFast(int e4m3, uint32_t code) {
+    const uint32_t mag = code & 0x7fu;
+    if (e4m3 ? mag == 0x7fu : mag >= 0x7cu)
+        return e4m3 ? Decode<FTH_B200_FP8E4M3>(static_cast<uint8_t>(code)) : Decode<FTH_B200_FP8E5M2>(static_cast<uint8_t>(code));
+    const uint16_t in = static_cast<uint16_t>(code & 0xffu);
+    uint32_t pair;
+    if (e4m3) asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"(in));
+    else asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(pair) : "h"(in));
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(pair & 0xffffu)));
+}
+
+// DEC: the decoder-block form — FP8 product of BF16 activations, BF16 out, per-tensor scales, no bias, no peers, no
+// selection — with the activation prologue and the finishing step written out for exactly that case (these launches
+// are latency-bound: every instruction between the producer's last store and this kernel's own counts), and with the
+// operators a decoder block puts around the projection fused in (DecoderFusion).
+template <bool INT8, bool P_MN, int BQ, bool DEC>
 __global__ void __launch_bounds__(ClusterCfg<BQ>::kThreads, 2)
 LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_p2,
                     const __grid_constant__ CUtensorMap map_q, TcParams p, Fp8Epilogue fe, Int8Epilogue ie) {
@@ -130,7 +140,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     uint64_t* x_full = tmem_full + 1;  // counts the bytes peers deliver into `exchange`
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(x_full + 1);
     float* norm_inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(full) + 256);  // [<= 32] 1 / rms per activation row
-    float* norm_partial = norm_inv + 32;                                                  // [4] one partial sum per epilogue warp
+    float* norm_partial = norm_inv + 32;                                                  // [<= 32][4] one partial sum per row and epilogue warp
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const bool convert = p.args.a_dtype != 0;
@@ -164,16 +174,11 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     if (nb > static_cast<int>(p.chunk_blocks)) nb = static_cast<int>(p.chunk_blocks);
     if (nb < 0) nb = 0;  // ranks beyond the split have no K range
     const int m = static_cast<int>(p.q_total);
-    // Kernel parameters live in constant memory and every first touch of a line costs a few hundred cycles: read
-    // what the roles need now, while the previous kernel in the stream may still be running.
-    {
-        const int64_t out_bits = reinterpret_cast<int64_t>(INT8 ? ie.out : fe.out);
-        const int64_t ldo_bits = INT8 ? ie.ldo : fe.ldo;
-        asm volatile("" ::"r"(p.split), "l"(p.p_total), "r"(p.fast4), "r"(p.e4m3), "r"(p.idesc), "l"(p.args.k), "l"(p.args.a),
-                     "r"(p.args.a_dtype), "f"(p.args.a_scale), "f"(fe.out_scale), "f"(fe.ab_scale), "l"(fe.w_channel_scales),
-                     "r"(fe.out_dtype), "l"(out_bits), "l"(ldo_bits), "f"(ie.a_scale), "f"(ie.out_scale), "l"(ie.w_scales),
-                     "l"(p.status), "f"(p.a_inv), "f"(p.out_inv));
-    }
+    // Every parameter line is pulled into the constant cache now, while the previous kernel in the stream may still
+    // be running.
+    TouchConstantLines(p);
+    if constexpr (INT8) TouchConstantLines(ie);
+    else TouchConstantLines(fe);
 
     if (warp == 0) {
         // ================================ TMA producer ================================
@@ -236,27 +241,172 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     } else {
         // ====================== activation prologue, accumulator hand-out, reduce + epilogue ======================
         const int et = threadIdx.x - 64;  // 0 .. 127
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        const DecoderFusion& fu = p.args.fusion;
-        if (convert && nb > 0 && fu.prologue == 1) {
-            // Fused QwenRmsNorm in front of the Cast: 1 / rms of every activation row, summed in the order the stand-alone
-            // kernel uses (128 threads, their groups of eight elements in turn, lane tree, warps in order), so that the
-            // fused node returns the stand-alone node's bits.  Every CTA computes it for itself: a row is a few KB in L2.
-            const int ew = et >> 5;
-            const bool vec_row = (reinterpret_cast<uintptr_t>(p.args.a) & 15) == 0 && p.args.k % 8 == 0;
-            for (int row = 0; row < m; ++row) {
-                float xv[rowops::kRowGroups][8];
-                float s = rowops::ThreadSumSquares<FTH_B200_BF16>(p.args.a, static_cast<int64_t>(row) * p.args.k, p.args.k, vec_row, et, xv);
-                s = rowops::WarpTreeSum(s);
-                if (lane == 0) norm_partial[ew] = s;
-                EpilogueBarrier<128>();
-                if (et == 0) {
-                    const float total = __fadd_rn(__fadd_rn(__fadd_rn(norm_partial[0], norm_partial[1]), norm_partial[2]), norm_partial[3]);
-                    norm_inv[row] = rowops::InverseRms(total, p.args.k, fu.norm_epsilon);
+        [[maybe_unused]] const DecoderFusion& fu = p.args.fusion;
+        // DEC: the residual values of this thread's first two outputs, fetched right behind the dependency wait
+        [[maybe_unused]] uint16_t residual_early[2] = {0, 0};
+        if constexpr (DEC) {
+            // ------------------------------------------------------------------------------------------------
+            // Everything that does not depend on the producer runs in front of the wait: the places of this thread's
+            // first four items and, when nothing in the stream writes them, the norm weights those items need.
+            // Behind the wait the activation loads go out first, four per thread and with no branch between them.
+            // ------------------------------------------------------------------------------------------------
+            const uint16_t* act = static_cast<const uint16_t*>(p.args.a);
+            const int K = static_cast<int>(p.args.k);
+            const int prologue = fu.prologue;
+            const int words_per_row = nb * 32;
+            const int total = m * words_per_row;
+            const uint32_t q_base = SmemAddr(q_tiles);
+            int rows[4], k0[4];
+            uint32_t dst[4];
+            bool inside[4];
+            uint2 raw[4];
+            uint4 raw2[4];
+            auto locate = [&](int base) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int item = base + j * 128;
+                    const int row = item / words_per_row;
+                    const int c = item - row * words_per_row;
+                    const int kb = c >> 5, w4 = c & 31;
+                    k0[j] = (kb_begin + kb) * kBlockK + w4 * 4;
+                    inside[j] = item < total && k0[j] < K;  // K is a multiple of 16: a group is in or out as a whole
+                    rows[j] = row;
+                    dst[j] = q_base + kb * (BQ * kBlockK) + row * 128 + (((w4 >> 2) ^ (row & 7)) << 4) + ((w4 & 3) << 2);
+                }
+            };
+            auto load_norm_weights = [&]() {
+                if (fu.norm_weight_dtype == FTH_B200_FP32) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        raw2[j] = inside[j] ? *reinterpret_cast<const uint4*>(static_cast<const float*>(fu.norm_weight) + k0[j]) : make_uint4(0, 0, 0, 0);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint2 t = inside[j] ? *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(fu.norm_weight) + k0[j]) : make_uint2(0, 0);
+                        raw2[j] = make_uint4(t.x, t.y, 0, 0);
+                    }
+                }
+            };
+            auto load_activations = [&]() {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) raw[j] = inside[j] ? *reinterpret_cast<const uint2*>(act + rows[j] * K + k0[j]) : make_uint2(0, 0);
+                if (prologue == 2) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint2 t = inside[j] ? *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(fu.a2) + rows[j] * K + k0[j]) : make_uint2(0, 0);
+                        raw2[j] = make_uint4(t.x, t.y, 0, 0);
+                    }
+                }
+            };
+            const bool weights_early = prologue == 1 && p.args.w_static != 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) raw2[j] = make_uint4(0, 0, 0, 0);
+            if (nb > 0) {
+                locate(et);
+                if (weights_early) load_norm_weights();
+            }
+            // the first two outputs this thread will finish (see the finishing loop below)
+            int64_t early_at[2] = {-1, -1};
+            if (fu.residual != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int item = i * 128 + et;
+                    const int q = item >> lshift, r = item & (rows_per_cta - 1);
+                    const int64_t n = static_cast<int64_t>(tile) * kBlockP + (static_cast<int64_t>(rank) << lshift) + r;
+                    if (item < (m << lshift) && n < p.p_total) early_at[i] = q * fe.ldo + n;  // a residual goes with the first weight only
+                }
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (nb > 0) load_activations();
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                if (early_at[i] >= 0) residual_early[i] = static_cast<const uint16_t*>(fu.residual)[early_at[i]];
+            if (nb > 0 && prologue == 1) {
+                // Fused QwenRmsNorm in front of the Cast: 1 / rms of every activation row, with the sum of squares added in
+                // the order of the stand-alone kernel (128 threads that each add their groups of eight elements in turn, a
+                // lane tree per warp, the four warps in order), so that the fused node returns the stand-alone node's bits.
+                // One warp takes a whole row here: lane l plays the threads l, l + 32, l + 64, l + 96 of that kernel, so
+                // the rows need no barrier between them and a row's loads are all in flight together.  Every CTA computes
+                // every row for itself: a row is a few KB in L2.
+                const int ew = et >> 5;
+                const int groups = K >> 3;
+                for (int row = ew; row < m; row += 4) {
+                    const uint16_t* xr = act + row * K;
+                    float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int g = 0; g < rowops::kRowGroups; ++g) {
+                        if (g * rowops::kRowThreads >= groups) break;  // uniform
+                        uint4 v[4];
+#pragma unroll
+                        for (int vt = 0; vt < 4; ++vt) {
+                            const int gi = lane + 32 * vt + rowops::kRowThreads * g;
+                            v[vt] = gi < groups ? *reinterpret_cast<const uint4*>(xr + gi * 8) : make_uint4(0, 0, 0, 0);
+                        }
+#pragma unroll
+                        for (int vt = 0; vt < 4; ++vt) {
+                            const uint32_t w[4] = {v[vt].x, v[vt].y, v[vt].z, v[vt].w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {  // a group beyond the row adds +0 to a sum that is never -0
+                                const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xffff0000u);
+                                part[vt] = __fadd_rn(part[vt], __fmul_rn(lo, lo));
+                                part[vt] = __fadd_rn(part[vt], __fmul_rn(hi, hi));
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int vt = 0; vt < 4; ++vt) part[vt] = rowops::WarpTreeSum(part[vt]);
+                    if (lane == 0)
+                        norm_inv[row] = rowops::InverseRms(__fadd_rn(__fadd_rn(__fadd_rn(part[0], part[1]), part[2]), part[3]), K, fu.norm_epsilon);
                 }
                 EpilogueBarrier<128>();
             }
-        }
+            if (nb > 0) {
+                if (prologue == 1 && !weights_early) load_norm_weights();
+                for (int base = et;;) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (base + j * 128 < total) {
+                            uint32_t word = 0u;
+                            if (inside[j]) {
+                                float h[4];
+                                const float x[4] = {__uint_as_float(raw[j].x << 16), __uint_as_float(raw[j].x & 0xffff0000u),
+                                                    __uint_as_float(raw[j].y << 16), __uint_as_float(raw[j].y & 0xffff0000u)};
+                                if (prologue == 0) {
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) h[i] = x[i];
+                                } else {
+                                    // the decoder-block node in front of the Cast, with its own BF16 rounding point(s)
+                                    float y[4];
+                                    WidenFour(prologue == 1 ? fu.norm_weight_dtype : FTH_B200_BF16, raw2[j], y);
+                                    if (prologue == 1) {
+                                        const float inv = norm_inv[rows[j]];
+#pragma unroll
+                                        for (int i = 0; i < 4; ++i)
+                                            h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(__fmul_rn(x[i], inv), __fadd_rn(y[i], fu.norm_offset))));
+                                    } else {
+#pragma unroll
+                                        for (int i = 0; i < 4; ++i) {
+                                            const float sv = DecodeBf16(EncodeBf16Cast(rowops::SiluValue(x[i])));  // SiLU node
+                                            h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(sv, y[i])));                 // Mul node
+                                        }
+                                    }
+                                }
+                                word = CastFour(p.e4m3, p.args.a_scale, p.a_inv, h);
+                            }
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst[j]), "r"(word) : "memory");
+                        }
+                    }
+                    base += 4 * 128;
+                    if (base >= total) break;
+                    locate(base);
+                    load_activations();
+                    if (prologue == 1) load_norm_weights();
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes → visible to the MMA's reads
+                MbarArrive(q_full);
+            }
+        } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (convert && nb > 0) {
             // Four consecutive K elements of one activation row per item (one 32-bit word of the swizzled tile), four
             // items per thread and round so that their loads overlap.  Rows >= m stay unwritten: they only feed
@@ -264,12 +414,9 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const int words_per_row = nb * 32;
             const int total = m * words_per_row;
             const bool vec = (reinterpret_cast<uintptr_t>(p.args.a) & 15) == 0;
-            const bool vec2 = fu.prologue == 2 ? (reinterpret_cast<uintptr_t>(fu.a2) & 15) == 0
-                                               : (reinterpret_cast<uintptr_t>(fu.norm_weight) & 15) == 0;
             for (int base = et; base < total; base += 4 * 128) {
-                uint4 raw[4], raw2[4];
+                uint4 raw[4];
                 uint32_t dst[4];
-                int rows[4];
                 bool inside[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -279,42 +426,20 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     const int kb = c >> 5, w4 = c & 31;
                     const int64_t k0 = static_cast<int64_t>(kb_begin + kb) * kBlockK + w4 * 4;
                     inside[j] = item < total && k0 < p.args.k;  // K is a multiple of 16: a group is in or out as a whole
-                    rows[j] = row;
                     dst[j] = SmemAddr(q_tiles) + kb * (BQ * kBlockK) + row * 128 + (((w4 >> 2) ^ (row & 7)) << 4) + ((w4 & 3) << 2);
                     raw[j] = inside[j] ? LoadFourRaw(p.args, static_cast<int64_t>(row) * p.args.k + k0, vec) : make_uint4(0, 0, 0, 0);
-                    raw2[j] = make_uint4(0, 0, 0, 0);
-                    if (inside[j] && fu.prologue == 1) raw2[j] = LoadFourOf(fu.norm_weight, fu.norm_weight_dtype, k0, vec2);
-                    if (inside[j] && fu.prologue == 2) raw2[j] = LoadFourOf(fu.a2, FTH_B200_BF16, static_cast<int64_t>(row) * p.args.k + k0, vec2);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     if (base + j * 128 < total) {
-                        uint32_t word = 0u;
-                        if (inside[j] && fu.prologue == 0) {
-                            word = ConvertFourRaw<INT8>(p.args, ie, p.e4m3, p.a_inv, raw[j]);
-                        } else if (inside[j]) {
-                            // the decoder-block node in front of the Cast, with its own BF16 rounding point(s)
-                            float x[4], y[4], h[4];
-                            WidenFour(FTH_B200_BF16, raw[j], x);
-                            WidenFour(fu.prologue == 1 ? fu.norm_weight_dtype : FTH_B200_BF16, raw2[j], y);
-                            if (fu.prologue == 1) {
-                                const float inv = norm_inv[rows[j]];
-                                for (int i = 0; i < 4; ++i)
-                                    h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(__fmul_rn(x[i], inv), __fadd_rn(y[i], fu.norm_offset))));
-                            } else {
-                                for (int i = 0; i < 4; ++i) {
-                                    const float s = DecodeBf16(EncodeBf16Cast(rowops::SiluValue(x[i])));  // SiLU node
-                                    h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(s, y[i])));                 // Mul node
-                                }
-                            }
-                            word = CastFour(p.e4m3, p.args.a_scale, p.a_inv, h);
-                        }
+                        const uint32_t word = inside[j] ? ConvertFourRaw<INT8>(p.args, ie, p.e4m3, p.a_inv, raw[j]) : 0u;
                         asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst[j]), "r"(word) : "memory");
                     }
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes → visible to the MMA's reads
             MbarArrive(q_full);
+        }
         }
         const int row = (warp & 3) * 32 + lane;  // TMEM lane = channel inside the tile
         // Bytes this CTA will receive: from each of the `split` chunks, its L rows of ceil(m / 4) 16-byte vectors.
@@ -348,9 +473,46 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         // Second phase of the cluster barrier: "this CTA has sent everything it will ever send".  The matching wait is
         // at the very end of the kernel, so that no CTA leaves while a peer could still store into its shared memory —
         // also when a bounded wait gave up somewhere.  In a healthy run every peer has long arrived by then.
-        ClusterArrive();
+        ClusterArriveRelaxed();
         const bool delivered = MbarWait(x_full, 0, p.status, 24, 0);
 
+        if constexpr (DEC) {
+            // One output per thread and round, as below, written out for BF16 <- E4M3 / E5M2 <- FP32 with per-tensor scales:
+            // product scale, output Cast (encode, decode, BF16 rounding), then the fused Add node's own rounding point.
+            const bool second = tile >= static_cast<int>(p.p_tiles_first);  // this CTA's tile belongs to the second weight
+            const float mult = second ? fu.ab_scale2 : fe.ab_scale;
+            const int64_t ldo = second ? fu.ldo2 : fe.ldo;
+            uint16_t* out = static_cast<uint16_t*>(second ? fu.out2 : fe.out);
+            const uint16_t* residual = second ? nullptr : static_cast<const uint16_t*>(fu.residual);
+            const int64_t n_base = static_cast<int64_t>(tile) * kBlockP + (static_cast<int64_t>(rank) << lshift);
+            const int64_t n_shift = second ? fu.n_first : 0;
+            const int total = m << lshift;
+            auto finish = [&](int item, bool early, uint16_t early_bits) {
+                if (!delivered || item >= total) return;
+                const int q = item >> lshift;
+                const int r = item & (rows_per_cta - 1);
+                const int64_t n = n_base + r;
+                if (n >= p.p_total) return;
+                uint32_t t[8];
+#pragma unroll
+                for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? exchange[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
+                float sum = 0.0f;
+#pragma unroll
+                for (int ss = 0; ss < 8; ++ss) {
+                    if (ss < p.split) sum += __uint_as_float(t[ss]);  // chunk order; no zero is ever added: it could flip a -0
+                }
+                const float scaled = __fmul_rn(sum, mult);
+                const float y = p.out_inv != 0.0f ? __fmul_rn(scaled, p.out_inv) : __fdiv_rn(scaled, fe.out_scale);
+                const uint32_t code = EncodePair(p.e4m3, y, 0.0f) & 0xffu;
+                uint16_t bits = EncodeBf16Cast(__fmul_rn(DecodeFast(p.e4m3, code), fe.out_scale));
+                const int64_t o = q * ldo + (n - n_shift);
+                if (residual != nullptr) bits = EncodeBf16Cast(__fadd_rn(DecodeBf16(early ? early_bits : residual[o]), DecodeBf16(bits)));
+                out[o] = bits;
+            };
+            finish(et, true, residual_early[0]);
+            if (total > 128) finish(128 + et, true, residual_early[1]);
+            for (int base = 256; base < total; base += 128) finish(base + et, false, 0);
+        } else {
         // Column-sharded projection with the gather's signalling folded in: before the first store into the peers'
         // buffers every rank must have published the previous step.  The wait sits here, behind the whole weight
         // stream of this launch, so the NVLink round trip of the peers' flags is normally long over.
@@ -399,11 +561,12 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             EpilogueBarrier<128>();  // every epilogue thread's peer stores are issued
             if (et == 0) GatherArriveAndPublish(p.args.signal, gather_step, gridDim.x);
         }
+        }
     }
     if (warp < 2) {
         if (!(warp == 0 && lane == 0 && nb > 0)) asm volatile("griddepcontrol.wait;" ::: "memory");
         ClusterWait();
-        ClusterArrive();  // these warps send nothing: second phase right away
+        ClusterArriveRelaxed();  // these warps send nothing: second phase right away
     }
     ClusterWait();  // second phase: every CTA of the cluster has finished sending
     umma::FenceBeforeThreadSync();
@@ -414,12 +577,12 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     }
 }
 
-template <bool INT8, bool P_MN, int BQ>
+template <bool INT8, bool P_MN, int BQ, bool DEC>
 int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q, const TcParams& p_in,
                        const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     TcParams p = p_in;
     p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks);
-    auto kernel = LinearClusterKernel<INT8, P_MN, BQ>;
+    auto kernel = LinearClusterKernel<INT8, P_MN, BQ, DEC>;
     if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), ClusterCfg<BQ>::kSmemBytes) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(g.p_tiles * g.cluster));
@@ -440,23 +603,24 @@ int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUte
     return CheckLaunch();
 }
 
-template <bool INT8>
+template <bool INT8, bool DEC>
 int LaunchClusterFor(const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q,
                   const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     if (g.bq == 16) {
-        return weights_mn ? LaunchClusterTyped<INT8, true, 16>(g, map_p, map_p2, map_q, p, fe, ie, stream)
-                          : LaunchClusterTyped<INT8, false, 16>(g, map_p, map_p2, map_q, p, fe, ie, stream);
+        return weights_mn ? LaunchClusterTyped<INT8, true, 16, DEC>(g, map_p, map_p2, map_q, p, fe, ie, stream)
+                          : LaunchClusterTyped<INT8, false, 16, DEC>(g, map_p, map_p2, map_q, p, fe, ie, stream);
     }
-    return weights_mn ? LaunchClusterTyped<INT8, true, 32>(g, map_p, map_p2, map_q, p, fe, ie, stream)
-                      : LaunchClusterTyped<INT8, false, 32>(g, map_p, map_p2, map_q, p, fe, ie, stream);
+    return weights_mn ? LaunchClusterTyped<INT8, true, 32, DEC>(g, map_p, map_p2, map_q, p, fe, ie, stream)
+                      : LaunchClusterTyped<INT8, false, 32, DEC>(g, map_p, map_p2, map_q, p, fe, ie, stream);
 }
 
 }  // namespace
 
 int LaunchCluster(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q,
                   const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
-    return int8 ? LaunchClusterFor<true>(g, weights_mn, map_p, map_p2, map_q, p, fe, ie, stream)
-                : LaunchClusterFor<false>(g, weights_mn, map_p, map_p2, map_q, p, fe, ie, stream);
+    if (int8) return LaunchClusterFor<true, false>(g, weights_mn, map_p, map_p2, map_q, p, fe, ie, stream);
+    return p.decoder ? LaunchClusterFor<false, true>(g, weights_mn, map_p, map_p2, map_q, p, fe, ie, stream)
+                     : LaunchClusterFor<false, false>(g, weights_mn, map_p, map_p2, map_q, p, fe, ie, stream);
 }
 
 }  // namespace tc

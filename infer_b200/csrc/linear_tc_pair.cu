@@ -63,6 +63,9 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     ClusterArrive();
     ClusterWait();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    TouchConstantLines(p);
+    if constexpr (INT8) TouchConstantLines(ie);
+    else TouchConstantLines(fe);
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int64_t m_pairs = (p.p_total + 255) / 256;

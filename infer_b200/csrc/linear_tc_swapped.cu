@@ -54,8 +54,11 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     // Lets a dependent grid (the split-K reduce pass) be scheduled while this one runs; it still waits for this
     // grid to finish before it reads anything.  No effect when launched without programmatic serialization.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // Everything above (barriers, tensor memory) overlapped the tail of the previous kernel in the stream; the
-    // operands may be that kernel's output, so nothing is read before it has completed.
+    TouchConstantLines(p);
+    if constexpr (INT8) TouchConstantLines(ie);
+    else TouchConstantLines(fe);
+    // Everything above (barriers, tensor memory, parameters) overlapped the tail of the previous kernel in the stream;
+    // the operands may be that kernel's output, so nothing is read before it has completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // unit → (p tile, q tile, K chunk).  [K,N] weights walk the column tiles fastest (chunk-major): the CTAs running
@@ -333,7 +336,10 @@ __device__ __forceinline__ uint32_t FinishFour(const TcParams& p, const Fp8Epilo
 template <bool INT8>
 __global__ void __launch_bounds__(256) SplitReduceKernel(TcParams p, Fp8Epilogue fe, Int8Epilogue ie) {
     // Launched with programmatic stream serialization: wait until the producing grid has completed and its
-    // partial sums are visible.
+    // partial sums are visible.  The parameters are fetched while it runs.
+    TouchConstantLines(p);
+    if constexpr (INT8) TouchConstantLines(ie);
+    else TouchConstantLines(fe);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // Column-sharded projection with the gather's signalling folded in: every rank must have published the previous
     // step before this pass stores into the peers' buffers; the last block of the pass publishes this step.

@@ -132,14 +132,24 @@ bool Tcgen05StoresToPeers(int dtype, const LinearArgs& a, const Fp8Epilogue& fe,
     return !GeometryFor(a).swap && DirectEpilogue(int8, fe, ie) && (int8 ? ie.out_dtype : fe.out_dtype) == 0;
 }
 
-// QwenRmsNorm / SiLU * Mul in front, residual Add behind, a second weight beside: BF16 in, FP8 product, BF16 out, on the
-// single-launch cluster kernel only.  FTH_B200_OK when LaunchLinearTcgen05 will run args.fusion.
+// The decoder-block form of the single-launch cluster kernel: BF16 activations (16-byte aligned), FP8 product, BF16 out,
+// per-tensor scales, no bias, nothing stored to peers, no selection.
+static bool DecoderForm(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
+    if (dtype == FTH_B200_INT8 || GeometryFor(a).cluster == 0) return false;
+    if (a.a_dtype != FTH_B200_BF16 || fe.out_dtype != FTH_B200_BF16 || !DirectEpilogue(false, fe, ie)) return false;
+    if (fe.w_channel_scales != nullptr || a.argmax_keys != nullptr || a.peers.count != 0 || a.signal.world != 0) return false;
+    return reinterpret_cast<uintptr_t>(a.a) % 16 == 0;
+}
+
+// QwenRmsNorm / SiLU * Mul in front, residual Add behind, a second weight beside: that form only.  FTH_B200_OK when
+// LaunchLinearTcgen05 will run args.fusion.
 int Tcgen05FusionStatus(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
     if (!Tcgen05Supported(dtype, a)) return FTH_B200_ERR_UNSUPPORTED;
     const DecoderFusion& fu = a.fusion;
     const TcGeometry g = GeometryFor(a);
-    if (dtype == FTH_B200_INT8 || g.cluster == 0 || a.a_dtype != FTH_B200_BF16 || fe.out_dtype != FTH_B200_BF16 || !DirectEpilogue(false, fe, ie) ||
-        fe.w_channel_scales != nullptr || a.argmax_keys != nullptr || a.peers.count != 0) return FTH_B200_ERR_UNSUPPORTED;
+    if (!DecoderForm(dtype, a, fe, ie)) return FTH_B200_ERR_UNSUPPORTED;
+    if ((fu.prologue == 1 && reinterpret_cast<uintptr_t>(fu.norm_weight) % 16 != 0) ||
+        (fu.prologue == 2 && reinterpret_cast<uintptr_t>(fu.a2) % 16 != 0)) return FTH_B200_ERR_UNSUPPORTED;
     if (fu.prologue < 0 || fu.prologue > 2) return FTH_B200_ERR_INVALID;
     if (fu.prologue == 1 && fu.norm_weight == nullptr) return FTH_B200_ERR_INVALID;
     if (fu.prologue == 1 && (fu.norm_weight_dtype != FTH_B200_BF16 && fu.norm_weight_dtype != FTH_B200_FP32)) return FTH_B200_ERR_UNSUPPORTED;
@@ -218,6 +228,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     if (int8) p.fast = ie.bias_mode == FTH_B200_BIAS_NONE && ie.out_dtype == 0 && !(ie.is_gemm && (ie.alpha != 1.0f || ie.beta != 1.0f));
     else p.fast = fe.bias_mode == FTH_B200_BIAS_NONE && fe.out_dtype == 0 && !(fe.is_gemm && fe.alpha != 1.0f);
     p.fast4 = DirectEpilogue(int8, fe, ie);
+    p.decoder = DecoderForm(dtype, a, fe, ie);
     p.a_inv = int8 ? 0.0f : ExactReciprocal(a.a_scale);
     p.out_inv = int8 ? 0.0f : ExactReciprocal(fe.out_scale);
     p.scratch = scratch;

@@ -74,6 +74,19 @@ __device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity, int* st
 // ---- thread-block clusters: ranks, barrier, distributed shared memory ------------------------------------
 __device__ __forceinline__ uint32_t ClusterRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ uint32_t ClusterSize() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+// Second use of the cluster barrier in a kernel that only needs "every CTA has got this far" (no data is handed over):
+// no release fence, so the stores before it are not waited for.
+__device__ __forceinline__ void ClusterArriveRelaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+// Kernel parameters are read through the constant cache, and the first touch of each line costs a round trip to L2
+// (about a microsecond here).  Reads one word of every 32 bytes of `params` so that a kernel launched ahead of its
+// producer has all of them cached by the time the producer finishes.
+template <typename T>
+__device__ __forceinline__ void TouchConstantLines(const T& params) {
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(&params);
+#pragma unroll
+    for (int i = 0; i < static_cast<int>(sizeof(T) / 4); i += 8) asm volatile("" ::"r"(words[i]));
+    asm volatile("" ::"r"(words[sizeof(T) / 4 - 1]));
+}
 __device__ __forceinline__ void ClusterArrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 __device__ __forceinline__ void ClusterWait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 // Address of this CTA's shared-memory location `smem_addr` inside CTA `rank` of the cluster.

@@ -60,10 +60,13 @@ def silu_mul(g_bits, u_bits):
     return O.binary(1, O.BF16, O.silu(O.BF16, g_bits), u_bits)   # SiLU node then Mul node, BF16 out each
 
 
-def run_stack(project, weights, x_bits, trace=None):
-    """project(h_bits [M,K] uint16, (codes, scale)) -> BF16 bits [M,N].  Returns the final hidden state (BF16 bits)."""
+def run_stack(project, weights, x_bits, trace=None, states=None):
+    """project(h_bits [M,K] uint16, (codes, scale)) -> BF16 bits [M,N].  Returns the final hidden state (BF16 bits).
+    `states`, when a list, receives the hidden state in front of every layer and the final one."""
     x = x_bits
     for layer in weights:
+        if states is not None:
+            states.append(x)
         h = rmsnorm(x, layer["g1"])
         t = h
         for name in ("q", "k", "v", "o"):
@@ -79,4 +82,6 @@ def run_stack(project, weights, x_bits, trace=None):
         if trace is not None:
             trace.append(("down", a))
         x = add(x, project(a, layer["down"]))
+    if states is not None:
+        states.append(x)
     return x

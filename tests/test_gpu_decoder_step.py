@@ -3,8 +3,15 @@ between them — against the CPU oracle, and the six-launch-per-layer fused form
 
 * fused == unfused, byte for byte: fth_b200_fp8_linear_fused keeps every rounding point of the nodes it absorbs
   (QwenRmsNorm, SiLU, Mul, Add, both Casts) and sums the squares of a row in the stand-alone kernel's order.
-* against the oracle (reference Common kernels for every node, tests/decoder_stack.py): cosine of the final hidden state
-  >= 0.999 over all 24 layers, as tools/compare_qwen_logits.py:41-58 computes it."""
+* against the oracle (reference Common kernels for every node, tests/decoder_stack.py), layer by layer: every layer run
+  on the device from the oracle's own input to that layer gives the oracle's output up to isolated one-code steps
+  and what the six projections behind such a step make of it (cosine >= 0.9999, as tools/compare_qwen_logits.py:41-58
+  computes it; at most 5 % of the outputs differ at all; tests/test_gpu_decoder_stack.py holds the node-by-node
+  comparison, where each projection starts from the oracle's input: at most one code apart).
+* the free-running 24-layer step: cosine >= 0.995 and the same greedy index per row.  A row of E5M2 codes has two
+  mantissa bits, so one output that lands on the other side of a rounding boundary (the tensor core adds the products
+  of a dot product in another order than the sequential CPU loop) moves by 25 % and the layers behind it carry that
+  on; the per-layer check above is the one that bounds the kernels."""
 import ctypes as C
 
 import numpy as np
@@ -79,7 +86,30 @@ def test_whole_step_on_device_matches_oracle(cuda, stack_weights, m):
     rmse = float(np.sqrt(((got - want) ** 2).mean()))
     print(f"M={m}: whole step on device, {step.launches} launches: cosine {cos:.6f} rmse {rmse:.4g} max|err| {np.abs(got - want).max():.4g} "
           f"argmax equal {bool((got.argmax(axis=1) == want.argmax(axis=1)).all())}")
-    assert cos >= 0.999
+    assert cos >= 0.995
+    assert (got.argmax(axis=1) == want.argmax(axis=1)).all()
+
+
+@pytest.mark.parametrize("m", [1, 16])
+@pytest.mark.parametrize("fused", [True, False])
+def test_every_layer_from_the_oracles_input(cuda, stack_weights, m, fused):
+    rng = np.random.default_rng(100 + m)
+    x0 = D.to_bf16(rng.standard_normal((m, D.HIDDEN)).astype(np.float32))
+    states = []
+    D.run_stack(oracle_project, stack_weights, x0, states=states)
+    worst_cos, worst_frac, total_diff = 1.0, 0.0, 0
+    for index in range(D.LAYERS):
+        layers = device_layers(cuda, stack_weights[index:index + 1])
+        got_bits, _ = run_device(cuda, layers, states[index], m, fused=fused)
+        want_bits = states[index + 1]
+        got, want = D.from_bf16(got_bits).astype(np.float64), D.from_bf16(want_bits).astype(np.float64)
+        cos = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want)))
+        differing = int((got_bits != want_bits).sum())
+        worst_cos, worst_frac, total_diff = min(worst_cos, cos), max(worst_frac, differing / want_bits.size), total_diff + differing
+        assert cos >= 0.9999, f"layer {index}: cosine {cos}"
+        assert differing <= 0.05 * want_bits.size, f"layer {index}: {differing} of {want_bits.size} outputs differ"
+    print(f"M={m} {'fused' if fused else 'node by node'}: 24 layers, each from the oracle's input: worst cosine {worst_cos:.7f}, "
+          f"{total_diff} of {24 * m * D.HIDDEN} BF16 outputs differ (worst layer {100 * worst_frac:.3f} %)")
 
 
 def test_fused_call_rejections(cuda):
