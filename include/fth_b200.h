@@ -166,8 +166,12 @@ size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc)
  *             (src/kernel/common/qwen_rms_norm.cc:71-95, BF16 output); FTH_B200_FUSE_SILU_MUL: the activation is
  *             Mul(SiLU(a), a2) of two BF16 tensors (the SiLU and Mul nodes between gate / up and the down projection).
  *   residual  BF16, laid out like `out`: out = Add(residual, out) (the residual connection behind o / down).
- *   w2        a second weight of the same format and layout on the same activation (gate and up): [K,n2] / [n2,K]
- *             with scale w2_scale, output out2 [M,n2] (row stride ldo2, 0 = n2); desc->n must be a multiple of 128.
+ *   w2        a second weight of the same format and layout on the same activation (gate and up): [K,n2] / [n2,K],
+ *             n2 = desc->n, with scale w2_scale, output out2 [M,n2] (row stride ldo2, 0 = n2).
+ *   epilogue  FTH_B200_FUSE_OUT_SILU_MUL (needs w2, no residual): desc->out receives Mul(SiLU(first product), second
+ *             product), the activation of the down projection; out2 is not written and may be null.
+ * A norm weight is read ahead of the work queued in front of the call when desc->weights_static says the same of the
+ * projection weights: it is a constant of the model like them.
  * Every rounding point of the unfused nodes is kept (BF16 after the norm / SiLU / Mul, FP8 after the Cast, FP8 after
  * the product, BF16 after the second Cast and after the Add), and the squares of a row are summed in the order
  * fth_b200_qwen_rms_norm uses, so the call returns the bytes of the separate calls.  Shapes of the single-launch
@@ -175,6 +179,7 @@ size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc)
  * No counterpart in the reference, which runs each node as its own kernel (src/kernel/cuda/{qwen_rms_norm,silu,mul,add}.cu).
  * ------------------------------------------------------------------------------------------------- */
 enum { FTH_B200_FUSE_NONE = 0, FTH_B200_FUSE_RMS_NORM = 1, FTH_B200_FUSE_SILU_MUL = 2 };
+enum { FTH_B200_FUSE_OUT_NONE = 0, FTH_B200_FUSE_OUT_SILU_MUL = 1 };
 typedef struct {
     int32_t prologue;            /* FTH_B200_FUSE_* */
     int32_t norm_weight_dtype;   /* FTH_B200_BF16 or FTH_B200_FP32 */
@@ -188,6 +193,7 @@ typedef struct {
     void* out2;
     int64_t n2;
     int64_t ldo2;
+    int32_t epilogue;            /* FTH_B200_FUSE_OUT_* */
 } fth_b200_fp8_linear_fusion;
 int fth_b200_fp8_linear_fused(const fth_b200_fp8_linear_desc* desc, const fth_b200_fp8_linear_fusion* fusion, fth_b200_stream_t stream);
 int fth_b200_fp8_linear_fused_supported(const fth_b200_fp8_linear_desc* desc, const fth_b200_fp8_linear_fusion* fusion);

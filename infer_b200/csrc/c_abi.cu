@@ -350,7 +350,7 @@ static int BuildFused(const fth_b200_fp8_linear_desc* d, const fth_b200_fp8_line
     fu.residual = f->residual;
     fu.w2 = f->w2; fu.out2 = f->out2; fu.n2 = f->n2; fu.ldo2 = f->ldo2 ? f->ldo2 : f->n2;
     fu.ab_scale2 = d->a_scale * f->w2_scale;
-    fu.n_first = d->n;
+    fu.epilogue = f->epilogue;
     if (fu.prologue == 1 && (!std::isfinite(fu.norm_epsilon) || fu.norm_epsilon < 0.0f)) return FTH_B200_ERR_INVALID;
     if (fu.w2 != nullptr && !ValidScale(f->w2_scale)) return FTH_B200_ERR_INVALID;
     Int8Epilogue ie = {};

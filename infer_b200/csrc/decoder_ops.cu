@@ -114,6 +114,14 @@ __global__ void __launch_bounds__(kThreads) RmsNormKernel(const void* __restrict
 
 enum { kOpAdd = 0, kOpMul = 1, kOpSilu = 2, kOpSiluMul = 3 };
 
+// SiLU of one element, as the FP32 value the node's output rounding starts from.  A BF16 node takes the short path of
+// rowops::SiluToBf16 (its result is the rounded output already; rounding it again changes nothing).
+template <int DTYPE>
+__device__ __forceinline__ float SiluOf(float x) {
+    if constexpr (DTYPE == FTH_B200_BF16) return DecodeBf16(SiluToBf16(x));
+    else return SiluValue(x);
+}
+
 // out[i] = lhs[i] op rhs[i % rhs_count]   (Add, Mul; rhs_count is the total count or one row)
 // out[i] = silu(lhs[i])                    (SiLU)
 // out[i] = round(silu(lhs[i])) * rhs[i]    (SiLU node followed by Mul node: both rounding points kept)
@@ -132,9 +140,9 @@ __global__ void __launch_bounds__(256) PointwiseKernel(const void* __restrict__ 
         for (int j = 0; j < 8; ++j) {
             if constexpr (OP == kOpAdd) o[j] = __fadd_rn(a[j], b[j]);
             else if constexpr (OP == kOpMul) o[j] = __fmul_rn(a[j], b[j]);
-            else if constexpr (OP == kOpSilu) o[j] = SiluValue(a[j]);
+            else if constexpr (OP == kOpSilu) o[j] = SiluOf<DTYPE>(a[j]);
             else {
-                float s = SiluValue(a[j]);
+                float s = SiluOf<DTYPE>(a[j]);
                 if constexpr (DTYPE == FTH_B200_BF16) s = DecodeBf16(EncodeBf16Cast(s));
                 else if constexpr (DTYPE == FTH_B200_FP16) s = __half2float(__float2half_rn(s));
                 o[j] = __fmul_rn(s, b[j]);
@@ -146,13 +154,13 @@ __global__ void __launch_bounds__(256) PointwiseKernel(const void* __restrict__ 
         const float a = ReadFloat<DTYPE>(lhs, i);
         float o;
         if constexpr (OP == kOpSilu) {
-            o = SiluValue(a);
+            o = SiluOf<DTYPE>(a);
         } else {
             const float b = ReadFloat<DTYPE>(rhs, i % rhs_count);
             if constexpr (OP == kOpAdd) o = __fadd_rn(a, b);
             else if constexpr (OP == kOpMul) o = __fmul_rn(a, b);
             else {
-                float s = SiluValue(a);
+                float s = SiluOf<DTYPE>(a);
                 if constexpr (DTYPE == FTH_B200_BF16) s = DecodeBf16(EncodeBf16Cast(s));
                 else if constexpr (DTYPE == FTH_B200_FP16) s = __half2float(__float2half_rn(s));
                 o = __fmul_rn(s, b);

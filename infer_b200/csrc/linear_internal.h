@@ -32,11 +32,11 @@ struct DecoderFusion {
     float norm_offset, norm_epsilon;
     const void* a2;           // prologue 2: the second BF16 input [M,K]
     const void* residual;     // epilogue: out = Add(residual, out); BF16, laid out like out; null: none
-    const void* w2;           // second weight [K,n2] / [n2,K] on the same activation; null: none
+    const void* w2;           // second weight [K,n2] / [n2,K] on the same activation (n2 == n); null: none
     float ab_scale2;          // a_scale * scale of w2
     void* out2;               // its BF16 output [M,n2], row stride ldo2
     int64_t n2, ldo2;
-    int64_t n_first;          // columns of the first weight (a multiple of 128 when w2 is given)
+    int epilogue;             // with w2: 1 = out receives Mul(SiLU(first product), second product); out2 is not written
     bool active() const { return prologue != 0 || residual != nullptr || w2 != nullptr; }
 };
 

@@ -23,7 +23,7 @@ struct TcParams {
     int64_t chunk_blocks;      // 128-byte K blocks per chunk
     int ring_stages;           // cluster kernel: weight ring depth of this launch
     int64_t k_blocks;          // ceil(K / 128)
-    int64_t p_tiles_first;     // cluster kernel with a second weight: tiles that belong to the first one (else p_tiles)
+    int tiles_per_cta;         // cluster kernel: 2 when a second weight shares the activation (its tile rides in the same CTA)
     int64_t units;             // p_tiles * q_tiles * split
     uint32_t idesc;
     int e4m3;                  // FP8 format of operands and output (1 = E4M3, 0 = E5M2)

@@ -27,15 +27,16 @@ struct ClusterCfg {
     static constexpr int kQBytes = kQBlocks * BQ * kBlockK;  // 16 KB / 32 KB
     static constexpr int kStages = BQ <= 16 ? 5 : 3;         // weight ring (16 KB per stage), upper limit
     static constexpr int kMaxStages = 8;                     // barrier slots
-    static constexpr int kExchangeBytes = kBlockP * BQ * 4;  // partials of this CTA's rows, all chunks
-    static constexpr uint32_t kTmemCols = 32;
+    static constexpr int kExchangeBytes = kBlockP * BQ * 4;  // partials of this CTA's rows, all chunks (per weight tile)
+    static constexpr int kMaxTiles = 2;                      // weight tiles per CTA: a second weight on the same activation
+    __host__ __device__ static constexpr uint32_t TmemCols(int tiles) { return tiles * BQ <= 32 ? 32u : 64u; }
     static constexpr int kThreads = 192;
     static constexpr int kNormBytes = 768;                   // a fused QwenRmsNorm: 1 / rms per row + four partial sums per row
-    static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kPBytes + kQBytes + kExchangeBytes + 256 + kNormBytes;
-    static int StagesFor(int64_t chunk_blocks) { return chunk_blocks < kStages ? static_cast<int>(chunk_blocks) : kStages; }
-    static size_t SmemFor(int64_t chunk_blocks) {
-        return 1024 + static_cast<size_t>(StagesFor(chunk_blocks)) * kPBytes + static_cast<size_t>(chunk_blocks) * BQ * kBlockK +
-               kExchangeBytes + 256 + kNormBytes;
+    static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kPBytes + kQBytes + kMaxTiles * kExchangeBytes + 256 + kNormBytes;
+    static int StagesFor(int64_t loads) { return loads < kStages ? static_cast<int>(loads) : kStages; }  // loads = chunk blocks x tiles
+    static size_t SmemFor(int64_t chunk_blocks, int tiles) {
+        return 1024 + static_cast<size_t>(StagesFor(chunk_blocks * tiles)) * kPBytes + static_cast<size_t>(chunk_blocks) * BQ * kBlockK +
+               static_cast<size_t>(tiles) * kExchangeBytes + 256 + kNormBytes;
     }
 };
 
@@ -132,8 +133,11 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     // then takes ~30 KB instead of ~100 KB, and the CTAs of the next kernel in the stream can move in early.
     const int stages = p.ring_stages;
     uint8_t* q_tiles = ring + static_cast<size_t>(stages) * kPBytes;            // [chunk_blocks][BQ][128], 128-byte swizzle
-    uint32_t* exchange = reinterpret_cast<uint32_t*>(q_tiles + p.chunk_blocks * (BQ * kBlockK));  // [chunk][L][BQ]
-    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(exchange) + C::kExchangeBytes);
+    // A second weight on the same activation (gate and up) is this CTA's second tile: the same columns of the other
+    // weight, its own accumulator columns and its own exchange area.
+    const int tiles_here = DEC ? p.tiles_per_cta : 1;
+    uint32_t* exchange = reinterpret_cast<uint32_t*>(q_tiles + p.chunk_blocks * (BQ * kBlockK));  // [tile][chunk][L][BQ]
+    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(exchange) + tiles_here * C::kExchangeBytes);
     uint64_t* empty = full + C::kMaxStages;
     uint64_t* q_full = empty + C::kMaxStages;
     uint64_t* tmem_full = q_full + 1;
@@ -147,7 +151,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 
     if (threadIdx.x == 0) {
         TmaPrefetchDescriptor(&map_p);  // kernel parameters: safe to touch before the previous grid has finished
-        if (p.p_tiles_first < p.p_tiles) TmaPrefetchDescriptor(&map_p2);
+        if (tiles_here > 1) TmaPrefetchDescriptor(&map_p2);
         if (!convert) TmaPrefetchDescriptor(&map_q);
         for (int s = 0; s < stages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
         MbarInit(q_full, convert ? 128 : 1);
@@ -155,7 +159,8 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         MbarInit(x_full, 1);
         FenceBarrierInit();
     }
-    if (warp == 1) umma::TmemAlloc(tmem_base_slot, C::kTmemCols);
+    const uint32_t tmem_cols = C::TmemCols(tiles_here);
+    if (warp == 1) umma::TmemAlloc(tmem_base_slot, tmem_cols);
     umma::FenceBeforeThreadSync();
     __syncthreads();
     umma::FenceAfterThreadSync();
@@ -185,14 +190,14 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         if (lane == 0 && nb > 0) {
             int stage = 0;
             uint32_t phase = 0;
-            auto load_weights = [&](int kb) -> bool {
+            const int loads = nb * tiles_here;
+            auto load_weights = [&](int i) -> bool {
                 // the first pass over the ring finds every stage free; later passes wait for the MMAs that read it
-                if (kb >= stages && !MbarWait(&empty[stage], phase ^ 1u, p.status, 20, stage)) return false;
-                const int32_t k0 = (kb_begin + kb) * kBlockK;
-                // tiles behind the first weight's belong to the second weight that shares the activation
-                const bool second = tile >= p.p_tiles_first;
+                if (i >= stages && !MbarWait(&empty[stage], phase ^ 1u, p.status, 20, stage)) return false;
+                const bool second = i >= nb;  // the first weight's K blocks, then the second weight's
+                const int32_t k0 = (kb_begin + (second ? i - nb : i)) * kBlockK;
                 const CUtensorMap* map = second ? &map_p2 : &map_p;
-                const int32_t p0 = (second ? tile - static_cast<int>(p.p_tiles_first) : tile) * kBlockP;
+                const int32_t p0 = tile * kBlockP;
                 uint8_t* ps = ring + static_cast<size_t>(stage) * kPBytes;
                 MbarExpectTx(&full[stage], kPBytes);
                 if constexpr (P_MN) TmaLoad2D(ps, map, p0, k0, &full[stage]);
@@ -204,14 +209,14 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             // finished: their DRAM latency then overlaps its tail.
             int kb = 0;
             if (p.args.w_static) {
-                for (; kb < nb && kb < stages; ++kb) load_weights(kb);
+                for (; kb < loads && kb < stages; ++kb) load_weights(kb);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             if (!convert) {
                 MbarExpectTx(q_full, static_cast<uint32_t>(nb) * BQ * kBlockK);
                 for (int j = 0; j < nb; ++j) TmaLoad2D(q_tiles + j * (BQ * kBlockK), &map_q, (kb_begin + j) * kBlockK, 0, q_full);
             }
-            for (; kb < nb; ++kb) {
+            for (; kb < loads; ++kb) {
                 if (!load_weights(kb)) break;
             }
         }
@@ -221,17 +226,19 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             int stage = 0;
             uint32_t phase = 0;
             bool failed = false;
-            for (int kb = 0; kb < nb && !failed; ++kb) {
+            for (int i = 0; i < nb * tiles_here && !failed; ++i) {
                 if (!MbarWait(&full[stage], phase, p.status, 22, stage)) { failed = true; break; }
-                if (kb == 0 && !MbarWait(q_full, 0, p.status, 21, 0)) { failed = true; break; }  // activations arrive last
+                if (i == 0 && !MbarWait(q_full, 0, p.status, 21, 0)) { failed = true; break; }  // activations arrive last
                 umma::FenceAfterThreadSync();
+                const int kb = i >= nb ? i - nb : i;
+                const uint32_t acc = tmem_base + (i >= nb ? BQ : 0);  // the second weight's accumulator sits beside the first's
                 const uint32_t ps = SmemAddr(ring + static_cast<size_t>(stage) * kPBytes);
                 const uint32_t qs = SmemAddr(q_tiles + kb * (BQ * kBlockK));
 #pragma unroll
                 for (int ks = 0; ks < kBlockK / 32; ++ks) {
                     const uint64_t a_desc = P_MN ? umma::SmemDesc(ps + ks * 4096, 16384, 1024) : umma::SmemDesc(ps + ks * 32, 16, 1024);
                     const uint64_t b_desc = umma::SmemDesc(qs + ks * 32, 16, 1024);
-                    umma::Mma<INT8>(tmem_base, a_desc, b_desc, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    umma::Mma<INT8>(acc, a_desc, b_desc, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma::Commit(&empty[stage]);
                 if (++stage == stages) { stage = 0; phase ^= 1u; }
@@ -386,7 +393,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                                     } else {
 #pragma unroll
                                         for (int i = 0; i < 4; ++i) {
-                                            const float sv = DecodeBf16(EncodeBf16Cast(rowops::SiluValue(x[i])));  // SiLU node
+                                            const float sv = DecodeBf16(rowops::SiluToBf16(x[i]));                 // SiLU node
                                             h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(sv, y[i])));                 // Mul node
                                         }
                                     }
@@ -443,7 +450,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         }
         const int row = (warp & 3) * 32 + lane;  // TMEM lane = channel inside the tile
         // Bytes this CTA will receive: from each of the `split` chunks, its L rows of ceil(m / 4) 16-byte vectors.
-        if (et == 0) MbarExpectTx(x_full, static_cast<uint32_t>(p.split) * rows_per_cta * ((m + 3) / 4) * 16);
+        if (et == 0) MbarExpectTx(x_full, static_cast<uint32_t>(p.split) * rows_per_cta * ((m + 3) / 4) * 16 * tiles_here);
         ClusterWait();  // every CTA of the cluster is running and has initialised its barriers
         if (nb > 0) {
             const bool ok = MbarWait(tmem_full, 0, p.status, 23, 0);
@@ -456,15 +463,18 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 const uint32_t slot = SmemAddr(exchange) + (((rank << lshift) + (row & (rows_per_cta - 1))) * BQ) * 4;
                 const uint32_t remote = MapToRank(slot, owner);
                 const uint32_t remote_bar = MapToRank(SmemAddr(x_full), owner);
+                for (int w = 0; w < tiles_here; ++w) {
 #pragma unroll
-                for (int c0 = 0; c0 < BQ; c0 += 16) {
-                    if (c0 >= m) break;  // uniform
-                    uint32_t v[16];
-                    umma::TmemLoad16(taddr + c0, v);
-                    umma::TmemLoadWait();
+                    for (int c0 = 0; c0 < BQ; c0 += 16) {
+                        if (c0 >= m) break;  // uniform
+                        uint32_t v[16];
+                        umma::TmemLoad16(taddr + w * BQ + c0, v);
+                        umma::TmemLoadWait();
 #pragma unroll
-                    for (int j = 0; j < 16; j += 4) {
-                        if (c0 + j < m) StoreClusterAsync4(remote + (c0 + j) * 4, remote_bar, v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        for (int j = 0; j < 16; j += 4) {
+                            if (c0 + j < m)
+                                StoreClusterAsync4(remote + w * C::kExchangeBytes + (c0 + j) * 4, remote_bar, v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        }
                     }
                 }
             }
@@ -479,33 +489,46 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         if constexpr (DEC) {
             // One output per thread and round, as below, written out for BF16 <- E4M3 / E5M2 <- FP32 with per-tensor scales:
             // product scale, output Cast (encode, decode, BF16 rounding), then the fused Add node's own rounding point.
-            const bool second = tile >= static_cast<int>(p.p_tiles_first);  // this CTA's tile belongs to the second weight
-            const float mult = second ? fu.ab_scale2 : fe.ab_scale;
-            const int64_t ldo = second ? fu.ldo2 : fe.ldo;
-            uint16_t* out = static_cast<uint16_t*>(second ? fu.out2 : fe.out);
-            const uint16_t* residual = second ? nullptr : static_cast<const uint16_t*>(fu.residual);
+            const bool dual = tiles_here > 1;
+            const float mult[2] = {fe.ab_scale, fu.ab_scale2};
+            uint16_t* out = static_cast<uint16_t*>(fe.out);
+            const uint16_t* residual = static_cast<const uint16_t*>(fu.residual);
             const int64_t n_base = static_cast<int64_t>(tile) * kBlockP + (static_cast<int64_t>(rank) << lshift);
-            const int64_t n_shift = second ? fu.n_first : 0;
             const int total = m << lshift;
+            // the BF16 bits of one projection output: chunks added in chunk order, product scale, output Cast
+            auto project = [&](int w, int r, int q) -> uint16_t {
+                const uint32_t* part = exchange + w * (C::kExchangeBytes / 4);
+                uint32_t t[8];
+#pragma unroll
+                for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? part[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
+                float sum = 0.0f;
+#pragma unroll
+                for (int ss = 0; ss < 8; ++ss) {
+                    if (ss < p.split) sum += __uint_as_float(t[ss]);  // no zero is ever added: it could flip a -0
+                }
+                const float scaled = __fmul_rn(sum, mult[w]);
+                const float y = p.out_inv != 0.0f ? __fmul_rn(scaled, p.out_inv) : __fdiv_rn(scaled, fe.out_scale);
+                const uint32_t code = EncodePair(p.e4m3, y, 0.0f) & 0xffu;
+                return EncodeBf16Cast(__fmul_rn(DecodeFast(p.e4m3, code), fe.out_scale));
+            };
             auto finish = [&](int item, bool early, uint16_t early_bits) {
                 if (!delivered || item >= total) return;
                 const int q = item >> lshift;
                 const int r = item & (rows_per_cta - 1);
                 const int64_t n = n_base + r;
                 if (n >= p.p_total) return;
-                uint32_t t[8];
-#pragma unroll
-                for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? exchange[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
-                float sum = 0.0f;
-#pragma unroll
-                for (int ss = 0; ss < 8; ++ss) {
-                    if (ss < p.split) sum += __uint_as_float(t[ss]);  // chunk order; no zero is ever added: it could flip a -0
+                uint16_t bits = project(0, r, q);
+                const int64_t o = q * fe.ldo + n;
+                if (dual) {
+                    const uint16_t bits2 = project(1, r, q);
+                    if (fu.epilogue == 1) {
+                        // the SiLU and Mul nodes behind gate and up, each with its BF16 rounding point
+                        bits = EncodeBf16Cast(__fmul_rn(DecodeBf16(rowops::SiluToBf16(DecodeBf16(bits))), DecodeBf16(bits2)));
+                    } else {
+                        static_cast<uint16_t*>(fu.out2)[q * fu.ldo2 + n] = bits2;
+                    }
                 }
-                const float scaled = __fmul_rn(sum, mult);
-                const float y = p.out_inv != 0.0f ? __fmul_rn(scaled, p.out_inv) : __fdiv_rn(scaled, fe.out_scale);
-                const uint32_t code = EncodePair(p.e4m3, y, 0.0f) & 0xffu;
-                uint16_t bits = EncodeBf16Cast(__fmul_rn(DecodeFast(p.e4m3, code), fe.out_scale));
-                const int64_t o = q * ldo + (n - n_shift);
+                // fused Add node behind the output Cast (the residual connection): one more BF16 rounding point
                 if (residual != nullptr) bits = EncodeBf16Cast(__fadd_rn(DecodeBf16(early ? early_bits : residual[o]), DecodeBf16(bits)));
                 out[o] = bits;
             };
@@ -573,7 +596,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         umma::FenceAfterThreadSync();
-        umma::TmemDealloc(tmem_base, C::kTmemCols);
+        umma::TmemDealloc(tmem_base, tmem_cols);
     }
 }
 
@@ -581,13 +604,13 @@ template <bool INT8, bool P_MN, int BQ, bool DEC>
 int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q, const TcParams& p_in,
                        const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     TcParams p = p_in;
-    p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks);
+    p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks * (DEC ? p.tiles_per_cta : 1));
     auto kernel = LinearClusterKernel<INT8, P_MN, BQ, DEC>;
     if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), ClusterCfg<BQ>::kSmemBytes) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(g.p_tiles * g.cluster));
     cfg.blockDim = dim3(ClusterCfg<BQ>::kThreads);
-    cfg.dynamicSmemBytes = ClusterCfg<BQ>::SmemFor(g.chunk_blocks);
+    cfg.dynamicSmemBytes = ClusterCfg<BQ>::SmemFor(g.chunk_blocks, DEC ? p.tiles_per_cta : 1);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -43,9 +43,8 @@ TcGeometry GeometryFor(const LinearArgs& a) {
     TcGeometry g;
     g.swap = a.m <= 128;
     g.bq = g.swap ? SwapBlockQ(a.m) : 256;
-    // a second weight that shares the activation (decoder-block fusion) lines its columns up behind the first one's
-    const int64_t n_all = a.n + (a.fusion.w2 != nullptr ? a.fusion.n2 : 0);
-    g.p_total = g.swap ? n_all : a.m;
+    // (a second weight that shares the activation, a decoder-block fusion, rides in the CTAs of the first one's tiles)
+    g.p_total = g.swap ? a.n : a.m;
     g.q_total = g.swap ? a.m : a.n;
     g.p_tiles = (g.p_total + kBlockP - 1) / kBlockP;
     g.q_tiles = (g.q_total + g.bq - 1) / g.bq;
@@ -64,8 +63,8 @@ TcGeometry GeometryFor(const LinearArgs& a) {
         int c = 1;
         while (c < g.split) c *= 2;
         // more than one wave of CTAs: the persistent kernel keeps its ring full across tiles and is faster (measured).
-        // Decoder-block fusions exist in this kernel only; its CTAs are small (several fit an SM), so twice the limit.
-        if (g.p_tiles * c <= static_cast<int64_t>(SmCount()) * (a.fusion.active() ? 4 : 2)) g.cluster = c;
+        // Decoder-block fusions exist in this kernel only; its CTAs are small (several fit an SM), so a higher limit.
+        if (g.p_tiles * c <= static_cast<int64_t>(SmCount()) * (a.fusion.active() ? 3 : 2)) g.cluster = c;
     }
     return g;
 }
@@ -155,9 +154,11 @@ int Tcgen05FusionStatus(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, c
     if (fu.prologue == 1 && (fu.norm_weight_dtype != FTH_B200_BF16 && fu.norm_weight_dtype != FTH_B200_FP32)) return FTH_B200_ERR_UNSUPPORTED;
     if (fu.prologue == 1 && a.k > rowops_max_hidden()) return FTH_B200_ERR_UNSUPPORTED;
     if (fu.prologue == 2 && fu.a2 == nullptr) return FTH_B200_ERR_INVALID;
+    if (fu.epilogue < 0 || fu.epilogue > 1 || (fu.epilogue == 1 && (fu.w2 == nullptr || fu.residual != nullptr))) return FTH_B200_ERR_INVALID;
     if (fu.w2 != nullptr) {
-        if (fu.n2 <= 0 || fu.out2 == nullptr || fu.ldo2 < fu.n2) return FTH_B200_ERR_INVALID;
-        if (a.n % kBlockP != 0 || reinterpret_cast<uintptr_t>(fu.w2) % 16 != 0 || (!a.trans_b && fu.n2 % 16 != 0)) return FTH_B200_ERR_UNSUPPORTED;
+        if (fu.n2 != a.n) return FTH_B200_ERR_INVALID;  // the two weights' columns pair up
+        if (fu.epilogue == 0 && (fu.out2 == nullptr || fu.ldo2 < fu.n2)) return FTH_B200_ERR_INVALID;
+        if (reinterpret_cast<uintptr_t>(fu.w2) % 16 != 0) return FTH_B200_ERR_UNSUPPORTED;
     }
     return FTH_B200_OK;
 }
@@ -222,7 +223,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     p.p_total = g.p_total; p.q_total = g.q_total; p.p_tiles = g.p_tiles; p.q_tiles = g.q_tiles;
     p.ring_stages = 0;
     p.split = g.split; p.chunk_blocks = g.chunk_blocks; p.k_blocks = g.k_blocks; p.units = g.units;
-    p.p_tiles_first = a.fusion.w2 != nullptr ? a.n / kBlockP : g.p_tiles;
+    p.tiles_per_cta = a.fusion.w2 != nullptr ? 2 : 1;
     p.p_pad = g.p_pad;
     p.e4m3 = dtype == FTH_B200_FP8E4M3;
     if (int8) p.fast = ie.bias_mode == FTH_B200_BIAS_NONE && ie.out_dtype == 0 && !(ie.is_gemm && (ie.alpha != 1.0f || ie.beta != 1.0f));

@@ -7,7 +7,7 @@ projections wrapped in Cast nodes, QwenRmsNorm with weight offset 1, SiLU * Mul 
     h = QwenRmsNorm(x, g2);  a = Mul(SiLU(gate(h)), up(h));  x = Add(x, down(a))
 
 `fused=True` issues six launches per layer through fth_b200_fp8_linear_fused — norm + q, k, v, o + residual,
-norm + gate | up (one launch, two weights), SiLU * Mul + down + residual; `fused=False` issues every node's own kernel
+norm + gate | up + SiLU * Mul (one launch, two weights), down + residual; `fused=False` issues every node's own kernel
 (twelve launches per layer: fth_b200_qwen_rms_norm, the Cast -> MatMul -> Cast projections, fth_b200_binary,
 fth_b200_silu_mul).  Both give the same bytes.  Everything stays on the device; the caller may capture `run` in a CUDA
 graph.  torch supplies the device buffers only.
@@ -67,8 +67,9 @@ class DecoderStep:
                 self._fused(self._proj(self.t[0], layer["o"], layer["o_scale"], nxt, H, H), residual=x)
                 x, nxt = nxt, x
                 self._fused(self._proj(x, layer["gate"], layer["gate_scale"], self.gate, H, I), prologue=B.FUSE_RMS_NORM, norm_weight=layer["g2"],
-                            norm_weight_offset=1.0, norm_epsilon=self.eps, w2=layer["up"], w2_scale=layer["up_scale"], out2=self.up, n2=I)
-                self._fused(self._proj(self.gate, layer["down"], layer["down_scale"], nxt, I, H), prologue=B.FUSE_SILU_MUL, a2=self.up, residual=x)
+                            norm_weight_offset=1.0, norm_epsilon=self.eps, w2=layer["up"], w2_scale=layer["up_scale"], n2=I,
+                            epilogue=B.FUSE_OUT_SILU_MUL)
+                self._fused(self._proj(self.gate, layer["down"], layer["down_scale"], nxt, I, H), residual=x)
                 x, nxt = nxt, x
             else:
                 self.calls.append(("norm", (x, layer["g1"], self.h), None))

@@ -114,6 +114,29 @@ def test_silu_and_silu_mul(cuda, dtype):
     assert B.last_variant() == "silu_mul" and B.device_status() == 0
 
 
+def test_silu_bf16_every_input(cuda):
+    """All 65536 BF16 inputs.  The BF16 kernels take a short path (FP32 expf, and the exact evaluation only where the
+    quotient sits next to a rounding boundary): it must give the bits of the exact evaluation everywhere, and those are
+    the oracle's up to the rare last-place difference between the C library's expf and the correctly rounded one."""
+    x = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    xf = (x.astype(np.uint32) << 16).view(np.float32)
+    finite = np.isfinite(xf)
+    out16 = cuda.zeros(x.size, dtype=cuda.int16, device="cuda")
+    out32 = cuda.zeros(x.size, dtype=cuda.float32, device="cuda")
+    B.silu(B.BF16, dev(cuda, x.view(np.int16)), out16, x.size)
+    B.silu(B.FP32, dev(cuda, xf), out32, x.size)
+    cuda.cuda.synchronize()
+    got = out16.cpu().numpy().view(np.uint16)
+    exact = G.to_bf16(out32.cpu().numpy())
+    assert np.array_equal(got[finite], exact[finite]), f"{int((got[finite] != exact[finite]).sum())} inputs leave the short path with other bits"
+    nan = np.isnan(xf)
+    assert np.isnan((got[nan].astype(np.uint32) << 16).view(np.float32)).all()
+    want = O.silu(B.BF16, x)
+    dist = _steps(got[finite], want[finite])
+    print(f"silu over every finite BF16 input: {int((dist > 0).sum())} of {int(finite.sum())} differ from the oracle, max {int(dist.max())} step(s)")
+    assert dist.max() <= 1 and (dist > 0).mean() < 1e-3
+
+
 def test_rejections(cuda):
     t = cuda.zeros(64, dtype=cuda.float32, device="cuda")
     lib = B.lib()

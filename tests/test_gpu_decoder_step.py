@@ -112,6 +112,48 @@ def test_every_layer_from_the_oracles_input(cuda, stack_weights, m, fused):
           f"{total_diff} of {24 * m * D.HIDDEN} BF16 outputs differ (worst layer {100 * worst_frac:.3f} %)")
 
 
+@pytest.mark.parametrize("m,k,n", [(1, 1024, 3584), (16, 1024, 3584), (4, 512, 208), (32, 2048, 1024)])
+def test_two_weights_in_one_launch(cuda, m, k, n):
+    """gate and up on one activation: one launch gives the two separate launches' bytes; with the SiLU * Mul epilogue it
+    gives what fth_b200_silu_mul makes of them; and the down projection that starts from SiLU * Mul of two inputs
+    (prologue form) gives the bytes of the separate nodes as well."""
+    torch = cuda
+    rng = np.random.default_rng(m * 7 + n)
+    a = dev(torch, D.to_bf16(rng.standard_normal((m, k)).astype(np.float32)).view(np.int16))
+    w1 = dev(torch, rng.integers(0, 120, (k, n), dtype=np.uint8) | (rng.integers(0, 2, (k, n), dtype=np.uint8) << 7))
+    w2 = dev(torch, rng.integers(0, 120, (k, n), dtype=np.uint8) | (rng.integers(0, 2, (k, n), dtype=np.uint8) << 7))
+    outs = [torch.zeros((m, n), dtype=torch.int16, device="cuda") for _ in range(6)]
+    common = dict(dtype=B.E5M2, op=B.OP_MATMUL, m=m, k=k, n=n, a=a, a_scale=2.0 ** -7, out_scale=2.0 ** -6, a_dtype=B.BF16, out_dtype=B.BF16)
+    keep = []
+    for w, ws, out in ((w1, 2.0 ** -18, outs[0]), (w2, 2.0 ** -19, outs[1])):
+        d = B.fp8_linear_desc(w=w, w_scale=ws, out=out, **common)
+        keep.append(B.linear_workspace(torch, d))
+        B.fp8_linear(d)
+    B.silu_mul(B.BF16, outs[0], outs[1], outs[2], m * n)
+    d = B.fp8_linear_desc(w=w1, w_scale=2.0 ** -18, out=outs[3], **common)
+    B.fp8_linear_fused(d, B.fp8_linear_fusion(w2=w2, w2_scale=2.0 ** -19, out2=outs[4], n2=n))
+    d5 = B.fp8_linear_desc(w=w1, w_scale=2.0 ** -18, out=outs[5], **common)
+    B.fp8_linear_fused(d5, B.fp8_linear_fusion(w2=w2, w2_scale=2.0 ** -19, n2=n, epilogue=B.FUSE_OUT_SILU_MUL))
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
+    h = [o.cpu().numpy() for o in outs]
+    assert h[0].any() and h[1].any()
+    assert np.array_equal(h[3], h[0]) and np.array_equal(h[4], h[1])
+    assert np.array_equal(h[5], h[2]), f"{int((h[5] != h[2]).sum())} of {h[2].size} SiLU * Mul outputs differ"
+    # SiLU * Mul in front of a projection (K = n here): prologue form against the separate node
+    wd = dev(torch, rng.integers(0, 120, (n, 256), dtype=np.uint8))
+    o_plain = torch.zeros((m, 256), dtype=torch.int16, device="cuda")
+    o_fused = torch.zeros((m, 256), dtype=torch.int16, device="cuda")
+    base = dict(dtype=B.E5M2, op=B.OP_MATMUL, m=m, k=n, n=256, w=wd, a_scale=2.0 ** -7, w_scale=2.0 ** -18, out_scale=2.0 ** -6, a_dtype=B.BF16, out_dtype=B.BF16)
+    dp = B.fp8_linear_desc(a=outs[2], out=o_plain, **base)
+    keep.append(B.linear_workspace(torch, dp))
+    B.fp8_linear(dp)
+    B.fp8_linear_fused(B.fp8_linear_desc(a=outs[0], out=o_fused, **base), B.fp8_linear_fusion(prologue=B.FUSE_SILU_MUL, a2=outs[1]))
+    torch.cuda.synchronize()
+    assert B.device_status() == 0
+    assert np.array_equal(o_fused.cpu().numpy(), o_plain.cpu().numpy())
+
+
 def test_fused_call_rejections(cuda):
     torch = cuda
     a = torch.zeros((1, 1024), dtype=torch.int16, device="cuda")
@@ -128,3 +170,9 @@ def test_fused_call_rejections(cuda):
     big = B.fp8_linear_desc(a_dtype=B.BF16, out_dtype=B.BF16, **dict(base, m=64))
     assert sup(C.byref(big), C.byref(f)) == B.ERR_UNSUPPORTED                                             # not a decode-sized shape
     assert sup(C.byref(ok), None) == B.ERR_INVALID
+    w2 = dict(w2=w, w2_scale=1.0, n2=1024)
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(epilogue=B.FUSE_OUT_SILU_MUL))) == B.ERR_INVALID              # needs the second weight
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(epilogue=B.FUSE_OUT_SILU_MUL, residual=out, **w2))) == B.ERR_INVALID
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(epilogue=B.FUSE_OUT_SILU_MUL, **w2))) == B.OK             # out2 not needed
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(**w2))) == B.ERR_INVALID                                  # ... but needed here
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(out2=out, **dict(w2, n2=512)))) == B.ERR_INVALID          # columns must pair up
