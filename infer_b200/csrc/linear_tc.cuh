@@ -75,13 +75,16 @@ __device__ __forceinline__ void StoreOne(const Fp8Epilogue& fe, const Int8Epilog
     }
 }
 
+// Inf / NaN inputs of EncodePair: the software encoder, whose special codes are the reference's.  Kept out of line: the
+// callers sit on latency-bound paths that run once per CTA, where every instruction fetched counts.
+static __device__ __noinline__ uint32_t EncodePairSpecial(int e4m3, float y0, float y1) {
+    if (e4m3) return Encode<FTH_B200_FP8E4M3>(y0) | (static_cast<uint32_t>(Encode<FTH_B200_FP8E4M3>(y1)) << 8);
+    return Encode<FTH_B200_FP8E5M2>(y0) | (static_cast<uint32_t>(Encode<FTH_B200_FP8E5M2>(y1)) << 8);
+}
 // Encodes y0, y1 (already divided by the output scale) into two FP8 codes: low byte = y0, high byte = y1.
 __device__ __forceinline__ uint32_t EncodePair(int e4m3, float y0, float y1) {
     const bool special = ((__float_as_uint(y0) & 0x7f800000u) == 0x7f800000u) || ((__float_as_uint(y1) & 0x7f800000u) == 0x7f800000u);
-    if (special) {
-        if (e4m3) return Encode<FTH_B200_FP8E4M3>(y0) | (static_cast<uint32_t>(Encode<FTH_B200_FP8E4M3>(y1)) << 8);
-        return Encode<FTH_B200_FP8E5M2>(y0) | (static_cast<uint32_t>(Encode<FTH_B200_FP8E5M2>(y1)) << 8);
-    }
+    if (special) return EncodePairSpecial(e4m3, y0, y1);
     uint16_t packed;
     if (e4m3) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(packed) : "f"(y1), "f"(y0));
     else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(packed) : "f"(y1), "f"(y0));

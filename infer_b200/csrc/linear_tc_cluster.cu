@@ -107,15 +107,36 @@ __device__ __forceinline__ uint32_t CastFour(int e4m3, float a_scale, float a_in
 
 // decode(code) for the fused Cast behind the MatMul.  Finite codes widen exactly through FP16 in hardware; Inf / NaN
 // codes take the software path, whose NaN pattern is the reference's.
+static __device__ __noinline__ float DecodeSpecial(int e4m3, uint32_t code) {
+    return e4m3 ? Decode<FTH_B200_FP8E4M3>(static_cast<uint8_t>(code)) : Decode<FTH_B200_FP8E5M2>(static_cast<uint8_t>(code));
+}
 __device__ __forceinline__ float DecodeFast(int e4m3, uint32_t code) {
     const uint32_t mag = code & 0x7fu;
-    if (e4m3 ? mag == 0x7fu : mag >= 0x7cu)
-        return e4m3 ? Decode<FTH_B200_FP8E4M3>(static_cast<uint8_t>(code)) : Decode<FTH_B200_FP8E5M2>(static_cast<uint8_t>(code));
+    if (e4m3 ? mag == 0x7fu : mag >= 0x7cu) return DecodeSpecial(e4m3, code);
     const uint16_t in = static_cast<uint16_t>(code & 0xffu);
     uint32_t pair;
     if (e4m3) asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"(in));
     else asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(pair) : "h"(in));
     return __half2float(__ushort_as_half(static_cast<unsigned short>(pair & 0xffffu)));
+}
+
+// The decoder-block node in front of the Cast, for four elements, with its own BF16 rounding point(s): QwenRmsNorm
+// (x * inv * (weight + offset)) or Mul(SiLU(x), y).  Out of line: it keeps the four-item conversion loop short.
+static __device__ __noinline__ void DecoderNodeFour(int prologue, int weight_dtype, float offset, float inv, uint2 raw, uint4 raw2, float (&h)[4]) {
+    const float x[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                        __uint_as_float(raw.y & 0xffff0000u)};
+    float y[4];
+    WidenFour(prologue == 1 ? weight_dtype : FTH_B200_BF16, raw2, y);
+    if (prologue == 1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(__fmul_rn(x[i], inv), __fadd_rn(y[i], offset))));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float sv = DecodeBf16(rowops::SiluToBf16(x[i]));   // SiLU node
+            h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(sv, y[i])));   // Mul node
+        }
+    }
 }
 
 // DEC: the decoder-block form — FP8 product of BF16 activations, BF16 out, per-tensor scales, no bias, no peers, no
@@ -375,29 +396,11 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                         if (base + j * 128 < total) {
                             uint32_t word = 0u;
                             if (inside[j]) {
-                                float h[4];
-                                const float x[4] = {__uint_as_float(raw[j].x << 16), __uint_as_float(raw[j].x & 0xffff0000u),
-                                                    __uint_as_float(raw[j].y << 16), __uint_as_float(raw[j].y & 0xffff0000u)};
-                                if (prologue == 0) {
-#pragma unroll
-                                    for (int i = 0; i < 4; ++i) h[i] = x[i];
-                                } else {
-                                    // the decoder-block node in front of the Cast, with its own BF16 rounding point(s)
-                                    float y[4];
-                                    WidenFour(prologue == 1 ? fu.norm_weight_dtype : FTH_B200_BF16, raw2[j], y);
-                                    if (prologue == 1) {
-                                        const float inv = norm_inv[rows[j]];
-#pragma unroll
-                                        for (int i = 0; i < 4; ++i)
-                                            h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(__fmul_rn(x[i], inv), __fadd_rn(y[i], fu.norm_offset))));
-                                    } else {
-#pragma unroll
-                                        for (int i = 0; i < 4; ++i) {
-                                            const float sv = DecodeBf16(rowops::SiluToBf16(x[i]));                 // SiLU node
-                                            h[i] = DecodeBf16(EncodeBf16Cast(__fmul_rn(sv, y[i])));                 // Mul node
-                                        }
-                                    }
-                                }
+                                float h[4] = {__uint_as_float(raw[j].x << 16), __uint_as_float(raw[j].x & 0xffff0000u),
+                                              __uint_as_float(raw[j].y << 16), __uint_as_float(raw[j].y & 0xffff0000u)};
+                                if (prologue != 0)
+                                    DecoderNodeFour(prologue, fu.norm_weight_dtype, fu.norm_offset, prologue == 1 ? norm_inv[rows[j]] : 0.0f, raw[j],
+                                                    raw2[j], h);
                                 word = CastFour(p.e4m3, p.args.a_scale, p.a_inv, h);
                             }
                             asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst[j]), "r"(word) : "memory");
@@ -511,12 +514,13 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 const uint32_t code = EncodePair(p.e4m3, y, 0.0f) & 0xffu;
                 return EncodeBf16Cast(__fmul_rn(DecodeFast(p.e4m3, code), fe.out_scale));
             };
-            auto finish = [&](int item, bool early, uint16_t early_bits) {
-                if (!delivered || item >= total) return;
+            for (int base = 0; base < total; base += 128) {
+                const int item = base + et;
+                if (!delivered || item >= total) break;
                 const int q = item >> lshift;
                 const int r = item & (rows_per_cta - 1);
                 const int64_t n = n_base + r;
-                if (n >= p.p_total) return;
+                if (n >= p.p_total) continue;
                 uint16_t bits = project(0, r, q);
                 const int64_t o = q * fe.ldo + n;
                 if (dual) {
@@ -529,12 +533,12 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     }
                 }
                 // fused Add node behind the output Cast (the residual connection): one more BF16 rounding point
-                if (residual != nullptr) bits = EncodeBf16Cast(__fadd_rn(DecodeBf16(early ? early_bits : residual[o]), DecodeBf16(bits)));
+                if (residual != nullptr) {
+                    const uint16_t other = base == 0 ? residual_early[0] : base == 128 ? residual_early[1] : residual[o];
+                    bits = EncodeBf16Cast(__fadd_rn(DecodeBf16(other), DecodeBf16(bits)));
+                }
                 out[o] = bits;
-            };
-            finish(et, true, residual_early[0]);
-            if (total > 128) finish(128 + et, true, residual_early[1]);
-            for (int base = 256; base < total; base += 128) finish(base + et, false, 0);
+            }
         } else {
         // Column-sharded projection with the gather's signalling folded in: before the first store into the peers'
         // buffers every rank must have published the previous step.  The wait sits here, behind the whole weight

@@ -125,12 +125,13 @@ __device__ __forceinline__ float SiluValue(float x) {
 // same way on both paths, so the FP32 quotient is at most a few FP32 steps off, and the BF16 rounding of both is the
 // same unless the quotient sits that close to the midpoint between two BF16 values.  Those inputs, and Inf / NaN, take
 // the exact path.  (tests/test_gpu_decoder_ops.py runs all 65536 BF16 inputs.)
+static __device__ __noinline__ float SiluValueOutOfLine(float x) { return SiluValue(x); }
 __device__ __forceinline__ uint16_t SiluToBf16(float x) {
     const float e = expf(-x);
     float s = __fdiv_rn(x, __fadd_rn(1.0f, e));
     const uint32_t low = __float_as_uint(s) & 0xffffu;
     const bool finite = (__float_as_uint(x) & 0x7f800000u) != 0x7f800000u;
-    if (!finite || (low >= 0x7fc0u && low <= 0x8040u)) s = SiluValue(x);
+    if (!finite || (low >= 0x7fc0u && low <= 0x8040u)) s = SiluValueOutOfLine(x);
     return EncodeBf16Cast(s);
 }
 
