@@ -117,3 +117,48 @@ class DecoderStep:
     @property
     def launches(self):
         return len(self.calls)
+
+
+def _main():
+    """Runs the synthetic stack a few times with random weights and prints the time per step (CUDA events), e.g. as the
+    workload of a profiler capture: python -m infer_b200.decoder_step --m 16 --layers 4"""
+    import argparse
+
+    import torch
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--hidden", type=int, default=1024)
+    ap.add_argument("--inter", type=int, default=3584)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--nodes", action="store_true", help="every node as its own launch instead of the fused calls")
+    args = ap.parse_args()
+    H, I = args.hidden, args.inter
+    shapes = {"q": (H, H), "k": (H, H), "v": (H, H), "o": (H, H), "gate": (H, I), "up": (H, I), "down": (I, H)}
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    weights = []
+    for _ in range(args.layers):
+        layer = {}
+        for name, (k, n) in shapes.items():
+            layer[name] = torch.randint(0, 120, (k, n), dtype=torch.uint8, device="cuda", generator=gen)
+            layer[name + "_scale"] = 2.0 ** -20
+        for g in ("g1", "g2"):
+            layer[g] = (torch.randn(H, device="cuda", generator=gen) * 0.1).to(torch.bfloat16).view(torch.int16)
+        weights.append(layer)
+    step = DecoderStep(torch, weights, args.m, H, I, 2.0 ** -9, 2.0 ** -9, fused=not args.nodes)
+    step.x.copy_(torch.randn((args.m, H), device="cuda", generator=gen).to(torch.bfloat16).view(torch.int16))
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    step.run()
+    torch.cuda.synchronize()
+    begin.record()
+    for _ in range(args.steps):
+        step.run()
+    end.record()
+    torch.cuda.synchronize()
+    print(f"m={args.m} layers={args.layers} launches/step={step.launches} {begin.elapsed_time(end) / args.steps * 1e3:.1f} us/step "
+          f"(stream launches, no graph) status={B.device_status()}")
+
+
+if __name__ == "__main__":
+    _main()
