@@ -36,6 +36,13 @@ struct TcParams {
     int* status;
 };
 
+// Tensor maps of the output block in this GPU's buffer ([0]) and in the peers' replicas, for the CTA-pair kernel's tile
+// stores (count 0: the epilogue stores from registers instead).
+struct OutMaps {
+    CUtensorMap map[kMaxPeers + 1];
+    int count;
+};
+
 constexpr int kClusterQBlocks = 8;  // K blocks of activations the cluster kernel keeps resident per CTA
 
 struct TcGeometry {
@@ -52,8 +59,8 @@ struct TcGeometry {
 int LaunchSwapped(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p,
                   const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream);
 // M > 128: CTA pairs.  map_a: activations, box {128 B of K, 128 rows}; map_w: weights, box of 128 columns.
-int LaunchPair(bool int8, bool weights_mn, const CUtensorMap& map_a, const CUtensorMap& map_w, const TcParams& p, const Fp8Epilogue& fe,
-               const Int8Epilogue& ie, cudaStream_t stream);
+int LaunchPair(bool int8, bool weights_mn, const CUtensorMap& map_a, const CUtensorMap& map_w, const OutMaps& out_maps, const TcParams& p,
+               const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream);
 // M <= 32, one wave: single-launch cluster kernel.
 int LaunchCluster(bool int8, const TcGeometry& g, bool weights_mn, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q,
                   const TcParams& p, const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream);

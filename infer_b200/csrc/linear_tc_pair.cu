@@ -17,12 +17,21 @@ namespace {
 //   warp 0 (each CTA)   TMA producer for the CTA's own A / B halves; bytes are reported to the LEADER's full barrier
 //   warp 1 (leader)     MMA issue; tcgen05.commit multicast frees the stage in both CTAs / publishes the accumulator
 //   warps 2-9 (each)    epilogue of the CTA's own 128 rows; buffers are handed back on the leader's barrier
+//
+// Column shards with replicas on other GPUs: 16-byte stores from registers, one row per lane, cross NVLink as 16-byte
+// writes (measured 105-135 GB/s per GPU, so the sharded M = 4096 step was slower than the unsharded one).  With replicas
+// the epilogue therefore puts the CTA's 128 x 256 output tile into shared memory (the sixth ring stage is given up for
+// it) and one thread sends it to this GPU's buffer and to every replica as tile stores (cp.async.bulk.tensor, no
+// multicast): full rows of 256 bytes per request, and the copy of tile i overlaps the MMAs and the epilogue of tile i+1.
 // ---------------------------------------------------------------------------------------------------------
 struct PairCfg {
     static constexpr int kTileN = 256;
     static constexpr int kHalfN = 128;                          // B columns staged by one CTA
     static constexpr int kStageBytes = kPBytes + kHalfN * kBlockK;  // 32 KB
     static constexpr int kStages = 6;
+    static constexpr int kStagesWithTileStores = 5;             // the last stage's 32 KB hold the output tile
+    static constexpr int kOutTileBytes = kBlockP * kTileN;      // 128 rows x 256 one-byte outputs
+    static_assert(kOutTileBytes <= kStageBytes, "the output tile takes the place of one ring stage");
     static constexpr uint32_t kTmemCols = 512;                  // two 256-column accumulator buffers
     static constexpr int kEpilogueThreads = 256;
     static constexpr int kThreads = 64 + kEpilogueThreads;
@@ -31,8 +40,8 @@ struct PairCfg {
 
 template <bool INT8, bool Q_MN>
 __global__ void __launch_bounds__(PairCfg::kThreads, 1)
-LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, TcParams p,
-                 Fp8Epilogue fe, Int8Epilogue ie) {
+LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                 const __grid_constant__ OutMaps out_maps, TcParams p, Fp8Epilogue fe, Int8Epilogue ie) {
     using C = PairCfg;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -48,6 +57,9 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t rank = ClusterRank();           // 0 = leader
     const bool leader = rank == 0;
+    const bool tile_stores = out_maps.count > 0;
+    const int stages = tile_stores ? C::kStagesWithTileStores : C::kStages;
+    uint8_t* out_tile = ring + static_cast<size_t>(C::kStagesWithTileStores) * C::kStageBytes;  // [128][256], only with tile_stores
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) { MbarInit(&full[s], 1); MbarInit(&empty[s], 1); }
@@ -95,7 +107,7 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                     TmaLoad2DPair(ps, &map_p, k0, p0, bar);
                     if constexpr (Q_MN) TmaLoad2DPair(qs, &map_q, q0, k0, bar);
                     else TmaLoad2DPair(qs, &map_q, k0, q0, bar);
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -123,7 +135,7 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                         umma::MmaPair<INT8>(d_tmem, a_desc, b_desc, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
                     }
                     umma::CommitPair(&empty[stage], 3);  // the stage is free in both CTAs once these MMAs have read it
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
                 if (!failed) umma::CommitPair(&tmem_full[acc], 3);
             }
@@ -180,6 +192,10 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             }
             if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 33, acc)) failed = true;
             umma::FenceAfterThreadSync();
+            if (tile_stores) {  // the stores of the previous tile must have read the shared-memory tile before it is rewritten
+                if (et == 0) BulkWaitGroupRead0();
+                EpilogueBarrier<C::kEpilogueThreads>();
+            }
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * C::kTileN);
 #pragma unroll 1
             for (int c0 = col_group * 128; c0 < (col_group + 1) * 128; c0 += 16) {
@@ -219,7 +235,15 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                     }
                 }
                 uint8_t* dst = out8 + mg * ldo + n_begin + c0;
-                if (cnt == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                if (tile_stores) {
+                    // columns past the end of the row and rows past M are never written: the tile store clips them
+                    uint4 w;
+                    w.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+                    w.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+                    w.z = b[8] | (b[9] << 8) | (b[10] << 16) | (b[11] << 24);
+                    w.w = b[12] | (b[13] << 8) | (b[14] << 16) | (b[15] << 24);
+                    *reinterpret_cast<uint4*>(out_tile + row * C::kTileN + c0) = w;
+                } else if (cnt == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                     uint4 w;
                     w.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
                     w.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
@@ -234,6 +258,19 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             umma::FenceBeforeThreadSync();
             __syncwarp();
             if (lane == 0) MbarArriveRemote(leader_empty + acc * 8);
+            if (tile_stores) {
+                FenceProxyAsync();  // this thread's writes to the tile, visible to the copy engine
+                EpilogueBarrier<C::kEpilogueThreads>();
+                if (et == 0 && !failed) {
+                    const int32_t x = static_cast<int32_t>(n_begin), y = static_cast<int32_t>(mt * 256 + rank * 128);
+                    for (int d = 0; d < out_maps.count; ++d) TmaStore2D(&out_maps.map[d], out_tile, x, y);
+                    BulkCommitGroup();
+                }
+            }
+        }
+        if (tile_stores && et == 0) {
+            BulkWaitGroup0();                                  // every tile is written, here and in the replicas
+            asm volatile("fence.proxy.async;" ::: "memory");   // ... and ordered in front of what this thread does next (the step flag)
         }
         if (p.args.signal.world > 0) {
             EpilogueBarrier<C::kEpilogueThreads>();
@@ -254,7 +291,7 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
 }
 
 template <bool INT8, bool Q_MN>
-int LaunchPairTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const TcParams& p, const Fp8Epilogue& fe,
+int LaunchPairTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const OutMaps& out_maps, const TcParams& p, const Fp8Epilogue& fe,
                     const Int8Epilogue& ie, cudaStream_t stream) {
     auto kernel = LinearPairKernel<INT8, Q_MN>;
     if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), PairCfg::kSmemBytes) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
@@ -275,19 +312,19 @@ int LaunchPairTyped(const CUtensorMap& map_p, const CUtensorMap& map_q, const Tc
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    if (cudaLaunchKernelEx(&cfg, kernel, map_p, map_q, p, fe, ie) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    if (cudaLaunchKernelEx(&cfg, kernel, map_p, map_q, out_maps, p, fe, ie) != cudaSuccess) return FTH_B200_ERR_CUDA;
     NoteLaunch("tcgen05");
     return CheckLaunch();
 }
 
 }  // namespace
 
-int LaunchPair(bool int8, bool weights_mn, const CUtensorMap& map_a, const CUtensorMap& map_w, const TcParams& p, const Fp8Epilogue& fe,
-               const Int8Epilogue& ie, cudaStream_t stream) {
-    if (int8) return weights_mn ? LaunchPairTyped<true, true>(map_a, map_w, p, fe, ie, stream)
-                                : LaunchPairTyped<true, false>(map_a, map_w, p, fe, ie, stream);
-    return weights_mn ? LaunchPairTyped<false, true>(map_a, map_w, p, fe, ie, stream)
-                      : LaunchPairTyped<false, false>(map_a, map_w, p, fe, ie, stream);
+int LaunchPair(bool int8, bool weights_mn, const CUtensorMap& map_a, const CUtensorMap& map_w, const OutMaps& out_maps, const TcParams& p,
+               const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
+    if (int8) return weights_mn ? LaunchPairTyped<true, true>(map_a, map_w, out_maps, p, fe, ie, stream)
+                                : LaunchPairTyped<true, false>(map_a, map_w, out_maps, p, fe, ie, stream);
+    return weights_mn ? LaunchPairTyped<false, true>(map_a, map_w, out_maps, p, fe, ie, stream)
+                      : LaunchPairTyped<false, false>(map_a, map_w, out_maps, p, fe, ie, stream);
 }
 
 }  // namespace tc

@@ -245,7 +245,21 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
         CUtensorMap map_w_half = map_w;
         if (!weights_mn && !CachedMap(&map_w_half, a.w, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), 128, 128)) return FTH_B200_ERR_CUDA;
         p.idesc = umma::InstrDesc(int8 ? 2u : 1u, fmt, fmt, false, q_mn, 256, 256);
-        return LaunchPair(int8, weights_mn, map_a, map_w_half, p, fe, ie, stream);
+        // Replicas on other GPUs, native one-byte output: whole tiles leave through tile stores (see linear_tc_pair.cu).
+        OutMaps out_maps = {};
+        uint8_t* out = static_cast<uint8_t*>(int8 ? ie.out : fe.out);
+        const int64_t ldo = int8 ? ie.ldo : fe.ldo;
+        bool tile_stores = a.peers.count > 0 && p.fast && ldo % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+        for (int r = 0; r < a.peers.count; ++r) tile_stores = tile_stores && a.peers.delta[r] % 16 == 0;
+        if (tile_stores) {
+            for (int d = 0; d <= a.peers.count; ++d) {
+                const uint8_t* base = d == 0 ? out : out + a.peers.delta[d - 1];
+                if (!MakeTensorMap2D(&out_maps.map[d], base, static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m), static_cast<uint64_t>(ldo),
+                                     256, kBlockP, TmaSwizzle::kNone)) return FTH_B200_ERR_CUDA;
+            }
+            out_maps.count = a.peers.count + 1;
+        }
+        return LaunchPair(int8, weights_mn, map_a, map_w_half, out_maps, p, fe, ie, stream);
     }
     return LaunchSwapped(int8, g, weights_mn, map_p, map_q, p, fe, ie, stream);
 }

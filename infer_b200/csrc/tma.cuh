@@ -129,6 +129,18 @@ __device__ __forceinline__ void TmaLoad4D(void* smem_dst, const CUtensorMap* map
         ::"r"(SmemAddr(smem_dst)), "l"(map), "r"(SmemAddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// Tile store from shared memory (dense rows of the box's width, no swizzle) to global memory, this GPU's or a peer's;
+// the part of the box outside the tensor is not written.  Stores of one thread are grouped with BulkCommitGroup;
+// BulkWaitGroupRead0 returns when every committed group has read its shared memory (the buffer may be overwritten),
+// BulkWaitGroup0 when their writes are complete.
+__device__ __forceinline__ void TmaStore2D(const CUtensorMap* map, const void* smem_src, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(SmemAddr(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void BulkCommitGroup() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void BulkWaitGroupRead0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void BulkWaitGroup0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void TmaPrefetchDescriptor(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

@@ -19,9 +19,11 @@ def cuda():
     return torch
 
 
-# (m, k, n, variant): cluster kernel, two-kernel split path, CTA-pair dense kernel, CUDA-core kernels
+# (m, k, n, variant): cluster kernel, two-kernel split path, CTA-pair dense kernel (ragged tile; four tiles per CTA pair, so
+# the shared-memory tile behind its tile stores is reused), CUDA-core kernels
 CASES = [(1, 1024, 2048, B.VARIANT_AUTO), (16, 8192, 8192, B.VARIANT_AUTO), (48, 2048, 4096, B.VARIANT_AUTO),
-         (300, 512, 640, B.VARIANT_AUTO), (4, 256, 384, B.VARIANT_SKINNY), (3, 96, 80, B.VARIANT_SIMT)]
+         (300, 512, 640, B.VARIANT_AUTO), (512, 256, 256 * 74 * 2, B.VARIANT_AUTO), (4, 256, 384, B.VARIANT_SKINNY),
+         (3, 96, 80, B.VARIANT_SIMT)]
 
 
 @pytest.mark.parametrize("m,k,n,variant", CASES)
@@ -58,9 +60,9 @@ def test_fp8_output_reaches_every_replica(cuda, m, k, n, variant):
     del ws
 
 
-def test_int8_output_reaches_every_replica(cuda):
+@pytest.mark.parametrize("m,k,n", [(8, 1024, 1024), (300, 512, 1280)])
+def test_int8_output_reaches_every_replica(cuda, m, k, n):
     torch = cuda
-    m, k, n = 8, 1024, 1024
     rng = np.random.default_rng(5)
     a = torch.from_numpy(rng.integers(-127, 128, (m, k), dtype=np.int8)).cuda()
     w = torch.from_numpy(rng.integers(-127, 128, (k, n), dtype=np.int8)).cuda()
@@ -75,6 +77,12 @@ def test_int8_output_reaches_every_replica(cuda):
     torch.cuda.synchronize()
     host = [b.cpu().numpy() for b in bufs]
     assert (host[0] != 77).any() and np.array_equal(host[0], host[1]) and np.array_equal(host[0], host[2])
+    d.gather_peers = 0  # the same call without replicas (stores from registers) gives the same block
+    plain = torch.full((m, n), 77, dtype=torch.int8, device="cuda")
+    d.out = plain.data_ptr()
+    B.int8_linear(d)
+    torch.cuda.synchronize()
+    assert np.array_equal(plain.cpu().numpy(), host[0])
     del ws
 
 
