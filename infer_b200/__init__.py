@@ -12,7 +12,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfth_b200.so")
+# FTH_B200_LIBRARY names another build of the same library (an instrumented or experimental one); default: the in-tree build
+LIB_PATH = os.environ.get("FTH_B200_LIBRARY") or os.path.join(_HERE, "libfth_b200.so")
 
 INT8, FP16, FP32, INT32, BF16, E4M3, E5M2 = 1, 3, 4, 5, 11, 12, 13
 OP_FC, OP_MATMUL, OP_GEMM = 0, 1, 2

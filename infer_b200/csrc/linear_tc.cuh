@@ -167,12 +167,15 @@ __device__ __forceinline__ void GatherWaitPrevious(const GatherSignal& g, int r,
     }
 }
 // Called by ONE thread of every thread block of the launch, after a block-wide barrier behind the block's output
-// stores: the barrier orders the other threads' stores before this thread, whose system-scope fence then orders them
-// (cumulatively) before its arrival.  The last block to arrive advances the step counter and publishes the step in
-// every rank's array.
+// stores.  The barrier orders the other threads' stores before this thread; its fence and arrival are a release at GPU
+// scope (all blocks of the launch are on this GPU), the last block's read of the counter and its system-scope fence
+// acquire every arrival and release, cumulatively, all blocks' stores to the other GPUs before the flags below.  Only
+// that one fence has to wait for the peers to acknowledge the stores: a system-scope fence in every block cost 5 us
+// per step on eight GPUs (15.0 -> 10.2 us), all blocks draining their own stores at the same time.  The last block
+// advances the step counter and publishes the step in every rank's array.
 __device__ __forceinline__ void GatherArriveAndPublish(const GatherSignal& g, uint32_t step, unsigned blocks) {
     uint32_t* mine = g.flags[g.rank];
-    __threadfence_system();
+    __threadfence();
     const unsigned arrived = atomicAdd(mine + g.world + 1, 1u);
     if (arrived != blocks - 1) return;
     __threadfence_system();  // the other blocks' stores (ordered before their arrivals) before the flags below

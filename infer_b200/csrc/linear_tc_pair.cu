@@ -263,7 +263,14 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                 EpilogueBarrier<C::kEpilogueThreads>();
                 if (et == 0 && !failed) {
                     const int32_t x = static_cast<int32_t>(n_begin), y = static_cast<int32_t>(mt * 256 + rank * 128);
-                    for (int d = 0; d < out_maps.count; ++d) TmaStore2D(&out_maps.map[d], out_tile, x, y);
+                    // The destinations are taken in an order that differs from pair to pair and from tile to tile: every GPU
+                    // runs this loop at the same time, and all of them starting with the same replica would queue up
+                    // on that GPU's links while the others idle.
+                    const int first = static_cast<int>((pair_id + iter + p.args.signal.rank) % out_maps.count);
+                    for (int i = 0; i < out_maps.count; ++i) {
+                        const int d = first + i < out_maps.count ? first + i : first + i - out_maps.count;
+                        TmaStore2D(&out_maps.map[d], out_tile, x, y);
+                    }
                     BulkCommitGroup();
                 }
             }
