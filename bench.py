@@ -335,7 +335,10 @@ class LinearCase:
         ctx = self.ctx
         if ctx.peer_ok:
             try:
-                self.gather = PeerGather(ctx.B.lib(), ctx.dist, ctx.world, ctx.rank, self.m, N)  # raises on every rank or on none
+                # symmetric memory first (it brings an NVLink multicast address where the box has NVLS), CUDA IPC otherwise;
+                # FTH_B200_NO_MULTICAST=1 keeps to the IPC buffers (A/B).  Raises on every rank or on none.
+                self.gather = PeerGather(ctx.B.lib(), ctx.dist, ctx.world, ctx.rank, self.m, N,
+                                         torch=None if os.environ.get("FTH_B200_NO_MULTICAST") == "1" else ctx.torch)
                 # the kernels do the step signalling themselves (gather_world in the descriptors): no extra launch per step
                 self.prepared = [tuple(point_at_step_buffers(ctx.shard, self.gather, type(d).from_buffer_copy(d), parity, fold_signal=True)
                                        for parity in (0, 1)) for d in self.descs]
@@ -548,7 +551,12 @@ def sweep(ctx, peaks, quick):
                 rec["whole_job_weight_GB/s"] = round(K * N / (ms * 1e-3) / 1e9, 1)
                 rec["nvlink_bytes_out_per_rank_per_step"] = m * n_local * (ctx.world - 1)
                 rec["nvlink_GB/s_out_per_rank"] = round(m * n_local * (ctx.world - 1) / (ms * 1e-3) / 1e9, 1)
-                rec["gather"] = "peer stores + flag wait" if case.gather is not None else "NCCL all-gather"
+                if case.gather is None:
+                    rec["gather"] = "NCCL all-gather"
+                elif case.gather.multicast and m > 128:
+                    rec["gather"] = "one multicast store per output tile (NVLS) + flag wait"
+                else:
+                    rec["gather"] = "peer stores + flag wait"
             out[f"{kind}_m{m}"] = rec
             case.close()
             del case

@@ -137,6 +137,13 @@ typedef struct {
     int32_t gather_world;
     int32_t gather_rank;
     void* gather_flags[8];
+    /* Optional, with gather_peers > 0: the address that corresponds to `out` in an NVLink multicast mapping (NVLS) that
+     * covers the output buffers of ALL ranks, this rank's included — one store there is delivered to every GPU by the
+     * switch, so a rank's output crosses its links once instead of gather_peers times.  Used by the dense (M > 128)
+     * kernel for one-byte outputs when n is a multiple of 16; every other kernel keeps storing to gather_out[], which
+     * must still be filled in.  Null: not available.  (The mapping itself is the host's business: cuMulticastCreate /
+     * cuMulticastBindMem, or torch.distributed._symmetric_memory as infer_b200/sharded.py does.) */
+    void* gather_multicast_out;
 } fth_b200_fp8_linear_desc;
 
 int fth_b200_fp8_linear(const fth_b200_fp8_linear_desc* desc, fth_b200_stream_t stream);
@@ -262,6 +269,7 @@ typedef struct {
     int32_t gather_world;   /* as in fth_b200_fp8_linear_desc */
     int32_t gather_rank;
     void* gather_flags[8];
+    void* gather_multicast_out;   /* as in fth_b200_fp8_linear_desc */
 } fth_b200_int8_linear_desc;
 
 int fth_b200_int8_linear(const fth_b200_int8_linear_desc* desc, fth_b200_stream_t stream);

@@ -49,7 +49,7 @@ class Fp8LinearDesc(C.Structure):
         ("w_channel_scales", C.c_void_p), ("alpha", C.c_float), ("beta", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32), ("weights_static", C.c_int32),
         ("gather_peers", C.c_int32), ("gather_out", C.c_void_p * 7),
-        ("gather_world", C.c_int32), ("gather_rank", C.c_int32), ("gather_flags", C.c_void_p * 8),
+        ("gather_world", C.c_int32), ("gather_rank", C.c_int32), ("gather_flags", C.c_void_p * 8), ("gather_multicast_out", C.c_void_p),
     ]
 
 
@@ -75,7 +75,7 @@ class Int8LinearDesc(C.Structure):
         ("alpha", C.c_float), ("beta", C.c_float), ("bias_max_abs", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("variant", C.c_int32), ("weights_static", C.c_int32),
         ("gather_peers", C.c_int32), ("gather_out", C.c_void_p * 7),
-        ("gather_world", C.c_int32), ("gather_rank", C.c_int32), ("gather_flags", C.c_void_p * 8),
+        ("gather_world", C.c_int32), ("gather_rank", C.c_int32), ("gather_flags", C.c_void_p * 8), ("gather_multicast_out", C.c_void_p),
     ]
 
 

@@ -173,12 +173,15 @@ size_t WorkspaceFor(int variant, int dtype, const LinearArgs& args) {
 template <typename Desc>
 int BuildPeers(const Desc* d, PeerOut* peers) {
     peers->count = 0;
+    peers->multicast_delta = 0;
     if (d->gather_peers < 0 || d->gather_peers > kMaxPeers) return FTH_B200_ERR_INVALID;
     for (int r = 0; r < d->gather_peers; ++r) {
         if (d->gather_out[r] == nullptr) return FTH_B200_ERR_INVALID;
         peers->delta[r] = static_cast<int64_t>(reinterpret_cast<intptr_t>(d->gather_out[r]) - reinterpret_cast<intptr_t>(d->out));
     }
     peers->count = d->gather_peers;
+    if (d->gather_peers > 0 && d->gather_multicast_out != nullptr)
+        peers->multicast_delta = static_cast<int64_t>(reinterpret_cast<intptr_t>(d->gather_multicast_out) - reinterpret_cast<intptr_t>(d->out));
     return FTH_B200_OK;
 }
 

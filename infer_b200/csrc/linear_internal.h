@@ -11,6 +11,7 @@ constexpr int kMaxPeers = 7;
 struct PeerOut {
     int count;
     int64_t delta[kMaxPeers];
+    int64_t multicast_delta;  // X + multicast_delta is X in a multicast mapping of all ranks' buffers; 0: none
 };
 
 // Step signalling of a gather, folded into the kernels: flags[r] is rank r's flag array (uint32; slot [q] = last step rank

@@ -41,6 +41,8 @@ struct TcParams {
 struct OutMaps {
     CUtensorMap map[kMaxPeers + 1];
     int count;
+    uint8_t* multicast;  // the output block in a multicast mapping of all ranks' buffers (then `map` is unused), or null
+    int64_t ldo;         // its row pitch
 };
 
 constexpr int kClusterQBlocks = 8;  // K blocks of activations the cluster kernel keeps resident per CTA

@@ -23,6 +23,10 @@ namespace {
 // the epilogue therefore puts the CTA's 128 x 256 output tile into shared memory (the sixth ring stage is given up for
 // it) and one thread sends it to this GPU's buffer and to every replica as tile stores (cp.async.bulk.tensor, no
 // multicast): full rows of 256 bytes per request, and the copy of tile i overlaps the MMAs and the epilogue of tile i+1.
+// SM-issued stores to seven replicas still top out near 280 GB/s per GPU (measured, eight GPUs).  Where the caller has
+// an NVLink multicast mapping of all ranks' buffers, the tile goes there ONCE instead (multimem.st from the epilogue
+// threads, 512 contiguous bytes per warp): the switch replicates it, and a rank's links carry its output one time, not
+// seven.
 // ---------------------------------------------------------------------------------------------------------
 struct PairCfg {
     static constexpr int kTileN = 256;
@@ -57,7 +61,7 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t rank = ClusterRank();           // 0 = leader
     const bool leader = rank == 0;
-    const bool tile_stores = out_maps.count > 0;
+    const bool tile_stores = out_maps.count > 0 || out_maps.multicast != nullptr;
     const int stages = tile_stores ? C::kStagesWithTileStores : C::kStages;
     uint8_t* out_tile = ring + static_cast<size_t>(C::kStagesWithTileStores) * C::kStageBytes;  // [128][256], only with tile_stores
 
@@ -193,7 +197,7 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 33, acc)) failed = true;
             umma::FenceAfterThreadSync();
             if (tile_stores) {  // the stores of the previous tile must have read the shared-memory tile before it is rewritten
-                if (et == 0) BulkWaitGroupRead0();
+                if (et == 0 && out_maps.count > 0) BulkWaitGroupRead0();
                 EpilogueBarrier<C::kEpilogueThreads>();
             }
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * C::kTileN);
@@ -261,7 +265,18 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             if (tile_stores) {
                 FenceProxyAsync();  // this thread's writes to the tile, visible to the copy engine
                 EpilogueBarrier<C::kEpilogueThreads>();
-                if (et == 0 && !failed) {
+                if (out_maps.multicast != nullptr) {
+                    // 16 lanes per 256-byte row of the tile, two rows per warp and instruction; n is a multiple of 16
+                    if (!failed) {
+                        for (int c = et; c < C::kOutTileBytes / 16; c += C::kEpilogueThreads) {
+                            const int r = c >> 4, col = (c & 15) * 16;
+                            const int64_t gr = mt * 256 + rank * 128 + r;
+                            if (gr < p.p_total && col < n_count)
+                                MulticastStore16(out_maps.multicast + gr * out_maps.ldo + n_begin + col,
+                                                 *reinterpret_cast<const uint4*>(out_tile + r * C::kTileN + col));
+                        }
+                    }
+                } else if (et == 0 && !failed) {
                     const int32_t x = static_cast<int32_t>(n_begin), y = static_cast<int32_t>(mt * 256 + rank * 128);
                     // The destinations are taken in an order that differs from pair to pair and from tile to tile: every GPU
                     // runs this loop at the same time, and all of them starting with the same replica would queue up
@@ -275,7 +290,7 @@ LinearPairKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                 }
             }
         }
-        if (tile_stores && et == 0) {
+        if (out_maps.count > 0 && et == 0) {
             BulkWaitGroup0();                                  // every tile is written, here and in the replicas
             asm volatile("fence.proxy.async;" ::: "memory");   // ... and ordered in front of what this thread does next (the step flag)
         }

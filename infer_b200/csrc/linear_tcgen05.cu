@@ -251,7 +251,10 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
         const int64_t ldo = int8 ? ie.ldo : fe.ldo;
         bool tile_stores = a.peers.count > 0 && p.fast && ldo % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
         for (int r = 0; r < a.peers.count; ++r) tile_stores = tile_stores && a.peers.delta[r] % 16 == 0;
-        if (tile_stores) {
+        if (tile_stores && a.peers.multicast_delta != 0 && a.n % 16 == 0 && a.peers.multicast_delta % 16 == 0) {
+            out_maps.multicast = out + a.peers.multicast_delta;
+            out_maps.ldo = ldo;
+        } else if (tile_stores) {
             for (int d = 0; d <= a.peers.count; ++d) {
                 const uint8_t* base = d == 0 ? out : out + a.peers.delta[d - 1];
                 if (!MakeTensorMap2D(&out_maps.map[d], base, static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m), static_cast<uint64_t>(ldo),

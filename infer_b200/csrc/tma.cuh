@@ -141,6 +141,10 @@ __device__ __forceinline__ void TmaStore2D(const CUtensorMap* map, const void* s
 __device__ __forceinline__ void BulkCommitGroup() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void BulkWaitGroupRead0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void BulkWaitGroup0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// 16 bytes to a multicast address (NVLS): the switch delivers the store to every GPU bound to the mapping.
+__device__ __forceinline__ void MulticastStore16(void* multicast_addr, uint4 v) {
+    asm volatile("multimem.st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(multicast_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 __device__ __forceinline__ void TmaPrefetchDescriptor(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

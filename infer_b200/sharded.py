@@ -84,14 +84,27 @@ class PeerGather:
     Two buffers per rank, used by step parity: a rank can run at most one step ahead of the slowest one (it
     cannot pass step s before every rank has signalled s), so the buffer of step s is not written again until
     everybody has consumed it.  `dist` is only used to exchange the 64-byte handles at set-up.
+
+    With `torch` given (and world > 1) the buffers are first tried as torch symmetric memory
+    (torch.distributed._symmetric_memory): the same peer-mapped addresses, plus — where the box has NVLink multicast
+    (NVLS) — one multicast address per buffer (`multicast`, 0 if there is none), which the dense kernel stores to once
+    instead of once per peer.  If that set-up is not available the CUDA IPC path below is used.
     """
 
-    def __init__(self, lib, dist, world: int, rank: int, m: int, n: int, elem_bytes: int = 1):
+    def __init__(self, lib, dist, world: int, rank: int, m: int, n: int, elem_bytes: int = 1, torch=None):
         import ctypes as C
         self.lib, self.world, self.rank = lib, world, rank
         self.m, self.n, self.elem = m, n, elem_bytes
         self.block = (m * n * elem_bytes + 255) // 256 * 256
         total = 2 * self.block + 256  # two output buffers, then uint32 flags[world]
+        self.multicast = 0
+        self._symmetric = None
+        if torch is not None and world > 1 and self._try_symmetric(torch, dist, total):
+            self.flags = (C.c_void_p * world)(*[b + 2 * self.block for b in self.base])
+            self._world, self._rank = C.c_int32(world), C.c_int32(rank)
+            self.epoch = 0
+            dist.barrier()
+            return
         own = C.c_void_p()
         handle = (C.c_ubyte * 64)()
         created = lib.fth_b200_peer_buffer_create(C.c_size_t(total), C.byref(own), handle) == 0
@@ -125,9 +138,38 @@ class PeerGather:
         if world > 1:
             dist.barrier()  # nobody stores into a buffer before every rank has mapped it
 
+    def _try_symmetric(self, torch, dist, total: int) -> bool:
+        """Allocates the buffers as symmetric memory; every rank reports, and all ranks take the same branch."""
+        ok, tensor, handle = True, None, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            tensor = symm.empty(total, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+            tensor.zero_()
+            torch.cuda.synchronize()
+            handle = symm.rendezvous(tensor, dist.group.WORLD)
+            base = [int(p) for p in handle.buffer_ptrs]
+            ok = len(base) == self.world and all(base)
+        except Exception:  # set-up not available here: the IPC path takes over, on every rank alike
+            ok = False
+        verdicts = [ok] * self.world
+        dist.all_gather_object(verdicts, ok)
+        if not all(verdicts):
+            return False
+        self.base = base
+        multicast = int(handle.multicast_ptr) if getattr(handle, "has_multicast_support", False) or getattr(handle, "multicast_ptr", 0) else 0
+        present = [multicast != 0] * self.world
+        dist.all_gather_object(present, multicast != 0)
+        self.multicast = multicast if all(present) else 0
+        self._symmetric = (tensor, handle)
+        return True
+
     def buffer(self, r: int, parity: int) -> int:
         """Device address of rank r's output buffer for steps of this parity, as seen from this rank."""
         return self.base[r] + parity * self.block
+
+    def multicast_buffer(self, parity: int) -> int:
+        """The multicast address of the buffers of this parity (a store there lands in every rank's), or 0."""
+        return self.multicast + parity * self.block if self.multicast else 0
 
     def view(self, torch, parity: int):
         """This rank's gathered [M, N] buffer as a uint8 tensor of M * N * elem_bytes bytes per row block."""
@@ -152,6 +194,11 @@ class PeerGather:
             raise RuntimeError("fth_b200_gather_wait failed")
 
     def close(self) -> None:
+        if self._symmetric is not None:
+            self._symmetric = None  # torch frees the allocation with the tensor
+            self.base = [0] * self.world
+            self.multicast = 0
+            return
         for r, b in enumerate(self.base):
             if b and r != self.rank:
                 self.lib.fth_b200_peer_buffer_close(b)
@@ -177,6 +224,8 @@ def point_at_step_buffers(shard: "ShardedLinear", gather: PeerGather, desc, pari
     desc.gather_peers = len(others)
     for i, r in enumerate(others):
         desc.gather_out[i] = gather.buffer(r, parity) + offset
+    multicast = gather.multicast_buffer(parity) if hasattr(gather, "multicast_buffer") else 0
+    desc.gather_multicast_out = multicast + offset if multicast else None
     return desc
 
 

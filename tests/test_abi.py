@@ -42,6 +42,7 @@ int main(void) {
   P(fth_b200_fp8_linear_desc, a); P(fth_b200_fp8_linear_desc, ldo); P(fth_b200_fp8_linear_desc, w_channel_scales);
   P(fth_b200_fp8_linear_desc, workspace); P(fth_b200_fp8_linear_desc, variant); P(fth_b200_fp8_linear_desc, gather_out);
   P(fth_b200_fp8_linear_desc, gather_world); P(fth_b200_fp8_linear_desc, gather_flags); P(fth_b200_int8_linear_desc, gather_flags);
+  P(fth_b200_fp8_linear_desc, gather_multicast_out); P(fth_b200_int8_linear_desc, gather_multicast_out);
   P(fth_b200_int8_linear_desc, a); P(fth_b200_int8_linear_desc, w_scales); P(fth_b200_int8_linear_desc, bias_max_abs);
   P(fth_b200_int8_linear_desc, workspace); P(fth_b200_int8_linear_desc, variant);
   P(fth_b200_int8_conv2d_desc, x); P(fth_b200_int8_conv2d_desc, relu_lut); P(fth_b200_int8_conv2d_desc, workspace_bytes);
