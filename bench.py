@@ -339,6 +339,10 @@ class LinearCase:
                 # FTH_B200_NO_MULTICAST=1 keeps to the IPC buffers (A/B).  Raises on every rank or on none.
                 self.gather = PeerGather(ctx.B.lib(), ctx.dist, ctx.world, ctx.rank, self.m, N,
                                          torch=None if os.environ.get("FTH_B200_NO_MULTICAST") == "1" else ctx.torch)
+                if ctx.rank == 0 and not getattr(ctx, "gather_reported", False):
+                    ctx.gather_reported = True
+                    print(f"[bench] gather buffers: {'torch symmetric memory' if self.gather._symmetric is not None else 'CUDA IPC'}, "
+                          f"NVLink multicast address {'present' if self.gather.multicast else 'absent'}", file=sys.stderr)
                 # the kernels do the step signalling themselves (gather_world in the descriptors): no extra launch per step
                 self.prepared = [tuple(point_at_step_buffers(ctx.shard, self.gather, type(d).from_buffer_copy(d), parity, fold_signal=True)
                                        for parity in (0, 1)) for d in self.descs]
