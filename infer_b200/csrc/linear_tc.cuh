@@ -23,7 +23,8 @@ struct TcParams {
     int64_t chunk_blocks;      // 128-byte K blocks per chunk
     int ring_stages;           // cluster kernel: weight ring depth of this launch
     int64_t k_blocks;          // ceil(K / 128)
-    int tiles_per_cta;         // cluster kernel: 2 when a second weight shares the activation (its tile rides in the same CTA)
+    int tiles_per_cta;         // cluster kernel: weight tiles per CTA (1 or 2)
+    int second_tile_offset;    // the second tile: 0 = the same tile of the second weight (fusion.w2), else tile + this of the same weight
     int64_t units;             // p_tiles * q_tiles * split
     uint32_t idesc;
     int e4m3;                  // FP8 format of operands and output (1 = E4M3, 0 = E5M2)
@@ -53,6 +54,7 @@ struct TcGeometry {
     int split;
     int64_t chunk_blocks, k_blocks, p_total, q_total, p_tiles, q_tiles, units, p_pad;
     int cluster;  // > 0: single-launch cluster kernel with this many CTAs per weight tile
+    int tiles_per_cta, second_tile_offset;  // cluster kernel: see TcParams
 };
 
 

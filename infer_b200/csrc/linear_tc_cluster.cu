@@ -33,9 +33,16 @@ struct ClusterCfg {
     static constexpr int kThreads = 192;
     static constexpr int kNormBytes = 768;                   // a fused QwenRmsNorm: 1 / rms per row + four partial sums per row
     static constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kPBytes + kQBytes + kMaxTiles * kExchangeBytes + 256 + kNormBytes;
-    static int StagesFor(int64_t loads) { return loads < kStages ? static_cast<int>(loads) : kStages; }  // loads = chunk blocks x tiles
+    // Ring depth of a launch: its loads (chunk blocks x tiles) at most, and no deeper than lets two CTAs share an SM.
+    static int StagesFor(int64_t chunk_blocks, int tiles) {
+        const int64_t fixed = 1024 + chunk_blocks * BQ * kBlockK + static_cast<int64_t>(tiles) * kExchangeBytes + 256 + kNormBytes;
+        int64_t stages = (113 * 1024 - fixed) / kPBytes;
+        if (stages > kStages) stages = kStages;
+        if (stages > chunk_blocks * tiles) stages = chunk_blocks * tiles;
+        return stages < 1 ? 1 : static_cast<int>(stages);
+    }
     static size_t SmemFor(int64_t chunk_blocks, int tiles) {
-        return 1024 + static_cast<size_t>(StagesFor(chunk_blocks * tiles)) * kPBytes + static_cast<size_t>(chunk_blocks) * BQ * kBlockK +
+        return 1024 + static_cast<size_t>(StagesFor(chunk_blocks, tiles)) * kPBytes + static_cast<size_t>(chunk_blocks) * BQ * kBlockK +
                static_cast<size_t>(tiles) * kExchangeBytes + 256 + kNormBytes;
     }
 };
@@ -154,9 +161,12 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     // then takes ~30 KB instead of ~100 KB, and the CTAs of the next kernel in the stream can move in early.
     const int stages = p.ring_stages;
     uint8_t* q_tiles = ring + static_cast<size_t>(stages) * kPBytes;            // [chunk_blocks][BQ][128], 128-byte swizzle
-    // A second weight on the same activation (gate and up) is this CTA's second tile: the same columns of the other
-    // weight, its own accumulator columns and its own exchange area.
-    const int tiles_here = DEC ? p.tiles_per_cta : 1;
+    // A CTA may carry a second weight tile, with its own accumulator columns and its own exchange area: the same
+    // columns of a second weight on the same activation (gate and up), or — for a weight with up to twice as many tiles
+    // as one wave of clusters holds — the tile half the weight further on, so that such a projection is still one launch.
+    const int cshift = 31 - __clz(static_cast<int>(ClusterSize()));  // the cluster size is a power of two
+    const int tile = static_cast<int>(blockIdx.x >> cshift);
+    const int tiles_here = p.tiles_per_cta > 1 && tile + p.second_tile_offset < p.p_tiles ? 2 : 1;
     uint32_t* exchange = reinterpret_cast<uint32_t*>(q_tiles + p.chunk_blocks * (BQ * kBlockK));  // [tile][chunk][L][BQ]
     uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(exchange) + tiles_here * C::kExchangeBytes);
     uint64_t* empty = full + C::kMaxStages;
@@ -190,9 +200,6 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const uint32_t rank = ClusterRank();
-    const uint32_t csize = ClusterSize();                  // a power of two
-    const int cshift = 31 - __clz(static_cast<int>(csize));
-    const int tile = static_cast<int>(blockIdx.x >> cshift);
     const int lshift = 7 - cshift;                         // log2 of L = rows of the tile this CTA finishes
     const int rows_per_cta = 1 << lshift;
     const int kb_begin = static_cast<int>(rank) * static_cast<int>(p.chunk_blocks);
@@ -218,7 +225,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 const bool second = i >= nb;  // the first weight's K blocks, then the second weight's
                 const int32_t k0 = (kb_begin + (second ? i - nb : i)) * kBlockK;
                 const CUtensorMap* map = second ? &map_p2 : &map_p;
-                const int32_t p0 = tile * kBlockP;
+                const int32_t p0 = (second ? tile + p.second_tile_offset : tile) * kBlockP;
                 uint8_t* ps = ring + static_cast<size_t>(stage) * kPBytes;
                 MbarExpectTx(&full[stage], kPBytes);
                 if constexpr (P_MN) TmaLoad2D(ps, map, p0, k0, &full[stage]);
@@ -553,18 +560,20 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         // One output per thread and round: channel r of this CTA's rows (fastest, so a warp stores consecutive
         // channels) of activation row q.  The chunks are added in chunk order, as the two-kernel path adds them.
         const int total = m << lshift;
+        for (int w = 0; w < tiles_here; ++w)
         for (int base = 0; base < total; base += 128) {  // the same trip count in every lane: the argmax step below shuffles
             const int item = base + et;
             const bool valid = delivered && item < total;
             const int q = item >> lshift;
             const int r = item & (rows_per_cta - 1);
-            const int64_t n = static_cast<int64_t>(tile) * kBlockP + (static_cast<int64_t>(rank) << lshift) + r;
+            const int64_t n = static_cast<int64_t>(tile + w * p.second_tile_offset) * kBlockP + (static_cast<int64_t>(rank) << lshift) + r;
+            const uint32_t* part = exchange + w * (C::kExchangeBytes / 4);
             uint32_t code = 0;
             bool stored = false;
             if (valid) {
                 uint32_t t[8];
 #pragma unroll
-                for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? exchange[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
+                for (int ss = 0; ss < 8; ++ss) t[ss] = ss < p.split ? part[((ss << lshift) + r) * BQ + q] : 0u;  // all in flight
                 uint32_t acc;
                 if constexpr (INT8) {
                     int32_t sum = 0;
@@ -608,13 +617,14 @@ template <bool INT8, bool P_MN, int BQ, bool DEC>
 int LaunchClusterTyped(const TcGeometry& g, const CUtensorMap& map_p, const CUtensorMap& map_p2, const CUtensorMap& map_q, const TcParams& p_in,
                        const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     TcParams p = p_in;
-    p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks * (DEC ? p.tiles_per_cta : 1));
+    p.ring_stages = ClusterCfg<BQ>::StagesFor(g.chunk_blocks, p.tiles_per_cta);
     auto kernel = LinearClusterKernel<INT8, P_MN, BQ, DEC>;
     if (EnsureDynamicSmem(reinterpret_cast<const void*>(kernel), ClusterCfg<BQ>::kSmemBytes) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(g.p_tiles * g.cluster));
+    const int64_t clusters = g.second_tile_offset > 0 ? g.second_tile_offset : g.p_tiles;
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * g.cluster));
     cfg.blockDim = dim3(ClusterCfg<BQ>::kThreads);
-    cfg.dynamicSmemBytes = ClusterCfg<BQ>::SmemFor(g.chunk_blocks, DEC ? p.tiles_per_cta : 1);
+    cfg.dynamicSmemBytes = ClusterCfg<BQ>::SmemFor(g.chunk_blocks, p.tiles_per_cta);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -59,12 +59,25 @@ TcGeometry GeometryFor(const LinearArgs& a) {
     // Decode-sized problems that fit one wave of CTAs take the single-launch cluster kernel.  Which kernel runs
     // depends on N, but both add the same chunks in the same order, so the bits do not.
     g.cluster = 0;
+    g.tiles_per_cta = a.fusion.w2 != nullptr ? 2 : 1;
+    g.second_tile_offset = 0;
     if (g.swap && g.bq <= 32 && g.q_tiles == 1 && g.chunk_blocks <= kClusterQBlocks) {
         int c = 1;
         while (c < g.split) c *= 2;
         // more than one wave of CTAs: the persistent kernel keeps its ring full across tiles and is faster (measured).
         // Decoder-block fusions exist in this kernel only; its CTAs are small (several fit an SM), so a higher limit.
-        if (g.p_tiles * c <= static_cast<int64_t>(SmCount()) * (a.fusion.active() ? 3 : 2)) g.cluster = c;
+        const int64_t wave = static_cast<int64_t>(SmCount()) * 2;
+        if (g.p_tiles * c <= (a.fusion.active() ? wave * 3 / 2 : wave)) {
+            g.cluster = c;
+        } else if (!a.fusion.active() && g.bq <= 16 && (g.p_tiles + 1) / 2 * c <= wave * 4 / 5) {
+            // up to two waves' worth of tiles: every CTA takes two of them (tile t and tile t + half), still one launch.
+            // Measured against the persistent kernel + reduce pass at M = 1: K = 8192, N = 7168 (224 CTAs) 13.4 vs 15.9 us,
+            // N = 6016 12.1 vs 15.1 us; with every CTA slot taken (K = 4096, N = 9472: 296 CTAs) 14.2 vs 13.1 us, hence the
+            // margin below a full wave.
+            g.cluster = c;
+            g.tiles_per_cta = 2;
+            g.second_tile_offset = static_cast<int>((g.p_tiles + 1) / 2);
+        }
     }
     return g;
 }
@@ -210,7 +223,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     if (!ok) return FTH_B200_ERR_CUDA;
     map_p = g.swap ? map_w : map_a;
     map_q = g.swap ? map_a : map_w;
-    CUtensorMap map_p2 = map_p;
+    CUtensorMap map_p2 = map_p;  // two tiles of one weight per CTA: the same map
     if (a.fusion.w2 != nullptr) {
         if (weights_mn) ok = CachedMap(&map_p2, a.fusion.w2, static_cast<uint64_t>(a.fusion.n2), static_cast<uint64_t>(a.k), 128, 128);
         else ok = CachedMap(&map_p2, a.fusion.w2, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.fusion.n2), 128, kBlockP);
@@ -223,13 +236,14 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     p.p_total = g.p_total; p.q_total = g.q_total; p.p_tiles = g.p_tiles; p.q_tiles = g.q_tiles;
     p.ring_stages = 0;
     p.split = g.split; p.chunk_blocks = g.chunk_blocks; p.k_blocks = g.k_blocks; p.units = g.units;
-    p.tiles_per_cta = a.fusion.w2 != nullptr ? 2 : 1;
+    p.tiles_per_cta = g.tiles_per_cta;
+    p.second_tile_offset = g.second_tile_offset;
     p.p_pad = g.p_pad;
     p.e4m3 = dtype == FTH_B200_FP8E4M3;
     if (int8) p.fast = ie.bias_mode == FTH_B200_BIAS_NONE && ie.out_dtype == 0 && !(ie.is_gemm && (ie.alpha != 1.0f || ie.beta != 1.0f));
     else p.fast = fe.bias_mode == FTH_B200_BIAS_NONE && fe.out_dtype == 0 && !(fe.is_gemm && fe.alpha != 1.0f);
     p.fast4 = DirectEpilogue(int8, fe, ie);
-    p.decoder = DecoderForm(dtype, a, fe, ie);
+    p.decoder = DecoderForm(dtype, a, fe, ie) && g.second_tile_offset == 0;  // (two tiles of one weight: the general form)
     p.a_inv = int8 ? 0.0f : ExactReciprocal(a.a_scale);
     p.out_inv = int8 ? 0.0f : ExactReciprocal(fe.out_scale);
     p.scratch = scratch;
