@@ -184,6 +184,38 @@ def test_swapped_kernel_many_units_per_cta(cuda, kind, m, k, n, trans_b):
     assert B.device_status() == 0
 
 
+# ---- two weight tiles per CTA in the single-launch kernel ------------------------------------------------------------
+# A weight with more tiles than one wave of clusters holds, but at most twice as many, runs as one launch in which every
+# CTA takes tile t and tile t + half (the N/4 shard of the headline shape is such a weight).  An odd tile count leaves
+# the last cluster with one tile.
+TWO_TILES = [(1, 8192, 7168, False), (16, 8192, 7168, False), (4, 8192, 7040, False), (1, 4096, 7168, True)]
+
+
+@pytest.mark.parametrize("m,k,n,trans_b", TWO_TILES)
+@pytest.mark.parametrize("kind", ["fp8_e4m3", "int8"])
+def test_cluster_kernel_two_tiles_per_cta(cuda, kind, m, k, n, trans_b):
+    rng = np.random.default_rng(m * 11 + n)
+    B.lib().fth_b200_reset_launch_count()
+    if kind == "int8":
+        w, ws = util.make_int8_weight(k, n, seed=k + n + 3)
+        a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+        so = util.int8_out_scale(k, ws)
+        w_host = np.ascontiguousarray(w.T) if trans_b else w
+        got = _run_int8(cuda, a, dev(cuda, w_host), dev(cuda, ws), so, m, k, n, trans_b)
+        want = O.int8_linear(O.OP_GEMM if trans_b else O.OP_MATMUL, a, 0.02, 0, w_host, ws, None, so, 0, trans_b=trans_b)
+        assert int((got != want).sum()) == 0
+    else:
+        w, sw = util.make_fp8_weight(O.E4M3, k, n, seed=k + n + 2)
+        a, sa = util.make_fp8_activation(O.E4M3, m, k, seed=m + k + 2)
+        so = util.fp8_out_scale(O.E4M3, k)
+        w_host = np.ascontiguousarray(w.T) if trans_b else w
+        got = _run_fp8(cuda, a, sa, dev(cuda, w_host), sw, so, m, k, n, trans_b)
+        want = O.fp8_linear(O.OP_GEMM if trans_b else O.OP_MATMUL, O.E4M3, a, sa, w_host, sw, so, trans_b=trans_b)
+        _fp8_check(f"two tiles per CTA {kind} {m}x{k}x{n} trans_b={trans_b}", got, want, a, sa, w_host, sw, so, O.E4M3, trans_b)
+    assert B.lib().fth_b200_launch_count() == 1, "expected the single-launch kernel"
+    assert B.device_status() == 0
+
+
 PAIR = [
     # m, k, n, trans_b: 256 x 256 tiles on 74 CTA pairs, two accumulator buffers, ring of 6 stages
     (512, 128, 256 * 74 * 3, False),   # 444 tiles, 6 per pair, one K block per tile: the ring wraps once per 6 tiles

@@ -121,7 +121,8 @@ def test_gather_sync_gives_up_when_a_peer_never_signals(cuda):
 # ---- gather signalling folded into the linear kernels ----------------------------------------------------------------
 # Two "ranks" on one GPU take turns on one stream (kernels of different ranks never have to run at the same time: every
 # wait finds its condition already true, except in the test that lets one run out on purpose).
-FOLD_CASES = [(1, 1024, 2048, B.VARIANT_AUTO, "cluster kernel"), (16, 8192, 16384, B.VARIANT_AUTO, "split-K reduce pass"),
+FOLD_CASES = [(1, 1024, 2048, B.VARIANT_AUTO, "cluster kernel"), (16, 8192, 32768, B.VARIANT_AUTO, "split-K reduce pass"),
+              (4, 8192, 14336, B.VARIANT_AUTO, "cluster kernel, two tiles per CTA"),
               (300, 512, 640, B.VARIANT_AUTO, "CTA-pair dense kernel"), (4, 256, 384, B.VARIANT_SKINNY, "small kernels around a CUDA-core kernel")]
 
 
