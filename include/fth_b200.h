@@ -402,7 +402,11 @@ void fth_b200_plan_destroy(fth_b200_plan* plan);
  * counter on the device (slot [world] of this rank's own array, incremented by the call), so that a captured CUDA graph
  * can be replayed; all ranks must then use epoch = 0 for every step.  Each array has room for world + 2 words.
  * fth_b200_gather_wait only waits (bounded, same reporting) until every rank has signalled the step this rank signalled
- * last — the consumer side of the signalling that the linear kernels do themselves (gather_world in their descriptors). */
+ * last — the consumer side of the signalling that the linear kernels do themselves (gather_world in their descriptors).
+ * A wait that runs out does NOT fail the stream: the kernel records the site and the missing rank in the status word and
+ * returns, and what follows on the stream reads a buffer some ranks have not written.  A caller must therefore read
+ * fth_b200_device_status() — at the latest where it hands a result that depends on a gathered buffer to its own caller —
+ * and treat a non-zero word as a failed step. */
 #define FTH_B200_PEER_HANDLE_BYTES 64
 int fth_b200_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle);
 int fth_b200_peer_buffer_open(const unsigned char* handle, void** ptr);
