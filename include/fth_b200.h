@@ -340,6 +340,14 @@ int fth_b200_quantize_linear(int32_t x_dtype, const void* x, const float* scales
                              fth_b200_stream_t stream);
 int fth_b200_dequantize_linear(const int8_t* x, const float* scales, const int32_t* zps, int64_t params, void* out,
                                int32_t to_dtype, int64_t rows, int64_t channels, fth_b200_stream_t stream);
+/* The same two nodes with the channel axis anywhere: x is [outer, channels, inner] (QuantizeLinearParam::axis names the
+ * middle extent; inner = 1 is the last-axis form above). */
+int fth_b200_quantize_linear_axis(int32_t x_dtype, const void* x, const float* scales, const int32_t* zps,
+                                  int64_t params, int8_t* out, int64_t outer, int64_t channels, int64_t inner,
+                                  fth_b200_stream_t stream);
+int fth_b200_dequantize_linear_axis(const int8_t* x, const float* scales, const int32_t* zps, int64_t params, void* out,
+                                    int32_t to_dtype, int64_t outer, int64_t channels, int64_t inner,
+                                    fth_b200_stream_t stream);
 
 /* Cast among FP32 / FP16 / BF16 / FP8 with per-tensor FP8 scales.
  * Replaces CastFloatingKernelCuda (src/kernel/cuda/cast.cu:54-93); contract src/kernel/common/cast.cc:62-126. */

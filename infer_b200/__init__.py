@@ -236,18 +236,19 @@ def cast(in_dtype, x, in_scale, out_dtype, out, out_scale, count, stream=None) -
                               stream or current_stream()), "fth_b200_cast")
 
 
-def quantize_linear(x_dtype, x, scales, zps, params, out, rows, channels, stream=None) -> None:
-    check(lib().fth_b200_quantize_linear(C.c_int32(x_dtype), C.c_void_p(ptr(x)), C.c_void_p(ptr(scales)),
-                                         C.c_void_p(ptr(zps)), C.c_int64(params), C.c_void_p(ptr(out)),
-                                         C.c_int64(rows), C.c_int64(channels), stream or current_stream()),
-          "fth_b200_quantize_linear")
+def quantize_linear(x_dtype, x, scales, zps, params, out, rows, channels, stream=None, inner=1) -> None:
+    """x is [rows, channels, inner]; the parameters run along `channels` (inner = 1: the last axis)."""
+    check(lib().fth_b200_quantize_linear_axis(C.c_int32(x_dtype), C.c_void_p(ptr(x)), C.c_void_p(ptr(scales)),
+                                              C.c_void_p(ptr(zps)), C.c_int64(params), C.c_void_p(ptr(out)),
+                                              C.c_int64(rows), C.c_int64(channels), C.c_int64(inner), stream or current_stream()),
+          "fth_b200_quantize_linear_axis")
 
 
-def dequantize_linear(x, scales, zps, params, out, to_dtype, rows, channels, stream=None) -> None:
-    check(lib().fth_b200_dequantize_linear(C.c_void_p(ptr(x)), C.c_void_p(ptr(scales)), C.c_void_p(ptr(zps)),
-                                           C.c_int64(params), C.c_void_p(ptr(out)), C.c_int32(to_dtype),
-                                           C.c_int64(rows), C.c_int64(channels), stream or current_stream()),
-          "fth_b200_dequantize_linear")
+def dequantize_linear(x, scales, zps, params, out, to_dtype, rows, channels, stream=None, inner=1) -> None:
+    check(lib().fth_b200_dequantize_linear_axis(C.c_void_p(ptr(x)), C.c_void_p(ptr(scales)), C.c_void_p(ptr(zps)),
+                                                C.c_int64(params), C.c_void_p(ptr(out)), C.c_int32(to_dtype),
+                                                C.c_int64(rows), C.c_int64(channels), C.c_int64(inner), stream or current_stream()),
+          "fth_b200_dequantize_linear_axis")
 
 
 def int8_lookup(x, out, count, lut, stream=None) -> None:

@@ -437,13 +437,20 @@ class QdqBase : public B200Kernel {
     int32_t PrepareParams(Param* p) {
         if (!p || !p->input || !p->scale || !p->zero_point || !p->out) return -1;
         if (!quantize_linear_detail::BuildQuantizationParams(*p->input, *p->scale, *p->zero_point, p->axis, &quantization_)) return -1;
-        const auto& dims = p->input->dims().data();
-        if (quantization_.granularity == QuantizationGranularity::kPerChannel &&
-            quantization_.axis != static_cast<int64_t>(dims.size()) - 1) return 1;  // only last-axis channels on the GPU path
         std::vector<int32_t> zps = quantization_.zero_points;
         if (zps.size() == 1 && quantization_.scales.size() > 1) zps.assign(quantization_.scales.size(), zps[0]);
         if (scales_.Upload(quantization_.scales.data(), quantization_.scales.size() * sizeof(float)) != 0) return -1;
         return zps_.Upload(zps.data(), zps.size() * sizeof(int32_t));
+    }
+    // [outer, channels, inner] view of a tensor whose parameters run along quantization.axis (per tensor: one channel).
+    template <typename Dims>
+    static void ChannelExtents(const Dims& dims, const QuantizationParams& q, int64_t* channels, int64_t* inner) {
+        *channels = 1;
+        *inner = 1;
+        if (q.granularity != QuantizationGranularity::kPerChannel || dims.empty()) { *channels = dims.empty() ? 1 : dims.back(); return; }
+        const size_t axis = static_cast<size_t>(q.axis < 0 ? q.axis + static_cast<int64_t>(dims.size()) : q.axis);
+        *channels = dims[axis];
+        for (size_t i = axis + 1; i < dims.size(); ++i) *inner *= dims[i];
     }
     QuantizationParams quantization_;
     DeviceScratch scales_, zps_;
@@ -457,9 +464,7 @@ class QuantizeLinearKernelB200 final : public QdqBase<operators::QuantizeLinearP
         if (!p || !p->input || !p->scale || !p->zero_point ||
             !quantize_linear_detail::BuildQuantizationParams(*p->input, *p->scale, *p->zero_point, p->axis, &q))
             return Status::Error(StatusCode::kInvalidArgument, "b200: bad QuantizeLinear parameters");
-        if (q.granularity == QuantizationGranularity::kPerChannel && q.axis != static_cast<int64_t>(p->input->dims().size()) - 1)
-            return Status::Error(StatusCode::kUnsupported, "b200: per-channel QuantizeLinear on an inner axis");
-        return Status::Ok();
+        return Status::Ok();  // per tensor, or per channel on any axis
     }
     int32_t Prepare() override { return PrepareParams(ParamAs<operators::QuantizeLinearParam>()) == 0 ? 0 : -1; }
     int32_t compute() override {
@@ -467,7 +472,8 @@ class QuantizeLinearKernelB200 final : public QdqBase<operators::QuantizeLinearP
         auto* p = ParamAs<operators::QuantizeLinearParam>();
         if (!p || scales_.get() == nullptr) return -1;
         const int64_t count = p->input->numel();
-        const int64_t channels = p->input->dims().data().back();
+        int64_t channels = 1, inner = 1;
+        ChannelExtents(p->input->dims().data(), quantization_, &channels, &inner);
         void* in = nullptr; void* out = nullptr;
         if (cuda_detail::AcquireTensorDevice(p->input.get(), static_cast<size_t>(count) * DataTypeBytes(p->input->data_type()),
                                              p->input->raw_data(), &in) != 0) return -1;
@@ -475,9 +481,10 @@ class QuantizeLinearKernelB200 final : public QdqBase<operators::QuantizeLinearP
         p->out->set_data_type(DataType::INT8);
         p->out->set_quantization(quantization_);  // the output's parameters are set at run time (quantize_linear_utils.h:273-276)
         if (cuda_detail::AcquireOutputTensorDevice(p->out.get(), static_cast<size_t>(count), &out) != 0) return -1;
-        if (fth_b200_quantize_linear(static_cast<int32_t>(p->input->data_type()), in, static_cast<const float*>(scales_.get()),
-                                     static_cast<const int32_t*>(zps_.get()), static_cast<int64_t>(quantization_.scales.size()),
-                                     static_cast<int8_t*>(out), count / channels, channels, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        if (fth_b200_quantize_linear_axis(static_cast<int32_t>(p->input->data_type()), in, static_cast<const float*>(scales_.get()),
+                                          static_cast<const int32_t*>(zps_.get()), static_cast<int64_t>(quantization_.scales.size()),
+                                          static_cast<int8_t*>(out), count / (channels * inner), channels, inner,
+                                          cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
         if (cuda_detail::DeferredHostSyncEnabled()) return 0;
         return cuda_detail::SyncTensorToHost(p->out.get(), static_cast<size_t>(count), p->out->raw_data());
     }
@@ -492,9 +499,7 @@ class DequantizeLinearKernelB200 final : public QdqBase<operators::DequantizeLin
             (p->to != DataType::FP32 && p->to != DataType::FP16 && p->to != DataType::BF16) ||
             !quantize_linear_detail::BuildQuantizationParams(*p->input, *p->scale, *p->zero_point, p->axis, &q))
             return Status::Error(StatusCode::kInvalidArgument, "b200: bad DequantizeLinear parameters");
-        if (q.granularity == QuantizationGranularity::kPerChannel && q.axis != static_cast<int64_t>(p->input->dims().size()) - 1)
-            return Status::Error(StatusCode::kUnsupported, "b200: per-channel DequantizeLinear on an inner axis");
-        return Status::Ok();
+        return Status::Ok();  // per tensor, or per channel on any axis
     }
     int32_t Prepare() override { return PrepareParams(ParamAs<operators::DequantizeLinearParam>()) == 0 ? 0 : -1; }
     int32_t compute() override {
@@ -502,7 +507,8 @@ class DequantizeLinearKernelB200 final : public QdqBase<operators::DequantizeLin
         auto* p = ParamAs<operators::DequantizeLinearParam>();
         if (!p || scales_.get() == nullptr) return -1;
         const int64_t count = p->input->numel();
-        const int64_t channels = p->input->dims().data().back();
+        int64_t channels = 1, inner = 1;
+        ChannelExtents(p->input->dims().data(), quantization_, &channels, &inner);
         const size_t out_bytes = static_cast<size_t>(count) * DataTypeBytes(p->to);
         void* in = nullptr; void* out = nullptr;
         if (cuda_detail::AcquireTensorDevice(p->input.get(), static_cast<size_t>(count), p->input->raw_data(), &in) != 0) return -1;
@@ -510,9 +516,10 @@ class DequantizeLinearKernelB200 final : public QdqBase<operators::DequantizeLin
         p->out->set_data_type(p->to);
         p->out->set_quantization(QuantizationParams{});
         if (cuda_detail::AcquireOutputTensorDevice(p->out.get(), out_bytes, &out) != 0) return -1;
-        if (fth_b200_dequantize_linear(static_cast<const int8_t*>(in), static_cast<const float*>(scales_.get()),
-                                       static_cast<const int32_t*>(zps_.get()), static_cast<int64_t>(quantization_.scales.size()), out,
-                                       static_cast<int32_t>(p->to), count / channels, channels, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        if (fth_b200_dequantize_linear_axis(static_cast<const int8_t*>(in), static_cast<const float*>(scales_.get()),
+                                            static_cast<const int32_t*>(zps_.get()), static_cast<int64_t>(quantization_.scales.size()), out,
+                                            static_cast<int32_t>(p->to), count / (channels * inner), channels, inner,
+                                            cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
         if (cuda_detail::DeferredHostSyncEnabled()) return 0;
         return cuda_detail::SyncTensorToHost(p->out.get(), out_bytes, p->out->raw_data());
     }

@@ -87,14 +87,14 @@ int LaunchCastOut(int out_dtype, const void* x, void* out, int64_t count, float 
 template <int IN>
 __global__ void __launch_bounds__(kThreads) QuantizeKernel(const void* __restrict__ x, const float* __restrict__ scales,
                                                            const int32_t* __restrict__ zps, int64_t params,
-                                                           int8_t* __restrict__ out, int64_t count, int64_t channels) {
+                                                           int8_t* __restrict__ out, int64_t count, int64_t channels, int64_t inner) {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * 4;
     for (int64_t base = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) * 4; base < count; base += stride) {
         int8_t q[4];
         const int lim = count - base < 4 ? static_cast<int>(count - base) : 4;
         for (int j = 0; j < lim; ++j) {
             const int64_t i = base + j;
-            const int64_t c = params == 1 ? 0 : i % channels;
+            const int64_t c = params == 1 ? 0 : (inner == 1 ? i : i / inner) % channels;  // the channel axis may be an inner one
             q[j] = QuantizeValue(ReadAs<IN>(x, i, 1.0f), scales[c], zps[c]);
         }
         if (lim == 4 && (reinterpret_cast<uintptr_t>(out + base) & 3) == 0) {
@@ -108,10 +108,10 @@ __global__ void __launch_bounds__(kThreads) QuantizeKernel(const void* __restric
 template <int OUT>
 __global__ void __launch_bounds__(kThreads) DequantizeKernel(const int8_t* __restrict__ x, const float* __restrict__ scales,
                                                              const int32_t* __restrict__ zps, int64_t params,
-                                                             void* __restrict__ out, int64_t count, int64_t channels) {
+                                                             void* __restrict__ out, int64_t count, int64_t channels, int64_t inner) {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < count; i += stride) {
-        const int64_t c = params == 1 ? 0 : i % channels;
+        const int64_t c = params == 1 ? 0 : (inner == 1 ? i : i / inner) % channels;
         const float v = __fmul_rn(static_cast<float>(static_cast<int32_t>(x[i]) - zps[c]), scales[c]);
         if constexpr (OUT == FTH_B200_FP32) static_cast<float*>(out)[i] = v;
         else if constexpr (OUT == FTH_B200_FP16) static_cast<__half*>(out)[i] = __float2half_rn(v);
@@ -194,16 +194,22 @@ extern "C" int fth_b200_cast(int32_t in_dtype, const void* x, float in_scale, in
 extern "C" int fth_b200_quantize_linear(int32_t x_dtype, const void* x, const float* scales, const int32_t* zps,
                                         int64_t params, int8_t* out, int64_t rows, int64_t channels,
                                         fth_b200_stream_t stream_) {
+    return fth_b200_quantize_linear_axis(x_dtype, x, scales, zps, params, out, rows, channels, 1, stream_);
+}
+
+extern "C" int fth_b200_quantize_linear_axis(int32_t x_dtype, const void* x, const float* scales, const int32_t* zps,
+                                             int64_t params, int8_t* out, int64_t outer, int64_t channels, int64_t inner,
+                                             fth_b200_stream_t stream_) {
     ClearStaleError();
     auto stream = static_cast<cudaStream_t>(stream_);
-    if (!x || !scales || !zps || !out || rows <= 0 || channels <= 0) return FTH_B200_ERR_INVALID;
+    if (!x || !scales || !zps || !out || outer <= 0 || channels <= 0 || inner <= 0) return FTH_B200_ERR_INVALID;
     if (params != 1 && params != channels) return FTH_B200_ERR_INVALID;
-    const int64_t count = rows * channels;
+    const int64_t count = outer * channels * inner;
     const int grid = GridFor(count / 4 + 1);
     switch (x_dtype) {
-        case FTH_B200_FP32: QuantizeKernel<FTH_B200_FP32><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels); break;
-        case FTH_B200_BF16: QuantizeKernel<FTH_B200_BF16><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels); break;
-        case FTH_B200_FP16: QuantizeKernel<FTH_B200_FP16><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels); break;
+        case FTH_B200_FP32: QuantizeKernel<FTH_B200_FP32><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels, inner); break;
+        case FTH_B200_BF16: QuantizeKernel<FTH_B200_BF16><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels, inner); break;
+        case FTH_B200_FP16: QuantizeKernel<FTH_B200_FP16><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels, inner); break;
         default: return FTH_B200_ERR_UNSUPPORTED;
     }
     NoteLaunch("quantize_linear");
@@ -213,16 +219,22 @@ extern "C" int fth_b200_quantize_linear(int32_t x_dtype, const void* x, const fl
 extern "C" int fth_b200_dequantize_linear(const int8_t* x, const float* scales, const int32_t* zps, int64_t params,
                                           void* out, int32_t to_dtype, int64_t rows, int64_t channels,
                                           fth_b200_stream_t stream_) {
+    return fth_b200_dequantize_linear_axis(x, scales, zps, params, out, to_dtype, rows, channels, 1, stream_);
+}
+
+extern "C" int fth_b200_dequantize_linear_axis(const int8_t* x, const float* scales, const int32_t* zps, int64_t params,
+                                               void* out, int32_t to_dtype, int64_t outer, int64_t channels, int64_t inner,
+                                               fth_b200_stream_t stream_) {
     ClearStaleError();
     auto stream = static_cast<cudaStream_t>(stream_);
-    if (!x || !scales || !zps || !out || rows <= 0 || channels <= 0) return FTH_B200_ERR_INVALID;
+    if (!x || !scales || !zps || !out || outer <= 0 || channels <= 0 || inner <= 0) return FTH_B200_ERR_INVALID;
     if (params != 1 && params != channels) return FTH_B200_ERR_INVALID;
-    const int64_t count = rows * channels;
+    const int64_t count = outer * channels * inner;
     const int grid = GridFor(count);
     switch (to_dtype) {
-        case FTH_B200_FP32: DequantizeKernel<FTH_B200_FP32><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels); break;
-        case FTH_B200_BF16: DequantizeKernel<FTH_B200_BF16><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels); break;
-        case FTH_B200_FP16: DequantizeKernel<FTH_B200_FP16><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels); break;
+        case FTH_B200_FP32: DequantizeKernel<FTH_B200_FP32><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels, inner); break;
+        case FTH_B200_BF16: DequantizeKernel<FTH_B200_BF16><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels, inner); break;
+        case FTH_B200_FP16: DequantizeKernel<FTH_B200_FP16><<<grid, kThreads, 0, stream>>>(x, scales, zps, params, out, count, channels, inner); break;
         default: return FTH_B200_ERR_INVALID;  // the reference accepts FP32 / FP16 / BF16 only
     }
     NoteLaunch("dequantize_linear");

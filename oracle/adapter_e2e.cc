@@ -337,6 +337,36 @@ static void RunGpu() {
         CHECK_THAT(ok && diff == 0, "QuantizeLinear -> INT8 MatMul -> DequantizeLinear runs entirely on CUDA candidates, identical to COMMON");
     }
 
+    // ---- per-channel QuantizeLinear / DequantizeLinear on axis 1 of an NCHW activation ----
+    {
+        const int64_t n = 2, ch = 6, h = 5, w = 9, count = n * ch * h * w;
+        std::vector<float> x(static_cast<size_t>(count));
+        for (auto& v : x) v = Uniform(-3.0f, 3.0f);
+        std::vector<float> sc(static_cast<size_t>(ch));
+        std::vector<int32_t> zp(static_cast<size_t>(ch));
+        for (int64_t i = 0; i < ch; ++i) { sc[static_cast<size_t>(i)] = 0.01f + 0.005f * static_cast<float>(i); zp[static_cast<size_t>(i)] = static_cast<int32_t>(i) - 3; }
+        auto xin = MakeTensor(DataType::FP32, {n, ch, h, w}, x.data());
+        auto scale_t = MakeTensor(DataType::FP32, {ch}, sc.data());
+        auto zp_t = MakeTensor(DataType::INT32, {ch}, zp.data());
+        auto q_gpu = MakeTensor(DataType::INT8, {n, ch, h, w});
+        auto q_ref = MakeTensor(DataType::INT8, {n, ch, h, w});
+        auto y_gpu = MakeTensor(DataType::FP32, {n, ch, h, w});
+        auto y_ref = MakeTensor(DataType::FP32, {n, ch, h, w});
+        operators::QuantizeLinearParam qp; qp.input = xin; qp.scale = scale_t; qp.zero_point = zp_t; qp.out = q_gpu; qp.axis = 1;
+        operators::QuantizeLinearParam qr = qp; qr.out = q_ref;
+        bool ok = RunCommon(DataType::FP32, "QuantizeLinear", &qr) == 0;
+        auto kq = Select(DeviceType::CUDA, DataType::FP32, "QuantizeLinear", &qp);
+        ok = ok && kq && IsB200Kernel(kq.get()) && kq->Prepare() == 0 && kq->compute() == 0;
+        operators::DequantizeLinearParam dp; dp.input = q_ref; dp.scale = scale_t; dp.zero_point = zp_t; dp.out = y_gpu; dp.to = DataType::FP32; dp.axis = 1;
+        operators::DequantizeLinearParam dr = dp; dr.out = y_ref;
+        ok = ok && RunCommon(DataType::INT8, "DequantizeLinear", &dr) == 0;
+        auto kd = Select(DeviceType::CUDA, DataType::INT8, "DequantizeLinear", &dp);
+        ok = ok && kd && IsB200Kernel(kd.get()) && kd->Prepare() == 0 && kd->compute() == 0;
+        const bool same_q = ok && std::memcmp(q_gpu->raw_data(), q_ref->raw_data(), static_cast<size_t>(count)) == 0;
+        const bool same_y = ok && std::memcmp(y_gpu->raw_data(), y_ref->raw_data(), static_cast<size_t>(count) * 4) == 0;
+        CHECK_THAT(same_q && same_y, "per-channel QuantizeLinear / DequantizeLinear on axis 1 of [N,C,H,W] run on the CUDA candidates, identical to COMMON");
+    }
+
     // ---- INT8 Conv2D 3x3 pad 1 with int32 bias ----
     {
         const int64_t ic = 64, oc = 64, h = 24, w = 40;

@@ -106,6 +106,28 @@ def test_dequantize_linear(cuda, to, per_channel):
     assert np.array_equal(out.cpu().numpy().view(want.dtype).reshape(rows, channels), want)
 
 
+@pytest.mark.parametrize("outer,channels,inner", [(2, 5, 7), (1, 64, 400), (3, 17, 1)])
+def test_quantize_dequantize_per_channel_on_an_inner_axis(cuda, outer, channels, inner):
+    """Parameters along the middle extent of [outer, channels, inner] (QuantizeLinearParam::axis on an NCHW activation):
+    the oracle sees the same tensor with the channel axis moved last."""
+    rng = np.random.default_rng(outer * 100 + channels + inner)
+    x = (rng.standard_normal((outer, channels, inner)) * 2).astype(np.float32)
+    scales = rng.uniform(0.01, 0.1, channels).astype(np.float32)
+    zps = rng.integers(-20, 20, channels).astype(np.int32)
+    moved = np.ascontiguousarray(np.moveaxis(x, 1, 2)).reshape(-1, channels)
+    want_q = np.moveaxis(O.quantize_linear(O.FP32, moved, scales, zps).reshape(outer, inner, channels), 2, 1)
+    q = cuda.zeros((outer, channels, inner), dtype=cuda.int8, device="cuda")
+    B.quantize_linear(B.FP32, dev(cuda, x), dev(cuda, scales), dev(cuda, zps), channels, q, outer, channels, inner=inner)
+    cuda.cuda.synchronize()
+    assert np.array_equal(q.cpu().numpy(), want_q)
+    want_f = np.moveaxis(O.dequantize_linear(np.ascontiguousarray(np.moveaxis(want_q, 1, 2)).reshape(-1, channels), scales, zps, B.FP32)
+                         .reshape(outer, inner, channels), 2, 1)
+    f = cuda.zeros((outer, channels, inner), dtype=cuda.float32, device="cuda")
+    B.dequantize_linear(q, dev(cuda, scales), dev(cuda, zps), channels, f, B.FP32, outer, channels, inner=inner)
+    cuda.cuda.synchronize()
+    assert np.array_equal(f.cpu().numpy().view(np.uint32), np.ascontiguousarray(want_f).view(np.uint32))
+
+
 def test_quantize_known_answers(cuda):
     """include/quant/quantization.h:94-99 ties away from zero: 0.5 → 1, -0.5 → -1, 2.5 → 3; saturation."""
     x = np.array([[0.5, -0.5, 1.5, 2.5, -2.5, 1000.0, -1000.0, np.nan, np.inf, -np.inf]], np.float32)

@@ -1,11 +1,13 @@
 """GPU: the exact launches the ncu summaries under profiles/ were captured from — four calls of one kernel on the
-named workload (ncu: `-s 3 -c 1`).  As tests they check that the call succeeds on the expected kernel family,
-finishes, and leaves the device status word clean."""
+named workload (ncu: `-s 3 -c 1`).  As tests they check that the call runs on the expected kernel family, leaves the
+device status word clean, and that a seeded slice of what it wrote (the conv: all of it) is the oracle's result."""
 import ctypes as C
 
+import numpy as np
 import pytest
 
 import infer_b200 as B
+import oracle as O
 
 pytestmark = pytest.mark.gpu
 K, N = 8192, 28672
@@ -32,6 +34,20 @@ def _linear(torch, kind, m):
         assert call(C.byref(d), B.current_stream()) == B.OK
     torch.cuda.synchronize()
     assert B.last_variant() == "tcgen05"
+    # 16 rows x 64 columns of the output against the oracle on the sliced operands
+    rng = np.random.default_rng(m)
+    rows = np.sort(rng.choice(m, min(16, m), replace=False))
+    cols = np.sort(rng.choice(N, 64, replace=False))
+    a_h = np.ascontiguousarray(a.cpu().numpy()[rows])
+    w_h = np.ascontiguousarray(w[:, torch.from_numpy(cols).cuda()].cpu().numpy())
+    got = out.cpu().numpy()[np.ix_(rows, cols)]
+    if kind == "fp8":
+        want = O.fp8_linear(O.OP_MATMUL, O.E4M3, a_h, 1.0, w_h, 1.0, 64.0)
+        dist = np.abs(got.astype(np.int32) - want.astype(np.int32))
+        assert dist.max() <= 1
+    else:
+        want = O.int8_linear(O.OP_MATMUL, a_h, 0.02, 0, w_h, np.full(64, 0.005, np.float32), None, 1.0, 0)
+        assert np.array_equal(got, want)
 
 
 def _conv(torch):
@@ -52,6 +68,9 @@ def _conv(torch):
         d.weights_packed = 1
     torch.cuda.synchronize()
     assert B.last_variant() == "conv_tcgen05"
+    want = O.int8_conv2d(case["x"], case["sx"], 0, case["w"], case["ws"], None, case["bias"], case["so"], 0)
+    want = O.int8_relu(want, case["so"], 0, case["so"], 0)
+    assert np.array_equal(out.cpu().numpy(), want)
 
 
 def _decode_projection(torch):
@@ -69,6 +88,12 @@ def _decode_projection(torch):
             assert B.lib().fth_b200_fp8_linear(C.byref(d), B.current_stream()) == B.OK
     torch.cuda.synchronize()
     assert B.last_variant() == "tcgen05"
+    # the last weight's projection against the oracle: Cast -> MatMul -> Cast, at most one E5M2 code apart
+    a_bits = a.view(torch.int16).cpu().numpy().view(np.uint16)
+    codes = O.cast(O.BF16, a_bits, 1.0, O.E5M2, 2.0 ** -9).reshape(1, k)
+    y = O.fp8_linear(O.OP_MATMUL, O.E5M2, codes, 2.0 ** -9, weights[-1].cpu().numpy(), 2.0 ** -20, 2.0 ** -9)
+    got = O.cast(O.BF16, out.view(torch.int16).cpu().numpy().view(np.uint16), 1.0, O.E5M2, 2.0 ** -9).reshape(1, n)
+    assert np.abs(got.astype(np.int32) - y.astype(np.int32)).max() <= 1
 
 
 @pytest.mark.parametrize("case", ["gemv_m1_fp8", "dense_m4096_fp8", "dense_m4096_int8", "conv_c3", "decode_projection"])
