@@ -16,6 +16,7 @@
 //               src/kernel/cuda/kernel_io.cuh:285-340) and the launch goes to cuda_detail::InferenceStream(), so
 //               deferred host sync and CUDA-graph capture (src/kernel/backend.cc:80-118) keep working.
 #include "b200_common.cuh"
+#include "b200_shard.h"
 #include "src/operator/params.h"
 #include "util/bf16.h"
 #include "util/timer.h"
@@ -25,6 +26,26 @@ namespace kernel {
 namespace b200 {
 
 bool IsB200Kernel(const KernelBase* kernel) { return dynamic_cast<const B200Kernel*>(kernel) != nullptr; }
+
+namespace {
+// A node that is the current thread's rank of a column-sharded projection (ShardBindingScope): the descriptor is pointed
+// at the group's gathered buffers, and after the launch the rank's own block is copied into the node's output tensor.
+template <typename Desc>
+const ShardBindingScope* BindShard(Desc* d, int64_t elem_bytes, void** node_out) {
+    const ShardBindingScope* shard = ShardBindingScope::Current();
+    if (shard == nullptr || !shard->Matches(d->m, d->n, elem_bytes) || d->bias_mode == FTH_B200_BIAS_MATRIX) return nullptr;
+    *node_out = d->out;
+    shard->group().Point(d, shard->rank());
+    return shard;
+}
+template <typename Desc>
+int FinishShard(const ShardBindingScope* shard, const Desc& d, void* node_out, int64_t elem_bytes, cudaStream_t stream) {
+    if (shard == nullptr) return 0;
+    const size_t row = static_cast<size_t>(d.n * elem_bytes);
+    return cudaMemcpy2DAsync(node_out, row, d.out, static_cast<size_t>(d.ldo * elem_bytes), row, static_cast<size_t>(d.m),
+                             cudaMemcpyDeviceToDevice, stream) == cudaSuccess ? 0 : -1;
+}
+}  // namespace
 size_t PackedConvWeightEntries() { return PackedConvWeightCache::LiveEntries(); }
 
 namespace {
@@ -127,9 +148,11 @@ class Fp8LinearKernel final : public B200Kernel {
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
         // An immutable weight is uploaded by the first call; from the second call on nothing on the stream writes it.
         d.weights_static = weights_resident_ ? 1 : 0;
+        void* node_out = nullptr;
+        const ShardBindingScope* shard = scratch_ == Scratch::kBuiltIn ? nullptr : BindShard(&d, 1, &node_out);
         const int rc = scratch_ == Scratch::kBuiltIn ? fth_b200_fp8_linear_noalloc(&d, cuda_detail::InferenceStream())
                                                      : fth_b200_fp8_linear(&d, cuda_detail::InferenceStream());
-        if (rc != FTH_B200_OK) return -1;
+        if (rc != FTH_B200_OK || FinishShard(shard, d, node_out, 1, cuda_detail::InferenceStream()) != 0) return -1;
         weights_resident_ = v.w->is_immutable();
         return cuda_detail::CopyDeviceToTensor(&out, v.out);  // a no-op under deferred host sync
     }
@@ -237,7 +260,10 @@ class Int8LinearKernel final : public B200Kernel {
         d.bias_max_abs = bias_max_abs_;
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
         d.weights_static = weights_resident_ ? 1 : 0;
-        if (fth_b200_int8_linear(&d, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+        void* node_out = nullptr;
+        const ShardBindingScope* shard = BindShard(&d, 1, &node_out);
+        if (fth_b200_int8_linear(&d, cuda_detail::InferenceStream()) != FTH_B200_OK ||
+            FinishShard(shard, d, node_out, 1, cuda_detail::InferenceStream()) != 0) return -1;
         weights_resident_ = v.w->is_immutable();
         return cuda_detail::CopyDeviceToTensor(&out, v.out);
     }

@@ -25,6 +25,7 @@
 #include "core/kernel.h"
 #include "core/static_graph.h"
 #include "core/tensor.h"
+#include "b200_shard.h"
 #include "fth_b200.h"
 #include "pass/graph_pass.h"
 #include "quant/static_quantizer.h"
@@ -881,11 +882,131 @@ static void RunTime() {
     { Int8Case c = MakeInt8(1, 8192, 28672); TimeNode("INT8 MatMul M=1 K=8192 N=28672 per-channel (config 5)", DataType::INT8, &c, 20); }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// shard: one process, one CudaExecutionContext per GPU, a column-sharded MatMul node per rank on the B200 candidates,
+// gathered through a ShardGroup (infer_b200/adapter/b200_shard.h).  Needs two GPUs.
+// ---------------------------------------------------------------------------------------------------------
+template <typename Case>
+static void RunShardCase(const char* what, DataType dt, Case& full, int64_t m, int64_t k, int64_t n, int world) {
+    using feather::kernel::b200::ShardBindingScope;
+    using feather::kernel::b200::ShardGroup;
+    // the unsharded node on GPU 0 is the reference for the bytes
+    std::vector<uint8_t> want(static_cast<size_t>(m * n));
+    bool ok = true;
+    {
+        (void)cudaSetDevice(0);
+        auto context = cuda::CreateExecutionContext();
+        cuda::ExecutionContextScope scope(context);
+        auto kernel = Select(DeviceType::CUDA, dt, "MatMul", &full.param);
+        ok = kernel && IsB200Kernel(kernel.get()) && kernel->Prepare() == 0 && kernel->compute() == 0;
+        if (ok) std::memcpy(want.data(), full.out->raw_data(), want.size());
+    }
+    std::vector<int> devices;
+    for (int r = 0; r < world; ++r) devices.push_back(r);
+    auto group = ShardGroup::Create(devices, m, n);
+    ok = ok && group != nullptr;
+    struct Rank {
+        std::shared_ptr<cuda::CudaExecutionContext> context;
+        std::shared_ptr<Tensor> a, w, out;
+        operators::MatMulParam param;
+        std::unique_ptr<KernelBase> kernel;
+    };
+    std::vector<Rank> ranks(static_cast<size_t>(world));
+    for (int r = 0; r < world && ok; ++r) {
+        Rank& R = ranks[static_cast<size_t>(r)];
+        const auto cols = group->Columns(r);
+        const int64_t width = cols.second - cols.first;
+        std::vector<uint8_t> slice(static_cast<size_t>(k * width));
+        const uint8_t* w = static_cast<const uint8_t*>(full.w->raw_data());
+        for (int64_t row = 0; row < k; ++row) std::memcpy(&slice[static_cast<size_t>(row * width)], w + row * n + cols.first, static_cast<size_t>(width));
+        R.w = MakeTensor(dt, {k, width}, slice.data());
+        QuantizationParams wq = full.w->quantization();
+        if (wq.granularity == QuantizationGranularity::kPerChannel) {
+            wq.scales.assign(wq.scales.begin() + cols.first, wq.scales.begin() + cols.second);
+            wq.zero_points.assign(wq.zero_points.begin() + cols.first, wq.zero_points.begin() + cols.second);
+            wq.scale = wq.scales.front();
+        }
+        R.w->set_quantization(wq);
+        R.w->set_immutable(true);
+        R.out = MakeTensor(dt, {m, width});
+        R.out->set_quantization(full.out->quantization());
+        R.a = MakeTensor(dt, {m, k}, full.a->raw_data());  // the activation is replicated: every rank has its own copy
+        R.a->set_quantization(full.a->quantization());
+        R.param.a = R.a; R.param.b = R.w; R.param.out = R.out;
+        ok = cudaSetDevice(group->device(r)) == cudaSuccess;
+        R.context = cuda::CreateExecutionContext();  // records the GPU that is current when its stream is first created
+        cuda::ExecutionContextScope scope(R.context);
+        R.kernel = Select(DeviceType::CUDA, dt, "MatMul", &R.param);
+        ok = ok && R.kernel && IsB200Kernel(R.kernel.get()) && R.kernel->Prepare() == 0;
+    }
+    int wrong_gathered = 0, wrong_block = 0, status = 0;
+    for (int step = 1; step <= 3 && ok; ++step) {
+        group->NextStep();
+        for (int r = 0; r < world && ok; ++r) {
+            Rank& R = ranks[static_cast<size_t>(r)];
+            cuda::ExecutionContextScope scope(R.context);
+            ShardBindingScope bind(group, r);
+            ok = R.kernel->compute() == 0;
+        }
+        for (int r = 0; r < world && ok; ++r) {
+            Rank& R = ranks[static_cast<size_t>(r)];
+            cuda::ExecutionContextScope scope(R.context);
+            std::vector<uint8_t> gathered(want.size());
+            ok = group->Wait(r, cuda::InferenceStream()) == FTH_B200_OK && cuda::SynchronizeInferenceStream() == 0 &&
+                 cudaMemcpy(gathered.data(), group->Buffer(r, group->Parity()), gathered.size(), cudaMemcpyDeviceToHost) == cudaSuccess;
+            status |= fth_b200_device_status();
+            for (size_t i = 0; i < want.size(); ++i) wrong_gathered += gathered[i] != want[i];
+            const auto cols = group->Columns(r);
+            const int64_t width = cols.second - cols.first;
+            const uint8_t* block = static_cast<const uint8_t*>(R.out->raw_data());
+            for (int64_t row = 0; row < m; ++row)
+                for (int64_t c = 0; c < width; ++c) wrong_block += block[row * width + c] != want[static_cast<size_t>(row * n + cols.first + c)];
+            if (ok) (void)cudaMemset(group->Buffer(r, group->Parity()), 0x5A, want.size());  // the next use of this parity must rewrite it
+        }
+    }
+    for (auto& R : ranks) {
+        if (!R.context) continue;
+        cuda::ExecutionContextScope scope(R.context);
+        R.kernel.reset();
+    }
+    (void)cudaSetDevice(0);
+    std::printf("      %s on %d GPUs: %d gathered bytes and %d bytes of the nodes' own outputs differ from the unsharded node; device status %d\n",
+                what, world, wrong_gathered, wrong_block, status);
+    CHECK_THAT(ok && wrong_gathered == 0 && wrong_block == 0 && status == 0, what);
+}
+
+static void RunShard() {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count < 2) {
+        std::printf("skip  fewer than two CUDA devices\n");
+        return;
+    }
+    feather::kernel::b200::RegisterB200Kernels();
+    const int world = count >= 4 ? 4 : 2;
+    {
+        Fp8Case c = MakeFp8(DataType::FP8E4M3, 1, 4096, 8192);
+        RunShardCase("column-sharded FP8 MatMul [1,4096]x[4096,8192] (single-launch kernel): every rank's gathered row == the unsharded node", DataType::FP8E4M3, c, 1, 4096, 8192, world);
+    }
+    {
+        Fp8Case c = MakeFp8(DataType::FP8E5M2, 16, 8192, 16384);
+        RunShardCase("column-sharded FP8 MatMul [16,8192]x[8192,16384] (weight stream + reduce pass)", DataType::FP8E5M2, c, 16, 8192, 16384, world);
+    }
+    {
+        Fp8Case c = MakeFp8(DataType::FP8E4M3, 300, 512, 2048);
+        RunShardCase("column-sharded FP8 MatMul [300,512]x[512,2048] (dense kernel, tile stores into the other GPUs)", DataType::FP8E4M3, c, 300, 512, 2048, world);
+    }
+    {
+        Int8Case c = MakeInt8(8, 1024, 4096);
+        RunShardCase("column-sharded INT8 MatMul [8,1024]x[1024,4096], per-channel scales sliced with the columns", DataType::INT8, c, 8, 1024, 4096, world);
+    }
+}
+
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "select";
     if (mode == "select") { RunSelect(); RunPlanRewrite(); }
     else if (mode == "run") RunGpu();
     else if (mode == "time") RunTime();
+    else if (mode == "shard") RunShard();
     else { std::fprintf(stderr, "usage: adapter_e2e select|run|time\n"); return 2; }
     std::printf("%s: %d failure(s)\n", mode.c_str(), g_failures);
     return g_failures == 0 ? 0 : 1;

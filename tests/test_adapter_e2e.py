@@ -55,3 +55,15 @@ def test_timing_mode_runs_on_both_candidate_sets():
     proc = subprocess.run([EXE, "time"], capture_output=True, text=True, timeout=600, env=env)
     print(proc.stdout)
     assert proc.returncode == 0 and "the reference CUDA kernel" in proc.stdout and "the b200 candidate" not in proc.stdout
+
+
+@needs_binary
+@pytest.mark.gpu
+def test_sharded_nodes_one_process_several_gpus():
+    """`adapter_e2e shard`: one CudaExecutionContext per GPU in one process, a column slice of a MatMul node per rank on
+    the B200 candidates, gathered through infer_b200/adapter/b200_shard.h; every rank's gathered buffer must equal the
+    unsharded node's output.  Needs two GPUs."""
+    out = _run("shard")
+    if any(line.startswith("skip") for line in out.splitlines()):
+        pytest.skip("needs two GPUs")
+    assert out.count("ok  ") >= 4
