@@ -46,7 +46,18 @@ struct FusedCastMatMulCastParam : operators::ParamBase {
     float a_scale{1.0f};          // scale of the FP8 activation the first Cast produced
     float proj_scale{1.0f};       // scale of the FP8 product the second Cast consumed
     bool trans_b{false};
-    template <typename Visitor> void VisitTensors(Visitor&& visit) { visit(x); visit(w); visit(out); }
+    // Decoder-block neighbours absorbed by the pass (fth_b200_fp8_linear_fused; BF16 in and out, decode-sized M):
+    std::shared_ptr<Tensor> norm_weight;  // a QwenRmsNorm node in front of the first Cast: its weight; null: none
+    float norm_offset{0.0f}, norm_epsilon{0.0f};
+    std::shared_ptr<Tensor> residual;     // an Add node behind the last Cast: its other addend; null: none
+    std::shared_ptr<Tensor> w2;           // a second projection of the same activation, with Mul(SiLU(first), second) behind both
+    bool fused() const { return norm_weight != nullptr || residual != nullptr || w2 != nullptr; }
+    template <typename Visitor> void VisitTensors(Visitor&& visit) {
+        visit(x); visit(w); visit(out);
+        if (norm_weight) visit(norm_weight);
+        if (residual) visit(residual);
+        if (w2) visit(w2);
+    }
 };
 
 struct FusedQLinearDQParam : operators::ParamBase {
@@ -153,6 +164,26 @@ bool Describe(const FusedCastMatMulCastParam* p, fth_b200_fp8_linear_desc* d) {
     return true;
 }
 
+// What the node carries around the projection, as the C ABI names it (pointers left null: the caller fills them in).
+bool DescribeFusion(const FusedCastMatMulCastParam* p, const fth_b200_fp8_linear_desc& d, fth_b200_fp8_linear_fusion* f) {
+    *f = fth_b200_fp8_linear_fusion{};
+    if (p->norm_weight) {
+        if (p->norm_weight->numel() != d.k || (p->norm_weight->data_type() != DataType::BF16 && p->norm_weight->data_type() != DataType::FP32)) return false;
+        f->prologue = FTH_B200_FUSE_RMS_NORM;
+        f->norm_weight_dtype = static_cast<int32_t>(p->norm_weight->data_type());
+        f->norm_weight_offset = p->norm_offset;
+        f->norm_epsilon = p->norm_epsilon;
+    }
+    if (p->residual && (p->residual->numel() != d.m * d.n || p->residual->data_type() != DataType::BF16)) return false;
+    if (p->w2) {
+        if (p->w2->data_type() != p->w->data_type() || p->w2->numel() != p->w->numel() || !HasCompatiblePerTensorQuantization(p->w2->quantization())) return false;
+        f->w2_scale = p->w2->quantization_scale();
+        f->n2 = d.n;
+        f->epilogue = FTH_B200_FUSE_OUT_SILU_MUL;
+    }
+    return true;
+}
+
 bool Describe(const FusedQLinearDQParam* p, fth_b200_int8_linear_desc* d, Int8WeightParams* wq) {
     int64_t m = 0, k = 0, n = 0;
     if (!p || !p->x || !p->w || !p->out || p->x->data_type() != DataType::FP32 || p->out->data_type() != DataType::FP32) return false;
@@ -210,6 +241,15 @@ class FusedCastMatMulCastKernel final : public B200Kernel {
         if (!Describe(ParamAs<FusedCastMatMulCastParam>(), &d)) return Status::Error(StatusCode::kUnsupported, "b200: not a fused Cast -> MatMul -> Cast");
         d.a = d.w = d.out = kProbe;
         d.workspace = kProbe; d.workspace_bytes = static_cast<size_t>(-1);
+        auto* p = ParamAs<FusedCastMatMulCastParam>();
+        if (p->fused()) {
+            fth_b200_fp8_linear_fusion f;
+            if (!DescribeFusion(p, d, &f)) return Status::Error(StatusCode::kUnsupported, "b200: decoder-block operands do not fit the projection");
+            if (p->norm_weight) f.norm_weight = kProbe;
+            if (p->residual) f.residual = kProbe;
+            if (p->w2) f.w2 = kProbe;
+            return FromAbi(fth_b200_fp8_linear_fused_supported(&d, &f), kFusedCastMatMulCast);
+        }
         return FromAbi(fth_b200_fp8_linear_supported(&d), kFusedCastMatMulCast);
     }
     int32_t Prepare() override {
@@ -217,6 +257,7 @@ class FusedCastMatMulCastKernel final : public B200Kernel {
         if (!Describe(ParamAs<FusedCastMatMulCastParam>(), &d)) return -1;
         d.a = d.w = d.out = kProbe;
         weights_resident_ = false;
+        if (ParamAs<FusedCastMatMulCastParam>()->fused()) return 0;  // the single-launch kernel needs no scratch
         return workspace_.Reserve(fth_b200_fp8_linear_workspace_bytes(&d), true);
     }
     int32_t compute() override {
@@ -231,6 +272,16 @@ class FusedCastMatMulCastKernel final : public B200Kernel {
         d.a = x; d.w = w; d.out = out;
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
         d.weights_static = weights_resident_ ? 1 : 0;
+        if (p->fused()) {
+            fth_b200_fp8_linear_fusion f;
+            void* norm_weight = nullptr; void* residual = nullptr; void* w2 = nullptr;
+            if (!DescribeFusion(p, d, &f) || (p->norm_weight && AcquireIn(p->norm_weight.get(), &norm_weight) != 0) ||
+                (p->residual && AcquireIn(p->residual.get(), &residual) != 0) || (p->w2 && AcquireIn(p->w2.get(), &w2) != 0)) return -1;
+            f.norm_weight = norm_weight; f.residual = residual; f.w2 = w2;
+            if (fth_b200_fp8_linear_fused(&d, &f, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
+            weights_resident_ = p->w->is_immutable() && (!p->w2 || p->w2->is_immutable()) && (!p->norm_weight || p->norm_weight->is_immutable());
+            return FinishOut(p->out.get(), out_bytes);
+        }
         if (fth_b200_fp8_linear(&d, cuda_detail::InferenceStream()) != FTH_B200_OK) return -1;
         weights_resident_ = p->w->is_immutable();
         return FinishOut(p->out.get(), out_bytes);
@@ -366,10 +417,34 @@ class Conv2DReluKernel final : public B200Kernel {
 // ---------------------------------------------------------------------------------------------------------
 std::shared_ptr<OpBase> BuildFusedCastMatMulCast(const model::NodeDesc& node, OperatorRegistry::TensorMap& tensors,
                                                  const OperatorRegistry::BuildContext& context) {
-    if (node.inputs.size() != 2 || node.outputs.size() != 1) return nullptr;
+    if (node.inputs.size() < 2 || node.inputs.size() > 5 || node.outputs.size() != 1) return nullptr;
     FusedCastMatMulCastParam param;
     param.x = tensors[node.inputs[0]];
     param.w = tensors[node.inputs[1]];
+    // optional operands, in this order, each announced by its attribute
+    size_t next = 2;
+    std::vector<std::shared_ptr<Tensor>> extra;
+    if (IntAttr(node.attributes, "norm", 0) != 0) {
+        if (next >= node.inputs.size()) return nullptr;
+        param.norm_weight = tensors[node.inputs[next++]];
+        param.norm_offset = FloatAttr(node.attributes, "norm_offset", 0.0f);
+        param.norm_epsilon = FloatAttr(node.attributes, "norm_epsilon", 0.0f);
+        if (!param.norm_weight) return nullptr;
+        extra.push_back(param.norm_weight);
+    }
+    if (IntAttr(node.attributes, "residual", 0) != 0) {
+        if (next >= node.inputs.size()) return nullptr;
+        param.residual = tensors[node.inputs[next++]];
+        if (!param.residual) return nullptr;
+        extra.push_back(param.residual);
+    }
+    if (IntAttr(node.attributes, "silu_mul", 0) != 0) {
+        if (next >= node.inputs.size()) return nullptr;
+        param.w2 = tensors[node.inputs[next++]];
+        if (!param.w2) return nullptr;
+        extra.push_back(param.w2);
+    }
+    if (next != node.inputs.size()) return nullptr;
     param.a_scale = FloatAttr(node.attributes, "a_scale", 0.0f);
     param.proj_scale = FloatAttr(node.attributes, "proj_scale", 0.0f);
     param.trans_b = IntAttr(node.attributes, "transB", 0) != 0;
@@ -381,8 +456,9 @@ std::shared_ptr<OpBase> BuildFusedCastMatMulCast(const model::NodeDesc& node, Op
     if (!param.out) return nullptr;
     param.out->set_quantization(QuantizationParams{});
     tensors[node.outputs[0]] = param.out;
-    auto op = std::make_shared<FusedOp<FusedCastMatMulCastParam>>(node.name, kFusedCastMatMulCast, param,
-                                                                  std::vector<std::shared_ptr<Tensor>>{param.x, param.w}, param.out);
+    std::vector<std::shared_ptr<Tensor>> inputs{param.x, param.w};
+    inputs.insert(inputs.end(), extra.begin(), extra.end());
+    auto op = std::make_shared<FusedOp<FusedCastMatMulCastParam>>(node.name, kFusedCastMatMulCast, param, inputs, param.out);
     auto kernel = CreateKernelForTensor(context.device, kFusedCastMatMulCast, {param.x, param.w, param.out}, param.x->data_type());
     if (!kernel) return nullptr;
     op->AttachKernel(std::move(kernel));
@@ -499,10 +575,163 @@ class B200FusionPass final : public GraphPass {
             else if (node->op_type == "ReLU") rc = FuseConvRelu(graph, *node);
             if (rc != 0) return rc;
         }
+        // Second phase: the decoder-block nodes around the fused projections of the first phase.  Gate / up pairs
+        // first (they change which node reads the norm's output), then norms in front, then residual Adds behind.
+        for (int phase = 0; phase < 3; ++phase) {
+            names.clear();
+            for (const auto& node : graph->nodes())
+                if (!node.removed && node.op_type == (phase == 0 ? "Mul" : phase == 1 ? kFusedCastMatMulCast : "Add")) names.push_back(node.name);
+            for (const auto& n : names) {
+                const StaticNode* node = graph->GetNode(n);
+                if (node == nullptr || node->removed) continue;
+                const int rc = phase == 0 ? FuseGateUp(graph, *node) : phase == 1 ? FuseNorm(graph, *node) : FuseResidual(graph, *node);
+                if (rc != 0) return rc;
+            }
+        }
         return 0;
     }
 
    private:
+    // ---- decoder-block fusions (second phase) -------------------------------------------------------------------
+    // The parameter struct a FusedCastMatMulCast node of the graph would be built with (tensors from the graph).
+    static bool ParamOfNode(const StaticGraph& graph, const StaticNode& node, const model::NodeDesc& desc, FusedCastMatMulCastParam* p) {
+        if (node.inputs.size() < 2 || node.outputs.size() != 1) return false;
+        p->x = graph.GetTensor(node.inputs[0]);
+        p->w = graph.GetTensor(node.inputs[1]);
+        p->out = graph.GetTensor(node.outputs[0]);
+        p->a_scale = FloatAttr(desc.attributes, "a_scale", 0.0f);
+        p->proj_scale = FloatAttr(desc.attributes, "proj_scale", 0.0f);
+        p->trans_b = IntAttr(desc.attributes, "transB", 0) != 0;
+        size_t next = 2;
+        if (IntAttr(desc.attributes, "norm", 0) != 0 && next < node.inputs.size()) {
+            p->norm_weight = graph.GetTensor(node.inputs[next++]);
+            p->norm_offset = FloatAttr(desc.attributes, "norm_offset", 0.0f);
+            p->norm_epsilon = FloatAttr(desc.attributes, "norm_epsilon", 0.0f);
+        }
+        if (IntAttr(desc.attributes, "residual", 0) != 0 && next < node.inputs.size()) p->residual = graph.GetTensor(node.inputs[next++]);
+        if (IntAttr(desc.attributes, "silu_mul", 0) != 0 && next < node.inputs.size()) p->w2 = graph.GetTensor(node.inputs[next++]);
+        return p->x && p->w && p->out && next == node.inputs.size();
+    }
+    // Would the library run this projection with these neighbours in one launch?
+    static bool FusedFormSupported(const FusedCastMatMulCastParam& p) {
+        fth_b200_fp8_linear_desc d;
+        fth_b200_fp8_linear_fusion f;
+        if (!Describe(&p, &d) || !DescribeFusion(&p, d, &f)) return false;
+        d.a = d.w = d.out = kProbe;
+        if (p.norm_weight) f.norm_weight = kProbe;
+        if (p.residual) f.residual = kProbe;
+        if (p.w2) f.w2 = kProbe;
+        return fth_b200_fp8_linear_fused_supported(&d, &f) == FTH_B200_OK;
+    }
+    // The node list of a FusedCastMatMulCast node from its parameter struct (inputs in the builder's order).
+    static model::NodeDesc DescOf(const std::string& name, const model::NodeDesc& base, const std::vector<std::string>& inputs,
+                                  const std::vector<std::string>& outputs, const FusedCastMatMulCastParam& p) {
+        model::NodeDesc r;
+        r.name = name;
+        r.op_type = kFusedCastMatMulCast;
+        r.inputs = inputs;
+        r.outputs = outputs;
+        r.attributes = base.attributes;
+        r.attributes["norm"] = int64_t{p.norm_weight ? 1 : 0};
+        r.attributes["norm_offset"] = p.norm_offset;
+        r.attributes["norm_epsilon"] = p.norm_epsilon;
+        r.attributes["residual"] = int64_t{p.residual ? 1 : 0};
+        r.attributes["silu_mul"] = int64_t{p.w2 ? 1 : 0};
+        return r;
+    }
+    static const StaticNode* LiveNode(const StaticGraph& graph, const std::string& name) {
+        const StaticNode* node = name.empty() ? nullptr : graph.GetNode(name);
+        return node != nullptr && !node->removed ? node : nullptr;
+    }
+
+    // Mul(SiLU(gate(h)), up(h)) with gate and up two fused projections of the same activation -> one node with two
+    // weights (matched from the Mul; either operand order).
+    static int FuseGateUp(StaticGraph* graph, const StaticNode& mul) {
+        if (mul.inputs.size() != 2 || mul.outputs.size() != 1) return 0;
+        for (int order = 0; order < 2; ++order) {
+            const std::string& silu_out = mul.inputs[static_cast<size_t>(order)];
+            const std::string& up_out = mul.inputs[static_cast<size_t>(1 - order)];
+            const StaticNode* silu = SoleProducer(*graph, silu_out, mul.name);
+            const StaticNode* up = SoleProducer(*graph, up_out, mul.name);
+            if (silu == nullptr || up == nullptr || silu->op_type != "SiLU" || silu->inputs.size() != 1 || up->op_type != kFusedCastMatMulCast) continue;
+            const StaticNode* gate = SoleProducer(*graph, silu->inputs[0], silu->name);
+            if (gate == nullptr || gate->op_type != kFusedCastMatMulCast || gate->inputs.size() != 2 || up->inputs.size() != 2 ||
+                gate->inputs[0] != up->inputs[0]) continue;
+            const model::NodeDesc* gate_desc = ModelNode(*graph, gate->name);
+            const model::NodeDesc* up_desc = ModelNode(*graph, up->name);
+            if (gate_desc == nullptr || up_desc == nullptr) continue;
+            FusedCastMatMulCastParam g, u;
+            if (!ParamOfNode(*graph, *gate, *gate_desc, &g) || !ParamOfNode(*graph, *up, *up_desc, &u)) continue;
+            // one activation Cast and one output Cast serve both products: their scales and layouts must agree
+            if (g.a_scale != u.a_scale || g.proj_scale != u.proj_scale || g.trans_b != u.trans_b || g.fused() || u.fused()) continue;
+            const auto out = graph->GetTensor(mul.outputs[0]);
+            if (!out || out->data_type() != DataType::BF16 || out->numel() != g.out->numel()) continue;
+            g.w2 = u.w;
+            g.out = out;
+            if (!FusedFormSupported(g)) continue;
+            const model::NodeDesc r = DescOf(mul.name, *gate_desc, {gate->inputs[0], gate->inputs[1], up->inputs[1]}, mul.outputs, g);
+            const std::string gate_name = gate->name, up_name = up->name, silu_name = silu->name;
+            if (!graph->ReplaceNodeDesc(r) || !graph->RemoveNode(silu_name) || !graph->RemoveNode(gate_name) || !graph->RemoveNode(up_name)) return -1;
+            return 0;
+        }
+        return 0;
+    }
+
+    // QwenRmsNorm(x, weight, epsilon) read by this fused projection alone -> the projection normalises its activation itself.
+    static int FuseNorm(StaticGraph* graph, const StaticNode& proj) {
+        const model::NodeDesc* desc = ModelNode(*graph, proj.name);
+        FusedCastMatMulCastParam p;
+        if (desc == nullptr || !ParamOfNode(*graph, proj, *desc, &p) || p.norm_weight) return 0;
+        const StaticNode* norm = SoleProducer(*graph, proj.inputs[0], proj.name);
+        if (norm == nullptr || norm->op_type != "QwenRmsNorm" || norm->inputs.size() != 3 || norm->outputs.size() != 1) return 0;
+        const model::NodeDesc* norm_desc = ModelNode(*graph, norm->name);
+        const auto x = graph->GetTensor(norm->inputs[0]);
+        const auto weight = graph->GetTensor(norm->inputs[1]);
+        double epsilon = 0.0;
+        if (norm_desc == nullptr || !x || !weight || !weight->is_immutable() || x->data_type() != DataType::BF16 ||
+            p.x->data_type() != DataType::BF16 || !ScalarConstant(*graph, norm->inputs[2], &epsilon)) return 0;
+        p.x = x;
+        p.norm_weight = weight;
+        p.norm_offset = FloatAttr(norm_desc->attributes, "weight_offset", 0.0f);
+        p.norm_epsilon = static_cast<float>(epsilon);
+        if (!FusedFormSupported(p)) return 0;
+        std::vector<std::string> inputs{norm->inputs[0], proj.inputs[1], norm->inputs[1]};
+        inputs.insert(inputs.end(), proj.inputs.begin() + 2, proj.inputs.end());  // residual / second weight keep their places
+        const model::NodeDesc r = DescOf(proj.name, *desc, inputs, proj.outputs, p);
+        const std::string norm_name = norm->name;
+        if (!graph->ReplaceNodeDesc(r) || !graph->RemoveNode(norm_name)) return -1;
+        return 0;
+    }
+
+    // Add(residual, projection) with the projection read by the Add alone -> the projection adds the residual itself
+    // (matched from the Add; either operand order).
+    static int FuseResidual(StaticGraph* graph, const StaticNode& add) {
+        if (add.inputs.size() != 2 || add.outputs.size() != 1) return 0;
+        for (int order = 0; order < 2; ++order) {
+            const StaticNode* proj = SoleProducer(*graph, add.inputs[static_cast<size_t>(order)], add.name);
+            const std::string& other = add.inputs[static_cast<size_t>(1 - order)];
+            if (proj == nullptr || proj->op_type != kFusedCastMatMulCast) continue;
+            const model::NodeDesc* desc = ModelNode(*graph, proj->name);
+            FusedCastMatMulCastParam p;
+            if (desc == nullptr || !ParamOfNode(*graph, *proj, *desc, &p) || p.residual || p.w2) continue;
+            const auto residual = graph->GetTensor(other);
+            const auto out = graph->GetTensor(add.outputs[0]);
+            if (!residual || !out || residual->data_type() != DataType::BF16 || out->data_type() != DataType::BF16 ||
+                residual->numel() != p.out->numel() || out->numel() != p.out->numel()) continue;
+            p.residual = residual;
+            p.out = out;
+            if (!FusedFormSupported(p)) continue;
+            std::vector<std::string> inputs{proj->inputs[0], proj->inputs[1]};
+            if (p.norm_weight) inputs.push_back(proj->inputs[2]);
+            inputs.push_back(other);
+            const model::NodeDesc r = DescOf(add.name, *desc, inputs, add.outputs, p);
+            const std::string proj_name = proj->name;
+            if (!graph->ReplaceNodeDesc(r) || !graph->RemoveNode(proj_name)) return -1;
+            return 0;
+        }
+        return 0;
+    }
+
     // Cast(wide -> FP8) -> MatMul / Gemm(transB, no bias, alpha = beta = 1) -> Cast(FP8 -> wide), matched from the last
     // Cast.  The lm-head form (the last Cast writes the graph output "logits" of a Qwen plan, [1,K] x [N,K]) becomes
     // QwenGemmArgmax as in the reference's own pass; every other chain becomes FusedCastMatMulCast.

@@ -565,6 +565,56 @@ static Fp8Plan MakeFp8Plan() {
     return p;
 }
 
+// The MLP half of a Qwen decoder block as the exporter writes it, every projection wrapped in its two Casts:
+//   h = QwenRmsNorm(x, g, eps);  a = Mul(SiLU(gate(h)), up(h));  y = Add(x, down(a))
+static Fp8Plan MakeDecoderMlpPlan() {
+    const int64_t hidden = 1024, inter = 3584;
+    const float act_scale = 1.0f / 512, w_scale = 1.0f / 1048576, out_scale = 1.0f / 512;
+    Fp8Plan p;
+    p.model.name = "b200_decoder_mlp"; p.model.version = 1; p.model.graph.name = "main";
+    p.model.graph.inputs = {"x"};
+    p.model.graph.outputs = {"y"};
+    p.model.graph.values = {Value("x", {1, hidden}, DataType::BF16), Value("g", {hidden}, DataType::BF16, true), Value("eps", {1}, DataType::FP32, true),
+                            Value("h", {1, hidden}, DataType::BF16), Value("s", {1, inter}, DataType::BF16), Value("a", {1, inter}, DataType::BF16),
+                            Value("y", {1, hidden}, DataType::BF16)};
+    std::vector<uint16_t> x(static_cast<size_t>(hidden)), g(static_cast<size_t>(hidden));
+    for (auto& v : x) v = FloatToBFloat16(Uniform(-3, 3));
+    for (auto& v : g) v = FloatToBFloat16(Uniform(-0.2f, 0.2f));
+    p.input = MakeTensor(DataType::BF16, {1, hidden}, x.data());
+    p.weights["g"] = MakeTensor(DataType::BF16, {hidden}, g.data());
+    p.weights["g"]->set_immutable(true);
+    const float eps = 1e-6f;
+    p.weights["eps"] = MakeTensor(DataType::FP32, {1}, &eps);
+    p.weights["eps"]->set_immutable(true);
+    NodeDesc norm; norm.name = "norm"; norm.op_type = "QwenRmsNorm"; norm.inputs = {"x", "g", "eps"}; norm.outputs = {"h"}; norm.attributes["weight_offset"] = 1.0f;
+    p.model.graph.nodes.push_back(norm);
+    auto projection = [&](const std::string& n, const std::string& in, int64_t k, int64_t cols, float magnitude) {
+        std::vector<uint8_t> w(static_cast<size_t>(k * cols));
+        for (auto& v : w) v = FloatToFp8E5M2(Uniform(-magnitude, magnitude));
+        auto wt = MakeTensor(DataType::FP8E5M2, {k, cols}, w.data());
+        wt->set_quantization({true, w_scale});
+        wt->set_immutable(true);
+        p.weights[n + "_w"] = wt;
+        p.model.graph.values.push_back(Value(n + "_in8", {1, k}, DataType::FP8E5M2, false, act_scale));
+        p.model.graph.values.push_back(Value(n + "_w", {k, cols}, DataType::FP8E5M2, true, w_scale));
+        p.model.graph.values.push_back(Value(n + "_out8", {1, cols}, DataType::FP8E5M2, false, out_scale));
+        p.model.graph.values.push_back(Value(n + "_out", {1, cols}, DataType::BF16));
+        NodeDesc c0; c0.name = n + "_to_fp8"; c0.op_type = "Cast"; c0.inputs = {in}; c0.outputs = {n + "_in8"}; c0.attributes["to"] = int64_t{19};
+        NodeDesc mm; mm.name = n + "_matmul"; mm.op_type = "MatMul"; mm.inputs = {n + "_in8", n + "_w"}; mm.outputs = {n + "_out8"};
+        NodeDesc c1; c1.name = n + "_to_bf16"; c1.op_type = "Cast"; c1.inputs = {n + "_out8"}; c1.outputs = {n + "_out"}; c1.attributes["to"] = int64_t{16};
+        p.model.graph.nodes.push_back(c0); p.model.graph.nodes.push_back(mm); p.model.graph.nodes.push_back(c1);
+    };
+    projection("gate", "h", hidden, inter, 40000.0f);
+    projection("up", "h", hidden, inter, 40000.0f);
+    NodeDesc silu; silu.name = "silu"; silu.op_type = "SiLU"; silu.inputs = {"gate_out"}; silu.outputs = {"s"};
+    NodeDesc mul; mul.name = "mul"; mul.op_type = "Mul"; mul.inputs = {"s", "up_out"}; mul.outputs = {"a"};
+    p.model.graph.nodes.push_back(silu); p.model.graph.nodes.push_back(mul);
+    projection("down", "a", inter, hidden, 20000.0f);
+    NodeDesc add; add.name = "add"; add.op_type = "Add"; add.inputs = {"x", "down_out"}; add.outputs = {"y"};
+    p.model.graph.nodes.push_back(add);
+    return p;
+}
+
 // A float model quantised by the reference's own static quantiser (src/quant/static_quantizer.cc:602-806):
 //   x -> Conv2D 3x3 (64 -> 64, bias) -> ReLU -> Flatten -> Gemm (bias) -> y
 struct Int8Plan {
@@ -727,6 +777,14 @@ static void RunPlanRewrite() {
                    "pass: two Cast -> MatMul -> Cast projections of one activation become two FusedCastMatMulCast nodes (6 nodes -> 2)");
     }
     {
+        Fp8Plan p = MakeDecoderMlpPlan();
+        PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, false);
+        PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, false);
+        std::printf("      decoder MLP plan: %s  ->  %s  %s%s\n", Join(plain.op_types).c_str(), Join(fused.op_types).c_str(), plain.error.c_str(), fused.error.c_str());
+        CHECK_THAT(plain.ok && plain.op_types.size() == 13 && fused.ok && fused.op_types.size() == 2 && Count(fused.op_types, "FusedCastMatMulCast") == 2,
+                   "pass: QwenRmsNorm + gate | up + SiLU * Mul become one node, down + the residual Add another (13 nodes -> 2)");
+    }
+    {
         Int8Plan p = MakeInt8Plan();
         CHECK_THAT(p.ok && p.report.quantized_nodes.size() == 4, "the reference's StaticQuantizeModel quantises Conv2D / ReLU / Flatten / Gemm");
         PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, false);
@@ -771,6 +829,33 @@ static void RunPlansOnGpu() {
         }
         std::printf("      FP8 plan on CUDA: %s%s%s; max code distance from the COMMON plan %d\n", ref.error.c_str(), plain.error.c_str(), fused.error.c_str(), worst);
         CHECK_THAT(ok && worst >= 0 && worst <= 1, "FP8 projection plan: fused plan == unfused CUDA plan byte for byte, both within one code of the COMMON plan");
+    }
+    {
+        Fp8Plan p = MakeDecoderMlpPlan();
+        PlanRun ref = RunPlan(p.model, p.weights, "x", p.input, DeviceType::COMMON, false, true);
+        PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, true);
+        PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, true);
+        bool ok = ref.ok && plain.ok && fused.ok && fused.op_types.size() == 2;
+        int differ_plain = -1, differ_ref = -1;
+        double cosine = 0.0;
+        if (ok) {
+            differ_plain = differ_ref = 0;
+            const uint16_t* f = reinterpret_cast<const uint16_t*>(fused.outputs["y"].data());
+            const uint16_t* c = reinterpret_cast<const uint16_t*>(plain.outputs["y"].data());
+            const uint16_t* r = reinterpret_cast<const uint16_t*>(ref.outputs["y"].data());
+            double dot = 0, nf = 0, nr = 0;
+            for (size_t i = 0; i < fused.outputs["y"].size() / 2; ++i) {
+                differ_plain += f[i] != c[i];
+                differ_ref += f[i] != r[i];
+                const double a = BFloat16ToFloat(f[i]), b = BFloat16ToFloat(r[i]);
+                dot += a * b; nf += a * a; nr += b * b;
+            }
+            cosine = dot / std::sqrt(nf * nr);
+        }
+        std::printf("      decoder MLP plan on CUDA (%zu nodes fused to %zu): %d outputs differ from the node-by-node CUDA plan, %d from the COMMON plan (cosine %.6f) %s%s%s\n",
+                    plain.op_types.size(), fused.op_types.size(), differ_plain, differ_ref, cosine, ref.error.c_str(), plain.error.c_str(), fused.error.c_str());
+        CHECK_THAT(ok && differ_plain == 0 && cosine >= 0.9999,
+                   "decoder MLP plan: the two fused launches return the bytes of the thirteen nodes, and the COMMON plan's result up to single codes");
     }
     {
         Int8Plan p = MakeInt8Plan();
