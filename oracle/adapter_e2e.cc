@@ -615,6 +615,47 @@ static Fp8Plan MakeDecoderMlpPlan() {
     return p;
 }
 
+// The front of an attention block: one QwenRmsNorm read by three projections.
+static Fp8Plan MakeNormQkvPlan() {
+    const int64_t hidden = 1024;
+    const float act_scale = 1.0f / 512, w_scale = 1.0f / 1048576, out_scale = 1.0f / 512;
+    Fp8Plan p;
+    p.model.name = "b200_norm_qkv"; p.model.version = 1; p.model.graph.name = "main";
+    p.model.graph.inputs = {"x"};
+    p.model.graph.outputs = {"q_out", "k_out", "v_out"};
+    p.model.graph.values = {Value("x", {1, hidden}, DataType::BF16), Value("g", {hidden}, DataType::BF16, true), Value("eps", {1}, DataType::FP32, true),
+                            Value("h", {1, hidden}, DataType::BF16)};
+    std::vector<uint16_t> x(static_cast<size_t>(hidden)), g(static_cast<size_t>(hidden));
+    for (auto& v : x) v = FloatToBFloat16(Uniform(-3, 3));
+    for (auto& v : g) v = FloatToBFloat16(Uniform(-0.2f, 0.2f));
+    p.input = MakeTensor(DataType::BF16, {1, hidden}, x.data());
+    p.weights["g"] = MakeTensor(DataType::BF16, {hidden}, g.data());
+    p.weights["g"]->set_immutable(true);
+    const float eps = 1e-6f;
+    p.weights["eps"] = MakeTensor(DataType::FP32, {1}, &eps);
+    p.weights["eps"]->set_immutable(true);
+    NodeDesc norm; norm.name = "norm"; norm.op_type = "QwenRmsNorm"; norm.inputs = {"x", "g", "eps"}; norm.outputs = {"h"}; norm.attributes["weight_offset"] = 1.0f;
+    p.model.graph.nodes.push_back(norm);
+    for (const char* name : {"q", "k", "v"}) {
+        const std::string n = name;
+        std::vector<uint8_t> w(static_cast<size_t>(hidden * hidden));
+        for (auto& v : w) v = FloatToFp8E5M2(Uniform(-40000, 40000));
+        auto wt = MakeTensor(DataType::FP8E5M2, {hidden, hidden}, w.data());
+        wt->set_quantization({true, w_scale});
+        wt->set_immutable(true);
+        p.weights[n + "_w"] = wt;
+        p.model.graph.values.push_back(Value(n + "_in8", {1, hidden}, DataType::FP8E5M2, false, act_scale));
+        p.model.graph.values.push_back(Value(n + "_w", {hidden, hidden}, DataType::FP8E5M2, true, w_scale));
+        p.model.graph.values.push_back(Value(n + "_out8", {1, hidden}, DataType::FP8E5M2, false, out_scale));
+        p.model.graph.values.push_back(Value(n + "_out", {1, hidden}, DataType::BF16));
+        NodeDesc c0; c0.name = n + "_to_fp8"; c0.op_type = "Cast"; c0.inputs = {"h"}; c0.outputs = {n + "_in8"}; c0.attributes["to"] = int64_t{19};
+        NodeDesc mm; mm.name = n + "_matmul"; mm.op_type = "MatMul"; mm.inputs = {n + "_in8", n + "_w"}; mm.outputs = {n + "_out8"};
+        NodeDesc c1; c1.name = n + "_to_bf16"; c1.op_type = "Cast"; c1.inputs = {n + "_out8"}; c1.outputs = {n + "_out"}; c1.attributes["to"] = int64_t{16};
+        p.model.graph.nodes.push_back(c0); p.model.graph.nodes.push_back(mm); p.model.graph.nodes.push_back(c1);
+    }
+    return p;
+}
+
 // A float model quantised by the reference's own static quantiser (src/quant/static_quantizer.cc:602-806):
 //   x -> Conv2D 3x3 (64 -> 64, bias) -> ReLU -> Flatten -> Gemm (bias) -> y
 struct Int8Plan {
@@ -785,6 +826,14 @@ static void RunPlanRewrite() {
                    "pass: QwenRmsNorm + gate | up + SiLU * Mul become one node, down + the residual Add another (13 nodes -> 2)");
     }
     {
+        Fp8Plan p = MakeNormQkvPlan();
+        PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, false);
+        PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, false);
+        std::printf("      norm + q / k / v plan: %s  ->  %s  %s%s\n", Join(plain.op_types).c_str(), Join(fused.op_types).c_str(), plain.error.c_str(), fused.error.c_str());
+        CHECK_THAT(plain.ok && plain.op_types.size() == 10 && fused.ok && fused.op_types.size() == 3 && Count(fused.op_types, "FusedCastMatMulCast") == 3,
+                   "pass: a QwenRmsNorm read by three projections moves into each of them (10 nodes -> 3)");
+    }
+    {
         Int8Plan p = MakeInt8Plan();
         CHECK_THAT(p.ok && p.report.quantized_nodes.size() == 4, "the reference's StaticQuantizeModel quantises Conv2D / ReLU / Flatten / Gemm");
         PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, false);
@@ -829,6 +878,14 @@ static void RunPlansOnGpu() {
         }
         std::printf("      FP8 plan on CUDA: %s%s%s; max code distance from the COMMON plan %d\n", ref.error.c_str(), plain.error.c_str(), fused.error.c_str(), worst);
         CHECK_THAT(ok && worst >= 0 && worst <= 1, "FP8 projection plan: fused plan == unfused CUDA plan byte for byte, both within one code of the COMMON plan");
+    }
+    {
+        Fp8Plan p = MakeNormQkvPlan();
+        PlanRun plain = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, false, true);
+        PlanRun fused = RunPlan(p.model, p.weights, "x", p.input, DeviceType::CUDA, true, true);
+        bool ok = plain.ok && fused.ok && fused.op_types.size() == 3;
+        for (const char* name : {"q_out", "k_out", "v_out"}) ok = ok && fused.outputs[name] == plain.outputs[name] && !fused.outputs[name].empty();
+        CHECK_THAT(ok, "norm + q / k / v plan: three launches with the norm inside return the bytes of the ten nodes");
     }
     {
         Fp8Plan p = MakeDecoderMlpPlan();
