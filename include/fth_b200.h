@@ -177,6 +177,11 @@ size_t fth_b200_fp8_linear_workspace_bytes(const fth_b200_fp8_linear_desc* desc)
  *             n2 = desc->n, with scale w2_scale, output out2 [M,n2] (row stride ldo2, 0 = n2).
  *   epilogue  FTH_B200_FUSE_OUT_SILU_MUL (needs w2, no residual): desc->out receives Mul(SiLU(first product), second
  *             product), the activation of the down projection; out2 is not written and may be null.
+ *   out_codes (with out_codes_scale, row stride ldo_codes, 0 = n): every output is also stored as the FP8 code the Cast
+ *             node in front of the NEXT projection would make of it (format = desc->dtype) — that projection then takes
+ *             the codes as its activation (a_dtype = 0) and runs no Cast of its own.  Not with a second weight unless the
+ *             SiLU * Mul epilogue joins the two products.
+ * desc->a_dtype may be 0 here (activations that are such codes already) when no prologue is asked for.
  * A norm weight is read ahead of the work queued in front of the call when desc->weights_static says the same of the
  * projection weights: it is a constant of the model like them.
  * Every rounding point of the unfused nodes is kept (BF16 after the norm / SiLU / Mul, FP8 after the Cast, FP8 after
@@ -201,6 +206,9 @@ typedef struct {
     int64_t n2;
     int64_t ldo2;
     int32_t epilogue;            /* FTH_B200_FUSE_OUT_* */
+    float out_codes_scale;
+    void* out_codes;             /* or null */
+    int64_t ldo_codes;
 } fth_b200_fp8_linear_fusion;
 int fth_b200_fp8_linear_fused(const fth_b200_fp8_linear_desc* desc, const fth_b200_fp8_linear_fusion* fusion, fth_b200_stream_t stream);
 int fth_b200_fp8_linear_fused_supported(const fth_b200_fp8_linear_desc* desc, const fth_b200_fp8_linear_fusion* fusion);

@@ -57,7 +57,8 @@ class Fp8LinearFusion(C.Structure):
     _fields_ = [
         ("prologue", C.c_int32), ("norm_weight_dtype", C.c_int32), ("norm_weight", C.c_void_p), ("norm_weight_offset", C.c_float),
         ("norm_epsilon", C.c_float), ("a2", C.c_void_p), ("residual", C.c_void_p), ("w2", C.c_void_p), ("w2_scale", C.c_float),
-        ("out2", C.c_void_p), ("n2", C.c_int64), ("ldo2", C.c_int64), ("epilogue", C.c_int32),
+        ("out2", C.c_void_p), ("n2", C.c_int64), ("ldo2", C.c_int64), ("epilogue", C.c_int32), ("out_codes_scale", C.c_float),
+        ("out_codes", C.c_void_p), ("ldo_codes", C.c_int64),
     ]
 
 
@@ -209,12 +210,14 @@ def fp8_linear(desc: Fp8LinearDesc, stream=None) -> None:
 
 
 def fp8_linear_fusion(*, prologue=FUSE_NONE, norm_weight=None, norm_weight_dtype=BF16, norm_weight_offset=0.0, norm_epsilon=1e-6, a2=None,
-                      residual=None, w2=None, w2_scale=1.0, out2=None, n2=0, ldo2=0, epilogue=FUSE_OUT_NONE) -> Fp8LinearFusion:
+                      residual=None, w2=None, w2_scale=1.0, out2=None, n2=0, ldo2=0, epilogue=FUSE_OUT_NONE, out_codes=None,
+                      out_codes_scale=1.0, ldo_codes=0) -> Fp8LinearFusion:
     f = Fp8LinearFusion()
     f.prologue, f.norm_weight_dtype, f.norm_weight = prologue, norm_weight_dtype, ptr(norm_weight)
     f.norm_weight_offset, f.norm_epsilon = norm_weight_offset, norm_epsilon
     f.a2, f.residual, f.w2, f.w2_scale, f.out2, f.n2, f.ldo2 = ptr(a2), ptr(residual), ptr(w2), w2_scale, ptr(out2), n2, ldo2
     f.epilogue = epilogue
+    f.out_codes, f.out_codes_scale, f.ldo_codes = ptr(out_codes), out_codes_scale, ldo_codes
     return f
 
 

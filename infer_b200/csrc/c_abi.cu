@@ -354,6 +354,11 @@ static int BuildFused(const fth_b200_fp8_linear_desc* d, const fth_b200_fp8_line
     fu.w2 = f->w2; fu.out2 = f->out2; fu.n2 = f->n2; fu.ldo2 = f->ldo2 ? f->ldo2 : f->n2;
     fu.ab_scale2 = d->a_scale * f->w2_scale;
     fu.epilogue = f->epilogue;
+    fu.out_codes = f->out_codes;
+    fu.codes_scale = f->out_codes_scale;
+    fu.codes_inv = 0.0f;  // set by the launcher
+    fu.ldo_codes = f->ldo_codes ? f->ldo_codes : d->n;
+    if (fu.out_codes != nullptr && !ValidScale(f->out_codes_scale)) return FTH_B200_ERR_INVALID;
     if (fu.prologue == 1 && (!std::isfinite(fu.norm_epsilon) || fu.norm_epsilon < 0.0f)) return FTH_B200_ERR_INVALID;
     if (fu.w2 != nullptr && !ValidScale(f->w2_scale)) return FTH_B200_ERR_INVALID;
     Int8Epilogue ie = {};

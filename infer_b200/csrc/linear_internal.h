@@ -38,7 +38,10 @@ struct DecoderFusion {
     void* out2;               // its BF16 output [M,n2], row stride ldo2
     int64_t n2, ldo2;
     int epilogue;             // with w2: 1 = out receives Mul(SiLU(first product), second product); out2 is not written
-    bool active() const { return prologue != 0 || residual != nullptr || w2 != nullptr; }
+    void* out_codes;          // also store Cast(out -> FP8 of the projection's format, codes_scale) [M, N], row stride ldo_codes; null: none
+    float codes_scale, codes_inv;  // (codes_inv: the exact reciprocal of a power-of-two scale, else 0)
+    int64_t ldo_codes;
+    bool active() const { return prologue != 0 || residual != nullptr || w2 != nullptr || out_codes != nullptr; }
 };
 
 // Operand description common to FP8 and INT8 linear kernels.

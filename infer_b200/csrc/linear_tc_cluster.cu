@@ -336,7 +336,9 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const bool weights_early = prologue == 1 && p.args.w_static != 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) raw2[j] = make_uint4(0, 0, 0, 0);
-            if (nb > 0) {
+            // (8-bit activations — a producer's epilogue has already run the Cast — arrive by TMA: no prologue at all)
+            const bool prologue_here = convert && nb > 0;
+            if (prologue_here) {
                 locate(et);
                 if (weights_early) load_norm_weights();
             }
@@ -352,11 +354,11 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 }
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            if (nb > 0) load_activations();
+            if (prologue_here) load_activations();
 #pragma unroll
             for (int i = 0; i < 2; ++i)
                 if (early_at[i] >= 0) residual_early[i] = static_cast<const uint16_t*>(fu.residual)[early_at[i]];
-            if (nb > 0 && prologue == 1) {
+            if (prologue_here && prologue == 1) {
                 // Fused QwenRmsNorm in front of the Cast: 1 / rms of every activation row, with the sum of squares added in
                 // the order of the stand-alone kernel (128 threads that each add their groups of eight elements in turn, a
                 // lane tree per warp, the four warps in order), so that the fused node returns the stand-alone node's bits.
@@ -395,7 +397,7 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 }
                 EpilogueBarrier<128>();
             }
-            if (nb > 0) {
+            if (prologue_here) {
                 if (prologue == 1 && !weights_early) load_norm_weights();
                 for (int base = et;;) {
 #pragma unroll
@@ -545,6 +547,12 @@ LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     bits = EncodeBf16Cast(__fadd_rn(DecodeBf16(other), DecodeBf16(bits)));
                 }
                 out[o] = bits;
+                if (fu.out_codes != nullptr) {
+                    // the Cast node in front of the NEXT projection, run here once per output instead of once per CTA there
+                    const float v = DecodeBf16(bits);
+                    const float y = v != v ? v : (fu.codes_inv != 0.0f ? __fmul_rn(v, fu.codes_inv) : __fdiv_rn(v, fu.codes_scale));
+                    static_cast<uint8_t*>(fu.out_codes)[q * fu.ldo_codes + n] = static_cast<uint8_t>(EncodePair(p.e4m3, y, 0.0f) & 0xffu);
+                }
             }
         } else {
         // Column-sharded projection with the gather's signalling folded in: before the first store into the peers'

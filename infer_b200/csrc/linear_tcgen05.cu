@@ -148,7 +148,8 @@ bool Tcgen05StoresToPeers(int dtype, const LinearArgs& a, const Fp8Epilogue& fe,
 // per-tensor scales, no bias, nothing stored to peers, no selection.
 static bool DecoderForm(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, const Int8Epilogue& ie) {
     if (dtype == FTH_B200_INT8 || GeometryFor(a).cluster == 0) return false;
-    if (a.a_dtype != FTH_B200_BF16 || fe.out_dtype != FTH_B200_BF16 || !DirectEpilogue(false, fe, ie)) return false;
+    // activations: BF16 (the kernel runs the Cast) or already FP8 codes of the projection's format (a producer ran it)
+    if ((a.a_dtype != FTH_B200_BF16 && a.a_dtype != 0) || fe.out_dtype != FTH_B200_BF16 || !DirectEpilogue(false, fe, ie)) return false;
     if (fe.w_channel_scales != nullptr || a.argmax_keys != nullptr || a.peers.count != 0 || a.signal.world != 0) return false;
     return reinterpret_cast<uintptr_t>(a.a) % 16 == 0;
 }
@@ -163,6 +164,8 @@ int Tcgen05FusionStatus(int dtype, const LinearArgs& a, const Fp8Epilogue& fe, c
     if ((fu.prologue == 1 && reinterpret_cast<uintptr_t>(fu.norm_weight) % 16 != 0) ||
         (fu.prologue == 2 && reinterpret_cast<uintptr_t>(fu.a2) % 16 != 0)) return FTH_B200_ERR_UNSUPPORTED;
     if (fu.prologue < 0 || fu.prologue > 2) return FTH_B200_ERR_INVALID;
+    if (fu.prologue != 0 && a.a_dtype != FTH_B200_BF16) return FTH_B200_ERR_INVALID;  // the nodes in front work on BF16 values
+    if (fu.out_codes != nullptr && (fu.ldo_codes < a.n || (fu.w2 != nullptr && fu.epilogue == 0))) return FTH_B200_ERR_INVALID;
     if (fu.prologue == 1 && fu.norm_weight == nullptr) return FTH_B200_ERR_INVALID;
     if (fu.prologue == 1 && (fu.norm_weight_dtype != FTH_B200_BF16 && fu.norm_weight_dtype != FTH_B200_FP32)) return FTH_B200_ERR_UNSUPPORTED;
     if (fu.prologue == 1 && a.k > rowops_max_hidden()) return FTH_B200_ERR_UNSUPPORTED;
@@ -200,6 +203,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     if (a.fusion.active()) {
         const int rc = Tcgen05FusionStatus(dtype, a, fe, ie);
         if (rc != FTH_B200_OK) return rc;
+        a.fusion.codes_inv = a.fusion.out_codes != nullptr ? ExactReciprocal(a.fusion.codes_scale) : 0.0f;
     }
     if (a.a_dtype != 0 && g.cluster == 0) {
         int rc;

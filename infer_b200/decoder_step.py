@@ -7,7 +7,9 @@ projections wrapped in Cast nodes, QwenRmsNorm with weight offset 1, SiLU * Mul 
     h = QwenRmsNorm(x, g2);  a = Mul(SiLU(gate(h)), up(h));  x = Add(x, down(a))
 
 `fused=True` issues six launches per layer through fth_b200_fp8_linear_fused — norm + q, k, v, o + residual,
-norm + gate | up + SiLU * Mul (one launch, two weights), down + residual; `fused=False` issues every node's own kernel
+norm + gate | up + SiLU * Mul (one launch, two weights), down + residual — and every launch whose output feeds the next
+projection directly also stores the FP8 codes that projection's Cast would make of it (out_codes), so that k, v, o and
+down read 8-bit activations and run no Cast of their own; `fused=False` issues every node's own kernel
 (twelve launches per layer: fth_b200_qwen_rms_norm, the Cast -> MatMul -> Cast projections, fth_b200_binary,
 fth_b200_silu_mul).  Both give the same bytes.  Everything stays on the device; the caller may capture `run` in a CUDA
 graph.  torch supplies the device buffers only.
@@ -34,14 +36,19 @@ class DecoderStep:
         self.gate = torch.zeros((m, inter), **bf)
         self.up = torch.zeros((m, inter), **bf)
         self.act = torch.zeros((m, inter), **bf)
+        codes = dict(dtype=torch.uint8, device="cuda")
+        self.c = [torch.zeros((m, hidden), **codes) for _ in range(2)]   # FP8 codes of t[0] / t[1] for the next projection
+        self.act_codes = torch.zeros((m, inter), **codes)
         self.keep = []
         self.calls = []
         self._build()
 
     # ---- descriptors -------------------------------------------------------------------------------------------------
-    def _proj(self, a, w, w_scale, out, k, n):
+    def _proj(self, a, w, w_scale, out, k, n, codes_in=False):
+        """codes_in: `a` holds the FP8 codes of the activation already (a producer's out_codes)."""
         d = B.fp8_linear_desc(dtype=self.dtype, op=B.OP_MATMUL, m=self.m, k=k, n=n, a=a, w=w, out=out, a_scale=self.act_scale,
-                              w_scale=w_scale, out_scale=self.out_scale, a_dtype=B.BF16, out_dtype=B.BF16, weights_static=True)
+                              w_scale=w_scale, out_scale=self.out_scale, a_dtype=0 if codes_in else B.BF16, out_dtype=B.BF16,
+                              weights_static=True)
         self.keep.append(B.linear_workspace(self.torch, d))
         return d
 
@@ -60,16 +67,17 @@ class DecoderStep:
         x, nxt = self.x, self.x2
         for layer in self.layers:
             if self.fused:
+                cast = dict(out_codes_scale=self.act_scale)  # the Cast in front of the next projection, run by the producer
                 self._fused(self._proj(x, layer["q"], layer["q_scale"], self.t[0], H, H), prologue=B.FUSE_RMS_NORM, norm_weight=layer["g1"],
-                            norm_weight_offset=1.0, norm_epsilon=self.eps)
-                self._plain(self._proj(self.t[0], layer["k"], layer["k_scale"], self.t[1], H, H))
-                self._plain(self._proj(self.t[1], layer["v"], layer["v_scale"], self.t[0], H, H))
-                self._fused(self._proj(self.t[0], layer["o"], layer["o_scale"], nxt, H, H), residual=x)
+                            norm_weight_offset=1.0, norm_epsilon=self.eps, out_codes=self.c[0], **cast)
+                self._fused(self._proj(self.c[0], layer["k"], layer["k_scale"], self.t[1], H, H, codes_in=True), out_codes=self.c[1], **cast)
+                self._fused(self._proj(self.c[1], layer["v"], layer["v_scale"], self.t[0], H, H, codes_in=True), out_codes=self.c[0], **cast)
+                self._fused(self._proj(self.c[0], layer["o"], layer["o_scale"], nxt, H, H, codes_in=True), residual=x)
                 x, nxt = nxt, x
                 self._fused(self._proj(x, layer["gate"], layer["gate_scale"], self.gate, H, I), prologue=B.FUSE_RMS_NORM, norm_weight=layer["g2"],
                             norm_weight_offset=1.0, norm_epsilon=self.eps, w2=layer["up"], w2_scale=layer["up_scale"], n2=I,
-                            epilogue=B.FUSE_OUT_SILU_MUL)
-                self._fused(self._proj(self.gate, layer["down"], layer["down_scale"], nxt, I, H), residual=x)
+                            epilogue=B.FUSE_OUT_SILU_MUL, out_codes=self.act_codes, **cast)
+                self._fused(self._proj(self.act_codes, layer["down"], layer["down_scale"], nxt, I, H, codes_in=True), residual=x)
                 x, nxt = nxt, x
             else:
                 self.calls.append(("norm", (x, layer["g1"], self.h), None))

@@ -38,7 +38,7 @@ def test_struct_layouts_match_the_c_compiler():
 #define P(T, F) printf(#T "." #F " %zu\n", offsetof(T, F))
 int main(void) {
   printf("sizeof.fp8 %zu\nsizeof.int8 %zu\nsizeof.conv %zu\nsizeof.fusion %zu\n", sizeof(fth_b200_fp8_linear_desc), sizeof(fth_b200_int8_linear_desc), sizeof(fth_b200_int8_conv2d_desc), sizeof(fth_b200_fp8_linear_fusion));
-  P(fth_b200_fp8_linear_fusion, norm_weight); P(fth_b200_fp8_linear_fusion, norm_epsilon); P(fth_b200_fp8_linear_fusion, w2_scale); P(fth_b200_fp8_linear_fusion, ldo2); P(fth_b200_fp8_linear_fusion, epilogue);
+  P(fth_b200_fp8_linear_fusion, norm_weight); P(fth_b200_fp8_linear_fusion, norm_epsilon); P(fth_b200_fp8_linear_fusion, w2_scale); P(fth_b200_fp8_linear_fusion, ldo2); P(fth_b200_fp8_linear_fusion, epilogue); P(fth_b200_fp8_linear_fusion, out_codes); P(fth_b200_fp8_linear_fusion, ldo_codes);
   P(fth_b200_fp8_linear_desc, a); P(fth_b200_fp8_linear_desc, ldo); P(fth_b200_fp8_linear_desc, w_channel_scales);
   P(fth_b200_fp8_linear_desc, workspace); P(fth_b200_fp8_linear_desc, variant); P(fth_b200_fp8_linear_desc, gather_out);
   P(fth_b200_fp8_linear_desc, gather_world); P(fth_b200_fp8_linear_desc, gather_flags); P(fth_b200_int8_linear_desc, gather_flags);

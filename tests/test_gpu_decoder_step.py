@@ -176,3 +176,10 @@ def test_fused_call_rejections(cuda):
     assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(epilogue=B.FUSE_OUT_SILU_MUL, **w2))) == B.OK             # out2 not needed
     assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(**w2))) == B.ERR_INVALID                                  # ... but needed here
     assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(out2=out, **dict(w2, n2=512)))) == B.ERR_INVALID          # columns must pair up
+    codes = torch.zeros((1, 1024), dtype=torch.uint8, device="cuda")
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(out_codes=codes, out_codes_scale=0.5))) == B.OK
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(out_codes=codes, out_codes_scale=0.0))) == B.ERR_INVALID
+    assert sup(C.byref(ok), C.byref(B.fp8_linear_fusion(out_codes=codes, out2=out, **w2))) == B.ERR_INVALID       # which of the two outputs?
+    from_codes = B.fp8_linear_desc(a_dtype=0, out_dtype=B.BF16, **dict(base, a=codes))
+    assert sup(C.byref(from_codes), C.byref(B.fp8_linear_fusion(residual=out))) == B.OK                           # 8-bit activations in
+    assert sup(C.byref(from_codes), C.byref(B.fp8_linear_fusion(prologue=B.FUSE_RMS_NORM, norm_weight=a))) == B.ERR_INVALID  # a norm works on BF16
