@@ -279,7 +279,7 @@ void BuildInt8(const fth_b200_int8_linear_desc* d, LinearArgs* args, Int8Epilogu
 
 using namespace fth;
 
-extern "C" int fth_b200_abi_version(void) { return 4; }
+extern "C" int fth_b200_abi_version(void) { return 5; }
 extern "C" const char* fth_b200_last_variant(void) { return g_last_variant; }
 extern "C" int64_t fth_b200_launch_count(void) { return g_launches; }
 extern "C" void fth_b200_reset_launch_count(void) { g_launches = 0; }

@@ -27,7 +27,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/fth_b200.h but not exported"
     assert set(B.EXPORTS) <= set(names)
-    assert lib.fth_b200_abi_version() == 4
+    assert lib.fth_b200_abi_version() == 5
 
 
 def test_struct_layouts_match_the_c_compiler():
