@@ -151,7 +151,7 @@ static __device__ __noinline__ void DecoderNodeFour(int prologue, int weight_dty
 // are latency-bound: every instruction between the producer's last store and this kernel's own counts), and with the
 // operators a decoder block puts around the projection fused in (DecoderFusion).
 template <bool INT8, bool P_MN, int BQ, bool DEC>
-__global__ void __launch_bounds__(ClusterCfg<BQ>::kThreads, 2)  // (3 per SM: 92 registers, decode step 533 vs 547 us at M = 1 but 1056 vs 1015 us at M = 16)
+__global__ void __launch_bounds__(ClusterCfg<BQ>::kThreads, 2)  // (3 per SM for the decoder form: 92 registers; decode step 510 vs 517 us at M = 1 but 892 vs 833 us at M = 16)
 LinearClusterKernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_p2,
                     const __grid_constant__ CUtensorMap map_q, TcParams p, Fp8Epilogue fe, Int8Epilogue ie) {
     using C = ClusterCfg<BQ>;
