@@ -809,12 +809,13 @@ def run_gpu_arm(args):
             plans[pc[0] & 1].run(a_host, out_host, ctx.stream)
             pc[0] += 1
             return
-        # N > 1: pinned-host activation in, sharded kernels with peer stores, the gathered row back to the host
-        a_stage.copy_(a_host, non_blocking=True)
+        # N > 1: pinned-host activation in, sharded kernels with peer stores, the gathered row back to the host (both rows
+        # are a few KB: copied by the SMs on the stream, fth_b200_small_copy)
+        B.small_copy(a_stage, a_host, K, ctx.stream)
         e2e_case.step()
         if e2e_case.gather is not None:
             e2e_case.gather.wait(ctx.stream)
-            full_host.copy_(e2e_case.gather.view(torch, e2e_case.gather.epoch & 1), non_blocking=True)
+            B.small_copy(full_host, e2e_case.gather.buffer(e2e_case.gather.rank, e2e_case.gather.epoch & 1), N, ctx.stream)
         else:
             full_host.copy_(e2e_case.nccl_gathered.view(1, -1)[:, :N], non_blocking=True)
         torch.cuda.current_stream().synchronize()

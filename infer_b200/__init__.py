@@ -30,6 +30,7 @@ EXPORTS = [
     "fth_b200_int8_conv2d_packed_weight_bytes", "fth_b200_int8_conv2d_pack_weights",
     "fth_b200_int8_relu_table", "fth_b200_int8_lookup",
     "fth_b200_quantize_linear", "fth_b200_dequantize_linear", "fth_b200_cast",
+    "fth_b200_quantize_linear_axis", "fth_b200_dequantize_linear_axis", "fth_b200_small_copy",
     "fth_b200_plan_create_fp8_linear", "fth_b200_plan_create_int8_linear", "fth_b200_plan_create_int8_conv2d",
     "fth_b200_plan_run", "fth_b200_plan_launch", "fth_b200_plan_input_bytes", "fth_b200_plan_output_bytes",
     "fth_b200_plan_destroy",
@@ -252,6 +253,12 @@ def dequantize_linear(x, scales, zps, params, out, to_dtype, rows, channels, str
                                                 C.c_int64(params), C.c_void_p(ptr(out)), C.c_int32(to_dtype),
                                                 C.c_int64(rows), C.c_int64(channels), C.c_int64(inner), stream or current_stream()),
           "fth_b200_dequantize_linear_axis")
+
+
+def small_copy(dst, src, nbytes, stream=None) -> None:
+    """A few KB between a page-locked host buffer and device memory, copied by the SMs on the stream."""
+    check(lib().fth_b200_small_copy(C.c_void_p(ptr(dst)), C.c_void_p(ptr(src)), C.c_int64(nbytes), stream or current_stream()),
+          "fth_b200_small_copy")
 
 
 def int8_lookup(x, out, count, lut, stream=None) -> None:

@@ -229,6 +229,23 @@ extern "C" int fth_b200_plan_create_int8_conv2d(const fth_b200_int8_conv2d_desc*
 }
 
 // `host_view`: when not null, the GPU's address of a host buffer that receives every output as well.
+// Public form of the staging copy: either side may be a page-locked host buffer (the GPU reaches it under the address
+// cudaPointerGetAttributes reports) or device memory.
+extern "C" int fth_b200_small_copy(void* dst, const void* src, int64_t bytes, fth_b200_stream_t stream) {
+    if (dst == nullptr || src == nullptr || bytes < 0) return FTH_B200_ERR_INVALID;
+    if (bytes == 0) return FTH_B200_OK;
+    auto view = [](const void* p) -> void* {
+        cudaPointerAttributes attr = {};
+        if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        if (attr.type == cudaMemoryTypeHost || attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) return attr.devicePointer;
+        return nullptr;  // pageable host memory
+    };
+    void* d = view(dst);
+    void* s = view(src);
+    if (d == nullptr || s == nullptr) return FTH_B200_ERR_UNSUPPORTED;
+    return LaunchStageIn(s, d, bytes, static_cast<cudaStream_t>(stream));
+}
+
 static int LaunchPlan(fth_b200_plan* p, const void* device_in, void* device_out, fth_b200_stream_t stream, void* host_view = nullptr) {
     if (!p || !device_in || !device_out) return FTH_B200_ERR_INVALID;
     switch (p->kind) {

@@ -1,5 +1,7 @@
 """Host-buffer plans (fth_b200_plan_*): the convenience layer bench.py's end-to-end figure goes through.  The result
 must be the bytes of the direct device call, for pageable and for pinned host buffers."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -74,3 +76,20 @@ def test_int8_plan_matches_device_call(cuda):
     plan.close()
     assert np.array_equal(pageable, want) and np.array_equal(pinned_out.numpy(), want)
     del ws
+
+
+@pytest.mark.parametrize("nbytes", [1, 17, 8192, 28672, 100003])
+def test_small_copy_between_pinned_host_and_device(cuda, nbytes):
+    torch = cuda
+    rng = np.random.default_rng(nbytes)
+    src = torch.from_numpy(rng.integers(0, 256, nbytes, dtype=np.uint8)).pin_memory()
+    mid = torch.zeros(nbytes + 32, dtype=torch.uint8, device="cuda")
+    back = torch.zeros(nbytes + 2, dtype=torch.uint8).pin_memory()
+    B.small_copy(mid[16:], src, nbytes)                       # host -> device (16-byte aligned destination)
+    B.small_copy(back.data_ptr() + 1, mid.data_ptr() + 16, nbytes)   # device -> host, unaligned destination
+    torch.cuda.synchronize()
+    assert torch.equal(back[1:nbytes + 1], src) and int(back[0]) == 0 and int(back[-1]) == 0
+    assert int(mid[:16].sum()) == 0 and int(mid[16 + nbytes:].sum()) == 0
+    pageable = np.zeros(nbytes, dtype=np.uint8)
+    assert B.lib().fth_b200_small_copy(ctypes.c_void_p(pageable.ctypes.data), ctypes.c_void_p(mid.data_ptr()), ctypes.c_int64(nbytes),
+                                       B.current_stream()) == B.ERR_UNSUPPORTED
