@@ -867,7 +867,12 @@ def run_gpu_arm(args):
 
     if rank == 0:
         achieved = value if world == 1 else value / world
-        cluster = per_step_launches == 1
+        # one launch: the cluster kernel (up to about two waves of CTAs: 8 per 128-column tile) or, with more tiles, the
+        # persistent kernel in its folded form (a CTA runs all K chunks of a tile and adds them from tensor memory)
+        tiles_local = (ctx.n_local + 127) // 128
+        step_kernel = ("tcgen05 GEMV + split-K reduce kernel" if per_step_launches != 1 else
+                       "single-launch tcgen05 cluster kernel" if tiles_local < 98 else
+                       "persistent tcgen05 weight-streaming kernel, one launch (the K chunks of a tile are added from tensor memory)")
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong",
@@ -879,7 +884,7 @@ def run_gpu_arm(args):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
                          "peak_source": peaks["source"],
-                         "note": "per GPU; step = " + ("single-launch tcgen05 cluster kernel" if cluster else "tcgen05 GEMV + split-K reduce kernel") +
+                         "note": "per GPU; step = " + (step_kernel) +
                                  (", gather signalling inside the kernel (one fth_b200_gather_wait per timed block)" if world > 1 else "") + "; median of the timed blocks"},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": K, "d2h_bytes_per_step": width if world == 1 else N,
                     "ms_per_step": round(e2e_ms, 5),

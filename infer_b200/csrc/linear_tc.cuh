@@ -25,7 +25,8 @@ struct TcParams {
     int64_t k_blocks;          // ceil(K / 128)
     int tiles_per_cta;         // cluster kernel: weight tiles per CTA (1 or 2)
     int second_tile_offset;    // the second tile: 0 = the same tile of the second weight (fusion.w2), else tile + this of the same weight
-    int64_t units;             // p_tiles * q_tiles * split
+    int64_t units;             // p_tiles * q_tiles * split (folded: p_tiles * q_tiles)
+    int fold;                  // persistent swapped kernel: one CTA runs all K chunks of a tile and adds them itself (no reduce pass)
     uint32_t idesc;
     int e4m3;                  // FP8 format of operands and output (1 = E4M3, 0 = E5M2)
     int fast;                  // 1: no bias, alpha = beta = 1, native output dtype → vectorised epilogue

@@ -19,7 +19,8 @@ struct Cfg {
     // accumulator buffers in tensor memory (512 columns per SM shared by the resident CTAs)
     static constexpr int kAccBuffers = BQ <= 32 ? 4 : 2;
     static constexpr uint32_t kTmemColsRaw = kAccBuffers * BQ;
-    static constexpr uint32_t kTmemCols = kTmemColsRaw < 32 ? 32 : kTmemColsRaw;
+    // BQ = 16 also has the folded form (all K chunks of a tile in one CTA, one accumulator per chunk): 8 x 16 columns
+    static constexpr uint32_t kTmemCols = BQ == 16 ? 128 : kTmemColsRaw;
     static constexpr int kEpilogueThreads = 128;
     static constexpr int kThreads = 64 + kEpilogueThreads;
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
@@ -64,9 +65,14 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     // unit → (p tile, q tile, K chunk).  [K,N] weights walk the column tiles fastest (chunk-major): the CTAs running
     // together then read whole contiguous weight rows of one K range, which keeps DRAM pages open; with [N,K]
     // weights the chunks of one tile are the contiguous direction, so the chunk index varies fastest instead.
+    // Folded form (p.fold): a unit is a whole tile; its CTA walks the chunks s = 0 .. split-1 in turn, each into an
+    // accumulator of its own, and the epilogue adds them in chunk order — the sums the reduce pass would form.
     auto decode_unit = [&](int64_t u, int64_t* pt, int64_t* qt, int* s) {
         int64_t t;
-        if (P_MN) {
+        if (p.fold) {
+            *s = 0;
+            t = u;
+        } else if (P_MN) {
             const int64_t tiles = p.p_tiles * p.q_tiles;
             *s = static_cast<int>(u / tiles);
             t = u % tiles;
@@ -82,6 +88,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         const int64_t left = p.k_blocks - begin;
         return left < p.chunk_blocks ? left : p.chunk_blocks;
     };
+    const int chunks_per_unit = p.fold ? p.split : 1;
 
     if (warp == 0) {
         // ================================ TMA producer ================================
@@ -92,8 +99,9 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             uint32_t phase = 0;
             bool failed = false;
             for (int64_t u = blockIdx.x; u < p.units && !failed; u += gridDim.x) {
-                int64_t pt, qt; int s;
-                decode_unit(u, &pt, &qt, &s);
+                int64_t pt, qt; int s0;
+                decode_unit(u, &pt, &qt, &s0);
+                for (int s = s0; s < s0 + chunks_per_unit && !failed; ++s) {
                 const int64_t nb = blocks_of(s);
                 for (int64_t kb = 0; kb < nb; ++kb) {
                     if (!MbarWait(&empty[stage], phase ^ 1u, p.status, 10, stage)) { failed = true; break; }
@@ -108,6 +116,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     TmaLoad2D(qs, &map_q, k0, q0, &full[stage]);
                     if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
                 }
+                }
             }
         }
     } else if (warp == 1) {
@@ -118,14 +127,16 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             bool failed = false;
             int64_t iter = 0;
             for (int64_t u = blockIdx.x; u < p.units && !failed; u += gridDim.x, ++iter) {
-                int64_t pt, qt; int s;
-                decode_unit(u, &pt, &qt, &s);
-                const int64_t nb = blocks_of(s);
-                const int acc = static_cast<int>(iter % kAcc);
-                const uint32_t acc_phase = static_cast<uint32_t>((iter / kAcc) & 1);
+                int64_t pt, qt; int s0;
+                decode_unit(u, &pt, &qt, &s0);
+                // folded: the chunks' accumulators together are the one buffer, handed over once per tile
+                const int acc = p.fold ? 0 : static_cast<int>(iter % kAcc);
+                const uint32_t acc_phase = static_cast<uint32_t>((p.fold ? iter : iter / kAcc) & 1);
                 if (!MbarWait(&tmem_empty[acc], acc_phase ^ 1u, p.status, 11, acc)) { failed = true; break; }
                 umma::FenceAfterThreadSync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BQ);
+                for (int s = s0; s < s0 + chunks_per_unit && !failed; ++s) {
+                const int64_t nb = blocks_of(s);
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((p.fold ? s : acc) * BQ);
                 for (int64_t kb = 0; kb < nb; ++kb) {
                     if (!MbarWait(&full[stage], phase, p.status, 12, stage)) { failed = true; break; }
                     umma::FenceAfterThreadSync();
@@ -139,6 +150,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     }
                     umma::Commit(&empty[stage]);  // the stage is free once these MMAs have read it
                     if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
                 }
                 if (!failed) umma::Commit(&tmem_full[acc]);
             }
@@ -157,12 +169,22 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         uint8_t* out8 = static_cast<uint8_t*>(INT8 ? ie.out : fe.out);
         bool failed = false;
         int64_t iter = 0;
+        // Column shard, folded form: this kernel stores into the other GPUs' buffers itself, so it also carries the step
+        // signalling — every rank must have published the previous step before the first such store, and the last block
+        // to finish publishes this one.  (The flags polled here are in this GPU's memory.)
+        const bool signalling = p.fold && p.args.signal.world > 0;
+        uint32_t gather_step = 0;
+        if (signalling) {
+            gather_step = GatherStep(p.args.signal);
+            if (et < p.args.signal.world) GatherWaitPrevious(p.args.signal, et, gather_step, p.status);
+            EpilogueBarrier<C::kEpilogueThreads>();
+        }
 
         for (int64_t u = blockIdx.x; u < p.units; u += gridDim.x, ++iter) {
             int64_t pt, qt; int s;
             decode_unit(u, &pt, &qt, &s);
-            const int acc = static_cast<int>(iter % kAcc);
-            const uint32_t acc_phase = static_cast<uint32_t>((iter / kAcc) & 1);
+            const int acc = p.fold ? 0 : static_cast<int>(iter % kAcc);
+            const uint32_t acc_phase = static_cast<uint32_t>((p.fold ? iter : iter / kAcc) & 1);
             const int64_t pg = pt * kBlockP + row;
             const bool row_ok = pg < p.p_total;
             const int64_t q_begin = qt * BQ;
@@ -222,10 +244,15 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     const uint32_t word = (lane & 2) ? (other2 | (pair << 16)) : (pair | (other2 << 16));
                     uint8_t* dst = out8 + (q_begin + c0 + j) * ldo + base_pg;
                     const bool group_ok = base_pg + 3 < p.p_total && (reinterpret_cast<uintptr_t>(dst) & 3) == 0;
+                    // (only the folded form has replicas on other GPUs to write: without it a copy follows the launch)
                     if (group_ok) {
-                        if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = word;
+                        if ((lane & 3) == 0) {
+                            if (p.fold) StoreWithPeers(p.args.peers, reinterpret_cast<uint32_t*>(dst), word);
+                            else *reinterpret_cast<uint32_t*>(dst) = word;
+                        }
                     } else if (row_ok) {
-                        dst[lane & 3] = static_cast<uint8_t>(b[j]);
+                        if (p.fold) StoreWithPeers(p.args.peers, dst + (lane & 3), static_cast<uint8_t>(b[j]));
+                        else dst[lane & 3] = static_cast<uint8_t>(b[j]);
                     }
                 }
             };
@@ -233,8 +260,42 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 13, acc)) failed = true;
             umma::FenceAfterThreadSync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BQ);
+            if constexpr (BQ == 16) {
+                if (p.fold && !failed) {
+                    // four activation rows at a time: the chunks' partial accumulators, all loads in flight before the
+                    // first add, then summed in chunk order (FP32: never a zero that could flip the sign of -0)
+#pragma unroll 1
+                    for (int c0 = 0; c0 < q_count; c0 += 4) {
+                        uint32_t t[8][4];
+#pragma unroll
+                        for (int ss = 0; ss < 8; ++ss)
+                            if (ss < p.split) umma::TmemLoad4(taddr + static_cast<uint32_t>(ss * BQ + c0), t[ss]);
+                        umma::TmemLoadWait();
+                        uint32_t v[16];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if constexpr (INT8) {
+                                int32_t sum = 0;
+#pragma unroll
+                                for (int ss = 0; ss < 8; ++ss) sum += ss < p.split ? static_cast<int32_t>(t[ss][j]) : 0;
+                                v[j] = static_cast<uint32_t>(sum);
+                            } else {
+                                float sum = 0.0f;  // as the reduce pass starts
+#pragma unroll
+                                for (int ss = 0; ss < 8; ++ss)
+                                    if (ss < p.split) sum += __uint_as_float(t[ss][j]);
+                                v[j] = __float_as_uint(sum);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 4; j < 16; ++j) v[j] = 0u;
+                        finish(v, c0, q_count - c0 < 4 ? q_count - c0 : 4);
+                    }
+                }
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BQ; c0 += 16) {
+                if (p.fold) break;
                 // uniform across the warp; after a wait has given up the accumulator is not valid: nothing is read or
                 // stored any more (the status word tells the host), the loop only keeps handing buffers back
                 if (c0 >= q_count || failed) break;
@@ -254,6 +315,10 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             __syncwarp();
             if (lane == 0) MbarArrive(&tmem_empty[acc]);
 
+        }
+        if (signalling) {
+            EpilogueBarrier<C::kEpilogueThreads>();  // every epilogue thread's stores are issued
+            if (et == 0) GatherArriveAndPublish(p.args.signal, gather_step, gridDim.x);
         }
     }
 
@@ -452,7 +517,7 @@ int LaunchSwapped(bool int8, const TcGeometry& g, bool weights_mn, const CUtenso
                   const Fp8Epilogue& fe, const Int8Epilogue& ie, cudaStream_t stream) {
     const int rc = int8 ? LaunchForLayout<true>(g, weights_mn, map_p, map_q, p, fe, ie, stream)
                         : LaunchForLayout<false>(g, weights_mn, map_p, map_q, p, fe, ie, stream);
-    if (rc != FTH_B200_OK || g.split == 1) return rc;
+    if (rc != FTH_B200_OK || g.split == 1 || p.fold) return rc;
     const int64_t threads = (g.p_pad / 4) * g.q_total;
     const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
     cudaLaunchConfig_t cfg = {};

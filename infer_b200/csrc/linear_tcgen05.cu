@@ -83,6 +83,22 @@ TcGeometry GeometryFor(const LinearArgs& a) {
 }
 
 
+// M <= 16 on the persistent kernel: whether every CTA runs whole tiles (all K chunks, one accumulator in tensor memory
+// each) and adds the chunks itself, in the reduce pass's order — one launch, no partial sums in memory, the same bits.
+// A CTA then streams 128 weight columns alone, at ~45 GB/s: that needs about a hundred CTAs at work to keep HBM busy, in
+// the last round of tiles too.  Measured, FP8, one GPU, M = 1 (M = 16), folded against GEMV + reduce pass, us:
+//   K = 8192:  64 tiles 22.8 / 17.3;  96: 23.7 / 22.8;  112: 24.0 / 25.9;  224: 40.0 / 43.1 (41.8 / 47.4);
+//              296: 51.2 / 55.9 (53.5 / 61.3);  300: 64.9 / 58.0;  330: 66.7 / 61.5;  400: 71.9 / 75.3;  600: 108.7 / 108.5
+//   K = 4096:  1187 tiles, M = 16: 108.4 / 130.5
+bool FoldsSplit(const TcGeometry& g, int64_t m) {
+    if (!g.swap || g.cluster != 0 || g.split <= 1 || g.bq != 16) return false;
+    const int64_t tiles = g.p_tiles * g.q_tiles, slots = static_cast<int64_t>(SmCount()) * 2, busy = slots / 3;
+    if (tiles < busy) return false;
+    const int64_t last_round = tiles % slots;
+    if (tiles <= slots || last_round == 0 || last_round >= busy) return true;
+    return tiles >= 4 * slots && m > 4;  // many rounds, and partial sums that would weigh as much as the weights' tail
+}
+
 // Encoding a tensor map costs a few microseconds of host time; decode steps call the same (pointer, shape)
 // pairs over and over, so the last few encodings are kept per host thread.
 bool CachedMap(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols, uint32_t box_rows) {
@@ -252,6 +268,8 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
     p.out_inv = int8 ? 0.0f : ExactReciprocal(fe.out_scale);
     p.scratch = scratch;
     p.status = DeviceStatusPtr();
+    p.fold = p.fast && a.argmax_keys == nullptr && FoldsSplit(g, a.m);
+    if (p.fold) p.units = g.p_tiles * g.q_tiles;
     // operand formats: kind::f8f6f4 0 = E4M3, 1 = E5M2; kind::i8 1 = signed 8-bit.  D: 1 = F32, 2 = S32.
     const uint32_t fmt = int8 ? 1u : (dtype == FTH_B200_FP8E5M2 ? 1u : 0u);
     const bool p_mn = g.swap && weights_mn;

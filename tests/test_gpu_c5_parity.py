@@ -184,6 +184,50 @@ def test_swapped_kernel_many_units_per_cta(cuda, kind, m, k, n, trans_b):
     assert B.device_status() == 0
 
 
+# ---- folded split-K: whole tiles per CTA, the chunks added from tensor memory ----------------------------------------
+# With about a hundred tiles or more (and M <= 16) the persistent kernel runs as ONE launch: every CTA takes all K chunks of
+# a tile into accumulators of their own and adds them in chunk order itself.  A narrower weight still takes the weight-
+# streaming pass plus the pass that adds the partial sums from memory; both must give the same bytes for the same columns.
+FOLDED = [(1, 1024, 128 * 224, False), (5, 2048, 128 * 130 + 48, False), (16, 1024, 128 * 224, False), (3, 1024, 128 * 200, True)]
+
+
+def _count_launches(run):
+    B.lib().fth_b200_reset_launch_count()
+    out = run()
+    return out, B.lib().fth_b200_launch_count()
+
+
+@pytest.mark.parametrize("m,k,n,trans_b", FOLDED)
+@pytest.mark.parametrize("kind", ["fp8_e4m3", "int8"])
+def test_folded_split_gives_the_reduce_pass_bytes(cuda, kind, m, k, n, trans_b):
+    rng = np.random.default_rng(m * 11 + k + n)
+    narrow = 128 * 64  # this many columns alone: too few tiles to fold
+    op = O.OP_GEMM if trans_b else O.OP_MATMUL
+    if kind == "int8":
+        w, ws = util.make_int8_weight(k, n, seed=k + n)
+        a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+        so = util.int8_out_scale(k, ws)
+        layout = (lambda x: np.ascontiguousarray(x.T)) if trans_b else np.ascontiguousarray
+        got, launches = _count_launches(lambda: _run_int8(cuda, a, dev(cuda, layout(w)), dev(cuda, ws), so, m, k, n, trans_b))
+        part, launches_part = _count_launches(
+            lambda: _run_int8(cuda, a, dev(cuda, layout(w[:, :narrow])), dev(cuda, ws[:narrow]), so, m, k, narrow, trans_b))
+        want = O.int8_linear(op, a, 0.02, 0, layout(w), ws, None, so, 0, trans_b=trans_b)
+        assert int((got != want).sum()) == 0
+    else:
+        w, sw = util.make_fp8_weight(O.E4M3, k, n, seed=k + n)
+        a, sa = util.make_fp8_activation(O.E4M3, m, k, seed=m + k)
+        so = util.fp8_out_scale(O.E4M3, k)
+        layout = (lambda x: np.ascontiguousarray(x.T)) if trans_b else np.ascontiguousarray
+        got, launches = _count_launches(lambda: _run_fp8(cuda, a, sa, dev(cuda, layout(w)), sw, so, m, k, n, trans_b))
+        part, launches_part = _count_launches(lambda: _run_fp8(cuda, a, sa, dev(cuda, layout(w[:, :narrow])), sw, so, m, k, narrow, trans_b))
+        want = O.fp8_linear(op, O.E4M3, a, sa, layout(w), sw, so, trans_b=trans_b)
+        _fp8_check(f"folded split {kind} {m}x{k}x{n} trans_b={trans_b}", got, want, a, sa, layout(w), sw, so, O.E4M3, trans_b)
+    assert launches == 1, "expected the folded form: one launch"
+    assert launches_part == 2, "expected the weight-streaming pass plus the reduce pass"
+    assert np.array_equal(got[:, :narrow], part), "the folded form and the reduce pass disagree"
+    assert B.device_status() == 0
+
+
 # ---- two weight tiles per CTA in the single-launch kernel ------------------------------------------------------------
 # A weight with more tiles than one wave of clusters holds, but at most twice as many, runs as one launch in which every
 # CTA takes tile t and tile t + half (the N/4 shard of the headline shape is such a weight).  An odd tile count leaves

@@ -19,9 +19,9 @@ def cuda():
     return torch
 
 
-# (m, k, n, variant): cluster kernel, two-kernel split path, CTA-pair dense kernel (ragged tile; four tiles per CTA pair, so
+# (m, k, n, variant): cluster kernel, two-kernel split path, folded split (one launch; ragged last tile), CTA-pair dense kernel (ragged tile; four tiles per CTA pair, so
 # the shared-memory tile behind its tile stores is reused), CUDA-core kernels
-CASES = [(1, 1024, 2048, B.VARIANT_AUTO), (16, 8192, 8192, B.VARIANT_AUTO), (48, 2048, 4096, B.VARIANT_AUTO),
+CASES = [(1, 1024, 2048, B.VARIANT_AUTO), (16, 8192, 8192, B.VARIANT_AUTO), (5, 1024, 128 * 119 + 48, B.VARIANT_AUTO), (48, 2048, 4096, B.VARIANT_AUTO),
          (300, 512, 640, B.VARIANT_AUTO), (512, 256, 256 * 74 * 2, B.VARIANT_AUTO), (4, 256, 384, B.VARIANT_SKINNY),
          (3, 96, 80, B.VARIANT_SIMT)]
 
@@ -121,7 +121,8 @@ def test_gather_sync_gives_up_when_a_peer_never_signals(cuda):
 # ---- gather signalling folded into the linear kernels ----------------------------------------------------------------
 # Two "ranks" on one GPU take turns on one stream (kernels of different ranks never have to run at the same time: every
 # wait finds its condition already true, except in the test that lets one run out on purpose).
-FOLD_CASES = [(1, 1024, 2048, B.VARIANT_AUTO, "cluster kernel"), (16, 8192, 32768, B.VARIANT_AUTO, "split-K reduce pass"),
+FOLD_CASES = [(1, 1024, 2048, B.VARIANT_AUTO, "cluster kernel"), (16, 8192, 32768, B.VARIANT_AUTO, "folded split-K, one launch"),
+              (16, 8192, 16384, B.VARIANT_AUTO, "split-K reduce pass"),
               (4, 8192, 14336, B.VARIANT_AUTO, "cluster kernel, two tiles per CTA"),
               (300, 512, 640, B.VARIANT_AUTO, "CTA-pair dense kernel"), (4, 256, 384, B.VARIANT_SKINNY, "small kernels around a CUDA-core kernel")]
 
