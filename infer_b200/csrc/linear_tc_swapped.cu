@@ -19,7 +19,7 @@ struct Cfg {
     // accumulator buffers in tensor memory (512 columns per SM shared by the resident CTAs)
     static constexpr int kAccBuffers = BQ <= 32 ? 4 : 2;
     static constexpr uint32_t kTmemColsRaw = kAccBuffers * BQ;
-    // BQ = 16 also has the folded form (all K chunks of a tile in one CTA, one accumulator per chunk): 8 x 16 columns
+    // BQ <= 32 also has the folded form (all K chunks of a tile in one CTA, one accumulator per chunk): 8 x 16 or 4 x 32 columns
     static constexpr uint32_t kTmemCols = BQ == 16 ? 128 : kTmemColsRaw;
     static constexpr int kEpilogueThreads = 128;
     static constexpr int kThreads = 64 + kEpilogueThreads;
@@ -260,7 +260,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             if (!failed && !MbarWait(&tmem_full[acc], acc_phase, p.status, 13, acc)) failed = true;
             umma::FenceAfterThreadSync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + static_cast<uint32_t>(acc * BQ);
-            if constexpr (BQ == 16) {
+            if constexpr (BQ <= 32) {
                 if (p.fold && !failed) {
                     // four activation rows at a time: the chunks' partial accumulators, all loads in flight before the
                     // first add, then summed in chunk order (FP32: never a zero that could flip the sign of -0)
