@@ -7,7 +7,7 @@
 //           Decode-sized linear plans with page-locked host buffers skip the two copy-engine transfers (4.5 us and
 //           6.6 us of a 74 us step, measured): a small kernel reads the activation from the host buffer, overlapped
 //           with the next kernel's set-up, and the linear kernels store each output to the host buffer as they do to a
-//           replica on another GPU.
+//           replica on another GPU; the two launches are replayed from a graph (one driver call per step).
 // launch  = the same launch on device-resident buffers, no copies and no wait.
 #include <cstdlib>
 #include <cstring>
@@ -86,6 +86,19 @@ struct fth_b200_plan {
     fth_b200_int8_conv2d_desc conv{};
     DeviceBuffer in, out, w, bias, scales, zps, lut, workspace;
     int64_t in_bytes{0}, out_bytes{0};
+    // fth_b200_plan_run on page-locked host buffers replays its two launches (activation in, linear kernel) from a
+    // graph: one driver call per step instead of two launches with their descriptor work (8.5 us of host time per
+    // linear launch through this ABI, measured, all of it in front of the GPU's first instruction).  Captured on a
+    // stream of the plan's own for the pair of host buffers of the last call; another pair is captured again.
+    cudaGraphExec_t step_exec{nullptr};
+    cudaStream_t capture_stream{nullptr};
+    const void* step_in{nullptr};
+    void* step_out{nullptr};
+    bool step_graph_failed{false};
+    ~fth_b200_plan() {
+        if (step_exec) cudaGraphExecDestroy(step_exec);
+        if (capture_stream) cudaStreamDestroy(capture_stream);
+    }
 };
 
 #define FTH_TRY(expr) do { const int rc_ = (expr); if (rc_ != FTH_B200_OK) { delete p; return rc_; } } while (0)
@@ -272,6 +285,31 @@ static int LaunchPlan(fth_b200_plan* p, const void* device_in, void* device_out,
     return FTH_B200_ERR_INVALID;
 }
 
+// Records [activation in, linear kernel with the host buffer as a replica of the output] for this pair of host buffers.
+// On any failure the plan keeps launching the two kernels one by one (step_graph_failed).
+static void CaptureStep(fth_b200_plan* p, void* in_view, void* out_view) {
+    if (p->step_exec) { cudaGraphExecDestroy(p->step_exec); p->step_exec = nullptr; }
+    p->step_graph_failed = true;
+    if (p->capture_stream == nullptr && cudaStreamCreateWithFlags(&p->capture_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    if (cudaStreamBeginCapture(p->capture_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); return; }
+    const bool recorded = LaunchStageIn(in_view, p->in.ptr, p->in_bytes, p->capture_stream) == FTH_B200_OK &&
+                          LaunchPlan(p, p->in.ptr, p->out.ptr, p->capture_stream, out_view) == FTH_B200_OK;
+    cudaGraph_t graph = nullptr;
+    const bool ended = cudaStreamEndCapture(p->capture_stream, &graph) == cudaSuccess && graph != nullptr;
+    if (recorded && ended && cudaGraphInstantiate(&p->step_exec, graph, 0) == cudaSuccess) {
+        p->step_in = in_view;
+        p->step_out = out_view;
+        p->step_graph_failed = false;
+    } else {
+        cudaGetLastError();
+        p->step_exec = nullptr;
+    }
+    if (graph) cudaGraphDestroy(graph);
+}
+
 extern "C" int fth_b200_plan_launch(fth_b200_plan* p, const void* device_in, void* device_out, fth_b200_stream_t stream) {
     return LaunchPlan(p, device_in, device_out, stream);
 }
@@ -285,6 +323,13 @@ extern "C" int fth_b200_plan_run(fth_b200_plan* p, const void* host_in, void* ho
     // asked on every call: an address that was page-locked last time may belong to a pageable buffer now
     void* in_view = direct ? DeviceViewOfHost(host_in) : nullptr;
     void* out_view = direct ? DeviceViewOfHost(host_out) : nullptr;
+    if (in_view != nullptr && out_view != nullptr && !p->step_graph_failed) {
+        if (p->step_exec == nullptr || p->step_in != in_view || p->step_out != out_view) CaptureStep(p, in_view, out_view);
+        if (p->step_exec != nullptr) {
+            if (cudaGraphLaunch(p->step_exec, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
+            return cudaStreamSynchronize(stream) == cudaSuccess ? FTH_B200_OK : FTH_B200_ERR_CUDA;
+        }
+    }
     if (in_view != nullptr) {
         if (LaunchStageIn(in_view, p->in.ptr, p->in_bytes, stream) != FTH_B200_OK) return FTH_B200_ERR_CUDA;
     } else if (cudaMemcpyAsync(p->in.ptr, host_in, static_cast<size_t>(p->in_bytes), cudaMemcpyHostToDevice, stream) != cudaSuccess) {
