@@ -270,7 +270,7 @@ class LinearCase:
     because a sharded decode step is less GPU time than the host needs to issue it.  Without peer mapping the
     gather is one NCCL all-gather of the 1-byte outputs."""
 
-    def __init__(self, ctx, kind, m, weights=None, seed=SEED, rotate_bytes=2 * L2_BYTES, use_graph=None):
+    def __init__(self, ctx, kind, m, weights=None, seed=SEED, rotate_bytes=2 * L2_BYTES, use_graph=None, graph_steps=None):
         torch, B = ctx.torch, ctx.B
         self.ctx, self.kind, self.m = ctx, kind, m
         self.int8 = kind == "int8"
@@ -306,13 +306,14 @@ class LinearCase:
         self.counter = 0
         self.gather = None
         self.graph = None
+        self.graph_is_block = False
         self.rotation = 0
         self.stream = ctx.stream
         self.nccl_gathered = None
         if ctx.world > 1:
             self._setup_gather()
             if self.gather is not None and (use_graph if use_graph is not None else True):
-                self._capture()
+                self._capture(graph_steps)
 
     # ---- descriptors ----
     def _desc(self, w, sw, a, out, ldo=0):
@@ -386,9 +387,14 @@ class LinearCase:
         return self.local_out
 
     # ---- CUDA graph of one rotation (every weight set, both buffer parities) ----
-    def _capture(self):
+    def _capture(self, graph_steps=None):
         ctx, torch, gather = self.ctx, self.ctx.torch, self.gather
         rotation = self.n_sets * (2 if self.n_sets % 2 else 1)  # an even number of steps: the buffer parity repeats
+        # A timed block of a known, even length that visits every weight set is recorded whole, its closing wait for the
+        # other ranks included: the block is then one graph launch, with no step issued from the host behind it.
+        self.graph_is_block = bool(graph_steps) and graph_steps % 2 == 0 and graph_steps >= self.n_sets
+        if self.graph_is_block:
+            rotation = graph_steps
         for _ in range(rotation):
             self.step()
         torch.cuda.synchronize()
@@ -403,6 +409,8 @@ class LinearCase:
                     self.stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
                     for _ in range(rotation):
                         self.step()
+                    if self.graph_is_block:
+                        gather.wait(self.stream)
         except Exception as exc:  # capture is an optimisation of the issue rate, never a requirement
             captured = False
             print(f"[bench] rank {ctx.rank}: CUDA-graph capture failed ({type(exc).__name__}: {exc}); issuing steps one by one", file=sys.stderr)
@@ -418,7 +426,16 @@ class LinearCase:
         """Issues exactly `steps` steps on the stream (graph replays of whole rotations, the rest one by one).  With the
         signalling folded into the kernels a step's wait for the other ranks rides in the next step's kernel; the wait
         of the last step is issued here, so that the timed block ends with every rank's columns in place."""
-        self._run_steps(steps)
+        if self.graph is not None and self.graph_is_block:
+            if steps == self.rotation and (self.gather.epoch & 1) == self.graph_parity:
+                self.graph.replay()
+                self.gather.epoch += self.rotation
+                self.counter += self.rotation
+                return
+            for _ in range(steps):
+                self.step()
+        else:
+            self._run_steps(steps)
         if self.gather is not None:
             self.gather.wait(self.stream)
 
@@ -544,9 +561,9 @@ def sweep(ctx, peaks, quick):
             if quick and m in (16, 256):
                 continue
             key = kind
-            case = LinearCase(ctx, kind, m, weights=shared.get(key))
-            shared[key] = case.weights
             steps = 200 if m <= 256 else 20
+            case = LinearCase(ctx, kind, m, weights=shared.get(key), graph_steps=steps)
+            shared[key] = case.weights
             if m > 256:
                 torch.cuda.synchronize()
                 time.sleep(1.0)
@@ -768,7 +785,7 @@ def run_gpu_arm(args):
         if gather_mismatch != 0:
             failures.append(f"gathered result differs from the single-GPU result in {gather_mismatch} bytes")
 
-    main = LinearCase(ctx, "fp8_e4m3", 1)
+    main = LinearCase(ctx, "fp8_e4m3", 1, graph_steps=args.steps)
     sampler = ClockSampler(local_rank)
     sampler.start()
 
