@@ -123,7 +123,10 @@ class Fp8LinearKernel final : public B200Kernel {
 
     int32_t Prepare() override {
         fth_b200_fp8_linear_desc d;
-        if (!Describe(&d)) return -1;
+        const std::vector<float>* channel_scales = nullptr;
+        if (!Describe(&d, nullptr, &channel_scales)) return -1;
+        // per-channel weight scales go to the device once, here
+        if (channel_scales != nullptr && scales_.Upload(channel_scales->data(), channel_scales->size() * sizeof(float)) != 0) return -1;
         d.a = d.w = d.out = kProbe;
         if (d.bias_mode != FTH_B200_BIAS_NONE) d.bias = kProbe;
         weights_resident_ = false;
@@ -138,13 +141,21 @@ class Fp8LinearKernel final : public B200Kernel {
         fth_b200_fp8_linear_desc d;
         LinearView v;
         if (!Describe(&d, &v)) return -1;
-        if (!cuda_detail::IsTensorReady<dtype>(v.a) || !cuda_detail::IsTensorReady<dtype>(v.w) ||
-            !cuda_detail::IsOutputReady<dtype>(v.out)) return -1;
+        // (IsTensorReady insists on a per-tensor scale, src/kernel/cuda/kernel_io.cuh:245-252: a weight with per-channel
+        // scales, which Describe() has validated, is checked for its bytes only)
+        const bool w_ready = d.w_channel_scales != nullptr
+                                 ? v.w->IsInitialized() && v.w->data_type() == dtype && v.w->memory_size() >= static_cast<size_t>(d.k * d.n)
+                                 : cuda_detail::IsTensorReady<dtype>(v.w);
+        if (!cuda_detail::IsTensorReady<dtype>(v.a) || !w_ready || !cuda_detail::IsOutputReady<dtype>(v.out)) return -1;
         cuda_detail::DeviceBuffer<T> a, w, bias, out;
         if (cuda_detail::CopyTensorToDevice(v.a, &a) != 0 || cuda_detail::CopyTensorToDevice(v.w, &w) != 0 ||
             (v.bias && cuda_detail::CopyTensorToDevice(v.bias, &bias) != 0) ||
             cuda_detail::AllocateTensorOnDevice(v.out, &out) != 0) return -1;
         d.a = a.get(); d.w = w.get(); d.bias = v.bias ? bias.get() : nullptr; d.out = out.get();
+        if (d.w_channel_scales != nullptr) {
+            if (scales_.get() == nullptr) return -1;
+            d.w_channel_scales = static_cast<const float*>(scales_.get());
+        }
         d.workspace = workspace_.get(); d.workspace_bytes = workspace_.bytes();
         // An immutable weight is uploaded by the first call; from the second call on nothing on the stream writes it.
         d.weights_static = weights_resident_ ? 1 : 0;
@@ -170,21 +181,37 @@ class Fp8LinearKernel final : public B200Kernel {
         return need <= fth_b200_noalloc_scratch_bytes() ? Scratch::kBuiltIn : Scratch::kNone;
     }
 
-    bool Describe(fth_b200_fp8_linear_desc* d, LinearView* view = nullptr) const {
+    bool Describe(fth_b200_fp8_linear_desc* d, LinearView* view = nullptr, const std::vector<float>** channel_scales = nullptr) const {
         LinearView v;
         if (!View(ParamAs<Param>(), &v)) return false;
         int64_t m = 0, k = 0, n = 0;
         if (!LinearShape(v, &m, &k, &n)) return false;
-        // FP8 tensors carry one scale per tensor (include/util/types.h:96-101)
-        if (!HasCompatiblePerTensorQuantization(v.a->quantization()) || !HasCompatiblePerTensorQuantization(v.w->quantization()) ||
-            !HasCompatiblePerTensorQuantization(v.out->quantization())) return false;
+        // FP8 activations, bias and outputs carry one scale per tensor (include/util/types.h:96-101).  The weight may carry
+        // one scale per output channel instead.  The reference's FP8 linear kernels read the scalar field only
+        // (include/core/tensor.h:105; a non-scalar scheme "needs a kernel that explicitly implements their indexing
+        // semantics", types.h:96-98), while its tensor metadata and the .fth files hold the vector already
+        // (src/model/model_io.cc:228-246).  Here output channel n takes w_scale = scales[n].
+        if (!HasCompatiblePerTensorQuantization(v.a->quantization()) || !HasCompatiblePerTensorQuantization(v.out->quantization())) return false;
+        const QuantizationParams& wq = v.w->quantization();
+        const bool per_channel = wq.enabled && wq.granularity == QuantizationGranularity::kPerChannel;
+        if (per_channel) {
+            const int64_t rank = static_cast<int64_t>(v.w->dims().size());
+            const int64_t axis = wq.axis < 0 ? wq.axis + rank : wq.axis;
+            if (rank != 2 || axis != (v.trans_b ? 0 : 1) || wq.block_size != 0 || wq.scales.size() != static_cast<size_t>(n)) return false;
+            for (int32_t z : wq.zero_points) if (z != 0) return false;
+            for (float sc : wq.scales) if (!(sc > 0.0f) || !std::isfinite(sc)) return false;
+        } else if (!HasCompatiblePerTensorQuantization(wq)) {
+            return false;
+        }
+        if (channel_scales) *channel_scales = per_channel ? &wq.scales : nullptr;
         const int bias_mode = BiasMode(v.bias, m, n);
         if (bias_mode < 0 || (v.bias && v.bias->data_type() != dtype)) return false;
         *d = fth_b200_fp8_linear_desc{};
         d->dtype = static_cast<int32_t>(dtype);
         d->op = v.op; d->m = m; d->k = k; d->n = n; d->trans_b = v.trans_b ? 1 : 0;
         d->bias_mode = bias_mode;
-        d->a_scale = v.a->quantization_scale(); d->w_scale = v.w->quantization_scale();
+        d->a_scale = v.a->quantization_scale(); d->w_scale = per_channel ? 1.0f : v.w->quantization_scale();
+        if (per_channel) d->w_channel_scales = static_cast<const float*>(kProbe);  // compute() points it at the uploaded copy
         d->bias_scale = v.bias ? v.bias->quantization_scale() : 1.0f;
         d->out_scale = v.out->quantization_scale();
         d->alpha = v.alpha; d->beta = v.beta;
@@ -192,7 +219,7 @@ class Fp8LinearKernel final : public B200Kernel {
         return true;
     }
 
-    DeviceScratch workspace_;
+    DeviceScratch workspace_, scales_;
     bool weights_resident_{false};
     size_t workspace_limit_;
     Scratch scratch_{Scratch::kOwned};

@@ -187,6 +187,29 @@ def fp8_linear(op, dtype, a, a_scale, w, w_scale, out_scale, *, bias=None, bias_
     return kern if return_kernel else kern.run()
 
 
+def fp8_linear_per_channel(op, dtype, a, a_scale, w, w_scales, out_scale, *, bias=None, bias_scale=1.0, trans_b=False,
+                           alpha=1.0, beta=1.0, impl="port", device=COMMON):
+    """FP8 linear whose weight carries one scale per output channel — a quantisation the reference's FP8 linear
+    kernels cannot express (they read the tensor's scalar scale only, include/core/tensor.h:105; per-tensor rule in
+    include/util/types.h:96-101), although its tensor metadata and the .fth files can hold the vector
+    (src/model/model_io.cc:228-246).  Defined column by column: output
+    channel n is what the reference's kernel gives for that column alone with w_scale = w_scales[n].  Channels that
+    share a scale are computed in one call."""
+    a = _arr(a, np.uint8)
+    w = _arr(w, np.uint8)
+    w_scales = _arr(w_scales, np.float32).reshape(-1)
+    n = w.shape[0] if trans_b else w.shape[1]
+    assert w_scales.size == n
+    out = np.empty((a.shape[0], n), np.uint8)
+    for scale in np.unique(w_scales):
+        cols = np.nonzero(w_scales == scale)[0]
+        w_part = np.ascontiguousarray(w[cols] if trans_b else w[:, cols])
+        b_part = None if bias is None else np.ascontiguousarray(bias[cols] if bias.ndim == 1 else bias[:, cols])
+        out[:, cols] = fp8_linear(op, dtype, a, a_scale, w_part, float(scale), out_scale, bias=b_part, bias_scale=bias_scale,
+                                  trans_b=trans_b, alpha=alpha, beta=beta, impl=impl, device=device)
+    return out
+
+
 # ------------------------------------------------------------------------------------------------
 # INT8 linear
 # ------------------------------------------------------------------------------------------------

@@ -142,6 +142,9 @@ static Int8Case MakeInt8(int64_t m, int64_t k, int64_t n) {
 // ---------------------------------------------------------------------------------------------------------
 // select: host only
 // ---------------------------------------------------------------------------------------------------------
+template <typename Param>
+static int RunCommon(DataType dtype, const char* op, Param* param);
+
 static void RunSelect() {
     // Before registration the reference cannot build a statically quantised INT8 plan for CUDA under
     // kRequireRequested: DequantizeLinear has no CUDA candidate and INT8 requests never fall back to COMMON.
@@ -176,6 +179,29 @@ static void RunSelect() {
         Int8Case c = MakeInt8(128, 1024, 1024);
         auto k = Select(DeviceType::CUDA, DataType::INT8, "MatMul", &c.param);
         CHECK_THAT(k && IsB200Kernel(k.get()), "INT8 MatMul [128,1024]x[1024,1024] per-channel selects the b200 candidate");
+    }
+    // An FP8 weight with one scale per output channel: the reference's linear kernels read the tensor's scalar scale only
+    // (include/core/tensor.h:105) — the vector is ignored, every column gets scales[0]; the new candidate applies the
+    // vector, on the output-channel axis only.
+    {
+        Fp8Case c = MakeFp8(DataType::FP8E4M3, 2, 512, 384);
+        std::vector<float> scales(384);
+        for (size_t i = 0; i < scales.size(); ++i) scales[i] = (i & 1) ? 0.0625f : 0.03125f;
+        c.w->set_quantization(PerChannel(1, scales));
+        {
+            const bool ran = RunCommon(DataType::FP8E4M3, "MatMul", &c.param) == 0;
+            std::vector<uint8_t> with_vector(static_cast<const uint8_t*>(c.out->raw_data()), static_cast<const uint8_t*>(c.out->raw_data()) + 2 * 384);
+            c.w->set_quantization({true, scales.front()});
+            const bool ran_scalar = RunCommon(DataType::FP8E4M3, "MatMul", &c.param) == 0;
+            const bool same = std::memcmp(with_vector.data(), c.out->raw_data(), with_vector.size()) == 0;
+            CHECK_THAT(ran && ran_scalar && same, "FP8 MatMul with per-channel weight scales: the reference's COMMON kernel ignores the vector (same bytes as scale = scales[0])");
+            c.w->set_quantization(PerChannel(1, scales));
+        }
+        auto k = Select(DeviceType::CUDA, DataType::FP8E4M3, "MatMul", &c.param);
+        CHECK_THAT(k && IsB200Kernel(k.get()), "FP8 MatMul with per-channel weight scales selects the b200 candidate");
+        c.w->set_quantization(PerChannel(0, std::vector<float>(512, 0.03125f)));
+        auto wrong_axis = Select(DeviceType::CUDA, DataType::FP8E4M3, "MatMul", &c.param);
+        CHECK_THAT(!(wrong_axis && IsB200Kernel(wrong_axis.get())), "FP8 MatMul with scales along K: the b200 candidate declines");
     }
     // a request the new backend declines moves on to the reference's CUDA candidate, never to a CPU kernel
     {
@@ -272,6 +298,41 @@ static void RunGpu() {
         std::printf("      [%s] max code distance vs COMMON: %d\n", fth_b200_last_variant(), max_dist);
         CHECK_THAT(ok && max_dist >= 0 && max_dist <= 1, dt == DataType::FP8E4M3 ? "CUDA FP8E4M3 MatMul through the reference runtime matches COMMON within one code"
                                                                                : "CUDA FP8E5M2 MatMul through the reference runtime matches COMMON within one code");
+    }
+
+    // ---- FP8 MatMul whose weight carries one scale per output channel: column n is what COMMON gives with w_scale = scales[n] ----
+    for (DataType dt : {DataType::FP8E4M3, DataType::FP8E5M2}) {
+        const int64_t m = 3, kk = 1024, n = 2048;
+        Fp8Case c = MakeFp8(dt, m, kk, n);
+        std::vector<float> scales(static_cast<size_t>(n));
+        for (size_t i = 0; i < scales.size(); ++i) scales[i] = (i & 1) ? 0.0625f : 0.03125f;
+        c.w->set_quantization(PerChannel(1, scales));
+        auto k = Select(DeviceType::CUDA, dt, "MatMul", &c.param);
+        bool ok = k && IsB200Kernel(k.get()) && k->Prepare() == 0;
+        if (ok) {
+            cuda::DeferredHostSyncScope deferred;
+            ok = k->compute() == 0 && cuda::SyncTensorToHostIfNeeded(c.out.get(), c.out->memory_size(), c.out->raw_data()) == 0;
+        }
+        const uint8_t* got = static_cast<const uint8_t*>(c.out->raw_data());
+        int max_dist = ok ? 0 : -1, differ = 0;
+        std::vector<uint8_t> first;
+        for (int pass = 0; pass < 2 && ok; ++pass) {  // COMMON with the even columns' scale, then with the odd columns'
+            c.w->set_quantization({true, pass == 0 ? 0.03125f : 0.0625f});
+            auto ref_out = MakeTensor(dt, {m, n}); ref_out->set_quantization({true, 0.25f});
+            operators::MatMulParam rp; rp.a = c.a; rp.b = c.w; rp.out = ref_out;
+            ok = RunCommon(dt, "MatMul", &rp) == 0;
+            const uint8_t* want = static_cast<const uint8_t*>(ref_out->raw_data());
+            if (pass == 0) first.assign(want, want + m * n);
+            for (int64_t i = 0; i < m * n && ok; ++i) {
+                if ((i % n) % 2 != pass) continue;
+                max_dist = std::max(max_dist, std::abs(CodeIndex(got[i]) - CodeIndex(want[i])));
+            }
+            if (pass == 1) for (int64_t i = 0; i < m * n; ++i) differ += first[static_cast<size_t>(i)] != want[i];
+        }
+        std::printf("      [%s] per-channel weight scales: max code distance vs COMMON column by column: %d (the two scales' results differ in %d bytes)\n",
+                    fth_b200_last_variant(), max_dist, differ);
+        CHECK_THAT(ok && max_dist >= 0 && max_dist <= 1 && differ > 0, dt == DataType::FP8E4M3 ? "CUDA FP8E4M3 MatMul with per-channel weight scales matches COMMON column by column"
+                                                                                             : "CUDA FP8E5M2 MatMul with per-channel weight scales matches COMMON column by column");
     }
 
     // ---- INT8 MatMul (config 2 shape), per-channel weight scales: bit-exact ----

@@ -195,3 +195,38 @@ def test_tensor_core_path_shapes(cuda, dtype, m, k, n, trans_b):
     got = run_fp8_linear(cuda, dtype, op, case, trans_b=trans_b, variant=B.VARIANT_TCGEN05)
     assert B.last_variant() == "tcgen05" and B.device_status() == 0
     check_codes(got, want, dtype, f"tcgen05 {m}x{k}x{n}", case=case, trans_b=trans_b)
+
+
+# ---- one weight scale per output channel --------------------------------------------------------------------------------
+# The reference's FP8 kernels take per-tensor scales only; its tensor metadata and model files can hold a per-channel
+# vector.  The extension is defined column by column (oracle.fp8_linear_per_channel): every kernel family must give, for
+# channel n, what the reference gives for that column alone with w_scale = scales[n].
+PER_CHANNEL = [(1, 1024, 2048, False, B.VARIANT_AUTO),        # single-launch cluster kernel
+               (4, 2048, 128 * 120, False, B.VARIANT_AUTO),   # persistent kernel, K chunks added from tensor memory
+               (16, 4096, 4096, True, B.VARIANT_AUTO),        # persistent kernel + reduce pass, [N,K] weights
+               (48, 1024, 1024, False, B.VARIANT_AUTO),       # 64-wide swapped tiles
+               (300, 512, 640, False, B.VARIANT_AUTO),        # CTA pairs
+               (3, 96, 80, False, B.VARIANT_SIMT), (4, 256, 384, False, B.VARIANT_SKINNY), (2, 1024, 1024, False, B.VARIANT_STREAM)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,k,n,trans_b,variant", PER_CHANNEL)
+def test_per_channel_weight_scales(cuda, dtype, m, k, n, trans_b, variant):
+    case = util.make_fp8_linear(dtype, m, k, n, seed=m * 3 + n, trans_b=trans_b, pow2=True, out_headroom=4.0)
+    rng = np.random.default_rng(n + k)
+    scales = (case["sw"] * np.exp2(rng.integers(-1, 3, n))).astype(np.float32)  # four powers of two around the tensor's scale
+    op = B.OP_GEMM if trans_b else B.OP_MATMUL
+    want = O.fp8_linear_per_channel(op, dtype, case["a"], case["sa"], case["w"], scales, case["so"], trans_b=trans_b)
+    got = run_fp8_linear(cuda, dtype, op, case, trans_b=trans_b, variant=variant, w_channel_scales=scales)
+    assert B.device_status() == 0
+    dist = util.fp8_code_distance(got, want)
+    if dist.max() > 1:  # near zero: within the FP32 accumulation bound of the oracle's value
+        a = np.abs(O.fp8_decode(dtype, case["a"]).astype(np.float64)) * case["sa"]
+        w = np.abs(O.fp8_decode(dtype, case["w"]).astype(np.float64))
+        w = (w.T if trans_b else w) * scales.astype(np.float64)[None, :]
+        err = np.abs(O.fp8_decode(dtype, got).astype(np.float64) - O.fp8_decode(dtype, want).astype(np.float64)) * case["so"]
+        dist = np.where((dist > 1) & (err <= (a @ w) * 2.0 ** -20), 1, dist)
+    assert dist.max() <= 1, f"per-channel scales {m}x{k}x{n}: max code distance {dist.max()}"
+    # and the scales are really applied per channel: the per-tensor result differs
+    plain = run_fp8_linear(cuda, dtype, op, case, trans_b=trans_b, variant=variant)
+    assert not np.array_equal(plain, got)

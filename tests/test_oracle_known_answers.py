@@ -112,3 +112,21 @@ def test_conv_known_answer_and_padding():
                 t = acc / 4096.0
                 want = int(np.clip(np.sign(t) * np.floor(abs(t) + 0.5), -128, 127))
                 assert out[0, o, y, z] == want
+
+
+def test_fp8_per_channel_weight_scales_are_the_per_tensor_kernel_column_by_column():
+    """The per-channel extension has no reference kernel (include/util/types.h:96-101 keeps FP8 per-tensor); its
+    definition is the reference's kernel applied to each column with that column's scale — on both implementations."""
+    from tests import util
+    case = util.make_fp8_linear(O.E4M3, 3, 256, 96, seed=7, pow2=True)
+    same = np.full(96, case["sw"], np.float32)
+    plain = O.fp8_linear(O.OP_MATMUL, O.E4M3, case["a"], case["sa"], case["w"], case["sw"], case["so"])
+    assert np.array_equal(O.fp8_linear_per_channel(O.OP_MATMUL, O.E4M3, case["a"], case["sa"], case["w"], same, case["so"]), plain)
+    scales = (case["sw"] * np.exp2(np.arange(96) % 4 - 1)).astype(np.float32)
+    port = O.fp8_linear_per_channel(O.OP_MATMUL, O.E4M3, case["a"], case["sa"], case["w"], scales, case["so"])
+    ref = O.fp8_linear_per_channel(O.OP_MATMUL, O.E4M3, case["a"], case["sa"], case["w"], scales, case["so"], impl="ref")
+    assert np.array_equal(port, ref)
+    for n in (0, 1, 2, 3, 95):
+        col = O.fp8_linear(O.OP_MATMUL, O.E4M3, case["a"], case["sa"], np.ascontiguousarray(case["w"][:, n:n + 1]), float(scales[n]), case["so"])
+        assert np.array_equal(port[:, n:n + 1], col)
+    assert not np.array_equal(port, plain)
