@@ -20,11 +20,13 @@
 #include <vector>
 
 #include <cuda_runtime.h>
+#include <unistd.h>
 
 #include "core/execution_plan.h"
 #include "core/kernel.h"
 #include "core/static_graph.h"
 #include "core/tensor.h"
+#include "model/model_io.h"
 #include "b200_shard.h"
 #include "fth_b200.h"
 #include "pass/graph_pass.h"
@@ -202,6 +204,43 @@ static void RunSelect() {
         c.w->set_quantization(PerChannel(0, std::vector<float>(512, 0.03125f)));
         auto wrong_axis = Select(DeviceType::CUDA, DataType::FP8E4M3, "MatMul", &c.param);
         CHECK_THAT(!(wrong_axis && IsB200Kernel(wrong_axis.get())), "FP8 MatMul with scales along K: the b200 candidate declines");
+
+        // The model file needs no new field for it: the reference's own writer and loader carry the vector (as its test
+        // test/model_io_quantization_test.cc:27-78 shows for INT8), and the weight read back selects the b200 candidate.
+        c.w->set_quantization(PerChannel(1, scales));
+        model::ModelDesc file;
+        file.name = "fp8_per_channel"; file.version = 1; file.graph.name = "main";
+        file.graph.inputs = {"x"}; file.graph.outputs = {"y"};
+        model::ValueDesc x, w, y;
+        x.tensor.name = "x"; x.tensor.dims = {2, 512}; x.tensor.data_type = DataType::FP8E4M3; x.tensor.quantization = c.a->quantization();
+        w.tensor.name = "w"; w.tensor.dims = {512, 384}; w.tensor.data_type = DataType::FP8E4M3; w.tensor.quantization = PerChannel(1, scales);
+        w.constant = true;
+        y.tensor.name = "y"; y.tensor.dims = {2, 384}; y.tensor.data_type = DataType::FP8E4M3; y.tensor.quantization = c.out->quantization();
+        model::NodeDesc node;
+        node.name = "projection"; node.op_type = "MatMul"; node.inputs = {"x", "w"}; node.outputs = {"y"};
+        file.graph.values = {x, w, y};
+        file.graph.nodes = {node};
+        const std::string path = "/tmp/fth_b200_fp8_per_channel_" + std::to_string(static_cast<long long>(getpid())) + ".fth";
+        model::ModelLoader loader;
+        const bool saved = model::ModelWriter().Save(path, file, {{"w", c.w}}) && loader.Load(path);
+        bool carried = false, selected = false;
+        if (saved) {
+            const QuantizationParams& q = loader.model().graph.values[1].tensor.quantization;
+            carried = q.enabled && q.granularity == QuantizationGranularity::kPerChannel && q.axis == 1 && q.scales == scales;
+            auto loaded = loader.CreateWeightTensor("w");
+            if (loaded) {
+                // the weight view takes the value's metadata itself (src/model/weight_store.cc: CreateTensorView)
+                carried = carried && loaded->quantization().granularity == QuantizationGranularity::kPerChannel && loaded->quantization().scales == scales;
+                loaded->set_immutable(true);
+                carried = carried && std::memcmp(loaded->raw_data(), c.w->raw_data(), 512 * 384) == 0;
+                operators::MatMulParam from_file = c.param;
+                from_file.b = loaded;
+                auto kf = Select(DeviceType::CUDA, DataType::FP8E4M3, "MatMul", &from_file);
+                selected = kf && IsB200Kernel(kf.get());
+            }
+        }
+        std::remove(path.c_str());
+        CHECK_THAT(saved && carried && selected, "a .fth file written and read by the reference carries the per-channel FP8 scales; the loaded weight selects the b200 candidate");
     }
     // a request the new backend declines moves on to the reference's CUDA candidate, never to a CPU kernel
     {
