@@ -45,6 +45,27 @@ def test_fp8_plan_matches_device_call(cuda, m, k, n):
         pinned_out.zero_()
         plan.run(pinned_in, pinned_out)
         assert np.array_equal(pinned_out.numpy(), want)
+    # Decode-sized plans replay a recorded step for the pair of page-locked buffers of the last call: other data in the
+    # same buffers must be read afresh, another pair of buffers must be recorded again, and a mixed pair too.
+    a2 = rng.integers(0, 0x78, (m, k), dtype=np.uint8)
+    a_dev.copy_(torch.from_numpy(a2).cuda())
+    B.fp8_linear(d)
+    torch.cuda.synchronize()
+    want2 = out_dev.cpu().numpy()
+    assert not np.array_equal(want, want2)
+    pinned_in.copy_(torch.from_numpy(a2))
+    pinned_out.zero_()
+    plan.run(pinned_in, pinned_out)
+    assert np.array_equal(pinned_out.numpy(), want2)
+    other_in = torch.from_numpy(a).pin_memory()
+    other_out = torch.zeros((m, n), dtype=torch.uint8).pin_memory()
+    plan.run(other_in, other_out)
+    assert np.array_equal(other_out.numpy(), want)
+    other_out.zero_()
+    plan.run(pinned_in, other_out)
+    assert np.array_equal(other_out.numpy(), want2)
+    plan.run(a, pageable)  # and pageable memory still goes through the copy engine
+    assert np.array_equal(pageable, want)
     plan.close()
     assert B.device_status() == 0
     del ws
