@@ -58,9 +58,10 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     TouchConstantLines(p);
     if constexpr (INT8) TouchConstantLines(ie);
     else TouchConstantLines(fe);
-    // Everything above (barriers, tensor memory, parameters) overlapped the tail of the previous kernel in the stream;
-    // the operands may be that kernel's output, so nothing is read before it has completed.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Everything above (barriers, tensor memory, parameters) overlapped the tail of the previous kernel in the stream.
+    // The activations may be that kernel's output and the output buffer may be its input: the producer thread and the
+    // epilogue warps wait for it (griddepcontrol.wait, below) before they read the one or write the other.  The MMA
+    // thread touches shared and tensor memory only.
 
     // unit → (p tile, q tile, K chunk).  [K,N] weights walk the column tiles fastest (chunk-major): the CTAs running
     // together then read whole contiguous weight rows of one K range, which keeps DRAM pages open; with [N,K]
@@ -95,29 +96,45 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         if (lane == 0) {
             TmaPrefetchDescriptor(&map_p);
             TmaPrefetchDescriptor(&map_q);
-            int stage = 0;
-            uint32_t phase = 0;
+            // Weights that nothing earlier in the stream writes are fetched before the dependency wait — one ring-full per
+            // CTA (the first pass over the ring finds every stage free): the weight half of each stage first, the activation
+            // half behind the wait.  A step that follows a short kernel (the activation coming in from the host, a norm in
+            // front of an lm-head) then starts with its pipeline full.
+            // pass 0: the weight tiles of the first `early` K blocks; pass 1: everything else, in the same order
             bool failed = false;
-            for (int64_t u = blockIdx.x; u < p.units && !failed; u += gridDim.x) {
-                int64_t pt, qt; int s0;
-                decode_unit(u, &pt, &qt, &s0);
-                for (int s = s0; s < s0 + chunks_per_unit && !failed; ++s) {
-                const int64_t nb = blocks_of(s);
-                for (int64_t kb = 0; kb < nb; ++kb) {
-                    if (!MbarWait(&empty[stage], phase ^ 1u, p.status, 10, stage)) { failed = true; break; }
-                    const int32_t k0 = static_cast<int32_t>((static_cast<int64_t>(s) * p.chunk_blocks + kb) * kBlockK);
-                    const int32_t p0 = static_cast<int32_t>(pt * kBlockP);
-                    const int32_t q0 = static_cast<int32_t>(qt * BQ);
-                    uint8_t* ps = ring + static_cast<size_t>(stage) * C::kStageBytes;
-                    uint8_t* qs = ps + kPBytes;
-                    MbarExpectTx(&full[stage], C::kStageBytes);
-                    if constexpr (P_MN) TmaLoad2D(ps, &map_p, p0, k0, &full[stage]);
-                    else TmaLoad2D(ps, &map_p, k0, p0, &full[stage]);
-                    TmaLoad2D(qs, &map_q, k0, q0, &full[stage]);
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+            auto produce = [&](int pass, int early) {
+                int stage = 0;
+                uint32_t phase = 0;
+                int count = 0;
+                for (int64_t u = blockIdx.x; u < p.units && !failed; u += gridDim.x) {
+                    int64_t pt, qt; int s0;
+                    decode_unit(u, &pt, &qt, &s0);
+                    for (int s = s0; s < s0 + chunks_per_unit && !failed; ++s) {
+                        const int64_t nb = blocks_of(s);
+                        for (int64_t kb = 0; kb < nb; ++kb, ++count) {
+                            const bool fetched_early = count < early;
+                            if (pass == 0 && !fetched_early) return;
+                            if (!fetched_early && !MbarWait(&empty[stage], phase ^ 1u, p.status, 10, stage)) { failed = true; break; }
+                            const int32_t k0 = static_cast<int32_t>((static_cast<int64_t>(s) * p.chunk_blocks + kb) * kBlockK);
+                            const int32_t p0 = static_cast<int32_t>(pt * kBlockP);
+                            const int32_t q0 = static_cast<int32_t>(qt * BQ);
+                            uint8_t* ps = ring + static_cast<size_t>(stage) * C::kStageBytes;
+                            uint8_t* qs = ps + kPBytes;
+                            if (pass == 0 || !fetched_early) {
+                                MbarExpectTx(&full[stage], C::kStageBytes);  // both halves; the stage completes with the second
+                                if constexpr (P_MN) TmaLoad2D(ps, &map_p, p0, k0, &full[stage]);
+                                else TmaLoad2D(ps, &map_p, k0, p0, &full[stage]);
+                            }
+                            if (pass == 1) TmaLoad2D(qs, &map_q, k0, q0, &full[stage]);
+                            if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                        }
+                    }
                 }
-                }
-            }
+            };
+            const int early = p.args.w_static ? C::kStages : 0;
+            if (early > 0) produce(0, early);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            produce(1, early);
         }
     } else if (warp == 1) {
         // ================================ MMA issuer ================================
@@ -157,6 +174,7 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         }
     } else {
         // ================================ epilogue ================================
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // the output buffer (and the scratch) may still be read by the kernel in front
         const int et = threadIdx.x - 64;            // 0 .. kEpilogueThreads-1
         const int lane_group = warp & 3;            // TMEM lanes 32*lane_group .. +31 belong to this warp
         const int row = lane_group * 32 + lane;     // row inside the P tile
