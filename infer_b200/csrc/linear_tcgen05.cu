@@ -86,7 +86,7 @@ TcGeometry GeometryFor(const LinearArgs& a) {
 // M <= 32 on the persistent kernel: whether every CTA runs whole tiles (all K chunks, one accumulator in tensor memory
 // each) and adds the chunks itself, in the reduce pass's order — one launch, no partial sums in memory, the same bits.
 // A CTA then streams 128 weight columns alone, at ~45 GB/s: that needs about a hundred CTAs at work to keep HBM busy, in
-// the last round of tiles too.  Measured, FP8, one GPU, M = 1 (M = 16), folded against GEMV + reduce pass, us:
+// the last wave of tiles too.  Measured, FP8, one GPU, M = 1 (M = 16), folded against GEMV + reduce pass, us:
 //   K = 8192:  64 tiles 22.8 / 17.3;  96: 23.7 / 22.8;  112: 24.0 / 25.9;  224: 40.0 / 43.1 (41.8 / 47.4);
 //              296: 51.2 / 55.9 (53.5 / 61.3);  300: 64.9 / 58.0;  330: 66.7 / 61.5;  400: 71.9 / 75.3;  600: 108.7 / 108.5
 //   K = 4096:  1187 tiles, M = 16: 108.4 / 130.5
@@ -94,9 +94,9 @@ bool FoldsSplit(const TcGeometry& g, int64_t m) {
     if (!g.swap || g.cluster != 0 || g.split <= 1 || g.bq > 32) return false;
     const int64_t tiles = g.p_tiles * g.q_tiles, slots = static_cast<int64_t>(SmCount()) * 2, busy = slots / 3;
     if (tiles < busy) return false;
-    const int64_t last_round = tiles % slots;
-    if (tiles <= slots || last_round == 0 || last_round >= busy) return true;
-    return tiles >= 4 * slots && m > 4;  // many rounds, and partial sums that would weigh as much as the weights' tail
+    const int64_t last_wave = tiles % slots;
+    if (tiles <= slots || last_wave == 0 || last_wave >= busy) return true;
+    return tiles >= 4 * slots && m > 4;  // many waves, and partial sums that would weigh as much as the weights' tail
 }
 
 // Encoding a tensor map costs a few microseconds of host time; decode steps call the same (pointer, shape)
@@ -280,7 +280,7 @@ int LaunchLinearTcgen05(int dtype, const LinearArgs& a_in, const Fp8Epilogue& fe
         // CTA pairs: each CTA stages 128 activation rows and 128 weight columns of a 256 x 256 tile
         CUtensorMap map_w_half = map_w;
         if (!weights_mn && !CachedMap(&map_w_half, a.w, static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), 128, 128)) return FTH_B200_ERR_CUDA;
-        // (Narrower tiles, 224 .. 128 columns, would fill the last round of tiles better at M = 256 .. 1024; measured, they
+        // (Narrower tiles, 224 .. 128 columns, would fill the last wave of tiles better at M = 256 .. 1024; measured, they
         // are slower per column by more than that gains: K = 8192, N = 28672, FP8, M = 256: 63.8 us at 256 columns, 68.1 at
         // 224, 80.7 at 192; M = 4096: 645 / 850 / 824 us.)
         p.idesc = umma::InstrDesc(int8 ? 2u : 1u, fmt, fmt, false, q_mn, 256, 256);
