@@ -109,7 +109,9 @@ typedef struct {
     /* Device scratch (256-byte aligned) of the kernel family `variant` selects: split-K partial sums and, for a fused
      * Cast / QuantizeLinear that runs as a separate pass, the 8-bit activations.  fth_b200_fp8_linear_workspace_bytes
      * says how much that family needs for this descriptor — 0 for shapes the single-launch cluster kernel and the dense
-     * kernel take.  It must be zero-filled once after allocation (VARIANT_STREAM keeps arrival counters in it and leaves
+     * kernel take.  The figure is an upper bound over the entry points that take the descriptor: a decode-sized call with
+     * a wide weight adds its K chunks in tensor memory and leaves the scratch untouched, the lm-head call with the same
+     * descriptor still uses it.  It must be zero-filled once after allocation (VARIANT_STREAM keeps arrival counters in it and leaves
      * them zero again).  Calls that share a workspace must not overlap on the GPU.  May be null: the library then picks
      * kernels that need no scratch. */
     void* workspace;
