@@ -281,7 +281,8 @@ LinearTcgen05Kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             if constexpr (BQ <= 32) {
                 if (p.fold && !failed) {
                     // four activation rows at a time: the chunks' partial accumulators, all loads in flight before the
-                    // first add, then summed in chunk order (FP32: never a zero that could flip the sign of -0)
+                    // first add, then summed in chunk order starting from +0, exactly as the reduce pass does (chunks
+                    // beyond the split are skipped, not added as zeros)
 #pragma unroll 1
                     for (int c0 = 0; c0 < q_count; c0 += 4) {
                         uint32_t t[8][4];
