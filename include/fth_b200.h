@@ -397,8 +397,8 @@ int fth_b200_silu_mul(int32_t dtype, const void* gate, const void* up, void* out
  * synchronises — never call it during capture); run() copies the activation from host memory, launches,
  * and copies the result back, all on `stream`, then waits for the stream.  A decode-sized linear plan (M <= 32) whose
  * two host buffers are page-locked needs no copy-engine transfer: a small kernel reads the activation from the host
- * buffer and the linear kernel stores its output there as well; the two launches are recorded on the first run() for a
- * pair of host buffers and replayed with one graph launch afterwards (another pair of buffers records again).  A plan is
+ * buffer and the linear kernel stores its output there as well; after the plan's first run() the two launches are
+ * recorded for the pair of host buffers in use and replayed with one graph launch (another pair of buffers records again).  A plan is
  * used by one thread at a time, and `stream` must not be capturing.
  * ------------------------------------------------------------------------------------------------- */
 typedef struct fth_b200_plan fth_b200_plan;

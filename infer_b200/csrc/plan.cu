@@ -95,6 +95,7 @@ struct fth_b200_plan {
     const void* step_in{nullptr};
     void* step_out{nullptr};
     bool step_graph_failed{false};
+    int direct_steps{0};  // steps launched kernel by kernel so far (the first one always is)
     ~fth_b200_plan() {
         if (step_exec) cudaGraphExecDestroy(step_exec);
         if (capture_stream) cudaStreamDestroy(capture_stream);
@@ -323,7 +324,9 @@ extern "C" int fth_b200_plan_run(fth_b200_plan* p, const void* host_in, void* ho
     // asked on every call: an address that was page-locked last time may belong to a pageable buffer now
     void* in_view = direct ? DeviceViewOfHost(host_in) : nullptr;
     void* out_view = direct ? DeviceViewOfHost(host_out) : nullptr;
-    if (in_view != nullptr && out_view != nullptr && !p->step_graph_failed) {
+    // (the plan's first step is launched directly: what the library looks up once per device — the status word's address,
+    // the kernels' shared-memory opt-in — must not happen inside a capture)
+    if (in_view != nullptr && out_view != nullptr && !p->step_graph_failed && p->direct_steps > 0) {
         if (p->step_exec == nullptr || p->step_in != in_view || p->step_out != out_view) CaptureStep(p, in_view, out_view);
         if (p->step_exec != nullptr) {
             if (cudaGraphLaunch(p->step_exec, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
@@ -340,6 +343,7 @@ extern "C" int fth_b200_plan_run(fth_b200_plan* p, const void* host_in, void* ho
     if (out_view == nullptr &&
         cudaMemcpyAsync(host_out, p->out.ptr, static_cast<size_t>(p->out_bytes), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
     if (cudaStreamSynchronize(stream) != cudaSuccess) return FTH_B200_ERR_CUDA;
+    if (p->direct_steps < 1) p->direct_steps = 1;
     return FTH_B200_OK;
 }
 
